@@ -1,0 +1,74 @@
+// Argument blocks and host launchers shared between the kernels' translation units and api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include "layout.cuh"
+
+namespace dq {
+
+struct QuantArgs {
+  ActGeom g;
+  const __nv_bfloat16* x;
+  int64_t x_pitch;
+  const int64_t* perm;
+  int64_t M;
+  int64_t ldm;
+  uint8_t* codes;
+  __nv_bfloat16* scales;   // INT / NVFP4_REF
+  uint8_t* sf;             // NVFP4_HW tiled bytes
+  __nv_bfloat16* zeros;
+  __nv_bfloat16* tail;
+};
+
+struct PackIntArgs {
+  const float* w;       // [N, n_low]
+  int64_t N;
+  int64_t n_low;
+  int group;
+  int n_groups;
+  int cpg;
+  int n_chunks;
+  const float* scale_in;  // [N, n_groups] or null
+  int w_is_codes;
+  uint8_t* codes;       // [N, n_chunks*32]
+  float* scales;        // [n_chunks, ldn]
+  float* wsum;          // [n_chunks, ldn]
+  int64_t ldn;
+};
+
+struct PackFp4Args {
+  const float* w;
+  int64_t N;
+  int64_t n_low;
+  int n_chunks;
+  float T;
+  const uint8_t* scale_in;  // [N, ceil(n_low/16)] e4m3 bytes or null
+  int w_is_codes;
+  uint8_t* codes;           // [N, n_chunks*32]
+  uint8_t* sf;              // tiled
+};
+
+struct RotArgs {
+  ActGeom g;
+  int64_t M;
+  int64_t ldm;
+  int BN;
+  int n_tiles;
+  int m_tiles;
+  int band;               // 0 = dense rotation, else head_dim of a block-diagonal rotation
+  __nv_bfloat16* x_rot;   // optional [M, D]
+  uint8_t* codes;
+  __nv_bfloat16* scales;
+  uint8_t* sf;
+  __nv_bfloat16* zeros;
+  __nv_bfloat16* tail;
+  int* status;
+};
+
+int launch_quantize(const QuantArgs& a, cudaStream_t st);
+int launch_pack_int4(const PackIntArgs& a, cudaStream_t st);
+int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st);
+int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, int64_t M, RotArgs a, cudaStream_t st);
+int num_sms();
+
+}  // namespace dq

@@ -1,0 +1,139 @@
+// Kernel 3: weight quantiser + packer (offline, bandwidth-bound).  Arithmetic follows
+// _quant_group_int / _quant_group_nvfp4 (DiRotQ utils/quant_utils.py:714-767) in fp32 and the
+// two-level NVFP4 recipe of speedup/weight_only_nvfp4.py:42-72; the byte layouts are the
+// tensor-core-friendly ones declared in include/dirotq_b200.h (K-major rows, 64-slot chunks,
+// group-major scale planes, 512-byte scale-factor tiles), not an mma.sync fragment order.
+#include <cuda_runtime.h>
+#include "layout.cuh"
+#include "launchers.cuh"
+#include "quant_math.cuh"
+
+namespace dq {
+
+
+// One thread = one block of 32 code slots of one output row (same slot layout as activations).
+__global__ void __launch_bounds__(256) pack_int4_kernel(const PackIntArgs a) {
+  const int bpr = a.n_chunks * 2;
+  const int64_t total = a.N * bpr;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = tid < total;
+  const int64_t t = live ? tid : total - 1;
+  const int64_t n = t / bpr;
+  const int b = (int)(t - n * bpr);
+  const int chunk = b >> 1, half = b & 1;
+  const int grp = chunk / a.cpg;
+  const int e0 = (chunk % a.cpg) * 64 + half * 32;
+  const int glen = (int)min((int64_t)a.group, a.n_low - (int64_t)grp * a.group);
+  const int nvalid = max(0, min(32, glen - e0));
+  const float* wr = a.w + n * a.n_low + (int64_t)grp * a.group + e0;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = (j < nvalid) ? __ldg(wr + j) : 0.f;
+  float scale;
+  if (a.scale_in) {
+    scale = a.scale_in[n * a.n_groups + grp];
+  } else {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    for (int o = 1; o < 2 * a.cpg; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    scale = __fdiv_rn(fmaxf(amax, 1e-5f), 7.f);
+  }
+  int q[32];
+  int sum = 0;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    int c = 0;
+    if (j < nvalid) {
+      float r = a.w_is_codes ? v[j] : rintf(__fdiv_rn(v[j], scale));
+      c = (int)fminf(fmaxf(r, -8.f), 7.f);
+    }
+    q[j] = c;
+    sum += c;
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);   // both halves of the chunk
+  if (!live) return;
+  uint32_t w4[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t x = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t byte = ((uint32_t)q[4 * i + j] & 0xF) | (((uint32_t)q[16 + 4 * i + j] & 0xF) << 4);
+      x |= byte << (8 * j);
+    }
+    w4[i] = x;
+  }
+  *reinterpret_cast<uint4*>(a.codes + n * (int64_t)(a.n_chunks * 32) + (int64_t)b * 16) =
+      make_uint4(w4[0], w4[1], w4[2], w4[3]);
+  if (half == 0) {
+    a.scales[(int64_t)chunk * a.ldn + n] = scale;
+    a.wsum[(int64_t)chunk * a.ldn + n] = (float)sum;
+  }
+}
+
+
+// One thread = one 64-slot chunk (4 groups of 16) of one output row.
+__global__ void __launch_bounds__(256) pack_nvfp4_kernel(const PackFp4Args a) {
+  const int64_t total = a.N * a.n_chunks;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= total) return;
+  const int64_t n = tid / a.n_chunks;
+  const int chunk = (int)(tid - n * a.n_chunks);
+  const int n_kb64_pad = (a.n_chunks + 3) & ~3;
+  const int ngrp_row = (int)((a.n_low + 15) / 16);
+  uint32_t packed[8];
+  uint32_t sfw = 0;
+#pragma unroll
+  for (int gi = 0; gi < 4; ++gi) {
+    const int64_t cg = (int64_t)chunk * 64 + gi * 16;
+    const int nvalid = (int)max((int64_t)0, min((int64_t)16, a.n_low - cg));
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = (j < nvalid) ? __ldg(a.w + n * a.n_low + cg + j) : 0.f;
+    uint8_t sb = 0;
+    float eff = 0.f;
+    if (nvalid > 0) {
+      if (a.scale_in) {
+        sb = a.scale_in[n * ngrp_row + chunk * 4 + gi];
+        eff = __fmul_rn(e4m3_to_float(sb), a.T);
+      } else {
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        sb = nvfp4_hw_scale(amax, 1.f, a.T, &eff);
+      }
+    }
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t c0 = 0, c1 = 0;
+      if (j < nvalid) c0 = a.w_is_codes ? ((uint32_t)v[j] & 0xF) : nvfp4_hw_code(v[j], eff);
+      if (8 + j < nvalid) c1 = a.w_is_codes ? ((uint32_t)v[8 + j] & 0xF) : nvfp4_hw_code(v[8 + j], eff);
+      lo |= c0 << (4 * j);
+      hi |= c1 << (4 * j);
+    }
+    packed[gi * 2] = lo;
+    packed[gi * 2 + 1] = hi;
+    sfw |= (uint32_t)sb << (8 * gi);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(a.codes + n * (int64_t)(a.n_chunks * 32) + (int64_t)chunk * 32);
+  dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+  *reinterpret_cast<uint32_t*>(a.sf + sf_offset(n, chunk * 4, n_kb64_pad)) = sfw;
+}
+
+int launch_pack_int4(const PackIntArgs& a, cudaStream_t st) {
+  int64_t total = a.N * a.n_chunks * 2;
+  if (total <= 0) return DIROTQ_OK;
+  pack_int4_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st) {
+  int64_t total = a.N * a.n_chunks;
+  if (total <= 0) return DIROTQ_OK;
+  pack_nvfp4_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+}  // namespace dq

@@ -1,0 +1,115 @@
+// Activation-quantiser arithmetic, one operation at a time with explicit rounding, so that codes,
+// scales and zero points are bit-identical to what torch computes for the reference expressions
+// (DiRotQ utils/quant_utils.py:63-85, :148-180, :201-216) on a bf16 (or fp32) tensor.
+// No fused multiply-add, no reciprocal tricks: every step is an IEEE round-to-nearest operation
+// followed, in bf16 mode, by a round to bf16 -- exactly the sequence of eager tensor ops.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+
+namespace dq {
+
+enum QuantMode : int {
+  MODE_INT4_SYM = 0,   // codes in [-8, 7]
+  MODE_INT4_ASYM = 1,  // codes in [0, 15] + zero point
+  MODE_INT8_ASYM = 2,  // codes in [0, 255] + zero point (W4A8)
+  MODE_NVFP4_REF = 3,  // E2M1 codes, bf16 group scale exactly as the reference (not GEMM-consumable)
+  MODE_NVFP4_HW = 4,   // E2M1 codes, UE4M3 group scale relative to an fp32 tensor scale
+};
+
+template <bool BF16>
+__device__ __forceinline__ float rnd(float v) {
+  if constexpr (BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return v;
+}
+
+struct GroupParams {
+  float scale;
+  float zero;
+};
+
+// quant_utils.py:202-209 (symmetric branch).  mx/mn: max and min over the group.
+template <bool BF16>
+__device__ __forceinline__ GroupParams int_sym_params(float mx, float mn, float clip, float maxq) {
+  float xmax = rnd<BF16>(__fmul_rn(mx, clip));
+  float xmin = rnd<BF16>(__fmul_rn(mn, clip));
+  float a = fmaxf(fabsf(xmin), xmax);
+  GroupParams p;
+  p.scale = (a == 0.f) ? 1.f : rnd<BF16>(__fdiv_rn(a, maxq));
+  p.zero = 0.f;
+  return p;
+}
+// quant_utils.py:67
+template <bool BF16>
+__device__ __forceinline__ int int_sym_code(float x, float scale, float maxq) {
+  float q = rintf(rnd<BF16>(__fdiv_rn(x, scale)));
+  q = fminf(fmaxf(q, -maxq - 1.f), maxq);
+  return (int)q;
+}
+// quant_utils.py:211-215
+template <bool BF16>
+__device__ __forceinline__ GroupParams int_asym_params(float mx, float mn, float clip, float maxq) {
+  float xmax = rnd<BF16>(__fmul_rn(mx, clip));
+  float xmin = rnd<BF16>(__fmul_rn(mn, clip));
+  if (xmin == 0.f && xmax == 0.f) { xmin = -1.f; xmax = 1.f; }
+  float d = rnd<BF16>(__fsub_rn(xmax, xmin));
+  d = fmaxf(d, rnd<BF16>(1e-5f));
+  GroupParams p;
+  p.scale = rnd<BF16>(__fdiv_rn(d, maxq));
+  p.zero = rnd<BF16>(rintf(rnd<BF16>(__fdiv_rn(-xmin, p.scale))));
+  return p;
+}
+// quant_utils.py:80
+template <bool BF16>
+__device__ __forceinline__ int int_asym_code(float x, float scale, float zero, float maxq) {
+  float q = rnd<BF16>(__fadd_rn(rintf(rnd<BF16>(__fdiv_rn(x, scale))), zero));
+  q = fminf(fmaxf(q, 0.f), maxq);
+  return (int)q;
+}
+
+// E2M1 nibble of a normalised value with the reference's bucketize rule (quant_utils.py:30-35):
+// an exact midpoint goes to the LOWER codebook value (toward -inf); there is no negative zero.
+__device__ __forceinline__ uint32_t e2m1_nibble(float v) {
+  float a = fabsf(v);
+  uint32_t m;
+  if (v >= 0.f) {
+    m = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.f);
+    return m;
+  }
+  m = (a >= 0.25f) + (a >= 0.75f) + (a >= 1.25f) + (a >= 1.75f) + (a >= 2.5f) + (a >= 3.5f) + (a >= 5.f);
+  return m ? (8u | m) : 0u;
+}
+
+// quant_utils.py:172-173
+template <bool BF16>
+__device__ __forceinline__ float nvfp4_ref_scale(float amax, float clip) {
+  float s = rnd<BF16>(__fmul_rn(amax, clip));
+  s = rnd<BF16>(__fdiv_rn(s, 6.f));
+  return fmaxf(s, rnd<BF16>(1e-5f));
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t nvfp4_ref_code(float x, float scale) {
+  return e2m1_nibble(rnd<BF16>(__fdiv_rn(x, scale)));
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+  return __half2float(__half(h));
+}
+// Two-level scale: micro = e4m3_rn(clamp(amax*clip/6/T, 2^-9, 448)), 0 for an all-zero group.
+// Returns the e4m3 byte and the effective fp32 scale micro*T.
+__device__ __forceinline__ uint8_t nvfp4_hw_scale(float amax, float clip, float T, float* eff) {
+  if (amax == 0.f) { *eff = 0.f; return 0; }
+  float s = __fdiv_rn(__fmul_rn(amax, clip), 6.f);
+  float r = fmaxf(__fdiv_rn(s, T), 0.001953125f);
+  r = fminf(r, 448.f);
+  uint8_t b = (uint8_t)__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+  *eff = __fmul_rn(e4m3_to_float(b), T);
+  return b;
+}
+__device__ __forceinline__ uint32_t nvfp4_hw_code(float x, float eff) {
+  return eff > 0.f ? e2m1_nibble(__fdiv_rn(x, eff)) : 0u;
+}
+
+}  // namespace dq

@@ -1,0 +1,227 @@
+// Kernel 1a: split + quantise of an already rotated / permuted activation tensor.  HBM-bound:
+// every input element is read once (16-byte loads where alignment allows), group extrema are
+// combined with warp shuffles, and codes leave as packed 16/32-byte stores.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include "layout.cuh"
+#include "launchers.cuh"
+#include "quant_math.cuh"
+
+namespace dq {
+
+
+// Source column of element e of group grp.
+__device__ __forceinline__ int src_col(const ActGeom& g, int grp, int e) {
+  return g.H > 0 ? grp * g.d + e : grp * g.group + e;
+}
+
+// One thread = one block of 32 code slots of one row.  The 2*cpg threads that share a group sit
+// on consecutive lanes (aligned), so the group extrema need log2(2*cpg) shuffles.
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
+  const ActGeom& g = a.g;
+  const int bpr = g.n_chunks * 2;                      // 32-slot blocks per row
+  const int64_t total = a.M * bpr;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = tid < total;
+  const int64_t t = live ? tid : total - 1;
+  const int64_t row = t / bpr;
+  const int b = (int)(t - row * bpr);
+  const int chunk = b >> 1, half = b & 1;
+  const int grp = chunk / g.cpg;
+  const int e0 = (chunk % g.cpg) * 64 + half * 32;     // first element of the group this block covers
+  int glen = g.group;
+  if (g.H == 0) glen = min(g.group, g.q_len - grp * g.group);
+  const int nvalid = max(0, min(32, glen - e0));
+  const bool padded = glen < g.group;                  // zero padding takes part in min / max
+
+  float v[32];
+  const __nv_bfloat16* xr = a.x + row * a.x_pitch;
+  const int c0 = src_col(g, grp, e0);
+  const bool vec_ok = (a.perm == nullptr) && ((c0 & 7) == 0) && ((a.x_pitch & 7) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) && (c0 + 32 <= g.D);
+  if (vec_ok) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 q = __ldg(reinterpret_cast<const uint4*>(xr + c0) + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        v[i * 8 + j * 2] = f.x;
+        v[i * 8 + j * 2 + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float f = 0.f;
+      if (j < nvalid) {
+        int64_t c = c0 + j;
+        if (a.perm) c = a.perm[c];
+        f = __bfloat162float(xr[c]);
+      }
+      v[j] = f;
+    }
+  }
+  float mx = -INFINITY, mn = INFINITY;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (j < nvalid) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
+  }
+  if (padded || nvalid == 0) {
+    // an all-padding block of a real group, or zero padding inside the group
+    if (padded) { mx = fmaxf(mx, 0.f); mn = fminf(mn, 0.f); }
+  }
+  const int nb = 2 * g.cpg;
+  for (int o = 1; o < nb; o <<= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  }
+  constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
+  GroupParams p;
+  if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
+  else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+
+  uint32_t q[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    int c = 0;
+    if (j < nvalid) {
+      if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(v[j], p.scale, maxq);
+      else c = int_asym_code<true>(v[j], p.scale, p.zero, maxq);
+    }
+    q[j] = (uint32_t)c;
+  }
+  if (!live) return;
+  if constexpr (MODE == MODE_INT8_ASYM) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      w[i] = (q[4 * i] & 0xFF) | ((q[4 * i + 1] & 0xFF) << 8) | ((q[4 * i + 2] & 0xFF) << 16) | ((q[4 * i + 3] & 0xFF) << 24);
+    uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 32);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t x = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t byte = (q[4 * i + j] & 0xF) | ((q[16 + 4 * i + j] & 0xF) << 4);
+        x |= byte << (8 * j);
+      }
+      w[i] = x;
+    }
+    *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  if (half == 0) {
+    a.scales[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.scale);
+    if constexpr (MODE != MODE_INT4_SYM) a.zeros[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.zero);
+  }
+}
+
+// One thread = one 64-slot chunk (4 groups of 16) of one row; hidden layout only.
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_nvfp4_kernel(const QuantArgs a) {
+  const ActGeom& g = a.g;
+  const int64_t total = a.M * g.n_chunks;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= total) return;
+  const int64_t row = tid / g.n_chunks;
+  const int chunk = (int)(tid - row * g.n_chunks);
+  const __nv_bfloat16* xr = a.x + row * a.x_pitch;
+  const int c0 = chunk * 64;
+  const int n_kb64_pad = (g.n_chunks + 3) & ~3;
+  uint32_t packed[8];
+  uint32_t sfw = 0;
+#pragma unroll
+  for (int gi = 0; gi < 4; ++gi) {
+    float v[16];
+    const int cg = c0 + gi * 16;
+    const int nvalid = max(0, min(16, g.q_len - cg));
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float f = 0.f;
+      if (j < nvalid) {
+        int64_t c = cg + j;
+        if (a.perm) c = a.perm[c];
+        f = __bfloat162float(xr[c]);
+      }
+      v[j] = f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    uint32_t lo = 0, hi = 0;
+    if constexpr (MODE == MODE_NVFP4_REF) {
+      float s = nvfp4_ref_scale<true>(amax, g.clip);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lo |= (j < nvalid ? nvfp4_ref_code<true>(v[j], s) : 0u) << (4 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hi |= (8 + j < nvalid ? nvfp4_ref_code<true>(v[8 + j], s) : 0u) << (4 * j);
+      if (nvalid > 0) a.scales[(int64_t)(chunk * 4 + gi) * a.ldm + row] = __float2bfloat16_rn(s);
+    } else {
+      float eff;
+      uint8_t sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
+      if (nvalid == 0) { sb = 0; eff = 0.f; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lo |= (j < nvalid ? nvfp4_hw_code(v[j], eff) : 0u) << (4 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hi |= (8 + j < nvalid ? nvfp4_hw_code(v[8 + j], eff) : 0u) << (4 * j);
+      sfw |= (uint32_t)sb << (8 * gi);
+    }
+    packed[gi * 2] = lo;
+    packed[gi * 2 + 1] = hi;
+  }
+  uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
+  dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+  if constexpr (MODE == MODE_NVFP4_HW)
+    *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, chunk * 4, n_kb64_pad)) = sfw;
+}
+
+// Passthrough channels -> tail buffer [M, tail_pitch] (pad columns zero).
+__global__ void __launch_bounds__(256) copy_tail_kernel(const QuantArgs a) {
+  const ActGeom& g = a.g;
+  const int64_t total = a.M * g.tail_pitch;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= total) return;
+  const int64_t row = tid / g.tail_pitch;
+  const int t = (int)(tid - row * g.tail_pitch);
+  __nv_bfloat16 val = __float2bfloat16_rn(0.f);
+  if (t < g.tail_total) {
+    int64_t c;
+    if (g.H > 0) { int h = t / g.hlen; c = (int64_t)h * g.d + g.group + (t - h * g.hlen); }
+    else c = g.q_len + t;
+    if (a.perm) c = a.perm[c];
+    val = a.x[row * a.x_pitch + c];
+  }
+  a.tail[tid] = val;
+}
+
+int launch_quantize(const QuantArgs& a, cudaStream_t st) {
+  const ActGeom& g = a.g;
+  if (a.M <= 0) return DIROTQ_OK;
+  const int threads = 256;
+  if (is_nvfp4(g.mode)) {
+    int64_t total = a.M * g.n_chunks;
+    unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (g.mode == DIROTQ_NVFP4_REF) quant_nvfp4_kernel<MODE_NVFP4_REF><<<blocks, threads, 0, st>>>(a);
+    else quant_nvfp4_kernel<MODE_NVFP4_HW><<<blocks, threads, 0, st>>>(a);
+  } else {
+    int64_t total = a.M * g.n_chunks * 2;
+    unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (g.mode == DIROTQ_INT4_SYM) quant_int_kernel<MODE_INT4_SYM><<<blocks, threads, 0, st>>>(a);
+    else if (g.mode == DIROTQ_INT4_ASYM) quant_int_kernel<MODE_INT4_ASYM><<<blocks, threads, 0, st>>>(a);
+    else quant_int_kernel<MODE_INT8_ASYM><<<blocks, threads, 0, st>>>(a);
+  }
+  if (g.tail_total > 0 && a.tail) {
+    int64_t total = a.M * g.tail_pitch;
+    copy_tail_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+}  // namespace dq

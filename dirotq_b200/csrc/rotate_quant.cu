@@ -1,0 +1,606 @@
+// Kernel 1: fused rotate + split + quantise.
+//
+//   x [M, D] bf16  --TMA-->  smem (128-byte swizzle)  --tcgen05.mma kind::f16-->  TMEM fp32
+//   TMEM --tcgen05.ld--> registers: round to bf16 (this IS x_rot of the reference's bf16 path),
+//   split into the quantised region and the passthrough tail, per-group extrema, scale / zero
+//   point, 4-bit (or 8-bit) codes, packed 16-byte stores.  The rotated tensor never touches HBM.
+//
+// Persistent, warp-specialised: warp 0 = TMA producer, warp 1 = UMMA issuer (owns TMEM),
+// warps 2..5 = epilogue (one TMEM lane quarter each).  Two TMEM accumulators of 256 columns let
+// the epilogue of tile i overlap the main loop of tile i+1.  Tiles are 128 rows x BN columns of
+// the rotated tensor; consecutive tiles share the x row-block, so x and the rotation stay in L2.
+//
+// Replaces: `x_flat @ self.rotation` + find_params + quantizer (DiRotQ
+// dirotq_fused_unrotation_fast.py:69-74), the per-head branch (:76-104) and the stand-alone
+// rotation kernels speedup/kernels/{int8,fp8,bf16}_rotation.py.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include "layout.cuh"
+#include "launchers.cuh"
+#include "ptx.cuh"
+#include "quant_math.cuh"
+
+namespace dq {
+
+constexpr int RQ_STAGES = 4;
+constexpr int RQ_A_BYTES = 128 * 128;           // 128 rows x 64 bf16
+constexpr int RQ_B_BYTES = 256 * 128;           // up to 256 rows x 64 bf16
+constexpr int RQ_STAGE_BYTES = RQ_A_BYTES + RQ_B_BYTES;
+constexpr int RQ_THREADS = 192;
+constexpr int RQ_SMEM_BYTES = RQ_STAGES * RQ_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3 };
+
+
+__device__ __forceinline__ void tile_k_range(const RotArgs& a, int nb, int& kb, int& ke) {
+  const int kchunks = (a.g.D + 63) / 64;
+  if (a.band == 0) { kb = 0; ke = kchunks; return; }
+  const int n0 = nb * a.BN;
+  const int n1 = min(n0 + a.BN, a.g.D);
+  const int h0 = n0 / a.band, h1 = (n1 - 1) / a.band;
+  kb = (h0 * a.band) / 64;
+  ke = min(kchunks, ((h1 + 1) * a.band + 63) / 64);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 32 code slots -> 16 bytes; byte j = slot j | slot 16+j << 4
+__device__ __forceinline__ uint4 pack_planar32(const uint32_t* q) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t x = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x |= ((q[4 * i + j] & 0xF) | ((q[16 + 4 * i + j] & 0xF) << 4)) << (8 * j);
+    w[i] = x;
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---- epilogues: thread = one row of the tile; `taddr` already points at this warp's lanes ----
+template <int MODE>
+__device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+  const ActGeom& g = a.g;
+  const bool row_ok = row < a.M;
+  constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
+  for (int c0 = 0; c0 < a.BN; c0 += 64) {
+    const int col = n0 + c0;
+    if (col >= g.D) break;
+    uint32_t r[64];
+    tmem_ld32(taddr + c0, r);
+    tmem_ld32(taddr + c0 + 32, r + 32);
+    tmem_wait_ld();
+    float v[64];
+#pragma unroll
+    for (int j = 0; j < 64; ++j) v[j] = rnd<true>(__uint_as_float(r[j]));
+    if (a.x_rot && row_ok) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (col + 8 * i + 8 <= g.D) {
+          uint4 o = make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                               pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) = o;
+        }
+      }
+    }
+    if (!a.codes) continue;
+    const int nq = max(0, min(64, g.q_len - col));
+    if (nq > 0) {
+      const int chunk = col >> 6;
+      float mx = -INFINITY, mn = INFINITY;
+#pragma unroll
+      for (int j = 0; j < 64; ++j)
+        if (j < nq) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
+      if (nq < 64) { mx = fmaxf(mx, 0.f); mn = fminf(mn, 0.f); }   // zero padding of the last group
+      GroupParams p;
+      if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
+      else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+      uint32_t q[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        int c = 0;
+        if (j < nq) {
+          if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(v[j], p.scale, maxq);
+          else c = int_asym_code<true>(v[j], p.scale, p.zero, maxq);
+        }
+        q[j] = (uint32_t)c;
+      }
+      if (row_ok) {
+        if constexpr (MODE == MODE_INT8_ASYM) {
+          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 64);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t* s = q + 16 * i + 4 * k;
+              w[k] = (s[0] & 0xFF) | ((s[1] & 0xFF) << 8) | ((s[2] & 0xFF) << 16) | ((s[3] & 0xFF) << 24);
+            }
+            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
+          dst[0] = pack_planar32(q);
+          dst[1] = pack_planar32(q + 32);
+        }
+        a.scales[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.scale);
+        if constexpr (MODE != MODE_INT4_SYM) a.zeros[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.zero);
+      }
+    }
+    if (nq < 64 && row_ok && a.tail) {
+      __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
+      const int t0 = col - g.q_len;               // tail index of v[0] (may be negative)
+      if (nq == 0 && (t0 & 7) == 0 && col + 64 <= g.D) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(tr + t0 + 8 * i) =
+              make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                         pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (j >= nq && col + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+  const ActGeom& g = a.g;
+  const bool row_ok = row < a.M;
+  const int n_kb64_pad = (g.n_chunks + 3) & ~3;
+  for (int c0 = 0; c0 < a.BN; c0 += 64) {
+    const int col = n0 + c0;
+    if (col >= g.D) break;
+    uint32_t r[64];
+    tmem_ld32(taddr + c0, r);
+    tmem_ld32(taddr + c0 + 32, r + 32);
+    tmem_wait_ld();
+    float v[64];
+#pragma unroll
+    for (int j = 0; j < 64; ++j) v[j] = rnd<true>(__uint_as_float(r[j]));
+    if (a.x_rot && row_ok) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (col + 8 * i + 8 <= g.D)
+          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) =
+              make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                         pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+    }
+    if (!a.codes) continue;
+    const int nq = max(0, min(64, g.q_len - col));
+    if (nq > 0) {
+      const int chunk = col >> 6;
+      uint32_t packed[8];
+      uint32_t sfw = 0;
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        const int nvalid = max(0, min(16, nq - 16 * gi));
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (j < nvalid) amax = fmaxf(amax, fabsf(v[16 * gi + j]));
+        uint32_t lo = 0, hi = 0;
+        if constexpr (MODE == MODE_NVFP4_REF) {
+          const float s = nvfp4_ref_scale<true>(amax, g.clip);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            lo |= (j < nvalid ? nvfp4_ref_code<true>(v[16 * gi + j], s) : 0u) << (4 * j);
+            hi |= (8 + j < nvalid ? nvfp4_ref_code<true>(v[16 * gi + 8 + j], s) : 0u) << (4 * j);
+          }
+          if (nvalid > 0 && row_ok) a.scales[(int64_t)(chunk * 4 + gi) * a.ldm + row] = __float2bfloat16_rn(s);
+        } else {
+          float eff = 0.f;
+          uint8_t sb = 0;
+          if (nvalid > 0) sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            lo |= (j < nvalid ? nvfp4_hw_code(v[16 * gi + j], eff) : 0u) << (4 * j);
+            hi |= (8 + j < nvalid ? nvfp4_hw_code(v[16 * gi + 8 + j], eff) : 0u) << (4 * j);
+          }
+          sfw |= (uint32_t)sb << (8 * gi);
+        }
+        packed[2 * gi] = lo;
+        packed[2 * gi + 1] = hi;
+      }
+      if (row_ok) {
+        uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        if constexpr (MODE == MODE_NVFP4_HW)
+          *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, chunk * 4, n_kb64_pad)) = sfw;
+      }
+    }
+    if (nq < 64 && row_ok && a.tail) {
+      __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
+      const int t0 = col - g.q_len;
+#pragma unroll
+      for (int j = 0; j < 64; ++j)
+        if (j >= nq && col + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+// 32 columns starting at a column that is only 8-aligned (heads of 72 channels): four
+// naturally aligned 8-column reads, one wait.
+__device__ __forceinline__ void ld32_by8(uint32_t taddr, uint32_t* r) {
+  tmem_ld8(taddr, r);
+  tmem_ld8(taddr + 8, r + 8);
+  tmem_ld8(taddr + 16, r + 16);
+  tmem_ld8(taddr + 24, r + 24);
+  tmem_wait_ld();
+}
+
+// Per-head layout: head h = tile columns [hh*d, hh*d + d): first d_q quantised as ONE group,
+// last hlen passthrough.  Two passes over TMEM (extrema, then codes) keep registers small.
+template <int MODE>
+__device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+  const ActGeom& g = a.g;
+  const bool row_ok = row < a.M;
+  constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
+  const int d = g.d, d_q = g.group;
+  const int nblk = (d_q + 31) >> 5;
+  for (int cb = 0; cb < a.BN; cb += d) {
+    const int h = (n0 + cb) / d;
+    if (h >= g.H) break;
+    if (a.x_rot) {
+      for (int c8 = 0; c8 < d; c8 += 8) {
+        uint32_t r[8];
+        tmem_ld8(taddr + cb + c8, r);
+        tmem_wait_ld();
+        if (row_ok)
+          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + n0 + cb + c8) =
+              make_uint4(pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                         pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                         pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                         pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+      }
+    }
+    if (!a.codes) continue;
+    float mx = -INFINITY, mn = INFINITY;
+    for (int b = 0; b < nblk; ++b) {
+      uint32_t r[32];
+      ld32_by8(taddr + cb + 32 * b, r);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (32 * b + j < d_q) {
+          float f = rnd<true>(__uint_as_float(r[j]));
+          mx = fmaxf(mx, f);
+          mn = fminf(mn, f);
+        }
+    }
+    GroupParams p;
+    if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
+    else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+    for (int b = 0; b < 2 * g.cpg; ++b) {
+      uint32_t q[32];
+      if (b < nblk) {
+        uint32_t r[32];
+        ld32_by8(taddr + cb + 32 * b, r);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          int c = 0;
+          if (32 * b + j < d_q) {
+            float f = rnd<true>(__uint_as_float(r[j]));
+            if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(f, p.scale, maxq);
+            else c = int_asym_code<true>(f, p.scale, p.zero, maxq);
+          }
+          q[j] = (uint32_t)c;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) q[j] = 0;
+      }
+      if (row_ok) {
+        const int64_t slot = (int64_t)h * g.cpg * 64 + 32 * b;
+        if constexpr (MODE == MODE_INT8_ASYM) {
+          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t* s = q + 16 * i + 4 * k;
+              w[k] = (s[0] & 0xFF) | ((s[1] & 0xFF) << 8) | ((s[2] & 0xFF) << 16) | ((s[3] & 0xFF) << 24);
+            }
+            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+          *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot / 2) = pack_planar32(q);
+        }
+      }
+    }
+    if (row_ok) {
+      for (int c = 0; c < g.cpg; ++c) {
+        a.scales[(int64_t)(h * g.cpg + c) * a.ldm + row] = __float2bfloat16_rn(p.scale);
+        if constexpr (MODE != MODE_INT4_SYM) a.zeros[(int64_t)(h * g.cpg + c) * a.ldm + row] = __float2bfloat16_rn(p.zero);
+      }
+    }
+    if (a.tail) {
+      for (int c8 = d_q & ~7; c8 < d; c8 += 8) {
+        uint32_t r[8];
+        tmem_ld8(taddr + cb + c8, r);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (c8 + j >= d_q)
+              a.tail[row * g.tail_pitch + h * g.hlen + (c8 + j - d_q)] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+  const ActGeom& g = a.g;
+  const bool row_ok = row < a.M;
+  for (int c0 = 0; c0 < a.BN; c0 += 32) {
+    const int col = n0 + c0;
+    if (col >= g.D) break;
+    uint32_t r[32];
+    tmem_ld32(taddr + c0, r);
+    tmem_wait_ld();
+    if (row_ok) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (col + 8 * i + 8 <= g.D)
+          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) =
+              make_uint4(pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                         pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                         pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                         pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+    }
+  }
+}
+
+template <int EPI, int MODE>
+__global__ void __launch_bounds__(RQ_THREADS, 1)
+rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_u, const RotArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RQ_STAGES * RQ_STAGE_BYTES);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) acc_full, [2S+2..2S+4) acc_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * RQ_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (RQ_STAGES + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * RQ_STAGES + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * RQ_STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RQ_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 128); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_x);
+    prefetch_tmap(&tm_u);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = a.m_tiles * a.n_tiles;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t issued = 0;   // bit s set: a load into stage s has been issued at least once
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
+        int kb, ke;
+        tile_k_range(a, nb, kb, ke);
+        for (int kc = kb; kc < ke; ++kc) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sa = smem_base + s * RQ_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), RQ_A_BYTES + a.BN * 128);
+          tma_load_2d(sa, &tm_x, full_bar(s), kc * 64, mb * 128);
+          tma_load_2d(sa + RQ_A_BYTES, &tm_u, full_bar(s), kc * 64, nb * a.BN);
+          issued |= 1u << s;
+          if (++s == RQ_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) {
+        // unwind: let copies already in flight land before the CTA exits (bounded)
+        const long long t0 = clock64();
+        for (int i = 0; i < RQ_STAGES; ++i) {
+          if (!(issued & (1u << i))) continue;
+          const uint32_t last_ph = (i < s) ? ph : (ph ^ 1);
+          while (!mbar_try(full_bar(i), last_ph)) {
+            if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, (uint32_t)a.BN);
+      int s = 0, buf = 0;
+      uint32_t ph = 0, aph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
+        int kb, ke;
+        tile_k_range(a, nb, kb, ke);
+        if (!mbar_wait(acce_bar(buf), aph ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 256;
+        for (int kc = kb; kc < ke; ++kc) {
+          if (!mbar_wait(full_bar(s), ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * RQ_STAGE_BYTES;
+          const uint64_t adesc = smem_desc_sw128(sa);
+          const uint64_t bdesc = smem_desc_sw128(sa + RQ_A_BYTES);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kc > kb || j > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));
+          if (++s == RQ_STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(accf_bar(buf));
+        buf ^= 1;
+        if (buf == 0) aph ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int buf = 0;
+    uint32_t aph = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
+      if (!mbar_wait(accf_bar(buf), aph, abort_flag, a.status, ERR_WAIT_ACC_FULL)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256;
+      const int64_t row = (int64_t)mb * 128 + q * 32 + lane;
+      const int n0 = nb * a.BN;
+      if constexpr (EPI == EPI_ROT_ONLY) epi_rot_only(a, taddr, row, n0);
+      else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0);
+      else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0);
+      else epi_int_perhead<MODE>(a, taddr, row, n0);
+      tc_fence_before();
+      mbar_arrive(acce_bar(buf));
+      buf ^= 1;
+      if (buf == 0) aph ^= 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `esize`-byte elements, box = 128 bytes x box_rows, 128-byte swizzle.
+int make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dt, int esize, const void* ptr, uint64_t cols, uint64_t rows,
+                 uint64_t pitch_bytes, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return DIROTQ_E_CUDA;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (pitch_bytes & 15)) return DIROTQ_E_ALIGN;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int EPI, int MODE>
+static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs& a, cudaStream_t st) {
+  auto k = rotate_quant_kernel<EPI, MODE>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_SMEM_BYTES) != cudaSuccess)
+      return DIROTQ_E_CUDA;
+    attr_set = true;
+  }
+  const int grid = min(a.m_tiles * a.n_tiles, num_sms());
+  k<<<grid, RQ_THREADS, RQ_SMEM_BYTES, st>>>(tx, tu, a);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+// Picks the N tile: hidden layouts want a multiple of 64 with the least padding of D; per-head
+// layouts a whole number of heads (and a multiple of 16 for the UMMA shape).
+int pick_bn(const ActGeom& g) {
+  if (g.H > 0) {
+    int best = 0;
+    for (int k = 1; k * g.d <= 256; ++k)
+      if ((k * g.d) % 16 == 0) best = k * g.d;
+    return best;
+  }
+  int best = 256, waste = 1 << 30;
+  const int cand[3] = {256, 192, 128};
+  for (int i = 0; i < 3; ++i) {
+    int w = ceil_div(g.D, cand[i]) * cand[i] - g.D;
+    if (w < waste) { waste = w; best = cand[i]; }
+  }
+  return best;
+}
+
+int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, int64_t M, RotArgs a, cudaStream_t st) {
+  if (M <= 0) return DIROTQ_OK;
+  a.g = g;
+  a.M = M;
+  a.ldm = ld_rows(M);
+  a.BN = pick_bn(g);
+  if (a.BN <= 0) return DIROTQ_E_UNSUPPORTED;
+  a.n_tiles = ceil_div(g.D, a.BN);
+  a.m_tiles = (int)((M + 127) / 128);
+  a.band = g.H > 0 ? g.d : 0;
+  const bool rot_only = a.codes == nullptr;
+  if (rot_only && !a.x_rot) return DIROTQ_E_ARG;
+  if (!rot_only && g.H > 0) {
+    // 32-column TMEM reads of a head's group must stay inside the head
+    if (((g.group + 31) / 32) * 32 > g.d) return DIROTQ_E_UNSUPPORTED;
+  }
+  if (!rot_only && g.H == 0 && !is_nvfp4(g.mode) && g.group != 64) return DIROTQ_E_UNSUPPORTED;
+  CUtensorMap tx, tu;
+  int rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)g.D, (uint64_t)M, (uint64_t)g.D * 2, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rot_t, (uint64_t)g.D, (uint64_t)g.D, (uint64_t)g.D * 2,
+                    (uint32_t)a.BN);
+  if (rc) return rc;
+  if (rot_only) return launch_rq<EPI_ROT_ONLY, 0>(tx, tu, a, st);
+  if (g.H > 0) {
+    switch (g.mode) {
+      case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_SYM>(tx, tu, a, st);
+      case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_ASYM>(tx, tu, a, st);
+      case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT8_ASYM>(tx, tu, a, st);
+      default: return DIROTQ_E_UNSUPPORTED;
+    }
+  }
+  switch (g.mode) {
+    case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT4_SYM>(tx, tu, a, st);
+    case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT4_ASYM>(tx, tu, a, st);
+    case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT8_ASYM>(tx, tu, a, st);
+    case DIROTQ_NVFP4_REF: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_REF>(tx, tu, a, st);
+    case DIROTQ_NVFP4_HW: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_HW>(tx, tu, a, st);
+  }
+  return DIROTQ_E_UNSUPPORTED;
+}
+
+}  // namespace dq

@@ -1,0 +1,208 @@
+"""Torch-tensor front end of the C ABI: allocates outputs as torch tensors, passes raw device
+pointers and the current CUDA stream, raises on any non-zero return code.
+
+Buffer layouts are documented in include/dirotq_b200.h.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import ActFormatC, ActLayoutC, check
+
+INT4_SYM, INT4_ASYM, INT8_ASYM, NVFP4_REF, NVFP4_HW = 0, 1, 2, 3, 4
+_ASYM = (INT4_ASYM, INT8_ASYM)
+
+
+@dataclass(frozen=True)
+class ActFormat:
+    mode: int
+    width: int
+    tail_len: int = 0
+    group_size: int = 64
+    num_heads: int = 0
+    head_dim: int = 0
+    clip_ratio: float = 1.0
+    tensor_scale: float = 1.0
+
+    def c(self) -> ActFormatC:
+        return ActFormatC(self.mode, self.width, self.num_heads, self.head_dim, self.tail_len, self.group_size,
+                          self.clip_ratio, self.tensor_scale)
+
+
+@dataclass(frozen=True)
+class ActLayout:
+    q_len: int
+    group: int
+    n_groups: int
+    chunks_per_group: int
+    n_chunks: int
+    k_pad: int
+    code_row_bytes: int
+    tail_total: int
+    tail_pitch: int
+    n_scales: int
+
+
+def act_layout(fmt: ActFormat) -> ActLayout:
+    out = ActLayoutC()
+    check(_lib.lib().dirotq_act_layout_of(C.byref(fmt.c()), C.byref(out)), "dirotq_act_layout_of")
+    return ActLayout(*[getattr(out, f) for f, _ in ActLayoutC._fields_])
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """int32 device word the kernels write a timeout code into (zero = healthy)."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{key}")
+    return _status[key]
+
+
+def check_status(device=None):
+    """Synchronising read of the status word; raises if a bounded device-side wait ran out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    s = int(status_word(dev)[0].item())
+    if s != 0:
+        status_word(dev).zero_()
+        raise RuntimeError("dirotq_b200 kernel reported: " + _lib.lib().dirotq_status_string(s).decode())
+
+
+@dataclass
+class ActBuffers:
+    fmt: ActFormat
+    layout: ActLayout
+    M: int
+    codes: torch.Tensor
+    scales: torch.Tensor
+    zeros: Optional[torch.Tensor]
+    tail: Optional[torch.Tensor]
+
+    @property
+    def ldm(self):
+        return (self.M + 7) // 8 * 8
+
+
+def alloc_act(fmt: ActFormat, M: int, device) -> ActBuffers:
+    """Zero-initialised code / scale / zero / tail buffers for M rows (pad entries must stay zero)."""
+    lay = act_layout(fmt)
+    l = _lib.lib()
+    fc, lc = fmt.c(), ActLayoutC(*[getattr(lay, f) for f, _ in ActLayoutC._fields_])
+    nb = lambda fn, *a: int(fn(*a))
+    codes = torch.zeros(nb(l.dirotq_act_codes_bytes, C.byref(lc), M), dtype=torch.uint8, device=device)
+    scales = torch.zeros(nb(l.dirotq_act_scales_bytes, C.byref(fc), C.byref(lc), M), dtype=torch.uint8, device=device)
+    zb = nb(l.dirotq_act_zeros_bytes, C.byref(fc), C.byref(lc), M)
+    zeros = torch.zeros(zb, dtype=torch.uint8, device=device) if zb else None
+    tb = nb(l.dirotq_act_tail_bytes, C.byref(lc), M)
+    tail = torch.zeros(tb, dtype=torch.uint8, device=device) if lay.tail_total > 0 else None
+    return ActBuffers(fmt, lay, M, codes, scales, zeros, tail)
+
+
+def quantize_act(x2d: torch.Tensor, fmt: ActFormat, perm_idx: Optional[torch.Tensor] = None,
+                 out: Optional[ActBuffers] = None) -> ActBuffers:
+    """Kernel 1a: quantise an already rotated / permuted [M, D] bf16 tensor."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.dim() == 2 and x2d.stride(1) == 1
+    M = x2d.shape[0]
+    buf = out if out is not None else alloc_act(fmt, M, x2d.device)
+    check(_lib.lib().dirotq_quantize_act(C.byref(fmt.c()), _ptr(x2d), x2d.stride(0), _ptr(perm_idx), M,
+                                         _ptr(buf.codes), _ptr(buf.scales), _ptr(buf.zeros), _ptr(buf.tail),
+                                         _stream()), "dirotq_quantize_act")
+    return buf
+
+
+def rotate_quantize(x2d: torch.Tensor, rot_t: torch.Tensor, fmt: ActFormat, want_x_rot: bool = False,
+                    out: Optional[ActBuffers] = None):
+    """Kernel 1: fused rotate + split + quantise.  rot_t = rotation transposed ([D_out, D_in] bf16)."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
+    assert rot_t.dtype == torch.bfloat16 and rot_t.is_contiguous()
+    M = x2d.shape[0]
+    buf = out if out is not None else alloc_act(fmt, M, x2d.device)
+    x_rot = torch.empty_like(x2d) if want_x_rot else None
+    check(_lib.lib().dirotq_rotate_quantize(C.byref(fmt.c()), _ptr(x2d), _ptr(rot_t), M, _ptr(x_rot),
+                                            _ptr(buf.codes), _ptr(buf.scales), _ptr(buf.zeros), _ptr(buf.tail),
+                                            _ptr(status_word(x2d.device)), _stream()), "dirotq_rotate_quantize")
+    return (buf, x_rot) if want_x_rot else buf
+
+
+def rotate(x2d: torch.Tensor, rot_t: torch.Tensor, num_heads: int = 0, head_dim: int = 0) -> torch.Tensor:
+    """Rotation only (bf16 tcgen05 GEMM): y = x @ rot_t.T."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
+    D = x2d.shape[1]
+    fmt = ActFormat(INT4_SYM, D, tail_len=1 if num_heads else 0, num_heads=num_heads, head_dim=head_dim)
+    y = torch.empty_like(x2d)
+    check(_lib.lib().dirotq_rotate_quantize(C.byref(fmt.c()), _ptr(x2d), _ptr(rot_t), x2d.shape[0], _ptr(y),
+                                            None, None, None, None, _ptr(status_word(x2d.device)), _stream()),
+          "dirotq_rotate_quantize(rotation only)")
+    return y
+
+
+@dataclass
+class PackedWeightInt4:
+    N: int
+    n_low: int
+    group: int
+    n_chunks: int
+    codes: torch.Tensor     # uint8 [N, n_chunks*32]
+    scales: torch.Tensor    # fp32 [n_chunks, ldn]
+    wsum: torch.Tensor      # fp32 [n_chunks, ldn]
+
+
+def pack_weight_int4(w_low: torch.Tensor, group: int, scales: Optional[torch.Tensor] = None,
+                     w_is_codes: bool = False) -> PackedWeightInt4:
+    """Kernel 3 (INT4).  w_low fp32 [N, n_low] rotated weight (or integer codes if w_is_codes)."""
+    w = w_low.to(torch.float32).contiguous()
+    N, n_low = w.shape
+    n_groups = (n_low + group - 1) // group
+    n_chunks = n_groups * ((group + 63) // 64)
+    ldn = (N + 7) // 8 * 8
+    codes = torch.zeros(N, n_chunks * 32, dtype=torch.uint8, device=w.device)
+    sc = torch.zeros(n_chunks, ldn, dtype=torch.float32, device=w.device)
+    ws = torch.zeros(n_chunks, ldn, dtype=torch.float32, device=w.device)
+    s_in = None if scales is None else scales.to(torch.float32).contiguous()
+    if s_in is not None:
+        assert s_in.shape == (N, n_groups)
+    check(_lib.lib().dirotq_pack_weight_int4(_ptr(w), N, n_low, group, _ptr(s_in), int(w_is_codes), _ptr(codes),
+                                             _ptr(sc), _ptr(ws), _stream()), "dirotq_pack_weight_int4")
+    return PackedWeightInt4(N, n_low, group, n_chunks, codes, sc, ws)
+
+
+@dataclass
+class PackedWeightNvfp4:
+    N: int
+    n_low: int
+    n_chunks: int
+    tensor_scale: float
+    codes: torch.Tensor     # uint8 [N, n_chunks*32]
+    sf: torch.Tensor        # uint8 tiled UE4M3
+
+
+def pack_weight_nvfp4(w_low: torch.Tensor, tensor_scale: float, scales_e4m3: Optional[torch.Tensor] = None,
+                      w_is_codes: bool = False) -> PackedWeightNvfp4:
+    """Kernel 3 (NVFP4, group 16, two-level scale)."""
+    w = w_low.to(torch.float32).contiguous()
+    N, n_low = w.shape
+    n_chunks = (n_low + 63) // 64
+    codes = torch.zeros(N, n_chunks * 32, dtype=torch.uint8, device=w.device)
+    sf = torch.zeros(((N + 127) // 128) * ((n_chunks + 3) // 4 * 4) * 512, dtype=torch.uint8, device=w.device)
+    s_in = None
+    if scales_e4m3 is not None:
+        s_in = scales_e4m3.contiguous()
+        assert s_in.dtype == torch.uint8 and s_in.shape == (N, (n_low + 15) // 16)
+    check(_lib.lib().dirotq_pack_weight_nvfp4(_ptr(w), N, n_low, float(tensor_scale), _ptr(s_in), int(w_is_codes),
+                                              _ptr(codes), _ptr(sf), _stream()), "dirotq_pack_weight_nvfp4")
+    return PackedWeightNvfp4(N, n_low, n_chunks, float(tensor_scale), codes, sf)

@@ -1,0 +1,202 @@
+/* dirotq_b200 -- C ABI of the B200 (sm_100a) quantized-linear path of DiRotQ.
+ *
+ * The reference project is pure Python and has no native ABI; each entry point below names the
+ * reference code it replaces (paths inside the DiRotQ project).  All pointers are DEVICE pointers
+ * unless the name ends in `_host`.  `stream` is a cudaStream_t passed as void*.  The library never
+ * allocates, frees or caches device memory (one exception, documented at its declaration).
+ *
+ * Return value: 0 = launched, < 0 = argument rejected on the host before any launch (see
+ * dirotq_error_string).  Device-side bounded waits that run out write a positive code into the
+ * caller's `status` word (int32, device memory, must be zero before the call); the kernel then
+ * unwinds and returns normally, so the context stays usable.
+ */
+#ifndef DIROTQ_B200_H
+#define DIROTQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DIROTQ_ABI_VERSION 1
+
+/* ---- activation quantiser modes (ActQuantizer.configure, utils/quant_utils.py:182-199) ---- */
+enum {
+  DIROTQ_INT4_SYM = 0,  /* bits=4 sym=True  : codes [-8,7], scale = amax/7            (:63-68, :204-209) */
+  DIROTQ_INT4_ASYM = 1, /* bits=4 sym=False : codes [0,15] + zero point               (:75-81, :211-215) */
+  DIROTQ_INT8_ASYM = 2, /* bits=8 sym=False : codes [0,255] + zero point (W4A8)                         */
+  DIROTQ_NVFP4_REF = 3, /* quant_dtype="nvfp4": E2M1 codes + UNROUNDED bf16 group scale (:148-180);
+                           bit-exact to the reference, not consumable by block-scaled tensor cores */
+  DIROTQ_NVFP4_HW = 4   /* E2M1 codes + UE4M3 group scale relative to an fp32 tensor scale (the
+                           two-level recipe of speedup/weight_only_nvfp4.py:42-72 applied to activations) */
+};
+
+/* Error codes (negative returns). */
+enum {
+  DIROTQ_OK = 0,
+  DIROTQ_E_ARG = -1,        /* null pointer / bad size */
+  DIROTQ_E_UNSUPPORTED = -2,/* combination not implemented */
+  DIROTQ_E_ALIGN = -3,      /* pointer or pitch not aligned as required */
+  DIROTQ_E_CUDA = -4,       /* a CUDA runtime / driver call failed */
+  DIROTQ_E_TOO_LARGE = -5   /* exceeds a fixed capacity */
+};
+
+/* How one linear's input is split and grouped.  Mirrors what ActQuantWrapper + ActQuantizer carry
+ * (utils/quant_utils.py:300-323, :101-106) after the per-head override of
+ * dirotq_fused_unrotation_fast.py:89-93 (groupsize := head_dim - tail, tail := H * tail). */
+typedef struct dirotq_act_format {
+  int32_t mode;         /* DIROTQ_* above */
+  int32_t width;        /* D, input features */
+  int32_t num_heads;    /* 0: hidden layout [low | tail]; H > 0: per-head layout */
+  int32_t head_dim;     /* d (per-head only; H * d == D) */
+  int32_t tail_len;     /* high_bits_length: hidden = total, per-head = per head */
+  int32_t group_size;   /* hidden: 64 (INT) or 16 (NVFP4); per-head: ignored, group = d - tail_len */
+  float clip_ratio;     /* ActQuantizer.clip_ratio */
+  float tensor_scale;   /* DIROTQ_NVFP4_HW only: fp32 per-tensor scale T (> 0) */
+} dirotq_act_format;
+
+/* Sizes derived from a format (all per row unless stated). */
+typedef struct dirotq_act_layout {
+  int32_t q_len;          /* quantised channels per row */
+  int32_t group;          /* effective group size */
+  int32_t n_groups;       /* reference groups per row (incl. a zero-padded last one) */
+  int32_t chunks_per_group; /* 64-wide GEMM chunks per group (1, or 2 for groups of 65..128) */
+  int32_t n_chunks;       /* INT: n_groups * chunks_per_group; NVFP4: ceil(q_len / 64) */
+  int32_t k_pad;          /* code slots per row = n_chunks * 64 */
+  int32_t code_row_bytes; /* k_pad / 2 (4-bit) or k_pad (8-bit) */
+  int32_t tail_total;     /* passthrough channels per row */
+  int32_t tail_pitch;     /* elements; tail_total rounded up to 8 */
+  int32_t n_scales;       /* scale entries per row: INT n_chunks, NVFP4_REF q_len/16 (rounded up) */
+} dirotq_act_layout;
+
+/* Fills *out; returns DIROTQ_OK or an error for an unsupported format. */
+int dirotq_act_layout_of(const dirotq_act_format* fmt, dirotq_act_layout* out);
+
+/* Buffer sizes in bytes for M rows (each rounded up to 256 B).  Data layouts:
+ *  codes : [M, code_row_bytes].  INT4: inside every block of 32 code slots, byte j holds slot j in
+ *          its low nibble and slot 16+j in its high nibble.  NVFP4: slot 2j in the low nibble of
+ *          byte j.  INT8: one byte per slot.  Slot of element e of group g: (g*chunks_per_group)*64+e.
+ *  scales: INT / NVFP4_REF: bf16 [n_scales, ldm] (GROUP-major, ldm = M rounded up to 8).
+ *          NVFP4_HW: UE4M3 bytes in 512-byte tiles of 128 rows x 4 groups:
+ *            tile(rb, kb) at ((rb * ceil4(n_chunks)) + kb) * 512, inside it
+ *            (row%32)*16 + (row%128/32)*4 + (group%4); buffers must be zeroed once by the caller
+ *            (pad entries are never written).
+ *  zeros : bf16 [n_scales, ldm] (asymmetric modes only).
+ *  tail  : bf16 [M, tail_pitch].
+ */
+size_t dirotq_act_codes_bytes(const dirotq_act_layout* l, int64_t M);
+size_t dirotq_act_scales_bytes(const dirotq_act_format* f, const dirotq_act_layout* l, int64_t M);
+size_t dirotq_act_zeros_bytes(const dirotq_act_format* f, const dirotq_act_layout* l, int64_t M);
+size_t dirotq_act_tail_bytes(const dirotq_act_layout* l, int64_t M);
+
+/* ---------------------------------------------------------------------------------------------
+ * Kernel 1a: quantise an already rotated (or permuted / unrotated) activation tensor.
+ * Replaces ActQuantizer.find_params + ActQuantizer.forward (utils/quant_utils.py:112-180,
+ * :201-240) and the perm_idx gather of dirotq_fused_unrotation_fast.py:130-134.
+ *   x        : bf16 [M, width], row pitch x_pitch elements
+ *   perm_idx : int64 [width] or NULL  (x[..., perm_idx] is quantised)
+ * Per-head formats expect x in the interleaved [H, d] layout the wrapper receives.
+ */
+int dirotq_quantize_act(const dirotq_act_format* fmt, const void* x, int64_t x_pitch, const int64_t* perm_idx,
+                        int64_t M, void* codes, void* scales, void* zeros, void* tail, void* stream);
+
+/* Kernel 1: fused rotate + split + quantise.  Replaces `x_flat @ self.rotation` / the per-head
+ * einsum followed by find_params + quantizer (dirotq_fused_unrotation_fast.py:69-104) and the
+ * stand-alone rotation kernels speedup/kernels/{int8,fp8,bf16}_rotation.py.
+ *   x     : bf16 [M, width] contiguous
+ *   rot_t : bf16 [width, width] = TRANSPOSE of the rotation (row n = column n of U); for per-head
+ *           formats the block-diagonal matrix of the H transposed d x d blocks
+ *   x_rot : optional bf16 [M, width] output of the rotated tensor (may be NULL)
+ *   codes/scales/zeros/tail: as above; all four NULL = rotation only (x_rot required)
+ *   status: int32 device word (zero on entry)
+ */
+int dirotq_rotate_quantize(const dirotq_act_format* fmt, const void* x, const void* rot_t, int64_t M, void* x_rot,
+                           void* codes, void* scales, void* zeros, void* tail, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Kernel 3: weight quantiser / packer.  Replaces speedup/nunchaku_pack.py:225-459
+ * (convert_to_nunchaku_w4x4y16, convert_dirotq_low_weight_to_nunchaku[_fp4]) and the NVFP4 weight
+ * quantiser speedup/weight_only_nvfp4.py:42-72; arithmetic of utils/quant_utils.py:714-767.
+ *
+ * INT4: w_low fp32 [N, n_low] in the rotated basis.  group = reference group size (any value in
+ *   1..128).  scale_in fp32 [N, n_groups] or NULL (NULL: RTN scale = clamp(amax,1e-5)/7).
+ *   w_is_codes != 0: w_low already holds integer codes in [-8,7] (scale_in required).
+ *   Outputs: codes [N, k_pad/2] (same slot layout as activations), scales fp32 [n_chunks, ldn]
+ *   (group-major, ldn = N rounded up to 8), wsum fp32 [n_chunks, ldn] = sum of the codes of a chunk.
+ */
+int dirotq_pack_weight_int4(const float* w_low, int64_t N, int64_t n_low, int32_t group, const float* scale_in,
+                            int32_t w_is_codes, void* codes, float* scales, float* wsum, void* stream);
+
+/* NVFP4: group 16, two-level scale.  tensor_scale T > 0 (fp32; the host picks a power of two).
+ *   scale_in: UE4M3 bytes [N, n_low/16] or NULL (NULL: micro = e4m3(clamp(amax/6/T, 2^-9, 448))).
+ *   w_is_codes != 0: w_low holds E2M1 nibble values 0..15 as floats (scale_in required).
+ *   Outputs: codes [N, k_pad/2] sequential nibbles (k_pad = ceil64(n_low)), sf = tiled UE4M3 bytes
+ *   (same tiling as activations, rows = N; zero the buffer once before the call).
+ */
+int dirotq_pack_weight_nvfp4(const float* w_low, int64_t N, int64_t n_low, float tensor_scale,
+                             const uint8_t* scale_in, int32_t w_is_codes, void* codes, void* sf, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Kernel 2: W4A4 GEMM + bf16 high-precision branch + dequant + bias.  Replaces the inner
+ * `self.module(x)` of the fused forward (dirotq_fused_unrotation_fast.py:141) as a real 4-bit GEMM
+ * (the reference's speed path calls the third-party nunchaku gemm_w4a4 for this).
+ *
+ * INT (exact int32 accumulation per 64-chunk, tcgen05 kind::i8):
+ *   y[m,n] = sum_c xs[c,m] ws[c,n] (sum_k qx qw  -  xz[c,m] wsum[c,n]) + x_tail[m,:].w_tail[n,:] + bias[n]
+ *   a_mode : DIROTQ_INT4_SYM / INT4_ASYM / INT8_ASYM (layout of x_codes / presence of x_zeros)
+ *   w_tail : bf16 [N, tail_pitch]; x_tail bf16 [M, tail_pitch]; tail_total may be 0
+ *   acc_dump: optional int32 [n_chunks, M, N] receiving the raw per-chunk accumulators (tests)
+ */
+int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
+                         const void* x_scales, const void* x_zeros, const void* w_codes, const float* w_scales,
+                         const float* w_sum, const void* x_tail, const void* w_tail, int32_t tail_total,
+                         int32_t tail_pitch, const void* bias, void* y, int32_t* acc_dump, int32_t* status,
+                         void* stream);
+
+/* NVFP4 (tcgen05 kind::mxf4nvf4, UE4M3 scale factors in TMEM):
+ *   y = out_scale * (sum_blocks sfx sfw (e2m1.e2m1) + x_tail . w_tail_scaled) + bias
+ *   out_scale = Tx * Tw; w_tail_scaled = w_tail / out_scale (bf16, prepared once by the host).
+ */
+int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
+                           const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
+                           const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
+                           void* y, int32_t* status, void* stream);
+
+/* W4A16: bf16 activations x INT4 group-quantised weights (PixArt ff.net.2 under
+ * --skip-quant-layers; forward model: speedup/weight_only_nvfp4.py:128-178).  Weights in the
+ * dirotq_pack_weight_int4 format (group 64). */
+int dirotq_gemm_w4a16(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const float* w_scales,
+                      const void* bias, void* y, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * One wrapped linear end to end: what the patched ActQuantWrapper.forward runs
+ * (dirotq_fused_unrotation_fast.py:56-141).  `workspace` holds codes / scales / zeros / tail. */
+typedef struct dirotq_linear {
+  dirotq_act_format fmt;
+  int64_t out_features;
+  const void* rot_t;        /* NULL: no rotation (quantise only) */
+  const int64_t* perm_idx;  /* optional, only when rot_t == NULL */
+  const void* w_codes;
+  const void* w_scales;     /* INT: fp32 [n_chunks, ldn]; NVFP4: tiled UE4M3 */
+  const float* w_sum;       /* INT only */
+  const void* w_tail;       /* bf16 [N, tail_pitch] (NVFP4: divided by out_scale) */
+  const void* bias;         /* bf16 [N] or NULL */
+  float w_tensor_scale;     /* NVFP4 only */
+} dirotq_linear;
+
+size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M);
+int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ---- misc ---- */
+int dirotq_abi_version(void);
+const char* dirotq_error_string(int code);
+/* Text for a positive device status code (which wait ran out). */
+const char* dirotq_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIROTQ_B200_H */
