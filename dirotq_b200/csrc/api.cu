@@ -169,3 +169,130 @@ int dirotq_pack_weight_nvfp4(const float* w_low, int64_t N, int64_t n_low, float
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// GEMMs and the whole wrapped linear
+// ---------------------------------------------------------------------------------------------
+extern "C" {
+
+int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
+                         const void* x_scales, const void* x_zeros, const void* w_codes, const float* w_scales,
+                         const float* w_sum, const void* x_tail, const void* w_tail, int32_t tail_total,
+                         int32_t tail_pitch, const void* bias, void* y, int32_t* acc_dump, int32_t* status,
+                         void* stream) {
+  if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM && a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
+  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_codes || !w_scales || !y) return DIROTQ_E_ARG;
+  if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
+  if (a_mode != DIROTQ_INT4_SYM && (!x_zeros || !w_sum)) return DIROTQ_E_ARG;
+  if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail || tail_pitch < tail_total || tail_pitch % 8))) return DIROTQ_E_ARG;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(w_codes) |
+                       reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x_tail) |
+                       reinterpret_cast<uintptr_t>(w_tail);
+  if (al & 15) return DIROTQ_E_ALIGN;
+  GemmIntArgs a;
+  a.a_mode = a_mode;
+  a.M = M;
+  a.N = N;
+  a.n_chunks = n_chunks;
+  a.xq = static_cast<const uint8_t*>(x_codes);
+  a.x_row_bytes = (a_mode == DIROTQ_INT8_ASYM) ? (int64_t)n_chunks * 64 : (int64_t)n_chunks * 32;
+  a.xs = static_cast<const __nv_bfloat16*>(x_scales);
+  a.xz = static_cast<const __nv_bfloat16*>(x_zeros);
+  a.ldm = ld_rows(M);
+  a.wq = static_cast<const uint8_t*>(w_codes);
+  a.w_row_bytes = (int64_t)n_chunks * 32;
+  a.ws = w_scales;
+  a.wsum = w_sum;
+  a.ldn = ld_rows(N);
+  a.xt = static_cast<const __nv_bfloat16*>(x_tail);
+  a.wt = static_cast<const __nv_bfloat16*>(w_tail);
+  a.kt = tail_total;
+  a.kt_pitch = tail_pitch;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.acc_dump = acc_dump;
+  a.status = status;
+  return launch_gemm_int(a, static_cast<cudaStream_t>(stream));
+}
+
+int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
+                           const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
+                           const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
+                           void* y, int32_t* status, void* stream) {
+  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_sf || !w_codes || !w_sf || !y) return DIROTQ_E_ARG;
+  if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
+  if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8))) return DIROTQ_E_ARG;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x_sf) | reinterpret_cast<uintptr_t>(w_sf) | reinterpret_cast<uintptr_t>(y);
+  if (al & 15) return DIROTQ_E_ALIGN;
+  GemmFp4Args a;
+  a.M = M;
+  a.N = N;
+  a.n_chunks = n_chunks;
+  a.xq = static_cast<const uint8_t*>(x_codes);
+  a.xsf = static_cast<const uint8_t*>(x_sf);
+  a.wq = static_cast<const uint8_t*>(w_codes);
+  a.wsf = static_cast<const uint8_t*>(w_sf);
+  a.out_scale = out_scale;
+  a.xt = static_cast<const __nv_bfloat16*>(x_tail);
+  a.wt = static_cast<const __nv_bfloat16*>(w_tail_scaled);
+  a.kt = tail_total;
+  a.kt_pitch = tail_pitch;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.status = status;
+  return launch_gemm_nvfp4(a, static_cast<cudaStream_t>(stream));
+}
+
+struct WsCarve {
+  size_t codes, scales, zeros, tail, total;
+};
+static int carve(const dirotq_linear* lin, int64_t M, ActGeom* g, WsCarve* w) {
+  int rc = make_geom(&lin->fmt, g);
+  if (rc) return rc;
+  dirotq_act_layout l;
+  dirotq_act_layout_of(&lin->fmt, &l);
+  w->codes = 0;
+  w->scales = w->codes + dirotq_act_codes_bytes(&l, M);
+  w->zeros = w->scales + dirotq_act_scales_bytes(&lin->fmt, &l, M);
+  w->tail = w->zeros + dirotq_act_zeros_bytes(&lin->fmt, &l, M);
+  w->total = w->tail + (g->tail_total > 0 ? dirotq_act_tail_bytes(&l, M) : 0);
+  return DIROTQ_OK;
+}
+
+size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M) {
+  ActGeom g;
+  WsCarve w;
+  if (!lin || M < 0 || carve(lin, M, &g, &w)) return 0;
+  return w.total;
+}
+
+int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  if (!lin || !x || !y || !workspace) return DIROTQ_E_ARG;
+  ActGeom g;
+  WsCarve w;
+  int rc = carve(lin, M, &g, &w);
+  if (rc) return rc;
+  if (workspace_bytes < w.total) return DIROTQ_E_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return DIROTQ_E_ALIGN;
+  if (g.mode == DIROTQ_NVFP4_REF) return DIROTQ_E_UNSUPPORTED;   // bf16 scales cannot feed the FP4 tensor cores
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* codes = ws + w.codes;
+  void* scales = ws + w.scales;
+  void* zeros = is_asym(g.mode) ? ws + w.zeros : nullptr;
+  void* tail = g.tail_total > 0 ? ws + w.tail : nullptr;
+  if (lin->rot_t)
+    rc = dirotq_rotate_quantize(&lin->fmt, x, lin->rot_t, M, nullptr, codes, scales, zeros, tail, status, stream);
+  else
+    rc = dirotq_quantize_act(&lin->fmt, x, g.D, lin->perm_idx, M, codes, scales, zeros, tail, stream);
+  if (rc) return rc;
+  if (g.mode == DIROTQ_NVFP4_HW)
+    return dirotq_gemm_w4a4_nvfp4(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
+                                  lin->fmt.tensor_scale * lin->w_tensor_scale, tail, lin->w_tail, g.tail_total,
+                                  g.tail_pitch, lin->bias, y, status, stream);
+  return dirotq_gemm_w4a4_int(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
+                              static_cast<const float*>(lin->w_scales), lin->w_sum, tail, lin->w_tail, g.tail_total,
+                              g.tail_pitch, lin->bias, y, nullptr, status, stream);
+}
+
+}  // extern "C"

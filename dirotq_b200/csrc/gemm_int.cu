@@ -21,6 +21,7 @@
 #include "layout.cuh"
 #include "launchers.cuh"
 #include "ptx.cuh"
+#include "quant_math.cuh"
 
 namespace dq {
 

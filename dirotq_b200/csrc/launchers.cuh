@@ -65,10 +65,55 @@ struct RotArgs {
   int* status;
 };
 
+struct GemmIntArgs {
+  int a_mode;
+  int64_t M, N;
+  int n_chunks;
+  const uint8_t* xq;           // activation codes [M, x_row_bytes]
+  int64_t x_row_bytes;
+  const __nv_bfloat16* xs;     // [n_chunks, ldm]
+  const __nv_bfloat16* xz;     // [n_chunks, ldm] or null
+  int64_t ldm;
+  const uint8_t* wq;           // weight codes [N, n_chunks * 32]
+  int64_t w_row_bytes;
+  const float* ws;             // [n_chunks, ldn]
+  const float* wsum;           // [n_chunks, ldn]
+  int64_t ldn;
+  const __nv_bfloat16* xt;     // [M, kt_pitch]
+  const __nv_bfloat16* wt;     // [N, kt_pitch]
+  int kt;
+  int kt_pitch;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;            // [M, N]
+  int32_t* acc_dump;
+  int* status;
+};
+
+struct GemmFp4Args {
+  int64_t M, N;
+  int n_chunks;
+  const uint8_t* xq;           // [M, n_chunks * 32]
+  const uint8_t* xsf;          // tiled UE4M3
+  const uint8_t* wq;           // [N, n_chunks * 32]
+  const uint8_t* wsf;
+  float out_scale;
+  const __nv_bfloat16* xt;
+  const __nv_bfloat16* wt;
+  int kt;
+  int kt_pitch;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;
+  int* status;
+};
+
+int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
+int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st);
+
 int launch_quantize(const QuantArgs& a, cudaStream_t st);
 int launch_pack_int4(const PackIntArgs& a, cudaStream_t st);
 int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st);
 int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, int64_t M, RotArgs a, cudaStream_t st);
 int num_sms();
+
 
 }  // namespace dq

@@ -206,3 +206,45 @@ def pack_weight_nvfp4(w_low: torch.Tensor, tensor_scale: float, scales_e4m3: Opt
     check(_lib.lib().dirotq_pack_weight_nvfp4(_ptr(w), N, n_low, float(tensor_scale), _ptr(s_in), int(w_is_codes),
                                               _ptr(codes), _ptr(sf), _stream()), "dirotq_pack_weight_nvfp4")
     return PackedWeightNvfp4(N, n_low, n_chunks, float(tensor_scale), codes, sf)
+
+
+def pad_tail_weight(w_tail: Optional[torch.Tensor], tail_pitch: int, N: int, device) -> Optional[torch.Tensor]:
+    """bf16 [N, tail_total] -> bf16 [N, tail_pitch] (zero padded), the layout the GEMMs read."""
+    if w_tail is None or tail_pitch == 0:
+        return None
+    out = torch.zeros(N, tail_pitch, dtype=torch.bfloat16, device=device)
+    out[:, : w_tail.shape[1]] = w_tail.to(device=device, dtype=torch.bfloat16)
+    return out
+
+
+def gemm_w4a4_int(act: ActBuffers, w: PackedWeightInt4, w_tail: Optional[torch.Tensor],
+                  bias: Optional[torch.Tensor], dump_acc: bool = False):
+    """Kernel 2 (INT).  Returns y bf16 [M, N] (and the int32 per-chunk accumulators if dump_acc)."""
+    lay, M, N = act.layout, act.M, w.N
+    assert lay.n_chunks == w.n_chunks, (lay.n_chunks, w.n_chunks)
+    dev = act.codes.device
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    dump = torch.zeros(lay.n_chunks, M, N, dtype=torch.int32, device=dev) if dump_acc else None
+    if lay.tail_total > 0:
+        assert w_tail is not None and tuple(w_tail.shape) == (N, lay.tail_pitch) and w_tail.dtype == torch.bfloat16
+    check(_lib.lib().dirotq_gemm_w4a4_int(act.fmt.mode, M, N, lay.n_chunks, _ptr(act.codes), _ptr(act.scales),
+                                          _ptr(act.zeros), _ptr(w.codes), _ptr(w.scales), _ptr(w.wsum),
+                                          _ptr(act.tail), _ptr(w_tail), lay.tail_total, lay.tail_pitch, _ptr(bias),
+                                          _ptr(y), _ptr(dump), _ptr(status_word(dev)), _stream()),
+          "dirotq_gemm_w4a4_int")
+    return (y, dump) if dump_acc else y
+
+
+def gemm_w4a4_nvfp4(act: ActBuffers, w: PackedWeightNvfp4, w_tail_scaled: Optional[torch.Tensor],
+                    bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """Kernel 2 (NVFP4).  w_tail_scaled = w_tail / (Tx * Tw), bf16 [N, tail_pitch]."""
+    lay, M, N = act.layout, act.M, w.N
+    assert act.fmt.mode == NVFP4_HW and lay.n_chunks == w.n_chunks
+    dev = act.codes.device
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    out_scale = float(act.fmt.tensor_scale) * float(w.tensor_scale)
+    check(_lib.lib().dirotq_gemm_w4a4_nvfp4(M, N, lay.n_chunks, _ptr(act.codes), _ptr(act.scales), _ptr(w.codes),
+                                            _ptr(w.sf), out_scale, _ptr(act.tail), _ptr(w_tail_scaled),
+                                            lay.tail_total, lay.tail_pitch, _ptr(bias), _ptr(y),
+                                            _ptr(status_word(dev)), _stream()), "dirotq_gemm_w4a4_nvfp4")
+    return y

@@ -482,22 +482,27 @@ def sf_atom_offset(row: torch.Tensor, kblk: torch.Tensor, n_kblk64: int) -> torc
     return (rb * n_kblk64 + kb64) * 512 + (r % 32) * 16 + (r // 32) * 4 + j
 
 
+def _sf_n_kb64_pad(nb16: int) -> int:
+    """64-element k-blocks per row tile, padded to a multiple of 4 (one pipeline stage = 256 elements)."""
+    return ((nb16 + 3) // 4 + 3) // 4 * 4
+
+
 def sf_tile(sf: torch.Tensor) -> torch.Tensor:
-    """[R, K/16] e4m3 bytes (uint8) -> flat tiled buffer (rows padded to 128, k-blocks to 4, zeros)."""
+    """[R, K/16] e4m3 bytes (uint8) -> flat tiled buffer (rows padded to 128, zeros in the padding)."""
     R, nb = sf.shape
-    Rp, nbp = (R + 127) // 128 * 128, (nb + 3) // 4 * 4
-    out = torch.zeros(Rp * nbp, dtype=torch.uint8)
+    Rp, nkb = (R + 127) // 128 * 128, _sf_n_kb64_pad(nb)
+    out = torch.zeros(Rp // 128 * nkb * 512, dtype=torch.uint8)
     rr = torch.arange(R).reshape(R, 1).expand(R, nb)
     kk = torch.arange(nb).reshape(1, nb).expand(R, nb)
-    out[sf_atom_offset(rr, kk, nbp // 4).reshape(-1)] = sf.reshape(-1)
+    out[sf_atom_offset(rr, kk, nkb).reshape(-1)] = sf.reshape(-1)
     return out
 
 
 def sf_untile(buf: torch.Tensor, R: int, nb: int) -> torch.Tensor:
-    nbp = (nb + 3) // 4 * 4
+    nkb = _sf_n_kb64_pad(nb)
     rr = torch.arange(R).reshape(R, 1).expand(R, nb)
     kk = torch.arange(nb).reshape(1, nb).expand(R, nb)
-    return buf[sf_atom_offset(rr, kk, nbp // 4).reshape(-1)].reshape(R, nb)
+    return buf[sf_atom_offset(rr, kk, nkb).reshape(-1)].reshape(R, nb)
 
 
 # ---------------------------------------------------------------------------

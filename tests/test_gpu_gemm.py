@@ -1,0 +1,118 @@
+"""GPU parity of kernel 2: int32 per-chunk accumulators bit-exact, layer outputs within bf16 rounding
+of the exact-arithmetic oracle (rel-L2 <= 3e-3 here; the end-to-end bound vs the reference is 1e-2)."""
+import pytest
+import torch
+
+from conftest import rel_l2, cosine
+from oracle import dirotq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup_int(ops, M, N, fmt, seed):
+    from gpu_helpers import decode_act
+    g = torch.Generator().manual_seed(seed)
+    x = O.synth_activations(M, fmt.width, g)
+    act = ops.quantize_act(x.cuda(), fmt)
+    lay = act.layout
+    dec = decode_act(act)
+    n_low = lay.n_groups * lay.group if fmt.num_heads else lay.q_len
+    qw = torch.randint(-8, 8, (N, n_low), generator=g)
+    n_groups_w = (n_low + lay.group - 1) // lay.group
+    sw = (torch.rand(N, n_groups_w, generator=g) * 0.015 + 0.005).to(torch.float16).float()
+    pk = ops.pack_weight_int4(qw.float().cuda(), lay.group, scales=sw.cuda(), w_is_codes=True)
+    w_tail = (torch.randn(N, lay.tail_total, generator=g) * 0.02).to(torch.bfloat16) if lay.tail_total else None
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    return x, act, dec, qw, sw, pk, w_tail, bias
+
+
+def _oracle_int(dec, lay, qw, sw, w_tail, bias, asym):
+    M = dec["codes"].shape[0]
+    N = qw.shape[0]
+    pad = lay.n_groups * lay.group - qw.shape[1]
+    qwp = torch.nn.functional.pad(qw, (0, pad)).reshape(N, lay.n_groups, lay.group)
+    cx = dec["codes"].clone()
+    # slots beyond q_len in a partial last group hold no data
+    if pad:
+        cx[:, -1, lay.group - pad:] = 0
+    zero = dec["zero"].float() if asym else None
+    y = O.w4a4_int_linear(cx, dec["scale"].float(), qwp, sw, dec.get("tail"), w_tail, bias, zero_x=zero)
+    cxi = cx.to(torch.int32)
+    if asym:
+        cxi = cxi - zero.to(torch.int32).unsqueeze(-1)
+        if pad:
+            cxi[:, -1, lay.group - pad:] = 0
+    acc = O.int_group_accumulators(cxi, qwp)
+    return y, acc
+
+
+@pytest.mark.parametrize("mode,M,N,D,tail", [("sym", 300, 256, 320, 64), ("sym", 1000, 1152, 1152, 64),
+                                             ("asym", 520, 384, 1152, 64), ("int8", 520, 384, 1152, 64),
+                                             ("sym", 260, 128, 256, 0), ("sym", 200, 136, 160, 0),
+                                             ("sym", 2048, 3072, 3072, 384)])
+def test_int_gemm_hidden(mode, M, N, D, tail):
+    from dirotq_b200 import ops
+    m = {"sym": ops.INT4_SYM, "asym": ops.INT4_ASYM, "int8": ops.INT8_ASYM}[mode]
+    fmt = ops.ActFormat(m, D, tail_len=tail)
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 11)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    y, dump = ops.gemm_w4a4_int(act, pk, wt, bias.cuda(), dump_acc=True)
+    ops.check_status()
+    y_ref, acc_ref = _oracle_int(dec, lay, qw, sw, w_tail, bias, mode != "sym")
+    assert torch.equal(dump.cpu(), acc_ref.to(torch.int32)), "int32 accumulators differ"
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
+    assert cosine(y.float().cpu(), y_ref) > 0.9999
+
+
+@pytest.mark.parametrize("H,d,hlen", [(16, 72, 9), (6, 32, 4), (4, 128, 16)])
+def test_int_gemm_per_head(H, d, hlen):
+    from dirotq_b200 import ops
+    fmt = ops.ActFormat(ops.INT4_SYM, H * d, tail_len=hlen, num_heads=H, head_dim=d)
+    M, N = 390, 256
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 12)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    y, dump = ops.gemm_w4a4_int(act, pk, wt, bias.cuda(), dump_acc=True)
+    ops.check_status()
+    y_ref, acc_ref = _oracle_int(dec, lay, qw, sw, w_tail, bias, False)
+    cpg = lay.chunks_per_group
+    got = dump.cpu().reshape(lay.n_groups, cpg, M, N).sum(1)
+    assert torch.equal(got, acc_ref.to(torch.int32))
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
+
+
+@pytest.mark.parametrize("M,N,D,tail", [(128, 128, 320, 64), (300, 256, 320, 64), (1000, 1152, 1152, 144),
+                                        (520, 384, 1152, 64), (260, 128, 256, 0), (2048, 3072, 3072, 384)])
+def test_nvfp4_gemm(M, N, D, tail):
+    from dirotq_b200 import ops
+    from gpu_helpers import decode_act
+    g = torch.Generator().manual_seed(13)
+    Tx = 0.5
+    fmt = ops.ActFormat(ops.NVFP4_HW, D, tail_len=tail, group_size=16, tensor_scale=Tx)
+    x = O.synth_activations(M, D, g)
+    act = ops.quantize_act(x.cuda(), fmt)
+    lay = act.layout
+    dec = decode_act(act)
+    nib_w = torch.randint(0, 16, (N, lay.q_len), generator=g).to(torch.uint8)
+    # log-normal group scales rounded to E4M3, fp32 (power-of-two) tensor scale
+    s = torch.exp(torch.randn(N, lay.n_groups, generator=g) * 0.5 - 4.0)
+    Tw = O.pow2_tensor_scale(float(s.max()))
+    micro_w = O.e4m3_round(s / Tw)
+    pk = ops.pack_weight_nvfp4(nib_w.float().cuda(), Tw,
+                               scales_e4m3=micro_w.to(torch.float8_e4m3fn).view(torch.uint8).cuda(), w_is_codes=True)
+    w_tail = (torch.randn(N, lay.tail_total, generator=g) * 0.02).to(torch.bfloat16) if tail else None
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    wts = None
+    if tail:
+        wts = ops.pad_tail_weight((w_tail.float() / (Tx * Tw)).to(torch.bfloat16), lay.tail_pitch, N, "cuda")
+        assert torch.equal(wts[:, :tail].float().cpu() * (Tx * Tw), w_tail.float())   # power of two: exact
+    y = ops.gemm_w4a4_nvfp4(act, pk, wts, bias.cuda())
+    ops.check_status()
+    nib_x = dec["codes"].reshape(M, -1)[:, : lay.q_len]
+    pad = (-lay.q_len) % 16
+    if pad:
+        nib_x = torch.nn.functional.pad(nib_x, (0, pad)); nib_w = torch.nn.functional.pad(nib_w, (0, pad))
+    y_ref = O.w4a4_nvfp4_linear(nib_x, dec["scale"], Tx, nib_w, micro_w, Tw, dec.get("tail"), w_tail, bias)
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
+    assert cosine(y.float().cpu(), y_ref) > 0.9999
