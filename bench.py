@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the DiRotQ quantized-linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload pixart_int4|pixart_nvfp4]
+    python bench.py --impl reference ...      # the reference's fp32 CPU forward on a bounded sample
+
+One "step" = every wrapped linear of one denoising step of the named DiT (BASELINE config 1 by
+default: PixArt-Sigma shapes, 28 blocks x 8 linears, batch 8 x 4096 tokens per GPU), each through
+rotate -> split -> 4-bit quantise -> W4A4 GEMM + bf16 branch + dequant + bias.  `value` counts the
+algorithmic operations of the linears (2*M*N*D each; the online rotation is overhead, not credited)
+over the device time of the step.  Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (block fn name, n_blocks, quant, tokens per sample, batch per GPU, description)
+    "pixart_int4": ("pixart_block", 28, "int4", 4096, 8,
+                    "BASELINE config 1: PixArt-Sigma-shaped step, 28 blocks x (7 INT W4A4 g64 k=64 + ff.net.2 W4A16), "
+                    "batch 8 x 4096 tokens per GPU"),
+    "pixart_nvfp4": ("pixart_block", 28, "nvfp4", 4096, 8,
+                     "BASELINE config 2: same step in NVFP4 W4A4 (E2M1 g16, UE4M3 group scales, fp32 tensor scale)"),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="pixart_int4", choices=sorted(WORKLOADS))
+    ap.add_argument("--blocks", type=int, default=0, help="override the number of blocks (smoke runs only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's fp32 fused-unrotation forward (oracle port), bounded sample
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_tflops(workload, steps, warmup, budget_s=20.0):
+    """Times dirotq_fused_unrotation._fused_forward (fp32 rotation + fake quant + nn.Linear), restated in
+    oracle/dirotq_oracle.py, on one block of the workload at M = 2048 tokens with all host threads."""
+    from oracle import dirotq_oracle as O
+    from dirotq_b200 import dit
+    blk_name, _, quant, _, _, _ = WORKLOADS[workload]
+    block = getattr(dit, blk_name)()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    M = 2048
+    g = torch.Generator().manual_seed(0)
+    x = O.synth_activations(M, block[0].in_f, g).reshape(1, M, -1)
+    specs = []
+    for ld in block:
+        W = (torch.randn(ld.out_f, ld.in_f, generator=g) * 0.02).to(torch.bfloat16)
+        b = (torch.randn(ld.out_f, generator=g) * 0.1).to(torch.bfloat16)
+        if ld.kind == "w4a16":
+            specs.append((ld, None, W, b))
+            continue
+        cfg = O.QuantCfg(4, 16 if quant == "nvfp4" else 64, True, 1.0, ld.tail, "nvfp4" if quant == "nvfp4" else "int")
+        U = O.random_orthogonal(ld.in_f, g).float() if ld.kind == "hidden" else None
+        specs.append((ld, O.LayerSpec(W, b, cfg, rotation=U), W, b))
+    ops = sum(dit.linear_ops(ld, M) for ld in block)
+
+    def one_pass():
+        ff = None
+        for ld, spec, W, b in specs:
+            src = x if ld.source == "x" else ff
+            if spec is None:
+                y = torch.nn.functional.linear(src, W, b)
+            else:
+                y = O.fused_forward(src, spec, fp32=True)
+            if ld.out_f > ld.in_f:
+                ff = torch.nn.functional.gelu(y, approximate="tanh") * 0.25
+        return y
+
+    for _ in range(max(1, warmup)):
+        one_pass()
+    times = []
+    t_all = time.perf_counter()
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_all > budget_s:
+            break
+    t = statistics.median(times)
+    return {"value": ops / t / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"one {blk_name} ({len(block)} linears) at M=2048 tokens, fp32 _fused_forward restated in "
+                      f"oracle/, torch CPU {cores} threads, median of {len(times)} passes ({t*1e3:.0f} ms each)"}, t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, t = cpu_reference_tflops(args.workload, args.steps, args.warmup, budget_s=120.0)
+    line = {"impl": "reference", "metric": "w4a4_linear_tflops", "value": cb["value"], "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOADS[args.workload][5], "sample": cb["sample"]},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                      stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+            out = ""
+        sm, mx, reasons, pw = [], [], set(), []
+        for ln in out.strip().splitlines():
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load = upper half by power
+        if sm:
+            order = sorted(range(len(sm)), key=lambda i: pw[i])
+            load = [sm[i] for i in order[len(order) // 2:]]
+            return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                    "samples": len(sm), "power_w_max": max(pw)}
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from dirotq_b200 import backend, dit, ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    blk_name, n_blocks, quant, tokens, batch, desc = WORKLOADS[args.workload]
+    if args.blocks:
+        n_blocks = args.blocks
+    block = getattr(dit, blk_name)()
+    M = tokens * batch                               # rows per GPU (weak scaling: fixed per-GPU batch)
+    D = block[0].in_f
+
+    backend.patch_forward()
+    step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
+    backend.preconvert_rotations_to_device(step, dev)
+    lin_ops, rot_ops = step.ops_per_step(M)
+
+    # step input: synthetic activations with the config-0 distribution, in PINNED host memory
+    g = torch.Generator().manual_seed(1234 + rank)
+    from dirotq_b200.synth import synth_activations
+    x_host = synth_activations(M, D, g).reshape(batch, tokens, D).pin_memory()
+    x_dev = x_host.to(dev, non_blocking=True)
+    y_host = torch.empty(batch, tokens, block[-1].out_f, dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def step_resident():
+        return step(x_dev)
+
+    def step_e2e():
+        xd = x_host.to(dev, non_blocking=True)       # host -> device copy of the step's input (pinned)
+        y = step(xd)
+        y_host.copy_(y.reshape(y_host.shape), non_blocking=True)   # device -> host read of the step's result
+        return y
+
+    for _ in range(max(3, args.warmup)):
+        step_resident()
+    ops.check_status(dev)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps) / args.steps
+    ops.check_status(dev)
+
+    # roofline pass: the same launches, the dominant kernel bracketed by CUDA events on its stream
+    roof = roofline_pass(step, x_dev, M, quant, dev, args.steps) if rank == 0 else None
+
+    cb = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cb, _ = cpu_reference_tflops(args.workload, 10, 1)
+
+    if rank == 0:
+        line = {
+            "metric": "w4a4_linear_tflops", "value": world * lin_ops / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e2m1" if quant == "nvfp4" else "s8", "data": "synthetic",
+            "config": {"workload": desc, "blocks": n_blocks, "rows_per_gpu": M, "global_batch": batch * world,
+                       "l2": "inputs larger than L2 (75 MB activations + 224 distinct weight sets per step)",
+                       "linear_gflop_per_step_per_gpu": lin_ops / 1e9, "rotation_gflop_per_step_per_gpu": rot_ops / 1e9},
+            "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+            "gpu_launches": step.kernel_launches_per_step() * args.steps,
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def roofline_pass(step, x_dev, M, quant, dev, steps):
+    """Runs the step's layers through the two C-ABI stages separately and brackets every launch of the
+    W4A4 GEMM (the kernel with the largest share of the step) with CUDA events on the launching stream."""
+    from dirotq_b200 import ops
+    hbm, bf16_burst, bf16_sust, which = measured_peaks()
+    pairs = []
+    bufs = {}
+    ops_total = 0.0
+    nb = len(step.block)
+    for _ in range(max(1, min(steps, 2))):
+        for idx, lyr in enumerate(step.layers):
+            ld = step.block[idx % nb]
+            st = getattr(lyr, "_b200_state", None)
+            if st is None or ld.source != "x":
+                continue
+            key = (st.fmt, M)
+            if key not in bufs:
+                bufs[key] = ops.alloc_act(st.fmt, M, dev)
+            buf = bufs[key]
+            x2d = x_dev.reshape(M, -1)
+            ops.rotate_quantize(x2d, st.rot_t, st.fmt, out=buf)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if quant == "nvfp4":
+                w = ops.PackedWeightNvfp4(st.out_features, st.layout.q_len, st.layout.n_chunks, st.w_tensor_scale,
+                                          st.w_codes, st.w_scales)
+                ops.gemm_w4a4_nvfp4(buf, w, st.w_tail, st.bias)
+            else:
+                w = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks,
+                                         st.w_codes, st.w_scales, st.w_sum)
+                ops.gemm_w4a4_int(buf, w, st.w_tail, st.bias)
+            e1.record()
+            pairs.append((e0, e1))
+            ops_total += 2.0 * M * ld.out_f * ld.in_f
+    torch.cuda.synchronize()
+    t_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    achieved = ops_total / (t_ms * 1e-3) / 1e12
+    return {"bound": "tensor", "kernel": "gemm_nvfp4_kernel" if quant == "nvfp4" else "gemm_int_kernel",
+            "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
+            "peak_source": f"{which}: cuBLAS bf16 sustained; dense INT8 is nominally 2x and FP4 4x that figure",
+            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None}
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

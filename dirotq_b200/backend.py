@@ -115,8 +115,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     fmt = _act_format(w)
     lay = ops.act_layout(fmt)
     fused = getattr(w, "_unrot_fused", False)
-    W = w.module.weight.data
-    N, D = W.shape
+    N, D = w.module.out_features, w.module.in_features
     dev = torch.device(device)
     rot_t = perm = None
     if fused and w.rotation is not None:
@@ -126,16 +125,20 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
         rot_t = torch.block_diag(*[U[h].t() for h in range(U.shape[0])]).contiguous().to(torch.bfloat16)
     elif fused and getattr(w, "perm_idx", None) is not None:
         perm = w.perm_idx.to(device=dev, dtype=torch.int64).contiguous()
-    # split the fused weight into the quantised block and the 16-bit tail (quant_utils.py:574-587, :659-685)
-    Wf = W.to(device=dev, dtype=torch.float32)
-    if fmt.num_heads > 0:
-        H, d, hl = fmt.num_heads, fmt.head_dim, fmt.tail_len
-        W3 = Wf.reshape(N, H, d)
-        w_low = W3[:, :, : d - hl].reshape(N, H * (d - hl)).contiguous()
-        w_tail = W3[:, :, d - hl:].reshape(N, H * hl).contiguous()
-    else:
-        w_low = Wf[:, : lay.q_len].contiguous()
-        w_tail = Wf[:, lay.q_len:].contiguous() if lay.tail_total else None
+    have_codes = bool(explicit) and ("codes" in explicit or "nibbles" in explicit)
+    have_tail = lay.tail_total == 0 or (bool(explicit) and "w_tail" in explicit)
+    w_low = w_tail = None
+    if not (have_codes and have_tail):
+        # split the fused weight into the quantised block and the 16-bit tail (quant_utils.py:574-587, :659-685)
+        Wf = w.module.weight.data.to(device=dev, dtype=torch.float32)
+        if fmt.num_heads > 0:
+            H, d, hl = fmt.num_heads, fmt.head_dim, fmt.tail_len
+            W3 = Wf.reshape(N, H, d)
+            w_low = W3[:, :, : d - hl].reshape(N, H * (d - hl)).contiguous()
+            w_tail = W3[:, :, d - hl:].reshape(N, H * hl).contiguous()
+        else:
+            w_low = Wf[:, : lay.q_len].contiguous()
+            w_tail = Wf[:, lay.q_len:].contiguous() if lay.tail_total else None
     if explicit and "w_tail" in explicit:
         w_tail = explicit["w_tail"].to(device=dev, dtype=torch.float32)
     n_lossy, Tw, w_sum = 0, 1.0, None
@@ -161,14 +164,53 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
         w_codes, w_scales, w_sum = pk.codes, pk.scales, pk.wsum
         wt = None if w_tail is None else w_tail.to(torch.bfloat16)
     w_tail_p = ops.pad_tail_weight(wt, lay.tail_pitch, N, dev)
-    bias = None if w.module.bias is None else w.module.bias.data.to(device=dev, dtype=torch.bfloat16).contiguous()
+    if explicit and "bias" in explicit:
+        bias = None if explicit["bias"] is None else explicit["bias"].to(device=dev, dtype=torch.bfloat16).contiguous()
+    else:
+        bias = None if w.module.bias is None else w.module.bias.data.to(device=dev, dtype=torch.bfloat16).contiguous()
     return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy)
+
+
+@dataclass
+class W4A16State:
+    """A layer whose activations stay 16-bit while its weight is 4-bit (bits == 16 under
+    --skip-quant-layers, e.g. PixArt ff.net.2)."""
+    w: ops.PackedWeightInt4
+    bias: Optional[torch.Tensor]
+    scratch: torch.Tensor
+
+
+def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int = 64) -> Optional[W4A16State]:
+    """Pack the 4-bit weight of an activation-unquantised layer, if its weight IS on a 4-bit grid."""
+    N, K = w.module.out_features, w.module.in_features
+    if K % 64 or N % 8 or group != 64:
+        return None
+    dev = torch.device(device)
+    if explicit and "codes" in explicit:
+        pk = pack.convert_dirotq_low_weight_to_b200(None, 64, scales=explicit["scales"], codes=explicit["codes"])
+        bias = explicit.get("bias")
+    else:
+        W = w.module.weight.data.to(device=dev, dtype=torch.float32)
+        rec = pack.recover_int4_grid(W, 64)
+        if rec.n_lossy:
+            return None            # a genuine 16-bit layer: stays an nn.Linear
+        pk = ops.pack_weight_int4(W, 64, scales=rec.scales.to(dev))
+        bias = w.module.bias.data if w.module.bias is not None else None
+    bias = None if bias is None else bias.to(device=dev, dtype=torch.bfloat16).contiguous()
+    n = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(N, K))
+    return W4A16State(pk, bias, torch.empty(n, dtype=torch.uint8, device=dev))
 
 
 def _fused_forward_b200(self, x):
     """ActQuantWrapper.forward on the B200 kernels (contract: dirotq_fused_unrotation_fast.py:56-141)."""
     if self.quantizer.bits >= 16:
-        return self.module(x).to(x.dtype)
+        s16 = getattr(self, "_b200_w4a16", None)
+        if s16 is None:
+            return self.module(x).to(x.dtype)
+        shp = x.shape
+        x2d = x.reshape(-1, shp[-1]).to(torch.bfloat16).contiguous()
+        y = ops.gemm_w4a16(x2d, s16.w, s16.bias, workspace=s16.scratch)
+        return y.reshape(*shp[:-1], s16.w.N).to(x.dtype)
     st = getattr(self, "_b200_state", None)
     if st is None:
         st = prepare_layer(self, x.device, getattr(self, "_b200_explicit", None))
@@ -206,7 +248,12 @@ def preconvert_rotations_to_device(transformer, device="cuda", dtype=None):
     classes = tuple(_wrapper_classes())
     n = 0
     for _, mod in transformer.named_modules():
-        if not isinstance(mod, classes) or mod.quantizer.bits >= 16:
+        if not isinstance(mod, classes):
+            continue
+        if mod.quantizer.bits >= 16:
+            s16 = prepare_w4a16(mod, device, getattr(mod, "_b200_explicit", None))
+            if s16 is not None:
+                object.__setattr__(mod, "_b200_w4a16", s16)
             continue
         st = prepare_layer(mod, device, getattr(mod, "_b200_explicit", None))
         object.__setattr__(mod, "_b200_state", st)

@@ -55,7 +55,9 @@ struct RotArgs {
   int BN;
   int n_tiles;
   int m_tiles;
+  int K;                  // contraction length (== g.D for a rotation)
   int band;               // 0 = dense rotation, else head_dim of a block-diagonal rotation
+  const __nv_bfloat16* bias;  // plain-GEMM epilogue only
   __nv_bfloat16* x_rot;   // optional [M, D]
   uint8_t* codes;
   __nv_bfloat16* scales;
@@ -114,6 +116,10 @@ int launch_pack_int4(const PackIntArgs& a, cudaStream_t st);
 int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st);
 int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, int64_t M, RotArgs a, cudaStream_t st);
 int num_sms();
+int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64_t K, const void* bias, void* y,
+                     int* status, cudaStream_t st);
+int launch_dequant_int4(const uint8_t* codes, const float* scales, int64_t N, int n_chunks, int64_t ldn,
+                        __nv_bfloat16* w, cudaStream_t st);
 
 
 }  // namespace dq

@@ -136,4 +136,40 @@ int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
+// Packed INT4 weight -> bf16 [N, n_chunks*64] (q * scale rounded once), the operand of the W4A16 GEMM.
+// One thread = one block of 32 code slots.
+__global__ void __launch_bounds__(256) dequant_int4_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales,
+                                                           int64_t N, int n_chunks, int64_t ldn, __nv_bfloat16* __restrict__ w) {
+  const int bpr = n_chunks * 2;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= N * bpr) return;
+  const int64_t n = tid / bpr;
+  const int b = (int)(tid - n * bpr);
+  const uint4 p = __ldg(reinterpret_cast<const uint4*>(codes + n * (int64_t)(n_chunks * 32) + (int64_t)b * 16));
+  const float s = __ldg(scales + (int64_t)(b >> 1) * ldn + n);
+  const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
+  __nv_bfloat16 out[32];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t byte = (pw[i] >> (8 * j)) & 0xFF;
+      const int lo = (int)((byte & 0xF) ^ 8) - 8, hi = (int)((byte >> 4) ^ 8) - 8;
+      out[4 * i + j] = __float2bfloat16_rn((float)lo * s);
+      out[16 + 4 * i + j] = __float2bfloat16_rn((float)hi * s);
+    }
+  uint4* dst = reinterpret_cast<uint4*>(w + n * (int64_t)(n_chunks * 64) + (int64_t)b * 32);
+  const uint4* src = reinterpret_cast<const uint4*>(out);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) dst[i] = src[i];
+}
+
+int launch_dequant_int4(const uint8_t* codes, const float* scales, int64_t N, int n_chunks, int64_t ldn,
+                        __nv_bfloat16* w, cudaStream_t st) {
+  const int64_t total = N * n_chunks * 2;
+  if (total <= 0) return DIROTQ_OK;
+  dequant_int4_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(codes, scales, N, n_chunks, ldn, w);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
 }  // namespace dq

@@ -35,7 +35,7 @@ enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT
 
 
 __device__ __forceinline__ void tile_k_range(const RotArgs& a, int nb, int& kb, int& ke) {
-  const int kchunks = (a.g.D + 63) / 64;
+  const int kchunks = (a.K + 63) / 64;
   if (a.band == 0) { kb = 0; ke = kchunks; return; }
   const int n0 = nb * a.BN;
   const int n1 = min(n0 + a.BN, a.g.D);
@@ -338,6 +338,8 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
   }
 }
 
+// Plain GEMM epilogue: y[M, N] = acc (+ bias) as bf16; used for the stand-alone rotation and for
+// the bf16 GEMM behind the W4A16 layer.
 __device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
@@ -350,12 +352,16 @@ __device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, i
     if (row_ok) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        if (col + 8 * i + 8 <= g.D)
+        if (col + 8 * i + 8 <= g.D) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            f[e] = __uint_as_float(r[8 * i + e]);
+            if (a.bias) f[e] += __bfloat162float(a.bias[col + 8 * i + e]);
+          }
           *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) =
-              make_uint4(pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                         pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                         pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                         pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+              make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        }
     }
   }
 }
@@ -534,6 +540,8 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
   if (M <= 0) return DIROTQ_OK;
   a.g = g;
   a.M = M;
+  a.K = g.D;
+  a.bias = nullptr;
   a.ldm = ld_rows(M);
   a.BN = pick_bn(g);
   if (a.BN <= 0) return DIROTQ_E_UNSUPPORTED;
@@ -570,6 +578,32 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
     case DIROTQ_NVFP4_HW: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_HW>(tx, tu, a, st);
   }
   return DIROTQ_E_UNSUPPORTED;
+}
+
+// y[M, N] = x[M, K] @ w_t[N, K]^T (+ bias), all bf16, fp32 accumulation on tcgen05.
+int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64_t K, const void* bias, void* y,
+                     int* status, cudaStream_t st) {
+  if (M <= 0) return DIROTQ_OK;
+  if (N % 8 || K % 8) return DIROTQ_E_UNSUPPORTED;
+  RotArgs a{};
+  a.g = ActGeom{};
+  a.g.D = (int)N;
+  a.M = M;
+  a.K = (int)K;
+  a.ldm = ld_rows(M);
+  a.BN = pick_bn(a.g);
+  a.n_tiles = ceil_div((int)N, a.BN);
+  a.m_tiles = (int)((M + 127) / 128);
+  a.band = 0;
+  a.x_rot = static_cast<__nv_bfloat16*>(y);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.status = status;
+  CUtensorMap tx, tu;
+  int rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_t, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, (uint32_t)a.BN);
+  if (rc) return rc;
+  return launch_rq<EPI_ROT_ONLY, 0>(tx, tu, a, st);
 }
 
 }  // namespace dq

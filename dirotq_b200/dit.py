@@ -1,0 +1,175 @@
+"""Layer census of the DiT families the quantized-linear path runs in, and a builder of
+random-initialised wrapped linears with those shapes.
+
+Shapes follow the reference's model adapters (models/pixart-sigma/model_utils.py:164-290,
+models/flux-schnell/model_utils.py, models/sana-1.6b/model_utils.py, models/*/config.yaml:6-11):
+which linears are wrapped, which rotation they get (hidden [D,D] or per-head [H,d,d]) and how many
+PCA coefficients stay 16-bit.  Weights are synthetic (random codes + scales): calibrated checkpoints
+are not redistributable.  Every linear is an ActQuantWrapper, run through the patched forward.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from .wrapper import ActQuantWrapper
+
+
+@dataclass(frozen=True)
+class LayerDef:
+    name: str
+    in_f: int
+    out_f: int
+    kind: str = "hidden"        # "hidden" | "perhead" | "w4a16" | "norot"
+    tail: int = 0               # hidden: total 16-bit channels; perhead: per head
+    heads: int = 0
+    head_dim: int = 0
+    source: str = "x"           # which activation feeds it: "x" (block input) or "ff" (FFN hidden)
+
+
+def pixart_block(k: int = 64, per_head_out: bool = False) -> List[LayerDef]:
+    """One PixArt-Sigma block: hidden 1152, 16 heads x 72, FFN 4608 (config.yaml:6-11).  k = 16-bit
+    PCA coefficients of the hidden-rotation layers; ff.net.2 runs W4A16 (activations not quantised)."""
+    out_kw = dict(kind="perhead", tail=9, heads=16, head_dim=72) if per_head_out else dict(kind="hidden", tail=k)
+    return [
+        LayerDef("attn1.to_q", 1152, 1152, tail=k), LayerDef("attn1.to_k", 1152, 1152, tail=k),
+        LayerDef("attn1.to_v", 1152, 1152, tail=k), LayerDef("attn1.to_out.0", 1152, 1152, **out_kw),
+        LayerDef("attn2.to_q", 1152, 1152, tail=k), LayerDef("attn2.to_out.0", 1152, 1152, **out_kw),
+        LayerDef("ff.net.0.proj", 1152, 4608, tail=k),
+        LayerDef("ff.net.2", 4608, 1152, kind="w4a16", source="ff"),
+    ]
+
+
+def flux_double_block(k: int = 384, k_down: int = 1536, rotate_down: bool = False) -> List[LayerDef]:
+    """One FLUX double-stream block, image stream (the text stream has the same linears at M_txt)."""
+    down = LayerDef("ff.net.2", 12288, 3072, kind="hidden" if rotate_down else "norot", tail=k_down, source="ff")
+    return [LayerDef("attn.to_q", 3072, 3072, tail=k), LayerDef("attn.to_k", 3072, 3072, tail=k),
+            LayerDef("attn.to_v", 3072, 3072, tail=k), LayerDef("attn.to_out.0", 3072, 3072, tail=k),
+            LayerDef("ff.net.0.proj", 3072, 12288, tail=k), down]
+
+
+def flux_single_block(k: int = 384, k_down: int = 1536) -> List[LayerDef]:
+    return [LayerDef("attn.to_q", 3072, 3072, tail=k), LayerDef("attn.to_k", 3072, 3072, tail=k),
+            LayerDef("attn.to_v", 3072, 3072, tail=k), LayerDef("proj_mlp", 3072, 12288, tail=k),
+            LayerDef("proj_out.linears.0", 3072, 3072, tail=k),
+            LayerDef("proj_out.linears.1", 12288, 3072, kind="norot", tail=k_down, source="ff")]
+
+
+def sana_block(k: int = 320) -> List[LayerDef]:
+    """One SANA-1.6B block: hidden 2240, 70 heads x 32; the Mix-FFN convolutions are not quantised."""
+    ph = dict(kind="perhead", tail=4, heads=70, head_dim=32)
+    return [LayerDef("attn1.to_q", 2240, 2240, tail=k), LayerDef("attn1.to_k", 2240, 2240, tail=k),
+            LayerDef("attn1.to_v", 2240, 2240, tail=k), LayerDef("attn1.to_out.0", 2240, 2240, **ph),
+            LayerDef("attn2.to_q", 2240, 2240, tail=k), LayerDef("attn2.to_out.0", 2240, 2240, **ph)]
+
+
+def linear_ops(ld: LayerDef, M: int) -> float:
+    """Algorithmic operations of the linear itself (4-bit part + 16-bit branch): 2 M N D."""
+    return 2.0 * M * ld.in_f * ld.out_f
+
+
+def rotation_ops(ld: LayerDef, M: int) -> float:
+    if ld.kind == "hidden":
+        return 2.0 * M * ld.in_f * ld.in_f
+    if ld.kind == "perhead":
+        return 2.0 * M * ld.heads * ld.head_dim * ld.head_dim
+    return 0.0
+
+
+def _random_orthogonal(n: int, gen: torch.Generator, device) -> torch.Tensor:
+    """QR of a seeded Gaussian with the sign fix of the reference (utils/hadamard_utils.py:13-28)."""
+    a = torch.randn(n, n, generator=gen, device=device, dtype=torch.float32)
+    q, r = torch.linalg.qr(a)
+    return q * torch.sign(torch.diagonal(r)).unsqueeze(0)
+
+
+def make_wrapped_linear(ld: LayerDef, quant: str, seed: int, device="cuda", a_sym: bool = True) -> ActQuantWrapper:
+    """quant: "int4" (group 64, W4A4), "int8" (W4A8 asymmetric) or "nvfp4" (group 16, E4M3 scales)."""
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    lin = nn.Linear(ld.in_f, ld.out_f, bias=True, device="meta", dtype=torch.bfloat16)
+    w = ActQuantWrapper(lin)
+    N, D = ld.out_f, ld.in_f
+    bias = (torch.randn(N, generator=gen, device=dev) * 0.1).to(torch.bfloat16)
+    if ld.kind == "w4a16":
+        w.quantizer.configure(bits=16, groupsize=-1, sym=True)
+        codes = torch.randint(-8, 8, (N, D), generator=gen, device=dev)
+        scales = (torch.rand(N, D // 64, generator=gen, device=dev) * 0.015 + 0.005).to(torch.float16).float()
+        w._b200_explicit = {"codes": codes, "scales": scales, "bias": bias}
+        return w
+    if ld.kind == "perhead":
+        H, d = ld.heads, ld.head_dim
+        w.rotation_per_head = torch.stack([_random_orthogonal(d, gen, dev) for _ in range(H)])
+        w.num_heads, w.head_dim = H, d
+        n_low, group, tail_total = H * (d - ld.tail), d - ld.tail, H * ld.tail
+    else:
+        if ld.kind == "hidden":
+            w.rotation = _random_orthogonal(D, gen, dev)
+        tail_total = ld.tail
+        n_low = D - ld.tail
+        group = 16 if quant == "nvfp4" else 64
+    w._unrot_fused = True
+    w_tail = (torch.randn(N, tail_total, generator=gen, device=dev) * 0.02) if tail_total else None
+    if quant == "nvfp4":
+        assert ld.kind != "perhead", "per-head layers run INT4 (their groups are not multiples of 16)"
+        w.quantizer.configure(bits=4, groupsize=16, high_bits_length=ld.tail, quant_dtype="nvfp4")
+        nib = torch.randint(0, 16, (N, n_low), generator=gen, device=dev).to(torch.uint8)
+        s = torch.exp(torch.randn(N, (n_low + 15) // 16, generator=gen, device=dev) * 0.5 - 4.0)
+        from .pack import pow2_tensor_scale
+        T = pow2_tensor_scale(float(s.max()))
+        micro = (s / T).clamp(min=2.0 ** -9, max=448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        w._b200_explicit = {"nibbles": nib, "scales_e4m3": micro, "tensor_scale": T, "bias": bias}
+    else:
+        bits = 8 if quant == "int8" else 4
+        w.quantizer.configure(bits=bits, groupsize=group, sym=(a_sym and bits == 4), high_bits_length=ld.tail,
+                              quant_dtype="int")
+        codes = torch.randint(-8, 8, (N, n_low), generator=gen, device=dev)
+        scales = (torch.rand(N, (n_low + group - 1) // group, generator=gen, device=dev) * 0.015 + 0.005)
+        w._b200_explicit = {"codes": codes, "scales": scales.to(torch.float16).float(), "bias": bias}
+    if w_tail is not None:
+        w._b200_explicit["w_tail"] = w_tail
+    return w
+
+
+class LinearPathStep(nn.Module):
+    """All wrapped linears of one denoising step of a DiT, run in block order on the block input
+    (and, for FFN down-projections, on the activated up-projection output).  Attention, norms and
+    modulation are outside the quantized-linear path and are not part of this step."""
+
+    def __init__(self, block: List[LayerDef], n_blocks: int, quant: str, device="cuda", seed: int = 1000,
+                 a_sym: bool = True):
+        super().__init__()
+        self.block = block
+        self.n_blocks = n_blocks
+        self.layers = nn.ModuleList()
+        for b in range(n_blocks):
+            for i, ld in enumerate(block):
+                q = "int4" if (quant == "nvfp4" and ld.kind == "perhead") else quant
+                self.layers.append(make_wrapped_linear(ld, q, seed + b * len(block) + i, device, a_sym))
+
+    def ops_per_step(self, M: int):
+        lin = sum(linear_ops(ld, M) for ld in self.block) * self.n_blocks
+        rot = sum(rotation_ops(ld, M) for ld in self.block) * self.n_blocks
+        return lin, rot
+
+    def kernel_launches_per_step(self) -> int:
+        return 2 * len(self.block) * self.n_blocks      # rotate/quantise (or dequantise) + GEMM per linear
+
+    def forward(self, x: torch.Tensor, ff_scale: float = 0.25) -> torch.Tensor:
+        y = x
+        nb = len(self.block)
+        for b in range(self.n_blocks):
+            ff = None
+            for i, ld in enumerate(self.block):
+                lyr = self.layers[b * nb + i]
+                if ld.source == "ff":
+                    y = lyr(ff)
+                else:
+                    y = lyr(x)
+                    if ld.out_f != ld.in_f and ld.out_f > ld.in_f:
+                        ff = torch.nn.functional.gelu(y, approximate="tanh")
+                        ff.mul_(ff_scale)
+        return y

@@ -3,7 +3,7 @@
  * The reference project is pure Python and has no native ABI; each entry point below names the
  * reference code it replaces (paths inside the DiRotQ project).  All pointers are DEVICE pointers
  * unless the name ends in `_host`.  `stream` is a cudaStream_t passed as void*.  The library never
- * allocates, frees or caches device memory (one exception, documented at its declaration).
+ * allocates, frees or caches device memory: every buffer, scratch included, is the caller's.
  *
  * Return value: 0 = launched, < 0 = argument rejected on the host before any launch (see
  * dirotq_error_string).  Device-side bounded waits that run out write a positive code into the
@@ -164,11 +164,15 @@ int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x
                            const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
                            void* y, int32_t* status, void* stream);
 
-/* W4A16: bf16 activations x INT4 group-quantised weights (PixArt ff.net.2 under
- * --skip-quant-layers; forward model: speedup/weight_only_nvfp4.py:128-178).  Weights in the
- * dirotq_pack_weight_int4 format (group 64). */
+/* W4A16: bf16 activations x INT4 group-64 weights (PixArt ff.net.2 under --skip-quant-layers; the
+ * reference's model of this layer is dequantise-then-GEMM, speedup/weight_only_nvfp4.py:128-178).
+ * Weights in the dirotq_pack_weight_int4 format with group 64 (K = n_chunks * 64).  The weight is
+ * dequantised to bf16 into `workspace` (N * K * 2 bytes, caller-owned scratch, 16-byte aligned) and
+ * multiplied on the bf16 tensor cores; x bf16 [M, K], y bf16 [M, N]. */
+size_t dirotq_gemm_w4a16_workspace_bytes(int64_t N, int64_t K);
 int dirotq_gemm_w4a16(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const float* w_scales,
-                      const void* bias, void* y, int32_t* status, void* stream);
+                      const void* bias, void* y, void* workspace, size_t workspace_bytes, int32_t* status,
+                      void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * One wrapped linear end to end: what the patched ActQuantWrapper.forward runs
