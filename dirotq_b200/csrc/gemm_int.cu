@@ -11,8 +11,8 @@
 //                  sign-extended value times 16: two logic ops per 8 codes, the power-of-two factor is
 //                  folded into the activation scale), written in the 128-byte-swizzled K-major layout
 //   UMMA issuer    tcgen05.mma kind::i8, two K=32 instructions per chunk -> 128 x 128 int32 in TMEM;
-//                  two accumulators alternate
-//   8 epilogue warps  tcgen05.ld, exact int -> float, * ws[c,n] * xs[c,m], fp32 accumulate in registers
+//                  four accumulators rotate, so the issuer runs ahead of the drain
+//   16 epilogue warps tcgen05.ld, exact int -> float, * ws[c,n] * xs[c,m], fp32 accumulate in registers
 //   tail           bf16 TMA tiles straight into the expanded ring, kind::f16 UMMAs, added last
 //
 // Replaces the inner `self.module(x)` of the fused forward (DiRotQ
@@ -36,7 +36,8 @@ constexpr int GI_AUX_BYTES = 4 * 2 * 128 * 4;            // sw, sx, wsum, xz : [
 constexpr int GI_EXP_STAGE_BYTES = 2 * GI_TILE_BYTES + GI_AUX_BYTES;   // 36864
 constexpr int GI_RAW_B_BYTES = 128 * 64;
 constexpr int GI_RAW_AUX_BYTES = 1024 + 1024 + 512 + 512;   // ws, wsum (fp32 [2][128]); xs, xz (bf16 [2][128])
-constexpr int GI_EPI_WARPS = 8;
+constexpr int GI_EPI_WARPS = 16;                       // 4 lane quarters x 4 column quarters
+constexpr int GI_NACC = 4;                             // TMEM accumulators of 128 columns in flight
 constexpr int GI_CONV_WARPS = 2;
 constexpr int GI_THREADS = (GI_EPI_WARPS + 2 + GI_CONV_WARPS) * 32;     // 384
 constexpr int GI_CONV_THREADS = GI_CONV_WARPS * 32;
@@ -77,8 +78,8 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_area = smem + GI_EXP_STAGES * GI_EXP_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw_area + GI_RAW_STAGES * Cfg::RAW_STAGE_BYTES);
-  // barriers: raw_full[R], raw_empty[R], exp_full[E], exp_empty[E], acc_full[2], acc_empty[2]
-  constexpr int NB = 2 * GI_RAW_STAGES + 2 * GI_EXP_STAGES + 4;
+  // barriers: raw_full[R], raw_empty[R], exp_full[E], exp_empty[E], acc_full[NACC], acc_empty[NACC]
+  constexpr int NB = 2 * GI_RAW_STAGES + 2 * GI_EXP_STAGES + 2 * GI_NACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NB);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -89,19 +90,19 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   auto expf_bar = [&](int s) { return bar0 + 8u * (2 * GI_RAW_STAGES + s); };
   auto expe_bar = [&](int s) { return bar0 + 8u * (2 * GI_RAW_STAGES + GI_EXP_STAGES + s); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (2 * GI_RAW_STAGES + 2 * GI_EXP_STAGES + b); };
-  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * GI_RAW_STAGES + 2 * GI_EXP_STAGES + 2 + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * GI_RAW_STAGES + 2 * GI_EXP_STAGES + GI_NACC + b); };
 
   constexpr int W_MMA = GI_EPI_WARPS, W_TMA = GI_EPI_WARPS + 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < GI_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), GI_CONV_WARPS); }
     for (int s = 0; s < GI_EXP_STAGES; ++s) { mbar_init(expf_bar(s), GI_CONV_WARPS); mbar_init(expe_bar(s), 1 + GI_EPI_WARPS); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GI_EPI_WARPS); }
+    for (int b = 0; b < GI_NACC; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GI_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm.xq);
     prefetch_tmap(&tm.wq);
   }
-  if (warp == W_MMA) tmem_alloc(smem_u32(tmem_slot), 256);
+  if (warp == W_MMA) tmem_alloc(smem_u32(tmem_slot), 128 * GI_NACC);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -257,7 +258,7 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       const uint32_t idesc_i8 = idesc_dense(ACC_S32, ASYM ? FMT_U8 : FMT_S8, FMT_S8, 128, 128);
       const uint32_t idesc_bf = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, 128);
       RingN<GI_EXP_STAGES> e;
-      int use = 0;   // accumulator uses so far: buffer = use & 1, phase = (use >> 1) & 1
+      int use = 0;   // accumulator uses so far: buffer = use % NACC, phase = (use / NACC) & 1
       bool ok = true;
       for (int st = 0; st < n_main && ok; ++st) {
         if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
@@ -266,8 +267,8 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
         const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + GI_TILE_BYTES);
         for (int c = 0; c < 2; ++c) {
           if (st * 2 + c >= a.n_chunks) break;
-          const int buf = use & 1;
-          if (!mbar_wait(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+          const int buf = use % GI_NACC;
+          if (!mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d = tmem_base + buf * 128;
           umma_i8(d, adesc + 4 * c, bdesc + 4 * c, idesc_i8, 0u);
@@ -279,8 +280,8 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
         e.next();
       }
       if (ok && n_tail > 0) {
-        const int buf = use & 1;
-        if (mbar_wait(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) {
+        const int buf = use % GI_NACC;
+        if (mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) {
           tc_fence_after();
           const uint32_t d = tmem_base + buf * 128;
           for (int st = 0; st < n_tail; ++st) {
@@ -298,14 +299,15 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       }
     }
   } else {
-    // ------------------------------ epilogue: 8 warps ----------------------------------------
-    const int q = warp & 3, half = warp >> 2;
+    // ------------------------------ epilogue: 16 warps ---------------------------------------
+    // warp w: TMEM lane quarter w & 3 (rows), column quarter w >> 2 (32 of the tile's 128 columns)
+    const int q = warp & 3, cq = warp >> 2;
     const int trow = q * 32 + lane;                       // row inside the tile
     const int64_t row = (int64_t)m0 + trow;
-    const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + half * 64;
-    float acc[64];
+    const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + cq * 32;
+    float acc[32];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+    for (int j = 0; j < 32; ++j) acc[j] = 0.f;
     RingN<GI_EXP_STAGES> e;
     int use = 0;
     bool ok = true;
@@ -314,33 +316,33 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       const float* aux = reinterpret_cast<const float*>(smem + e.s * GI_EXP_STAGE_BYTES + 2 * GI_TILE_BYTES);
       for (int c = 0; c < 2; ++c) {
         if (st * 2 + c >= a.n_chunks) break;
-        const int buf = use & 1;
-        if (!mbar_wait(accf_bar(buf), (use >> 1) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
+        const int buf = use % GI_NACC;
+        if (!mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
+        __syncwarp();
         tc_fence_after();
-        uint32_t v[64];
+        uint32_t v[32];
         tmem_ld32(tlane + buf * 128, v);
-        tmem_ld32(tlane + buf * 128 + 32, v + 32);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acce_bar(buf));
         ++use;
         const float sx = aux[256 + c * 128 + trow];
-        const float4* sw4 = reinterpret_cast<const float4*>(aux + c * 128 + half * 64);
-        const float4* ws4 = reinterpret_cast<const float4*>(aux + 512 + c * 128 + half * 64);
+        const float4* sw4 = reinterpret_cast<const float4*>(aux + c * 128 + cq * 32);
+        const float4* ws4 = reinterpret_cast<const float4*>(aux + 512 + c * 128 + cq * 32);
         float zf = 0.f;
         if constexpr (ASYM) zf = aux[768 + c * 128 + trow];
         if (a.acc_dump) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
+          for (int j = 0; j < 32; ++j) {
             float f = __int_as_float((int)v[j] + 0x4B400000) - 12582912.f;
-            if constexpr (ASYM) f = __fmaf_rn(-zf, aux[512 + c * 128 + half * 64 + j], f);
-            if (row < a.M && n0 + half * 64 + j < a.N)
-              a.acc_dump[((int64_t)(st * 2 + c) * a.M + row) * a.N + n0 + half * 64 + j] = (int)(f * INV_F);
+            if constexpr (ASYM) f = __fmaf_rn(-zf, aux[512 + c * 128 + cq * 32 + j], f);
+            if (row < a.M && n0 + cq * 32 + j < a.N)
+              a.acc_dump[((int64_t)(st * 2 + c) * a.M + row) * a.N + n0 + cq * 32 + j] = (int)(f * INV_F);
           }
         }
 #pragma unroll
-        for (int j4 = 0; j4 < 16; ++j4) {
+        for (int j4 = 0; j4 < 8; ++j4) {
           const float4 s4 = sw4[j4];
           float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
           if constexpr (ASYM) w4 = ws4[j4];
@@ -367,24 +369,24 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
         if (lane == 0) mbar_arrive(expe_bar(e.s));
         e.next();
       }
-      const int buf = use & 1;
-      if (ok && mbar_wait(accf_bar(buf), (use >> 1) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) {
+      const int buf = use % GI_NACC;
+      if (ok && mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) {
+        __syncwarp();
         tc_fence_after();
-        uint32_t v[64];
+        uint32_t v[32];
         tmem_ld32(tlane + buf * 128, v);
-        tmem_ld32(tlane + buf * 128 + 32, v + 32);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 64; ++j) acc[j] += __uint_as_float(v[j]);
+        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
       } else {
         ok = false;
       }
     }
     if (ok && row < a.M) {
-      const int64_t col0 = (int64_t)n0 + half * 64;
+      const int64_t col0 = (int64_t)n0 + cq * 32;
       __nv_bfloat16* yr = a.y + row * a.N + col0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         if (col0 + 8 * i + 8 <= a.N) {
           float b[8];
           if (a.bias) {
@@ -412,7 +414,7 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   if (warp == W_MMA) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 128 * GI_NACC);
   }
 }
 

@@ -1,8 +1,9 @@
 // Activation-quantiser arithmetic, one operation at a time with explicit rounding, so that codes,
 // scales and zero points are bit-identical to what torch computes for the reference expressions
 // (DiRotQ utils/quant_utils.py:63-85, :148-180, :201-216) on a bf16 (or fp32) tensor.
-// No fused multiply-add, no reciprocal tricks: every step is an IEEE round-to-nearest operation
-// followed, in bf16 mode, by a round to bf16 -- exactly the sequence of eager tensor ops.
+// Every step is an IEEE round-to-nearest operation followed, in bf16 mode, by a round to bf16 --
+// exactly the sequence of eager tensor ops.  The "fast" forms further down replace the per-element
+// divide by a guarded reciprocal multiply that is proven bit-identical (see div_round_bf16).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -47,6 +48,36 @@ __device__ __forceinline__ int int_sym_code(float x, float scale, float maxq) {
   q = fminf(fmaxf(q, -maxq - 1.f), maxq);
   return (int)q;
 }
+// ---- fast exact forms used by the fused kernel's epilogue ---------------------------------------
+// bf16_rn(fl32(x / s)) without a divide per element: multiply by the correctly rounded reciprocal
+// (one per group) and fall back to the IEEE divide only when the approximate quotient lies within
+// 3 fp32 ulps of a bf16 rounding boundary (low half in [0x7FFD, 0x8003], probability ~1e-4), where
+// the <= 2 ulp error of the product could change the bf16 result.  Bit-identical to the slow form.
+__device__ __forceinline__ float div_round_bf16(float x, float s, float rcp_s) {
+  float qa = __fmul_rn(x, rcp_s);
+  const uint32_t b = __float_as_uint(qa);
+  if (((b + 0x8003u) & 0xFFFFu) <= 6u) qa = __fdiv_rn(x, s);
+  return __bfloat162float(__float2bfloat16_rn(qa));
+}
+// round-half-even of a bf16-valued float: the 1.5 * 2^23 trick below 2^22, identity above (bf16
+// values >= 256 are integers already)
+__device__ __forceinline__ float rint_small(float r) { return (r + 12582912.f) - 12582912.f; }
+__device__ __forceinline__ float rint_bf16(float r) { return fabsf(r) < 4194304.f ? rint_small(r) : r; }
+// two's-complement nibble of an integer-valued float in [-8, 7] (or the byte of one in [0, 255])
+__device__ __forceinline__ uint32_t int_bits(float c) { return __float_as_uint(c + 12582912.f); }
+
+__device__ __forceinline__ uint32_t int_sym_nibble_fast(float x, float s, float rcp_s) {
+  float r = div_round_bf16(x, s, rcp_s);
+  r = fminf(fmaxf(r, -8.f), 7.f);          // clamp commutes with round-half-even for integer bounds
+  return int_bits(r) & 0xFu;               // the add rounds half-even, the low mantissa bits are the code
+}
+__device__ __forceinline__ uint32_t int_asym_code_fast(float x, float s, float rcp_s, float zero, float maxq) {
+  float r = rint_bf16(div_round_bf16(x, s, rcp_s));
+  float q = __bfloat162float(__float2bfloat16_rn(__fadd_rn(r, zero)));
+  q = fminf(fmaxf(q, 0.f), maxq);
+  return int_bits(q) & 0xFFu;
+}
+
 // quant_utils.py:211-215
 template <bool BF16>
 __device__ __forceinline__ GroupParams int_asym_params(float mx, float mn, float clip, float maxq) {

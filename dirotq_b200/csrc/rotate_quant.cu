@@ -6,7 +6,7 @@
 //   point, 4-bit (or 8-bit) codes, packed 16-byte stores.  The rotated tensor never touches HBM.
 //
 // Persistent, warp-specialised: warp 0 = TMA producer, warp 1 = UMMA issuer (owns TMEM),
-// warps 2..5 = epilogue (one TMEM lane quarter each).  Two TMEM accumulators of 256 columns let
+// warps 2..9 = epilogue (two per TMEM lane quarter, alternating over the 64-column groups).  Two TMEM accumulators of 256 columns let
 // the epilogue of tile i overlap the main loop of tile i+1.  Tiles are 128 rows x BN columns of
 // the rotated tensor; consecutive tiles share the x row-block, so x and the rotation stay in L2.
 //
@@ -28,7 +28,8 @@ constexpr int RQ_STAGES = 4;
 constexpr int RQ_A_BYTES = 128 * 128;           // 128 rows x 64 bf16
 constexpr int RQ_B_BYTES = 256 * 128;           // up to 256 rows x 64 bf16
 constexpr int RQ_STAGE_BYTES = RQ_A_BYTES + RQ_B_BYTES;
-constexpr int RQ_THREADS = 192;
+constexpr int RQ_EPI_WARPS = 8;                 // two per TMEM lane quarter
+constexpr int RQ_THREADS = (2 + RQ_EPI_WARPS) * 32;
 constexpr int RQ_SMEM_BYTES = RQ_STAGES * RQ_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
 enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3 };
@@ -62,53 +63,65 @@ __device__ __forceinline__ uint4 pack_planar32(const uint32_t* q) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// ---- epilogues: thread = one row of the tile; `taddr` already points at this warp's lanes ----
+// ---- epilogues: thread = one row of the tile; `taddr` already points at this warp's lanes.
+// Two warps share a lane quarter; `turn` counts work items (64-column chunks, heads) across tiles
+// and a warp takes the items whose parity equals its `half`, which balances odd counts per tile.
 template <int MODE>
-__device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+__device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
   for (int c0 = 0; c0 < a.BN; c0 += 64) {
     const int col = n0 + c0;
     if (col >= g.D) break;
+    if (((turn++) & 1u) != (uint32_t)half) continue;
     uint32_t r[64];
     tmem_ld32(taddr + c0, r);
     tmem_ld32(taddr + c0 + 32, r + 32);
     tmem_wait_ld();
+    // round the fp32 accumulators to bf16: this IS x_rot of the reference's bf16 forward
+    uint32_t xb[32];     // bf16x2 pairs
     float v[64];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) v[j] = rnd<true>(__uint_as_float(r[j]));
+    for (int j = 0; j < 32; ++j) {
+      xb[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+      v[2 * j] = __uint_as_float(xb[j] << 16);
+      v[2 * j + 1] = __uint_as_float(xb[j] & 0xFFFF0000u);
+    }
     if (a.x_rot && row_ok) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (col + 8 * i + 8 <= g.D) {
-          uint4 o = make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
-                               pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
-          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) = o;
-        }
-      }
+      for (int i = 0; i < 8; ++i)
+        if (col + 8 * i + 8 <= g.D)
+          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) = make_uint4(xb[4 * i], xb[4 * i + 1], xb[4 * i + 2], xb[4 * i + 3]);
     }
     if (!a.codes) continue;
     const int nq = max(0, min(64, g.q_len - col));
     if (nq > 0) {
       const int chunk = col >> 6;
       float mx = -INFINITY, mn = INFINITY;
+      if (nq == 64) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j)
-        if (j < nq) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
-      if (nq < 64) { mx = fmaxf(mx, 0.f); mn = fminf(mn, 0.f); }   // zero padding of the last group
+        for (int j = 0; j < 64; ++j) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (j < nq) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
+        mx = fmaxf(mx, 0.f);                                     // zero padding of the last group
+        mn = fminf(mn, 0.f);
+      }
       GroupParams p;
       if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
       else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+      const float rcp = __frcp_rn(p.scale);
       uint32_t q[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) {
-        int c = 0;
-        if (j < nq) {
-          if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(v[j], p.scale, maxq);
-          else c = int_asym_code<true>(v[j], p.scale, p.zero, maxq);
+        uint32_t c = 0;
+        if (nq == 64 || j < nq) {
+          if constexpr (MODE == MODE_INT4_SYM) c = int_sym_nibble_fast(v[j], p.scale, rcp);
+          else c = int_asym_code_fast(v[j], p.scale, rcp, p.zero, maxq);
         }
-        q[j] = (uint32_t)c;
+        q[j] = c;
       }
       if (row_ok) {
         if constexpr (MODE == MODE_INT8_ASYM) {
@@ -138,9 +151,7 @@ __device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr,
       if (nq == 0 && (t0 & 7) == 0 && col + 64 <= g.D) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<uint4*>(tr + t0 + 8 * i) =
-              make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
-                         pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+          *reinterpret_cast<uint4*>(tr + t0 + 8 * i) = make_uint4(xb[4 * i], xb[4 * i + 1], xb[4 * i + 2], xb[4 * i + 3]);
       } else {
 #pragma unroll
         for (int j = 0; j < 64; ++j)
@@ -151,13 +162,14 @@ __device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr,
 }
 
 template <int MODE>
-__device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+__device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   const int n_kb64_pad = (g.n_chunks + 3) & ~3;
   for (int c0 = 0; c0 < a.BN; c0 += 64) {
     const int col = n0 + c0;
     if (col >= g.D) break;
+    if (((turn++) & 1u) != (uint32_t)half) continue;
     uint32_t r[64];
     tmem_ld32(taddr + c0, r);
     tmem_ld32(taddr + c0 + 32, r + 32);
@@ -240,7 +252,7 @@ __device__ __forceinline__ void ld32_by8(uint32_t taddr, uint32_t* r) {
 // Per-head layout: head h = tile columns [hh*d, hh*d + d): first d_q quantised as ONE group,
 // last hlen passthrough.  Two passes over TMEM (extrema, then codes) keep registers small.
 template <int MODE>
-__device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+__device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
@@ -249,6 +261,7 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
   for (int cb = 0; cb < a.BN; cb += d) {
     const int h = (n0 + cb) / d;
     if (h >= g.H) break;
+    if (((turn++) & 1u) != (uint32_t)half) continue;
     if (a.x_rot) {
       for (int c8 = 0; c8 < d; c8 += 8) {
         uint32_t r[8];
@@ -340,12 +353,13 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
 
 // Plain GEMM epilogue: y[M, N] = acc (+ bias) as bf16; used for the stand-alone rotation and for
 // the bf16 GEMM behind the W4A16 layer.
-__device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0) {
+__device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   for (int c0 = 0; c0 < a.BN; c0 += 32) {
     const int col = n0 + c0;
     if (col >= g.D) break;
+    if (((turn++) & 1u) != (uint32_t)half) continue;
     uint32_t r[32];
     tmem_ld32(taddr + c0, r);
     tmem_wait_ld();
@@ -385,7 +399,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RQ_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), RQ_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_x);
@@ -463,22 +477,24 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 2) >> 2;
     int buf = 0;
-    uint32_t aph = 0;
+    uint32_t aph = 0, turn = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
       if (!mbar_wait(accf_bar(buf), aph, abort_flag, a.status, ERR_WAIT_ACC_FULL)) break;
+      __syncwarp();
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256;
       const int64_t row = (int64_t)mb * 128 + q * 32 + lane;
       const int n0 = nb * a.BN;
-      if constexpr (EPI == EPI_ROT_ONLY) epi_rot_only(a, taddr, row, n0);
-      else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0);
-      else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0);
-      else epi_int_perhead<MODE>(a, taddr, row, n0);
+      if constexpr (EPI == EPI_ROT_ONLY) epi_rot_only(a, taddr, row, n0, half, turn);
+      else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0, half, turn);
+      else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn);
+      else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn);
       tc_fence_before();
-      mbar_arrive(acce_bar(buf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce_bar(buf));
       buf ^= 1;
       if (buf == 0) aph ^= 1;
     }
