@@ -4,7 +4,7 @@
 //   y[m,n] = sum_c xs[c,m] ws[c,n] ( sum_k qx[m,c,k] qw[n,c,k]  -  xz[c,m] wsum[c,n] )
 //            + x_tail[m,:] . w_tail[n,:] + bias[n]
 //
-// Data flow per CTA (one 128 x 128 output tile, K walked in stages of two 64-wide chunks):
+// Data flow per persistent CTA (128 x 128 output tiles, K walked in stages of two 64-wide chunks):
 //   TMA            packed 4-bit codes (64 B per row per stage) and the per-chunk scale rows
 //                  -> "raw" shared-memory ring (deep: hides L2 / HBM latency with no registers held)
 //   converter warps  raw ring -> "expanded" ring: every nibble widened to a byte (nibble << 4 is the
@@ -110,10 +110,10 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   const uint32_t exp_base = smem_u32(smem);
   const uint32_t raw_base = smem_u32(raw_area);
 
-  const int m0 = blockIdx.y * 128;
-  const int n0 = blockIdx.x * 128;
   const int n_main = (a.n_chunks + 1) >> 1;               // stages of two chunks
   const int n_tail = (a.kt + 63) >> 6;                    // stages of 64 bf16
+  const int n_tiles_n = (int)((a.N + 127) / 128);
+  const int total_tiles = n_tiles_n * (int)((a.M + 127) / 128);
   constexpr bool ASYM = (A_MODE != MODE_INT4_SYM);
   constexpr float INV_F = ASYM ? (1.f / 16.f) : (1.f / 256.f);
   constexpr float F_ = ASYM ? 16.f : 256.f;
@@ -121,6 +121,10 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   // raw stage layout: A | B | ws | wsum | xs | xz
   constexpr int OFF_B = Cfg::RAW_A_BYTES, OFF_WS = OFF_B + GI_RAW_B_BYTES, OFF_WSUM = OFF_WS + 1024,
                 OFF_XS = OFF_WSUM + 1024, OFF_XZ = OFF_XS + 512;
+  // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; consecutive tiles share the
+  // activation row block (n fastest), so concurrently running CTAs hit the same rows in L2.  All
+  // rings and the accumulator counter run on across tiles, so the loads and UMMAs of tile i+1
+  // overlap the drain of tile i.
 
   if (warp == W_TMA) {
     // ------------------------------ TMA producer ---------------------------------------------
@@ -128,21 +132,24 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       RingN<GI_RAW_STAGES> r;
       uint32_t issued = 0;
       bool ok = true;
-      for (int st = 0; st < n_main; ++st) {
-        if (!mbar_wait(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-        const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE_BYTES;
-        const uint32_t bar = rawf_bar(r.s);
-        mbar_expect_tx(bar, RAW_TX);
-        tma_load_2d(sb, &tm.xq, bar, st * (A_MODE == MODE_INT8_ASYM ? 128 : 64), m0);
-        tma_load_2d(sb + OFF_B, &tm.wq, bar, st * 64, n0);
-        tma_load_2d(sb + OFF_WS, &tm.ws, bar, n0, st * 2);
-        tma_load_2d(sb + OFF_XS, &tm.xs, bar, m0, st * 2);
-        if constexpr (ASYM) {
-          tma_load_2d(sb + OFF_WSUM, &tm.wsum, bar, n0, st * 2);
-          tma_load_2d(sb + OFF_XZ, &tm.xz, bar, m0, st * 2);
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * 128;
+        for (int st = 0; st < n_main; ++st) {
+          if (!mbar_wait(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE_BYTES;
+          const uint32_t bar = rawf_bar(r.s);
+          mbar_expect_tx(bar, RAW_TX);
+          tma_load_2d(sb, &tm.xq, bar, st * (A_MODE == MODE_INT8_ASYM ? 128 : 64), m0);
+          tma_load_2d(sb + OFF_B, &tm.wq, bar, st * 64, n0);
+          tma_load_2d(sb + OFF_WS, &tm.ws, bar, n0, st * 2);
+          tma_load_2d(sb + OFF_XS, &tm.xs, bar, m0, st * 2);
+          if constexpr (ASYM) {
+            tma_load_2d(sb + OFF_WSUM, &tm.wsum, bar, n0, st * 2);
+            tma_load_2d(sb + OFF_XZ, &tm.xz, bar, m0, st * 2);
+          }
+          issued |= 1u << r.s;
+          r.next();
         }
-        issued |= 1u << r.s;
-        r.next();
       }
       if (!ok) {
         const long long t0 = clock64();
@@ -159,97 +166,116 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
     const int ct = threadIdx.x - (W_TMA + 1) * 32;        // 0..63
     RingN<GI_RAW_STAGES> r;
     RingN<GI_EXP_STAGES> e;
-    for (int st = 0; st < n_main; ++st) {
-      if (!mbar_wait(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) break;
-      if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) break;
-      const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE_BYTES;
-      const uint32_t sA = exp_base + e.s * GI_EXP_STAGE_BYTES;
-      const uint32_t sB = sA + GI_TILE_BYTES;
-      // B (weights): 128 rows x 4 granules of 32 codes
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int id = ct + i * GI_CONV_THREADS;
-        const int row = id >> 2, gi = id & 3;
-        const uint4 p = lds128(sraw + OFF_B + id * 16);
-        sts128(swz(sB, row, 2 * gi), make_uint4((p.x << 4) & 0xF0F0F0F0u, (p.y << 4) & 0xF0F0F0F0u,
-                                                (p.z << 4) & 0xF0F0F0F0u, (p.w << 4) & 0xF0F0F0F0u));
-        sts128(swz(sB, row, 2 * gi + 1), make_uint4(p.x & 0xF0F0F0F0u, p.y & 0xF0F0F0F0u, p.z & 0xF0F0F0F0u, p.w & 0xF0F0F0F0u));
-      }
-      if constexpr (A_MODE == MODE_INT8_ASYM) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int id = ct + i * GI_CONV_THREADS;
-          sts128(swz(sA, id >> 3, id & 7), lds128(sraw + id * 16));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int id = ct + i * GI_CONV_THREADS;
-          const int row = id >> 2, gi = id & 3;
-          const uint4 p = lds128(sraw + id * 16);
-          if constexpr (A_MODE == MODE_INT4_SYM) {
-            sts128(swz(sA, row, 2 * gi), make_uint4((p.x << 4) & 0xF0F0F0F0u, (p.y << 4) & 0xF0F0F0F0u,
-                                                    (p.z << 4) & 0xF0F0F0F0u, (p.w << 4) & 0xF0F0F0F0u));
-            sts128(swz(sA, row, 2 * gi + 1), make_uint4(p.x & 0xF0F0F0F0u, p.y & 0xF0F0F0F0u, p.z & 0xF0F0F0F0u, p.w & 0xF0F0F0F0u));
-          } else {
-            sts128(swz(sA, row, 2 * gi), make_uint4(p.x & 0x0F0F0F0Fu, p.y & 0x0F0F0F0Fu, p.z & 0x0F0F0F0Fu, p.w & 0x0F0F0F0Fu));
-            sts128(swz(sA, row, 2 * gi + 1), make_uint4((p.x >> 4) & 0x0F0F0F0Fu, (p.y >> 4) & 0x0F0F0F0Fu,
-                                                        (p.z >> 4) & 0x0F0F0F0Fu, (p.w >> 4) & 0x0F0F0F0Fu));
-          }
-        }
-      }
-      // per-chunk scales / zero points / code sums of the tile's 128 rows and 128 columns
-      {
-        const uint8_t* rs = raw_area + r.s * Cfg::RAW_STAGE_BYTES;
-        float* aux = reinterpret_cast<float*>(smem + e.s * GI_EXP_STAGE_BYTES + 2 * GI_TILE_BYTES);
-        const float* rws = reinterpret_cast<const float*>(rs + OFF_WS);
-        const float* rwsum = reinterpret_cast<const float*>(rs + OFF_WSUM);
-        const __nv_bfloat16* rxs = reinterpret_cast<const __nv_bfloat16*>(rs + OFF_XS);
-        const __nv_bfloat16* rxz = reinterpret_cast<const __nv_bfloat16*>(rs + OFF_XZ);
-#pragma unroll
-        for (int i = ct; i < 256; i += GI_CONV_THREADS) {
-          aux[i] = rws[i];
-          aux[256 + i] = __bfloat162float(rxs[i]) * INV_F;
-          if constexpr (ASYM) {
-            aux[512 + i] = rwsum[i];
-            aux[768 + i] = __bfloat162float(rxz[i]) * F_;
-          }
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(expf_bar(e.s));
-        mbar_arrive(rawe_bar(r.s));
-      }
-      r.next();
-      e.next();
-    }
-    // tail: bf16 tiles go by TMA straight into the expanded ring.  Issued from here (not from the
-    // TMA warp) because this warp walks the expanded ring in order: a waiter may never be more than
-    // one phase away from the barrier it polls.
-    if (ct == 0) {
-      uint32_t issued_e = 0;
-      bool ok = !*abort_flag;
-      for (int st = 0; st < n_tail && ok; ++st) {
+    uint32_t issued_e = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * 128;
+      for (int st = 0; st < n_main; ++st) {
+        if (!mbar_wait(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE_BYTES;
         const uint32_t sA = exp_base + e.s * GI_EXP_STAGE_BYTES;
-        const uint32_t bar = expf_bar(e.s);
-        mbar_expect_tx(bar, 2 * GI_TILE_BYTES);           // first of the two expected arrivals
-        mbar_arrive(bar);                                  // second (the other converter warp's slot)
-        tma_load_2d(sA, &tm.xt, bar, st * 64, m0);
-        tma_load_2d(sA + GI_TILE_BYTES, &tm.wt, bar, st * 64, n0);
-        issued_e |= 1u << e.s;
+        const uint32_t sB = sA + GI_TILE_BYTES;
+        // B (weights): 128 rows x 4 granules of 32 codes; all loads first, then widen + store
+        {
+          uint4 p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) p[i] = lds128(sraw + OFF_B + (ct + i * GI_CONV_THREADS) * 16);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int id = ct + i * GI_CONV_THREADS;
+            const int row = id >> 2, gi = id & 3;
+            sts128(swz(sB, row, 2 * gi), make_uint4((p[i].x << 4) & 0xF0F0F0F0u, (p[i].y << 4) & 0xF0F0F0F0u,
+                                                    (p[i].z << 4) & 0xF0F0F0F0u, (p[i].w << 4) & 0xF0F0F0F0u));
+            sts128(swz(sB, row, 2 * gi + 1), make_uint4(p[i].x & 0xF0F0F0F0u, p[i].y & 0xF0F0F0F0u,
+                                                        p[i].z & 0xF0F0F0F0u, p[i].w & 0xF0F0F0F0u));
+          }
+        }
+        if constexpr (A_MODE == MODE_INT8_ASYM) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint4 p[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) p[i] = lds128(sraw + (ct + (h * 8 + i) * GI_CONV_THREADS) * 16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int id = ct + (h * 8 + i) * GI_CONV_THREADS;
+              sts128(swz(sA, id >> 3, id & 7), p[i]);
+            }
+          }
+        } else {
+          uint4 p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) p[i] = lds128(sraw + (ct + i * GI_CONV_THREADS) * 16);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int id = ct + i * GI_CONV_THREADS;
+            const int row = id >> 2, gi = id & 3;
+            if constexpr (A_MODE == MODE_INT4_SYM) {
+              sts128(swz(sA, row, 2 * gi), make_uint4((p[i].x << 4) & 0xF0F0F0F0u, (p[i].y << 4) & 0xF0F0F0F0u,
+                                                      (p[i].z << 4) & 0xF0F0F0F0u, (p[i].w << 4) & 0xF0F0F0F0u));
+              sts128(swz(sA, row, 2 * gi + 1), make_uint4(p[i].x & 0xF0F0F0F0u, p[i].y & 0xF0F0F0F0u,
+                                                          p[i].z & 0xF0F0F0F0u, p[i].w & 0xF0F0F0F0u));
+            } else {
+              sts128(swz(sA, row, 2 * gi), make_uint4(p[i].x & 0x0F0F0F0Fu, p[i].y & 0x0F0F0F0Fu,
+                                                      p[i].z & 0x0F0F0F0Fu, p[i].w & 0x0F0F0F0Fu));
+              sts128(swz(sA, row, 2 * gi + 1), make_uint4((p[i].x >> 4) & 0x0F0F0F0Fu, (p[i].y >> 4) & 0x0F0F0F0Fu,
+                                                          (p[i].z >> 4) & 0x0F0F0F0Fu, (p[i].w >> 4) & 0x0F0F0F0Fu));
+            }
+          }
+        }
+        // per-chunk scales / zero points / code sums of the tile's 128 rows and 128 columns
+        {
+          const uint8_t* rs = raw_area + r.s * Cfg::RAW_STAGE_BYTES;
+          float* aux = reinterpret_cast<float*>(smem + e.s * GI_EXP_STAGE_BYTES + 2 * GI_TILE_BYTES);
+          const float* rws = reinterpret_cast<const float*>(rs + OFF_WS);
+          const float* rwsum = reinterpret_cast<const float*>(rs + OFF_WSUM);
+          const __nv_bfloat16* rxs = reinterpret_cast<const __nv_bfloat16*>(rs + OFF_XS);
+          const __nv_bfloat16* rxz = reinterpret_cast<const __nv_bfloat16*>(rs + OFF_XZ);
+#pragma unroll
+          for (int i = ct; i < 256; i += GI_CONV_THREADS) {
+            aux[i] = rws[i];
+            aux[256 + i] = __bfloat162float(rxs[i]) * INV_F;
+            if constexpr (ASYM) {
+              aux[512 + i] = rwsum[i];
+              aux[768 + i] = __bfloat162float(rxz[i]) * F_;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(expf_bar(e.s));
+          mbar_arrive(rawe_bar(r.s));
+        }
+        r.next();
         e.next();
       }
-      if (!ok) {
-        const long long t0 = clock64();
-        for (int i = 0; i < GI_EXP_STAGES; ++i) {
-          if (!(issued_e & (1u << i))) continue;
-          const uint32_t last_ph = (i < e.s) ? e.ph : (e.ph ^ 1);
-          while (!mbar_try(expf_bar(i), last_ph))
-            if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
+      // tail: bf16 tiles go by TMA straight into the expanded ring.  Issued from a converter thread
+      // (not from the TMA warp) because the converters walk the expanded ring in order; both
+      // converter warps poll every slot so that no waiter is ever more than one phase away from
+      // the barrier it polls.
+      for (int st = 0; st < n_tail && ok; ++st) {
+        if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+        if (ct == 0) {
+          const uint32_t sA = exp_base + e.s * GI_EXP_STAGE_BYTES;
+          const uint32_t bar = expf_bar(e.s);
+          mbar_expect_tx(bar, 2 * GI_TILE_BYTES);           // first of the two expected arrivals
+          mbar_arrive(bar);                                  // second (the other converter warp's slot)
+          tma_load_2d(sA, &tm.xt, bar, st * 64, m0);
+          tma_load_2d(sA + GI_TILE_BYTES, &tm.wt, bar, st * 64, n0);
+          issued_e |= 1u << e.s;
         }
+        e.next();
+      }
+    }
+    if (!ok && ct == 0) {
+      const long long t0 = clock64();
+      for (int i = 0; i < GI_EXP_STAGES; ++i) {
+        if (!(issued_e & (1u << i))) continue;
+        const uint32_t last_ph = (i < e.s) ? e.ph : (e.ph ^ 1);
+        while (!mbar_try(expf_bar(i), last_ph))
+          if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
       }
     }
   } else if (warp == W_MMA) {
@@ -260,28 +286,29 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       RingN<GI_EXP_STAGES> e;
       int use = 0;   // accumulator uses so far: buffer = use % NACC, phase = (use / NACC) & 1
       bool ok = true;
-      for (int st = 0; st < n_main && ok; ++st) {
-        if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sA = exp_base + e.s * GI_EXP_STAGE_BYTES;
-        const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + GI_TILE_BYTES);
-        for (int c = 0; c < 2; ++c) {
-          if (st * 2 + c >= a.n_chunks) break;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int st = 0; st < n_main && ok; ++st) {
+          if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = exp_base + e.s * GI_EXP_STAGE_BYTES;
+          const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + GI_TILE_BYTES);
+          for (int c = 0; c < 2; ++c) {
+            if (st * 2 + c >= a.n_chunks) break;
+            const int buf = use % GI_NACC;
+            if (!mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d = tmem_base + buf * 128;
+            umma_i8(d, adesc + 4 * c, bdesc + 4 * c, idesc_i8, 0u);
+            umma_i8(d, adesc + 4 * c + 2, bdesc + 4 * c + 2, idesc_i8, 1u);
+            umma_commit(accf_bar(buf));
+            ++use;
+          }
+          umma_commit(expe_bar(e.s));
+          e.next();
+        }
+        if (ok && n_tail > 0) {
           const int buf = use % GI_NACC;
           if (!mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t d = tmem_base + buf * 128;
-          umma_i8(d, adesc + 4 * c, bdesc + 4 * c, idesc_i8, 0u);
-          umma_i8(d, adesc + 4 * c + 2, bdesc + 4 * c + 2, idesc_i8, 1u);
-          umma_commit(accf_bar(buf));
-          ++use;
-        }
-        umma_commit(expe_bar(e.s));
-        e.next();
-      }
-      if (ok && n_tail > 0) {
-        const int buf = use % GI_NACC;
-        if (mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) {
           tc_fence_after();
           const uint32_t d = tmem_base + buf * 128;
           for (int st = 0; st < n_tail; ++st) {
@@ -294,117 +321,131 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
             umma_commit(expe_bar(e.s));
             e.next();
           }
-          if (ok) umma_commit(accf_bar(buf));
+          if (ok) { umma_commit(accf_bar(buf)); ++use; }
         }
       }
     }
   } else {
     // ------------------------------ epilogue: 16 warps ---------------------------------------
-    // warp w: TMEM lane quarter w & 3 (rows), column quarter w >> 2 (32 of the tile's 128 columns)
+    // warp w: TMEM lane quarter w & 3 (rows), column quarter w >> 2 (32 of the tile's 128 columns).
+    // The drain is the kernel's critical resource (CUDA-core issue slots), so it runs on the packed
+    // fp32x2 pipe: per PAIR of values two integer adds (exact int32 -> fp32), one packed subtract,
+    // one packed multiply by ws[c,n], one packed fused multiply-add by xs[c,m].
     const int q = warp & 3, cq = warp >> 2;
     const int trow = q * 32 + lane;                       // row inside the tile
-    const int64_t row = (int64_t)m0 + trow;
     const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + cq * 32;
-    float acc[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) acc[j] = 0.f;
     RingN<GI_EXP_STAGES> e;
     int use = 0;
     bool ok = true;
-    for (int st = 0; st < n_main && ok; ++st) {
-      if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
-      const float* aux = reinterpret_cast<const float*>(smem + e.s * GI_EXP_STAGE_BYTES + 2 * GI_TILE_BYTES);
-      for (int c = 0; c < 2; ++c) {
-        if (st * 2 + c >= a.n_chunks) break;
-        const int buf = use % GI_NACC;
-        if (!mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
-        __syncwarp();
-        tc_fence_after();
-        uint32_t v[32];
-        tmem_ld32(tlane + buf * 128, v);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acce_bar(buf));
-        ++use;
-        const float sx = aux[256 + c * 128 + trow];
-        const float4* sw4 = reinterpret_cast<const float4*>(aux + c * 128 + cq * 32);
-        const float4* ws4 = reinterpret_cast<const float4*>(aux + 512 + c * 128 + cq * 32);
-        float zf = 0.f;
-        if constexpr (ASYM) zf = aux[768 + c * 128 + trow];
-        if (a.acc_dump) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * 128;
+      const int64_t row = (int64_t)m0 + trow;
+      float2 acc[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float f = __int_as_float((int)v[j] + 0x4B400000) - 12582912.f;
-            if constexpr (ASYM) f = __fmaf_rn(-zf, aux[512 + c * 128 + cq * 32 + j], f);
-            if (row < a.M && n0 + cq * 32 + j < a.N)
-              a.acc_dump[((int64_t)(st * 2 + c) * a.M + row) * a.N + n0 + cq * 32 + j] = (int)(f * INV_F);
-          }
-        }
-#pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-          const float4 s4 = sw4[j4];
-          float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
-          if constexpr (ASYM) w4 = ws4[j4];
-          const float sj[4] = {s4.x, s4.y, s4.z, s4.w};
-          const float wj[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int j = 4 * j4 + t;
-            // exact int32 -> fp32 for |v| < 2^22: add 1.5 * 2^23 as integer, subtract as float
-            float f = __int_as_float((int)v[j] + 0x4B400000) - 12582912.f;
-            if constexpr (ASYM) f = __fmaf_rn(-zf, wj[t], f);
-            acc[j] = __fmaf_rn(f * sj[t], sx, acc[j]);
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(expe_bar(e.s));
-      e.next();
-    }
-    if (ok && n_tail > 0) {
-      for (int st = 0; st < n_tail; ++st) {
+      for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.f, 0.f);
+      for (int st = 0; st < n_main && ok; ++st) {
         if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+        const float* aux = reinterpret_cast<const float*>(smem + e.s * GI_EXP_STAGE_BYTES + 2 * GI_TILE_BYTES);
+        for (int c = 0; c < 2; ++c) {
+          if (st * 2 + c >= a.n_chunks) break;
+          const int buf = use % GI_NACC;
+          if (!mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
+          __syncwarp();
+          tc_fence_after();
+          uint32_t v[32];
+          tmem_ld32(tlane + buf * 128, v);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acce_bar(buf));
+          ++use;
+          const float sx = aux[256 + c * 128 + trow];
+          const float2 sx2 = make_float2(sx, sx);
+          const float4* sw4 = reinterpret_cast<const float4*>(aux + c * 128 + cq * 32);
+          const float4* ws4 = reinterpret_cast<const float4*>(aux + 512 + c * 128 + cq * 32);
+          float zf = 0.f;
+          if constexpr (ASYM) zf = aux[768 + c * 128 + trow];
+          const float2 nz2 = make_float2(-zf, -zf);
+          const float2 nmagic = make_float2(-12582912.f, -12582912.f);
+          if (a.acc_dump) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float f = __int_as_float((int)v[j] + 0x4B400000) - 12582912.f;
+              if constexpr (ASYM) f = __fmaf_rn(-zf, aux[512 + c * 128 + cq * 32 + j], f);
+              if (row < a.M && n0 + cq * 32 + j < a.N)
+                a.acc_dump[((int64_t)(st * 2 + c) * a.M + row) * a.N + n0 + cq * 32 + j] = (int)(f * INV_F);
+            }
+          }
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 s4 = sw4[j4];
+            float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if constexpr (ASYM) w4 = ws4[j4];
+            const float2 sp[2] = {make_float2(s4.x, s4.y), make_float2(s4.z, s4.w)};
+            const float2 wp[2] = {make_float2(w4.x, w4.y), make_float2(w4.z, w4.w)};
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int j = 4 * j4 + 2 * u;
+              // exact int32 -> fp32 for |v| < 2^22: add 1.5 * 2^23 as integer, subtract as float
+              float2 f = make_float2(__int_as_float((int)v[j] + 0x4B400000), __int_as_float((int)v[j + 1] + 0x4B400000));
+              f = __fadd2_rn(f, nmagic);
+              if constexpr (ASYM) f = __ffma2_rn(nz2, wp[u], f);
+              acc[j >> 1] = __ffma2_rn(__fmul2_rn(f, sp[u]), sx2, acc[j >> 1]);
+            }
+          }
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(expe_bar(e.s));
         e.next();
       }
-      const int buf = use % GI_NACC;
-      if (ok && mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) {
-        __syncwarp();
-        tc_fence_after();
-        uint32_t v[32];
-        tmem_ld32(tlane + buf * 128, v);
-        tmem_wait_ld();
+      if (ok && n_tail > 0) {
+        for (int st = 0; st < n_tail; ++st) {
+          if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(expe_bar(e.s));
+          e.next();
+        }
+        const int buf = use % GI_NACC;
+        if (ok && mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) {
+          __syncwarp();
+          tc_fence_after();
+          uint32_t v[32];
+          tmem_ld32(tlane + buf * 128, v);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acce_bar(buf));
+          ++use;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
-      } else {
-        ok = false;
+          for (int j = 0; j < 16; ++j) { acc[j].x += __uint_as_float(v[2 * j]); acc[j].y += __uint_as_float(v[2 * j + 1]); }
+        } else {
+          ok = false;
+        }
       }
-    }
-    if (ok && row < a.M) {
-      const int64_t col0 = (int64_t)n0 + cq * 32;
-      __nv_bfloat16* yr = a.y + row * a.N + col0;
+      if (ok && row < a.M) {
+        const int64_t col0 = (int64_t)n0 + cq * 32;
+        __nv_bfloat16* yr = a.y + row * a.N + col0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (col0 + 8 * i + 8 <= a.N) {
-          float b[8];
-          if (a.bias) {
-            const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col0 + 8 * i));
-            const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
+        for (int i = 0; i < 4; ++i) {
+          if (col0 + 8 * i + 8 <= a.N) {
+            float b[8];
+            if (a.bias) {
+              const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col0 + 8 * i));
+              const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
 #pragma unroll
-            for (int e2 = 0; e2 < 4; ++e2) { float2 f = __bfloat1622float2(bh[e2]); b[2 * e2] = f.x; b[2 * e2 + 1] = f.y; }
-          } else {
+              for (int e2 = 0; e2 < 4; ++e2) { float2 f = __bfloat1622float2(bh[e2]); b[2 * e2] = f.x; b[2 * e2 + 1] = f.y; }
+            } else {
 #pragma unroll
-            for (int e2 = 0; e2 < 8; ++e2) b[e2] = 0.f;
+              for (int e2 = 0; e2 < 8; ++e2) b[e2] = 0.f;
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(acc[4 * i + e2].x + b[2 * e2], acc[4 * i + e2].y + b[2 * e2 + 1]);
+              w[e2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(yr + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          uint32_t w[4];
-#pragma unroll
-          for (int e2 = 0; e2 < 4; ++e2) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(acc[8 * i + 2 * e2] + b[2 * e2], acc[8 * i + 2 * e2 + 1] + b[2 * e2 + 1]);
-            w[e2] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          *reinterpret_cast<uint4*>(yr + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
@@ -427,7 +468,8 @@ static int launch_gi(const GiMaps& tm, const GemmIntArgs& a, cudaStream_t st) {
       return DIROTQ_E_CUDA;
     attr_set = true;
   }
-  dim3 grid((unsigned)((a.N + 127) / 128), (unsigned)((a.M + 127) / 128));
+  const int tiles = (int)((a.N + 127) / 128) * (int)((a.M + 127) / 128);
+  const int grid = min(tiles, num_sms());
   k<<<grid, GI_THREADS, GiCfg<A_MODE>::SMEM_BYTES, st>>>(tm, a);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
