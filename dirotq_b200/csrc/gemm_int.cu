@@ -70,7 +70,7 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   return v;
 }
 
-template <int A_MODE>
+template <int A_MODE, bool DUMP>
 __global__ void __launch_bounds__(GI_THREADS, 1)
 gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   using Cfg = GiCfg<A_MODE>;
@@ -367,7 +367,7 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
           if constexpr (ASYM) zf = aux[768 + c * 128 + trow];
           const float2 nz2 = make_float2(-zf, -zf);
           const float2 nmagic = make_float2(-12582912.f, -12582912.f);
-          if (a.acc_dump) {
+          if constexpr (DUMP) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               float f = __int_as_float((int)v[j] + 0x4B400000) - 12582912.f;
@@ -459,9 +459,9 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   }
 }
 
-template <int A_MODE>
+template <int A_MODE, bool DUMP>
 static int launch_gi(const GiMaps& tm, const GemmIntArgs& a, cudaStream_t st) {
-  auto k = gemm_int_kernel<A_MODE>;
+  auto k = gemm_int_kernel<A_MODE, DUMP>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, GiCfg<A_MODE>::SMEM_BYTES) != cudaSuccess)
@@ -513,9 +513,10 @@ int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st) {
     tm.wt = tm.wq;
   }
   switch (a.a_mode) {
-    case DIROTQ_INT4_SYM: return launch_gi<MODE_INT4_SYM>(tm, a, st);
-    case DIROTQ_INT4_ASYM: return launch_gi<MODE_INT4_ASYM>(tm, a, st);
-    case DIROTQ_INT8_ASYM: return launch_gi<MODE_INT8_ASYM>(tm, a, st);
+    // the per-chunk int32 dump (tests) is a separate instantiation: the production kernel carries none of its code
+    case DIROTQ_INT4_SYM: return a.acc_dump ? launch_gi<MODE_INT4_SYM, true>(tm, a, st) : launch_gi<MODE_INT4_SYM, false>(tm, a, st);
+    case DIROTQ_INT4_ASYM: return a.acc_dump ? launch_gi<MODE_INT4_ASYM, true>(tm, a, st) : launch_gi<MODE_INT4_ASYM, false>(tm, a, st);
+    case DIROTQ_INT8_ASYM: return a.acc_dump ? launch_gi<MODE_INT8_ASYM, true>(tm, a, st) : launch_gi<MODE_INT8_ASYM, false>(tm, a, st);
   }
   return DIROTQ_E_UNSUPPORTED;
 }

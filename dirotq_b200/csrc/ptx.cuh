@@ -39,25 +39,30 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+// One poll.  `suspend_ns` is the hardware suspend-time hint: the thread sleeps inside the instruction
+// (no issue slots used) until the phase completes or roughly that long has passed.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t suspend_ns = 0) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(suspend_ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  `abort_flag` lives in shared memory: once any role gave up, all later waits of
-// the CTA return at once.
+// Bounded wait.  Waiters sleep in hardware (20 us per poll) instead of spinning, so they do not
+// compete with the working warps for issue slots; between polls the shared abort flag and the clock
+// are checked.  `abort_flag` lives in shared memory: once any role gave up, all later waits of the
+// CTA return at once.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_try(bar, parity, 20000u)) return true;
+    __nanosleep(128);            // keep pollers off the issue ports of the working warps
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
