@@ -77,6 +77,20 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     return y
 
 
+def linear_forward_static(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """linear_forward without any scratch from the caller: the library's built-in device array is used
+    (see dirotq_linear_forward_static in include/dirotq_b200.h for the capacity and the sharing rules)."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
+    M = x2d.shape[0]
+    y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
+    check(_lib.lib().dirotq_linear_forward_static(C.byref(st.c_struct()), C.c_void_p(x2d.data_ptr()), M,
+                                                  C.c_void_p(y.data_ptr()),
+                                                  C.c_void_p(ops.status_word(x2d.device).data_ptr()),
+                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+          "dirotq_linear_forward_static")
+    return y
+
+
 def _act_format(w) -> ops.ActFormat:
     q = w.quantizer
     D = w.module.in_features

@@ -295,4 +295,53 @@ int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, vo
                               g.tail_pitch, lin->bias, y, nullptr, status, stream);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of dirotq_linear_forward
+// ---------------------------------------------------------------------------------------------
+// Scratch for callers that cannot provide any: a fixed array in device global memory, part of the
+// library image.  Every GPU that loads the library holds these bytes until the process exits.
+#define DIROTQ_STATIC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[DIROTQ_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the real
+// address is looked up once per device (with that device current) and cached here.
+static void* g_static_scratch_addr[64] = {nullptr};
+
+static int static_scratch_ptr(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DIROTQ_E_CUDA;
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return DIROTQ_E_CUDA;
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return DIROTQ_OK;
+}
+
+size_t dirotq_linear_forward_static_capacity(void) { return DIROTQ_STATIC_SCRATCH_BYTES; }
+
+int dirotq_linear_forward_static(const dirotq_linear* lin, const void* x, int64_t M, void* y, int32_t* status,
+                                 void* stream) {
+  if (!lin || !x || !y || M < 0) return DIROTQ_E_ARG;
+  ActGeom g;
+  WsCarve w;
+  int rc = carve(lin, M, &g, &w);
+  if (rc) return rc;
+  if (w.total > DIROTQ_STATIC_SCRATCH_BYTES) return DIROTQ_E_TOO_LARGE;
+  void* ws = nullptr;
+  rc = static_scratch_ptr(&ws);
+  if (rc) return rc;
+  // The array still holds whatever the previous call left.  Only the scale-factor tiles of the
+  // NVFP4 format rely on zeros (their padding entries are never written), so that region is cleared
+  // here, in stream order, before the kernels run.
+  if (g.mode == DIROTQ_NVFP4_HW) {
+    if (cudaMemsetAsync(static_cast<uint8_t*>(ws) + w.scales, 0, w.zeros - w.scales,
+                        static_cast<cudaStream_t>(stream)) != cudaSuccess)
+      return DIROTQ_E_CUDA;
+  }
+  return dirotq_linear_forward(lin, x, M, y, ws, w.total, status, stream);
+}
+
 }  // extern "C"

@@ -194,6 +194,25 @@ size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M);
 int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
                           size_t workspace_bytes, int32_t* status, void* stream);
 
+/* Same computation as dirotq_linear_forward, for callers that can hand over nothing but the input
+ * and the output.  (No counterpart in the reference: its eager forward allocates freely through
+ * torch.)  Meant for hosts that give a plug-in no allocator at all -- an inference server whose
+ * device memory is carved up once at start-up, or a latency-critical loop that cannot afford the
+ * device-wide synchronisation a cudaMalloc / cudaFree may cause.  The codes / scales / zero points /
+ * tail of the call live in a fixed array inside the library's device image
+ * (dirotq_linear_forward_static_capacity() bytes, 32 MiB; each GPU that loads the library carries
+ * it until the process exits).  The call allocates and frees nothing.
+ *  - Sizes whose scratch need (dirotq_linear_workspace_bytes) exceeds the capacity are refused with
+ *    DIROTQ_E_TOO_LARGE before anything is launched.
+ *  - The first call on each device looks up the array's device address (a host-side runtime query);
+ *    make that first call before starting any stream capture.
+ *  - All calls share the one array and it keeps the previous call's bytes; the entry point clears
+ *    the part that must start at zero itself.  Two calls whose kernels may overlap on the GPU
+ *    (different streams, no dependency) race on the array: serialise them. */
+size_t dirotq_linear_forward_static_capacity(void);
+int dirotq_linear_forward_static(const dirotq_linear* lin, const void* x, int64_t M, void* y, int32_t* status,
+                                 void* stream);
+
 /* ---- misc ---- */
 int dirotq_abi_version(void);
 const char* dirotq_error_string(int code);
