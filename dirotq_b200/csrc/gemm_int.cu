@@ -11,7 +11,7 @@
 //                  sign-extended value times 16: two logic ops per 8 codes, the power-of-two factor is
 //                  folded into the activation scale), written in the 128-byte-swizzled K-major layout
 //   UMMA issuer    tcgen05.mma kind::i8, two K=32 instructions per chunk -> 128 x 128 int32 in TMEM;
-//                  four accumulators rotate, so the issuer runs ahead of the drain
+//                  two PAIRS of accumulators alternate, one hand-off per stage (two chunks)
 //   16 epilogue warps tcgen05.ld, exact int -> float, * ws[c,n] * xs[c,m], fp32 accumulate in registers
 //   tail           bf16 TMA tiles straight into the expanded ring, kind::f16 UMMAs, added last
 //
@@ -96,7 +96,7 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < GI_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), GI_CONV_WARPS); }
     for (int s = 0; s < GI_EXP_STAGES; ++s) { mbar_init(expf_bar(s), GI_CONV_WARPS); mbar_init(expe_bar(s), 1 + GI_EPI_WARPS); }
-    for (int b = 0; b < GI_NACC; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GI_EPI_WARPS); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GI_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm.xq);
@@ -284,7 +284,7 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       const uint32_t idesc_i8 = idesc_dense(ACC_S32, ASYM ? FMT_U8 : FMT_S8, FMT_S8, 128, 128);
       const uint32_t idesc_bf = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, 128);
       RingN<GI_EXP_STAGES> e;
-      int use = 0;   // accumulator uses so far: buffer = use % NACC, phase = (use / NACC) & 1
+      int use = 0;   // hand-offs so far: accumulator pair = use & 1, phase = (use >> 1) & 1
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int st = 0; st < n_main && ok; ++st) {
@@ -292,25 +292,26 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
           tc_fence_after();
           const uint32_t sA = exp_base + e.s * GI_EXP_STAGE_BYTES;
           const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + GI_TILE_BYTES);
+          // one hand-off per stage: the stage's two chunks go to the two accumulators of a pair
+          const int pair = use & 1;
+          if (!mbar_wait(acce_bar(pair), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+          tc_fence_after();
           for (int c = 0; c < 2; ++c) {
             if (st * 2 + c >= a.n_chunks) break;
-            const int buf = use % GI_NACC;
-            if (!mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t d = tmem_base + buf * 128;
+            const uint32_t d = tmem_base + (2 * pair + c) * 128;
             umma_i8(d, adesc + 4 * c, bdesc + 4 * c, idesc_i8, 0u);
             umma_i8(d, adesc + 4 * c + 2, bdesc + 4 * c + 2, idesc_i8, 1u);
-            umma_commit(accf_bar(buf));
-            ++use;
           }
+          umma_commit(accf_bar(pair));
+          ++use;
           umma_commit(expe_bar(e.s));
           e.next();
         }
         if (ok && n_tail > 0) {
-          const int buf = use % GI_NACC;
-          if (!mbar_wait(acce_bar(buf), ((use / GI_NACC) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+          const int pair = use & 1;
+          if (!mbar_wait(acce_bar(pair), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d = tmem_base + buf * 128;
+          const uint32_t d = tmem_base + (2 * pair) * 128;
           for (int st = 0; st < n_tail; ++st) {
             if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
@@ -321,7 +322,7 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
             umma_commit(expe_bar(e.s));
             e.next();
           }
-          if (ok) { umma_commit(accf_bar(buf)); ++use; }
+          if (ok) { umma_commit(accf_bar(pair)); ++use; }
         }
       }
     }
@@ -346,19 +347,21 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
       for (int st = 0; st < n_main && ok; ++st) {
         if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         const float* aux = reinterpret_cast<const float*>(smem + e.s * GI_EXP_STAGE_BYTES + 2 * GI_TILE_BYTES);
-        for (int c = 0; c < 2; ++c) {
-          if (st * 2 + c >= a.n_chunks) break;
-          const int buf = use % GI_NACC;
-          if (!mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
-          __syncwarp();
-          tc_fence_after();
+        const int pair = use & 1;
+        if (!mbar_wait(accf_bar(pair), (use >> 1) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
+        __syncwarp();
+        tc_fence_after();
+        ++use;
+        const int nc = min(2, a.n_chunks - st * 2);
+        for (int c = 0; c < nc; ++c) {
           uint32_t v[32];
-          tmem_ld32(tlane + buf * 128, v);
+          tmem_ld32(tlane + (2 * pair + c) * 128, v);
           tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acce_bar(buf));
-          ++use;
+          if (c == nc - 1) {                       // both chunks are out of TMEM: hand the pair back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(pair));
+          }
           const float sx = aux[256 + c * 128 + trow];
           const float2 sx2 = make_float2(sx, sx);
           const float4* sw4 = reinterpret_cast<const float4*>(aux + c * 128 + cq * 32);
@@ -405,16 +408,16 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
           if (lane == 0) mbar_arrive(expe_bar(e.s));
           e.next();
         }
-        const int buf = use % GI_NACC;
-        if (ok && mbar_wait(accf_bar(buf), (use / GI_NACC) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) {
+        const int pair = use & 1;
+        if (ok && mbar_wait(accf_bar(pair), (use >> 1) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) {
           __syncwarp();
           tc_fence_after();
           uint32_t v[32];
-          tmem_ld32(tlane + buf * 128, v);
+          tmem_ld32(tlane + (2 * pair) * 128, v);
           tmem_wait_ld();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acce_bar(buf));
+          if (lane == 0) mbar_arrive(acce_bar(pair));
           ++use;
 #pragma unroll
           for (int j = 0; j < 16; ++j) { acc[j].x += __uint_as_float(v[2 * j]); acc[j].y += __uint_as_float(v[2 * j + 1]); }

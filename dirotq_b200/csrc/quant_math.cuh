@@ -7,6 +7,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include <cstdint>
 
 namespace dq {
@@ -99,6 +100,74 @@ __device__ __forceinline__ int int_asym_code(float x, float scale, float zero, f
   return (int)q;
 }
 
+// Eight consecutive values -> eight codes (nibble i = value i; bytes for the 8-bit mode).  The guard
+// of div_round_bf16 is evaluated for all eight and OR-ed; only if one of them is close to a rounding
+// boundary are the eight redone with the IEEE divide, in an out-of-line function so that the compiler
+// cannot if-convert the expensive path into the common one.
+static __device__ __noinline__ uint32_t int_sym_nib8_exact(float v0, float v1, float v2, float v3, float v4, float v5,
+                                                           float v6, float v7, float s) {
+  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+  uint32_t w = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) w |= ((uint32_t)int_sym_code<true>(v[j], s, 7.f) & 0xFu) << (4 * j);
+  return w;
+}
+__device__ __forceinline__ uint32_t int_sym_nib8_fast(const float* v, float s, float rcp_s) {
+  uint32_t w = 0, near = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float qa = __fmul_rn(v[j], rcp_s);
+    near |= (uint32_t)(((__float_as_uint(qa) + 0x8003u) & 0xFFFFu) <= 6u);
+    float r = __bfloat162float(__float2bfloat16_rn(qa));
+    r = fminf(fmaxf(r, -8.f), 7.f);
+    w |= (int_bits(r) & 0xFu) << (4 * j);
+  }
+  if (near) w = int_sym_nib8_exact(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], s);
+  return w;
+}
+// asymmetric: codes in [0, maxq]; returned as eight bytes in two words
+static __device__ __noinline__ uint2 int_asym_byte8_exact(float v0, float v1, float v2, float v3, float v4, float v5,
+                                                          float v6, float v7, float s, float zero, float maxq) {
+  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) w[j >> 2] |= ((uint32_t)int_asym_code<true>(v[j], s, zero, maxq) & 0xFFu) << (8 * (j & 3));
+  return make_uint2(w[0], w[1]);
+}
+__device__ __forceinline__ uint2 int_asym_byte8_fast(const float* v, float s, float rcp_s, float zero, float maxq) {
+  uint32_t w[2] = {0u, 0u};
+  uint32_t near = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float qa = __fmul_rn(v[j], rcp_s);
+    near |= (uint32_t)(((__float_as_uint(qa) + 0x8003u) & 0xFFFFu) <= 6u);
+    const float r = rint_bf16(__bfloat162float(__float2bfloat16_rn(qa)));
+    float q = __bfloat162float(__float2bfloat16_rn(__fadd_rn(r, zero)));
+    q = fminf(fmaxf(q, 0.f), maxq);
+    w[j >> 2] |= (int_bits(q) & 0xFFu) << (8 * (j & 3));
+  }
+  if (near) return int_asym_byte8_exact(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], s, zero, maxq);
+  return make_uint2(w[0], w[1]);
+}
+// four bytes holding 4-bit values -> four nibbles in the low 16 bits
+__device__ __forceinline__ uint32_t squeeze_nibbles(uint32_t b) {
+  b = (b | (b >> 4)) & 0x00FF00FFu;
+  return (b | (b >> 8)) & 0xFFFFu;
+}
+// four nibbles (low 16 bits) -> four bytes
+__device__ __forceinline__ uint32_t spread_nibbles(uint32_t x) {
+  x = (x | (x << 8)) & 0x00FF00FFu;
+  return (x | (x << 4)) & 0x0F0F0F0Fu;
+}
+// 32 codes given as four words of eight sequential nibbles -> the planar-32 layout
+// (byte j = code j | code 16+j << 4)
+__device__ __forceinline__ uint4 planar32_from_nib8(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+  return make_uint4(spread_nibbles(a0 & 0xFFFFu) | (spread_nibbles(a2 & 0xFFFFu) << 4),
+                    spread_nibbles(a0 >> 16) | (spread_nibbles(a2 >> 16) << 4),
+                    spread_nibbles(a1 & 0xFFFFu) | (spread_nibbles(a3 & 0xFFFFu) << 4),
+                    spread_nibbles(a1 >> 16) | (spread_nibbles(a3 >> 16) << 4));
+}
+
 // E2M1 nibble of a normalised value with the reference's bucketize rule (quant_utils.py:30-35):
 // an exact midpoint goes to the LOWER codebook value (toward -inf); there is no negative zero.
 __device__ __forceinline__ uint32_t e2m1_nibble(float v) {
@@ -141,6 +210,54 @@ __device__ __forceinline__ uint8_t nvfp4_hw_scale(float amax, float clip, float 
 }
 __device__ __forceinline__ uint32_t nvfp4_hw_code(float x, float eff) {
   return eff > 0.f ? e2m1_nibble(__fdiv_rn(x, eff)) : 0u;
+}
+// ---- fast exact form of the two-level NVFP4 quantiser -------------------------------------------
+// The reference decides  fl32(x / eff) > thr  (thr = 0.25 ... 5, '>=' for negative x).  x is a bf16
+// value (8 significant bits), eff = micro * T with micro a UE4M3 value (4 bits).  When T has at most 12
+// significant bits, thr * eff is exact in fp32 and is either equal to |x| or differs from it by more
+// than 2^-19 relative, far more than the 2^-24 the fp32 quotient can move; hence
+//      fl32(|x| / eff) > thr   <=>   |x| > thr * eff
+// and no division is needed at all: seven exact threshold products per group, seven integer compares
+// per value (adding the sign bit to the magnitude bits turns '>=' into '>').  The guarded-reciprocal
+// trick used for INT codes does not work here: with so few bits in eff, x * (1/eff) lands on or next to
+// a decision threshold for a quarter of all values.
+__device__ __forceinline__ bool nvfp4_short_tensor_scale(float T) { return (__float_as_uint(T) & 0xFFFu) == 0u; }
+static __device__ __noinline__ uint2 nvfp4_hw_group_exact(float v0, float v1, float v2, float v3, float v4, float v5, float v6, float v7, float v8, float v9, float v10, float v11, float v12, float v13, float v14, float v15, float eff) {
+  const float v[16] = {v0, v1, v2, v3, v4, v5, v6, v7, v8, v9, v10, v11, v12, v13, v14, v15};
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    lo |= nvfp4_hw_code(v[j], eff) << (4 * j);
+    hi |= nvfp4_hw_code(v[8 + j], eff) << (4 * j);
+  }
+  return make_uint2(lo, hi);
+}
+// Any group (partial, all-zero scale): exact per-element path, out of line for the same reason.
+static __device__ __noinline__ uint2 nvfp4_hw_group_partial(float v0, float v1, float v2, float v3, float v4, float v5, float v6, float v7, float v8, float v9, float v10, float v11, float v12, float v13, float v14, float v15, int nvalid, float eff) {
+  const float v[16] = {v0, v1, v2, v3, v4, v5, v6, v7, v8, v9, v10, v11, v12, v13, v14, v15};
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    lo |= (j < nvalid ? nvfp4_hw_code(v[j], eff) : 0u) << (4 * j);
+    hi |= (8 + j < nvalid ? nvfp4_hw_code(v[8 + j], eff) : 0u) << (4 * j);
+  }
+  return make_uint2(lo, hi);
+}
+__device__ __forceinline__ uint2 nvfp4_hw_group_fast(const float* v, float eff) {
+  const uint32_t t0 = __float_as_uint(__fmul_rn(0.25f, eff)), t1 = __float_as_uint(__fmul_rn(0.75f, eff)),
+                 t2 = __float_as_uint(__fmul_rn(1.25f, eff)), t3 = __float_as_uint(__fmul_rn(1.75f, eff)),
+                 t4 = __float_as_uint(__fmul_rn(2.5f, eff)), t5 = __float_as_uint(__fmul_rn(3.5f, eff)),
+                 t6 = __float_as_uint(__fmul_rn(5.f, eff));
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint32_t bits = __float_as_uint(v[j]);
+    const uint32_t neg = bits >> 31;
+    const uint32_t a = (bits & 0x7FFFFFFFu) + neg;
+    const uint32_t m = (a > t0) + (a > t1) + (a > t2) + (a > t3) + (a > t4) + (a > t5) + (a > t6);
+    w[j >> 3] |= (m | ((m != 0u ? neg : 0u) << 3)) << (4 * (j & 7));
+  }
+  return make_uint2(w[0], w[1]);
 }
 
 }  // namespace dq

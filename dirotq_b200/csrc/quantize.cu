@@ -134,22 +134,41 @@ __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const QuantArgs a) {
   const __nv_bfloat16* xr = a.x + row * a.x_pitch;
   const int c0 = chunk * 64;
   const int n_kb64_pad = (g.n_chunks + 3) & ~3;
+  const bool short_T = nvfp4_short_tensor_scale(g.T);
   uint32_t packed[8];
   uint32_t sfw = 0;
+  // whole chunk in range and 16-byte aligned: eight 16-byte loads instead of 64 scalar ones
+  const bool vec_ok = (a.perm == nullptr) && ((a.x_pitch & 7) == 0) && (c0 + 64 <= g.D) &&
+                      ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
+  uint4 raw[8];
+  if (vec_ok) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) raw[i] = __ldg(reinterpret_cast<const uint4*>(xr + c0) + i);
+  }
 #pragma unroll
   for (int gi = 0; gi < 4; ++gi) {
     float v[16];
     const int cg = c0 + gi * 16;
     const int nvalid = max(0, min(16, g.q_len - cg));
+    if (vec_ok) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[2 * gi]);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float f = 0.f;
-      if (j < nvalid) {
-        int64_t c = cg + j;
-        if (a.perm) c = a.perm[c];
-        f = __bfloat162float(xr[c]);
+      for (int j = 0; j < 8; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        v[2 * j] = (2 * j < nvalid) ? f.x : 0.f;
+        v[2 * j + 1] = (2 * j + 1 < nvalid) ? f.y : 0.f;
       }
-      v[j] = f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float f = 0.f;
+        if (j < nvalid) {
+          int64_t c = cg + j;
+          if (a.perm) c = a.perm[c];
+          f = __bfloat162float(xr[c]);
+        }
+        v[j] = f;
+      }
     }
     float amax = 0.f;
 #pragma unroll
@@ -166,10 +185,16 @@ __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const QuantArgs a) {
       float eff;
       uint8_t sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
       if (nvalid == 0) { sb = 0; eff = 0.f; }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) lo |= (j < nvalid ? nvfp4_hw_code(v[j], eff) : 0u) << (4 * j);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) hi |= (8 + j < nvalid ? nvfp4_hw_code(v[8 + j], eff) : 0u) << (4 * j);
+      if (nvalid == 16 && eff > 0.f && short_T) {
+        const uint2 c = nvfp4_hw_group_fast(v, eff);
+        lo = c.x;
+        hi = c.y;
+      } else {
+        const uint2 c = nvfp4_hw_group_partial(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11],
+                                               v[12], v[13], v[14], v[15], nvalid, eff);
+        lo = c.x;
+        hi = c.y;
+      }
       sfw |= (uint32_t)sb << (8 * gi);
     }
     packed[gi * 2] = lo;

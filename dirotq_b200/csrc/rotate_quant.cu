@@ -96,6 +96,19 @@ __device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr,
     }
     if (!a.codes) continue;
     const int nq = max(0, min(64, g.q_len - col));
+    if (nq < 64 && row_ok && a.tail) {
+      __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
+      const int t0 = col - g.q_len;               // tail index of v[0] (may be negative)
+      if (nq == 0 && (t0 & 7) == 0 && col + 64 <= g.D) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(tr + t0 + 8 * i) = make_uint4(xb[4 * i], xb[4 * i + 1], xb[4 * i + 2], xb[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (j >= nq && col + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+      }
+    }
     if (nq > 0) {
       const int chunk = col >> 6;
       float mx = -INFINITY, mn = INFINITY;
@@ -113,49 +126,40 @@ __device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr,
       if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
       else p = int_asym_params<true>(mx, mn, g.clip, maxq);
       const float rcp = __frcp_rn(p.scale);
-      uint32_t q[64];
+      if (nq < 64) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        uint32_t c = 0;
-        if (nq == 64 || j < nq) {
-          if constexpr (MODE == MODE_INT4_SYM) c = int_sym_nibble_fast(v[j], p.scale, rcp);
-          else c = int_asym_code_fast(v[j], p.scale, rcp, p.zero, maxq);
-        }
-        q[j] = c;
+        for (int j = 0; j < 64; ++j)
+          if (j >= nq) v[j] = 0.f;            // padding slots: symmetric code 0; asymmetric slots meet zero weights
       }
       if (row_ok) {
-        if constexpr (MODE == MODE_INT8_ASYM) {
+        if constexpr (MODE == MODE_INT4_SYM) {
+          uint32_t n8[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) n8[i] = int_sym_nib8_fast(v + 8 * i, p.scale, rcp);
+          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
+          dst[0] = planar32_from_nib8(n8[0], n8[1], n8[2], n8[3]);
+          dst[1] = planar32_from_nib8(n8[4], n8[5], n8[6], n8[7]);
+        } else if constexpr (MODE == MODE_INT4_ASYM) {
+          uint32_t n8[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint2 b = int_asym_byte8_fast(v + 8 * i, p.scale, rcp, p.zero, maxq);
+            n8[i] = squeeze_nibbles(b.x) | (squeeze_nibbles(b.y) << 16);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
+          dst[0] = planar32_from_nib8(n8[0], n8[1], n8[2], n8[3]);
+          dst[1] = planar32_from_nib8(n8[4], n8[5], n8[6], n8[7]);
+        } else {
           uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 64);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t* s = q + 16 * i + 4 * k;
-              w[k] = (s[0] & 0xFF) | ((s[1] & 0xFF) << 8) | ((s[2] & 0xFF) << 16) | ((s[3] & 0xFF) << 24);
-            }
-            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            const uint2 b0 = int_asym_byte8_fast(v + 16 * i, p.scale, rcp, p.zero, maxq);
+            const uint2 b1 = int_asym_byte8_fast(v + 16 * i + 8, p.scale, rcp, p.zero, maxq);
+            dst[i] = make_uint4(b0.x, b0.y, b1.x, b1.y);
           }
-        } else {
-          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
-          dst[0] = pack_planar32(q);
-          dst[1] = pack_planar32(q + 32);
         }
         a.scales[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.scale);
         if constexpr (MODE != MODE_INT4_SYM) a.zeros[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.zero);
-      }
-    }
-    if (nq < 64 && row_ok && a.tail) {
-      __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
-      const int t0 = col - g.q_len;               // tail index of v[0] (may be negative)
-      if (nq == 0 && (t0 & 7) == 0 && col + 64 <= g.D) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<uint4*>(tr + t0 + 8 * i) = make_uint4(xb[4 * i], xb[4 * i + 1], xb[4 * i + 2], xb[4 * i + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (j >= nq && col + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
       }
     }
   }
@@ -166,6 +170,7 @@ __device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t tadd
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   const int n_kb64_pad = (g.n_chunks + 3) & ~3;
+  const bool short_T = nvfp4_short_tensor_scale(g.T);
   for (int c0 = 0; c0 < a.BN; c0 += 64) {
     const int col = n0 + c0;
     if (col >= g.D) break;
@@ -211,10 +216,16 @@ __device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t tadd
           float eff = 0.f;
           uint8_t sb = 0;
           if (nvalid > 0) sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            lo |= (j < nvalid ? nvfp4_hw_code(v[16 * gi + j], eff) : 0u) << (4 * j);
-            hi |= (8 + j < nvalid ? nvfp4_hw_code(v[16 * gi + 8 + j], eff) : 0u) << (4 * j);
+          if (nvalid == 16 && eff > 0.f && short_T) {
+            const uint2 c = nvfp4_hw_group_fast(v + 16 * gi, eff);
+            lo = c.x;
+            hi = c.y;
+          } else {
+            const float* t = v + 16 * gi;
+            const uint2 c = nvfp4_hw_group_partial(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], t[9], t[10], t[11],
+                                                   t[12], t[13], t[14], t[15], nvalid, eff);
+            lo = c.x;
+            hi = c.y;
           }
           sfw |= (uint32_t)sb << (8 * gi);
         }
