@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--workload", default="pixart_int4", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=0, help="override the number of blocks (smoke runs only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run a small case for ncu instead of the benchmark: one 1152->1152 k=64 layer at M=16384 "
+                         "(38 MB in, 38 MB out), INT4 then NVFP4, three forwards each")
     return ap.parse_args()
 
 
@@ -192,9 +195,11 @@ def run_ours(args):
     M = tokens * batch                               # rows per GPU (weak scaling: fixed per-GPU batch)
     D = block[0].in_f
 
-    backend.patch_forward()
-    step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
-    backend.preconvert_rotations_to_device(step, dev)
+    import contextlib
+    with contextlib.redirect_stdout(sys.stderr):     # stdout carries the JSON line only
+        backend.patch_forward()
+        step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
+        backend.preconvert_rotations_to_device(step, dev)
     lin_ops, rot_ops = step.ops_per_step(M)
 
     # step input: synthetic activations with the config-0 distribution, in PINNED host memory
@@ -318,9 +323,29 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
             "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None}
 
 
+def profile_case():
+    import contextlib
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    torch.cuda.set_device(0)
+    M = 16384
+    x = synth_activations(M, 1152, torch.Generator().manual_seed(0)).cuda()
+    with contextlib.redirect_stdout(sys.stderr):
+        for quant in ("int4", "nvfp4"):
+            w = dit.make_wrapped_linear(dit.LayerDef("probe", 1152, 1152, tail=64), quant, 5, "cuda")
+            st = backend.prepare_layer(w, "cuda", w._b200_explicit)
+            for _ in range(3):
+                backend.linear_forward(st, x)
+    torch.cuda.synchronize()
+    ops.check_status()
+    print(json.dumps({"profile_case": "ok", "rows": M}))
+
+
 if __name__ == "__main__":
     a = parse()
-    if a.impl == "reference":
+    if a.profile_case:
+        profile_case()
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

@@ -222,7 +222,8 @@ int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_sf || !w_codes || !w_sf || !y) return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
   if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8))) return DIROTQ_E_ARG;
-  const uintptr_t al = reinterpret_cast<uintptr_t>(x_sf) | reinterpret_cast<uintptr_t>(w_sf) | reinterpret_cast<uintptr_t>(y);
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x_sf) | reinterpret_cast<uintptr_t>(w_sf) | reinterpret_cast<uintptr_t>(y) |
+                       reinterpret_cast<uintptr_t>(bias);
   if (al & 15) return DIROTQ_E_ALIGN;
   GemmFp4Args a;
   a.M = M;

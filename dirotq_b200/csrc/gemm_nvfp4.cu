@@ -26,7 +26,8 @@ constexpr int GF_STAGES = 6;
 constexpr int GF_TILE_BYTES = 128 * 128;     // 128 rows x 128 bytes (256 E2M1 or 64 bf16 per row)
 constexpr int GF_SF_BYTES = 4 * 512;         // four 64-element k-blocks of scale factors for 128 rows
 constexpr int GF_STAGE_BYTES = 2 * GF_TILE_BYTES + 2 * GF_SF_BYTES;   // 36864
-constexpr int GF_THREADS = 192;
+constexpr int GF_EPI_WARPS = 8;              // two per TMEM lane quarter, 64 output columns each
+constexpr int GF_THREADS = (2 + GF_EPI_WARPS) * 32;
 constexpr int GF_SMEM_BYTES = GF_STAGES * GF_STAGE_BYTES + 1024 + 256;
 constexpr uint32_t GF_TMEM_COLS = 512;
 constexpr uint32_t GF_SFA_COL = 256;         // two alternating slots of 16 columns each
@@ -57,7 +58,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_xq);
@@ -159,43 +160,50 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 2) >> 2;
     int buf = 0;
     uint32_t aph = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const int mb = t / n_tiles, nb = t - mb * n_tiles;
       if (!mbar_wait(accf_bar(buf), aph, abort_flag, a.status, ERR_WAIT_ACC_FULL)) break;
+      __syncwarp();
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 128;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 128 + half * 64;
       const int64_t row = (int64_t)mb * 128 + q * 32 + lane;
-      const int64_t n0 = (int64_t)nb * 128;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c0, v);
-        tmem_wait_ld();
-        if (row < a.M) {
+      const int64_t n0 = (int64_t)nb * 128 + half * 64;
+      uint32_t v[64];
+      tmem_ld32(taddr, v);
+      tmem_ld32(taddr + 32, v + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce_bar(buf));      // accumulator is in registers: hand it back early
+      if (row < a.M) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int64_t col = n0 + c0 + 8 * i;
-            if (col + 8 <= a.N) {
-              uint32_t w[4];
+        for (int i = 0; i < 8; ++i) {
+          const int64_t col = n0 + 8 * i;
+          if (col + 8 <= a.N) {
+            float b[8];
+            if (a.bias) {
+              const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col));
+              const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float b0 = a.bias ? __bfloat162float(a.bias[col + 2 * e]) : 0.f;
-                float b1 = a.bias ? __bfloat162float(a.bias[col + 2 * e + 1]) : 0.f;
-                __nv_bfloat162 h = __floats2bfloat162_rn(__fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), a.out_scale, b0),
-                                                         __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), a.out_scale, b1));
-                w[e] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(a.y + row * a.N + col) = make_uint4(w[0], w[1], w[2], w[3]);
+              for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(bh[e]); b[2 * e] = f.x; b[2 * e + 1] = f.y; }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) b[e] = 0.f;
             }
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), a.out_scale, b[2 * e]),
+                                                       __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), a.out_scale, b[2 * e + 1]));
+              w[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(a.y + row * a.N + col) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acce_bar(buf));
       buf ^= 1;
       if (buf == 0) aph ^= 1;
     }
