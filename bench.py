@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the DiRotQ quantized-linear path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload pixart_int4|pixart_nvfp4]
+    python bench.py [--gpus N] [--steps K] [--warmup W]
+                    [--workload pixart_int4|pixart_nvfp4|flux_int4|sana_int4|sana_w4a8] [--flux-ffn tp|dp]
     python bench.py --impl reference ...      # the reference's fp32 CPU forward on a bounded sample
 
 One "step" = every wrapped linear of one denoising step of the named DiT (BASELINE config 1 by
@@ -30,6 +31,16 @@ WORKLOADS = {
                     "batch 8 x 4096 tokens per GPU"),
     "pixart_nvfp4": ("pixart_block", 28, "nvfp4", 4096, 8,
                      "BASELINE config 2: same step in NVFP4 W4A4 (E2M1 g16, UE4M3 group scales, fp32 tensor scale)"),
+    "sana_int4": ("sana_block", 20, "int4", 1024, 16,
+                  "BASELINE config 4 (W4A4): SANA-1.6B-shaped step, 20 blocks x 6 linears (hidden 2240, k=320, per-head "
+                  "70 x 32 out-projections), batch 16 x 1024 tokens per GPU"),
+    "sana_w4a8": ("sana_block", 20, "int8", 1024, 16,
+                  "BASELINE config 4 (W4A8): same step with asymmetric 8-bit activations"),
+    # FLUX runs at a FIXED global batch (strong scaling); see dirotq_b200.parallel.FluxLinearStep
+    "flux_int4": ("flux_double_block", 57, "int4", 4608, 4,
+                  "BASELINE config 3: FLUX.1-dev-shaped step, 19 double-stream (image 4096 + text 512 tokens) + 38 "
+                  "single-stream blocks, INT W4A4 g64 k=384, per-head out-projections, K=12288 down-projections "
+                  "without rotation, global batch 4"),
 }
 
 
@@ -41,6 +52,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="pixart_int4", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=0, help="override the number of blocks (smoke runs only)")
+    ap.add_argument("--flux-ffn", default="tp", choices=["tp", "dp"],
+                    help="flux_int4 at N > 1: FFN pairs tensor-parallel (all-gather + reduce-scatter) or row-sharded")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-case", action="store_true",
                     help="run a small case for ncu instead of the benchmark: one 1152->1152 k=64 layer at M=16384 "
@@ -71,8 +84,13 @@ def cpu_reference_tflops(workload, steps, warmup, budget_s=20.0):
             specs.append((ld, None, W, b))
             continue
         cfg = O.QuantCfg(4, 16 if quant == "nvfp4" else 64, True, 1.0, ld.tail, "nvfp4" if quant == "nvfp4" else "int")
+        bits = 8 if quant == "int8" else 4
+        cfg = O.QuantCfg(bits, cfg.groupsize, bits == 4, 1.0, ld.tail, cfg.quant_dtype)
         U = O.random_orthogonal(ld.in_f, g).float() if ld.kind == "hidden" else None
-        specs.append((ld, O.LayerSpec(W, b, cfg, rotation=U), W, b))
+        Uh = None
+        if ld.kind == "perhead":
+            Uh = torch.stack([O.random_orthogonal(ld.head_dim, g).float() for _ in range(ld.heads)])
+        specs.append((ld, O.LayerSpec(W, b, cfg, rotation=U, rotation_per_head=Uh), W, b))
     ops = sum(dit.linear_ops(ld, M) for ld in block)
 
     def one_pass():
@@ -191,23 +209,45 @@ def run_ours(args):
     blk_name, n_blocks, quant, tokens, batch, desc = WORKLOADS[args.workload]
     if args.blocks:
         n_blocks = args.blocks
-    block = getattr(dit, blk_name)()
-    M = tokens * batch                               # rows per GPU (weak scaling: fixed per-GPU batch)
-    D = block[0].in_f
-
+    is_flux = args.workload.startswith("flux")
+    from dirotq_b200.synth import synth_activations
     import contextlib
+    g = torch.Generator().manual_seed(1234 + rank)
     with contextlib.redirect_stdout(sys.stderr):     # stdout carries the JSON line only
         backend.patch_forward()
-        step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
-        backend.preconvert_rotations_to_device(step, dev)
-    lin_ops, rot_ops = step.ops_per_step(M)
-
-    # step input: synthetic activations with the config-0 distribution, in PINNED host memory
-    g = torch.Generator().manual_seed(1234 + rank)
-    from dirotq_b200.synth import synth_activations
-    x_host = synth_activations(M, D, g).reshape(batch, tokens, D).pin_memory()
+        if is_flux:
+            from dirotq_b200.parallel import FluxLinearStep
+            n_double = args.blocks if args.blocks else 19
+            step = FluxLinearStep(world, rank, dev, batch=batch, n_double=n_double, n_single=2 * n_double,
+                                  ffn=args.flux_ffn, quant=quant)
+            backend.preconvert_rotations_to_device(step.layers, dev)
+            for lyr in step.layers:                  # the packed device state is all the forward needs
+                lyr._b200_explicit = None
+                lyr.rotation = lyr.rotation_per_head = None
+            torch.cuda.empty_cache()
+            n_blocks = 3 * n_double
+            M, D, out_f = step.rows_per_rank("single"), 3072, 3072   # rows per GPU (strong scaling: global batch fixed)
+            lin_ops, rot_ops = step.ops_per_step()
+            lin_ops, rot_ops = lin_ops / world, rot_ops / world      # per-GPU share; the JSON line reports world x this
+            x_host = synth_activations(M, D, g).pin_memory()
+            y_shape = (M, out_f)
+            scaling = "strong"
+            l2_note = f"inputs larger than L2 ({len(step.layers)} distinct weight sets per step)"
+        else:
+            block = getattr(dit, blk_name)()
+            M = tokens * batch                           # rows per GPU (weak scaling: fixed per-GPU batch)
+            D, out_f = block[0].in_f, block[-1].out_f
+            step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
+            backend.preconvert_rotations_to_device(step, dev)
+            lin_ops, rot_ops = step.ops_per_step(M)
+            # step input: synthetic activations with the config-0 distribution, in PINNED host memory
+            x_host = synth_activations(M, D, g).reshape(batch, tokens, D).pin_memory()
+            y_shape = (batch, tokens, out_f)
+            scaling = "weak"
+            l2_note = (f"inputs larger than L2 ({M * D * 2 / 1e6:.0f} MB activations + {len(step.layers)} distinct "
+                       f"weight sets per step)")
     x_dev = x_host.to(dev, non_blocking=True)
-    y_host = torch.empty(batch, tokens, block[-1].out_f, dtype=torch.bfloat16).pin_memory()
+    y_host = torch.empty(*y_shape, dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
 
     def barrier():
@@ -255,7 +295,9 @@ def run_ours(args):
     ops.check_status(dev)
 
     # roofline pass: the same launches, the dominant kernel bracketed by CUDA events on its stream
-    roof = roofline_pass(step, x_dev, M, quant, dev, args.steps) if rank == 0 else None
+    roof = roofline_pass(step, x_dev, M, quant, dev, args.steps) if rank == 0 and not is_flux else None
+    if rank == 0 and is_flux:
+        roof = roofline_pass_flux(step, x_dev, dev)
 
     cb = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -265,10 +307,12 @@ def run_ours(args):
         line = {
             "metric": "w4a4_linear_tflops", "value": world * lin_ops / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "e2m1" if quant == "nvfp4" else "s8", "data": "synthetic",
-            "config": {"workload": desc, "blocks": n_blocks, "rows_per_gpu": M, "global_batch": batch * world,
-                       "l2": "inputs larger than L2 (75 MB activations + 224 distinct weight sets per step)",
+            "config": {"workload": desc, "blocks": n_blocks, "rows_per_gpu": M,
+                       "global_batch": batch if is_flux else batch * world,
+                       "parallelism": (f"rows/{world} + ffn-{step.ffn}" if is_flux else f"dp{world}"),
+                       "l2": l2_note,
                        "linear_gflop_per_step_per_gpu": lin_ops / 1e9, "rotation_gflop_per_step_per_gpu": rot_ops / 1e9},
             "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
@@ -320,6 +364,36 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     return {"bound": "tensor", "kernel": "gemm_nvfp4_kernel" if quant == "nvfp4" else "gemm_int_kernel",
             "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained; dense INT8 is nominally 2x and FP4 4x that figure",
+            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None}
+
+
+def roofline_pass_flux(step, x_dev, dev):
+    """FLUX: the same bracketing over the hidden-rotation attention linears of the single-stream blocks."""
+    from dirotq_b200 import ops
+    hbm, bf16_burst, bf16_sust, which = measured_peaks()
+    pairs, ops_total, buf = [], 0.0, None
+    M = x_dev.shape[0]
+    for stream, ws, wu, wd in step.blocks:
+        if stream != "single":
+            continue
+        for w in ws[:3]:
+            st = w._b200_state
+            buf = buf if buf is not None else ops.alloc_act(st.fmt, M, dev)
+            ops.rotate_quantize(x_dev, st.rot_t, st.fmt, out=buf)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            pw = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks,
+                                      st.w_codes, st.w_scales, st.w_sum)
+            ops.gemm_w4a4_int(buf, pw, st.w_tail, st.bias)
+            e1.record()
+            pairs.append((e0, e1))
+            ops_total += 2.0 * M * 3072 * 3072
+    torch.cuda.synchronize()
+    t_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    achieved = ops_total / (t_ms * 1e-3) / 1e12
+    return {"bound": "tensor", "kernel": "gemm_int_kernel", "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s",
+            "frac": achieved / bf16_sust,
+            "peak_source": f"{which}: cuBLAS bf16 sustained; dense INT8 is nominally 2x that figure",
             "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None}
 
 

@@ -219,6 +219,9 @@ def _fused_forward_b200(self, x):
     """ActQuantWrapper.forward on the B200 kernels (contract: dirotq_fused_unrotation_fast.py:56-141)."""
     if self.quantizer.bits >= 16:
         s16 = getattr(self, "_b200_w4a16", None)
+        if s16 is None and getattr(self, "_b200_explicit", None) is not None:
+            s16 = prepare_w4a16(self, x.device, self._b200_explicit)     # synthetic layer: no dense weight
+            object.__setattr__(self, "_b200_w4a16", s16)
         if s16 is None:
             return self.module(x).to(x.dtype)
         shp = x.shape

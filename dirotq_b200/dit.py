@@ -43,18 +43,26 @@ def pixart_block(k: int = 64, per_head_out: bool = False) -> List[LayerDef]:
     ]
 
 
-def flux_double_block(k: int = 384, k_down: int = 1536, rotate_down: bool = False) -> List[LayerDef]:
-    """One FLUX double-stream block, image stream (the text stream has the same linears at M_txt)."""
+def flux_double_block(k: int = 384, k_down: int = 1536, rotate_down: bool = False,
+                      per_head_out: bool = True) -> List[LayerDef]:
+    """One FLUX double-stream block, one stream (image and text streams have the same linears, at
+    M_img and M_txt rows).  hidden 3072 = 24 heads x 128, MLP 12288.  The K = 12288 down-projection
+    runs without a rotation on the speed path (speedup/report_flux_w4a4_no_rot_ffdown.py:10-12);
+    the attention out-projection takes a per-head rotation (16 of 128 coefficients per head 16-bit)."""
     down = LayerDef("ff.net.2", 12288, 3072, kind="hidden" if rotate_down else "norot", tail=k_down, source="ff")
+    out_kw = dict(kind="perhead", tail=16, heads=24, head_dim=128) if per_head_out else dict(kind="hidden", tail=k)
     return [LayerDef("attn.to_q", 3072, 3072, tail=k), LayerDef("attn.to_k", 3072, 3072, tail=k),
-            LayerDef("attn.to_v", 3072, 3072, tail=k), LayerDef("attn.to_out.0", 3072, 3072, tail=k),
+            LayerDef("attn.to_v", 3072, 3072, tail=k), LayerDef("attn.to_out.0", 3072, 3072, **out_kw),
             LayerDef("ff.net.0.proj", 3072, 12288, tail=k), down]
 
 
-def flux_single_block(k: int = 384, k_down: int = 1536) -> List[LayerDef]:
+def flux_single_block(k: int = 384, k_down: int = 1536, per_head_out: bool = True) -> List[LayerDef]:
+    """One FLUX single-stream block; proj_out is split into its attention part (linears.0) and its
+    MLP part (linears.1), as speedup/split_proj_out.py:38-48 does."""
+    out_kw = dict(kind="perhead", tail=16, heads=24, head_dim=128) if per_head_out else dict(kind="hidden", tail=k)
     return [LayerDef("attn.to_q", 3072, 3072, tail=k), LayerDef("attn.to_k", 3072, 3072, tail=k),
             LayerDef("attn.to_v", 3072, 3072, tail=k), LayerDef("proj_mlp", 3072, 12288, tail=k),
-            LayerDef("proj_out.linears.0", 3072, 3072, tail=k),
+            LayerDef("proj_out.linears.0", 3072, 3072, **out_kw),
             LayerDef("proj_out.linears.1", 12288, 3072, kind="norot", tail=k_down, source="ff")]
 
 

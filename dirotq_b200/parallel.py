@@ -117,3 +117,100 @@ def build_flux_tp_ffn(world: int, rank: int, quant: str = "int4", device="cuda",
     backend.preconvert_rotations_to_device(holder, device)
     gelu = lambda t: torch.nn.functional.gelu(t, approximate="tanh")
     return TPFeedForward(lambda x: up(x), lambda h: down(h), gelu)
+
+
+class FluxLinearStep:
+    """Every wrapped linear of one FLUX.1-dev denoising step (19 double-stream blocks on the image and
+    the text stream, 38 single-stream blocks on their concatenation) at a FIXED global batch, split
+    over `world` ranks (strong scaling).
+
+    Token rows are independent through a quantised linear, so the attention-side linears (to_q/k/v,
+    out-projection) run on this rank's M/world rows with no communication.  The FFN pairs
+    (ff.net.0.proj -> GELU -> ff.net.2, and proj_mlp -> GELU -> proj_out.linears.1) run either the
+    same way (ffn="dp") or tensor-parallel (ffn="tp"): all-gather the rows, column-split
+    up-projection, row-split down-projection without rotation, reduce-scatter of the partial sums
+    back to row shards - two NCCL collectives per FFN, none elsewhere.  Weights are synthetic and
+    drawn per rank at the slice's shape; equality of a split FFN with the unsplit one is a property
+    of the slicing (build_flux_tp_ffn), tested separately.
+    """
+
+    def __init__(self, world: int, rank: int, device, batch: int = 4, n_double: int = 19, n_single: int = 38,
+                 ffn: str = "tp", quant: str = "int4", seed: int = 3000, k: int = 384):
+        from . import dit
+        import torch.nn as nn
+        assert ffn in ("tp", "dp")
+        self.world, self.rank, self.ffn = world, rank, ffn if world > 1 else "dp"
+        self.rows = {"img": batch * 4096, "txt": batch * 512, "single": batch * 4608}
+        for m in self.rows.values():
+            if m % world:
+                raise ValueError(f"{m} rows do not split over {world} ranks")
+        self.hidden, self.inner = 3072, 12288
+        tp = world if self.ffn == "tp" else 1
+        tp_slices(self.inner, tp, 0, 64)
+        ph = dict(kind="perhead", tail=16, heads=24, head_dim=128)
+        attn = [dit.LayerDef(n, 3072, 3072, tail=k) for n in ("to_q", "to_k", "to_v")] + \
+               [dit.LayerDef("to_out", 3072, 3072, **ph)]
+        up = dit.LayerDef("ffn_up", 3072, self.inner // tp, tail=k)
+        down = dit.LayerDef("ffn_down", self.inner // tp, 3072, kind="norot", tail=0, source="ff")
+        self.census = []            # (stream, LayerDef at full size) for the operation count
+        self.blocks = []            # (stream, [attn wrappers], up, down)
+        layers = []
+        s = seed + 104729 * rank
+        for stream, n in (("img", n_double), ("txt", n_double), ("single", n_single)):
+            for _ in range(n):
+                ws = [dit.make_wrapped_linear(ld, quant, s + i, device) for i, ld in enumerate(attn)]
+                wu = dit.make_wrapped_linear(up, quant, s + 4, device)
+                wd = dit.make_wrapped_linear(down, quant, s + 5, device)
+                if self.ffn == "tp" and rank != 0:
+                    wd._b200_explicit["bias"] = None        # the bias enters the reduced sum once
+                s += 6
+                self.blocks.append((stream, ws, wu, wd))
+                layers += ws + [wu, wd]
+                self.census += [(stream, ld) for ld in attn]
+                self.census += [(stream, dit.LayerDef("ffn_up", 3072, self.inner)),
+                                (stream, dit.LayerDef("ffn_down", self.inner, 3072))]
+        self.layers = nn.ModuleList(layers)
+        self._gather = {}
+
+    def ops_per_step(self):
+        """(linear, rotation) operations of the whole step at the global batch."""
+        from . import dit
+        lin = sum(dit.linear_ops(ld, self.rows[st]) for st, ld in self.census)
+        rot = sum(2.0 * self.rows[st] * 3072 * (128 if ld.kind == "perhead" else 3072)
+                  for st, ld in self.census if ld.in_f == 3072)
+        return lin, rot
+
+    def kernel_launches_per_step(self) -> int:
+        return 2 * len(self.layers)
+
+    def rows_per_rank(self, stream: str) -> int:
+        return self.rows[stream] // self.world
+
+    def _ffn(self, x, wu, wd):
+        if self.ffn == "dp":
+            h = torch.nn.functional.gelu(wu(x), approximate="tanh")
+            return wd(h.mul_(0.25))
+        m = x.shape[0]
+        key = (m, x.dtype)
+        if key not in self._gather:
+            self._gather[key] = (torch.empty(self.world * m, self.hidden, dtype=x.dtype, device=x.device),
+                                 torch.empty(m, self.hidden, dtype=x.dtype, device=x.device))
+        full, out = self._gather[key]
+        dist.all_gather_into_tensor(full, x.contiguous())
+        h = torch.nn.functional.gelu(wu(full.unsqueeze(0)), approximate="tanh")
+        part = wd(h.mul_(0.25)).reshape(self.world * m, self.hidden)
+        dist.reduce_scatter_tensor(out, part, op=dist.ReduceOp.SUM)
+        return out
+
+    def __call__(self, x_rows: torch.Tensor) -> torch.Tensor:
+        """x_rows: this rank's [rows_per_rank("single"), 3072] bf16 rows; image rows first, then text."""
+        m_img = self.rows_per_rank("img")
+        views = {"img": x_rows[:m_img], "txt": x_rows[m_img:], "single": x_rows}
+        y = None
+        for stream, ws, wu, wd in self.blocks:
+            x = views[stream]
+            x3 = x.unsqueeze(0)
+            for w in ws:
+                y = w(x3)
+            y = self._ffn(x, wu, wd) if self.ffn == "tp" else self._ffn(x3, wu, wd)
+        return y

@@ -90,3 +90,33 @@ def assert_act_matches_oracle(buf: ops.ActBuffers, x_rot2d: torch.Tensor):
     if lay.tail_total > 0:
         assert torch.equal(dec["tail"].view(torch.int16), r.tail.reshape(M, -1).contiguous().view(torch.int16))
     return dec, r
+
+
+def dense_reference_weight(w, ld) -> torch.Tensor:
+    """fp32 [N, D] fused weight, in the layout nn.Linear holds in the reference ([Q(low) | tail];
+    per head: [low_h | tail_h] for every head), rebuilt from the explicit codes a synthetic layer carries."""
+    ex = w._b200_explicit
+    N = ld.out_f
+    if "nibbles" in ex:
+        vals = torch.tensor(O.E2M1_VALUES)
+        nib = ex["nibbles"].cpu().long()
+        mag = vals[nib & 7] * torch.where((nib & 8) != 0, -1.0, 1.0)
+        sc = ex["scales_e4m3"].cpu().view(torch.float8_e4m3fn).float() * ex["tensor_scale"]
+        low = (mag.reshape(N, -1, 16) * sc.unsqueeze(-1)).reshape(N, -1)
+    else:
+        codes = ex["codes"].cpu().float()
+        sc = ex["scales"].cpu().float()
+        G = sc.shape[1]
+        gs = (ld.head_dim - ld.tail) if ld.kind == "perhead" else 64
+        pad = G * gs - codes.shape[1]
+        if pad:
+            codes = torch.nn.functional.pad(codes, (0, pad))
+        low = (codes.reshape(N, G, gs) * sc.unsqueeze(-1)).reshape(N, -1)[:, : ex["codes"].shape[1]]
+    tail = ex.get("w_tail")
+    if tail is None:
+        return low
+    tail = tail.cpu().float().to(torch.bfloat16).float()
+    if ld.kind == "perhead":
+        H, d, hl = ld.heads, ld.head_dim, ld.tail
+        return torch.cat([low.reshape(N, H, d - hl), tail.reshape(N, H, hl)], dim=2).reshape(N, H * d)
+    return torch.cat([low, tail], dim=1)
