@@ -43,14 +43,17 @@ class LayerState:
     bias: Optional[torch.Tensor]
     w_tensor_scale: float = 1.0
     n_lossy_groups: int = 0
+    folded: Optional[ops.FoldedWeightF16] = None     # INT4 activations: constants of the tensor-rate GEMM
     _c: Optional[LinearC] = None
     _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
 
     def c_struct(self) -> LinearC:
         if self._c is None:
             p = lambda t: C.c_void_p(0 if t is None else t.data_ptr())
+            f = self.folded
             self._c = LinearC(self.fmt.c(), self.out_features, p(self.rot_t), p(self.perm_idx), p(self.w_codes),
-                              p(self.w_scales), p(self.w_sum), p(self.w_tail), p(self.bias), self.w_tensor_scale)
+                              p(self.w_scales), p(self.w_sum), p(self.w_tail), p(self.bias), self.w_tensor_scale,
+                              p(f.mult if f else None), p(f.colscale if f else None), p(f.tail if f else None))
         return self._c
 
     def workspace(self, M: int, device) -> torch.Tensor:
@@ -118,6 +121,11 @@ def _act_format(w) -> ops.ActFormat:
                          tensor_scale=_HW_NVFP4_ACT_SCALE)
 
 
+# INT4-activation layers run the tensor-rate GEMM (4-bit codes expanded to fp16 next to the tensor core).
+# Set to False to route them through the exact-integer kind::i8 kernel instead (W4A8 always uses it).
+INT4_TENSOR_RATE_GEMM = True
+
+
 def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerState:
     """Build the packed device state of one ActQuantWrapper.
 
@@ -182,7 +190,10 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
         bias = None if explicit["bias"] is None else explicit["bias"].to(device=dev, dtype=torch.bfloat16).contiguous()
     else:
         bias = None if w.module.bias is None else w.module.bias.data.to(device=dev, dtype=torch.bfloat16).contiguous()
-    return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy)
+    folded = None
+    if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM):
+        folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
+    return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded)
 
 
 @dataclass

@@ -215,6 +215,94 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
   return launch_gemm_int(a, static_cast<cudaStream_t>(stream));
 }
 
+int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_scales, const void* w_tail,
+                                  int32_t tail_total, int32_t tail_pitch, void* w_mult, float* w_colscale,
+                                  void* w_tail_out, void* stream) {
+  if (n_chunks <= 0 || N <= 0 || !w_scales || !w_mult || !w_colscale) return DIROTQ_E_ARG;
+  if (tail_total < 0 || (tail_total > 0 && (!w_tail || !w_tail_out || tail_pitch < tail_total || tail_pitch % 8)))
+    return DIROTQ_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(w_tail) | reinterpret_cast<uintptr_t>(w_tail_out)) & 15) return DIROTQ_E_ALIGN;
+  return launch_fold_weight_scales(w_scales, n_chunks, N, ld_rows(N), w_mult, w_colscale,
+                                   tail_total > 0 ? static_cast<const __nv_bfloat16*>(w_tail) : nullptr,
+                                   static_cast<__nv_bfloat16*>(w_tail_out), tail_pitch, static_cast<cudaStream_t>(stream));
+}
+
+struct F16Carve {
+  size_t mult, add, rs, tail, total;
+};
+static F16Carve carve_f16(int64_t M, int32_t n_chunks, int32_t tail_pitch) {
+  F16Carve c;
+  const size_t ldm = (size_t)ld_rows(M);
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  c.mult = 0;
+  c.add = up(c.mult + (size_t)n_chunks * ldm * 2);
+  c.rs = up(c.add + (size_t)n_chunks * ldm * 2);
+  c.tail = up(c.rs + ldm * 4);
+  c.total = up(c.tail + (size_t)M * (size_t)tail_pitch * 2);
+  return c;
+}
+
+size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int32_t n_chunks, int32_t tail_pitch) {
+  if (M < 0 || n_chunks <= 0 || tail_pitch < 0) return 0;
+  return carve_f16(M, n_chunks, tail_pitch).total;
+}
+
+int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
+                             const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
+                             const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
+                             int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
+  if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM) return DIROTQ_E_UNSUPPORTED;
+  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_codes || !w_mult || !w_colscale || !y || !workspace)
+    return DIROTQ_E_ARG;
+  if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
+  if (a_mode == DIROTQ_INT4_ASYM && !x_zeros) return DIROTQ_E_ARG;
+  if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8)))
+    return DIROTQ_E_ARG;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(w_codes) |
+                       reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x_tail) |
+                       reinterpret_cast<uintptr_t>(w_tail_scaled) | reinterpret_cast<uintptr_t>(w_mult);
+  if (al & 15) return DIROTQ_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return DIROTQ_E_ALIGN;
+  const int32_t tp = tail_total > 0 ? tail_pitch : 0;
+  const F16Carve c = carve_f16(M, n_chunks, tp);
+  if (workspace_bytes < c.total) return DIROTQ_E_ARG;
+  if (M == 0) return DIROTQ_OK;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* tail_s = tail_total > 0 ? reinterpret_cast<__nv_bfloat16*>(ws + c.tail) : nullptr;
+  int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales),
+                                  a_mode == DIROTQ_INT4_ASYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
+                                  n_chunks, M, ld_rows(M), ws + c.mult, ws + c.add, reinterpret_cast<float*>(ws + c.rs),
+                                  tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
+  if (rc) return rc;
+  GemmIntF16Args a;
+  a.a_mode = a_mode;
+  a.M = M;
+  a.N = N;
+  a.n_chunks = n_chunks;
+  a.xq = static_cast<const uint8_t*>(x_codes);
+  a.x_row_bytes = (int64_t)n_chunks * 32;
+  a.a_mult = ws + c.mult;
+  a.a_add = ws + c.add;
+  a.rs = reinterpret_cast<const float*>(ws + c.rs);
+  a.ldm = ld_rows(M);
+  a.wq = static_cast<const uint8_t*>(w_codes);
+  a.w_row_bytes = (int64_t)n_chunks * 32;
+  a.w_mult = w_mult;
+  a.cs = w_colscale;
+  a.ldn = ld_rows(N);
+  a.xt = tail_s;
+  a.wt = static_cast<const __nv_bfloat16*>(w_tail_scaled);
+  a.kt = tail_total;
+  a.kt_pitch = tail_pitch;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.status = status;
+  a.force_bn = 0;
+  return launch_gemm_int_f16(a, st);
+}
+
 int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
                            const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
                            const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
@@ -245,8 +333,11 @@ int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x
 }
 
 struct WsCarve {
-  size_t codes, scales, zeros, tail, total;
+  size_t codes, scales, zeros, tail, fold, total;
 };
+static bool uses_f16_gemm(const dirotq_linear* lin, const ActGeom& g) {
+  return lin->w_mult != nullptr && (g.mode == DIROTQ_INT4_SYM || g.mode == DIROTQ_INT4_ASYM);
+}
 static int carve(const dirotq_linear* lin, int64_t M, ActGeom* g, WsCarve* w) {
   int rc = make_geom(&lin->fmt, g);
   if (rc) return rc;
@@ -256,7 +347,11 @@ static int carve(const dirotq_linear* lin, int64_t M, ActGeom* g, WsCarve* w) {
   w->scales = w->codes + dirotq_act_codes_bytes(&l, M);
   w->zeros = w->scales + dirotq_act_scales_bytes(&lin->fmt, &l, M);
   w->tail = w->zeros + dirotq_act_zeros_bytes(&lin->fmt, &l, M);
-  w->total = w->tail + (g->tail_total > 0 ? dirotq_act_tail_bytes(&l, M) : 0);
+  w->fold = w->tail + (g->tail_total > 0 ? dirotq_act_tail_bytes(&l, M) : 0);
+  w->fold = (w->fold + 255) & ~size_t(255);
+  w->total = w->fold;
+  if (uses_f16_gemm(lin, *g))
+    w->total += dirotq_gemm_w4a4_int_f16_workspace_bytes(M, g->n_chunks, g->tail_total > 0 ? g->tail_pitch : 0);
   return DIROTQ_OK;
 }
 
@@ -291,6 +386,12 @@ int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, vo
     return dirotq_gemm_w4a4_nvfp4(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
                                   lin->fmt.tensor_scale * lin->w_tensor_scale, tail, lin->w_tail, g.tail_total,
                                   g.tail_pitch, lin->bias, y, status, stream);
+  if (uses_f16_gemm(lin, g)) {
+    if (!lin->w_colscale || (g.tail_total > 0 && !lin->w_tail_f16)) return DIROTQ_E_ARG;
+    return dirotq_gemm_w4a4_int_f16(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
+                                    lin->w_mult, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
+                                    lin->bias, y, ws + w.fold, w.total - w.fold, status, stream);
+  }
   return dirotq_gemm_w4a4_int(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
                               static_cast<const float*>(lin->w_scales), lin->w_sum, tail, lin->w_tail, g.tail_total,
                               g.tail_pitch, lin->bias, y, nullptr, status, stream);

@@ -1,0 +1,515 @@
+// Kernel 2 (INT4, tensor-rate variant): W4A4 GEMM whose 4-bit operands are dequantised to fp16 on their
+// way from shared memory to the tensor core, so that ONE fp32 accumulator runs over the whole K and the
+// per-chunk CUDA-core drain of the exact-integer kernel (gemm_int.cu) disappears.
+//
+//   y[m,n] = rs[m] cs[n] ( sum_k a'[m,k] b'[n,k] + xt'[m,:] . wt'[n,:] ) + bias[n]
+//   a'[m,k] = (qx[m,k] - zx[m,c]) * sx[m,c] / rs[m]      exact in fp16 for symmetric codes
+//   b'[n,k] =  qw[n,k]            * sw[n,c] / cs[n]      rounded once to fp16 (11 bits; the reference
+//                                                         keeps bf16(qw * sw), 8 bits)
+//   rs[m], cs[n] = powers of two that bring a row's / a column's largest scale to [2^-10, 2^-9)
+//
+// This is the arithmetic of the reference's own linear on the fake-quantised tensor
+// (DiRotQ dirotq_fused_unrotation_fast.py:141: a 16-bit GEMM with fp32 accumulation over
+// s*(q-z) and the stored weight), with operands that stay 4-bit in HBM, L2 and the TMA ring.
+//
+// Nibble -> fp16 without integer-to-float conversion: a nibble m left in the low mantissa bits of an
+// otherwise zero half is the subnormal m * 2^-24; one fused multiply-add with the pre-scaled group
+// scale (s * 2^24) and the addend -(z * s) gives (m - z) * s with a single rounding.  Two nibbles
+// of a byte are taken in place (bits 0-3 and 4-7, the latter with the multiplier s * 2^20), so a
+// 32-bit word of eight codes costs one shift, four logic ops and four packed FMAs.
+// The order in which a chunk's 64 values land along K is a fixed permutation, the same for both
+// operands, which a dot product does not see.
+//
+// Data flow per persistent CTA (128 x BN output tiles, K walked in 64-wide chunks):
+//   TMA            4-bit codes (32 B per row per chunk) + the chunk's multipliers -> "raw" ring
+//   8 converter warps  raw ring -> fp16 operand tiles in the 128-byte-swizzled K-major layout
+//   UMMA issuer    tcgen05.mma kind::f16 (fp16 x fp16 -> fp32), 4 x K=16 per chunk, 128 x BN in TMEM;
+//                  bf16 tail tiles (TMA straight into the operand ring) accumulate into the same tile
+//   8 epilogue warps  tcgen05.ld, * rs[m] * cs[n], + bias, bf16, 16-byte stores; two accumulators
+//                  alternate so the next tile's UMMAs overlap the epilogue
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "layout.cuh"
+#include "launchers.cuh"
+#include "ptx.cuh"
+#include "tma_host.cuh"
+
+namespace dq {
+
+constexpr int GF_RAW_STAGES = 4;
+constexpr int GF_EXP_STAGES = 3;
+constexpr int GF_EPI_WARPS = 8;
+constexpr int GF_CONV_WARPS = 8;
+constexpr int GF_CONV_THREADS = GF_CONV_WARPS * 32;
+constexpr int GF_THREADS = (GF_EPI_WARPS + 2 + GF_CONV_WARPS) * 32;      // 576
+
+template <int BN> struct GfCfg {
+  static constexpr int A_EXP = 128 * 128;                  // 128 rows x 64 halves
+  static constexpr int B_EXP = BN * 128;
+  static constexpr int EXP_STAGE = A_EXP + B_EXP;
+  static constexpr int RAW_A = 128 * 32;
+  static constexpr int RAW_B = BN * 32;
+  static constexpr int OFF_B = RAW_A;
+  static constexpr int OFF_AM = OFF_B + RAW_B;              // a_mult [128] fp16
+  static constexpr int OFF_AA = OFF_AM + 256;               // a_add  [128] fp16
+  static constexpr int OFF_WM = OFF_AA + 256;               // w_mult [BN]  fp16
+  static constexpr int RAW_STAGE = OFF_WM + 512;
+  static constexpr uint32_t RAW_TX = RAW_A + RAW_B + 256 + 256 + BN * 2;
+  static constexpr int SMEM_BYTES = GF_EXP_STAGES * EXP_STAGE + GF_RAW_STAGES * RAW_STAGE + 1024 + 256;
+  static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+};
+
+struct GfMaps {
+  CUtensorMap xq, wq, am, aa, wm, xt, wt;
+};
+
+template <int N> struct GfRing {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void next() { if (++s == N) { s = 0; ph ^= 1; } }
+};
+
+__device__ __forceinline__ void gf_sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint4 gf_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t gf_lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+  return v;
+}
+// (a & b) ^ c in one logic op
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// One 32-slot block (16 bytes of planar nibbles) of one row -> 32 halves (4 x 16 bytes).
+//   xr    : per-nibble XOR (0x8 turns a two's-complement nibble into offset binary; 0 for unsigned codes)
+//   mlo   : (s * 2^24) twice;  mhi = (s * 2^20) twice;  add = -(z * s) twice (z = 8 for signed codes)
+__device__ __forceinline__ void expand_block(const uint4 p, uint32_t xr, uint32_t mlo, uint32_t mhi, uint32_t add,
+                                             uint32_t dst_row, int unit0, int rsw) {
+  const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+  const uint32_t xr_hi = xr << 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = w[i] >> 8;
+    const uint32_t y0 = hfma2_u(and_xor(w[i], 0x000F000Fu, xr), mlo, add);
+    const uint32_t y1 = hfma2_u(and_xor(w[i], 0x00F000F0u, xr_hi), mhi, add);
+    const uint32_t y2 = hfma2_u(and_xor(t, 0x000F000Fu, xr), mlo, add);
+    const uint32_t y3 = hfma2_u(and_xor(t, 0x00F000F0u, xr_hi), mhi, add);
+    gf_sts128(dst_row + (uint32_t)(((unit0 + i) ^ rsw) << 4), y0, y1, y2, y3);
+  }
+}
+
+template <int BN, bool ASYM>
+__global__ void __launch_bounds__(GF_THREADS, 1)
+gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
+  using Cfg = GfCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw_area = smem + GF_EXP_STAGES * Cfg::EXP_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw_area + GF_RAW_STAGES * Cfg::RAW_STAGE);
+  constexpr int NB = 2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NB);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto rawf_bar = [&](int s) { return bar0 + 8u * s; };
+  auto rawe_bar = [&](int s) { return bar0 + 8u * (GF_RAW_STAGES + s); };
+  auto expf_bar = [&](int s) { return bar0 + 8u * (2 * GF_RAW_STAGES + s); };
+  auto expe_bar = [&](int s) { return bar0 + 8u * (2 * GF_RAW_STAGES + GF_EXP_STAGES + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 2 + b); };
+
+  constexpr int W_MMA = GF_EPI_WARPS, W_TMA = GF_EPI_WARPS + 1;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GF_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), GF_CONV_WARPS); }
+    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), GF_CONV_WARPS); mbar_init(expe_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm.xq);
+    prefetch_tmap(&tm.wq);
+  }
+  if (warp == W_MMA) tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t exp_base = smem_u32(smem);
+  const uint32_t raw_base = smem_u32(raw_area);
+
+  const int n_main = a.n_chunks;
+  const int n_tail = (a.kt + 63) >> 6;
+  const int n_tiles_n = (int)((a.N + BN - 1) / BN);
+  const int total_tiles = n_tiles_n * (int)((a.M + 127) / 128);
+  // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... with n fastest, so CTAs running at
+  // the same time read the same activation rows through L2.  Rings and the accumulator counter run on
+  // across tiles.
+
+  if (warp == W_TMA) {
+    // ------------------------------ TMA producer ---------------------------------------------
+    if (lane == 0) {
+      GfRing<GF_RAW_STAGES> r;
+      uint32_t issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
+        for (int c = 0; c < n_main; ++c) {
+          if (!mbar_wait(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
+          const uint32_t bar = rawf_bar(r.s);
+          mbar_expect_tx(bar, Cfg::RAW_TX);
+          tma_load_2d(sb, &tm.xq, bar, c * 32, m0);
+          tma_load_2d(sb + Cfg::OFF_B, &tm.wq, bar, c * 32, n0);
+          tma_load_2d(sb + Cfg::OFF_AM, &tm.am, bar, m0, c);
+          tma_load_2d(sb + Cfg::OFF_AA, &tm.aa, bar, m0, c);
+          tma_load_2d(sb + Cfg::OFF_WM, &tm.wm, bar, n0, c);
+          issued |= 1u << r.s;
+          r.next();
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        for (int i = 0; i < GF_RAW_STAGES; ++i) {
+          if (!(issued & (1u << i))) continue;
+          const uint32_t last_ph = (i < r.s) ? r.ph : (r.ph ^ 1);
+          while (!mbar_try(rawf_bar(i), last_ph))
+            if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
+        }
+      }
+    }
+  } else if (warp > W_TMA) {
+    // ------------------------------ converters: raw ring -> fp16 operand ring ----------------
+    const int ct = threadIdx.x - (W_TMA + 1) * 32;        // 0..255
+    const int cw = ct >> 5;
+    GfRing<GF_RAW_STAGES> r;
+    GfRing<GF_EXP_STAGES> e;
+    uint32_t issued_e = 0;
+    bool ok = true;
+    constexpr uint32_t H2_2M4 = 0x2C002C00u;              // (2^-4, 2^-4) as halves
+    constexpr uint32_t H2_N2M21 = 0x80088008u;            // (-2^-21, -2^-21): subnormal 8 * 2^-24, sign set
+    constexpr uint32_t XR_A = ASYM ? 0u : 0x00080008u;
+    constexpr int B_TASKS = 2 * BN;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
+      for (int c = 0; c < n_main; ++c) {
+        if (!mbar_wait(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+        if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
+        const uint32_t sA = exp_base + e.s * Cfg::EXP_STAGE;
+        const uint32_t sB = sA + Cfg::A_EXP;
+        {   // activations: one task per thread
+          const int row = ct >> 1, h = ct & 1;
+          const uint4 p = gf_lds128(sraw + ct * 16);
+          uint32_t m = gf_lds16(sraw + Cfg::OFF_AM + row * 2);
+          uint32_t ad = gf_lds16(sraw + Cfg::OFF_AA + row * 2);
+          m |= m << 16;
+          ad |= ad << 16;
+          expand_block(p, XR_A, m, hmul2_u(m, H2_2M4), ad, sA + row * 128, 4 * h, row & 7);
+        }
+#pragma unroll
+        for (int i = 0; i < (B_TASKS + GF_CONV_THREADS - 1) / GF_CONV_THREADS; ++i) {   // weights
+          const int id = ct + i * GF_CONV_THREADS;
+          if (B_TASKS % GF_CONV_THREADS != 0 && id >= B_TASKS) break;
+          const int row = id >> 1, h = id & 1;
+          const uint4 p = gf_lds128(sraw + Cfg::OFF_B + id * 16);
+          uint32_t m = gf_lds16(sraw + Cfg::OFF_WM + row * 2);
+          m |= m << 16;
+          expand_block(p, 0x00080008u, m, hmul2_u(m, H2_2M4), hmul2_u(m, H2_N2M21), sB + row * 128, 4 * h, row & 7);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(expf_bar(e.s));
+          mbar_arrive(rawe_bar(r.s));
+        }
+        r.next();
+        e.next();
+      }
+      // tail: bf16 tiles (already divided by rs / cs) go by TMA straight into the operand ring.  Issued
+      // from a converter thread because the converters walk that ring in order; every converter warp
+      // waits on every slot, so no waiter is ever more than one phase away from the barrier it polls.
+      for (int st = 0; st < n_tail && ok; ++st) {
+        if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t bar = expf_bar(e.s);
+          if (cw == 0) {
+            const uint32_t sA = exp_base + e.s * Cfg::EXP_STAGE;
+            mbar_expect_tx(bar, Cfg::EXP_STAGE);
+            tma_load_2d(sA, &tm.xt, bar, st * 64, m0);
+            tma_load_2d(sA + Cfg::A_EXP, &tm.wt, bar, st * 64, n0);
+            issued_e |= 1u << e.s;
+          } else {
+            mbar_arrive(bar);
+          }
+        }
+        e.next();
+      }
+    }
+    if (!ok && ct == 0) {
+      const long long t0 = clock64();
+      for (int i = 0; i < GF_EXP_STAGES; ++i) {
+        if (!(issued_e & (1u << i))) continue;
+        const uint32_t last_ph = (i < e.s) ? e.ph : (e.ph ^ 1);
+        while (!mbar_try(expf_bar(i), last_ph))
+          if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
+      }
+    }
+  } else if (warp == W_MMA) {
+    // ------------------------------ UMMA issuer ----------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_h = idesc_dense(ACC_F32, FMT_F16, FMT_F16, 128, BN);
+      const uint32_t idesc_bf = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, BN);
+      GfRing<GF_EXP_STAGES> e;
+      int use = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int buf = use & 1;
+        if (!mbar_wait(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + buf * BN;
+        for (int st = 0; st < n_main + n_tail; ++st) {
+          if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = exp_base + e.s * Cfg::EXP_STAGE;
+          const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + Cfg::A_EXP);
+          const uint32_t idesc = st < n_main ? idesc_h : idesc_bf;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) umma_f16(d, adesc + 2 * j, bdesc + 2 * j, idesc, (st > 0 || j > 0) ? 1u : 0u);
+          umma_commit(expe_bar(e.s));
+          e.next();
+        }
+        if (ok) { umma_commit(accf_bar(buf)); ++use; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue: 8 warps -----------------------------------------
+    // warp w: TMEM lane quarter w & 3 (32 rows), column half w >> 2 (BN / 2 columns).
+    const int q = warp & 3, ch = warp >> 2;
+    const int trow = q * 32 + lane;
+    constexpr int CW = BN / 2;
+    int use = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
+      const int64_t row = (int64_t)m0 + trow;
+      const float rs = (row < a.M) ? __ldg(a.rs + row) : 0.f;
+      const int buf = use & 1;
+      if (!mbar_wait(accf_bar(buf), (use >> 1) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      ++use;
+      const uint32_t tl = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + ch * CW;
+#pragma unroll 1
+      for (int g = 0; g < CW / 32; ++g) {
+        uint32_t v[32];
+        tmem_ld32(tl + g * 32, v);
+        tmem_wait_ld();
+        if (g == CW / 32 - 1) {                      // the accumulator is out of TMEM: hand it back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acce_bar(buf));
+        }
+        const int64_t col0 = (int64_t)n0 + ch * CW + g * 32;
+        if (row < a.M) {
+          __nv_bfloat16* yr = a.y + row * a.N + col0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (col0 + 8 * i + 8 <= a.N) {
+              const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i));
+              const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i + 4));
+              const float cs8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+              float b[8];
+              if (a.bias) {
+                const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col0 + 8 * i));
+                const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+                for (int e2 = 0; e2 < 4; ++e2) { float2 f = __bfloat1622float2(bh[e2]); b[2 * e2] = f.x; b[2 * e2 + 1] = f.y; }
+              } else {
+#pragma unroll
+                for (int e2 = 0; e2 < 8; ++e2) b[e2] = 0.f;
+              }
+              uint32_t w[4];
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) {
+                const float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2]), rs * cs8[2 * e2], b[2 * e2]);
+                const float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2 + 1]), rs * cs8[2 * e2 + 1], b[2 * e2 + 1]);
+                __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                w[e2] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(yr + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == W_MMA) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Scale preparation.  One thread per row (activations: token; weights: output channel): the largest
+// chunk scale picks the row's power of two, every chunk scale becomes the fp16 multiplier s * 2^24 / rs
+// and the addend -(z * s) / rs; the row's 16-bit tail is divided by rs (exact) into its own buffer.
+// ---------------------------------------------------------------------------------------------------
+template <typename ST> __device__ __forceinline__ float scale_to_float(ST v);
+template <> __device__ __forceinline__ float scale_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float scale_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename ST>
+__global__ void __launch_bounds__(128)
+fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z, int n_chunks, int64_t rows, int64_t ld,
+                   __half* __restrict__ mult, __half* __restrict__ add, float* __restrict__ rs,
+                   const __nv_bfloat16* __restrict__ tail, __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
+  __shared__ float inv_s[128];
+  const int64_t r0 = (int64_t)blockIdx.x * 128;
+  const int64_t r = r0 + threadIdx.x;
+  float inv = 0.f;
+  if (r < rows) {
+    float smax = 0.f;
+    for (int c = 0; c < n_chunks; ++c) smax = fmaxf(smax, fabsf(scale_to_float<ST>(s[(int64_t)c * ld + r])));
+    int E = (int)((__float_as_uint(smax) >> 23) & 0xFF) - 127;        // smax = 1.f * 2^E
+    E = max(-100, min(100, E));
+    inv = __uint_as_float((uint32_t)(127 - 10 - E) << 23);             // 2^(-10 - E): smax * inv in [2^-10, 2^-9)
+    rs[r] = __uint_as_float((uint32_t)(127 + 10 + E) << 23);
+    const float up = inv * 16777216.f;                                  // * 2^24 (E >= -100 keeps this finite)
+    for (int c = 0; c < n_chunks; ++c) {
+      const float sc = scale_to_float<ST>(s[(int64_t)c * ld + r]);
+      mult[(int64_t)c * ld + r] = __float2half_rn(sc * up);
+      if (add) {
+        const float zp = z ? __bfloat162float(z[(int64_t)c * ld + r]) : 8.f;
+        add[(int64_t)c * ld + r] = __float2half_rn(-zp * sc * inv);
+      }
+    }
+  }
+  if (tail == nullptr) return;
+  inv_s[threadIdx.x] = inv;
+  __syncthreads();
+  const int units = kt_pitch / 8;                  // 16-byte units per row
+  for (int i = threadIdx.x; i < 128 * units; i += 128) {
+    const int rr = i / units, u = i % units;
+    if (r0 + rr >= rows) break;
+    const float f = inv_s[rr];
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(tail + (r0 + rr) * kt_pitch) + u);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = __bfloat1622float2(h[j]);
+      h[j] = __floats2bfloat162_rn(x.x * f, x.y * f);
+    }
+    *(reinterpret_cast<uint4*>(tail_out + (r0 + rr) * kt_pitch) + u) = v;
+  }
+}
+
+int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm,
+                           void* mult, void* add, float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out,
+                           int kt_pitch, cudaStream_t st) {
+  if (M <= 0) return DIROTQ_OK;
+  fold_scales_kernel<__nv_bfloat16><<<(unsigned)((M + 127) / 128), 128, 0, st>>>(
+      s, z, n_chunks, M, ldm, reinterpret_cast<__half*>(mult), reinterpret_cast<__half*>(add), rs, tail, tail_out, kt_pitch);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* mult, float* cs,
+                              const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, cudaStream_t st) {
+  if (N <= 0) return DIROTQ_OK;
+  fold_scales_kernel<float><<<(unsigned)((N + 127) / 128), 128, 0, st>>>(
+      s, nullptr, n_chunks, N, ldn, reinterpret_cast<__half*>(mult), nullptr, cs, tail, tail_out, kt_pitch);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+template <int BN, bool ASYM>
+static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st) {
+  auto k = gemm_int_f16_kernel<BN, ASYM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, GfCfg<BN>::SMEM_BYTES) != cudaSuccess)
+      return DIROTQ_E_CUDA;
+    attr_set = true;
+  }
+  const int tiles = (int)((a.N + BN - 1) / BN) * (int)((a.M + 127) / 128);
+  const int grid = min(tiles, num_sms());
+  k<<<grid, GF_THREADS, GfCfg<BN>::SMEM_BYTES, st>>>(tm, a);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+// Column-tile width: the candidate that wastes the fewest padded columns; ties go to the wider tile
+// (fewer conversions of the activation tile per output column).
+static int pick_bn_f16(int64_t N) {
+  const int cand[3] = {256, 192, 128};
+  int best = 128;
+  int64_t best_pad = -1;
+  for (int i = 0; i < 3; ++i) {
+    const int64_t pad = (N + cand[i] - 1) / cand[i] * cand[i] - N;
+    if (best_pad < 0 || pad < best_pad) { best_pad = pad; best = cand[i]; }
+  }
+  return best;
+}
+
+int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
+  if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
+  if (a.a_mode != DIROTQ_INT4_SYM && a.a_mode != DIROTQ_INT4_ASYM) return DIROTQ_E_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7))
+    return DIROTQ_E_ALIGN;
+  const int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
+  GfMaps tm;
+  int rc = make_tmap_2d_ex(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
+                           (uint64_t)a.x_row_bytes, 32, 128, false);
+  if (rc) return rc;
+  rc = make_tmap_2d_ex(&tm.wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, (uint64_t)a.w_row_bytes, (uint64_t)a.N,
+                       (uint64_t)a.w_row_bytes, 32, BN, false);
+  if (rc) return rc;
+  rc = make_tmap_2d_ex(&tm.am, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.a_mult, (uint64_t)a.M, (uint64_t)a.n_chunks,
+                       (uint64_t)a.ldm * 2, 128, 1, false);
+  if (rc) return rc;
+  rc = make_tmap_2d_ex(&tm.aa, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.a_add, (uint64_t)a.M, (uint64_t)a.n_chunks,
+                       (uint64_t)a.ldm * 2, 128, 1, false);
+  if (rc) return rc;
+  rc = make_tmap_2d_ex(&tm.wm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.w_mult, (uint64_t)a.N, (uint64_t)a.n_chunks,
+                       (uint64_t)a.ldn * 2, BN, 1, false);
+  if (rc) return rc;
+  if (a.kt > 0) {
+    rc = make_tmap_2d(&tm.xt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.xt, (uint64_t)a.kt, (uint64_t)a.M, (uint64_t)a.kt_pitch * 2, 128);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tm.wt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.wt, (uint64_t)a.kt, (uint64_t)a.N, (uint64_t)a.kt_pitch * 2, BN);
+    if (rc) return rc;
+  } else {
+    tm.xt = tm.xq;
+    tm.wt = tm.wq;
+  }
+  const bool asym = a.a_mode == DIROTQ_INT4_ASYM;
+  switch (BN) {
+    case 256: return asym ? launch_gf<256, true>(tm, a, st) : launch_gf<256, false>(tm, a, st);
+    case 192: return asym ? launch_gf<192, true>(tm, a, st) : launch_gf<192, false>(tm, a, st);
+    case 128: return asym ? launch_gf<128, true>(tm, a, st) : launch_gf<128, false>(tm, a, st);
+  }
+  return DIROTQ_E_ARG;
+}
+
+}  // namespace dq

@@ -91,6 +91,31 @@ struct GemmIntArgs {
   int* status;
 };
 
+struct GemmIntF16Args {
+  int a_mode;                  // DIROTQ_INT4_SYM or DIROTQ_INT4_ASYM
+  int64_t M, N;
+  int n_chunks;
+  const uint8_t* xq;           // activation codes [M, n_chunks * 32]
+  int64_t x_row_bytes;
+  const void* a_mult;          // fp16 [n_chunks, ldm]: s * 2^24 / rs
+  const void* a_add;           // fp16 [n_chunks, ldm]: -(z * s) / rs  (z = 8 for symmetric codes)
+  const float* rs;             // [ldm] row powers of two
+  int64_t ldm;
+  const uint8_t* wq;           // weight codes [N, n_chunks * 32]
+  int64_t w_row_bytes;
+  const void* w_mult;          // fp16 [n_chunks, ldn]: s * 2^24 / cs
+  const float* cs;             // [ldn] column powers of two
+  int64_t ldn;
+  const __nv_bfloat16* xt;     // [M, kt_pitch] tail / rs
+  const __nv_bfloat16* wt;     // [N, kt_pitch] tail / cs
+  int kt;
+  int kt_pitch;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;            // [M, N]
+  int* status;
+  int force_bn;                // 0 = pick the column-tile width from N
+};
+
 struct GemmFp4Args {
   int64_t M, N;
   int n_chunks;
@@ -110,6 +135,12 @@ struct GemmFp4Args {
 
 int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st);
+int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st);
+int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm,
+                           void* mult, void* add, float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out,
+                           int kt_pitch, cudaStream_t st);
+int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* mult, float* cs,
+                              const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, cudaStream_t st);
 
 int launch_quantize(const QuantArgs& a, cudaStream_t st);
 int launch_pack_int4(const PackIntArgs& a, cudaStream_t st);

@@ -235,6 +235,49 @@ def gemm_w4a4_int(act: ActBuffers, w: PackedWeightInt4, w_tail: Optional[torch.T
     return (y, dump) if dump_acc else y
 
 
+@dataclass
+class FoldedWeightF16:
+    """Weight-side constants of the tensor-rate INT4 GEMM (dirotq_fold_weight_scales_f16)."""
+    mult: torch.Tensor                    # fp16 [n_chunks, ldn]
+    colscale: torch.Tensor                # fp32 [ldn]
+    tail: Optional[torch.Tensor]          # bf16 [N, tail_pitch] = w_tail / colscale
+
+
+def fold_weight_scales_f16(w: PackedWeightInt4, w_tail: Optional[torch.Tensor], tail_total: int) -> FoldedWeightF16:
+    """Per-layer preparation for gemm_w4a4_int_f16: fp16 multipliers, column powers of two, scaled tail."""
+    dev = w.scales.device
+    ldn = w.scales.shape[1]
+    mult = torch.zeros(w.n_chunks, ldn, dtype=torch.float16, device=dev)
+    cs = torch.ones(ldn, dtype=torch.float32, device=dev)
+    tail_out, pitch = None, 0
+    if tail_total > 0:
+        assert w_tail is not None and w_tail.dtype == torch.bfloat16 and w_tail.is_contiguous()
+        pitch = w_tail.shape[1]
+        tail_out = torch.zeros_like(w_tail)
+    check(_lib.lib().dirotq_fold_weight_scales_f16(w.n_chunks, w.N, _ptr(w.scales), _ptr(w_tail), tail_total, pitch,
+                                                   _ptr(mult), _ptr(cs), _ptr(tail_out), _stream()),
+          "dirotq_fold_weight_scales_f16")
+    return FoldedWeightF16(mult, cs, tail_out)
+
+
+def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeightF16, bias: Optional[torch.Tensor],
+                      workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Kernel 2 (INT4, tensor-rate variant): codes expanded to fp16 in shared memory, one fp32 accumulator."""
+    lay, M, N = act.layout, act.M, w.N
+    assert act.fmt.mode in (INT4_SYM, INT4_ASYM) and lay.n_chunks == w.n_chunks
+    dev = act.codes.device
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    tp = lay.tail_pitch if lay.tail_total > 0 else 0
+    need = int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(M, lay.n_chunks, tp))
+    ws = workspace if workspace is not None else torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    check(_lib.lib().dirotq_gemm_w4a4_int_f16(act.fmt.mode, M, N, lay.n_chunks, _ptr(act.codes), _ptr(act.scales),
+                                              _ptr(act.zeros), _ptr(w.codes), _ptr(folded.mult), _ptr(folded.colscale),
+                                              _ptr(act.tail), _ptr(folded.tail), lay.tail_total, lay.tail_pitch,
+                                              _ptr(bias), _ptr(y), _ptr(ws), ws.numel(), _ptr(status_word(dev)),
+                                              _stream()), "dirotq_gemm_w4a4_int_f16")
+    return y
+
+
 def gemm_w4a4_nvfp4(act: ActBuffers, w: PackedWeightNvfp4, w_tail_scaled: Optional[torch.Tensor],
                     bias: Optional[torch.Tensor]) -> torch.Tensor:
     """Kernel 2 (NVFP4).  w_tail_scaled = w_tail / (Tx * Tw), bf16 [N, tail_pitch]."""

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DIROTQ_ABI_VERSION 1
+#define DIROTQ_ABI_VERSION 2
 
 /* ---- activation quantiser modes (ActQuantizer.configure, utils/quant_utils.py:182-199) ---- */
 enum {
@@ -155,6 +155,31 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
                          int32_t tail_pitch, const void* bias, void* y, int32_t* acc_dump, int32_t* status,
                          void* stream);
 
+/* INT4 at tensor rate (tcgen05 kind::f16): the same product as dirotq_gemm_w4a4_int for 4-bit
+ * activations, computed the way the reference's own linear computes it -- a 16-bit GEMM with fp32
+ * accumulation over the dequantised values s*(q-z) and s_w*q_w (dirotq_fused_unrotation_fast.py:141)
+ * -- while both operands stay 4-bit in memory: codes are expanded to fp16 between shared memory and
+ * the tensor core, one accumulator runs over the whole K, and nothing is drained per chunk.
+ * Activation values are exact in fp16; weight values are rounded once to fp16 (the reference rounds
+ * them to bf16).  Row / column powers of two keep every scale inside the fp16 range.
+ *
+ * dirotq_fold_weight_scales_f16 (once per layer): w_scales fp32 [n_chunks, ldn] ->
+ *   w_mult fp16 [n_chunks, ldn], w_colscale fp32 [ldn]; w_tail bf16 [N, tail_pitch] ->
+ *   w_tail_out = w_tail / colscale (may be NULL when tail_total == 0).
+ * dirotq_gemm_w4a4_int_f16: a_mode DIROTQ_INT4_SYM or DIROTQ_INT4_ASYM; workspace of
+ *   dirotq_gemm_w4a4_int_f16_workspace_bytes(M, n_chunks, tail_pitch) bytes, 256-byte aligned
+ *   (per-call activation multipliers and the scaled copy of the tail).
+ */
+int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_scales, const void* w_tail,
+                                  int32_t tail_total, int32_t tail_pitch, void* w_mult, float* w_colscale,
+                                  void* w_tail_out, void* stream);
+size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int32_t n_chunks, int32_t tail_pitch);
+int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
+                             const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
+                             const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
+                             int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream);
+
 /* NVFP4 (tcgen05 kind::mxf4nvf4, UE4M3 scale factors in TMEM):
  *   y = out_scale * (sum_blocks sfx sfw (e2m1.e2m1) + x_tail . w_tail_scaled) + bias
  *   out_scale = Tx * Tw; w_tail_scaled = w_tail / out_scale (bf16, prepared once by the host).
@@ -188,6 +213,11 @@ typedef struct dirotq_linear {
   const void* w_tail;       /* bf16 [N, tail_pitch] (NVFP4: divided by out_scale) */
   const void* bias;         /* bf16 [N] or NULL */
   float w_tensor_scale;     /* NVFP4 only */
+  /* INT4 activations only, all three from dirotq_fold_weight_scales_f16.  When w_mult is set the
+   * forward runs dirotq_gemm_w4a4_int_f16; when NULL, the exact-integer dirotq_gemm_w4a4_int. */
+  const void* w_mult;
+  const float* w_colscale;
+  const void* w_tail_f16;
 } dirotq_linear;
 
 size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M);

@@ -116,3 +116,72 @@ def test_nvfp4_gemm(M, N, D, tail):
     y_ref = O.w4a4_nvfp4_linear(nib_x, dec["scale"], Tx, nib_w, micro_w, Tw, dec.get("tail"), w_tail, bias)
     assert rel_l2(y.float().cpu(), y_ref) < 3e-3
     assert cosine(y.float().cpu(), y_ref) > 0.9999
+
+
+# ---- INT4 at tensor rate: codes expanded to fp16 next to the tensor core, one fp32 accumulator ----------
+@pytest.mark.parametrize("mode,M,N,D,tail", [("sym", 300, 256, 320, 64), ("sym", 1000, 1152, 1152, 64),
+                                             ("asym", 520, 384, 1152, 64), ("sym", 260, 128, 256, 0),
+                                             ("sym", 200, 136, 160, 0), ("asym", 130, 512, 256, 8),
+                                             ("sym", 2048, 3072, 3072, 384), ("sym", 700, 4608, 1152, 64)])
+def test_int4_f16_gemm_hidden(mode, M, N, D, tail):
+    from dirotq_b200 import ops
+    m = {"sym": ops.INT4_SYM, "asym": ops.INT4_ASYM}[mode]
+    fmt = ops.ActFormat(m, D, tail_len=tail)
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 21)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
+    y = ops.gemm_w4a4_int_f16(act, pk, folded, bias.cuda())
+    ops.check_status()
+    y_ref, _ = _oracle_int(dec, lay, qw, sw, w_tail, bias, mode != "sym")
+    y_int = ops.gemm_w4a4_int(act, pk, wt, bias.cuda())
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
+    assert cosine(y.float().cpu(), y_ref) > 0.9999
+    # against the exact-integer kernel: both round the same fp32 value to bf16 up to the weights' fp16 rounding
+    assert rel_l2(y.float().cpu(), y_int.float().cpu()) < 3e-3
+
+
+@pytest.mark.parametrize("H,d,hlen", [(16, 72, 9), (6, 32, 4), (4, 128, 16)])
+def test_int4_f16_gemm_per_head(H, d, hlen):
+    from dirotq_b200 import ops
+    fmt = ops.ActFormat(ops.INT4_SYM, H * d, tail_len=hlen, num_heads=H, head_dim=d)
+    M, N = 390, 256
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 22)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
+    y = ops.gemm_w4a4_int_f16(act, pk, folded, bias.cuda())
+    ops.check_status()
+    y_ref, _ = _oracle_int(dec, lay, qw, sw, w_tail, bias, False)
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
+
+
+def test_int4_f16_gemm_wide_dynamic_range():
+    """Rows and columns whose scales differ by many orders of magnitude: the per-row / per-column powers
+    of two keep every fp16 operand in range; the result still matches exact arithmetic."""
+    from dirotq_b200 import ops
+    from gpu_helpers import decode_act
+    M, N, D, tail = 256, 256, 576, 64
+    g = torch.Generator().manual_seed(23)
+    x = O.synth_activations(M, D, g).float()
+    x *= torch.logspace(-6, 5, M).unsqueeze(1)               # rows from 1e-6 to 1e5
+    x[:, 64:128] *= 300.0                                    # one loud group, one nearly silent
+    x[:, 128:192] *= 1e-3
+    x = x.to(torch.bfloat16)
+    fmt = ops.ActFormat(ops.INT4_SYM, D, tail_len=tail)
+    act = ops.quantize_act(x.cuda(), fmt)
+    lay = act.layout
+    dec = decode_act(act)
+    qw = torch.randint(-8, 8, (N, lay.q_len), generator=g)
+    sw = (torch.rand(N, lay.n_groups, generator=g) * 0.015 + 0.005) * torch.logspace(-5, 3, N).unsqueeze(1)
+    pk = ops.pack_weight_int4(qw.float().cuda(), 64, scales=sw.cuda(), w_is_codes=True)
+    w_tail = (torch.randn(N, tail, generator=g) * 0.02 * torch.logspace(-5, 3, N).unsqueeze(1)).to(torch.bfloat16)
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, tail)
+    y = ops.gemm_w4a4_int_f16(act, pk, folded, None).float().cpu()
+    ops.check_status()
+    y_ref, _ = _oracle_int(dec, lay, qw, sw, w_tail, None, False)
+    assert torch.isfinite(y).all()
+    # row-wise: every row, however small, is resolved (a global norm would hide the small rows)
+    err = (y - y_ref).norm(dim=1) / y_ref.norm(dim=1).clamp_min(1e-30)
+    assert float(err.max()) < 6e-3, float(err.max())
