@@ -222,24 +222,29 @@ int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_sc
   if (tail_total < 0 || (tail_total > 0 && (!w_tail || !w_tail_out || tail_pitch < tail_total || tail_pitch % 8)))
     return DIROTQ_E_ARG;
   if ((reinterpret_cast<uintptr_t>(w_tail) | reinterpret_cast<uintptr_t>(w_tail_out)) & 15) return DIROTQ_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(w_mult) & 15) return DIROTQ_E_ALIGN;
   return launch_fold_weight_scales(w_scales, n_chunks, N, ld_rows(N), w_mult, w_colscale,
                                    tail_total > 0 ? static_cast<const __nv_bfloat16*>(w_tail) : nullptr,
                                    static_cast<__nv_bfloat16*>(w_tail_out), tail_pitch, static_cast<cudaStream_t>(stream));
 }
 
 struct F16Carve {
-  size_t mult, add, rs, tail, total;
+  size_t rec, rs, tail, total;
 };
 static F16Carve carve_f16(int64_t M, int32_t n_chunks, int32_t tail_pitch) {
   F16Carve c;
-  const size_t ldm = (size_t)ld_rows(M);
+  const size_t ldm = (size_t)f16_ld_act(M);
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
-  c.mult = 0;
-  c.add = up(c.mult + (size_t)n_chunks * ldm * 2);
-  c.rs = up(c.add + (size_t)n_chunks * ldm * 2);
+  c.rec = 0;
+  c.rs = up(c.rec + (size_t)n_chunks * ldm * 8);
   c.tail = up(c.rs + ldm * 4);
   c.total = up(c.tail + (size_t)M * (size_t)tail_pitch * 2);
   return c;
+}
+
+size_t dirotq_fold_weight_records_bytes(int32_t n_chunks, int64_t N) {
+  if (n_chunks <= 0 || N <= 0) return 0;
+  return (size_t)n_chunks * (size_t)f16_ld_weight(N) * 8;
 }
 
 size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int32_t n_chunks, int32_t tail_pitch) {
@@ -273,7 +278,7 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
   __nv_bfloat16* tail_s = tail_total > 0 ? reinterpret_cast<__nv_bfloat16*>(ws + c.tail) : nullptr;
   int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales),
                                   a_mode == DIROTQ_INT4_ASYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
-                                  n_chunks, M, ld_rows(M), ws + c.mult, ws + c.add, reinterpret_cast<float*>(ws + c.rs),
+                                  n_chunks, M, ld_rows(M), ws + c.rec, reinterpret_cast<float*>(ws + c.rs),
                                   tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
   if (rc) return rc;
   GemmIntF16Args a;
@@ -283,15 +288,14 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
   a.n_chunks = n_chunks;
   a.xq = static_cast<const uint8_t*>(x_codes);
   a.x_row_bytes = (int64_t)n_chunks * 32;
-  a.a_mult = ws + c.mult;
-  a.a_add = ws + c.add;
+  a.a_const = reinterpret_cast<const uint2*>(ws + c.rec);
   a.rs = reinterpret_cast<const float*>(ws + c.rs);
-  a.ldm = ld_rows(M);
+  a.ldm = f16_ld_act(M);
   a.wq = static_cast<const uint8_t*>(w_codes);
   a.w_row_bytes = (int64_t)n_chunks * 32;
-  a.w_mult = w_mult;
+  a.w_const = static_cast<const uint2*>(w_mult);
   a.cs = w_colscale;
-  a.ldn = ld_rows(N);
+  a.ldn = f16_ld_weight(N);
   a.xt = tail_s;
   a.wt = static_cast<const __nv_bfloat16*>(w_tail_scaled);
   a.kt = tail_total;

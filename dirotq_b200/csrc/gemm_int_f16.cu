@@ -38,31 +38,34 @@
 
 namespace dq {
 
-constexpr int GF_RAW_STAGES = 4;
 constexpr int GF_EXP_STAGES = 3;
 constexpr int GF_EPI_WARPS = 8;
-constexpr int GF_CONV_WARPS = 8;
-constexpr int GF_CONV_THREADS = GF_CONV_WARPS * 32;
-constexpr int GF_THREADS = (GF_EPI_WARPS + 2 + GF_CONV_WARPS) * 32;      // 576
 
+// One conversion task = one 32-slot block (16 bytes of nibbles) of one operand row.  A chunk of a
+// 128 x BN tile has 2 * (128 + BN) tasks; the converter warp count gives every thread exactly two.
+// A raw stage carries TWO chunks (64 bytes of codes per row): TMA handles a tile row by row, and rows
+// of 32 bytes kept the copy engine, not the tensor core, on the critical path.
 template <int BN> struct GfCfg {
+  static constexpr int ROWS = 128 + BN;                    // activation rows, then weight rows
+  static constexpr int TASKS = 2 * ROWS;
+  static constexpr int CONV_WARPS = TASKS / 64;            // 8 / 10 / 12
+  static constexpr int CONV_THREADS = CONV_WARPS * 32;
+  static constexpr int THREADS = (GF_EPI_WARPS + 2 + CONV_WARPS) * 32;
   static constexpr int A_EXP = 128 * 128;                  // 128 rows x 64 halves
   static constexpr int B_EXP = BN * 128;
-  static constexpr int EXP_STAGE = A_EXP + B_EXP;
-  static constexpr int RAW_A = 128 * 32;
-  static constexpr int RAW_B = BN * 32;
+  static constexpr int EXP_STAGE = A_EXP + B_EXP;          // rows of both operands back to back
+  static constexpr int RAW_A = 128 * 64;
+  static constexpr int RAW_B = BN * 64;
   static constexpr int OFF_B = RAW_A;
-  static constexpr int OFF_AM = OFF_B + RAW_B;              // a_mult [128] fp16
-  static constexpr int OFF_AA = OFF_AM + 256;               // a_add  [128] fp16
-  static constexpr int OFF_WM = OFF_AA + 256;               // w_mult [BN]  fp16
-  static constexpr int RAW_STAGE = OFF_WM + 512;
-  static constexpr uint32_t RAW_TX = RAW_A + RAW_B + 256 + 256 + BN * 2;
-  static constexpr int SMEM_BYTES = GF_EXP_STAGES * EXP_STAGE + GF_RAW_STAGES * RAW_STAGE + 1024 + 256;
+  static constexpr int OFF_C = RAW_A + RAW_B;               // [2 chunks][ROWS] 8-byte records, same row order
+  static constexpr int RAW_STAGE = OFF_C + 2 * ROWS * 8;
+  static constexpr int RAW_STAGES = (BN > 192) ? 2 : 3;
+  static constexpr int SMEM_BYTES = GF_EXP_STAGES * EXP_STAGE + RAW_STAGES * RAW_STAGE + 1024 + 256;
   static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
 };
 
 struct GfMaps {
-  CUtensorMap xq, wq, am, aa, wm, xt, wt;
+  CUtensorMap xq, wq, xt, wt;
 };
 
 template <int N> struct GfRing {
@@ -74,14 +77,14 @@ template <int N> struct GfRing {
 __device__ __forceinline__ void gf_sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
+__device__ __forceinline__ uint2 gf_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint4 gf_lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint32_t gf_lds16(uint32_t addr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
   return v;
 }
 // (a & b) ^ c in one logic op
@@ -95,37 +98,38 @@ __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) 
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
-__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
 
 // One 32-slot block (16 bytes of planar nibbles) of one row -> 32 halves (4 x 16 bytes).
-//   xr    : per-nibble XOR (0x8 turns a two's-complement nibble into offset binary; 0 for unsigned codes)
-//   mlo   : (s * 2^24) twice;  mhi = (s * 2^20) twice;  add = -(z * s) twice (z = 8 for signed codes)
-__device__ __forceinline__ void expand_block(const uint4 p, uint32_t xr, uint32_t mlo, uint32_t mhi, uint32_t add,
-                                             uint32_t dst_row, int unit0, int rsw) {
+//   xr : per-nibble XOR (0x8 turns a two's-complement nibble into offset binary; 0 for unsigned codes)
+//   k  : the row's constants for this chunk: k.x = (s * 2^24) twice, k.y = -(z * s) twice (z = 8 for
+//        signed codes); the multiplier of the high nibbles, s * 2^20, is k.x * 2^-4
+//   dst: stage base; off[i] = byte offset of the i-th 16-byte unit (swizzle applied)
+__device__ __forceinline__ void expand_block(const uint4 p, uint32_t xr, const uint2 k2, uint32_t dst, const uint32_t* off) {
   const uint32_t w[4] = {p.x, p.y, p.z, p.w};
   const uint32_t xr_hi = xr << 4;
+  uint4 k;
+  k.x = k2.x;
+  k.z = k2.y;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(k.y) : "r"(k2.x), "r"(0x2C002C00u));
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t t = w[i] >> 8;
-    const uint32_t y0 = hfma2_u(and_xor(w[i], 0x000F000Fu, xr), mlo, add);
-    const uint32_t y1 = hfma2_u(and_xor(w[i], 0x00F000F0u, xr_hi), mhi, add);
-    const uint32_t y2 = hfma2_u(and_xor(t, 0x000F000Fu, xr), mlo, add);
-    const uint32_t y3 = hfma2_u(and_xor(t, 0x00F000F0u, xr_hi), mhi, add);
-    gf_sts128(dst_row + (uint32_t)(((unit0 + i) ^ rsw) << 4), y0, y1, y2, y3);
+    const uint32_t y0 = hfma2_u(and_xor(w[i], 0x000F000Fu, xr), k.x, k.z);
+    const uint32_t y1 = hfma2_u(and_xor(w[i], 0x00F000F0u, xr_hi), k.y, k.z);
+    const uint32_t y2 = hfma2_u(and_xor(t, 0x000F000Fu, xr), k.x, k.z);
+    const uint32_t y3 = hfma2_u(and_xor(t, 0x00F000F0u, xr_hi), k.y, k.z);
+    gf_sts128(dst + off[i], y0, y1, y2, y3);
   }
 }
 
 template <int BN, bool ASYM>
-__global__ void __launch_bounds__(GF_THREADS, 1)
+__global__ void __launch_bounds__(GfCfg<BN>::THREADS, 1)
 gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   using Cfg = GfCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_area = smem + GF_EXP_STAGES * Cfg::EXP_STAGE;
+  constexpr int GF_RAW_STAGES = Cfg::RAW_STAGES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw_area + GF_RAW_STAGES * Cfg::RAW_STAGE);
   constexpr int NB = 2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NB);
@@ -142,8 +146,8 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
 
   constexpr int W_MMA = GF_EPI_WARPS, W_TMA = GF_EPI_WARPS + 1;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < GF_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), GF_CONV_WARPS); }
-    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), GF_CONV_WARPS); mbar_init(expe_bar(s), 1); }
+    for (int s = 0; s < GF_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), Cfg::CONV_WARPS); }
+    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), Cfg::CONV_WARPS / 2); mbar_init(expe_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -174,16 +178,19 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
-        for (int c = 0; c < n_main; ++c) {
-          if (!mbar_wait(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+        for (int c = 0; c < n_main; c += 2) {
+          if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
           const uint32_t bar = rawf_bar(r.s);
-          mbar_expect_tx(bar, Cfg::RAW_TX);
+          const int nv = min(2, n_main - c);
+          mbar_expect_tx(bar, (uint32_t)(Cfg::OFF_C + nv * Cfg::ROWS * 8));
           tma_load_2d(sb, &tm.xq, bar, c * 32, m0);
           tma_load_2d(sb + Cfg::OFF_B, &tm.wq, bar, c * 32, n0);
-          tma_load_2d(sb + Cfg::OFF_AM, &tm.am, bar, m0, c);
-          tma_load_2d(sb + Cfg::OFF_AA, &tm.aa, bar, m0, c);
-          tma_load_2d(sb + Cfg::OFF_WM, &tm.wm, bar, n0, c);
+          for (int j = 0; j < nv; ++j) {
+            const uint32_t sc = sb + Cfg::OFF_C + j * Cfg::ROWS * 8;
+            bulk_load(sc, a.a_const + ((int64_t)(c + j) * a.ldm + m0), 128 * 8, bar);
+            bulk_load(sc + 128 * 8, a.w_const + ((int64_t)(c + j) * a.ldn + n0), BN * 8, bar);
+          }
           issued |= 1u << r.s;
           r.next();
         }
@@ -200,78 +207,85 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     }
   } else if (warp > W_TMA) {
     // ------------------------------ converters: raw ring -> fp16 operand ring ----------------
-    const int ct = threadIdx.x - (W_TMA + 1) * 32;        // 0..255
+    // The converter warps form TWO groups that take alternate operand stages (stage q of the kernel-wide
+    // sequence of chunks and tail stages goes to group q & 1), so one group's barrier waits, shared-memory
+    // latencies and proxy fence overlap the other group's arithmetic.  Within its stage a thread owns
+    // four tasks: task id = row id >> 1 of the combined (activation rows, then weight rows) tile,
+    // 32-slot block id & 1.  Raw codes, constants and operand rows are laid out in that same row order.
+    const int ct = threadIdx.x - (W_TMA + 1) * 32;
     const int cw = ct >> 5;
+    constexpr int GW = Cfg::CONV_WARPS / 2, GT = GW * 32;
+    const int grp = cw >= GW ? 1 : 0;
+    const int gt = ct - grp * GT, gw = cw - grp * GW;
     GfRing<GF_RAW_STAGES> r;
-    GfRing<GF_EXP_STAGES> e;
-    uint32_t issued_e = 0;
+    int q = 0;
+    int issued_q[2] = {-1, -1};
     bool ok = true;
-    constexpr uint32_t H2_2M4 = 0x2C002C00u;              // (2^-4, 2^-4) as halves
-    constexpr uint32_t H2_N2M21 = 0x80088008u;            // (-2^-21, -2^-21): subnormal 8 * 2^-24, sign set
-    constexpr uint32_t XR_A = ASYM ? 0u : 0x00080008u;
-    constexpr int B_TASKS = 2 * BN;
+    const int row0 = gt >> 1, h0 = gt & 1;
+    const uint32_t roff = (uint32_t)(row0 * 64 + h0 * 16), koff = (uint32_t)(row0 * 8);
+    uint32_t off[4], xr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      off[i] = (uint32_t)(row0 * 128 + (((4 * h0 + i) ^ (row0 & 7)) << 4));      // (GT / 2) % 8 == 0: same swizzle for all four tasks
+      xr[i] = (ASYM && gt + i * GT < 256) ? 0u : 0x00080008u;
+    }
+    auto exp_slot = [](int qq) { return qq % GF_EXP_STAGES; };
+    auto exp_phase = [](int qq) { return (uint32_t)((qq / GF_EXP_STAGES) & 1); };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
-      for (int c = 0; c < n_main; ++c) {
-        if (!mbar_wait(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
-        if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+      for (int c = 0; c < n_main && ok; c += 2) {
+        if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
-        const uint32_t sA = exp_base + e.s * Cfg::EXP_STAGE;
-        const uint32_t sB = sA + Cfg::A_EXP;
-        {   // activations: one task per thread
-          const int row = ct >> 1, h = ct & 1;
-          const uint4 p = gf_lds128(sraw + ct * 16);
-          uint32_t m = gf_lds16(sraw + Cfg::OFF_AM + row * 2);
-          uint32_t ad = gf_lds16(sraw + Cfg::OFF_AA + row * 2);
-          m |= m << 16;
-          ad |= ad << 16;
-          expand_block(p, XR_A, m, hmul2_u(m, H2_2M4), ad, sA + row * 128, 4 * h, row & 7);
-        }
+        const int nv = min(2, n_main - c);
+        for (int jc = 0; jc < nv; ++jc, ++q) {
+          if ((q & 1) != grp) continue;
+          uint4 p[4];
+          uint2 k[4];
 #pragma unroll
-        for (int i = 0; i < (B_TASKS + GF_CONV_THREADS - 1) / GF_CONV_THREADS; ++i) {   // weights
-          const int id = ct + i * GF_CONV_THREADS;
-          if (B_TASKS % GF_CONV_THREADS != 0 && id >= B_TASKS) break;
-          const int row = id >> 1, h = id & 1;
-          const uint4 p = gf_lds128(sraw + Cfg::OFF_B + id * 16);
-          uint32_t m = gf_lds16(sraw + Cfg::OFF_WM + row * 2);
-          m |= m << 16;
-          expand_block(p, 0x00080008u, m, hmul2_u(m, H2_2M4), hmul2_u(m, H2_N2M21), sB + row * 128, 4 * h, row & 7);
+          for (int i = 0; i < 4; ++i) {
+            p[i] = gf_lds128(sraw + roff + jc * 32 + i * (GT / 2) * 64);
+            k[i] = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + koff + i * (GT / 2) * 8);
+          }
+          const int es = exp_slot(q);
+          if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sdst = exp_base + es * Cfg::EXP_STAGE;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) expand_block(p[i], xr[i], k[i], sdst + i * (GT / 2) * 128, off);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(expf_bar(es));
         }
-        fence_proxy_async_smem();
+        if (!ok) break;
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(expf_bar(e.s));
-          mbar_arrive(rawe_bar(r.s));
-        }
+        if (lane == 0) mbar_arrive(rawe_bar(r.s));
         r.next();
-        e.next();
       }
-      // tail: bf16 tiles (already divided by rs / cs) go by TMA straight into the operand ring.  Issued
-      // from a converter thread because the converters walk that ring in order; every converter warp
-      // waits on every slot, so no waiter is ever more than one phase away from the barrier it polls.
-      for (int st = 0; st < n_tail && ok; ++st) {
-        if (!mbar_wait(expe_bar(e.s), e.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+      // tail: bf16 tiles (already divided by rs / cs) go by TMA straight into the operand ring, issued by
+      // the group that owns the stage (the converters are the ones walking that ring in order).
+      for (int st = 0; st < n_tail && ok; ++st, ++q) {
+        if ((q & 1) != grp) continue;
+        const int es = exp_slot(q);
+        if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
         if (lane == 0) {
-          const uint32_t bar = expf_bar(e.s);
-          if (cw == 0) {
-            const uint32_t sA = exp_base + e.s * Cfg::EXP_STAGE;
+          const uint32_t bar = expf_bar(es);
+          if (gw == 0) {
+            const uint32_t sA = exp_base + es * Cfg::EXP_STAGE;
             mbar_expect_tx(bar, Cfg::EXP_STAGE);
             tma_load_2d(sA, &tm.xt, bar, st * 64, m0);
             tma_load_2d(sA + Cfg::A_EXP, &tm.wt, bar, st * 64, n0);
-            issued_e |= 1u << e.s;
+            issued_q[0] = issued_q[1];
+            issued_q[1] = q;
           } else {
             mbar_arrive(bar);
           }
         }
-        e.next();
       }
     }
-    if (!ok && ct == 0) {
+    if (!ok && gw == 0 && lane == 0) {
       const long long t0 = clock64();
-      for (int i = 0; i < GF_EXP_STAGES; ++i) {
-        if (!(issued_e & (1u << i))) continue;
-        const uint32_t last_ph = (i < e.s) ? e.ph : (e.ph ^ 1);
-        while (!mbar_try(expf_bar(i), last_ph))
+      for (int i = 0; i < 2; ++i) {
+        if (issued_q[i] < 0) continue;
+        while (!mbar_try(expf_bar(exp_slot(issued_q[i])), exp_phase(issued_q[i])))
           if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
       }
     }
@@ -280,24 +294,24 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     if (lane == 0) {
       const uint32_t idesc_h = idesc_dense(ACC_F32, FMT_F16, FMT_F16, 128, BN);
       const uint32_t idesc_bf = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, BN);
-      GfRing<GF_EXP_STAGES> e;
+      int q = 0;
       int use = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int buf = use & 1;
-        if (!mbar_wait(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+        if (!mbar_wait_hot(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d = tmem_base + buf * BN;
-        for (int st = 0; st < n_main + n_tail; ++st) {
-          if (!mbar_wait(expf_bar(e.s), e.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+        for (int st = 0; st < n_main + n_tail; ++st, ++q) {
+          const int es = q % GF_EXP_STAGES;
+          if (!mbar_wait_hot(expf_bar(es), (uint32_t)((q / GF_EXP_STAGES) & 1), abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = exp_base + e.s * Cfg::EXP_STAGE;
+          const uint32_t sA = exp_base + es * Cfg::EXP_STAGE;
           const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + Cfg::A_EXP);
           const uint32_t idesc = st < n_main ? idesc_h : idesc_bf;
 #pragma unroll
           for (int j = 0; j < 4; ++j) umma_f16(d, adesc + 2 * j, bdesc + 2 * j, idesc, (st > 0 || j > 0) ? 1u : 0u);
-          umma_commit(expe_bar(e.s));
-          e.next();
+          umma_commit(expe_bar(es));
         }
         if (ok) { umma_commit(accf_bar(buf)); ++use; }
       }
@@ -375,17 +389,22 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
 
 // ---------------------------------------------------------------------------------------------------
 // Scale preparation.  One thread per row (activations: token; weights: output channel): the largest
-// chunk scale picks the row's power of two, every chunk scale becomes the fp16 multiplier s * 2^24 / rs
-// and the addend -(z * s) / rs; the row's 16-bit tail is divided by rs (exact) into its own buffer.
+// chunk scale picks the row's power of two; every chunk scale becomes one 8-byte record
+// { (s * 2^24 / rs) twice, -(z * s / rs) twice } of fp16 pairs, ready to be used as packed-FMA operands; the row's 16-bit tail is divided by rs (exact) into its own buffer.
 // ---------------------------------------------------------------------------------------------------
 template <typename ST> __device__ __forceinline__ float scale_to_float(ST v);
 template <> __device__ __forceinline__ float scale_to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float scale_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+__device__ __forceinline__ uint32_t half_twice(float v) {
+  const uint32_t h = __half_as_ushort(__float2half_rn(v));
+  return h | (h << 16);
+}
+
 template <typename ST>
 __global__ void __launch_bounds__(128)
-fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z, int n_chunks, int64_t rows, int64_t ld,
-                   __half* __restrict__ mult, __half* __restrict__ add, float* __restrict__ rs,
+fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z, int n_chunks, int64_t rows, int64_t ld_in,
+                   uint2* __restrict__ rec, int64_t ld_rec, float* __restrict__ rs,
                    const __nv_bfloat16* __restrict__ tail, __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
   __shared__ float inv_s[128];
   const int64_t r0 = (int64_t)blockIdx.x * 128;
@@ -393,20 +412,19 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
   float inv = 0.f;
   if (r < rows) {
     float smax = 0.f;
-    for (int c = 0; c < n_chunks; ++c) smax = fmaxf(smax, fabsf(scale_to_float<ST>(s[(int64_t)c * ld + r])));
+    for (int c = 0; c < n_chunks; ++c) smax = fmaxf(smax, fabsf(scale_to_float<ST>(s[(int64_t)c * ld_in + r])));
     int E = (int)((__float_as_uint(smax) >> 23) & 0xFF) - 127;        // smax = 1.f * 2^E
     E = max(-100, min(100, E));
     inv = __uint_as_float((uint32_t)(127 - 10 - E) << 23);             // 2^(-10 - E): smax * inv in [2^-10, 2^-9)
     rs[r] = __uint_as_float((uint32_t)(127 + 10 + E) << 23);
     const float up = inv * 16777216.f;                                  // * 2^24 (E >= -100 keeps this finite)
     for (int c = 0; c < n_chunks; ++c) {
-      const float sc = scale_to_float<ST>(s[(int64_t)c * ld + r]);
-      mult[(int64_t)c * ld + r] = __float2half_rn(sc * up);
-      if (add) {
-        const float zp = z ? __bfloat162float(z[(int64_t)c * ld + r]) : 8.f;
-        add[(int64_t)c * ld + r] = __float2half_rn(-zp * sc * inv);
-      }
+      const float sc = scale_to_float<ST>(s[(int64_t)c * ld_in + r]);
+      const float zp = z ? __bfloat162float(z[(int64_t)c * ld_in + r]) : 8.f;
+      rec[(int64_t)c * ld_rec + r] = make_uint2(half_twice(sc * up), half_twice(-zp * sc * inv));
     }
+  } else if (r < ld_rec) {
+    for (int c = 0; c < n_chunks; ++c) rec[(int64_t)c * ld_rec + r] = make_uint2(0u, 0u);
   }
   if (tail == nullptr) return;
   inv_s[threadIdx.x] = inv;
@@ -427,20 +445,27 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
   }
 }
 
+// Records are read in whole tiles of rows (bulk copies, no bounds handling), so the record arrays are
+// padded: activations to 128 rows, weights to 768 (a multiple of every column-tile width).
+int64_t f16_ld_act(int64_t M) { return round_up64(M, 128); }
+int64_t f16_ld_weight(int64_t N) { return round_up64(N, 768); }
+
 int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm,
-                           void* mult, void* add, float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out,
+                           void* rec, float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out,
                            int kt_pitch, cudaStream_t st) {
   if (M <= 0) return DIROTQ_OK;
-  fold_scales_kernel<__nv_bfloat16><<<(unsigned)((M + 127) / 128), 128, 0, st>>>(
-      s, z, n_chunks, M, ldm, reinterpret_cast<__half*>(mult), reinterpret_cast<__half*>(add), rs, tail, tail_out, kt_pitch);
+  const int64_t ld_rec = f16_ld_act(M);
+  fold_scales_kernel<__nv_bfloat16><<<(unsigned)(ld_rec / 128), 128, 0, st>>>(
+      s, z, n_chunks, M, ldm, reinterpret_cast<uint2*>(rec), ld_rec, rs, tail, tail_out, kt_pitch);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
-int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* mult, float* cs,
+int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* rec, float* cs,
                               const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, cudaStream_t st) {
   if (N <= 0) return DIROTQ_OK;
-  fold_scales_kernel<float><<<(unsigned)((N + 127) / 128), 128, 0, st>>>(
-      s, nullptr, n_chunks, N, ldn, reinterpret_cast<__half*>(mult), nullptr, cs, tail, tail_out, kt_pitch);
+  const int64_t ld_rec = f16_ld_weight(N);
+  fold_scales_kernel<float><<<(unsigned)(ld_rec / 128), 128, 0, st>>>(
+      s, nullptr, n_chunks, N, ldn, reinterpret_cast<uint2*>(rec), ld_rec, cs, tail, tail_out, kt_pitch);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
@@ -455,7 +480,7 @@ static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st)
   }
   const int tiles = (int)((a.N + BN - 1) / BN) * (int)((a.M + 127) / 128);
   const int grid = min(tiles, num_sms());
-  k<<<grid, GF_THREADS, GfCfg<BN>::SMEM_BYTES, st>>>(tm, a);
+  k<<<grid, GfCfg<BN>::THREADS, GfCfg<BN>::SMEM_BYTES, st>>>(tm, a);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
@@ -475,24 +500,16 @@ static int pick_bn_f16(int64_t N) {
 int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.a_mode != DIROTQ_INT4_SYM && a.a_mode != DIROTQ_INT4_ASYM) return DIROTQ_E_UNSUPPORTED;
-  if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7))
+  if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
+      (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_const) & 15))
     return DIROTQ_E_ALIGN;
   const int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
   GfMaps tm;
   int rc = make_tmap_2d_ex(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
-                           (uint64_t)a.x_row_bytes, 32, 128, false);
+                           (uint64_t)a.x_row_bytes, 64, 128, false);
   if (rc) return rc;
   rc = make_tmap_2d_ex(&tm.wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, (uint64_t)a.w_row_bytes, (uint64_t)a.N,
-                       (uint64_t)a.w_row_bytes, 32, BN, false);
-  if (rc) return rc;
-  rc = make_tmap_2d_ex(&tm.am, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.a_mult, (uint64_t)a.M, (uint64_t)a.n_chunks,
-                       (uint64_t)a.ldm * 2, 128, 1, false);
-  if (rc) return rc;
-  rc = make_tmap_2d_ex(&tm.aa, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.a_add, (uint64_t)a.M, (uint64_t)a.n_chunks,
-                       (uint64_t)a.ldm * 2, 128, 1, false);
-  if (rc) return rc;
-  rc = make_tmap_2d_ex(&tm.wm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.w_mult, (uint64_t)a.N, (uint64_t)a.n_chunks,
-                       (uint64_t)a.ldn * 2, BN, 1, false);
+                       (uint64_t)a.w_row_bytes, 64, BN, false);
   if (rc) return rc;
   if (a.kt > 0) {
     rc = make_tmap_2d(&tm.xt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.xt, (uint64_t)a.kt, (uint64_t)a.M, (uint64_t)a.kt_pitch * 2, 128);

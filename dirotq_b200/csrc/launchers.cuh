@@ -97,15 +97,14 @@ struct GemmIntF16Args {
   int n_chunks;
   const uint8_t* xq;           // activation codes [M, n_chunks * 32]
   int64_t x_row_bytes;
-  const void* a_mult;          // fp16 [n_chunks, ldm]: s * 2^24 / rs
-  const void* a_add;           // fp16 [n_chunks, ldm]: -(z * s) / rs  (z = 8 for symmetric codes)
-  const float* rs;             // [ldm] row powers of two
-  int64_t ldm;
+  const uint2* a_const;        // [n_chunks, ldm] records {s*2^24/rs, -(z*s)/rs}, fp16 pairs
+  const float* rs;             // [M] row powers of two
+  int64_t ldm;                 // f16_ld_act(M)
   const uint8_t* wq;           // weight codes [N, n_chunks * 32]
   int64_t w_row_bytes;
-  const void* w_mult;          // fp16 [n_chunks, ldn]: s * 2^24 / cs
-  const float* cs;             // [ldn] column powers of two
-  int64_t ldn;
+  const uint2* w_const;        // [n_chunks, ldn] records, z = 8
+  const float* cs;             // [N] column powers of two
+  int64_t ldn;                 // f16_ld_weight(N)
   const __nv_bfloat16* xt;     // [M, kt_pitch] tail / rs
   const __nv_bfloat16* wt;     // [N, kt_pitch] tail / cs
   int kt;
@@ -136,10 +135,12 @@ struct GemmFp4Args {
 int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st);
 int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st);
+int64_t f16_ld_act(int64_t M);
+int64_t f16_ld_weight(int64_t N);
 int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm,
-                           void* mult, void* add, float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out,
+                           void* rec, float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out,
                            int kt_pitch, cudaStream_t st);
-int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* mult, float* cs,
+int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* rec, float* cs,
                               const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, cudaStream_t st);
 
 int launch_quantize(const QuantArgs& a, cudaStream_t st);

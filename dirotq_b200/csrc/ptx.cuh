@@ -72,6 +72,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait for roles on the critical path (a stage hand-off every few hundred cycles): polls
+// back to back for a while -- a suspended waiter wakes up too late for such short intervals -- and
+// only then falls into the sleeping loop of mbar_wait.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                              int* status, int code) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag, status, code);
+}
+
 // generic-proxy writes to smem -> visible to the async proxy (UMMA / TMA reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -238,7 +238,7 @@ def gemm_w4a4_int(act: ActBuffers, w: PackedWeightInt4, w_tail: Optional[torch.T
 @dataclass
 class FoldedWeightF16:
     """Weight-side constants of the tensor-rate INT4 GEMM (dirotq_fold_weight_scales_f16)."""
-    mult: torch.Tensor                    # fp16 [n_chunks, ldn]
+    mult: torch.Tensor                    # uint8: 8-byte records per (chunk, channel)
     colscale: torch.Tensor                # fp32 [ldn]
     tail: Optional[torch.Tensor]          # bf16 [N, tail_pitch] = w_tail / colscale
 
@@ -247,7 +247,7 @@ def fold_weight_scales_f16(w: PackedWeightInt4, w_tail: Optional[torch.Tensor], 
     """Per-layer preparation for gemm_w4a4_int_f16: fp16 multipliers, column powers of two, scaled tail."""
     dev = w.scales.device
     ldn = w.scales.shape[1]
-    mult = torch.zeros(w.n_chunks, ldn, dtype=torch.float16, device=dev)
+    mult = torch.zeros(int(_lib.lib().dirotq_fold_weight_records_bytes(w.n_chunks, w.N)), dtype=torch.uint8, device=dev)
     cs = torch.ones(ldn, dtype=torch.float32, device=dev)
     tail_out, pitch = None, 0
     if tail_total > 0:

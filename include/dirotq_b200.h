@@ -164,12 +164,14 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
  * them to bf16).  Row / column powers of two keep every scale inside the fp16 range.
  *
  * dirotq_fold_weight_scales_f16 (once per layer): w_scales fp32 [n_chunks, ldn] ->
- *   w_mult fp16 [n_chunks, ldn], w_colscale fp32 [ldn]; w_tail bf16 [N, tail_pitch] ->
- *   w_tail_out = w_tail / colscale (may be NULL when tail_total == 0).
+ *   w_mult: dirotq_fold_weight_records_bytes(n_chunks, N) bytes of 8-byte per-(chunk, channel)
+ *   records (fp16 pairs: scale * 2^24 and -8 * scale, each divided by the channel's power of two), w_colscale fp32 [N]; w_tail bf16 [N, tail_pitch] -> w_tail_out = w_tail / colscale
+ *   (may be NULL when tail_total == 0).
  * dirotq_gemm_w4a4_int_f16: a_mode DIROTQ_INT4_SYM or DIROTQ_INT4_ASYM; workspace of
  *   dirotq_gemm_w4a4_int_f16_workspace_bytes(M, n_chunks, tail_pitch) bytes, 256-byte aligned
  *   (per-call activation multipliers and the scaled copy of the tail).
  */
+size_t dirotq_fold_weight_records_bytes(int32_t n_chunks, int64_t N);
 int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_scales, const void* w_tail,
                                   int32_t tail_total, int32_t tail_pitch, void* w_mult, float* w_colscale,
                                   void* w_tail_out, void* stream);
