@@ -1,6 +1,6 @@
 // Kernel 2 (INT4, tensor-rate variant): W4A4 GEMM whose 4-bit operands are dequantised to fp16 on their
-// way from shared memory to the tensor core, so that ONE fp32 accumulator runs over the whole K and the
-// per-chunk CUDA-core drain of the exact-integer kernel (gemm_int.cu) disappears.
+// way to the tensor core, so that ONE fp32 accumulator runs over the whole K and the per-chunk
+// CUDA-core drain of the exact-integer kernel (gemm_int.cu) disappears.
 //
 //   y[m,n] = rs[m] cs[n] ( sum_k a'[m,k] b'[n,k] + xt'[m,:] . wt'[n,:] ) + bias[n]
 //   a'[m,k] = (qx[m,k] - zx[m,c]) * sx[m,c] / rs[m]      exact in fp16 for symmetric codes
@@ -20,11 +20,20 @@
 // The order in which a chunk's 64 values land along K is a fixed permutation, the same for both
 // operands, which a dot product does not see.
 //
+// Shared-memory bandwidth, not arithmetic, bounds a kernel that expands operands on chip: every
+// expanded byte is written once and read once by the tensor core.  The activation operand therefore
+// never touches shared memory in expanded form: its converter threads (one per row = one TMEM lane)
+// store the fp16 values straight into tensor memory, and the UMMA takes A from TMEM, B from smem.
+//
 // Data flow per persistent CTA (128 x BN output tiles, K walked in 64-wide chunks):
-//   TMA            4-bit codes (32 B per row per chunk) + the chunk's multipliers -> "raw" ring
-//   8 converter warps  raw ring -> fp16 operand tiles in the 128-byte-swizzled K-major layout
-//   UMMA issuer    tcgen05.mma kind::f16 (fp16 x fp16 -> fp32), 4 x K=16 per chunk, 128 x BN in TMEM;
-//                  bf16 tail tiles (TMA straight into the operand ring) accumulate into the same tile
+//   TMA            4-bit codes (four chunks = 128 B per row per stage, 128-byte swizzle: the copy engine works
+//                  row by row, and shorter rows left it, not the tensor core, on the critical path) +
+//                  per-row records of the chunk's multipliers (bulk copies) -> "raw" ring
+//   converter warps  two groups taking alternate chunks; per chunk a warp expands 32 activation rows into
+//                  TMEM (tcgen05.st) and 32 weight rows into the 128-byte-swizzled K-major smem tile
+//   UMMA issuer    tcgen05.mma kind::f16 (A from TMEM, B from smem descriptor), 4 x K=16 per chunk, fp32
+//                  128 x BN accumulator in TMEM; bf16 tail tiles (TMA straight into the operand ring, both
+//                  operands from smem) accumulate into the same tile
 //   8 epilogue warps  tcgen05.ld, * rs[m] * cs[n], + bias, bf16, 16-byte stores; two accumulators
 //                  alternate so the next tile's UMMAs overlap the epilogue
 #include <cuda.h>
@@ -39,29 +48,36 @@
 namespace dq {
 
 constexpr int GF_EXP_STAGES = 3;
+#ifndef GF_CPS_DEF
+#define GF_CPS_DEF 4
+#endif
+#ifndef GF_RAW_DEF
+#define GF_RAW_DEF 2
+#endif
+constexpr int GF_RAW_STAGES = GF_RAW_DEF;
+constexpr int GF_CPS = GF_CPS_DEF;   // chunks per raw stage: 128 bytes of codes per row and stage
 constexpr int GF_EPI_WARPS = 8;
 
-// One conversion task = one 32-slot block (16 bytes of nibbles) of one operand row.  A chunk of a
-// 128 x BN tile has 2 * (128 + BN) tasks; the converter warp count gives every thread exactly two.
-// A raw stage carries TWO chunks (64 bytes of codes per row): TMA handles a tile row by row, and rows
-// of 32 bytes kept the copy engine, not the tensor core, on the critical path.
+// Conversion work comes in units of 32 rows x one 64-slot chunk (a thread per row).  A chunk of a
+// 128 x BN tile has 4 activation units and BN / 32 weight units; each group has (4 + BN / 32) / 2 warps
+// and every warp takes two units.
 template <int BN> struct GfCfg {
   static constexpr int ROWS = 128 + BN;                    // activation rows, then weight rows
-  static constexpr int TASKS = 2 * ROWS;
-  static constexpr int CONV_WARPS = TASKS / 64;            // 8 / 10 / 12
-  static constexpr int CONV_THREADS = CONV_WARPS * 32;
+  static constexpr int GROUP_WARPS = (4 + BN / 32) / 2;    // 4 (BN = 128) / 5 (BN = 192)
+  static constexpr int CONV_WARPS = 2 * GROUP_WARPS;
   static constexpr int THREADS = (GF_EPI_WARPS + 2 + CONV_WARPS) * 32;
-  static constexpr int A_EXP = 128 * 128;                  // 128 rows x 64 halves
-  static constexpr int B_EXP = BN * 128;
-  static constexpr int EXP_STAGE = A_EXP + B_EXP;          // rows of both operands back to back
-  static constexpr int RAW_A = 128 * 64;
-  static constexpr int RAW_B = BN * 64;
-  static constexpr int OFF_B = RAW_A;
-  static constexpr int OFF_C = RAW_A + RAW_B;               // [2 chunks][ROWS] 8-byte records, same row order
-  static constexpr int RAW_STAGE = OFF_C + 2 * ROWS * 8;
-  static constexpr int RAW_STAGES = (BN > 192) ? 2 : 3;
-  static constexpr int SMEM_BYTES = GF_EXP_STAGES * EXP_STAGE + RAW_STAGES * RAW_STAGE + 1024 + 256;
-  static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  static constexpr int A_EXP = 128 * 128;                  // bf16 tail tile of the activations (tail stages only)
+  static constexpr int B_EXP = BN * 128;                   // BN rows x 64 halves
+  static constexpr int EXP_STAGE = A_EXP + B_EXP;
+  static constexpr int RAW_A = 128 * 32 * GF_CPS;
+  static constexpr int RAW_B = BN * 32 * GF_CPS;
+  static constexpr int OFF_C = RAW_A + RAW_B;               // [chunk][ROWS] 8-byte records, same row order
+  static constexpr int RAW_STAGE = OFF_C + GF_CPS * ROWS * 8;
+  static constexpr int SMEM_BYTES = GF_EXP_STAGES * EXP_STAGE + GF_RAW_STAGES * RAW_STAGE + 1024 + 256;
+  static constexpr int TMEM_A0 = 2 * BN;                    // first column of the activation operand slots
+  static constexpr int TMEM_COLS = 512;                     // 2 accumulators + 3 x 32 columns of A
+  static_assert(2 * BN + GF_EXP_STAGES * 32 <= 512, "tensor memory");
+  static_assert((4 + BN / 32) % 2 == 0, "units must split evenly over the two groups");
 };
 
 struct GfMaps {
@@ -99,27 +115,20 @@ __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) 
   return r;
 }
 
-// One 32-slot block (16 bytes of planar nibbles) of one row -> 32 halves (4 x 16 bytes).
+// One 32-bit word of eight planar nibbles -> four fp16 pairs.
 //   xr : per-nibble XOR (0x8 turns a two's-complement nibble into offset binary; 0 for unsigned codes)
-//   k  : the row's constants for this chunk: k.x = (s * 2^24) twice, k.y = -(z * s) twice (z = 8 for
-//        signed codes); the multiplier of the high nibbles, s * 2^20, is k.x * 2^-4
-//   dst: stage base; off[i] = byte offset of the i-th 16-byte unit (swizzle applied)
-__device__ __forceinline__ void expand_block(const uint4 p, uint32_t xr, const uint2 k2, uint32_t dst, const uint32_t* off) {
-  const uint32_t w[4] = {p.x, p.y, p.z, p.w};
-  const uint32_t xr_hi = xr << 4;
-  uint4 k;
-  k.x = k2.x;
-  k.z = k2.y;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(k.y) : "r"(k2.x), "r"(0x2C002C00u));
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t t = w[i] >> 8;
-    const uint32_t y0 = hfma2_u(and_xor(w[i], 0x000F000Fu, xr), k.x, k.z);
-    const uint32_t y1 = hfma2_u(and_xor(w[i], 0x00F000F0u, xr_hi), k.y, k.z);
-    const uint32_t y2 = hfma2_u(and_xor(t, 0x000F000Fu, xr), k.x, k.z);
-    const uint32_t y3 = hfma2_u(and_xor(t, 0x00F000F0u, xr_hi), k.y, k.z);
-    gf_sts128(dst + off[i], y0, y1, y2, y3);
-  }
+//   mlo = (s * 2^24) twice, mhi = (s * 2^20) twice, add = -(z * s) twice (z = 8 for signed codes)
+__device__ __forceinline__ void expand_word(uint32_t w, uint32_t xr, uint32_t mlo, uint32_t mhi, uint32_t add, uint32_t* y) {
+  const uint32_t t = w >> 8;
+  y[0] = hfma2_u(and_xor(w, 0x000F000Fu, xr), mlo, add);
+  y[1] = hfma2_u(and_xor(w, 0x00F000F0u, xr << 4), mhi, add);
+  y[2] = hfma2_u(and_xor(t, 0x000F000Fu, xr), mlo, add);
+  y[3] = hfma2_u(and_xor(t, 0x00F000F0u, xr << 4), mhi, add);
+}
+__device__ __forceinline__ uint32_t hmul2_2m4(uint32_t m) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(0x2C002C00u));     // * 2^-4
+  return r;
 }
 
 template <int BN, bool ASYM>
@@ -129,7 +138,6 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_area = smem + GF_EXP_STAGES * Cfg::EXP_STAGE;
-  constexpr int GF_RAW_STAGES = Cfg::RAW_STAGES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw_area + GF_RAW_STAGES * Cfg::RAW_STAGE);
   constexpr int NB = 2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NB);
@@ -147,7 +155,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   constexpr int W_MMA = GF_EPI_WARPS, W_TMA = GF_EPI_WARPS + 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < GF_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), Cfg::CONV_WARPS); }
-    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), Cfg::CONV_WARPS / 2); mbar_init(expe_bar(s), 1); }
+    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), Cfg::GROUP_WARPS); mbar_init(expe_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -168,7 +176,8 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   const int total_tiles = n_tiles_n * (int)((a.M + 127) / 128);
   // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... with n fastest, so CTAs running at
   // the same time read the same activation rows through L2.  Rings and the accumulator counter run on
-  // across tiles.
+  // across tiles.  Operand stage q of the kernel-wide sequence (chunks and tail stages of all tiles)
+  // lives in slot q % 3; its barrier phase is (q / 3) & 1.
 
   if (warp == W_TMA) {
     // ------------------------------ TMA producer ---------------------------------------------
@@ -178,14 +187,14 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
-        for (int c = 0; c < n_main; c += 2) {
+        for (int c = 0; c < n_main; c += GF_CPS) {
           if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
           const uint32_t bar = rawf_bar(r.s);
-          const int nv = min(2, n_main - c);
+          const int nv = min(GF_CPS, n_main - c);
           mbar_expect_tx(bar, (uint32_t)(Cfg::OFF_C + nv * Cfg::ROWS * 8));
           tma_load_2d(sb, &tm.xq, bar, c * 32, m0);
-          tma_load_2d(sb + Cfg::OFF_B, &tm.wq, bar, c * 32, n0);
+          tma_load_2d(sb + Cfg::RAW_A, &tm.wq, bar, c * 32, n0);
           for (int j = 0; j < nv; ++j) {
             const uint32_t sc = sb + Cfg::OFF_C + j * Cfg::ROWS * 8;
             bulk_load(sc, a.a_const + ((int64_t)(c + j) * a.ldm + m0), 128 * 8, bar);
@@ -206,51 +215,83 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       }
     }
   } else if (warp > W_TMA) {
-    // ------------------------------ converters: raw ring -> fp16 operand ring ----------------
-    // The converter warps form TWO groups that take alternate operand stages (stage q of the kernel-wide
-    // sequence of chunks and tail stages goes to group q & 1), so one group's barrier waits, shared-memory
-    // latencies and proxy fence overlap the other group's arithmetic.  Within its stage a thread owns
-    // four tasks: task id = row id >> 1 of the combined (activation rows, then weight rows) tile,
-    // 32-slot block id & 1.  Raw codes, constants and operand rows are laid out in that same row order.
-    const int ct = threadIdx.x - (W_TMA + 1) * 32;
-    const int cw = ct >> 5;
-    constexpr int GW = Cfg::CONV_WARPS / 2, GT = GW * 32;
+    // ------------------------------ converters ------------------------------------------------
+    // Two groups take alternate operand stages (stage q goes to group q & 1), so one group's barrier
+    // waits, shared-memory latencies and fences overlap the other group's arithmetic.  Warp gw of a
+    // group owns two units of 32 rows: gw < 4: the activation rows of its own TMEM lane quarter
+    // (warp index mod 4) and weight rows 32 gw ..; the fifth warp (BN = 192): weight rows 128 .. 191.
+    const int cw = warp - (W_TMA + 1);
+    constexpr int GW = Cfg::GROUP_WARPS;
     const int grp = cw >= GW ? 1 : 0;
-    const int gt = ct - grp * GT, gw = cw - grp * GW;
+    const int gw = cw - grp * GW;
+    const int quarter = warp & 3;
+    // combined row index (activation rows 0..127, then weight rows) of this thread's two units
+    const int rowA = (gw < 4) ? quarter * 32 + lane : 128 + (4 + 2 * (gw - 4)) * 32 + lane;
+    const int rowB = (gw < 4) ? 128 + gw * 32 + lane : 128 + (5 + 2 * (gw - 4)) * 32 + lane;
+    const bool first_is_act = gw < 4;
     GfRing<GF_RAW_STAGES> r;
     int q = 0;
     int issued_q[2] = {-1, -1};
     bool ok = true;
-    const int row0 = gt >> 1, h0 = gt & 1;
-    const uint32_t roff = (uint32_t)(row0 * 64 + h0 * 16), koff = (uint32_t)(row0 * 8);
-    uint32_t off[4], xr[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      off[i] = (uint32_t)(row0 * 128 + (((4 * h0 + i) ^ (row0 & 7)) << 4));      // (GT / 2) % 8 == 0: same swizzle for all four tasks
-      xr[i] = (ASYM && gt + i * GT < 256) ? 0u : 0x00080008u;
-    }
     auto exp_slot = [](int qq) { return qq % GF_EXP_STAGES; };
     auto exp_phase = [](int qq) { return (uint32_t)((qq / GF_EXP_STAGES) & 1); };
+    // one row x one chunk: two 16-byte pieces of the swizzled raw row + the row's record
+    auto load_row = [&](uint32_t sraw, int row, int jc, uint4& p0, uint4& p1, uint2& k) {
+      const uint32_t rb = sraw + row * (32 * GF_CPS);
+      const int sw = (GF_CPS == 4) ? (row & 7) : ((row >> 1) & 3);
+      p0 = gf_lds128(rb + (((2 * jc) ^ sw) << 4));
+      p1 = gf_lds128(rb + (((2 * jc + 1) ^ sw) << 4));
+      k = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + row * 8);
+    };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
-      for (int c = 0; c < n_main && ok; c += 2) {
+      for (int c = 0; c < n_main && ok; c += GF_CPS) {
         if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
-        const int nv = min(2, n_main - c);
+        const int nv = min(GF_CPS, n_main - c);
         for (int jc = 0; jc < nv; ++jc, ++q) {
           if ((q & 1) != grp) continue;
-          uint4 p[4];
-          uint2 k[4];
+          uint4 pa0, pa1, pb0, pb1;
+          uint2 ka, kb;
+          load_row(sraw, rowA, jc, pa0, pa1, ka);
+          load_row(sraw, rowB, jc, pb0, pb1, kb);
+          // The first unit is expanded into registers before the slot is known to be free, so that only
+          // stores (and the second unit) remain on the path between "slot free" and "stage ready".
+          uint32_t y1[32];
+          {
+            const uint32_t w8[8] = {pa0.x, pa0.y, pa0.z, pa0.w, pa1.x, pa1.y, pa1.z, pa1.w};
+            const uint32_t mhi = hmul2_2m4(ka.x);
+            const uint32_t xr1 = (first_is_act && ASYM) ? 0u : 0x00080008u;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            p[i] = gf_lds128(sraw + roff + jc * 32 + i * (GT / 2) * 64);
-            k[i] = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + koff + i * (GT / 2) * 8);
+            for (int i = 0; i < 8; ++i) expand_word(w8[i], xr1, ka.x, mhi, ka.y, y1 + 4 * i);
           }
           const int es = exp_slot(q);
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-          const uint32_t sdst = exp_base + es * Cfg::EXP_STAGE;
+          tc_fence_after();
+          const uint32_t sB = exp_base + es * Cfg::EXP_STAGE + Cfg::A_EXP;
+          if (first_is_act) {      // activation rows -> TMEM
+            tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y1);
+          } else {                 // (fifth warp) weight rows -> smem
+            const int rw = rowA - 128;
+            const uint32_t dst = sB + rw * 128;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) expand_block(p[i], xr[i], k[i], sdst + i * (GT / 2) * 128, off);
+            for (int i = 0; i < 8; ++i)
+              gf_sts128(dst + (uint32_t)((i ^ (rw & 7)) << 4), y1[4 * i], y1[4 * i + 1], y1[4 * i + 2], y1[4 * i + 3]);
+          }
+          {   // second unit: weight rows -> smem
+            const uint32_t w8[8] = {pb0.x, pb0.y, pb0.z, pb0.w, pb1.x, pb1.y, pb1.z, pb1.w};
+            const uint32_t mhi = hmul2_2m4(kb.x);
+            const int rw = rowB - 128;
+            const uint32_t dst = sB + rw * 128;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t y[4];
+              expand_word(w8[i], 0x00080008u, kb.x, mhi, kb.y, y);
+              gf_sts128(dst + (uint32_t)((i ^ (rw & 7)) << 4), y[0], y[1], y[2], y[3]);
+            }
+          }
+          if (first_is_act) tmem_wait_st();
+          tc_fence_before();
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(expf_bar(es));
@@ -307,10 +348,16 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           if (!mbar_wait_hot(expf_bar(es), (uint32_t)((q / GF_EXP_STAGES) & 1), abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sA = exp_base + es * Cfg::EXP_STAGE;
-          const uint64_t adesc = smem_desc_sw128(sA), bdesc = smem_desc_sw128(sA + Cfg::A_EXP);
-          const uint32_t idesc = st < n_main ? idesc_h : idesc_bf;
+          const uint64_t bdesc = smem_desc_sw128(sA + Cfg::A_EXP);
+          if (st < n_main) {
+            const uint32_t a_tmem = tmem_base + Cfg::TMEM_A0 + es * 32;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) umma_f16(d, adesc + 2 * j, bdesc + 2 * j, idesc, (st > 0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < 4; ++j) umma_f16_ts(d, a_tmem + 8 * j, bdesc + 2 * j, idesc_h, (st > 0 || j > 0) ? 1u : 0u);
+          } else {
+            const uint64_t adesc = smem_desc_sw128(sA);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) umma_f16(d, adesc + 2 * j, bdesc + 2 * j, idesc_bf, (st > 0 || j > 0) ? 1u : 0u);
+          }
           umma_commit(expe_bar(es));
         }
         if (ok) { umma_commit(accf_bar(buf)); ++use; }
@@ -388,7 +435,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Scale preparation.  One thread per row (activations: token; weights: output channel): the largest
+// Scale preparation, per row (activations: token; weights: output channel): the largest
 // chunk scale picks the row's power of two; every chunk scale becomes one 8-byte record
 // { (s * 2^24 / rs) twice, -(z * s / rs) twice } of fp16 pairs, ready to be used as packed-FMA operands; the row's 16-bit tail is divided by rs (exact) into its own buffer.
 // ---------------------------------------------------------------------------------------------------
@@ -401,40 +448,61 @@ __device__ __forceinline__ uint32_t half_twice(float v) {
   return h | (h << 16);
 }
 
+// Block = 64 rows x 4 chunk phases (thread tid: row tid & 63, chunks c = tid >> 6 (mod 4)).
 template <typename ST>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z, int n_chunks, int64_t rows, int64_t ld_in,
                    uint2* __restrict__ rec, int64_t ld_rec, float* __restrict__ rs,
                    const __nv_bfloat16* __restrict__ tail, __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
-  __shared__ float inv_s[128];
-  const int64_t r0 = (int64_t)blockIdx.x * 128;
-  const int64_t r = r0 + threadIdx.x;
-  float inv = 0.f;
+  __shared__ float part_max[4][64];
+  __shared__ float inv_s[64];
+  const int lr = threadIdx.x & 63, part = threadIdx.x >> 6;
+  const int64_t r0 = (int64_t)blockIdx.x * 64;
+  const int64_t r = r0 + lr;
+  // the tail tile's loads go out first: they do not depend on the scales
+  const int units = tail ? kt_pitch / 8 : 0;             // 16-byte units per row
+  constexpr int TAIL_IT = 4;
+  uint4 tv[TAIL_IT];
+  int n_it = 0;
+  if (tail) {
+#pragma unroll
+    for (int it = 0; it < TAIL_IT; ++it) {
+      const int i = threadIdx.x + it * 256;
+      const int rr = i / units;
+      if (i < 64 * units && r0 + rr < rows) {
+        tv[it] = __ldg(reinterpret_cast<const uint4*>(tail + (r0 + rr) * kt_pitch) + (i % units));
+        n_it = it + 1;
+      }
+    }
+  }
+  float smax = 0.f;
+  if (r < rows)
+    for (int c = part; c < n_chunks; c += 4) smax = fmaxf(smax, fabsf(scale_to_float<ST>(s[(int64_t)c * ld_in + r])));
+  part_max[part][lr] = smax;
+  __syncthreads();
+  smax = fmaxf(fmaxf(part_max[0][lr], part_max[1][lr]), fmaxf(part_max[2][lr], part_max[3][lr]));
+  int E = (int)((__float_as_uint(smax) >> 23) & 0xFF) - 127;          // smax = 1.f * 2^E
+  E = max(-100, min(100, E));
+  const float inv = __uint_as_float((uint32_t)(127 - 10 - E) << 23);  // 2^(-10 - E): smax * inv in [2^-10, 2^-9)
+  if (part == 0) {
+    inv_s[lr] = inv;
+    if (r < rows) rs[r] = __uint_as_float((uint32_t)(127 + 10 + E) << 23);
+  }
+  const float up = inv * 16777216.f;                                    // * 2^24 (E >= -100 keeps this finite)
   if (r < rows) {
-    float smax = 0.f;
-    for (int c = 0; c < n_chunks; ++c) smax = fmaxf(smax, fabsf(scale_to_float<ST>(s[(int64_t)c * ld_in + r])));
-    int E = (int)((__float_as_uint(smax) >> 23) & 0xFF) - 127;        // smax = 1.f * 2^E
-    E = max(-100, min(100, E));
-    inv = __uint_as_float((uint32_t)(127 - 10 - E) << 23);             // 2^(-10 - E): smax * inv in [2^-10, 2^-9)
-    rs[r] = __uint_as_float((uint32_t)(127 + 10 + E) << 23);
-    const float up = inv * 16777216.f;                                  // * 2^24 (E >= -100 keeps this finite)
-    for (int c = 0; c < n_chunks; ++c) {
+    for (int c = part; c < n_chunks; c += 4) {
       const float sc = scale_to_float<ST>(s[(int64_t)c * ld_in + r]);
       const float zp = z ? __bfloat162float(z[(int64_t)c * ld_in + r]) : 8.f;
       rec[(int64_t)c * ld_rec + r] = make_uint2(half_twice(sc * up), half_twice(-zp * sc * inv));
     }
   } else if (r < ld_rec) {
-    for (int c = 0; c < n_chunks; ++c) rec[(int64_t)c * ld_rec + r] = make_uint2(0u, 0u);
+    for (int c = part; c < n_chunks; c += 4) rec[(int64_t)c * ld_rec + r] = make_uint2(0u, 0u);
   }
   if (tail == nullptr) return;
-  inv_s[threadIdx.x] = inv;
   __syncthreads();
-  const int units = kt_pitch / 8;                  // 16-byte units per row
-  for (int i = threadIdx.x; i < 128 * units; i += 128) {
+  auto scale_store = [&](int i, uint4 v) {
     const int rr = i / units, u = i % units;
-    if (r0 + rr >= rows) break;
     const float f = inv_s[rr];
-    uint4 v = __ldg(reinterpret_cast<const uint4*>(tail + (r0 + rr) * kt_pitch) + u);
     __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -442,6 +510,15 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
       h[j] = __floats2bfloat162_rn(x.x * f, x.y * f);
     }
     *(reinterpret_cast<uint4*>(tail_out + (r0 + rr) * kt_pitch) + u) = v;
+  };
+#pragma unroll
+  for (int it = 0; it < TAIL_IT; ++it)
+    if (it < n_it) scale_store(threadIdx.x + it * 256, tv[it]);
+  // wide tails (more than 4 x 256 units per 64 rows): the rest, load and store in turn
+  for (int i = threadIdx.x + TAIL_IT * 256; i < 64 * units; i += 256) {
+    const int rr = i / units;
+    if (r0 + rr >= rows) break;
+    scale_store(i, __ldg(reinterpret_cast<const uint4*>(tail + (r0 + rr) * kt_pitch) + (i % units)));
   }
 }
 
@@ -455,7 +532,7 @@ int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n
                            int kt_pitch, cudaStream_t st) {
   if (M <= 0) return DIROTQ_OK;
   const int64_t ld_rec = f16_ld_act(M);
-  fold_scales_kernel<__nv_bfloat16><<<(unsigned)(ld_rec / 128), 128, 0, st>>>(
+  fold_scales_kernel<__nv_bfloat16><<<(unsigned)(ld_rec / 64), 256, 0, st>>>(
       s, z, n_chunks, M, ldm, reinterpret_cast<uint2*>(rec), ld_rec, rs, tail, tail_out, kt_pitch);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
@@ -464,7 +541,7 @@ int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t l
                               const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, cudaStream_t st) {
   if (N <= 0) return DIROTQ_OK;
   const int64_t ld_rec = f16_ld_weight(N);
-  fold_scales_kernel<float><<<(unsigned)(ld_rec / 128), 128, 0, st>>>(
+  fold_scales_kernel<float><<<(unsigned)(ld_rec / 64), 256, 0, st>>>(
       s, nullptr, n_chunks, N, ldn, reinterpret_cast<uint2*>(rec), ld_rec, cs, tail, tail_out, kt_pitch);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
@@ -485,12 +562,13 @@ static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st)
 }
 
 // Column-tile width: the candidate that wastes the fewest padded columns; ties go to the wider tile
-// (fewer conversions of the activation tile per output column).
+// (fewer conversions of the activation tile per output column).  256 does not fit: two accumulators
+// of 256 columns would leave no tensor memory for the activation operand.
 static int pick_bn_f16(int64_t N) {
-  const int cand[3] = {256, 192, 128};
+  const int cand[2] = {192, 128};
   int best = 128;
   int64_t best_pad = -1;
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < 2; ++i) {
     const int64_t pad = (N + cand[i] - 1) / cand[i] * cand[i] - N;
     if (best_pad < 0 || pad < best_pad) { best_pad = pad; best = cand[i]; }
   }
@@ -505,11 +583,11 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
     return DIROTQ_E_ALIGN;
   const int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
   GfMaps tm;
-  int rc = make_tmap_2d_ex(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
-                           (uint64_t)a.x_row_bytes, 64, 128, false);
+  int rc = make_tmap_2d_sw(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
+                           (uint64_t)a.x_row_bytes, 32 * GF_CPS, 128, 32 * GF_CPS);
   if (rc) return rc;
-  rc = make_tmap_2d_ex(&tm.wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, (uint64_t)a.w_row_bytes, (uint64_t)a.N,
-                       (uint64_t)a.w_row_bytes, 64, BN, false);
+  rc = make_tmap_2d_sw(&tm.wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, (uint64_t)a.w_row_bytes, (uint64_t)a.N,
+                       (uint64_t)a.w_row_bytes, 32 * GF_CPS, BN, 32 * GF_CPS);
   if (rc) return rc;
   if (a.kt > 0) {
     rc = make_tmap_2d(&tm.xt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.xt, (uint64_t)a.kt, (uint64_t)a.M, (uint64_t)a.kt_pitch * 2, 128);
@@ -522,7 +600,6 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   }
   const bool asym = a.a_mode == DIROTQ_INT4_ASYM;
   switch (BN) {
-    case 256: return asym ? launch_gf<256, true>(tm, a, st) : launch_gf<256, false>(tm, a, st);
     case 192: return asym ? launch_gf<192, true>(tm, a, st) : launch_gf<192, false>(tm, a, st);
     case 128: return asym ? launch_gf<128, true>(tm, a, st) : launch_gf<128, false>(tm, a, st);
   }

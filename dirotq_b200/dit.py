@@ -164,7 +164,13 @@ class LinearPathStep(nn.Module):
         return lin, rot
 
     def kernel_launches_per_step(self) -> int:
-        return 2 * len(self.block) * self.n_blocks      # rotate/quantise (or dequantise) + GEMM per linear
+        """Library kernels per step: rotate/quantise (or weight dequantise) + GEMM per linear, plus the
+        scale-folding kernel of the tensor-rate INT4 GEMM where a layer uses it."""
+        n = 0
+        for lyr in self.layers:
+            st = getattr(lyr, "_b200_state", None)
+            n += 3 if (st is not None and st.folded is not None) else 2
+        return n
 
     def forward(self, x: torch.Tensor, ff_scale: float = 0.25) -> torch.Tensor:
         y = x

@@ -260,6 +260,12 @@ def fold_weight_scales_f16(w: PackedWeightInt4, w_tail: Optional[torch.Tensor], 
     return FoldedWeightF16(mult, cs, tail_out)
 
 
+def f16_workspace_bytes(act: ActBuffers) -> int:
+    lay = act.layout
+    tp = lay.tail_pitch if lay.tail_total > 0 else 0
+    return max(256, int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(act.M, lay.n_chunks, tp)))
+
+
 def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeightF16, bias: Optional[torch.Tensor],
                       workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Kernel 2 (INT4, tensor-rate variant): codes expanded to fp16 in shared memory, one fp32 accumulator."""

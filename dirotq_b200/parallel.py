@@ -181,7 +181,8 @@ class FluxLinearStep:
         return lin, rot
 
     def kernel_launches_per_step(self) -> int:
-        return 2 * len(self.layers)
+        return sum(3 if getattr(l, "_b200_state", None) is not None and l._b200_state.folded is not None else 2
+                   for l in self.layers)
 
     def rows_per_rank(self, stream: str) -> int:
         return self.rows[stream] // self.world
