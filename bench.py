@@ -221,7 +221,7 @@ def run_ours(args):
             step = FluxLinearStep(world, rank, dev, batch=batch, n_double=n_double, n_single=2 * n_double,
                                   ffn=args.flux_ffn, quant=quant)
             backend.preconvert_rotations_to_device(step.layers, dev)
-            for lyr in step.layers:                  # the packed device state is all the forward needs
+            for lyr in step._flat:                   # the packed device state is all the forward needs
                 lyr._b200_explicit = None
                 lyr.rotation = lyr.rotation_per_head = None
             torch.cuda.empty_cache()
@@ -232,7 +232,7 @@ def run_ours(args):
             x_host = synth_activations(M, D, g).pin_memory()
             y_shape = (M, out_f)
             scaling = "strong"
-            l2_note = f"inputs larger than L2 ({len(step.layers)} distinct weight sets per step)"
+            l2_note = f"inputs larger than L2 ({len(step._flat)} distinct weight sets per step)"
         else:
             block = getattr(dit, blk_name)()
             M = tokens * batch                           # rows per GPU (weak scaling: fixed per-GPU batch)

@@ -58,6 +58,7 @@ SIGNATURES = {
     "dirotq_gemm_w4a16": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_workspace_bytes": (_SZ, [C.POINTER(LinearC), _I64]),
     "dirotq_linear_forward": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _SZ, _P, _P]),
+    "dirotq_linear_gemm": (C.c_int, [C.POINTER(LinearC), _I64, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_forward_static_capacity": (_SZ, []),
     "dirotq_linear_forward_static": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _P]),
 }

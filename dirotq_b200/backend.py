@@ -28,6 +28,44 @@ from .wrapper import ActQuantWrapper
 _HW_NVFP4_ACT_SCALE = 1.0   # static fp32 tensor scale of NVFP4 activations (UE4M3 then covers amax up to 2688)
 
 
+class SharedActivation:
+    """Quantised activations shared by sibling layers that see the same input through the same rotation
+    and format (attn.to_q / to_k / to_v: the reference gives all three `evec @ R1` of one basis,
+    models/pixart-sigma/model_utils.py:84-92, and diffusers calls them on one hidden_states tensor).
+    The first member called on a tensor rotates and quantises it into the group's workspace; members
+    called next on the SAME tensor run only their GEMM.  "Same" = same storage address, shape and
+    in-place version counter, with a reference held so that the storage cannot be recycled in between;
+    the reference is dropped once every member has used it."""
+
+    def __init__(self, n_members: int):
+        self.n_members = n_members
+        self.ws: Dict[int, torch.Tensor] = {}
+        self.x_ref: Optional[torch.Tensor] = None
+        self.key = None
+        self.seen = set()
+        self.hits = 0
+        self.misses = 0
+
+    @staticmethod
+    def _key(x: torch.Tensor):
+        return (x.data_ptr(), x._version, tuple(x.shape), tuple(x.stride()), x.dtype, x.device.index,
+                torch.cuda.current_stream(x.device).cuda_stream)
+
+    def lookup(self, x: torch.Tensor, member_id: int) -> bool:
+        """True if the workspace already holds this tensor's codes and `member_id` has not used them yet."""
+        hit = self.x_ref is not None and self.key == self._key(x) and member_id not in self.seen
+        if hit:
+            self.hits += 1
+            self.seen.add(member_id)
+            if len(self.seen) == self.n_members:
+                self.x_ref, self.key = None, None
+        return hit
+
+    def store(self, x: torch.Tensor, member_id: int):
+        self.misses += 1
+        self.x_ref, self.key, self.seen = x, self._key(x), {member_id}
+
+
 @dataclass
 class LayerState:
     """Device-resident packed form of one wrapped linear."""
@@ -44,6 +82,8 @@ class LayerState:
     w_tensor_scale: float = 1.0
     n_lossy_groups: int = 0
     folded: Optional[ops.FoldedWeightF16] = None     # INT4 activations: constants of the tensor-rate GEMM
+    shared: Optional[SharedActivation] = None
+    member_id: int = 0
     _c: Optional[LinearC] = None
     _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
 
@@ -57,6 +97,14 @@ class LayerState:
         return self._c
 
     def workspace(self, M: int, device) -> torch.Tensor:
+        if self.shared is not None:
+            ws = self.shared.ws.get(M)
+            if ws is None:
+                n = int(_lib.lib().dirotq_linear_workspace_bytes(C.byref(self.c_struct()), M))
+                ws = torch.zeros(max(n, 256), dtype=torch.uint8, device=device)
+                self.shared.ws = {M: ws}
+                self.shared.x_ref, self.shared.key = None, None
+            return ws
         ws = self._ws.get(M)
         if ws is None:
             n = int(_lib.lib().dirotq_linear_workspace_bytes(C.byref(self.c_struct()), M))
@@ -72,6 +120,15 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     M = x2d.shape[0]
     y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
     ws = st.workspace(M, x2d.device)
+    if st.shared is not None:
+        if st.shared.lookup(x2d, st.member_id):
+            check(_lib.lib().dirotq_linear_gemm(C.byref(st.c_struct()), M, C.c_void_p(y.data_ptr()),
+                                                C.c_void_p(ws.data_ptr()), ws.numel(),
+                                                C.c_void_p(ops.status_word(x2d.device).data_ptr()),
+                                                C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                  "dirotq_linear_gemm")
+            return y
+        st.shared.store(x2d, st.member_id)
     check(_lib.lib().dirotq_linear_forward(C.byref(st.c_struct()), C.c_void_p(x2d.data_ptr()), M,
                                            C.c_void_p(y.data_ptr()), C.c_void_p(ws.data_ptr()), ws.numel(),
                                            C.c_void_p(ops.status_word(x2d.device).data_ptr()),
@@ -252,6 +309,43 @@ def _fused_forward_b200(self, x):
     return y.reshape(*shp[:-1], st.out_features).to(x_dtype)
 
 
+# Sibling layers with equal rotation and format (to_q / to_k / to_v) rotate and quantise their common
+# input once.  Set to False to give every layer its own pass.
+SHARE_SIBLING_ACTIVATIONS = True
+_SIBLING_SUFFIXES = ("to_q", "to_k", "to_v")
+
+
+def share_sibling_activations(transformer, classes=None) -> int:
+    """Group prepared sibling wrappers (same parent module, names to_q / to_k / to_v) whose rotations are
+    equal element for element and whose activation formats are identical.  Returns the number of groups."""
+    classes = tuple(classes or _wrapper_classes())
+    buckets: Dict[str, list] = {}
+    for name, mod in transformer.named_modules():
+        if not isinstance(mod, classes):
+            continue
+        st = getattr(mod, "_b200_state", None)
+        parent, _, leaf = name.rpartition(".")
+        if st is None or st.rot_t is None or leaf not in _SIBLING_SUFFIXES:
+            continue
+        buckets.setdefault(parent, []).append(st)
+    n_groups = 0
+    for members in buckets.values():
+        first = members[0]
+        same = [first] + [m for m in members[1:]
+                          if m.fmt == first.fmt and (m.folded is None) == (first.folded is None)
+                          and m.rot_t.shape == first.rot_t.shape and torch.equal(m.rot_t, first.rot_t)]
+        if len(same) < 2:
+            continue
+        grp = SharedActivation(len(same))
+        for i, m in enumerate(same):
+            m.shared, m.member_id = grp, i
+            m.rot_t = first.rot_t            # one copy of the rotation on the device
+            m._c = None
+            m._ws = {}
+        n_groups += 1
+    return n_groups
+
+
 def _wrapper_classes():
     classes = [ActQuantWrapper]
     ref = sys.modules.get("utils.quant_utils")
@@ -287,5 +381,8 @@ def preconvert_rotations_to_device(transformer, device="cuda", dtype=None):
         object.__setattr__(mod, "_b200_state", st)
         if st.rot_t is not None or st.perm_idx is not None:
             n += 1
+    n_groups = share_sibling_activations(transformer, classes) if SHARE_SIBLING_ACTIVATIONS else 0
+    if n_groups:
+        print(f"{n_groups} groups of sibling layers (same input, same rotation) share one rotate+quantise pass.")
     print(f"Preconverted {n} rotation/permutation tensors to {device} (bf16, K-major) and packed the weights.")
     return n

@@ -252,11 +252,13 @@ size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int32_t n_chunks, int
   return carve_f16(M, n_chunks, tail_pitch).total;
 }
 
-int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
-                             const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
-                             const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
-                             int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
-                             size_t workspace_bytes, int32_t* status, void* stream) {
+// skip_fold != 0: the workspace already holds the activation records and the scaled tail of these codes
+// (left there by an earlier call on the same activations).
+static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
+                                  const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
+                                  const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
+                                  int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
+                                  size_t workspace_bytes, int skip_fold, int32_t* status, void* stream) {
   if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM) return DIROTQ_E_UNSUPPORTED;
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_codes || !w_mult || !w_colscale || !y || !workspace)
     return DIROTQ_E_ARG;
@@ -276,11 +278,13 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   __nv_bfloat16* tail_s = tail_total > 0 ? reinterpret_cast<__nv_bfloat16*>(ws + c.tail) : nullptr;
-  int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales),
-                                  a_mode == DIROTQ_INT4_ASYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
-                                  n_chunks, M, ld_rows(M), ws + c.rec, reinterpret_cast<float*>(ws + c.rs),
-                                  tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
-  if (rc) return rc;
+  if (!skip_fold) {
+    int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales),
+                                    a_mode == DIROTQ_INT4_ASYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
+                                    n_chunks, M, ld_rows(M), ws + c.rec, reinterpret_cast<float*>(ws + c.rs),
+                                    tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
+    if (rc) return rc;
+  }
   GemmIntF16Args a;
   a.a_mode = a_mode;
   a.M = M;
@@ -305,6 +309,16 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
   a.status = status;
   a.force_bn = 0;
   return launch_gemm_int_f16(a, st);
+}
+
+int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
+                             const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
+                             const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
+                             int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
+  return gemm_w4a4_int_f16_impl(a_mode, M, N, n_chunks, x_codes, x_scales, x_zeros, w_codes, w_mult, w_colscale, x_tail,
+                                w_tail_scaled, tail_total, tail_pitch, bias, y, workspace, workspace_bytes, 0, status,
+                                stream);
 }
 
 int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
@@ -366,9 +380,10 @@ size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M) {
   return w.total;
 }
 
-int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
-                          size_t workspace_bytes, int32_t* status, void* stream) {
-  if (!lin || !x || !y || !workspace) return DIROTQ_E_ARG;
+// stages: 1 = rotate / quantise into the workspace, 2 = GEMM from the workspace, 3 = both
+static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
+                         size_t workspace_bytes, int stages, int32_t* status, void* stream) {
+  if (!lin || !workspace || ((stages & 1) && !x) || ((stages & 2) && !y)) return DIROTQ_E_ARG;
   ActGeom g;
   WsCarve w;
   int rc = carve(lin, M, &g, &w);
@@ -381,24 +396,38 @@ int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, vo
   void* scales = ws + w.scales;
   void* zeros = is_asym(g.mode) ? ws + w.zeros : nullptr;
   void* tail = g.tail_total > 0 ? ws + w.tail : nullptr;
-  if (lin->rot_t)
-    rc = dirotq_rotate_quantize(&lin->fmt, x, lin->rot_t, M, nullptr, codes, scales, zeros, tail, status, stream);
-  else
-    rc = dirotq_quantize_act(&lin->fmt, x, g.D, lin->perm_idx, M, codes, scales, zeros, tail, stream);
-  if (rc) return rc;
+  if (stages & 1) {
+    if (lin->rot_t)
+      rc = dirotq_rotate_quantize(&lin->fmt, x, lin->rot_t, M, nullptr, codes, scales, zeros, tail, status, stream);
+    else
+      rc = dirotq_quantize_act(&lin->fmt, x, g.D, lin->perm_idx, M, codes, scales, zeros, tail, stream);
+    if (rc) return rc;
+  }
+  if (!(stages & 2)) return DIROTQ_OK;
   if (g.mode == DIROTQ_NVFP4_HW)
     return dirotq_gemm_w4a4_nvfp4(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
                                   lin->fmt.tensor_scale * lin->w_tensor_scale, tail, lin->w_tail, g.tail_total,
                                   g.tail_pitch, lin->bias, y, status, stream);
   if (uses_f16_gemm(lin, g)) {
     if (!lin->w_colscale || (g.tail_total > 0 && !lin->w_tail_f16)) return DIROTQ_E_ARG;
-    return dirotq_gemm_w4a4_int_f16(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
-                                    lin->w_mult, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
-                                    lin->bias, y, ws + w.fold, w.total - w.fold, status, stream);
+    // the activation-side folding belongs to the first stage: a GEMM-only call finds its results in place
+    return gemm_w4a4_int_f16_impl(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
+                                  lin->w_mult, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
+                                  lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 1) ? 0 : 1, status, stream);
   }
   return dirotq_gemm_w4a4_int(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
                               static_cast<const float*>(lin->w_scales), lin->w_sum, tail, lin->w_tail, g.tail_total,
                               g.tail_pitch, lin->bias, y, nullptr, status, stream);
+}
+
+int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  return linear_stages(lin, x, M, y, workspace, workspace_bytes, 3, status, stream);
+}
+
+int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* workspace, size_t workspace_bytes,
+                       int32_t* status, void* stream) {
+  return linear_stages(lin, nullptr, M, y, workspace, workspace_bytes, 2, status, stream);
 }
 
 

@@ -142,6 +142,17 @@ def make_wrapped_linear(ld: LayerDef, quant: str, seed: int, device="cuda", a_sy
     return w
 
 
+def _set_nested(root: nn.Module, dotted: str, leaf: nn.Module):
+    """root.a.b.c = leaf for dotted == "a.b.c", creating plain container modules on the way."""
+    parts = dotted.split(".")
+    m = root
+    for p in parts[:-1]:
+        if not hasattr(m, p):
+            m.add_module(p, nn.Module())
+        m = getattr(m, p)
+    m.add_module(parts[-1], leaf)
+
+
 class LinearPathStep(nn.Module):
     """All wrapped linears of one denoising step of a DiT, run in block order on the block input
     (and, for FFN down-projections, on the activated up-projection output).  Attention, norms and
@@ -152,11 +163,25 @@ class LinearPathStep(nn.Module):
         super().__init__()
         self.block = block
         self.n_blocks = n_blocks
-        self.layers = nn.ModuleList()
+        self.blocks = nn.ModuleList()     # module tree with the reference's names (blocks.3.attn1.to_q ...)
+        self.layers = []                  # the same wrappers in call order
         for b in range(n_blocks):
+            blk = nn.Module()
+            qkv_rotation = {}
             for i, ld in enumerate(block):
                 q = "int4" if (quant == "nvfp4" and ld.kind == "perhead") else quant
-                self.layers.append(make_wrapped_linear(ld, q, seed + b * len(block) + i, device, a_sym))
+                w = make_wrapped_linear(ld, q, seed + b * len(block) + i, device, a_sym)
+                # to_q / to_k / to_v of one attention see the same input and get the same rotation
+                # (evec @ R1 of one basis: models/pixart-sigma/model_utils.py:84-92, flux-schnell:165-178)
+                parent, _, leaf = ld.name.rpartition(".")
+                if leaf in ("to_q", "to_k", "to_v") and ld.kind == "hidden":
+                    if parent in qkv_rotation:
+                        w.rotation = qkv_rotation[parent].clone()
+                    else:
+                        qkv_rotation[parent] = w.rotation
+                _set_nested(blk, ld.name, w)
+                self.layers.append(w)
+            self.blocks.append(blk)
 
     def ops_per_step(self, M: int):
         lin = sum(linear_ops(ld, M) for ld in self.block) * self.n_blocks
@@ -169,7 +194,10 @@ class LinearPathStep(nn.Module):
         n = 0
         for lyr in self.layers:
             st = getattr(lyr, "_b200_state", None)
-            n += 3 if (st is not None and st.folded is not None) else 2
+            if st is not None and st.shared is not None and st.member_id > 0:
+                n += 1                      # GEMM only: the sibling before it left the codes in place
+            else:
+                n += 3 if (st is not None and st.folded is not None) else 2
         return n
 
     def forward(self, x: torch.Tensor, ff_scale: float = 0.25) -> torch.Tensor:

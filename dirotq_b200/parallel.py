@@ -148,28 +148,36 @@ class FluxLinearStep:
         tp = world if self.ffn == "tp" else 1
         tp_slices(self.inner, tp, 0, 64)
         ph = dict(kind="perhead", tail=16, heads=24, head_dim=128)
-        attn = [dit.LayerDef(n, 3072, 3072, tail=k) for n in ("to_q", "to_k", "to_v")] + \
-               [dit.LayerDef("to_out", 3072, 3072, **ph)]
+        attn = [dit.LayerDef(n, 3072, 3072, tail=k) for n in ("attn.to_q", "attn.to_k", "attn.to_v")] + \
+               [dit.LayerDef("attn.to_out", 3072, 3072, **ph)]
         up = dit.LayerDef("ffn_up", 3072, self.inner // tp, tail=k)
         down = dit.LayerDef("ffn_down", self.inner // tp, 3072, kind="norot", tail=0, source="ff")
         self.census = []            # (stream, LayerDef at full size) for the operation count
         self.blocks = []            # (stream, [attn wrappers], up, down)
         layers = []
+        tree = nn.ModuleList()
         s = seed + 104729 * rank
         for stream, n in (("img", n_double), ("txt", n_double), ("single", n_single)):
             for _ in range(n):
                 ws = [dit.make_wrapped_linear(ld, quant, s + i, device) for i, ld in enumerate(attn)]
+                for w_ in ws[1:3]:      # to_k, to_v: same input, same rotation as to_q (flux-schnell/model_utils.py:165-178)
+                    w_.rotation = ws[0].rotation.clone()
                 wu = dit.make_wrapped_linear(up, quant, s + 4, device)
                 wd = dit.make_wrapped_linear(down, quant, s + 5, device)
                 if self.ffn == "tp" and rank != 0:
                     wd._b200_explicit["bias"] = None        # the bias enters the reduced sum once
                 s += 6
                 self.blocks.append((stream, ws, wu, wd))
+                blk = nn.Module()
+                for ld, w_ in zip(attn + [up, down], ws + [wu, wd]):
+                    dit._set_nested(blk, ld.name, w_)
+                tree.append(blk)
                 layers += ws + [wu, wd]
                 self.census += [(stream, ld) for ld in attn]
                 self.census += [(stream, dit.LayerDef("ffn_up", 3072, self.inner)),
                                 (stream, dit.LayerDef("ffn_down", self.inner, 3072))]
-        self.layers = nn.ModuleList(layers)
+        self.layers = tree               # module tree (blocks.i.attn.to_q ...); call order is in self.blocks
+        self._flat = layers
         self._gather = {}
 
     def ops_per_step(self):
@@ -181,8 +189,14 @@ class FluxLinearStep:
         return lin, rot
 
     def kernel_launches_per_step(self) -> int:
-        return sum(3 if getattr(l, "_b200_state", None) is not None and l._b200_state.folded is not None else 2
-                   for l in self.layers)
+        n = 0
+        for l in self._flat:
+            st = getattr(l, "_b200_state", None)
+            if st is not None and st.shared is not None and st.member_id > 0:
+                n += 1
+            else:
+                n += 3 if (st is not None and st.folded is not None) else 2
+        return n
 
     def rows_per_rank(self, stream: str) -> int:
         return self.rows[stream] // self.world

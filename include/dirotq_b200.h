@@ -226,6 +226,14 @@ size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M);
 int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
                           size_t workspace_bytes, int32_t* status, void* stream);
 
+/* Second half of dirotq_linear_forward alone: the GEMM of `lin` on the quantised activations that an
+ * earlier dirotq_linear_forward left in `workspace` (same M, a layer with the same activation format
+ * and rotation -- e.g. to_k and to_v after to_q, which the reference rotates with the same matrix,
+ * models/pixart-sigma/model_utils.py:84-92 -- and the same GEMM variant, i.e. w_mult set or not in
+ * both).  The caller guarantees that the activations are unchanged since. */
+int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* workspace, size_t workspace_bytes,
+                       int32_t* status, void* stream);
+
 /* Same computation as dirotq_linear_forward, for callers that can hand over nothing but the input
  * and the output.  (No counterpart in the reference: its eager forward allocates freely through
  * torch.)  Meant for hosts that give a plug-in no allocator at all -- an inference server whose

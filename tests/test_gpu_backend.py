@@ -189,3 +189,63 @@ def test_rotation_api_signature():
     assert sc is None
     y = bf16_rotation_forward(x, Up, sc, scale_x=None)
     assert rel_l2(y.float().cpu(), (x.float() @ U).cpu()) < 4e-3
+
+
+@pytest.mark.parametrize("quant", ["int4", "nvfp4"])
+def test_sibling_layers_share_one_rotate_quantise_pass(quant):
+    """to_q / to_k / to_v carry the same rotation (models/pixart-sigma/model_utils.py:84-92) and are called on
+    one tensor: the first call rotates and quantises, the other two run their GEMM on the same codes.  Outputs
+    are bit-identical to layers prepared without sharing; a changed or different input is never served from
+    the shared codes."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+
+    def build():
+        attn = nn.Module()
+        ws = []
+        for i, leaf in enumerate(("to_q", "to_k", "to_v")):
+            w = dit.make_wrapped_linear(dit.LayerDef("attn1." + leaf, 384, 256 + 64 * i, tail=64), quant, 77 + i, "cuda")
+            if ws:
+                w.rotation = ws[0].rotation.clone()
+            attn.add_module(leaf, w)
+            ws.append(w)
+        root = nn.Module()
+        root.add_module("attn1", attn)
+        return root, ws
+
+    root, ws = build()
+    backend.preconvert_rotations_to_device(root, "cuda")
+    grp = ws[0]._b200_state.shared
+    assert grp is not None and all(w._b200_state.shared is grp for w in ws)
+    root2, ws2 = build()
+    backend.SHARE_SIBLING_ACTIVATIONS = False
+    try:
+        backend.preconvert_rotations_to_device(root2, "cuda")
+    finally:
+        backend.SHARE_SIBLING_ACTIVATIONS = True
+    assert all(w._b200_state.shared is None for w in ws2)
+
+    x = synth_activations(300, 384, torch.Generator().manual_seed(9)).reshape(1, 300, 384).cuda()
+    ys = [w(x) for w in ws]
+    ops.check_status()
+    assert (grp.misses, grp.hits) == (1, 2) and grp.x_ref is None
+    for y, w2 in zip(ys, ws2):
+        assert torch.equal(y, w2(x))
+    # the same tensor again: a new pass (every member has used the old codes), then two hits
+    ys_again = [w(x) for w in ws]
+    assert (grp.misses, grp.hits) == (2, 4)
+    assert all(torch.equal(a, b) for a, b in zip(ys, ys_again))
+    # in-place change between siblings: the version counter moves, the codes are not reused
+    y_q = ws[0](x)
+    x.mul_(0.5)
+    y_k = ws[1](x)
+    assert grp.misses == 4
+    assert torch.equal(y_k, ws2[1](x)) and torch.equal(y_q, ys[0])
+    # a different tensor
+    x2 = synth_activations(300, 384, torch.Generator().manual_seed(10)).reshape(1, 300, 384).cuda()
+    assert torch.equal(ws[2](x2), ws2[2](x2))
+    # calling one member twice on the same tensor recomputes rather than reusing its own stale slot
+    a = ws[0](x2)
+    b = ws[0](x2)
+    assert torch.equal(a, b)
+    ops.check_status()
