@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--flux-ffn", default="tp", choices=["tp", "dp"],
                     help="flux_int4 at N > 1: FFN pairs tensor-parallel (all-gather + reduce-scatter) or row-sharded")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exact-int", action="store_true",
+                    help="INT4 layers through the exact-integer kind::i8 GEMM instead of the tensor-rate fp16 one")
     ap.add_argument("--profile-case", action="store_true",
                     help="run a small case for ncu instead of the benchmark: one 1152->1152 k=64 layer at M=16384 "
                          "(38 MB in, 38 MB out), INT4 then NVFP4, three forwards each")
@@ -333,6 +335,7 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     bufs = {}
     ops_total = 0.0
     f16_ws, f16_used = None, False
+    bytes_total = 0.0
     nb = len(step.block)
     for _ in range(max(1, min(steps, 2))):
         for idx, lyr in enumerate(step.layers):
@@ -365,6 +368,7 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
             e1.record()
             pairs.append((e0, e1))
             ops_total += 2.0 * M * ld.out_f * ld.in_f
+            bytes_total += gemm_algorithmic_bytes(M, ld.out_f, st.layout, quant)
     torch.cuda.synchronize()
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
@@ -374,7 +378,25 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
             "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained; the INT4 path computes in fp16 on the same tensor pipe, "
                            "dense FP4 is nominally 4x that figure",
-            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None}
+            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)),
+            "traffic": NCU_TRAFFIC_RATIO * bytes_total / max(1, len(pairs)),
+            "traffic_source": f"algorithmic bytes per launch x {NCU_TRAFFIC_RATIO} (dram read + write of one ncu capture of "
+                              "the INT4 GEMM at M=16384, N=K=1152 over its algorithmic bytes; traffic grows with M and N)"}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the captured launch (14.3 MB: the 38 MB of output it wrote
+# were still in the 126 MB L2 when the launch ended) / its algorithmic bytes (52 MB); see profiles/
+NCU_TRAFFIC_RATIO = 0.275
+
+
+def gemm_algorithmic_bytes(M, N, lay, quant):
+    """Bytes one W4A4 GEMM call must move: activation codes, scale data and tail, the weight's, bias, output."""
+    if quant == "nvfp4":
+        per_row = lay.code_row_bytes + lay.n_chunks * 4 + lay.tail_pitch * 2
+    else:   # codes + 8-byte records per chunk + bf16 scales read by the fold kernel + tail read, written and read again
+        per_row = lay.code_row_bytes + lay.n_chunks * (8 + 2 + 8) + lay.tail_pitch * 2 * 3
+    w_row = lay.code_row_bytes + lay.n_chunks * 8 + lay.tail_pitch * 2 + 2
+    return float(M * per_row + N * w_row + 2 * M * N)
 
 
 def roofline_pass_flux(step, x_dev, dev):
@@ -406,7 +428,10 @@ def roofline_pass_flux(step, x_dev, dev):
     return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_scales_kernel)", "achieved": achieved,
             "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained (the kernel computes in fp16 on the same tensor pipe)",
-            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None}
+            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)),
+            "traffic": NCU_TRAFFIC_RATIO * gemm_algorithmic_bytes(M, 3072, st.layout, "int4"),
+            "traffic_source": f"algorithmic bytes per launch x {NCU_TRAFFIC_RATIO} (ratio of one ncu capture of the INT4 "
+                              "GEMM at M=16384, N=K=1152)"}
 
 
 def profile_case():
@@ -429,6 +454,9 @@ def profile_case():
 
 if __name__ == "__main__":
     a = parse()
+    if a.exact_int:
+        from dirotq_b200 import backend as _backend
+        _backend.INT4_TENSOR_RATE_GEMM = False
     if a.profile_case:
         profile_case()
     elif a.impl == "reference":
