@@ -200,7 +200,7 @@ class LinearPathStep(nn.Module):
                 n += 3 if (st is not None and st.folded is not None) else 2
         return n
 
-    def forward(self, x: torch.Tensor, ff_scale: float = 0.25) -> torch.Tensor:
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = x
         nb = len(self.block)
         for b in range(self.n_blocks):
@@ -213,5 +213,4 @@ class LinearPathStep(nn.Module):
                     y = lyr(x)
                     if ld.out_f != ld.in_f and ld.out_f > ld.in_f:
                         ff = torch.nn.functional.gelu(y, approximate="tanh")
-                        ff.mul_(ff_scale)
         return y

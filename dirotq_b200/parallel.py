@@ -204,7 +204,7 @@ class FluxLinearStep:
     def _ffn(self, x, wu, wd):
         if self.ffn == "dp":
             h = torch.nn.functional.gelu(wu(x), approximate="tanh")
-            return wd(h.mul_(0.25))
+            return wd(h)
         m = x.shape[0]
         key = (m, x.dtype)
         if key not in self._gather:
@@ -213,7 +213,7 @@ class FluxLinearStep:
         full, out = self._gather[key]
         dist.all_gather_into_tensor(full, x.contiguous())
         h = torch.nn.functional.gelu(wu(full.unsqueeze(0)), approximate="tanh")
-        part = wd(h.mul_(0.25)).reshape(self.world * m, self.hidden)
+        part = wd(h).reshape(self.world * m, self.hidden)
         dist.reduce_scatter_tensor(out, part, op=dist.ReduceOp.SUM)
         return out
 
