@@ -32,8 +32,8 @@
 //   converter warps  two groups taking alternate chunks; per chunk a warp expands 32 activation rows into
 //                  TMEM (tcgen05.st) and 32 weight rows into the 128-byte-swizzled K-major smem tile
 //   UMMA issuer    tcgen05.mma kind::f16 (A from TMEM, B from smem descriptor), 4 x K=16 per chunk, fp32
-//                  128 x BN accumulator in TMEM; bf16 tail tiles (TMA straight into the operand ring, both
-//                  operands from smem) accumulate into the same tile
+//                  128 x BN accumulator in TMEM; the bf16 tail accumulates into the same tile (its weight
+//                  tile by TMA straight into the operand slot, its activation rows raw ring -> TMEM)
 //   8 epilogue warps  tcgen05.ld, * rs[m] * cs[n], + bias, bf16, 16-byte stores; two accumulators
 //                  alternate so the next tile's UMMAs overlap the epilogue
 #include <cuda.h>
@@ -52,7 +52,7 @@ constexpr int GF_EXP_STAGES = 3;
 #define GF_CPS_DEF 4
 #endif
 #ifndef GF_RAW_DEF
-#define GF_RAW_DEF 2
+#define GF_RAW_DEF 3
 #endif
 constexpr int GF_RAW_STAGES = GF_RAW_DEF;
 constexpr int GF_CPS = GF_CPS_DEF;   // chunks per raw stage: 128 bytes of codes per row and stage
@@ -66,9 +66,8 @@ template <int BN> struct GfCfg {
   static constexpr int GROUP_WARPS = (4 + BN / 32) / 2;    // 4 (BN = 128) / 5 (BN = 192)
   static constexpr int CONV_WARPS = 2 * GROUP_WARPS;
   static constexpr int THREADS = (GF_EPI_WARPS + 2 + CONV_WARPS) * 32;
-  static constexpr int A_EXP = 128 * 128;                  // bf16 tail tile of the activations (tail stages only)
   static constexpr int B_EXP = BN * 128;                   // BN rows x 64 halves
-  static constexpr int EXP_STAGE = A_EXP + B_EXP;
+  static constexpr int EXP_STAGE = B_EXP;                  // only the weight operand is staged in shared memory
   static constexpr int RAW_A = 128 * 32 * GF_CPS;
   static constexpr int RAW_B = BN * 32 * GF_CPS;
   static constexpr int OFF_C = RAW_A + RAW_B;               // [chunk][ROWS] 8-byte records, same row order
@@ -78,6 +77,7 @@ template <int BN> struct GfCfg {
   static constexpr int TMEM_COLS = 512;                     // 2 accumulators + 3 x 32 columns of A
   static_assert(2 * BN + GF_EXP_STAGES * 32 <= 512, "tensor memory");
   static_assert((4 + BN / 32) % 2 == 0, "units must split evenly over the two groups");
+  static_assert(RAW_A == 128 * 128, "a raw stage must hold one 128 x 64 bf16 tail tile of the activations");
 };
 
 struct GfMaps {
@@ -203,6 +203,15 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           issued |= 1u << r.s;
           r.next();
         }
+        // tail: the activations' bf16 tile travels through the raw ring like a chunk (its rows go on to TMEM)
+        for (int st = 0; st < n_tail && ok; ++st) {
+          if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t bar = rawf_bar(r.s);
+          mbar_expect_tx(bar, (uint32_t)Cfg::RAW_A);
+          tma_load_2d(raw_base + r.s * Cfg::RAW_STAGE, &tm.xt, bar, st * 64, m0);
+          issued |= 1u << r.s;
+          r.next();
+        }
       }
       if (!ok) {
         const long long t0 = clock64();
@@ -268,7 +277,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           const int es = exp_slot(q);
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sB = exp_base + es * Cfg::EXP_STAGE + Cfg::A_EXP;
+          const uint32_t sB = exp_base + es * Cfg::EXP_STAGE;
           if (first_is_act) {      // activation rows -> TMEM
             tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y1);
           } else {                 // (fifth warp) weight rows -> smem
@@ -301,25 +310,40 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         if (lane == 0) mbar_arrive(rawe_bar(r.s));
         r.next();
       }
-      // tail: bf16 tiles (already divided by rs / cs) go by TMA straight into the operand ring, issued by
-      // the group that owns the stage (the converters are the ones walking that ring in order).
+      // tail: the weights' bf16 tile (already divided by cs) goes by TMA straight into the stage's slot,
+      // issued by the group that owns the stage once the slot is free; the activations' tile (divided by
+      // rs) arrives in the raw ring and its rows are copied to TMEM like an expanded chunk.
       for (int st = 0; st < n_tail && ok; ++st, ++q) {
-        if ((q & 1) != grp) continue;
-        const int es = exp_slot(q);
-        if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-        if (lane == 0) {
+        if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
+        if ((q & 1) == grp) {
+          const int es = exp_slot(q);
+          if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          tc_fence_after();
           const uint32_t bar = expf_bar(es);
-          if (gw == 0) {
-            const uint32_t sA = exp_base + es * Cfg::EXP_STAGE;
-            mbar_expect_tx(bar, Cfg::EXP_STAGE);
-            tma_load_2d(sA, &tm.xt, bar, st * 64, m0);
-            tma_load_2d(sA + Cfg::A_EXP, &tm.wt, bar, st * 64, n0);
+          if (gw == 0 && lane == 0) {
+            mbar_expect_tx_only(bar, Cfg::B_EXP);
+            tma_load_2d(exp_base + es * Cfg::EXP_STAGE, &tm.wt, bar, st * 64, n0);
             issued_q[0] = issued_q[1];
             issued_q[1] = q;
-          } else {
-            mbar_arrive(bar);
           }
+          if (first_is_act) {
+            const uint32_t rb = raw_base + r.s * Cfg::RAW_STAGE + rowA * 128;
+            uint32_t y[32];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint4 v = gf_lds128(rb + (uint32_t)((i ^ (rowA & 7)) << 4));
+              y[4 * i] = v.x; y[4 * i + 1] = v.y; y[4 * i + 2] = v.z; y[4 * i + 3] = v.w;
+            }
+            tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y);
+            tmem_wait_st();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(rawe_bar(r.s));
+        r.next();
       }
     }
     if (!ok && gw == 0 && lane == 0) {
@@ -347,17 +371,11 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           const int es = q % GF_EXP_STAGES;
           if (!mbar_wait_hot(expf_bar(es), (uint32_t)((q / GF_EXP_STAGES) & 1), abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = exp_base + es * Cfg::EXP_STAGE;
-          const uint64_t bdesc = smem_desc_sw128(sA + Cfg::A_EXP);
-          if (st < n_main) {
-            const uint32_t a_tmem = tmem_base + Cfg::TMEM_A0 + es * 32;
+          const uint64_t bdesc = smem_desc_sw128(exp_base + es * Cfg::EXP_STAGE);
+          const uint32_t a_tmem = tmem_base + Cfg::TMEM_A0 + es * 32;
+          const uint32_t idesc = st < n_main ? idesc_h : idesc_bf;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) umma_f16_ts(d, a_tmem + 8 * j, bdesc + 2 * j, idesc_h, (st > 0 || j > 0) ? 1u : 0u);
-          } else {
-            const uint64_t adesc = smem_desc_sw128(sA);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) umma_f16(d, adesc + 2 * j, bdesc + 2 * j, idesc_bf, (st > 0 || j > 0) ? 1u : 0u);
-          }
+          for (int j = 0; j < 4; ++j) umma_f16_ts(d, a_tmem + 8 * j, bdesc + 2 * j, idesc, (st > 0 || j > 0) ? 1u : 0u);
           umma_commit(expe_bar(es));
         }
         if (ok) { umma_commit(accf_bar(buf)); ++use; }

@@ -109,3 +109,26 @@ def test_pixart_block_nvfp4_layers_run():
     y = step(x)
     ops.check_status()
     assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("quant", ["int4", "nvfp4"])
+def test_full_size_rows_are_independent(quant):
+    """BASELINE config 1 size (M = 8 x 4096 rows): a quantised linear treats every token on its own, so
+    (1) the forward of the whole batch equals, bit for bit, the forwards of its shards put together (the
+    property data-parallel sharding relies on), and (2) permuting the rows permutes the output."""
+    from dirotq_b200 import dit, ops
+    from dirotq_b200.synth import synth_activations
+    M, D = 32768, 1152
+    w = dit.make_wrapped_linear(dit.LayerDef("attn1.to_q", D, D, tail=64), quant, 4242, "cuda")
+    x = synth_activations(M, D, torch.Generator().manual_seed(42)).cuda()
+    y = w(x.reshape(8, 4096, D)).reshape(M, D)
+    ops.check_status()
+    assert torch.isfinite(y.float()).all()
+    parts = [w(x[i * 4096:(i + 1) * 4096].reshape(1, 4096, D)).reshape(4096, D) for i in range(8)]
+    assert torch.equal(torch.cat(parts), y)
+    odd = torch.cat([w(x[:12345].reshape(1, 12345, D)).reshape(12345, D),
+                     w(x[12345:].reshape(1, M - 12345, D)).reshape(M - 12345, D)])      # ragged split
+    assert torch.equal(odd, y)
+    perm = torch.randperm(M, generator=torch.Generator().manual_seed(1)).cuda()
+    assert torch.equal(w(x[perm].reshape(1, M, D)).reshape(M, D), y[perm])
+    ops.check_status()
