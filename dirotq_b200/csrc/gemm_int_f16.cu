@@ -34,8 +34,8 @@
 //   UMMA issuer    tcgen05.mma kind::f16 (A from TMEM, B from smem descriptor), 4 x K=16 per chunk, fp32
 //                  128 x BN accumulator in TMEM; the bf16 tail accumulates into the same tile (its weight
 //                  tile by TMA straight into the operand slot, its activation rows raw ring -> TMEM)
-//   8 epilogue warps  tcgen05.ld, * rs[m] * cs[n], + bias, bf16, 16-byte stores; two accumulators
-//                  alternate so the next tile's UMMAs overlap the epilogue
+//   8 epilogue warps  tcgen05.ld, * rs[m] * cs[n], + bias, bf16 -> 32 x 32 staging patches -> TMA stores; two
+//                  accumulators alternate so the next tile's UMMAs overlap the epilogue
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -47,14 +47,15 @@
 
 namespace dq {
 
-constexpr int GF_EXP_STAGES = 3;
 #ifndef GF_CPS_DEF
 #define GF_CPS_DEF 4
 #endif
 #ifndef GF_RAW_DEF
-#define GF_RAW_DEF 3
+#define GF_RAW_DEF 2
 #endif
-constexpr int GF_RAW_STAGES = GF_RAW_DEF;
+#ifndef GF_EXP_MAX
+#define GF_EXP_MAX 8
+#endif
 constexpr int GF_CPS = GF_CPS_DEF;   // chunks per raw stage: 128 bytes of codes per row and stage
 constexpr int GF_EPI_WARPS = 8;
 
@@ -72,16 +73,23 @@ template <int BN> struct GfCfg {
   static constexpr int RAW_B = BN * 32 * GF_CPS;
   static constexpr int OFF_C = RAW_A + RAW_B;               // [chunk][ROWS] 8-byte records, same row order
   static constexpr int RAW_STAGE = OFF_C + GF_CPS * ROWS * 8;
-  static constexpr int SMEM_BYTES = GF_EXP_STAGES * EXP_STAGE + GF_RAW_STAGES * RAW_STAGE + 1024 + 256;
+  // Operand stages in flight: every tensor-memory column the two accumulators leave free holds activations
+  // (32 columns per 64-wide chunk).  The hand-off latency between converters and the UMMA issuer is paid once
+  // per trip around this ring, so its depth, not the arithmetic, sets the pace when it is shallow.
+  static constexpr int EXP_STAGES = ((512 - 2 * BN) / 32 < GF_EXP_MAX) ? (512 - 2 * BN) / 32 : GF_EXP_MAX;
+  static constexpr int RAW_STAGES = GF_RAW_DEF;
+  static constexpr int STG_BYTES = GF_EPI_WARPS * 2048;     // per epilogue warp: 32 rows x 32 bf16 output staging
+  static constexpr int SMEM_BYTES = EXP_STAGES * EXP_STAGE + RAW_STAGES * RAW_STAGE + STG_BYTES + 1024 + 256;
   static constexpr int TMEM_A0 = 2 * BN;                    // first column of the activation operand slots
-  static constexpr int TMEM_COLS = 512;                     // 2 accumulators + 3 x 32 columns of A
-  static_assert(2 * BN + GF_EXP_STAGES * 32 <= 512, "tensor memory");
+  static constexpr int TMEM_COLS = 512;                     // 2 accumulators + EXP_STAGES x 32 columns of A
+  static_assert(2 * BN + EXP_STAGES * 32 <= 512, "tensor memory");
+  static_assert(SMEM_BYTES <= 232448, "shared memory");
   static_assert((4 + BN / 32) % 2 == 0, "units must split evenly over the two groups");
   static_assert(RAW_A == 128 * 128, "a raw stage must hold one 128 x 64 bf16 tail tile of the activations");
 };
 
 struct GfMaps {
-  CUtensorMap xq, wq, xt, wt;
+  CUtensorMap xq, wq, xt, wt, y;
 };
 
 template <int N> struct GfRing {
@@ -135,10 +143,12 @@ template <int BN, bool ASYM>
 __global__ void __launch_bounds__(GfCfg<BN>::THREADS, 1)
 gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   using Cfg = GfCfg<BN>;
+  constexpr int GF_EXP_STAGES = Cfg::EXP_STAGES, GF_RAW_STAGES = Cfg::RAW_STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_area = smem + GF_EXP_STAGES * Cfg::EXP_STAGE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw_area + GF_RAW_STAGES * Cfg::RAW_STAGE);
+  uint8_t* stg_area = raw_area + GF_RAW_STAGES * Cfg::RAW_STAGE;       // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_area + Cfg::STG_BYTES);
   constexpr int NB = 2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NB);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -177,7 +187,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... with n fastest, so CTAs running at
   // the same time read the same activation rows through L2.  Rings and the accumulator counter run on
   // across tiles.  Operand stage q of the kernel-wide sequence (chunks and tail stages of all tiles)
-  // lives in slot q % 3; its barrier phase is (q / 3) & 1.
+  // lives in slot q % EXP_STAGES; its barrier phase is (q / EXP_STAGES) & 1.
 
   if (warp == W_TMA) {
     // ------------------------------ TMA producer ---------------------------------------------
@@ -242,8 +252,8 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     int q = 0;
     int issued_q[2] = {-1, -1};
     bool ok = true;
-    auto exp_slot = [](int qq) { return qq % GF_EXP_STAGES; };
-    auto exp_phase = [](int qq) { return (uint32_t)((qq / GF_EXP_STAGES) & 1); };
+    auto exp_slot = [](int qq) { return qq % Cfg::EXP_STAGES; };
+    auto exp_phase = [](int qq) { return (uint32_t)((qq / Cfg::EXP_STAGES) & 1); };
     // one row x one chunk: two 16-byte pieces of the swizzled raw row + the row's record
     auto load_row = [&](uint32_t sraw, int row, int jc, uint4& p0, uint4& p1, uint2& k) {
       const uint32_t rb = sraw + row * (32 * GF_CPS);
@@ -383,10 +393,17 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     }
   } else {
     // ------------------------------ epilogue: 8 warps -----------------------------------------
-    // warp w: TMEM lane quarter w & 3 (32 rows), column half w >> 2 (BN / 2 columns).
+    // warp w: TMEM lane quarter w & 3 (32 rows), column half w >> 2 (BN / 2 columns), 32 columns at a time:
+    // tcgen05.ld -> * rs[m] * cs[n] + bias -> bf16 -> the warp's 32 x 32 staging patch in shared memory
+    // (64-byte rows, 64-byte swizzle: conflict-free) -> one TMA store, which clips the patch at the edges
+    // of y.  A row-per-thread store straight to global memory would put 32 separate 16-byte segments per
+    // instruction through the load/store unit that the converter warps depend on.
     const int q = warp & 3, ch = warp >> 2;
     const int trow = q * 32 + lane;
     constexpr int CW = BN / 2;
+    const uint32_t stg = smem_u32(stg_area) + warp * 2048;
+    const uint32_t stg_row = stg + lane * 64;
+    const int stg_sw = (lane >> 1) & 3;
     int use = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -410,38 +427,45 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           if (lane == 0) mbar_arrive(acce_bar(buf));
         }
         const int64_t col0 = (int64_t)n0 + ch * CW + g * 32;
-        if (row < a.M) {
-          __nv_bfloat16* yr = a.y + row * a.N + col0;
+        if (col0 >= a.N) continue;                     // warp-uniform: nothing of this patch lies inside y
+        if (lane == 0) bulk_wait_read0();              // the previous patch has left the staging buffer
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (col0 + 8 * i + 8 <= a.N) {
-              const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i));
-              const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i + 4));
-              const float cs8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-              float b[8];
-              if (a.bias) {
-                const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col0 + 8 * i));
-                const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
+        for (int i = 0; i < 4; ++i) {
+          uint32_t w[4] = {0u, 0u, 0u, 0u};
+          if (col0 + 8 * i + 8 <= a.N) {
+            const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i));
+            const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i + 4));
+            const float cs8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float b[8];
+            if (a.bias) {
+              const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col0 + 8 * i));
+              const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
 #pragma unroll
-                for (int e2 = 0; e2 < 4; ++e2) { float2 f = __bfloat1622float2(bh[e2]); b[2 * e2] = f.x; b[2 * e2 + 1] = f.y; }
-              } else {
+              for (int e2 = 0; e2 < 4; ++e2) { float2 f = __bfloat1622float2(bh[e2]); b[2 * e2] = f.x; b[2 * e2 + 1] = f.y; }
+            } else {
 #pragma unroll
-                for (int e2 = 0; e2 < 8; ++e2) b[e2] = 0.f;
-              }
-              uint32_t w[4];
+              for (int e2 = 0; e2 < 8; ++e2) b[e2] = 0.f;
+            }
 #pragma unroll
-              for (int e2 = 0; e2 < 4; ++e2) {
-                const float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2]), rs * cs8[2 * e2], b[2 * e2]);
-                const float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2 + 1]), rs * cs8[2 * e2 + 1], b[2 * e2 + 1]);
-                __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                w[e2] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(yr + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2]), rs * cs8[2 * e2], b[2 * e2]);
+              const float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2 + 1]), rs * cs8[2 * e2 + 1], b[2 * e2 + 1]);
+              __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+              w[e2] = *reinterpret_cast<uint32_t*>(&h);
             }
           }
+          gf_sts128(stg_row + (uint32_t)((i ^ stg_sw) << 4), w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tm.y, stg, (int)col0, m0 + q * 32);
+          bulk_commit_group();
         }
       }
     }
+    if (lane == 0) bulk_wait_all0();                   // the output is in global memory before the CTA retires
   }
   tc_fence_before();
   __syncthreads();
@@ -599,13 +623,19 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
       (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_const) & 15))
     return DIROTQ_E_ALIGN;
-  const int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
+  int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
+#ifdef GF_FORCE_BN
+  BN = GF_FORCE_BN;
+#endif
   GfMaps tm;
   int rc = make_tmap_2d_sw(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
                            (uint64_t)a.x_row_bytes, 32 * GF_CPS, 128, 32 * GF_CPS);
   if (rc) return rc;
   rc = make_tmap_2d_sw(&tm.wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, (uint64_t)a.w_row_bytes, (uint64_t)a.N,
                        (uint64_t)a.w_row_bytes, 32 * GF_CPS, BN, 32 * GF_CPS);
+  if (rc) return rc;
+  rc = make_tmap_2d_sw(&tm.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2,
+                       32, 32, 64);
   if (rc) return rc;
   if (a.kt > 0) {
     rc = make_tmap_2d(&tm.xt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.xt, (uint64_t)a.kt, (uint64_t)a.M, (uint64_t)a.kt_pitch * 2, 128);
