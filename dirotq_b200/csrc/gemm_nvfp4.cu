@@ -22,13 +22,14 @@
 
 namespace dq {
 
-constexpr int GF_STAGES = 6;
+constexpr int GF_STAGES = 5;
 constexpr int GF_TILE_BYTES = 128 * 128;     // 128 rows x 128 bytes (256 E2M1 or 64 bf16 per row)
 constexpr int GF_SF_BYTES = 4 * 512;         // four 64-element k-blocks of scale factors for 128 rows
 constexpr int GF_STAGE_BYTES = 2 * GF_TILE_BYTES + 2 * GF_SF_BYTES;   // 36864
 constexpr int GF_EPI_WARPS = 8;              // two per TMEM lane quarter, 64 output columns each
 constexpr int GF_THREADS = (2 + GF_EPI_WARPS) * 32;
-constexpr int GF_SMEM_BYTES = GF_STAGES * GF_STAGE_BYTES + 1024 + 256;
+constexpr int GF_STG_BYTES = GF_EPI_WARPS * 2048;   // per epilogue warp: 32 rows x 32 bf16 output staging patch
+constexpr int GF_SMEM_BYTES = GF_STAGES * GF_STAGE_BYTES + GF_STG_BYTES + 1024 + 256;
 constexpr uint32_t GF_TMEM_COLS = 512;
 constexpr uint32_t GF_SFA_COL = 256;         // two alternating slots of 16 columns each
 constexpr uint32_t GF_SFB_COL = 320;
@@ -42,10 +43,11 @@ struct GfRing {
 __global__ void __launch_bounds__(GF_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_constant__ CUtensorMap tm_wq,
                   const __grid_constant__ CUtensorMap tm_xt, const __grid_constant__ CUtensorMap tm_wt,
-                  const GemmFp4Args a) {
+                  const __grid_constant__ CUtensorMap tm_y, const GemmFp4Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GF_STAGES * GF_STAGE_BYTES);
+  uint8_t* stg_area = smem + GF_STAGES * GF_STAGE_BYTES;                 // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_area + GF_STG_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GF_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -161,6 +163,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
     }
   } else {
     const int q = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t stg = smem_u32(stg_area) + (warp - 2) * 2048;
     int buf = 0;
     uint32_t aph = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -178,10 +181,21 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acce_bar(buf));      // accumulator is in registers: hand it back early
-      if (row < a.M) {
+      // bf16 results leave through 32 x 32 staging patches (64-byte rows, 64-byte swizzle) and TMA stores,
+      // which clip at the edges of y; a row-per-thread store would issue 32 separate 16-byte segments per
+      // instruction.
+      (void)row;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+      for (int p = 0; p < 2; ++p) {
+        const int64_t pcol = n0 + 32 * p;
+        if (pcol >= a.N) continue;                       // warp-uniform
+        if (lane == 0) bulk_wait_read0();                // the previous patch has left the staging buffer
+        __syncwarp();
+#pragma unroll
+        for (int i4 = 0; i4 < 4; ++i4) {
+          const int i = 4 * p + i4;
           const int64_t col = n0 + 8 * i;
+          uint32_t w[4] = {0u, 0u, 0u, 0u};
           if (col + 8 <= a.N) {
             float b[8];
             if (a.bias) {
@@ -193,20 +207,28 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
 #pragma unroll
               for (int e = 0; e < 8; ++e) b[e] = 0.f;
             }
-            uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               __nv_bfloat162 h = __floats2bfloat162_rn(__fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), a.out_scale, b[2 * e]),
                                                        __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), a.out_scale, b[2 * e + 1]));
               w[e] = *reinterpret_cast<uint32_t*>(&h);
             }
-            *reinterpret_cast<uint4*>(a.y + row * a.N + col) = make_uint4(w[0], w[1], w[2], w[3]);
           }
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                       ::"r"(stg + lane * 64 + (uint32_t)((i4 ^ ((lane >> 1) & 3)) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tm_y, stg, (int)pcol, mb * 128 + q * 32);
+          bulk_commit_group();
         }
       }
       buf ^= 1;
       if (buf == 0) aph ^= 1;
     }
+    if (lane == 0) bulk_wait_all0();                     // the output is in global memory before the CTA retires
   }
   tc_fence_before();
   __syncthreads();
@@ -220,11 +242,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.n_chunks <= 0) return DIROTQ_E_ARG;
-  CUtensorMap txq, twq, txt, twt;
+  CUtensorMap txq, twq, txt, twt, ty;
+  if (a.N % 8) return DIROTQ_E_UNSUPPORTED;
   const uint64_t row_bytes = (uint64_t)a.n_chunks * 32;
   int rc = make_tmap_2d(&txq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, row_bytes, (uint64_t)a.M, row_bytes, 128);
   if (rc) return rc;
   rc = make_tmap_2d(&twq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, row_bytes, (uint64_t)a.N, row_bytes, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d_sw(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2, 32, 32, 64);
   if (rc) return rc;
   if (a.kt > 0) {
     rc = make_tmap_2d(&txt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.xt, (uint64_t)a.kt, (uint64_t)a.M, (uint64_t)a.kt_pitch * 2, 128);
@@ -243,7 +268,7 @@ int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
   }
   const int tiles = (int)((a.M + 127) / 128) * (int)((a.N + 127) / 128);
   const int grid = min(tiles, num_sms());
-  gemm_nvfp4_kernel<<<grid, GF_THREADS, GF_SMEM_BYTES, st>>>(txq, twq, txt, twt, a);
+  gemm_nvfp4_kernel<<<grid, GF_THREADS, GF_SMEM_BYTES, st>>>(txq, twq, txt, twt, ty, a);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
