@@ -48,6 +48,7 @@ SIGNATURES = {
     "dirotq_pack_weight_nvfp4": (C.c_int, [_P, _I64, _I64, _F, _P, _I32, _P, _P, _P]),
     "dirotq_gemm_w4a4_int": (C.c_int, [_I32, _I64, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P, _P,
                                         _P, _P, _P]),
+    "dirotq_hadamard_low": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P]),
     "dirotq_fold_weight_records_bytes": (_SZ, [_I32, _I64]),
     "dirotq_fold_weight_scales_f16": (C.c_int, [_I32, _I64, _P, _P, _I32, _I32, _P, _P, _P, _P]),
     "dirotq_gemm_w4a4_int_f16_workspace_bytes": (_SZ, [_I64, _I32, _I32]),

@@ -84,6 +84,8 @@ class LayerState:
     folded: Optional[ops.FoldedWeightF16] = None     # INT4 activations: constants of the tensor-rate GEMM
     shared: Optional[SharedActivation] = None
     member_id: int = 0
+    hadamard_low_dim: int = 0                        # use_hadamard layers: FWHT over the first channels
+    hadamard_flips: Optional[torch.Tensor] = None
     _c: Optional[LinearC] = None
     _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
 
@@ -119,6 +121,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
     M = x2d.shape[0]
     y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
+    if st.hadamard_low_dim:
+        x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
     ws = st.workspace(M, x2d.device)
     if st.shared is not None:
         if st.shared.lookup(x2d, st.member_id):
@@ -189,20 +193,25 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     explicit: optional dict with the true quantised weight instead of the dequantised
     ``module.weight``: INT {"codes" [N,n_low] int, "scales" [N,G]}, NVFP4 {"nibbles" [N,n_low],
     "scales_e4m3" uint8 [N,n_low/16], "tensor_scale" float}; optional "w_tail" [N, tail_total]."""
-    if getattr(w, "use_hadamard", False):
-        raise NotImplementedError("Hadamard layers (--hadamard-layers) are not implemented by the B200 backend")
     fmt = _act_format(w)
     lay = ops.act_layout(fmt)
     fused = getattr(w, "_unrot_fused", False)
     N, D = w.module.out_features, w.module.in_features
     dev = torch.device(device)
     rot_t = perm = None
+    had_dim, had_flips = 0, None
+    if fused and getattr(w, "use_hadamard", False):
+        # same branch order as the reference forward (rotation, per-head, Hadamard, permutation)
+        if w.rotation is None and w.rotation_per_head is None:
+            had_dim = int(w.hadamard_low_dim)
+            if getattr(w, "hadamard_sign_flips", None) is not None:
+                had_flips = w.hadamard_sign_flips.to(device=dev, dtype=torch.bfloat16).contiguous()
     if fused and w.rotation is not None:
         rot_t = w.rotation.to(device=dev, dtype=torch.float32).t().contiguous().to(torch.bfloat16)
     elif fused and w.rotation_per_head is not None:
         U = w.rotation_per_head.to(device=dev, dtype=torch.float32)
         rot_t = torch.block_diag(*[U[h].t() for h in range(U.shape[0])]).contiguous().to(torch.bfloat16)
-    elif fused and getattr(w, "perm_idx", None) is not None:
+    elif fused and not had_dim and getattr(w, "perm_idx", None) is not None:
         perm = w.perm_idx.to(device=dev, dtype=torch.int64).contiguous()
     have_codes = bool(explicit) and ("codes" in explicit or "nibbles" in explicit)
     have_tail = lay.tail_total == 0 or (bool(explicit) and "w_tail" in explicit)
@@ -250,7 +259,8 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     folded = None
     if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM):
         folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
-    return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded)
+    return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded,
+                      hadamard_low_dim=had_dim, hadamard_flips=had_flips)
 
 
 @dataclass

@@ -215,6 +215,14 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
   return launch_gemm_int(a, static_cast<cudaStream_t>(stream));
 }
 
+int dirotq_hadamard_low(const void* x, int64_t M, int32_t width, int32_t low_dim, const void* sign_flips, void* y,
+                        void* stream) {
+  if (!x || !y || M < 0 || width <= 0) return DIROTQ_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(sign_flips)) & 15)
+    return DIROTQ_E_ALIGN;
+  return launch_hadamard_low(x, M, width, low_dim, sign_flips, y, static_cast<cudaStream_t>(stream));
+}
+
 int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_scales, const void* w_tail,
                                   int32_t tail_total, int32_t tail_pitch, void* w_mult, float* w_colscale,
                                   void* w_tail_out, void* stream) {

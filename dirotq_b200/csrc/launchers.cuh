@@ -147,6 +147,7 @@ int launch_quantize(const QuantArgs& a, cudaStream_t st);
 int launch_pack_int4(const PackIntArgs& a, cudaStream_t st);
 int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st);
 int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, int64_t M, RotArgs a, cudaStream_t st);
+int launch_hadamard_low(const void* x, int64_t M, int D, int n, const void* flips, void* y, cudaStream_t st);
 int num_sms();
 int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64_t K, const void* bias, void* y,
                      int* status, cudaStream_t st);

@@ -139,6 +139,18 @@ def rotate_quantize(x2d: torch.Tensor, rot_t: torch.Tensor, fmt: ActFormat, want
     return (buf, x_rot) if want_x_rot else buf
 
 
+def hadamard_low(x2d: torch.Tensor, low_dim: int, sign_flips: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Hadamard front end: FWHT over the first low_dim channels (after +-1 sign flips), rest copied."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous() and x2d.dim() == 2
+    if sign_flips is not None:
+        assert sign_flips.dtype == torch.bfloat16 and sign_flips.numel() == low_dim and sign_flips.is_contiguous()
+    y = out if out is not None else torch.empty_like(x2d)
+    check(_lib.lib().dirotq_hadamard_low(_ptr(x2d), x2d.shape[0], x2d.shape[1], low_dim, _ptr(sign_flips), _ptr(y),
+                                         _stream()), "dirotq_hadamard_low")
+    return y
+
+
 def rotate(x2d: torch.Tensor, rot_t: torch.Tensor, num_heads: int = 0, head_dim: int = 0) -> torch.Tensor:
     """Rotation only (bf16 tcgen05 GEMM): y = x @ rot_t.T."""
     assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()

@@ -138,6 +138,14 @@ int dirotq_pack_weight_int4(const float* w_low, int64_t N, int64_t n_low, int32_
 int dirotq_pack_weight_nvfp4(const float* w_low, int64_t N, int64_t n_low, float tensor_scale,
                              const uint8_t* scale_in, int32_t w_is_codes, void* codes, void* sf, void* stream);
 
+/* Hadamard front end of layers with use_hadamard (dirotq_fused_unrotation_fast.py:106-128;
+ * utils/hadamard_utils.py:56-80): y[:, :low_dim] = FWHT(x[:, :low_dim] * sign_flips) / sqrt(low_dim) with
+ * fp32 butterflies in the reference's stage order (bit-identical to it), y[:, low_dim:] = x[:, low_dim:].
+ * x, y bf16 [M, width] (y != x); sign_flips bf16 [low_dim] of +-1 or NULL; low_dim a power of two in
+ * [16, 8192].  The quantiser (dirotq_quantize_act / dirotq_linear_forward without rotation) runs on y. */
+int dirotq_hadamard_low(const void* x, int64_t M, int32_t width, int32_t low_dim, const void* sign_flips, void* y,
+                        void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Kernel 2: W4A4 GEMM + bf16 high-precision branch + dequant + bias.  Replaces the inner
  * `self.module(x)` of the fused forward (dirotq_fused_unrotation_fast.py:141) as a real 4-bit GEMM

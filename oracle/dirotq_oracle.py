@@ -249,6 +249,39 @@ class LayerSpec:
     rotation: Optional[torch.Tensor] = None          # [D, D]
     rotation_per_head: Optional[torch.Tensor] = None  # [H, d, d]
     perm_idx: Optional[torch.Tensor] = None
+    hadamard_low_dim: Optional[int] = None            # use_hadamard layers (quant_utils.py:314-316)
+    hadamard_sign_flips: Optional[torch.Tensor] = None
+
+
+def fast_hadamard_transform(x: torch.Tensor) -> torch.Tensor:
+    """Walsh-Hadamard transform along the last (power-of-two) dimension, divided by sqrt(D): butterflies
+    (a + b, a - b) over blocks of size h = 1, 2, 4, ... in that order (utils/hadamard_utils.py:56-80)."""
+    D = x.shape[-1]
+    assert D & (D - 1) == 0
+    lead = x.shape[:-1]
+    h = 1
+    while h < D:
+        x = x.reshape(*lead, D // (2 * h), 2, h)
+        a, b = x[..., 0, :], x[..., 1, :]
+        x = torch.stack([a + b, a - b], dim=-2).reshape(*lead, D)
+        h *= 2
+    return x / (D ** 0.5)
+
+
+def hadamard_low(x: torch.Tensor, low_dim: int, sign_flips: Optional[torch.Tensor], fp32: bool) -> torch.Tensor:
+    """The use_hadamard branch of the forward up to the quantiser (dirotq_fused_unrotation_fast.py:106-125;
+    fp32 variant dirotq_fused_unrotation.py:98-121)."""
+    x_low, x_high = x[..., :low_dim], x[..., low_dim:]
+    if fp32:
+        x_low = x_low.float()
+        if sign_flips is not None:
+            x_low = x_low * sign_flips.float()
+        y = fast_hadamard_transform(x_low)
+        return torch.cat([y, x_high.float()], dim=-1) if x_high.shape[-1] else y
+    if sign_flips is not None:
+        x_low = x_low * sign_flips.to(x.dtype)
+    y = fast_hadamard_transform(x_low.float()).to(x.dtype)
+    return torch.cat([y, x_high], dim=-1) if x_high.shape[-1] else y
 
 
 def quantized_input(x: torch.Tensor, spec: LayerSpec, fp32: bool):
@@ -272,6 +305,10 @@ def quantized_input(x: torch.Tensor, spec: LayerSpec, fp32: bool):
         c2 = QuantCfg(cfg.bits, d_q if d_q > 0 else -1, cfg.sym, cfg.clip_ratio, H * hlen, cfg.quant_dtype)
         r = act_quant(xre, c2)
         return per_head_interleave(r.full, H, d, hlen), r, xre
+    if spec.hadamard_low_dim is not None:
+        x_rot = hadamard_low(x, spec.hadamard_low_dim, spec.hadamard_sign_flips, fp32)
+        r = act_quant(x_rot, cfg)
+        return r.full, r, x_rot
     if spec.perm_idx is not None:
         xp = x[..., spec.perm_idx]
         if fp32:

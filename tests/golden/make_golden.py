@@ -121,6 +121,12 @@ def main(ref_root):
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **to_np(out))
         print("wrote", name, {k: tuple(v.shape) for k, v in out.items() if hasattr(v, "shape")})
 
+    only_had = os.environ.get("GOLDEN_ONLY") == "hadamard"     # add the Hadamard fixtures without rewriting the others
+    _run_case = run_case
+    if only_had:
+        run_case = lambda *a, **k: None
+        build_saved = build
+        build = lambda *a, **k: None
     # 1. hidden rotation, INT4 symmetric g64, k=64 passthrough
     D, N = 192, 96
     cfg = dict(bits=4, groupsize=64, sym=True, high_bits_length=64, quant_dtype="int")
@@ -154,6 +160,40 @@ def main(ref_root):
     rph = torch.stack([random_orthogonal_matrix(d, device="cpu").float() for _ in range(H)])
     cfg = dict(bits=4, groupsize=64, sym=True, high_bits_length=4, quant_dtype="int")
     run_case("perhead_d32_int4_sym", build(H * d, N, 8, rph=rph, H=H, d=d, cfg=cfg), acts(2, 16, H * d, 28))
+
+    # Hadamard layers (use_hadamard: FWHT over the first low_dim channels with sign flips, the rest untouched)
+    from utils.hadamard_utils import generate_sign_flips, fast_hadamard_transform
+    for name, D, low_dim, hl, seed in (("hadamard_int4_sym", 320, 256, 64, 9), ("hadamard_int4_sym_n128", 192, 128, 64, 10)):
+        cfg = dict(bits=4, groupsize=64, sym=True, high_bits_length=hl, quant_dtype="int")
+        torch.manual_seed(seed)
+        lin = nn.Linear(D, N, bias=True).to(torch.bfloat16)
+        w = qu.ActQuantWrapper(lin)
+        w.quantizer.configure(**cfg)
+        w.use_hadamard, w.hadamard_low_dim = True, low_dim
+        w.hadamard_sign_flips = generate_sign_flips(low_dim, seed=42 + seed)
+        holder = nn.ModuleDict({"l": w})
+        qu.rtn_quantize_weights(holder, bits=4, groupsize=64, sym=True)
+        assert w._unrot_fused
+        x = acts(2, 24, D, 30 + seed)
+        out = {"x": x, "weight": w.module.weight.data, "bias": w.module.bias.data,
+               "sign_flips": w.hadamard_sign_flips, "low_dim": np.array([low_dim], dtype=np.int64),
+               "cfg": np.array([4, 64, 1, hl, 0], dtype=np.int64)}
+        flips_saved = w.hadamard_sign_flips
+        with torch.no_grad():
+            w.hadamard_sign_flips = flips_saved.to(torch.bfloat16)
+            out["y_fast"] = fast._fused_forward_fast(w, x)
+            x_low = x[..., :low_dim] * w.hadamard_sign_flips
+            x_rot = torch.cat([fast_hadamard_transform(x_low.float()).to(x.dtype), x[..., low_dim:]], dim=-1)
+            w.quantizer.find_params(x_rot)
+            out["x_rot_fast"] = x_rot
+            out["xq_fast"] = w.quantizer(x_rot)
+            out["scale_fast"] = w.quantizer.scale
+            w.hadamard_sign_flips = flips_saved.float()
+            out["y_slow"] = slow._fused_forward(w, x)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **to_np(out))
+        print("wrote", name, {k: tuple(v.shape) for k, v in out.items() if hasattr(v, "shape")})
+    if os.environ.get("GOLDEN_ONLY") == "hadamard":
+        return
 
     # 7. quantiser-only adversarial inputs (already "rotated"): exact .5 ties after the
     #    bf16 quotient rounding, an all-zero group, a tiny group, negative-only group.

@@ -249,3 +249,38 @@ def test_sibling_layers_share_one_rotate_quantise_pass(quant):
     b = ws[0](x2)
     assert torch.equal(a, b)
     ops.check_status()
+
+
+@pytest.mark.parametrize("name", ["hadamard_int4_sym", "hadamard_int4_sym_n128"])
+def test_hadamard_layers(name):
+    """use_hadamard layers: the FWHT front end is bit-identical to the reference's fp32 butterflies, so the
+    quantised activations and the layer output follow the reference's bf16 forward exactly up to the GEMM's
+    accumulation order."""
+    from dirotq_b200 import ops
+    g = load_golden(name)
+    w = _wrapper_from_golden(g)
+    low_dim = int(g["low_dim"][0])
+    w.use_hadamard, w.hadamard_low_dim, w.hadamard_sign_flips = True, low_dim, g["sign_flips"]
+    x = g["x"].cuda()
+    x_rot = ops.hadamard_low(x.reshape(-1, x.shape[-1]), low_dim, g["sign_flips"].to(torch.bfloat16).cuda())
+    assert torch.equal(x_rot.cpu().view(torch.int16), g["x_rot_fast"].reshape(x_rot.shape).view(torch.int16))
+    y = w(x)
+    ops.check_status()
+    assert w._b200_state.n_lossy_groups == 0
+    yc = y.float().cpu()
+    assert rel_l2(yc, g["y_fast"].float()) <= REL and cosine(yc, g["y_fast"].float()) >= COS
+
+
+@pytest.mark.parametrize("D,low_dim", [(4608, 4096), (12288, 8192), (2048, 2048), (576, 512)])
+def test_hadamard_front_end_model_sizes(D, low_dim):
+    """PixArt ff.net.2 (4608 -> FWHT over 4096) and FLUX-sized widths: bit-identical to the oracle."""
+    from dirotq_b200 import ops
+    from dirotq_b200.synth import synth_activations
+    g = torch.Generator().manual_seed(D)
+    x = synth_activations(300, D, g)
+    flips = (torch.randint(0, 2, (low_dim,), generator=g).float() * 2 - 1).to(torch.bfloat16)
+    y = ops.hadamard_low(x.cuda(), low_dim, flips.cuda()).cpu()
+    ref = O.hadamard_low(x, low_dim, flips, fp32=False)
+    assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
+    y2 = ops.hadamard_low(x.cuda(), low_dim, None).cpu()
+    assert torch.equal(y2.view(torch.int16), O.hadamard_low(x, low_dim, None, fp32=False).view(torch.int16))

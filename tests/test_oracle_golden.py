@@ -7,15 +7,20 @@ from oracle import dirotq_oracle as O
 
 HIDDEN = ["hidden_int4_sym", "hidden_int4_asym", "hidden_int4_pad_notail", "hidden_int8_asym", "hidden_nvfp4"]
 PERHEAD = ["perhead_int4_sym", "perhead_int4_asym", "perhead_d32_int4_sym"]
+HADAMARD = ["hadamard_int4_sym", "hadamard_int4_sym_n128"]
 
 
 def spec_of(g):
     bits, gs, sym, hlen, is_fp4 = [int(v) for v in g["cfg"]]
     cfg = O.QuantCfg(bits, gs, bool(sym), 1.0, hlen, "nvfp4" if is_fp4 else "int")
-    return O.LayerSpec(g["weight"], g["bias"], cfg, g.get("rotation"), g.get("rotation_per_head"))
+    spec = O.LayerSpec(g["weight"], g["bias"], cfg, g.get("rotation"), g.get("rotation_per_head"))
+    if "low_dim" in g:
+        spec.hadamard_low_dim = int(g["low_dim"][0])
+        spec.hadamard_sign_flips = g["sign_flips"]
+    return spec
 
 
-@pytest.mark.parametrize("name", HIDDEN + PERHEAD)
+@pytest.mark.parametrize("name", HIDDEN + PERHEAD + HADAMARD)
 def test_fast_path_bit_exact(name):
     g = load_golden(name)
     spec = spec_of(g)
@@ -29,7 +34,7 @@ def test_fast_path_bit_exact(name):
     assert bits_equal(O.fused_forward(g["x"], spec, fp32=False), g["y_fast"])
 
 
-@pytest.mark.parametrize("name", HIDDEN + PERHEAD)
+@pytest.mark.parametrize("name", HIDDEN + PERHEAD + HADAMARD)
 def test_slow_fp32_path_bit_exact(name):
     g = load_golden(name)
     assert bits_equal(O.fused_forward(g["x"], spec_of(g), fp32=True), g["y_slow"])
