@@ -56,6 +56,9 @@ namespace dq {
 #ifndef GF_EXP_MAX
 #define GF_EXP_MAX 8
 #endif
+#ifndef GF_GROUPS
+#define GF_GROUPS 2
+#endif
 constexpr int GF_CPS = GF_CPS_DEF;   // chunks per raw stage: 128 bytes of codes per row and stage
 constexpr int GF_EPI_WARPS = 8;
 
@@ -65,7 +68,8 @@ constexpr int GF_EPI_WARPS = 8;
 template <int BN> struct GfCfg {
   static constexpr int ROWS = 128 + BN;                    // activation rows, then weight rows
   static constexpr int GROUP_WARPS = (4 + BN / 32) / 2;    // 4 (BN = 128) / 5 (BN = 192)
-  static constexpr int CONV_WARPS = 2 * GROUP_WARPS;
+  static constexpr int GROUPS = GF_GROUPS;
+  static constexpr int CONV_WARPS = GROUPS * GROUP_WARPS;
   static constexpr int THREADS = (GF_EPI_WARPS + 2 + CONV_WARPS) * 32;
   static constexpr int B_EXP = BN * 128;                   // BN rows x 64 halves
   static constexpr int EXP_STAGE = B_EXP;                  // only the weight operand is staged in shared memory
@@ -241,7 +245,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     // (warp index mod 4) and weight rows 32 gw ..; the fifth warp (BN = 192): weight rows 128 .. 191.
     const int cw = warp - (W_TMA + 1);
     constexpr int GW = Cfg::GROUP_WARPS;
-    const int grp = cw >= GW ? 1 : 0;
+    const int grp = cw / GW;
     const int gw = cw - grp * GW;
     const int quarter = warp & 3;
     // combined row index (activation rows 0..127, then weight rows) of this thread's two units
@@ -269,7 +273,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
         const int nv = min(GF_CPS, n_main - c);
         for (int jc = 0; jc < nv; ++jc, ++q) {
-          if ((q & 1) != grp) continue;
+          if (q % Cfg::GROUPS != grp) continue;
           uint4 pa0, pa1, pb0, pb1;
           uint2 ka, kb;
           load_row(sraw, rowA, jc, pa0, pa1, ka);
@@ -325,7 +329,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       // rs) arrives in the raw ring and its rows are copied to TMEM like an expanded chunk.
       for (int st = 0; st < n_tail && ok; ++st, ++q) {
         if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
-        if ((q & 1) == grp) {
+        if (q % Cfg::GROUPS == grp) {
           const int es = exp_slot(q);
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           tc_fence_after();
