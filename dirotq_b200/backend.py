@@ -182,8 +182,8 @@ def _act_format(w) -> ops.ActFormat:
                          tensor_scale=_HW_NVFP4_ACT_SCALE)
 
 
-# INT4-activation layers run the tensor-rate GEMM (4-bit codes expanded to fp16 next to the tensor core).
-# Set to False to route them through the exact-integer kind::i8 kernel instead (W4A8 always uses it).
+# Integer-activation layers (W4A4 and W4A8) run the tensor-rate GEMM (codes expanded to fp16 next to the
+# tensor core).  Set to False to route them through the exact-integer kind::i8 kernel instead.
 INT4_TENSOR_RATE_GEMM = True
 
 
@@ -257,7 +257,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     else:
         bias = None if w.module.bias is None else w.module.bias.data.to(device=dev, dtype=torch.bfloat16).contiguous()
     folded = None
-    if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM):
+    if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM, ops.INT8_ASYM):
         folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
     return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded,
                       hadamard_low_dim=had_dim, hadamard_flips=had_flips)

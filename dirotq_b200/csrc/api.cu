@@ -267,11 +267,11 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
                                   const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
                                   int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
                                   size_t workspace_bytes, int skip_fold, int32_t* status, void* stream) {
-  if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM) return DIROTQ_E_UNSUPPORTED;
+  if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM && a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_codes || !w_mult || !w_colscale || !y || !workspace)
     return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
-  if (a_mode == DIROTQ_INT4_ASYM && !x_zeros) return DIROTQ_E_ARG;
+  if (a_mode != DIROTQ_INT4_SYM && !x_zeros) return DIROTQ_E_ARG;
   if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8)))
     return DIROTQ_E_ARG;
   const uintptr_t al = reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(w_codes) |
@@ -288,7 +288,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   __nv_bfloat16* tail_s = tail_total > 0 ? reinterpret_cast<__nv_bfloat16*>(ws + c.tail) : nullptr;
   if (!skip_fold) {
     int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales),
-                                    a_mode == DIROTQ_INT4_ASYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
+                                    a_mode != DIROTQ_INT4_SYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
                                     n_chunks, M, ld_rows(M), ws + c.rec, reinterpret_cast<float*>(ws + c.rs),
                                     tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
     if (rc) return rc;
@@ -299,7 +299,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   a.N = N;
   a.n_chunks = n_chunks;
   a.xq = static_cast<const uint8_t*>(x_codes);
-  a.x_row_bytes = (int64_t)n_chunks * 32;
+  a.x_row_bytes = (int64_t)n_chunks * (a_mode == DIROTQ_INT8_ASYM ? 64 : 32);
   a.a_const = reinterpret_cast<const uint2*>(ws + c.rec);
   a.rs = reinterpret_cast<const float*>(ws + c.rs);
   a.ldm = f16_ld_act(M);
@@ -362,7 +362,8 @@ struct WsCarve {
   size_t codes, scales, zeros, tail, fold, total;
 };
 static bool uses_f16_gemm(const dirotq_linear* lin, const ActGeom& g) {
-  return lin->w_mult != nullptr && (g.mode == DIROTQ_INT4_SYM || g.mode == DIROTQ_INT4_ASYM);
+  return lin->w_mult != nullptr &&
+         (g.mode == DIROTQ_INT4_SYM || g.mode == DIROTQ_INT4_ASYM || g.mode == DIROTQ_INT8_ASYM);
 }
 static int carve(const dirotq_linear* lin, int64_t M, ActGeom* g, WsCarve* w) {
   int rc = make_geom(&lin->fmt, g);

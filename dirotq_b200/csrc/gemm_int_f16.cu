@@ -65,7 +65,7 @@ constexpr int GF_EPI_WARPS = 8;
 // Conversion work comes in units of 32 rows x one 64-slot chunk (a thread per row).  A chunk of a
 // 128 x BN tile has 4 activation units and BN / 32 weight units; each group has (4 + BN / 32) / 2 warps
 // and every warp takes two units.
-template <int BN> struct GfCfg {
+template <int BN, bool A8 = false> struct GfCfg {
   static constexpr int ROWS = 128 + BN;                    // activation rows, then weight rows
   static constexpr int GROUP_WARPS = (4 + BN / 32) / 2;    // 4 (BN = 128) / 5 (BN = 192)
   static constexpr int GROUPS = GF_GROUPS;
@@ -73,14 +73,17 @@ template <int BN> struct GfCfg {
   static constexpr int THREADS = (GF_EPI_WARPS + 2 + CONV_WARPS) * 32;
   static constexpr int B_EXP = BN * 128;                   // BN rows x 64 halves
   static constexpr int EXP_STAGE = B_EXP;                  // only the weight operand is staged in shared memory
-  static constexpr int RAW_A = 128 * 32 * GF_CPS;
+  static constexpr int RAW_A = 128 * 32 * GF_CPS * (A8 ? 2 : 1);   // 8-bit activation codes: two 128-byte boxes per row
   static constexpr int RAW_B = BN * 32 * GF_CPS;
   static constexpr int OFF_C = RAW_A + RAW_B;               // [chunk][ROWS] 8-byte records, same row order
   static constexpr int RAW_STAGE = OFF_C + GF_CPS * ROWS * 8;
   // Operand stages in flight: every tensor-memory column the two accumulators leave free holds activations
   // (32 columns per 64-wide chunk).  The hand-off latency between converters and the UMMA issuer is paid once
   // per trip around this ring, so its depth, not the arithmetic, sets the pace when it is shallow.
-  static constexpr int EXP_STAGES = ((512 - 2 * BN) / 32 < GF_EXP_MAX) ? (512 - 2 * BN) / 32 : GF_EXP_MAX;
+  static constexpr int EXP_TMEM = (512 - 2 * BN) / 32;
+  static constexpr int EXP_CAP_A8 = BN > 128 ? 3 : 5;       // shared memory: 8-bit codes double the activations' raw bytes
+  static constexpr int EXP_CAP = (A8 && GF_EXP_MAX > EXP_CAP_A8) ? EXP_CAP_A8 : GF_EXP_MAX;
+  static constexpr int EXP_STAGES = EXP_TMEM < EXP_CAP ? EXP_TMEM : EXP_CAP;
   static constexpr int RAW_STAGES = GF_RAW_DEF;
   static constexpr int STG_BYTES = GF_EPI_WARPS * 2048;     // per epilogue warp: 32 rows x 32 bf16 output staging
   static constexpr int SMEM_BYTES = EXP_STAGES * EXP_STAGE + RAW_STAGES * RAW_STAGE + STG_BYTES + 1024 + 256;
@@ -89,7 +92,7 @@ template <int BN> struct GfCfg {
   static_assert(2 * BN + EXP_STAGES * 32 <= 512, "tensor memory");
   static_assert(SMEM_BYTES <= 232448, "shared memory");
   static_assert((4 + BN / 32) % 2 == 0, "units must split evenly over the two groups");
-  static_assert(RAW_A == 128 * 128, "a raw stage must hold one 128 x 64 bf16 tail tile of the activations");
+  static_assert(RAW_A >= 128 * 128 && GF_CPS == 4, "a raw stage must hold one 128 x 64 bf16 tail tile of the activations");
 };
 
 struct GfMaps {
@@ -143,10 +146,12 @@ __device__ __forceinline__ uint32_t hmul2_2m4(uint32_t m) {
   return r;
 }
 
-template <int BN, bool ASYM>
-__global__ void __launch_bounds__(GfCfg<BN>::THREADS, 1)
+// AMODE: 0 = signed 4-bit activation codes, 1 = unsigned 4-bit with zero points, 2 = unsigned 8-bit with zero points
+template <int BN, int AMODE>
+__global__ void __launch_bounds__(GfCfg<BN, AMODE == 2>::THREADS, 1)
 gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
-  using Cfg = GfCfg<BN>;
+  constexpr bool ASYM = AMODE != 0, A8 = AMODE == 2;
+  using Cfg = GfCfg<BN, A8>;
   constexpr int GF_EXP_STAGES = Cfg::EXP_STAGES, GF_RAW_STAGES = Cfg::RAW_STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -206,8 +211,16 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
           const uint32_t bar = rawf_bar(r.s);
           const int nv = min(GF_CPS, n_main - c);
-          mbar_expect_tx(bar, (uint32_t)(Cfg::OFF_C + nv * Cfg::ROWS * 8));
-          tma_load_2d(sb, &tm.xq, bar, c * 32, m0);
+          // 8-bit codes: the second 128-byte box is issued only when it holds a chunk (a box that lies
+          // wholly outside the tensor is never requested; its bytes are not part of the count either)
+          const bool second_box = A8 && nv > 2;
+          mbar_expect_tx(bar, (uint32_t)(Cfg::OFF_C - ((A8 && !second_box) ? 128 * 128 : 0) + nv * Cfg::ROWS * 8));
+          if constexpr (A8) {
+            tma_load_2d(sb, &tm.xq, bar, c * 64, m0);
+            if (second_box) tma_load_2d(sb + 128 * 128, &tm.xq, bar, c * 64 + 128, m0);
+          } else {
+            tma_load_2d(sb, &tm.xq, bar, c * 32, m0);
+          }
           tma_load_2d(sb + Cfg::RAW_A, &tm.wq, bar, c * 32, n0);
           for (int j = 0; j < nv; ++j) {
             const uint32_t sc = sb + Cfg::OFF_C + j * Cfg::ROWS * 8;
@@ -221,7 +234,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         for (int st = 0; st < n_tail && ok; ++st) {
           if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t bar = rawf_bar(r.s);
-          mbar_expect_tx(bar, (uint32_t)Cfg::RAW_A);
+          mbar_expect_tx(bar, 128u * 128u);                    // one 128 x 64 bf16 tile
           tma_load_2d(raw_base + r.s * Cfg::RAW_STAGE, &tm.xt, bar, st * 64, m0);
           issued |= 1u << r.s;
           r.next();
@@ -259,15 +272,17 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     auto exp_slot = [](int qq) { return qq % Cfg::EXP_STAGES; };
     auto exp_phase = [](int qq) { return (uint32_t)((qq / Cfg::EXP_STAGES) & 1); };
     // one row x one chunk: two 16-byte pieces of the swizzled raw row + the row's record
+    // `row` is the combined index (activation rows 0..127, then weight rows); 4-bit rows are 128 bytes per
+    // raw stage; the weight rows start at RAW_A
     auto load_row = [&](uint32_t sraw, int row, int jc, uint4& p0, uint4& p1, uint2& k) {
-      const uint32_t rb = sraw + row * (32 * GF_CPS);
-      const int sw = (GF_CPS == 4) ? (row & 7) : ((row >> 1) & 3);
+      const uint32_t rb = sraw + (row < 128 ? row * 128 : Cfg::RAW_A + (row - 128) * 128);
+      const int sw = row & 7;
       p0 = gf_lds128(rb + (((2 * jc) ^ sw) << 4));
       p1 = gf_lds128(rb + (((2 * jc + 1) ^ sw) << 4));
       k = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + row * 8);
     };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
+      const int n0 = (t % n_tiles_n) * BN;
       for (int c = 0; c < n_main && ok; c += GF_CPS) {
         if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
@@ -276,18 +291,40 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           if (q % Cfg::GROUPS != grp) continue;
           uint4 pa0, pa1, pb0, pb1;
           uint2 ka, kb;
-          load_row(sraw, rowA, jc, pa0, pa1, ka);
-          load_row(sraw, rowB, jc, pb0, pb1, kb);
           // The first unit is expanded into registers before the slot is known to be free, so that only
           // stores (and the second unit) remain on the path between "slot free" and "stage ready".
           uint32_t y1[32];
-          {
+          if (A8 && first_is_act) {
+            // 8-bit codes: 64 bytes of this row = four 16-byte pieces of box jc >> 1.  A byte alone in a zero
+            // half is the subnormal q * 2^-24, so (q - z) * s is one packed FMA again; the values are emitted
+            // in the K order the 4-bit weight expansion produces (see expand_word).
+            const uint32_t rb = sraw + (jc >> 1) * (128 * 128) + rowA * 128;
+            uint4 pq[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) pq[u] = gf_lds128(rb + ((((jc & 1) * 4 + u) ^ (rowA & 7)) << 4));
+            ka = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + rowA * 8);
+            const uint32_t w16[16] = {pq[0].x, pq[0].y, pq[0].z, pq[0].w, pq[1].x, pq[1].y, pq[1].z, pq[1].w,
+                                      pq[2].x, pq[2].y, pq[2].z, pq[2].w, pq[3].x, pq[3].y, pq[3].z, pq[3].w};
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t wl = w16[8 * h + i], wh = w16[8 * h + 4 + i];
+                uint32_t* y = y1 + 16 * h + 4 * i;
+                y[0] = hfma2_u(__byte_perm(wl, 0u, 0x4240), ka.x, ka.y);
+                y[1] = hfma2_u(__byte_perm(wh, 0u, 0x4240), ka.x, ka.y);
+                y[2] = hfma2_u(__byte_perm(wl, 0u, 0x4341), ka.x, ka.y);
+                y[3] = hfma2_u(__byte_perm(wh, 0u, 0x4341), ka.x, ka.y);
+              }
+          } else {
+            load_row(sraw, rowA, jc, pa0, pa1, ka);
             const uint32_t w8[8] = {pa0.x, pa0.y, pa0.z, pa0.w, pa1.x, pa1.y, pa1.z, pa1.w};
             const uint32_t mhi = hmul2_2m4(ka.x);
             const uint32_t xr1 = (first_is_act && ASYM) ? 0u : 0x00080008u;
 #pragma unroll
             for (int i = 0; i < 8; ++i) expand_word(w8[i], xr1, ka.x, mhi, ka.y, y1 + 4 * i);
           }
+          load_row(sraw, rowB, jc, pb0, pb1, kb);
           const int es = exp_slot(q);
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           tc_fence_after();
@@ -592,18 +629,19 @@ int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t l
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
-template <int BN, bool ASYM>
+template <int BN, int AMODE>
 static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st) {
-  auto k = gemm_int_f16_kernel<BN, ASYM>;
+  using Cfg = GfCfg<BN, AMODE == 2>;
+  auto k = gemm_int_f16_kernel<BN, AMODE>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, GfCfg<BN>::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return DIROTQ_E_CUDA;
     attr_set = true;
   }
   const int tiles = (int)((a.N + BN - 1) / BN) * (int)((a.M + 127) / 128);
   const int grid = min(tiles, num_sms());
-  k<<<grid, GfCfg<BN>::THREADS, GfCfg<BN>::SMEM_BYTES, st>>>(tm, a);
+  k<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tm, a);
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
@@ -623,7 +661,7 @@ static int pick_bn_f16(int64_t N) {
 
 int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
-  if (a.a_mode != DIROTQ_INT4_SYM && a.a_mode != DIROTQ_INT4_ASYM) return DIROTQ_E_UNSUPPORTED;
+  if (a.a_mode != DIROTQ_INT4_SYM && a.a_mode != DIROTQ_INT4_ASYM && a.a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
       (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_const) & 15))
     return DIROTQ_E_ALIGN;
@@ -650,10 +688,14 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
     tm.xt = tm.xq;
     tm.wt = tm.wq;
   }
-  const bool asym = a.a_mode == DIROTQ_INT4_ASYM;
-  switch (BN) {
-    case 192: return asym ? launch_gf<192, true>(tm, a, st) : launch_gf<192, false>(tm, a, st);
-    case 128: return asym ? launch_gf<128, true>(tm, a, st) : launch_gf<128, false>(tm, a, st);
+  const int amode = a.a_mode == DIROTQ_INT4_SYM ? 0 : a.a_mode == DIROTQ_INT4_ASYM ? 1 : 2;
+  switch (BN * 4 + amode) {
+    case 192 * 4 + 0: return launch_gf<192, 0>(tm, a, st);
+    case 192 * 4 + 1: return launch_gf<192, 1>(tm, a, st);
+    case 192 * 4 + 2: return launch_gf<192, 2>(tm, a, st);
+    case 128 * 4 + 0: return launch_gf<128, 0>(tm, a, st);
+    case 128 * 4 + 1: return launch_gf<128, 1>(tm, a, st);
+    case 128 * 4 + 2: return launch_gf<128, 2>(tm, a, st);
   }
   return DIROTQ_E_ARG;
 }

@@ -282,7 +282,7 @@ def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeight
                       workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Kernel 2 (INT4, tensor-rate variant): codes expanded to fp16 in shared memory, one fp32 accumulator."""
     lay, M, N = act.layout, act.M, w.N
-    assert act.fmt.mode in (INT4_SYM, INT4_ASYM) and lay.n_chunks == w.n_chunks
+    assert act.fmt.mode in (INT4_SYM, INT4_ASYM, INT8_ASYM) and lay.n_chunks == w.n_chunks
     dev = act.codes.device
     y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     tp = lay.tail_pitch if lay.tail_total > 0 else 0

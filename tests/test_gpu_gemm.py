@@ -122,10 +122,12 @@ def test_nvfp4_gemm(M, N, D, tail):
 @pytest.mark.parametrize("mode,M,N,D,tail", [("sym", 300, 256, 320, 64), ("sym", 1000, 1152, 1152, 64),
                                              ("asym", 520, 384, 1152, 64), ("sym", 260, 128, 256, 0),
                                              ("sym", 200, 136, 160, 0), ("asym", 130, 512, 256, 8),
-                                             ("sym", 2048, 3072, 3072, 384), ("sym", 700, 4608, 1152, 64)])
+                                             ("sym", 2048, 3072, 3072, 384), ("sym", 700, 4608, 1152, 64),
+                                             ("int8", 520, 384, 1152, 64), ("int8", 300, 256, 320, 0),
+                                             ("int8", 1000, 2240, 2240, 320), ("int8", 200, 136, 160, 0)])
 def test_int4_f16_gemm_hidden(mode, M, N, D, tail):
     from dirotq_b200 import ops
-    m = {"sym": ops.INT4_SYM, "asym": ops.INT4_ASYM}[mode]
+    m = {"sym": ops.INT4_SYM, "asym": ops.INT4_ASYM, "int8": ops.INT8_ASYM}[mode]
     fmt = ops.ActFormat(m, D, tail_len=tail)
     x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 21)
     lay = act.layout
@@ -141,10 +143,10 @@ def test_int4_f16_gemm_hidden(mode, M, N, D, tail):
     assert rel_l2(y.float().cpu(), y_int.float().cpu()) < 3e-3
 
 
-@pytest.mark.parametrize("H,d,hlen", [(16, 72, 9), (6, 32, 4), (4, 128, 16)])
-def test_int4_f16_gemm_per_head(H, d, hlen):
+@pytest.mark.parametrize("H,d,hlen,mode", [(16, 72, 9, "sym"), (6, 32, 4, "sym"), (4, 128, 16, "sym"), (6, 32, 4, "int8")])
+def test_int4_f16_gemm_per_head(H, d, hlen, mode):
     from dirotq_b200 import ops
-    fmt = ops.ActFormat(ops.INT4_SYM, H * d, tail_len=hlen, num_heads=H, head_dim=d)
+    fmt = ops.ActFormat(ops.INT8_ASYM if mode == "int8" else ops.INT4_SYM, H * d, tail_len=hlen, num_heads=H, head_dim=d)
     M, N = 390, 256
     x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 22)
     lay = act.layout
@@ -152,7 +154,7 @@ def test_int4_f16_gemm_per_head(H, d, hlen):
     folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
     y = ops.gemm_w4a4_int_f16(act, pk, folded, bias.cuda())
     ops.check_status()
-    y_ref, _ = _oracle_int(dec, lay, qw, sw, w_tail, bias, False)
+    y_ref, _ = _oracle_int(dec, lay, qw, sw, w_tail, bias, mode == "int8")
     assert rel_l2(y.float().cpu(), y_ref) < 3e-3
 
 
