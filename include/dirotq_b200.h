@@ -163,8 +163,8 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
                          int32_t tail_pitch, const void* bias, void* y, int32_t* acc_dump, int32_t* status,
                          void* stream);
 
-/* INT4 at tensor rate (tcgen05 kind::f16): the same product as dirotq_gemm_w4a4_int for 4-bit
- * activations, computed the way the reference's own linear computes it -- a 16-bit GEMM with fp32
+/* Integer activations at tensor rate (tcgen05 kind::f16): the same product as dirotq_gemm_w4a4_int for
+ * 4-bit and 8-bit activation codes, computed the way the reference's own linear computes it -- a 16-bit GEMM with fp32
  * accumulation over the dequantised values s*(q-z) and s_w*q_w (dirotq_fused_unrotation_fast.py:141)
  * -- while both operands stay 4-bit in memory: codes are expanded to fp16 between shared memory and
  * the tensor core, one accumulator runs over the whole K, and nothing is drained per chunk.
@@ -175,7 +175,7 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
  *   w_mult: dirotq_fold_weight_records_bytes(n_chunks, N) bytes of 8-byte per-(chunk, channel)
  *   records (fp16 pairs: scale * 2^24 and -8 * scale, each divided by the channel's power of two), w_colscale fp32 [N]; w_tail bf16 [N, tail_pitch] -> w_tail_out = w_tail / colscale
  *   (may be NULL when tail_total == 0).
- * dirotq_gemm_w4a4_int_f16: a_mode DIROTQ_INT4_SYM or DIROTQ_INT4_ASYM; workspace of
+ * dirotq_gemm_w4a4_int_f16: a_mode DIROTQ_INT4_SYM, DIROTQ_INT4_ASYM or DIROTQ_INT8_ASYM; workspace of
  *   dirotq_gemm_w4a4_int_f16_workspace_bytes(M, n_chunks, tail_pitch) bytes, 256-byte aligned
  *   (per-call activation multipliers and the scaled copy of the tail).
  */
@@ -223,7 +223,7 @@ typedef struct dirotq_linear {
   const void* w_tail;       /* bf16 [N, tail_pitch] (NVFP4: divided by out_scale) */
   const void* bias;         /* bf16 [N] or NULL */
   float w_tensor_scale;     /* NVFP4 only */
-  /* INT4 activations only, all three from dirotq_fold_weight_scales_f16.  When w_mult is set the
+  /* Integer activations only, all three from dirotq_fold_weight_scales_f16.  When w_mult is set the
    * forward runs dirotq_gemm_w4a4_int_f16; when NULL, the exact-integer dirotq_gemm_w4a4_int. */
   const void* w_mult;
   const float* w_colscale;
