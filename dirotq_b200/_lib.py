@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libdirotq_b200.so")
+# DIROTQ_B200_LIB selects another build of the same ABI (A/B measurements)
+LIB_PATH = os.environ.get("DIROTQ_B200_LIB") or os.path.join(_HERE, "libdirotq_b200.so")
 
 
 class ActFormatC(C.Structure):

@@ -185,6 +185,8 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_launch_dependents();
+  pdl_wait();                       // the kernels that produced the codes / records have completed
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t exp_base = smem_u32(smem);
   const uint32_t raw_base = smem_u32(raw_area);
@@ -539,6 +541,8 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
                    const __nv_bfloat16* __restrict__ tail, __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
   __shared__ float part_max[4][64];
   __shared__ float inv_s[64];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lr = threadIdx.x & 63, part = threadIdx.x >> 6;
   const int64_t r0 = (int64_t)blockIdx.x * 64;
   const int64_t r = r0 + lr;
@@ -615,9 +619,9 @@ int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n
                            int kt_pitch, cudaStream_t st) {
   if (M <= 0) return DIROTQ_OK;
   const int64_t ld_rec = f16_ld_act(M);
-  fold_scales_kernel<__nv_bfloat16><<<(unsigned)(ld_rec / 64), 256, 0, st>>>(
-      s, z, n_chunks, M, ldm, reinterpret_cast<uint2*>(rec), ld_rec, rs, tail, tail_out, kt_pitch);
-  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  return launch_pdl(fold_scales_kernel<__nv_bfloat16>, dim3((unsigned)(ld_rec / 64)), dim3(256), 0, st, s, z, n_chunks, M,
+                    ldm, reinterpret_cast<uint2*>(rec), ld_rec, rs, tail, tail_out, kt_pitch) == cudaSuccess
+             ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* rec, float* cs,
@@ -641,8 +645,7 @@ static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st)
   }
   const int tiles = (int)((a.N + BN - 1) / BN) * (int)((a.M + 127) / 128);
   const int grid = min(tiles, num_sms());
-  k<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tm, a);
-  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  return launch_pdl(k, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tm, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 // Column-tile width: the candidate that wastes the fewest padded columns; ties go to the wider tile

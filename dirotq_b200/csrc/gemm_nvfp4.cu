@@ -71,6 +71,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_launch_dependents();
+  pdl_wait();                       // the kernel that produced the codes has completed
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t smem_base = smem_u32(smem);
 
@@ -268,8 +270,8 @@ int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
   }
   const int tiles = (int)((a.M + 127) / 128) * (int)((a.N + 127) / 128);
   const int grid = min(tiles, num_sms());
-  gemm_nvfp4_kernel<<<grid, GF_THREADS, GF_SMEM_BYTES, st>>>(txq, twq, txt, twt, ty, a);
-  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  return launch_pdl(gemm_nvfp4_kernel, dim3(grid), dim3(GF_THREADS), GF_SMEM_BYTES, st, txq, twq, txt, twt, ty, a) == cudaSuccess
+             ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 }  // namespace dq

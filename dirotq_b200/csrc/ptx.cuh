@@ -87,6 +87,13 @@ __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, vol
   return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start
+// (and run its prologue: barrier init, TMEM allocation, descriptor prefetch) while the previous kernel of the
+// stream is still finishing.  pdl_wait() returns once that kernel has completed and its writes are visible;
+// nothing may touch global memory before it.  pdl_launch_dependents() lets the NEXT kernel start early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // generic-proxy writes to smem -> visible to the async proxy (UMMA / TMA reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -420,6 +420,8 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_launch_dependents();
+  pdl_wait();                       // whatever produced x (and last used the output buffers) has completed
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = a.m_tiles * a.n_tiles;
   const uint32_t smem_base = smem_u32(smem);
@@ -541,8 +543,7 @@ static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs
     attr_set = true;
   }
   const int grid = min(a.m_tiles * a.n_tiles, num_sms());
-  k<<<grid, RQ_THREADS, RQ_SMEM_BYTES, st>>>(tx, tu, a);
-  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  return launch_pdl(k, dim3(grid), dim3(RQ_THREADS), RQ_SMEM_BYTES, st, tx, tu, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 // Picks the N tile: hidden layouts want a multiple of 64 with the least padding of D; per-head
