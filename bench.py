@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--flux-ffn", default="tp", choices=["tp", "dp"],
                     help="flux_int4 at N > 1: FFN pairs tensor-parallel (all-gather + reduce-scatter) or row-sharded")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fuse-gelu", action="store_true",
+                    help="keep the GELU between the FFN linears as a separate PyTorch kernel")
     ap.add_argument("--exact-int", action="store_true",
                     help="INT4 layers through the exact-integer kind::i8 GEMM instead of the tensor-rate fp16 one")
     ap.add_argument("--profile-case", action="store_true",
@@ -223,6 +225,7 @@ def run_ours(args):
             step = FluxLinearStep(world, rank, dev, batch=batch, n_double=n_double, n_single=2 * n_double,
                                   ffn=args.flux_ffn, quant=quant)
             backend.preconvert_rotations_to_device(step.layers, dev)
+            n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else step.fuse_gelu()
             for lyr in step._flat:                   # the packed device state is all the forward needs
                 lyr._b200_explicit = None
                 lyr.rotation = lyr.rotation_per_head = None
@@ -241,6 +244,7 @@ def run_ours(args):
             D, out_f = block[0].in_f, block[-1].out_f
             step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
             backend.preconvert_rotations_to_device(step, dev)
+            n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else backend.fuse_gelu_modules(step)
             lin_ops, rot_ops = step.ops_per_step(M)
             # step input: synthetic activations with the config-0 distribution, in PINNED host memory
             x_host = synth_activations(M, D, g).reshape(batch, tokens, D).pin_memory()
@@ -314,6 +318,8 @@ def run_ours(args):
             "config": {"workload": desc, "blocks": n_blocks, "rows_per_gpu": M,
                        "global_batch": batch if is_flux else batch * world,
                        "parallelism": (f"rows/{world} + ffn-{step.ffn}" if is_flux else f"dp{world}"),
+                       "gelu": (f"fused into the up-projection GEMM epilogue ({n_fused} layers)" if n_fused
+                                else "separate PyTorch kernel"),
                        "l2": l2_note,
                        "linear_gflop_per_step_per_gpu": lin_ops / 1e9, "rotation_gflop_per_step_per_gpu": rot_ops / 1e9},
             "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,

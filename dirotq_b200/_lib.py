@@ -27,7 +27,7 @@ class LinearC(C.Structure):
     _fields_ = [("fmt", ActFormatC), ("out_features", C.c_int64), ("rot_t", C.c_void_p), ("perm_idx", C.c_void_p),
                 ("w_codes", C.c_void_p), ("w_scales", C.c_void_p), ("w_sum", C.c_void_p), ("w_tail", C.c_void_p),
                 ("bias", C.c_void_p), ("w_tensor_scale", C.c_float), ("w_mult", C.c_void_p),
-                ("w_colscale", C.c_void_p), ("w_tail_f16", C.c_void_p)]
+                ("w_colscale", C.c_void_p), ("w_tail_f16", C.c_void_p), ("epilogue_act", C.c_int32)]
 
 
 _P, _I64, _I32, _F, _SZ = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_size_t
@@ -80,7 +80,7 @@ def lib():
             fn = getattr(l, name)       # AttributeError if the library does not export it
             fn.restype = res
             fn.argtypes = args
-        if l.dirotq_abi_version() != 2:
+        if l.dirotq_abi_version() != 3:
             raise RuntimeError("libdirotq_b200.so ABI version mismatch")
         _lib = l
     return _lib

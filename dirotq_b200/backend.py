@@ -84,6 +84,7 @@ class LayerState:
     folded: Optional[ops.FoldedWeightF16] = None     # INT4 activations: constants of the tensor-rate GEMM
     shared: Optional[SharedActivation] = None
     member_id: int = 0
+    epilogue_act: int = 0                            # 1: GELU (tanh form) fused into the GEMM epilogue
     hadamard_low_dim: int = 0                        # use_hadamard layers: FWHT over the first channels
     hadamard_flips: Optional[torch.Tensor] = None
     _c: Optional[LinearC] = None
@@ -95,7 +96,8 @@ class LayerState:
             f = self.folded
             self._c = LinearC(self.fmt.c(), self.out_features, p(self.rot_t), p(self.perm_idx), p(self.w_codes),
                               p(self.w_scales), p(self.w_sum), p(self.w_tail), p(self.bias), self.w_tensor_scale,
-                              p(f.mult if f else None), p(f.colscale if f else None), p(f.tail if f else None))
+                              p(f.mult if f else None), p(f.colscale if f else None), p(f.tail if f else None),
+                              int(self.epilogue_act))
         return self._c
 
     def workspace(self, M: int, device) -> torch.Tensor:
@@ -354,6 +356,32 @@ def share_sibling_activations(transformer, classes=None) -> int:
             m._ws = {}
         n_groups += 1
     return n_groups
+
+
+def fuse_gelu_modules(transformer, classes=None) -> int:
+    """Fuse the activation that follows a wrapped linear into its GEMM epilogue.
+
+    Looks for modules shaped like diffusers' GELU feed-forward head (attributes `proj` -- a prepared wrapped
+    linear -- and `approximate == "tanh"`; forward = gelu(proj(x))), marks the linear to apply GELU (tanh
+    form) on its bf16-rounded output inside the GEMM epilogue, and replaces the module's forward by a plain
+    call of `proj`.  One full read + write pass over the [M, 4 * hidden] tensor disappears per block.
+    Call after preconvert_rotations_to_device.  Returns the number of fused modules."""
+    classes = tuple(classes or _wrapper_classes())
+    n = 0
+    for _, mod in transformer.named_modules():
+        proj = getattr(mod, "proj", None)
+        if not isinstance(proj, classes) or getattr(mod, "approximate", None) != "tanh":
+            continue
+        st = getattr(proj, "_b200_state", None)
+        if st is None or getattr(mod, "_b200_gelu_fused", False):
+            continue
+        if st.folded is None and st.fmt.mode != ops.NVFP4_HW:
+            continue                      # exact-integer route: no fused activation
+        st.epilogue_act, st._c = 1, None
+        object.__setattr__(mod, "_b200_gelu_fused", True)
+        mod.forward = (lambda p: (lambda hidden_states, *a, **k: p(hidden_states)))(proj)
+        n += 1
+    return n
 
 
 def _wrapper_classes():

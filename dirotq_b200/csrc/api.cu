@@ -266,7 +266,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
                                   const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
                                   const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
                                   int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
-                                  size_t workspace_bytes, int skip_fold, int32_t* status, void* stream) {
+                                  size_t workspace_bytes, int skip_fold, int act, int32_t* status, void* stream) {
   if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM && a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_codes || !w_mult || !w_colscale || !y || !workspace)
     return DIROTQ_E_ARG;
@@ -316,6 +316,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   a.y = static_cast<__nv_bfloat16*>(y);
   a.status = status;
   a.force_bn = 0;
+  a.act = act;
   return launch_gemm_int_f16(a, st);
 }
 
@@ -325,14 +326,14 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
                              int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
                              size_t workspace_bytes, int32_t* status, void* stream) {
   return gemm_w4a4_int_f16_impl(a_mode, M, N, n_chunks, x_codes, x_scales, x_zeros, w_codes, w_mult, w_colscale, x_tail,
-                                w_tail_scaled, tail_total, tail_pitch, bias, y, workspace, workspace_bytes, 0, status,
+                                w_tail_scaled, tail_total, tail_pitch, bias, y, workspace, workspace_bytes, 0, 0, status,
                                 stream);
 }
 
-int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
-                           const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
-                           const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
-                           void* y, int32_t* status, void* stream) {
+static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
+                                const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
+                                const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
+                                void* y, int act, int32_t* status, void* stream) {
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_sf || !w_codes || !w_sf || !y) return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
   if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8))) return DIROTQ_E_ARG;
@@ -355,7 +356,16 @@ int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x
   a.bias = static_cast<const __nv_bfloat16*>(bias);
   a.y = static_cast<__nv_bfloat16*>(y);
   a.status = status;
+  a.act = act;
   return launch_gemm_nvfp4(a, static_cast<cudaStream_t>(stream));
+}
+
+int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
+                           const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
+                           const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
+                           void* y, int32_t* status, void* stream) {
+  return gemm_w4a4_nvfp4_impl(M, N, n_chunks, x_codes, x_sf, w_codes, w_sf, out_scale, x_tail, w_tail_scaled, tail_total,
+                              tail_pitch, bias, y, 0, status, stream);
 }
 
 struct WsCarve {
@@ -414,16 +424,19 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
   }
   if (!(stages & 2)) return DIROTQ_OK;
   if (g.mode == DIROTQ_NVFP4_HW)
-    return dirotq_gemm_w4a4_nvfp4(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
-                                  lin->fmt.tensor_scale * lin->w_tensor_scale, tail, lin->w_tail, g.tail_total,
-                                  g.tail_pitch, lin->bias, y, status, stream);
+    return gemm_w4a4_nvfp4_impl(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
+                                lin->fmt.tensor_scale * lin->w_tensor_scale, tail, lin->w_tail, g.tail_total,
+                                g.tail_pitch, lin->bias, y, lin->epilogue_act, status, stream);
+  if (lin->epilogue_act < 0 || lin->epilogue_act > 1) return DIROTQ_E_ARG;
   if (uses_f16_gemm(lin, g)) {
     if (!lin->w_colscale || (g.tail_total > 0 && !lin->w_tail_f16)) return DIROTQ_E_ARG;
     // the activation-side folding belongs to the first stage: a GEMM-only call finds its results in place
     return gemm_w4a4_int_f16_impl(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
                                   lin->w_mult, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
-                                  lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 1) ? 0 : 1, status, stream);
+                                  lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 1) ? 0 : 1, lin->epilogue_act,
+                                  status, stream);
   }
+  if (lin->epilogue_act != 0) return DIROTQ_E_UNSUPPORTED;
   return dirotq_gemm_w4a4_int(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
                               static_cast<const float*>(lin->w_scales), lin->w_sum, tail, lin->w_tail, g.tail_total,
                               g.tail_pitch, lin->bias, y, nullptr, status, stream);

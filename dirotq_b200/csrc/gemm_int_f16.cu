@@ -492,8 +492,9 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
             }
 #pragma unroll
             for (int e2 = 0; e2 < 4; ++e2) {
-              const float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2]), rs * cs8[2 * e2], b[2 * e2]);
-              const float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2 + 1]), rs * cs8[2 * e2 + 1], b[2 * e2 + 1]);
+              float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2]), rs * cs8[2 * e2], b[2 * e2]);
+              float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2 + 1]), rs * cs8[2 * e2 + 1], b[2 * e2 + 1]);
+              if (a.act == 1) { f0 = gelu_tanh_bf16(f0); f1 = gelu_tanh_bf16(f1); }
               __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
               w[e2] = *reinterpret_cast<uint32_t*>(&h);
             }

@@ -211,8 +211,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), a.out_scale, b[2 * e]),
-                                                       __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), a.out_scale, b[2 * e + 1]));
+              float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), a.out_scale, b[2 * e]);
+              float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), a.out_scale, b[2 * e + 1]);
+              if (a.act == 1) { f0 = gelu_tanh_bf16(f0); f1 = gelu_tanh_bf16(f1); }
+              __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
               w[e] = *reinterpret_cast<uint32_t*>(&h);
             }
           }

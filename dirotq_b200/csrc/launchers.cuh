@@ -131,6 +131,7 @@ struct GemmIntF16Args {
   __nv_bfloat16* y;            // [M, N]
   int* status;
   int force_bn;                // 0 = pick the column-tile width from N
+  int act;                     // epilogue activation: 0 none, 1 GELU (tanh form) on the bf16-rounded output
 };
 
 struct GemmFp4Args {
@@ -141,6 +142,7 @@ struct GemmFp4Args {
   const uint8_t* wq;           // [N, n_chunks * 32]
   const uint8_t* wsf;
   float out_scale;
+  int act;                     // epilogue activation: 0 none, 1 GELU (tanh form)
   const __nv_bfloat16* xt;
   const __nv_bfloat16* wt;
   int kt;

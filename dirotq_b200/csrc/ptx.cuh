@@ -87,6 +87,17 @@ __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, vol
   return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
+// GELU, tanh form (torch.nn.functional.gelu(approximate="tanh")), applied to a value that was first rounded
+// to bf16 -- the tensor the reference's activation module sees -- with the hardware tanh (relative error about
+// 2^-11, below the bf16 rounding of the result).
+__device__ __forceinline__ float gelu_tanh_bf16(float x) {
+  x = __bfloat162float(__float2bfloat16_rn(x));
+  const float u = 0.7978845608028654f * __fmaf_rn(0.044715f * x * x, x, x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.f + t);
+}
+
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start
 // (and run its prologue: barrier init, TMEM allocation, descriptor prefetch) while the previous kernel of the
 // stream is still finishing.  pdl_wait() returns once that kernel has completed and its writes are visible;

@@ -142,6 +142,19 @@ def make_wrapped_linear(ld: LayerDef, quant: str, seed: int, device="cuda", a_sy
     return w
 
 
+class GeluProj(nn.Module):
+    """Mirror of diffusers.models.activations.GELU as the reference's transformers use it for ff.net.0:
+    a projection followed by GELU (here always the tanh form); `proj` is the wrapped linear."""
+
+    def __init__(self, proj: nn.Module, approximate: str = "tanh"):
+        super().__init__()
+        self.proj = proj
+        self.approximate = approximate
+
+    def forward(self, hidden_states):
+        return torch.nn.functional.gelu(self.proj(hidden_states), approximate=self.approximate)
+
+
 def _set_nested(root: nn.Module, dotted: str, leaf: nn.Module):
     """root.a.b.c = leaf for dotted == "a.b.c", creating plain container modules on the way."""
     parts = dotted.split(".")
@@ -165,6 +178,7 @@ class LinearPathStep(nn.Module):
         self.n_blocks = n_blocks
         self.blocks = nn.ModuleList()     # module tree with the reference's names (blocks.3.attn1.to_q ...)
         self.layers = []                  # the same wrappers in call order
+        self.heads = {}                   # index in self.layers -> GeluProj module that owns that wrapper
         for b in range(n_blocks):
             blk = nn.Module()
             qkv_rotation = {}
@@ -179,7 +193,12 @@ class LinearPathStep(nn.Module):
                         w.rotation = qkv_rotation[parent].clone()
                     else:
                         qkv_rotation[parent] = w.rotation
-                _set_nested(blk, ld.name, w)
+                if ld.out_f > ld.in_f:
+                    head = GeluProj(w)                    # ff.net.0 = GELU(proj(x)), as in the reference models
+                    _set_nested(blk, ld.name.rsplit(".", 1)[0] if ld.name.endswith(".proj") else ld.name + "_act", head)
+                    self.heads[len(self.layers)] = head
+                else:
+                    _set_nested(blk, ld.name, w)
                 self.layers.append(w)
             self.blocks.append(blk)
 
@@ -209,8 +228,8 @@ class LinearPathStep(nn.Module):
                 lyr = self.layers[b * nb + i]
                 if ld.source == "ff":
                     y = lyr(ff)
+                elif b * nb + i in self.heads:
+                    ff = y = self.heads[b * nb + i](x)        # projection + GELU (fused into the GEMM when enabled)
                 else:
                     y = lyr(x)
-                    if ld.out_f != ld.in_f and ld.out_f > ld.in_f:
-                        ff = torch.nn.functional.gelu(y, approximate="tanh")
         return y

@@ -179,6 +179,20 @@ class FluxLinearStep:
         self.layers = tree               # module tree (blocks.i.attn.to_q ...); call order is in self.blocks
         self._flat = layers
         self._gather = {}
+        self.fused_gelu = False
+
+    def fuse_gelu(self) -> int:
+        """GELU of the FFN pairs into the up-projection's GEMM epilogue (call after the layers are prepared)."""
+        n = 0
+        for _, _, wu, _ in self.blocks:
+            st = getattr(wu, "_b200_state", None)
+            if st is None or (st.folded is None and st.fmt.mode != 4):
+                return 0
+        for _, _, wu, _ in self.blocks:
+            wu._b200_state.epilogue_act, wu._b200_state._c = 1, None
+            n += 1
+        self.fused_gelu = n > 0
+        return n
 
     def ops_per_step(self):
         """(linear, rotation) operations of the whole step at the global batch."""
@@ -202,9 +216,9 @@ class FluxLinearStep:
         return self.rows[stream] // self.world
 
     def _ffn(self, x, wu, wd):
+        act = (lambda t: t) if self.fused_gelu else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
         if self.ffn == "dp":
-            h = torch.nn.functional.gelu(wu(x), approximate="tanh")
-            return wd(h)
+            return wd(act(wu(x)))
         m = x.shape[0]
         key = (m, x.dtype)
         if key not in self._gather:
@@ -212,8 +226,7 @@ class FluxLinearStep:
                                  torch.empty(m, self.hidden, dtype=x.dtype, device=x.device))
         full, out = self._gather[key]
         dist.all_gather_into_tensor(full, x.contiguous())
-        h = torch.nn.functional.gelu(wu(full.unsqueeze(0)), approximate="tanh")
-        part = wd(h).reshape(self.world * m, self.hidden)
+        part = wd(act(wu(full.unsqueeze(0)))).reshape(self.world * m, self.hidden)
         dist.reduce_scatter_tensor(out, part, op=dist.ReduceOp.SUM)
         return out
 

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DIROTQ_ABI_VERSION 2
+#define DIROTQ_ABI_VERSION 3
 
 /* ---- activation quantiser modes (ActQuantizer.configure, utils/quant_utils.py:182-199) ---- */
 enum {
@@ -228,6 +228,11 @@ typedef struct dirotq_linear {
   const void* w_mult;
   const float* w_colscale;
   const void* w_tail_f16;
+  /* Activation fused into the GEMM epilogue: 0 = none, 1 = GELU in its tanh form, applied to the bf16-rounded
+   * output (what the activation module that follows the linear in the reference model computes:
+   * diffusers' GELU(approximate="tanh") around ff.net.0.proj).  Supported by the tensor-rate integer GEMM
+   * and the NVFP4 GEMM; DIROTQ_E_UNSUPPORTED on the exact-integer route. */
+  int32_t epilogue_act;
 } dirotq_linear;
 
 size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M);

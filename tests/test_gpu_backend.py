@@ -284,3 +284,29 @@ def test_hadamard_front_end_model_sizes(D, low_dim):
     assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
     y2 = ops.hadamard_low(x.cuda(), low_dim, None).cpu()
     assert torch.equal(y2.view(torch.int16), O.hadamard_low(x, low_dim, None, fp32=False).view(torch.int16))
+
+
+@pytest.mark.parametrize("quant", ["int4", "int8", "nvfp4"])
+def test_gelu_fused_into_the_gemm_epilogue(quant):
+    """ff.net.0 = GELU(proj(x)): with the activation fused into the up-projection's epilogue the module returns
+    what PyTorch's gelu(approximate="tanh") makes of the unfused bf16 output, up to the hardware tanh."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    ld = dit.LayerDef("ff.net.0.proj", 384, 1536, tail=64)
+    w = dit.make_wrapped_linear(ld, quant, 31, "cuda")
+    head = dit.GeluProj(w)
+    root = nn.Module()
+    root.add_module("ff0", head)
+    backend.preconvert_rotations_to_device(root, "cuda")
+    x = synth_activations(520, 384, torch.Generator().manual_seed(3)).reshape(1, 520, 384).cuda()
+    y_plain = head(x)                                           # gelu as a separate PyTorch kernel
+    assert backend.fuse_gelu_modules(root) == 1
+    assert backend.fuse_gelu_modules(root) == 0                 # idempotent
+    y_fused = head(x)
+    ops.check_status()
+    assert y_fused.dtype == torch.bfloat16 and y_fused.shape == y_plain.shape
+    a, b = y_fused.float().cpu(), y_plain.float().cpu()
+    assert rel_l2(a, b) < 2e-3 and cosine(a, b) > 0.9999
+    # at most one bf16 ulp apart wherever the value is not tiny
+    big = b.abs() > 1e-2
+    assert float(((a - b).abs()[big] / b.abs()[big]).max()) < 2 ** -6
