@@ -123,6 +123,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
     M = x2d.shape[0]
     y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
+    if M == 0:
+        return y
     if st.hadamard_low_dim:
         x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
     ws = st.workspace(M, x2d.device)

@@ -119,6 +119,8 @@ def quantize_act(x2d: torch.Tensor, fmt: ActFormat, perm_idx: Optional[torch.Ten
     assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.dim() == 2 and x2d.stride(1) == 1
     M = x2d.shape[0]
     buf = out if out is not None else alloc_act(fmt, M, x2d.device)
+    if M == 0:
+        return buf
     check(_lib.lib().dirotq_quantize_act(C.byref(fmt.c()), _ptr(x2d), x2d.stride(0), _ptr(perm_idx), M,
                                          _ptr(buf.codes), _ptr(buf.scales), _ptr(buf.zeros), _ptr(buf.tail),
                                          _stream()), "dirotq_quantize_act")
@@ -133,6 +135,8 @@ def rotate_quantize(x2d: torch.Tensor, rot_t: torch.Tensor, fmt: ActFormat, want
     M = x2d.shape[0]
     buf = out if out is not None else alloc_act(fmt, M, x2d.device)
     x_rot = torch.empty_like(x2d) if want_x_rot else None
+    if M == 0:
+        return (buf, x_rot) if want_x_rot else buf
     check(_lib.lib().dirotq_rotate_quantize(C.byref(fmt.c()), _ptr(x2d), _ptr(rot_t), M, _ptr(x_rot),
                                             _ptr(buf.codes), _ptr(buf.scales), _ptr(buf.zeros), _ptr(buf.tail),
                                             _ptr(status_word(x2d.device)), _stream()), "dirotq_rotate_quantize")
@@ -288,6 +292,8 @@ def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeight
     tp = lay.tail_pitch if lay.tail_total > 0 else 0
     need = int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(M, lay.n_chunks, tp))
     ws = workspace if workspace is not None else torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    if M == 0:
+        return y
     check(_lib.lib().dirotq_gemm_w4a4_int_f16(act.fmt.mode, M, N, lay.n_chunks, _ptr(act.codes), _ptr(act.scales),
                                               _ptr(act.zeros), _ptr(w.codes), _ptr(folded.mult), _ptr(folded.colscale),
                                               _ptr(act.tail), _ptr(folded.tail), lay.tail_total, lay.tail_pitch,

@@ -310,3 +310,10 @@ def test_gelu_fused_into_the_gemm_epilogue(quant):
     # at most one bf16 ulp apart wherever the value is not tiny
     big = b.abs() > 1e-2
     assert float(((a - b).abs()[big] / b.abs()[big]).max()) < 2 ** -6
+
+
+def test_empty_batch_through_the_wrapper():
+    from dirotq_b200 import dit
+    w = dit.make_wrapped_linear(dit.LayerDef("attn1.to_q", 256, 128, tail=64), "int4", 5, "cuda")
+    y = w(torch.zeros(2, 0, 256, dtype=torch.bfloat16, device="cuda"))
+    assert tuple(y.shape) == (2, 0, 128) and y.dtype == torch.bfloat16

@@ -187,3 +187,34 @@ def test_int4_f16_gemm_wide_dynamic_range():
     # row-wise: every row, however small, is resolved (a global norm would hide the small rows)
     err = (y - y_ref).norm(dim=1) / y_ref.norm(dim=1).clamp_min(1e-30)
     assert float(err.max()) < 6e-3, float(err.max())
+
+
+@pytest.mark.parametrize("mode,M,N,D,tail", [("sym", 1, 8, 64, 0), ("sym", 127, 8, 128, 64), ("asym", 129, 200, 192, 8),
+                                             ("int8", 1, 16, 64, 0), ("int8", 130, 24, 128, 64), ("sym", 5, 1152, 1152, 64),
+                                             ("sym", 300, 200, 64, 0), ("int8", 64, 192, 384, 320)])
+def test_int_f16_gemm_edge_shapes(mode, M, N, D, tail):
+    """Single rows, output widths below one tile, one- and two-chunk K, tails wider than the quantised part."""
+    from dirotq_b200 import ops
+    m = {"sym": ops.INT4_SYM, "asym": ops.INT4_ASYM, "int8": ops.INT8_ASYM}[mode]
+    fmt = ops.ActFormat(m, D, tail_len=tail)
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, M, N, fmt, 31)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
+    y = ops.gemm_w4a4_int_f16(act, pk, folded, bias.cuda())
+    ops.check_status()
+    y_ref, _ = _oracle_int(dec, lay, qw, sw, w_tail, bias, mode != "sym")
+    assert rel_l2(y.float().cpu(), y_ref) < 4e-3
+
+
+def test_int_f16_gemm_empty_batch():
+    from dirotq_b200 import ops
+    fmt = ops.ActFormat(ops.INT4_SYM, 128, tail_len=64)
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, 8, 16, fmt, 32)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, 16, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
+    empty = ops.quantize_act(x[:0].cuda(), fmt)
+    y = ops.gemm_w4a4_int_f16(empty, pk, folded, bias.cuda())
+    assert tuple(y.shape) == (0, 16)
+    ops.check_status()
