@@ -28,8 +28,16 @@ constexpr int RQ_STAGES = 4;
 constexpr int RQ_A_BYTES = 128 * 128;           // 128 rows x 64 bf16
 constexpr int RQ_B_BYTES = 256 * 128;           // up to 256 rows x 64 bf16
 constexpr int RQ_STAGE_BYTES = RQ_A_BYTES + RQ_B_BYTES;
-constexpr int RQ_EPI_WARPS = 8;                 // two per TMEM lane quarter
-constexpr int RQ_THREADS = (2 + RQ_EPI_WARPS) * 32;
+// Epilogue warps per TMEM lane quarter: they take the 64-column chunks of their rows in turns.  The NVFP4
+// epilogue is the longest (seven threshold compares per value) and latency-bound, so it gets more warps.
+#ifndef RQ_WPQ_NVFP4
+#define RQ_WPQ_NVFP4 4
+#endif
+template <int EPI> struct RqCfg {
+  static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : 2;
+  static constexpr int EPI_WARPS = 4 * WPQ;
+  static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+};
 constexpr int RQ_SMEM_BYTES = RQ_STAGES * RQ_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
 enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3 };
@@ -64,17 +72,17 @@ __device__ __forceinline__ uint4 pack_planar32(const uint32_t* q) {
 }
 
 // ---- epilogues: thread = one row of the tile; `taddr` already points at this warp's lanes.
-// Two warps share a lane quarter; `turn` counts work items (64-column chunks, heads) across tiles
-// and a warp takes the items whose parity equals its `half`, which balances odd counts per tile.
+// Several warps (wpq) share a lane quarter; `turn` counts work items (64-column chunks, heads) across tiles
+// and a warp takes the items whose index modulo wpq equals its `half`, which balances odd counts per tile.
 template <int MODE>
-__device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
+__device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn, int wpq = 2) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
   for (int c0 = 0; c0 < a.BN; c0 += 64) {
     const int col = n0 + c0;
     if (col >= g.D) break;
-    if (((turn++) & 1u) != (uint32_t)half) continue;
+    if (((turn++) % (uint32_t)wpq) != (uint32_t)half) continue;
     uint32_t r[64];
     tmem_ld32(taddr + c0, r);
     tmem_ld32(taddr + c0 + 32, r + 32);
@@ -165,8 +173,11 @@ __device__ __forceinline__ void epi_int_hidden(const RotArgs& a, uint32_t taddr,
   }
 }
 
+// One 16-column quantisation group at a time (tcgen05.ld x16, a rolled loop over the chunk's four groups):
+// the longest epilogue of the kernel stays small in registers and in code, so more warps can share a lane
+// quarter and hide each other's latencies.
 template <int MODE>
-__device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
+__device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn, int wpq = 2) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   const int n_kb64_pad = (g.n_chunks + 3) & ~3;
@@ -174,79 +185,73 @@ __device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t tadd
   for (int c0 = 0; c0 < a.BN; c0 += 64) {
     const int col = n0 + c0;
     if (col >= g.D) break;
-    if (((turn++) & 1u) != (uint32_t)half) continue;
-    uint32_t r[64];
-    tmem_ld32(taddr + c0, r);
-    tmem_ld32(taddr + c0 + 32, r + 32);
-    tmem_wait_ld();
-    float v[64];
-#pragma unroll
-    for (int j = 0; j < 64; ++j) v[j] = rnd<true>(__uint_as_float(r[j]));
-    if (a.x_rot && row_ok) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (col + 8 * i + 8 <= g.D)
-          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) =
-              make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
-                         pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
-    }
-    if (!a.codes) continue;
+    if (((turn++) % (uint32_t)wpq) != (uint32_t)half) continue;
     const int nq = max(0, min(64, g.q_len - col));
-    if (nq > 0) {
-      const int chunk = col >> 6;
-      uint32_t packed[8];
-      uint32_t sfw = 0;
+    const int chunk = col >> 6;
+    uint32_t sfw = 0;
+#pragma unroll 1
+    for (int gi = 0; gi < 4; ++gi) {
+      const int gcol = col + 16 * gi;
+      if (gcol >= g.D) break;
+      uint32_t r[16];
+      tmem_ld16(taddr + c0 + 16 * gi, r);
+      tmem_wait_ld();
+      float v[16];
 #pragma unroll
-      for (int gi = 0; gi < 4; ++gi) {
-        const int nvalid = max(0, min(16, nq - 16 * gi));
+      for (int j = 0; j < 16; ++j) v[j] = rnd<true>(__uint_as_float(r[j]));
+      if (a.x_rot && row_ok) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          if (gcol + 8 * i + 8 <= g.D)
+            *reinterpret_cast<uint4*>(a.x_rot + row * g.D + gcol + 8 * i) =
+                make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                           pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+      }
+      if (!a.codes) continue;
+      const int nvalid = max(0, min(16, nq - 16 * gi));
+      if (nvalid > 0) {
         float amax = 0.f;
 #pragma unroll
         for (int j = 0; j < 16; ++j)
-          if (j < nvalid) amax = fmaxf(amax, fabsf(v[16 * gi + j]));
+          if (j < nvalid) amax = fmaxf(amax, fabsf(v[j]));
         uint32_t lo = 0, hi = 0;
         if constexpr (MODE == MODE_NVFP4_REF) {
-          const float s = nvfp4_ref_scale<true>(amax, g.clip);
+          const float sc = nvfp4_ref_scale<true>(amax, g.clip);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            lo |= (j < nvalid ? nvfp4_ref_code<true>(v[16 * gi + j], s) : 0u) << (4 * j);
-            hi |= (8 + j < nvalid ? nvfp4_ref_code<true>(v[16 * gi + 8 + j], s) : 0u) << (4 * j);
+            lo |= (j < nvalid ? nvfp4_ref_code<true>(v[j], sc) : 0u) << (4 * j);
+            hi |= (8 + j < nvalid ? nvfp4_ref_code<true>(v[8 + j], sc) : 0u) << (4 * j);
           }
-          if (nvalid > 0 && row_ok) a.scales[(int64_t)(chunk * 4 + gi) * a.ldm + row] = __float2bfloat16_rn(s);
+          if (row_ok) a.scales[(int64_t)(chunk * 4 + gi) * a.ldm + row] = __float2bfloat16_rn(sc);
         } else {
           float eff = 0.f;
-          uint8_t sb = 0;
-          if (nvalid > 0) sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
-          if (nvalid == 16 && eff > 0.f && short_T) {
-            const uint2 c = nvfp4_hw_group_fast(v + 16 * gi, eff);
-            lo = c.x;
-            hi = c.y;
-          } else {
-            const float* t = v + 16 * gi;
-            const uint2 c = nvfp4_hw_group_partial(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], t[9], t[10], t[11],
-                                                   t[12], t[13], t[14], t[15], nvalid, eff);
-            lo = c.x;
-            hi = c.y;
-          }
+          const uint8_t sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
+          uint2 c;
+          if (nvalid == 16 && eff > 0.f && short_T)
+            c = nvfp4_hw_group_fast(v, eff);
+          else
+            c = nvfp4_hw_group_partial(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12],
+                                       v[13], v[14], v[15], nvalid, eff);
+          lo = c.x;
+          hi = c.y;
           sfw |= (uint32_t)sb << (8 * gi);
         }
-        packed[2 * gi] = lo;
-        packed[2 * gi + 1] = hi;
+        if (row_ok)
+          *reinterpret_cast<uint2*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32 + gi * 8) = make_uint2(lo, hi);
+      } else if (nq > 0 && row_ok) {
+        // a group of the chunk that lies wholly in the tail region: its code slots stay zero
+        *reinterpret_cast<uint2*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32 + gi * 8) = make_uint2(0u, 0u);
       }
-      if (row_ok) {
-        uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
-        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        if constexpr (MODE == MODE_NVFP4_HW)
-          *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, chunk * 4, n_kb64_pad)) = sfw;
-      }
-    }
-    if (nq < 64 && row_ok && a.tail) {
-      __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
-      const int t0 = col - g.q_len;
+      if (nvalid < 16 && row_ok && a.tail) {
+        __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
+        const int t0 = gcol - g.q_len;
 #pragma unroll
-      for (int j = 0; j < 64; ++j)
-        if (j >= nq && col + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+        for (int j = 0; j < 16; ++j)
+          if (j >= nvalid && gcol + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+      }
     }
+    if constexpr (MODE == MODE_NVFP4_HW)
+      if (a.codes && nq > 0 && row_ok) *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, chunk * 4, n_kb64_pad)) = sfw;
   }
 }
 
@@ -263,7 +268,7 @@ __device__ __forceinline__ void ld32_by8(uint32_t taddr, uint32_t* r) {
 // Per-head layout: head h = tile columns [hh*d, hh*d + d): first d_q quantised as ONE group,
 // last hlen passthrough.  Two passes over TMEM (extrema, then codes) keep registers small.
 template <int MODE>
-__device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
+__device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn, int wpq = 2) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
@@ -272,7 +277,7 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
   for (int cb = 0; cb < a.BN; cb += d) {
     const int h = (n0 + cb) / d;
     if (h >= g.H) break;
-    if (((turn++) & 1u) != (uint32_t)half) continue;
+    if (((turn++) % (uint32_t)wpq) != (uint32_t)half) continue;
     if (a.x_rot) {
       for (int c8 = 0; c8 < d; c8 += 8) {
         uint32_t r[8];
@@ -364,13 +369,13 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
 
 // Plain GEMM epilogue: y[M, N] = acc (+ bias) as bf16; used for the stand-alone rotation and for
 // the bf16 GEMM behind the W4A16 layer.
-__device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn) {
+__device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn, int wpq = 2) {
   const ActGeom& g = a.g;
   const bool row_ok = row < a.M;
   for (int c0 = 0; c0 < a.BN; c0 += 32) {
     const int col = n0 + c0;
     if (col >= g.D) break;
-    if (((turn++) & 1u) != (uint32_t)half) continue;
+    if (((turn++) % (uint32_t)wpq) != (uint32_t)half) continue;
     uint32_t r[32];
     tmem_ld32(taddr + c0, r);
     tmem_wait_ld();
@@ -392,7 +397,7 @@ __device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, i
 }
 
 template <int EPI, int MODE>
-__global__ void __launch_bounds__(RQ_THREADS, 1)
+__global__ void __launch_bounds__(RqCfg<EPI>::THREADS, 1)
 rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_u, const RotArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -410,7 +415,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RQ_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), RQ_EPI_WARPS); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), RqCfg<EPI>::EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_x);
@@ -503,7 +508,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       const int n0 = nb * a.BN;
       if constexpr (EPI == EPI_ROT_ONLY) epi_rot_only(a, taddr, row, n0, half, turn);
       else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0, half, turn);
-      else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn);
+      else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
       else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn);
       tc_fence_before();
       __syncwarp();
@@ -543,7 +548,7 @@ static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs
     attr_set = true;
   }
   const int grid = min(a.m_tiles * a.n_tiles, num_sms());
-  return launch_pdl(k, dim3(grid), dim3(RQ_THREADS), RQ_SMEM_BYTES, st, tx, tu, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  return launch_pdl(k, dim3(grid), dim3(RqCfg<EPI>::THREADS), RQ_SMEM_BYTES, st, tx, tu, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 // Picks the N tile: hidden layouts want a multiple of 64 with the least padding of D; per-head
