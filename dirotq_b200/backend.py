@@ -48,8 +48,8 @@ class SharedActivation:
 
     @staticmethod
     def _key(x: torch.Tensor):
-        return (x.data_ptr(), x._version, tuple(x.shape), tuple(x.stride()), x.dtype, x.device.index,
-                torch.cuda.current_stream(x.device).cuda_stream)
+        stream = torch.cuda.current_stream(x.device).cuda_stream if x.is_cuda else 0
+        return (x.data_ptr(), x._version, tuple(x.shape), tuple(x.stride()), x.dtype, x.device.index, stream)
 
     def lookup(self, x: torch.Tensor, member_id: int) -> bool:
         """True if the workspace already holds this tensor's codes and `member_id` has not used them yet."""

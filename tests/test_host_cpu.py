@@ -112,3 +112,63 @@ def test_grid_recovery_on_reference_quantised_weights():
     gp = load_golden("perhead_int4_sym")
     wl = gp["weight"].reshape(96, 4, 72)[:, :, :63].reshape(96, -1)
     assert recover_int4_grid(wl, 63).n_lossy == 0
+
+
+def test_shared_activation_bookkeeping():
+    """The record that lets to_k / to_v reuse to_q's quantised activations: same storage + shape + in-place
+    version and a member that has not used it yet; anything else is a miss."""
+    import torch
+    from dirotq_b200.backend import SharedActivation
+    g = SharedActivation(3)
+    x = torch.zeros(4, 8)
+    assert not g.lookup(x, 0)
+    g.store(x, 0)
+    assert g.x_ref is x
+    assert g.lookup(x.view(4, 8), 1)              # another view of the same storage and shape
+    assert not g.lookup(x, 1)                     # member 1 has used it already
+    assert not g.lookup(x[:2], 2)                 # different shape
+    x.add_(1)                                     # in-place change: version moves
+    assert not g.lookup(x, 2)
+    g.store(x, 2)
+    assert g.lookup(x, 0) and g.lookup(x, 1)
+    assert g.x_ref is None                        # every member served: the reference is dropped
+    y = torch.zeros(4, 8)
+    assert not g.lookup(y, 0)
+    assert (g.hits, g.misses) == (3, 2)
+
+
+def test_sibling_grouping_needs_equal_rotations_and_formats():
+    import torch
+    import torch.nn as nn
+    from dirotq_b200 import backend, ops
+
+    class FakeState:
+        def __init__(self, rot, fmt, folded=None):
+            self.rot_t, self.fmt, self.folded = rot, fmt, folded
+            self.shared, self.member_id, self._c, self._ws = None, 0, None, {}
+
+    class Wrapped(nn.Module):
+        pass
+
+    def attn(rots, fmts):
+        m = nn.Module()
+        for leaf, r, f in zip(("to_q", "to_k", "to_v"), rots, fmts):
+            w = Wrapped()
+            object.__setattr__(w, "_b200_state", FakeState(r, f))
+            m.add_module(leaf, w)
+        return m
+
+    f4 = ops.ActFormat(ops.INT4_SYM, 64, tail_len=16)
+    f8 = ops.ActFormat(ops.INT8_ASYM, 64, tail_len=16)
+    r = torch.eye(64)
+    root = nn.Module()
+    root.add_module("a", attn([r, r.clone(), r.clone()], [f4, f4, f4]))          # all three equal
+    root.add_module("b", attn([r, r.clone(), r * 2], [f4, f4, f4]))              # to_v rotates differently
+    root.add_module("c", attn([r, r.clone(), r.clone()], [f4, f8, f4]))          # to_k has another format
+    assert backend.share_sibling_activations(root, classes=(Wrapped,)) == 3
+    sa = [m._b200_state for m in root.a.children()]
+    assert sa[0].shared is sa[1].shared is sa[2].shared and [s.member_id for s in sa] == [0, 1, 2]
+    sb = [m._b200_state for m in root.b.children()]
+    assert sb[0].shared is sb[1].shared and sb[2].shared is None and sb[0].shared.n_members == 2
+    sc = [m._b200_state for m in root.c.children()]
+    assert sc[0].shared is sc[2].shared and sc[1].shared is None
