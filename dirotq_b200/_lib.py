@@ -58,6 +58,7 @@ SIGNATURES = {
     "dirotq_gemm_w4a4_nvfp4": (C.c_int, [_I64, _I64, _I32, _P, _P, _P, _P, _F, _P, _P, _I32, _I32, _P, _P, _P, _P]),
     "dirotq_gemm_w4a16_workspace_bytes": (_SZ, [_I64, _I64]),
     "dirotq_gemm_w4a16": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _SZ, _P, _P]),
+    "dirotq_gemm_w4a16_nvfp4": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _F, _P, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_workspace_bytes": (_SZ, [C.POINTER(LinearC), _I64]),
     "dirotq_linear_forward": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_gemm": (C.c_int, [C.POINTER(LinearC), _I64, _P, _P, _SZ, _P, _P]),

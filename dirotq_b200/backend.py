@@ -270,8 +270,9 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
 @dataclass
 class W4A16State:
     """A layer whose activations stay 16-bit while its weight is 4-bit (bits == 16 under
-    --skip-quant-layers, e.g. PixArt ff.net.2)."""
-    w: ops.PackedWeightInt4
+    --skip-quant-layers, e.g. PixArt ff.net.2): INT4 group-64 weight, or NVFP4 weight as in the reference's
+    WeightOnlyNVFP4Linear (speedup/weight_only_nvfp4.py:128-178)."""
+    w: object                       # ops.PackedWeightInt4 or ops.PackedWeightNvfp4
     bias: Optional[torch.Tensor]
     scratch: torch.Tensor
 
@@ -282,7 +283,11 @@ def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int 
     if K % 64 or N % 8 or group != 64:
         return None
     dev = torch.device(device)
-    if explicit and "codes" in explicit:
+    if explicit and "nibbles" in explicit:
+        pk = pack.convert_dirotq_low_weight_to_b200_fp4(None, explicit["tensor_scale"], explicit["nibbles"],
+                                                        explicit["scales_e4m3"])
+        bias = explicit.get("bias")
+    elif explicit and "codes" in explicit:
         pk = pack.convert_dirotq_low_weight_to_b200(None, 64, scales=explicit["scales"], codes=explicit["codes"])
         bias = explicit.get("bias")
     else:
@@ -308,7 +313,10 @@ def _fused_forward_b200(self, x):
             return self.module(x).to(x.dtype)
         shp = x.shape
         x2d = x.reshape(-1, shp[-1]).to(torch.bfloat16).contiguous()
-        y = ops.gemm_w4a16(x2d, s16.w, s16.bias, workspace=s16.scratch)
+        if isinstance(s16.w, ops.PackedWeightNvfp4):
+            y = ops.gemm_w4a16_nvfp4(x2d, s16.w, s16.bias, workspace=s16.scratch)
+        else:
+            y = ops.gemm_w4a16(x2d, s16.w, s16.bias, workspace=s16.scratch)
         return y.reshape(*shp[:-1], s16.w.N).to(x.dtype)
     st = getattr(self, "_b200_state", None)
     if st is None:

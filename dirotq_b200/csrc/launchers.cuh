@@ -171,6 +171,8 @@ int launch_hadamard_low(const void* x, int64_t M, int D, int n, const void* flip
 int num_sms();
 int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64_t K, const void* bias, void* y,
                      int* status, cudaStream_t st);
+int launch_dequant_nvfp4(const uint8_t* codes, const uint8_t* sf, float T, int64_t N, int n_chunks, __nv_bfloat16* w,
+                         cudaStream_t st);
 int launch_dequant_int4(const uint8_t* codes, const float* scales, int64_t N, int n_chunks, int64_t ldn,
                         __nv_bfloat16* w, cudaStream_t st);
 

@@ -164,6 +164,42 @@ __global__ void __launch_bounds__(256) dequant_int4_kernel(const uint8_t* __rest
   for (int i = 0; i < 4; ++i) dst[i] = src[i];
 }
 
+// Packed NVFP4 weight (sequential E2M1 nibbles, tiled UE4M3 group scales, fp32 tensor scale) -> bf16
+// [N, n_chunks*64]: value * micro * T rounded once.  One thread = one group of 16.
+__global__ void __launch_bounds__(256) dequant_nvfp4_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
+                                                            float T, int64_t N, int n_chunks, __nv_bfloat16* __restrict__ w) {
+  const int gpr = n_chunks * 4;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= N * gpr) return;
+  const int64_t n = tid / gpr;
+  const int gi = (int)(tid - n * gpr);
+  const int n_kb64_pad = (n_chunks + 3) & ~3;
+  const float s = e4m3_to_float(__ldg(sf + sf_offset(n, gi, n_kb64_pad))) * T;
+  const uint2 p = __ldg(reinterpret_cast<const uint2*>(codes + n * (int64_t)(n_chunks * 32) + (int64_t)gi * 8));
+  const uint32_t pw[2] = {p.x, p.y};
+  __nv_bfloat16 out[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint32_t nib = (pw[j >> 3] >> (4 * (j & 7))) & 0xF;
+    const uint32_t m = nib & 7;
+    // E2M1 magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6
+    const float mag = m < 2 ? 0.5f * (float)m : (m < 4 ? 0.5f * (float)m : (m < 6 ? (float)(m - 2) : (m == 6 ? 4.f : 6.f)));
+    out[j] = __float2bfloat16_rn((nib & 8) ? -mag * s : mag * s);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(w + n * (int64_t)(n_chunks * 64) + (int64_t)gi * 16);
+  const uint4* src = reinterpret_cast<const uint4*>(out);
+  dst[0] = src[0];
+  dst[1] = src[1];
+}
+
+int launch_dequant_nvfp4(const uint8_t* codes, const uint8_t* sf, float T, int64_t N, int n_chunks, __nv_bfloat16* w,
+                         cudaStream_t st) {
+  const int64_t total = N * n_chunks * 4;
+  if (total <= 0) return DIROTQ_OK;
+  dequant_nvfp4_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(codes, sf, T, N, n_chunks, w);
+  return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
 int launch_dequant_int4(const uint8_t* codes, const float* scales, int64_t N, int n_chunks, int64_t ldn,
                         __nv_bfloat16* w, cudaStream_t st) {
   const int64_t total = N * n_chunks * 2;

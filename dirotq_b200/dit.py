@@ -104,6 +104,14 @@ def make_wrapped_linear(ld: LayerDef, quant: str, seed: int, device="cuda", a_sy
     bias = (torch.randn(N, generator=gen, device=dev) * 0.1).to(torch.bfloat16)
     if ld.kind == "w4a16":
         w.quantizer.configure(bits=16, groupsize=-1, sym=True)
+        if quant == "nvfp4":          # weight-only NVFP4 (the reference's WeightOnlyNVFP4Linear)
+            from .pack import pow2_tensor_scale
+            nib = torch.randint(0, 16, (N, D), generator=gen, device=dev).to(torch.uint8)
+            s_ = torch.exp(torch.randn(N, D // 16, generator=gen, device=dev) * 0.5 - 4.0)
+            T = pow2_tensor_scale(float(s_.max()))
+            micro = (s_ / T).clamp(min=2.0 ** -9, max=448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+            w._b200_explicit = {"nibbles": nib, "scales_e4m3": micro, "tensor_scale": T, "bias": bias}
+            return w
         codes = torch.randint(-8, 8, (N, D), generator=gen, device=dev)
         scales = (torch.rand(N, D // 64, generator=gen, device=dev) * 0.015 + 0.005).to(torch.float16).float()
         w._b200_explicit = {"codes": codes, "scales": scales, "bias": bias}

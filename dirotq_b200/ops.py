@@ -317,6 +317,24 @@ def gemm_w4a4_nvfp4(act: ActBuffers, w: PackedWeightNvfp4, w_tail_scaled: Option
     return y
 
 
+def gemm_w4a16_nvfp4(x2d: torch.Tensor, w: "PackedWeightNvfp4", bias: Optional[torch.Tensor],
+                     workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """W4A16 linear with an NVFP4 weight: bf16 x [M, K] (K = n_chunks * 64) times E2M1 codes x UE4M3 group scales
+    x tensor scale (dequantised into scratch, then the tcgen05 bf16 GEMM)."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
+    M, K = x2d.shape
+    assert K == w.n_chunks * 64
+    need = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(w.N, K))
+    ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x2d.device)
+    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x2d.device)
+    if M == 0:
+        return y
+    check(_lib.lib().dirotq_gemm_w4a16_nvfp4(M, w.N, K, _ptr(x2d), _ptr(w.codes), _ptr(w.sf), float(w.tensor_scale),
+                                             _ptr(bias), _ptr(y), _ptr(ws), ws.numel(), _ptr(status_word(x2d.device)),
+                                             _stream()), "dirotq_gemm_w4a16_nvfp4")
+    return y
+
+
 def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tensor],
                workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """W4A16 linear: bf16 x [M, K] times INT4 group-64 weights (dequantised into scratch, then tcgen05 bf16 GEMM)."""

@@ -208,6 +208,11 @@ size_t dirotq_gemm_w4a16_workspace_bytes(int64_t N, int64_t K);
 int dirotq_gemm_w4a16(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const float* w_scales,
                       const void* bias, void* y, void* workspace, size_t workspace_bytes, int32_t* status,
                       void* stream);
+/* Same with an NVFP4 weight (codes / tiled UE4M3 scales / tensor scale from dirotq_pack_weight_nvfp4):
+ * the forward of the reference's WeightOnlyNVFP4Linear (speedup/weight_only_nvfp4.py:128-178). */
+int dirotq_gemm_w4a16_nvfp4(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const void* w_sf,
+                            float w_tensor_scale, const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                            int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * One wrapped linear end to end: what the patched ActQuantWrapper.forward runs

@@ -43,3 +43,24 @@ def test_pixart_step_builder_runs_and_matches_layerwise():
             assert lin == 2 * 512 * (6 * 1152 * 1152 + 2 * 1152 * 4608) and rot == 2 * 512 * 7 * 1152 * 1152
     finally:
         ActQuantWrapper.forward = saved
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 256, 128), (1000, 1152, 4608), (130, 136, 192)])
+def test_w4a16_nvfp4_weight(M, N, K):
+    """Weight-only NVFP4 (speedup/weight_only_nvfp4.py:128-178): E2M1 codes x UE4M3 group scales x tensor scale,
+    dequantised once to bf16, then the bf16 GEMM."""
+    from dirotq_b200 import ops
+    g = torch.Generator().manual_seed(22)
+    x = O.synth_activations(M, K, g)
+    nib = torch.randint(0, 16, (N, K), generator=g).to(torch.uint8)
+    s = torch.exp(torch.randn(N, K // 16, generator=g) * 0.5 - 4.0)
+    T = O.pow2_tensor_scale(float(s.max()))
+    micro = O.e4m3_round(s / T)
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    pk = ops.pack_weight_nvfp4(nib.float().cuda(), T, scales_e4m3=micro.to(torch.float8_e4m3fn).view(torch.uint8).cuda(),
+                               w_is_codes=True)
+    y = ops.gemm_w4a16_nvfp4(x.cuda(), pk, bias.cuda())
+    ops.check_status()
+    W = (O.e2m1_values(nib, torch.float32).reshape(N, -1, 16) * (micro.float() * T).unsqueeze(-1)).reshape(N, K)
+    y_ref = torch.nn.functional.linear(x.float(), W.to(torch.bfloat16).float(), bias.float())
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
