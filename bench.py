@@ -132,7 +132,8 @@ def run_reference(args):
     cb, t = cpu_reference_tflops(args.workload, args.steps, args.warmup, budget_s=120.0)
     line = {"impl": "reference", "metric": "w4a4_linear_tflops", "value": cb["value"], "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if args.workload.startswith("flux") else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOADS[args.workload][5], "sample": cb["sample"]},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -206,6 +207,11 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    # stdout carries the JSON line only: everything else written to file descriptor 1 until then (library
+    # banners such as NCCL's version line included) goes to stderr
+    sys.stdout.flush()
+    saved_stdout_fd = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -327,9 +333,13 @@ def run_ours(args):
             "gpu_launches": step.kernel_launches_per_step() * args.steps,
             "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
         }
-        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(saved_stdout_fd, 1)
+    os.close(saved_stdout_fd)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
 
 
 def roofline_pass(step, x_dev, M, quant, dev, steps):
