@@ -15,6 +15,61 @@ __device__ __forceinline__ int src_col(const ActGeom& g, int grp, int e) {
   return g.H > 0 ? grp * g.d + e : grp * g.group + e;
 }
 
+// Partial blocks (the end of a group that is not a multiple of 32): the plain exact forms, padding slots get code 0.
+template <int MODE>
+static __device__ __noinline__ void quant_int_block_slow(const __nv_bfloat16* x, int64_t x_pitch, const int64_t* perm,
+                                                         uint8_t* codes, int code_row_bytes, float scale, float zero,
+                                                         int nvalid, int c0, int64_t row, int b) {
+  constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
+  GroupParams p;
+  p.scale = scale;
+  p.zero = zero;
+  float v[32];                      // re-read here: a pointer to the caller's values would push them to local memory
+  const __nv_bfloat16* xr = x + row * x_pitch;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float f = 0.f;
+    if (j < nvalid) {
+      int64_t c = c0 + j;
+      if (perm) c = perm[c];
+      f = __bfloat162float(xr[c]);
+    }
+    v[j] = f;
+  }
+  uint32_t q[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    int c = 0;
+    if (j < nvalid) {
+      if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(v[j], p.scale, maxq);
+      else c = int_asym_code<true>(v[j], p.scale, p.zero, maxq);
+    }
+    q[j] = (uint32_t)c;
+  }
+  if constexpr (MODE == MODE_INT8_ASYM) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      w[i] = (q[4 * i] & 0xFF) | ((q[4 * i + 1] & 0xFF) << 8) | ((q[4 * i + 2] & 0xFF) << 16) | ((q[4 * i + 3] & 0xFF) << 24);
+    uint4* dst = reinterpret_cast<uint4*>(codes + row * code_row_bytes + (int64_t)b * 32);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t x = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t byte = (q[4 * i + j] & 0xF) | ((q[16 + 4 * i + j] & 0xF) << 4);
+        x |= byte << (8 * j);
+      }
+      w[i] = x;
+    }
+    *reinterpret_cast<uint4*>(codes + row * code_row_bytes + (int64_t)b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // One thread = one block of 32 code slots of one row.  The 2*cpg threads that share a group sit
 // on consecutive lanes (aligned), so the group extrema need log2(2*cpg) shuffles.
 template <int MODE>
@@ -83,38 +138,34 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
   else p = int_asym_params<true>(mx, mn, g.clip, maxq);
 
-  uint32_t q[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    int c = 0;
-    if (j < nvalid) {
-      if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(v[j], p.scale, maxq);
-      else c = int_asym_code<true>(v[j], p.scale, p.zero, maxq);
-    }
-    q[j] = (uint32_t)c;
-  }
   if (!live) return;
-  if constexpr (MODE == MODE_INT8_ASYM) {
-    uint32_t w[8];
+  if (nvalid == 32) {
+    // full block: the division-free exact forms (guarded reciprocal, see quant_math.cuh)
+    const float rcp = __frcp_rn(p.scale);
+    if constexpr (MODE == MODE_INT4_SYM) {
+      uint32_t n8[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      w[i] = (q[4 * i] & 0xFF) | ((q[4 * i + 1] & 0xFF) << 8) | ((q[4 * i + 2] & 0xFF) << 16) | ((q[4 * i + 3] & 0xFF) << 24);
-    uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 32);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  } else {
-    uint32_t w[4];
+      for (int i = 0; i < 4; ++i) n8[i] = int_sym_nib8_fast(v + 8 * i, p.scale, rcp);
+      *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 16) = planar32_from_nib8(n8[0], n8[1], n8[2], n8[3]);
+    } else if constexpr (MODE == MODE_INT4_ASYM) {
+      uint32_t n8[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t x = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t byte = (q[4 * i + j] & 0xF) | ((q[16 + 4 * i + j] & 0xF) << 4);
-        x |= byte << (8 * j);
+      for (int i = 0; i < 4; ++i) {
+        const uint2 bb = int_asym_byte8_fast(v + 8 * i, p.scale, rcp, p.zero, maxq);
+        n8[i] = squeeze_nibbles(bb.x) | (squeeze_nibbles(bb.y) << 16);
       }
-      w[i] = x;
+      *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 16) = planar32_from_nib8(n8[0], n8[1], n8[2], n8[3]);
+    } else {
+      uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 32);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint2 b0 = int_asym_byte8_fast(v + 16 * i, p.scale, rcp, p.zero, maxq);
+        const uint2 b1 = int_asym_byte8_fast(v + 16 * i + 8, p.scale, rcp, p.zero, maxq);
+        dst[i] = make_uint4(b0.x, b0.y, b1.x, b1.y);
+      }
     }
-    *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    quant_int_block_slow<MODE>(a.x, a.x_pitch, a.perm, a.codes, g.code_row_bytes, p.scale, p.zero, nvalid, c0, row, b);
   }
   if (half == 0) {
     a.scales[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.scale);
@@ -226,6 +277,21 @@ __global__ void __launch_bounds__(256) copy_tail_kernel(const QuantArgs a) {
   a.tail[tid] = val;
 }
 
+
+// Passthrough channels of the hidden layout, eight per thread (16-byte loads and stores).
+__global__ void __launch_bounds__(256) copy_tail_vec_kernel(const QuantArgs a) {
+  const ActGeom& g = a.g;
+  const int per_row = g.tail_pitch >> 3;
+  const int64_t total = a.M * per_row;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= total) return;
+  const int64_t row = tid / per_row;
+  const int t = (int)(tid - row * per_row) * 8;
+  uint4 val = make_uint4(0u, 0u, 0u, 0u);
+  if (t < g.tail_total) val = __ldg(reinterpret_cast<const uint4*>(a.x + row * a.x_pitch + g.q_len + t));
+  *reinterpret_cast<uint4*>(a.tail + row * g.tail_pitch + t) = val;
+}
+
 int launch_quantize(const QuantArgs& a, cudaStream_t st) {
   const ActGeom& g = a.g;
   if (a.M <= 0) return DIROTQ_OK;
@@ -243,8 +309,16 @@ int launch_quantize(const QuantArgs& a, cudaStream_t st) {
     else quant_int_kernel<MODE_INT8_ASYM><<<blocks, threads, 0, st>>>(a);
   }
   if (g.tail_total > 0 && a.tail) {
-    int64_t total = a.M * g.tail_pitch;
-    copy_tail_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, st>>>(a);
+    const bool vec = g.H == 0 && !a.perm && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.x_pitch & 7) == 0 &&
+                     (reinterpret_cast<uintptr_t>(a.tail) & 15) == 0 && g.q_len % 8 == 0 && g.tail_total % 8 == 0 &&
+                     g.tail_pitch % 8 == 0;
+    if (vec) {
+      int64_t total = a.M * (g.tail_pitch / 8);
+      copy_tail_vec_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, st>>>(a);
+    } else {
+      int64_t total = a.M * g.tail_pitch;
+      copy_tail_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, st>>>(a);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
