@@ -57,6 +57,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-gelu", action="store_true",
                     help="keep the GELU between the FFN linears as a separate PyTorch kernel")
+    ap.add_argument("--cache-weight-panel", action="store_true",
+                    help="keep each INT4 layer's fp16 weight panel resident (2 bytes per weight) instead of rebuilding it "
+                         "from the 4-bit codes on every call")
     ap.add_argument("--exact-int", action="store_true",
                     help="INT4 layers through the exact-integer kind::i8 GEMM instead of the tensor-rate fp16 one")
     ap.add_argument("--profile-case", action="store_true",
@@ -376,8 +379,9 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
                                          st.w_codes, st.w_scales, st.w_sum)
                 if st.folded is not None:
                     f16_used = True
-                    if f16_ws is None or f16_ws.numel() < ops.f16_workspace_bytes(buf):
-                        f16_ws = torch.empty(ops.f16_workspace_bytes(buf), dtype=torch.uint8, device=dev)
+                    need = ops.f16_workspace_bytes(buf, 0 if st.folded.panel is not None else st.out_features)
+                    if f16_ws is None or f16_ws.numel() < need:
+                        f16_ws = torch.empty(need, dtype=torch.uint8, device=dev)
                     ops.gemm_w4a4_int_f16(buf, w, st.folded, st.bias, workspace=f16_ws)
                 else:
                     ops.gemm_w4a4_int(buf, w, st.w_tail, st.bias)
@@ -389,7 +393,7 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
     kname = "gemm_nvfp4_kernel" if quant == "nvfp4" else (
-        "gemm_int_f16_kernel (with its fold_scales_kernel)" if f16_used else "gemm_int_kernel")
+        "gemm_int_f16_kernel (with its fold_scales_kernel and expand_weight_panel_kernel)" if f16_used else "gemm_int_kernel")
     return {"bound": "tensor", "kernel": kname,
             "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained; the INT4 path computes in fp16 on the same tensor pipe, "
@@ -433,7 +437,7 @@ def roofline_pass_flux(step, x_dev, dev):
             pw = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks,
                                       st.w_codes, st.w_scales, st.w_sum)
             if f16_ws is None:
-                f16_ws = torch.empty(ops.f16_workspace_bytes(buf), dtype=torch.uint8, device=dev)
+                f16_ws = torch.empty(ops.f16_workspace_bytes(buf, st.out_features), dtype=torch.uint8, device=dev)
             ops.gemm_w4a4_int_f16(buf, pw, st.folded, st.bias, workspace=f16_ws)
             e1.record()
             pairs.append((e0, e1))
@@ -441,7 +445,7 @@ def roofline_pass_flux(step, x_dev, dev):
     torch.cuda.synchronize()
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
-    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_scales_kernel)", "achieved": achieved,
+    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_scales_kernel and expand_weight_panel_kernel)", "achieved": achieved,
             "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained (the kernel computes in fp16 on the same tensor pipe)",
             "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)),
@@ -470,6 +474,9 @@ def profile_case():
 
 if __name__ == "__main__":
     a = parse()
+    if a.cache_weight_panel:
+        from dirotq_b200 import backend as _backend
+        _backend.CACHE_WEIGHT_PANEL = True
     if a.exact_int:
         from dirotq_b200 import backend as _backend
         _backend.INT4_TENSOR_RATE_GEMM = False

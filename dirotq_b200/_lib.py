@@ -27,7 +27,8 @@ class LinearC(C.Structure):
     _fields_ = [("fmt", ActFormatC), ("out_features", C.c_int64), ("rot_t", C.c_void_p), ("perm_idx", C.c_void_p),
                 ("w_codes", C.c_void_p), ("w_scales", C.c_void_p), ("w_sum", C.c_void_p), ("w_tail", C.c_void_p),
                 ("bias", C.c_void_p), ("w_tensor_scale", C.c_float), ("w_mult", C.c_void_p),
-                ("w_colscale", C.c_void_p), ("w_tail_f16", C.c_void_p), ("epilogue_act", C.c_int32)]
+                ("w_colscale", C.c_void_p), ("w_tail_f16", C.c_void_p), ("epilogue_act", C.c_int32),
+                ("w_panel_f16", C.c_void_p)]
 
 
 _P, _I64, _I32, _F, _SZ = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_size_t
@@ -52,9 +53,11 @@ SIGNATURES = {
     "dirotq_hadamard_low": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P]),
     "dirotq_fold_weight_records_bytes": (_SZ, [_I32, _I64]),
     "dirotq_fold_weight_scales_f16": (C.c_int, [_I32, _I64, _P, _P, _I32, _I32, _P, _P, _P, _P]),
-    "dirotq_gemm_w4a4_int_f16_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
-    "dirotq_gemm_w4a4_int_f16": (C.c_int, [_I32, _I64, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P, _P,
-                                            _P, _SZ, _P, _P]),
+    "dirotq_weight_panel_bytes": (_SZ, [_I32, _I64]),
+    "dirotq_expand_weight_panel_f16": (C.c_int, [_I32, _I64, _P, _P, _P, _P]),
+    "dirotq_gemm_w4a4_int_f16_workspace_bytes": (_SZ, [_I64, _I64, _I32, _I32]),
+    "dirotq_gemm_w4a4_int_f16": (C.c_int, [_I32, _I64, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P,
+                                            _P, _P, _SZ, _P, _P]),
     "dirotq_gemm_w4a4_nvfp4": (C.c_int, [_I64, _I64, _I32, _P, _P, _P, _P, _F, _P, _P, _I32, _I32, _P, _P, _P, _P]),
     "dirotq_gemm_w4a16_workspace_bytes": (_SZ, [_I64, _I64]),
     "dirotq_gemm_w4a16": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _SZ, _P, _P]),
@@ -81,7 +84,7 @@ def lib():
             fn = getattr(l, name)       # AttributeError if the library does not export it
             fn.restype = res
             fn.argtypes = args
-        if l.dirotq_abi_version() != 3:
+        if l.dirotq_abi_version() != 4:
             raise RuntimeError("libdirotq_b200.so ABI version mismatch")
         _lib = l
     return _lib

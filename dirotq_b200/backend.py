@@ -39,6 +39,7 @@ class SharedActivation:
 
     def __init__(self, n_members: int):
         self.n_members = n_members
+        self.members: list = []          # the LayerStates: the workspace is sized for the largest of them
         self.ws: Dict[int, torch.Tensor] = {}
         self.x_ref: Optional[torch.Tensor] = None
         self.key = None
@@ -97,14 +98,15 @@ class LayerState:
             self._c = LinearC(self.fmt.c(), self.out_features, p(self.rot_t), p(self.perm_idx), p(self.w_codes),
                               p(self.w_scales), p(self.w_sum), p(self.w_tail), p(self.bias), self.w_tensor_scale,
                               p(f.mult if f else None), p(f.colscale if f else None), p(f.tail if f else None),
-                              int(self.epilogue_act))
+                              int(self.epilogue_act), p(f.panel if f else None))
         return self._c
 
     def workspace(self, M: int, device) -> torch.Tensor:
         if self.shared is not None:
             ws = self.shared.ws.get(M)
             if ws is None:
-                n = int(_lib.lib().dirotq_linear_workspace_bytes(C.byref(self.c_struct()), M))
+                n = max(int(_lib.lib().dirotq_linear_workspace_bytes(C.byref(m.c_struct()), M))
+                        for m in (self.shared.members or [self]))
                 ws = torch.zeros(max(n, 256), dtype=torch.uint8, device=device)
                 self.shared.ws = {M: ws}
                 self.shared.x_ref, self.shared.key = None, None
@@ -189,6 +191,10 @@ def _act_format(w) -> ops.ActFormat:
 # Integer-activation layers (W4A4 and W4A8) run the tensor-rate GEMM (codes expanded to fp16 next to the
 # tensor core).  Set to False to route them through the exact-integer kind::i8 kernel instead.
 INT4_TENSOR_RATE_GEMM = True
+# The tensor-rate GEMM reads the weight as an fp16 panel.  False: the panel is rebuilt from the 4-bit codes in
+# scratch on every call (weights stay 4-bit in memory; a pre-pass of N x K work per M x N x K GEMM).  True: built once
+# per layer and kept (2 bytes per weight of device memory, no pre-pass).
+CACHE_WEIGHT_PANEL = False
 
 
 def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerState:
@@ -263,6 +269,8 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     folded = None
     if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM, ops.INT8_ASYM):
         folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
+        if CACHE_WEIGHT_PANEL:
+            folded.panel = ops.expand_weight_panel_f16(pk, folded)
     return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded,
                       hadamard_low_dim=had_dim, hadamard_flips=had_flips)
 
@@ -359,6 +367,7 @@ def share_sibling_activations(transformer, classes=None) -> int:
         if len(same) < 2:
             continue
         grp = SharedActivation(len(same))
+        grp.members = list(same)
         for i, m in enumerate(same):
             m.shared, m.member_id = grp, i
             m.rot_t = first.rot_t            # one copy of the rotation on the device

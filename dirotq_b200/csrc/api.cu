@@ -237,16 +237,21 @@ int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_sc
 }
 
 struct F16Carve {
-  size_t rec, rs, tail, total;
+  size_t rec, rs, tail, panel, total;
 };
-static F16Carve carve_f16(int64_t M, int32_t n_chunks, int32_t tail_pitch) {
+static size_t panel_bytes(int32_t n_chunks, int64_t N) {
+  return ((size_t)N * (size_t)n_chunks * 128 + 255) & ~size_t(255);
+}
+// N_panel > 0: room for the fp16 weight panel of an N_panel-channel layer (callers without a panel of their own)
+static F16Carve carve_f16(int64_t M, int32_t n_chunks, int32_t tail_pitch, int64_t N_panel) {
   F16Carve c;
   const size_t ldm = (size_t)f16_ld_act(M);
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   c.rec = 0;
   c.rs = up(c.rec + (size_t)n_chunks * ldm * 8);
   c.tail = up(c.rs + ldm * 4);
-  c.total = up(c.tail + (size_t)M * (size_t)tail_pitch * 2);
+  c.panel = up(c.tail + (size_t)M * (size_t)tail_pitch * 2);
+  c.total = c.panel + (N_panel > 0 ? panel_bytes(n_chunks, N_panel) : 0);
   return c;
 }
 
@@ -255,32 +260,48 @@ size_t dirotq_fold_weight_records_bytes(int32_t n_chunks, int64_t N) {
   return (size_t)n_chunks * (size_t)f16_ld_weight(N) * 8;
 }
 
-size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int32_t n_chunks, int32_t tail_pitch) {
-  if (M < 0 || n_chunks <= 0 || tail_pitch < 0) return 0;
-  return carve_f16(M, n_chunks, tail_pitch).total;
+size_t dirotq_weight_panel_bytes(int32_t n_chunks, int64_t N) {
+  if (n_chunks <= 0 || N <= 0) return 0;
+  return panel_bytes(n_chunks, N);
+}
+
+int dirotq_expand_weight_panel_f16(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
+                                   void* stream) {
+  if (n_chunks <= 0 || N <= 0 || !w_codes || !w_mult || !panel) return DIROTQ_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(w_mult) | reinterpret_cast<uintptr_t>(panel)) & 15)
+    return DIROTQ_E_ALIGN;
+  return launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, panel,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int64_t N_panel, int32_t n_chunks, int32_t tail_pitch) {
+  if (M < 0 || N_panel < 0 || n_chunks <= 0 || tail_pitch < 0) return 0;
+  return carve_f16(M, n_chunks, tail_pitch, N_panel).total;
 }
 
 // skip_fold != 0: the workspace already holds the activation records and the scaled tail of these codes
 // (left there by an earlier call on the same activations).
 static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
                                   const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
-                                  const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
-                                  int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
-                                  size_t workspace_bytes, int skip_fold, int act, int32_t* status, void* stream) {
+                                  const void* w_panel, const float* w_colscale, const void* x_tail,
+                                  const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
+                                  void* y, void* workspace, size_t workspace_bytes, int skip_fold, int act,
+                                  int32_t* status, void* stream) {
   if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM && a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
-  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_codes || !w_mult || !w_colscale || !y || !workspace)
-    return DIROTQ_E_ARG;
+  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_colscale || !y || !workspace) return DIROTQ_E_ARG;
+  if (!w_panel && (!w_codes || !w_mult)) return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
   if (a_mode != DIROTQ_INT4_SYM && !x_zeros) return DIROTQ_E_ARG;
   if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8)))
     return DIROTQ_E_ARG;
   const uintptr_t al = reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(w_codes) |
                        reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x_tail) |
-                       reinterpret_cast<uintptr_t>(w_tail_scaled) | reinterpret_cast<uintptr_t>(w_mult);
+                       reinterpret_cast<uintptr_t>(w_tail_scaled) | reinterpret_cast<uintptr_t>(w_mult) |
+                       reinterpret_cast<uintptr_t>(w_panel);
   if (al & 15) return DIROTQ_E_ALIGN;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return DIROTQ_E_ALIGN;
   const int32_t tp = tail_total > 0 ? tail_pitch : 0;
-  const F16Carve c = carve_f16(M, n_chunks, tp);
+  const F16Carve c = carve_f16(M, n_chunks, tp, w_panel ? 0 : N);
   if (workspace_bytes < c.total) return DIROTQ_E_ARG;
   if (M == 0) return DIROTQ_OK;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -293,6 +314,12 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
                                     tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
     if (rc) return rc;
   }
+  if (!w_panel) {
+    // the weights stay 4-bit in memory; their fp16 panel is rebuilt in scratch for this call
+    int rc = launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, ws + c.panel, st);
+    if (rc) return rc;
+    w_panel = ws + c.panel;
+  }
   GemmIntF16Args a;
   a.a_mode = a_mode;
   a.M = M;
@@ -303,11 +330,8 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   a.a_const = reinterpret_cast<const uint2*>(ws + c.rec);
   a.rs = reinterpret_cast<const float*>(ws + c.rs);
   a.ldm = f16_ld_act(M);
-  a.wq = static_cast<const uint8_t*>(w_codes);
-  a.w_row_bytes = (int64_t)n_chunks * 32;
-  a.w_const = static_cast<const uint2*>(w_mult);
+  a.w_panel = w_panel;
   a.cs = w_colscale;
-  a.ldn = f16_ld_weight(N);
   a.xt = tail_s;
   a.wt = static_cast<const __nv_bfloat16*>(w_tail_scaled);
   a.kt = tail_total;
@@ -322,12 +346,12 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
 
 int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
                              const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
-                             const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
-                             int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
-                             size_t workspace_bytes, int32_t* status, void* stream) {
-  return gemm_w4a4_int_f16_impl(a_mode, M, N, n_chunks, x_codes, x_scales, x_zeros, w_codes, w_mult, w_colscale, x_tail,
-                                w_tail_scaled, tail_total, tail_pitch, bias, y, workspace, workspace_bytes, 0, 0, status,
-                                stream);
+                             const void* w_panel, const float* w_colscale, const void* x_tail,
+                             const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias, void* y,
+                             void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  return gemm_w4a4_int_f16_impl(a_mode, M, N, n_chunks, x_codes, x_scales, x_zeros, w_codes, w_mult, w_panel, w_colscale,
+                                x_tail, w_tail_scaled, tail_total, tail_pitch, bias, y, workspace, workspace_bytes, 0, 0,
+                                status, stream);
 }
 
 static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
@@ -388,7 +412,8 @@ static int carve(const dirotq_linear* lin, int64_t M, ActGeom* g, WsCarve* w) {
   w->fold = (w->fold + 255) & ~size_t(255);
   w->total = w->fold;
   if (uses_f16_gemm(lin, *g))
-    w->total += dirotq_gemm_w4a4_int_f16_workspace_bytes(M, g->n_chunks, g->tail_total > 0 ? g->tail_pitch : 0);
+    w->total += dirotq_gemm_w4a4_int_f16_workspace_bytes(M, lin->w_panel_f16 ? 0 : lin->out_features, g->n_chunks,
+                                                         g->tail_total > 0 ? g->tail_pitch : 0);
   return DIROTQ_OK;
 }
 
@@ -432,7 +457,7 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
     if (!lin->w_colscale || (g.tail_total > 0 && !lin->w_tail_f16)) return DIROTQ_E_ARG;
     // the activation-side folding belongs to the first stage: a GEMM-only call finds its results in place
     return gemm_w4a4_int_f16_impl(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
-                                  lin->w_mult, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
+                                  lin->w_mult, lin->w_panel_f16, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
                                   lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 1) ? 0 : 1, lin->epilogue_act,
                                   status, stream);
   }

@@ -20,20 +20,24 @@
 // The order in which a chunk's 64 values land along K is a fixed permutation, the same for both
 // operands, which a dot product does not see.
 //
-// Shared-memory bandwidth, not arithmetic, bounds a kernel that expands operands on chip: every
-// expanded byte is written once and read once by the tensor core.  The activation operand therefore
-// never touches shared memory in expanded form: its converter threads (one per row = one TMEM lane)
-// store the fp16 values straight into tensor memory, and the UMMA takes A from TMEM, B from smem.
+// Conversion work (issue slots, shared-memory stores), not tensor arithmetic, bounds a kernel that expands
+// operands on chip, and every CTA that expands a weight tile repeats what M / 128 other CTAs do.  So:
+//   * the weight operand is expanded ONCE per call by a small pre-pass (expand_weight_panel_kernel: codes
+//     + records -> an fp16 [N, K] panel in scratch, 2 bytes per weight, L2-resident for DiT layer sizes;
+//     the stored weights stay 4-bit) and reaches the operand ring by TMA, already swizzled;
+//   * the activation operand never touches shared memory in expanded form: its converter threads (one
+//     per row = one TMEM lane) store the fp16 values straight into tensor memory, and the UMMA takes A
+//     from TMEM, B from smem.
 //
 // Data flow per persistent CTA (128 x BN output tiles, K walked in 64-wide chunks):
-//   TMA            4-bit codes (four chunks = 128 B per row per stage, 128-byte swizzle: the copy engine works
-//                  row by row, and shorter rows left it, not the tensor core, on the critical path) +
-//                  per-row records of the chunk's multipliers (bulk copies) -> "raw" ring
-//   converter warps  two groups taking alternate chunks; per chunk a warp expands 32 activation rows into
-//                  TMEM (tcgen05.st) and 32 weight rows into the 128-byte-swizzled K-major smem tile
+//   TMA (A)        4-bit codes (four chunks = 128 B per row per stage, 128-byte swizzle) + per-row records of
+//                  the chunk's multipliers (bulk copies) -> "raw" ring
+//   TMA (B)        one BN x 64 fp16 tile of the panel (or of the bf16 tail weights) per operand stage, straight
+//                  into the stage's 128-byte-swizzled K-major slot as soon as the UMMAs that read it retire
+//   converter warps  two groups of four taking alternate chunks; a warp expands 32 activation rows into TMEM
+//                  (tcgen05.st); for a tail stage it copies the bf16 rows from the raw ring instead
 //   UMMA issuer    tcgen05.mma kind::f16 (A from TMEM, B from smem descriptor), 4 x K=16 per chunk, fp32
-//                  128 x BN accumulator in TMEM; the bf16 tail accumulates into the same tile (its weight
-//                  tile by TMA straight into the operand slot, its activation rows raw ring -> TMEM)
+//                  128 x BN accumulator in TMEM; the bf16 tail accumulates into the same tile
 //   8 epilogue warps  tcgen05.ld, * rs[m] * cs[n], + bias, bf16 -> 32 x 32 staging patches -> TMA stores; two
 //                  accumulators alternate so the next tile's UMMAs overlap the epilogue
 #include <cuda.h>
@@ -62,28 +66,22 @@ namespace dq {
 constexpr int GF_CPS = GF_CPS_DEF;   // chunks per raw stage: 128 bytes of codes per row and stage
 constexpr int GF_EPI_WARPS = 8;
 
-// Conversion work comes in units of 32 rows x one 64-slot chunk (a thread per row).  A chunk of a
-// 128 x BN tile has 4 activation units and BN / 32 weight units; each group has (4 + BN / 32) / 2 warps
-// and every warp takes two units.
+// A chunk of a 128-row tile is four conversion units of 32 rows (a thread per row = TMEM lane); a group is
+// the four warps that cover the four lane quarters.
 template <int BN, bool A8 = false> struct GfCfg {
-  static constexpr int ROWS = 128 + BN;                    // activation rows, then weight rows
-  static constexpr int GROUP_WARPS = (4 + BN / 32) / 2;    // 4 (BN = 128) / 5 (BN = 192)
+  static constexpr int GROUP_WARPS = 4;
   static constexpr int GROUPS = GF_GROUPS;
   static constexpr int CONV_WARPS = GROUPS * GROUP_WARPS;
-  static constexpr int THREADS = (GF_EPI_WARPS + 2 + CONV_WARPS) * 32;
+  static constexpr int THREADS = (GF_EPI_WARPS + 3 + CONV_WARPS) * 32;
   static constexpr int B_EXP = BN * 128;                   // BN rows x 64 halves
   static constexpr int EXP_STAGE = B_EXP;                  // only the weight operand is staged in shared memory
   static constexpr int RAW_A = 128 * 32 * GF_CPS * (A8 ? 2 : 1);   // 8-bit activation codes: two 128-byte boxes per row
-  static constexpr int RAW_B = BN * 32 * GF_CPS;
-  static constexpr int OFF_C = RAW_A + RAW_B;               // [chunk][ROWS] 8-byte records, same row order
-  static constexpr int RAW_STAGE = OFF_C + GF_CPS * ROWS * 8;
+  static constexpr int OFF_C = RAW_A;                      // [chunk][128] 8-byte records
+  static constexpr int RAW_STAGE = OFF_C + GF_CPS * 128 * 8;
   // Operand stages in flight: every tensor-memory column the two accumulators leave free holds activations
-  // (32 columns per 64-wide chunk).  The hand-off latency between converters and the UMMA issuer is paid once
-  // per trip around this ring, so its depth, not the arithmetic, sets the pace when it is shallow.
+  // (32 columns per 64-wide chunk).
   static constexpr int EXP_TMEM = (512 - 2 * BN) / 32;
-  static constexpr int EXP_CAP_A8 = BN > 128 ? 3 : 5;       // shared memory: 8-bit codes double the activations' raw bytes
-  static constexpr int EXP_CAP = (A8 && GF_EXP_MAX > EXP_CAP_A8) ? EXP_CAP_A8 : GF_EXP_MAX;
-  static constexpr int EXP_STAGES = EXP_TMEM < EXP_CAP ? EXP_TMEM : EXP_CAP;
+  static constexpr int EXP_STAGES = EXP_TMEM < GF_EXP_MAX ? EXP_TMEM : GF_EXP_MAX;
   static constexpr int RAW_STAGES = GF_RAW_DEF;
   static constexpr int STG_BYTES = GF_EPI_WARPS * 2048;     // per epilogue warp: 32 rows x 32 bf16 output staging
   static constexpr int SMEM_BYTES = EXP_STAGES * EXP_STAGE + RAW_STAGES * RAW_STAGE + STG_BYTES + 1024 + 256;
@@ -91,12 +89,11 @@ template <int BN, bool A8 = false> struct GfCfg {
   static constexpr int TMEM_COLS = 512;                     // 2 accumulators + EXP_STAGES x 32 columns of A
   static_assert(2 * BN + EXP_STAGES * 32 <= 512, "tensor memory");
   static_assert(SMEM_BYTES <= 232448, "shared memory");
-  static_assert((4 + BN / 32) % 2 == 0, "units must split evenly over the two groups");
   static_assert(RAW_A >= 128 * 128 && GF_CPS == 4, "a raw stage must hold one 128 x 64 bf16 tail tile of the activations");
 };
 
 struct GfMaps {
-  CUtensorMap xq, wq, xt, wt, y;
+  CUtensorMap xq, wp, xt, wt, y;
 };
 
 template <int N> struct GfRing {
@@ -158,7 +155,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   uint8_t* raw_area = smem + GF_EXP_STAGES * Cfg::EXP_STAGE;
   uint8_t* stg_area = raw_area + GF_RAW_STAGES * Cfg::RAW_STAGE;       // 1024-byte aligned
   uint64_t* bars = reinterpret_cast<uint64_t*>(stg_area + Cfg::STG_BYTES);
-  constexpr int NB = 2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 4;
+  constexpr int NB = 2 * GF_RAW_STAGES + 3 * GF_EXP_STAGES + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NB);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -168,18 +165,19 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   auto rawe_bar = [&](int s) { return bar0 + 8u * (GF_RAW_STAGES + s); };
   auto expf_bar = [&](int s) { return bar0 + 8u * (2 * GF_RAW_STAGES + s); };
   auto expe_bar = [&](int s) { return bar0 + 8u * (2 * GF_RAW_STAGES + GF_EXP_STAGES + s); };
-  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + b); };
-  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + 2 + b); };
+  auto expw_bar = [&](int s) { return bar0 + 8u * (2 * GF_RAW_STAGES + 2 * GF_EXP_STAGES + s); };   // weight tile landed
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * GF_RAW_STAGES + 3 * GF_EXP_STAGES + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * GF_RAW_STAGES + 3 * GF_EXP_STAGES + 2 + b); };
 
-  constexpr int W_MMA = GF_EPI_WARPS, W_TMA = GF_EPI_WARPS + 1;
+  constexpr int W_MMA = GF_EPI_WARPS, W_TMA = GF_EPI_WARPS + 1, W_TMB = GF_EPI_WARPS + 2;
   if (threadIdx.x == 0) {
     for (int s = 0; s < GF_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), Cfg::CONV_WARPS); }
-    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), Cfg::GROUP_WARPS); mbar_init(expe_bar(s), 1); }
+    for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), Cfg::GROUP_WARPS); mbar_init(expe_bar(s), 1); mbar_init(expw_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm.xq);
-    prefetch_tmap(&tm.wq);
+    prefetch_tmap(&tm.wp);
   }
   if (warp == W_MMA) tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
   tc_fence_before();
@@ -207,7 +205,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       uint32_t issued = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
+        const int m0 = (t / n_tiles_n) * 128;
         for (int c = 0; c < n_main; c += GF_CPS) {
           if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
@@ -216,19 +214,15 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
           // 8-bit codes: the second 128-byte box is issued only when it holds a chunk (a box that lies
           // wholly outside the tensor is never requested; its bytes are not part of the count either)
           const bool second_box = A8 && nv > 2;
-          mbar_expect_tx(bar, (uint32_t)(Cfg::OFF_C - ((A8 && !second_box) ? 128 * 128 : 0) + nv * Cfg::ROWS * 8));
+          mbar_expect_tx(bar, (uint32_t)(Cfg::RAW_A - ((A8 && !second_box) ? 128 * 128 : 0) + nv * 128 * 8));
           if constexpr (A8) {
             tma_load_2d(sb, &tm.xq, bar, c * 64, m0);
             if (second_box) tma_load_2d(sb + 128 * 128, &tm.xq, bar, c * 64 + 128, m0);
           } else {
             tma_load_2d(sb, &tm.xq, bar, c * 32, m0);
           }
-          tma_load_2d(sb + Cfg::RAW_A, &tm.wq, bar, c * 32, n0);
-          for (int j = 0; j < nv; ++j) {
-            const uint32_t sc = sb + Cfg::OFF_C + j * Cfg::ROWS * 8;
-            bulk_load(sc, a.a_const + ((int64_t)(c + j) * a.ldm + m0), 128 * 8, bar);
-            bulk_load(sc + 128 * 8, a.w_const + ((int64_t)(c + j) * a.ldn + n0), BN * 8, bar);
-          }
+          for (int j = 0; j < nv; ++j)
+            bulk_load(sb + Cfg::OFF_C + j * 128 * 8, a.a_const + ((int64_t)(c + j) * a.ldm + m0), 128 * 8, bar);
           issued |= 1u << r.s;
           r.next();
         }
@@ -252,51 +246,58 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         }
       }
     }
-  } else if (warp > W_TMA) {
+  } else if (warp == W_TMB) {
+    // ------------------------------ weight-tile producer ---------------------------------------
+    // Operand stage q's weight tile goes straight into slot q % EXP_STAGES as soon as the slot is free.
+    if (lane == 0) {
+      int q = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int n0 = (t % n_tiles_n) * BN;
+        for (int st = 0; st < n_main + n_tail; ++st, ++q) {
+          const int es = q % GF_EXP_STAGES;
+          if (!mbar_wait_hot(expe_bar(es), (uint32_t)(((q / GF_EXP_STAGES) & 1) ^ 1), abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t bar = expw_bar(es);
+          mbar_expect_tx(bar, Cfg::B_EXP);                     // the box is counted whole, zero fill included
+          if (st < n_main) tma_load_2d(exp_base + es * Cfg::EXP_STAGE, &tm.wp, bar, st * 64, n0);
+          else tma_load_2d(exp_base + es * Cfg::EXP_STAGE, &tm.wt, bar, (st - n_main) * 64, n0);
+        }
+      }
+      if (!ok) {
+        // the copies of the last EXP_STAGES stages issued may still be in flight
+        const long long t0 = clock64();
+        for (int qq = max(0, q - GF_EXP_STAGES); qq < q; ++qq)
+          while (!mbar_try(expw_bar(qq % GF_EXP_STAGES), (uint32_t)((qq / GF_EXP_STAGES) & 1)))
+            if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
+      }
+    }
+  } else if (warp > W_TMB) {
     // ------------------------------ converters ------------------------------------------------
-    // Two groups take alternate operand stages (stage q goes to group q & 1), so one group's barrier
-    // waits, shared-memory latencies and fences overlap the other group's arithmetic.  Warp gw of a
-    // group owns two units of 32 rows: gw < 4: the activation rows of its own TMEM lane quarter
-    // (warp index mod 4) and weight rows 32 gw ..; the fifth warp (BN = 192): weight rows 128 .. 191.
-    const int cw = warp - (W_TMA + 1);
+    // Two groups take alternate operand stages (stage q goes to group q % GROUPS), so one group's barrier
+    // waits, shared-memory latencies and fences overlap the other group's arithmetic.  A warp owns the 32
+    // activation rows of its own TMEM lane quarter (warp index mod 4).
+    const int cw = warp - (W_TMB + 1);
     constexpr int GW = Cfg::GROUP_WARPS;
     const int grp = cw / GW;
-    const int gw = cw - grp * GW;
     const int quarter = warp & 3;
-    // combined row index (activation rows 0..127, then weight rows) of this thread's two units
-    const int rowA = (gw < 4) ? quarter * 32 + lane : 128 + (4 + 2 * (gw - 4)) * 32 + lane;
-    const int rowB = (gw < 4) ? 128 + gw * 32 + lane : 128 + (5 + 2 * (gw - 4)) * 32 + lane;
-    const bool first_is_act = gw < 4;
+    const int rowA = quarter * 32 + lane;
     GfRing<GF_RAW_STAGES> r;
     int q = 0;
-    int issued_q[2] = {-1, -1};
     bool ok = true;
     auto exp_slot = [](int qq) { return qq % Cfg::EXP_STAGES; };
     auto exp_phase = [](int qq) { return (uint32_t)((qq / Cfg::EXP_STAGES) & 1); };
-    // one row x one chunk: two 16-byte pieces of the swizzled raw row + the row's record
-    // `row` is the combined index (activation rows 0..127, then weight rows); 4-bit rows are 128 bytes per
-    // raw stage; the weight rows start at RAW_A
-    auto load_row = [&](uint32_t sraw, int row, int jc, uint4& p0, uint4& p1, uint2& k) {
-      const uint32_t rb = sraw + (row < 128 ? row * 128 : Cfg::RAW_A + (row - 128) * 128);
-      const int sw = row & 7;
-      p0 = gf_lds128(rb + (((2 * jc) ^ sw) << 4));
-      p1 = gf_lds128(rb + (((2 * jc + 1) ^ sw) << 4));
-      k = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + row * 8);
-    };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int n0 = (t % n_tiles_n) * BN;
       for (int c = 0; c < n_main && ok; c += GF_CPS) {
         if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
         const int nv = min(GF_CPS, n_main - c);
         for (int jc = 0; jc < nv; ++jc, ++q) {
           if (q % Cfg::GROUPS != grp) continue;
-          uint4 pa0, pa1, pb0, pb1;
-          uint2 ka, kb;
-          // The first unit is expanded into registers before the slot is known to be free, so that only
-          // stores (and the second unit) remain on the path between "slot free" and "stage ready".
+          // The row is expanded into registers before the slot is known to be free, so that only the
+          // tensor-memory store remains on the path between "slot free" and "stage ready".
           uint32_t y1[32];
-          if (A8 && first_is_act) {
+          const uint2 ka = gf_lds64(sraw + Cfg::OFF_C + jc * 128 * 8 + rowA * 8);
+          if constexpr (A8) {
             // 8-bit codes: 64 bytes of this row = four 16-byte pieces of box jc >> 1.  A byte alone in a zero
             // half is the subnormal q * 2^-24, so (q - z) * s is one packed FMA again; the values are emitted
             // in the K order the 4-bit weight expansion produces (see expand_word).
@@ -304,7 +305,6 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
             uint4 pq[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) pq[u] = gf_lds128(rb + ((((jc & 1) * 4 + u) ^ (rowA & 7)) << 4));
-            ka = gf_lds64(sraw + Cfg::OFF_C + jc * Cfg::ROWS * 8 + rowA * 8);
             const uint32_t w16[16] = {pq[0].x, pq[0].y, pq[0].z, pq[0].w, pq[1].x, pq[1].y, pq[1].z, pq[1].w,
                                       pq[2].x, pq[2].y, pq[2].z, pq[2].w, pq[3].x, pq[3].y, pq[3].z, pq[3].w};
 #pragma unroll
@@ -319,42 +319,23 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
                 y[3] = hfma2_u(__byte_perm(wh, 0u, 0x4341), ka.x, ka.y);
               }
           } else {
-            load_row(sraw, rowA, jc, pa0, pa1, ka);
+            // two 16-byte pieces of the swizzled 128-byte raw row
+            const uint32_t rb = sraw + rowA * 128;
+            const int sw = rowA & 7;
+            const uint4 pa0 = gf_lds128(rb + (((2 * jc) ^ sw) << 4));
+            const uint4 pa1 = gf_lds128(rb + (((2 * jc + 1) ^ sw) << 4));
             const uint32_t w8[8] = {pa0.x, pa0.y, pa0.z, pa0.w, pa1.x, pa1.y, pa1.z, pa1.w};
             const uint32_t mhi = hmul2_2m4(ka.x);
-            const uint32_t xr1 = (first_is_act && ASYM) ? 0u : 0x00080008u;
+            const uint32_t xr1 = ASYM ? 0u : 0x00080008u;
 #pragma unroll
             for (int i = 0; i < 8; ++i) expand_word(w8[i], xr1, ka.x, mhi, ka.y, y1 + 4 * i);
           }
-          load_row(sraw, rowB, jc, pb0, pb1, kb);
           const int es = exp_slot(q);
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sB = exp_base + es * Cfg::EXP_STAGE;
-          if (first_is_act) {      // activation rows -> TMEM
-            tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y1);
-          } else {                 // (fifth warp) weight rows -> smem
-            const int rw = rowA - 128;
-            const uint32_t dst = sB + rw * 128;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              gf_sts128(dst + (uint32_t)((i ^ (rw & 7)) << 4), y1[4 * i], y1[4 * i + 1], y1[4 * i + 2], y1[4 * i + 3]);
-          }
-          {   // second unit: weight rows -> smem
-            const uint32_t w8[8] = {pb0.x, pb0.y, pb0.z, pb0.w, pb1.x, pb1.y, pb1.z, pb1.w};
-            const uint32_t mhi = hmul2_2m4(kb.x);
-            const int rw = rowB - 128;
-            const uint32_t dst = sB + rw * 128;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              uint32_t y[4];
-              expand_word(w8[i], 0x00080008u, kb.x, mhi, kb.y, y);
-              gf_sts128(dst + (uint32_t)((i ^ (rw & 7)) << 4), y[0], y[1], y[2], y[3]);
-            }
-          }
-          if (first_is_act) tmem_wait_st();
+          tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y1);
+          tmem_wait_st();
           tc_fence_before();
-          fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(expf_bar(es));
         }
@@ -363,48 +344,30 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         if (lane == 0) mbar_arrive(rawe_bar(r.s));
         r.next();
       }
-      // tail: the weights' bf16 tile (already divided by cs) goes by TMA straight into the stage's slot,
-      // issued by the group that owns the stage once the slot is free; the activations' tile (divided by
-      // rs) arrives in the raw ring and its rows are copied to TMEM like an expanded chunk.
+      // tail: the activations' bf16 tile (already divided by rs) arrives in the raw ring and its rows are
+      // copied to TMEM like an expanded chunk
       for (int st = 0; st < n_tail && ok; ++st, ++q) {
         if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         if (q % Cfg::GROUPS == grp) {
           const int es = exp_slot(q);
+          const uint32_t rb = raw_base + r.s * Cfg::RAW_STAGE + rowA * 128;
+          uint32_t y[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v = gf_lds128(rb + (uint32_t)((i ^ (rowA & 7)) << 4));
+            y[4 * i] = v.x; y[4 * i + 1] = v.y; y[4 * i + 2] = v.z; y[4 * i + 3] = v.w;
+          }
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t bar = expf_bar(es);
-          if (gw == 0 && lane == 0) {
-            mbar_expect_tx_only(bar, Cfg::B_EXP);
-            tma_load_2d(exp_base + es * Cfg::EXP_STAGE, &tm.wt, bar, st * 64, n0);
-            issued_q[0] = issued_q[1];
-            issued_q[1] = q;
-          }
-          if (first_is_act) {
-            const uint32_t rb = raw_base + r.s * Cfg::RAW_STAGE + rowA * 128;
-            uint32_t y[32];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const uint4 v = gf_lds128(rb + (uint32_t)((i ^ (rowA & 7)) << 4));
-              y[4 * i] = v.x; y[4 * i + 1] = v.y; y[4 * i + 2] = v.z; y[4 * i + 3] = v.w;
-            }
-            tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y);
-            tmem_wait_st();
-          }
+          tmem_st32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Cfg::TMEM_A0 + es * 32, y);
+          tmem_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar);
+          if (lane == 0) mbar_arrive(expf_bar(es));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(rawe_bar(r.s));
         r.next();
-      }
-    }
-    if (!ok && gw == 0 && lane == 0) {
-      const long long t0 = clock64();
-      for (int i = 0; i < 2; ++i) {
-        if (issued_q[i] < 0) continue;
-        while (!mbar_try(expf_bar(exp_slot(issued_q[i])), exp_phase(issued_q[i])))
-          if (clock64() - t0 > kWaitLimitCycles / 8) { if (a.status) atomicCAS(a.status, 0, ERR_WAIT_DRAIN); break; }
       }
     }
   } else if (warp == W_MMA) {
@@ -420,16 +383,45 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         if (!mbar_wait_hot(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d = tmem_base + buf * BN;
-        for (int st = 0; st < n_main + n_tail; ++st, ++q) {
-          const int es = q % GF_EXP_STAGES;
-          if (!mbar_wait_hot(expf_bar(es), (uint32_t)((q / GF_EXP_STAGES) & 1), abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t bdesc = smem_desc_sw128(exp_base + es * Cfg::EXP_STAGE);
-          const uint32_t a_tmem = tmem_base + Cfg::TMEM_A0 + es * 32;
-          const uint32_t idesc = st < n_main ? idesc_h : idesc_bf;
+        // A UMMA occupies the issuing thread until the tensor pipe has taken it, so whatever else this thread
+        // does between UMMAs is time the pipe idles; a barrier test costs about a hundred cycles, hit or miss.
+        // So stages go two at a time: the four tests of a pair are issued back to back (their latencies
+        // overlap) and eight UMMAs follow without a break.
+        const int ns = n_main + n_tail;
+        for (int st = 0; st < ns && ok;) {
+          const int nb = min(2, ns - st);
+          int es[2];
+          uint32_t ph[2];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) umma_f16_ts(d, a_tmem + 8 * j, bdesc + 2 * j, idesc, (st > 0 || j > 0) ? 1u : 0u);
-          umma_commit(expe_bar(es));
+          for (int i = 0; i < 2; ++i) {
+            const int qi = q + (i < nb ? i : 0);
+            es[i] = qi % GF_EXP_STAGES;
+            ph[i] = (uint32_t)((qi / GF_EXP_STAGES) & 1);
+          }
+          const uint32_t rdy = mbar_test4(expw_bar(es[0]), ph[0], expf_bar(es[0]), ph[0], expw_bar(es[1]), ph[1],
+                                          expf_bar(es[1]), ph[1]);
+          if (rdy != 15u) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (!(rdy & (1u << (2 * i))) && ok) ok = mbar_wait_hot(expw_bar(es[i]), ph[i], abort_flag, a.status, ERR_WAIT_FULL);
+              if (!(rdy & (2u << (2 * i))) && ok) ok = mbar_wait_hot(expf_bar(es[i]), ph[i], abort_flag, a.status, ERR_WAIT_FULL);
+            }
+            if (!ok) break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            if (i < nb) {
+              const uint64_t bdesc = smem_desc_sw128(exp_base + es[i] * Cfg::EXP_STAGE);
+              const uint32_t a_tmem = tmem_base + Cfg::TMEM_A0 + es[i] * 32;
+              const uint32_t idesc = (st + i) < n_main ? idesc_h : idesc_bf;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) umma_f16_ts(d, a_tmem + 8 * j, bdesc + 2 * j, idesc, (st + i > 0 || j > 0) ? 1u : 0u);
+              umma_commit(expe_bar(es[i]));
+            }
+          }
+          st += nb;
+          q += nb;
         }
         if (ok) { umma_commit(accf_bar(buf)); ++use; }
       }
@@ -610,6 +602,41 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
   }
 }
 
+// Weight pre-pass: codes + records -> the fp16 panel [N, n_chunks * 64] the GEMM's weight-tile TMA reads.
+// One thread = one row x one chunk: 32 bytes of codes in, 128 bytes out, with the arithmetic and the K
+// order of the activation converters (expand_word), so a dot product pairs the right values.
+__global__ void __launch_bounds__(256)
+expand_weight_panel_kernel(const uint8_t* __restrict__ wq, int64_t w_row_bytes, const uint2* __restrict__ rec, int64_t ld_rec,
+                           int64_t N, int n_chunks, uint4* __restrict__ panel) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= N * n_chunks) return;
+  const int64_t n = tid / n_chunks;
+  const int c = (int)(tid - n * n_chunks);
+  const uint4* src = reinterpret_cast<const uint4*>(wq + n * w_row_bytes + (int64_t)c * 32);
+  const uint4 p0 = __ldg(src), p1 = __ldg(src + 1);
+  const uint2 k = __ldg(rec + (int64_t)c * ld_rec + n);
+  const uint32_t w8[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+  const uint32_t mhi = hmul2_2m4(k.x);
+  uint4* dst = panel + tid * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t y[4];
+    expand_word(w8[i], 0x00080008u, k.x, mhi, k.y, y);
+    dst[i] = make_uint4(y[0], y[1], y[2], y[3]);
+  }
+}
+
+int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st) {
+  if (N <= 0 || n_chunks <= 0) return DIROTQ_OK;
+  const int64_t total = N * n_chunks;
+  return launch_pdl(expand_weight_panel_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, wq,
+                    (int64_t)n_chunks * 32, reinterpret_cast<const uint2*>(rec), f16_ld_weight(N), N, n_chunks,
+                    reinterpret_cast<uint4*>(panel)) == cudaSuccess
+             ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
 // Records are read in whole tiles of rows (bulk copies, no bounds handling), so the record arrays are
 // padded: activations to 128 rows, weights to 768 (a multiple of every column-tile width).
 int64_t f16_ld_act(int64_t M) { return round_up64(M, 128); }
@@ -667,7 +694,7 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.a_mode != DIROTQ_INT4_SYM && a.a_mode != DIROTQ_INT4_ASYM && a.a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
-      (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_const) & 15))
+      (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_panel) & 15) || !a.w_panel)
     return DIROTQ_E_ALIGN;
   int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
 #ifdef GF_FORCE_BN
@@ -677,8 +704,8 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   int rc = make_tmap_2d_sw(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
                            (uint64_t)a.x_row_bytes, 32 * GF_CPS, 128, 32 * GF_CPS);
   if (rc) return rc;
-  rc = make_tmap_2d_sw(&tm.wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, (uint64_t)a.w_row_bytes, (uint64_t)a.N,
-                       (uint64_t)a.w_row_bytes, 32 * GF_CPS, BN, 32 * GF_CPS);
+  rc = make_tmap_2d(&tm.wp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.w_panel, (uint64_t)a.n_chunks * 64, (uint64_t)a.N,
+                    (uint64_t)a.n_chunks * 128, BN);
   if (rc) return rc;
   rc = make_tmap_2d_sw(&tm.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2,
                        32, 32, 64);
@@ -690,7 +717,7 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
     if (rc) return rc;
   } else {
     tm.xt = tm.xq;
-    tm.wt = tm.wq;
+    tm.wt = tm.wp;
   }
   const int amode = a.a_mode == DIROTQ_INT4_SYM ? 0 : a.a_mode == DIROTQ_INT4_ASYM ? 1 : 2;
   switch (BN * 4 + amode) {

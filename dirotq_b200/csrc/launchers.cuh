@@ -118,11 +118,8 @@ struct GemmIntF16Args {
   const uint2* a_const;        // [n_chunks, ldm] records {s*2^24/rs, -(z*s)/rs}, fp16 pairs
   const float* rs;             // [M] row powers of two
   int64_t ldm;                 // f16_ld_act(M)
-  const uint8_t* wq;           // weight codes [N, n_chunks * 32]
-  int64_t w_row_bytes;
-  const uint2* w_const;        // [n_chunks, ldn] records, z = 8
+  const void* w_panel;         // [N, n_chunks * 64] fp16: (qw - 8) * sw / cs, in the converters' K order
   const float* cs;             // [N] column powers of two
-  int64_t ldn;                 // f16_ld_weight(N)
   const __nv_bfloat16* xt;     // [M, kt_pitch] tail / rs
   const __nv_bfloat16* wt;     // [N, kt_pitch] tail / cs
   int kt;
@@ -155,6 +152,7 @@ struct GemmFp4Args {
 int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st);
 int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st);
+int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st);
 int64_t f16_ld_act(int64_t M);
 int64_t f16_ld_weight(int64_t N);
 int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm,

@@ -56,6 +56,30 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t
       : "memory");
   return ok != 0;
 }
+// Four phase tests issued back to back, so that their latencies overlap (a test costs about a hundred
+// cycles even when the phase has long completed).  Bit i of the result: barrier i's phase is complete.
+__device__ __forceinline__ uint32_t mbar_test4(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2,
+                                               uint32_t b3, uint32_t p3) {
+  uint32_t m;
+  asm volatile(
+      "{\n\t.reg .pred q0, q1, q2, q3;\n\t.reg .u32 t0, t1, t2, t3;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 q2, [%5], %6;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 q3, [%7], %8;\n\t"
+      "selp.u32 t0, 1, 0, q0;\n\t"
+      "selp.u32 t1, 2, 0, q1;\n\t"
+      "selp.u32 t2, 4, 0, q2;\n\t"
+      "selp.u32 t3, 8, 0, q3;\n\t"
+      "or.b32 t0, t0, t1;\n\t"
+      "or.b32 t2, t2, t3;\n\t"
+      "or.b32 %0, t0, t2;\n\t}"
+      : "=r"(m)
+      : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2), "r"(b3), "r"(p3)
+      : "memory");
+  return m;
+}
+
 // Bounded wait.  Waiters sleep in hardware (20 us per poll) instead of spinning, so they do not
 // compete with the working warps for issue slots; between polls the shared abort flag and the clock
 // are checked.  `abort_flag` lives in shared memory: once any role gave up, all later waits of the

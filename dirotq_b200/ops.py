@@ -257,6 +257,7 @@ class FoldedWeightF16:
     mult: torch.Tensor                    # uint8: 8-byte records per (chunk, channel)
     colscale: torch.Tensor                # fp32 [ldn]
     tail: Optional[torch.Tensor]          # bf16 [N, tail_pitch] = w_tail / colscale
+    panel: Optional[torch.Tensor] = None  # fp16 [N, n_chunks * 64]: resident expanded weights (optional)
 
 
 def fold_weight_scales_f16(w: PackedWeightInt4, w_tail: Optional[torch.Tensor], tail_total: int) -> FoldedWeightF16:
@@ -276,10 +277,21 @@ def fold_weight_scales_f16(w: PackedWeightInt4, w_tail: Optional[torch.Tensor], 
     return FoldedWeightF16(mult, cs, tail_out)
 
 
-def f16_workspace_bytes(act: ActBuffers) -> int:
+def expand_weight_panel_f16(w: PackedWeightInt4, folded: FoldedWeightF16) -> torch.Tensor:
+    """fp16 [N, n_chunks * 64] panel of (q_w - 8) * s_w / colscale, in the K order of the GEMM's activation
+    converters: what dirotq_gemm_w4a4_int_f16 otherwise rebuilds in its workspace on every call."""
+    n = int(_lib.lib().dirotq_weight_panel_bytes(w.n_chunks, w.N))
+    panel = torch.empty(n // 2, dtype=torch.float16, device=w.codes.device)
+    check(_lib.lib().dirotq_expand_weight_panel_f16(w.n_chunks, w.N, _ptr(w.codes), _ptr(folded.mult), _ptr(panel),
+                                                    _stream()), "dirotq_expand_weight_panel_f16")
+    return panel[: w.N * w.n_chunks * 64].view(w.N, w.n_chunks * 64)
+
+
+def f16_workspace_bytes(act: ActBuffers, N_panel: int = 0) -> int:
+    """N_panel = the layer's out_features when the call has to rebuild the weight panel; 0 with a resident one."""
     lay = act.layout
     tp = lay.tail_pitch if lay.tail_total > 0 else 0
-    return max(256, int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(act.M, lay.n_chunks, tp)))
+    return max(256, int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(act.M, N_panel, lay.n_chunks, tp)))
 
 
 def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeightF16, bias: Optional[torch.Tensor],
@@ -290,12 +302,14 @@ def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeight
     dev = act.codes.device
     y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     tp = lay.tail_pitch if lay.tail_total > 0 else 0
-    need = int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(M, lay.n_chunks, tp))
+    need = int(_lib.lib().dirotq_gemm_w4a4_int_f16_workspace_bytes(M, 0 if folded.panel is not None else N,
+                                                                   lay.n_chunks, tp))
     ws = workspace if workspace is not None else torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     if M == 0:
         return y
     check(_lib.lib().dirotq_gemm_w4a4_int_f16(act.fmt.mode, M, N, lay.n_chunks, _ptr(act.codes), _ptr(act.scales),
-                                              _ptr(act.zeros), _ptr(w.codes), _ptr(folded.mult), _ptr(folded.colscale),
+                                              _ptr(act.zeros), _ptr(w.codes), _ptr(folded.mult), _ptr(folded.panel),
+                                              _ptr(folded.colscale),
                                               _ptr(act.tail), _ptr(folded.tail), lay.tail_total, lay.tail_pitch,
                                               _ptr(bias), _ptr(y), _ptr(ws), ws.numel(), _ptr(status_word(dev)),
                                               _stream()), "dirotq_gemm_w4a4_int_f16")

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DIROTQ_ABI_VERSION 3
+#define DIROTQ_ABI_VERSION 4
 
 /* ---- activation quantiser modes (ActQuantizer.configure, utils/quant_utils.py:182-199) ---- */
 enum {
@@ -166,8 +166,9 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
 /* Integer activations at tensor rate (tcgen05 kind::f16): the same product as dirotq_gemm_w4a4_int for
  * 4-bit and 8-bit activation codes, computed the way the reference's own linear computes it -- a 16-bit GEMM with fp32
  * accumulation over the dequantised values s*(q-z) and s_w*q_w (dirotq_fused_unrotation_fast.py:141)
- * -- while both operands stay 4-bit in memory: codes are expanded to fp16 between shared memory and
- * the tensor core, one accumulator runs over the whole K, and nothing is drained per chunk.
+ * -- while both operands stay 4-bit in memory: activation codes are expanded to fp16 between shared
+ * memory and the tensor core, weight codes once per call into an fp16 scratch panel that the GEMM's
+ * tiles read through L2; one accumulator runs over the whole K, and nothing is drained per chunk.
  * Activation values are exact in fp16; weight values are rounded once to fp16 (the reference rounds
  * them to bf16).  Row / column powers of two keep every scale inside the fp16 range.
  *
@@ -175,20 +176,29 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
  *   w_mult: dirotq_fold_weight_records_bytes(n_chunks, N) bytes of 8-byte per-(chunk, channel)
  *   records (fp16 pairs: scale * 2^24 and -8 * scale, each divided by the channel's power of two), w_colscale fp32 [N]; w_tail bf16 [N, tail_pitch] -> w_tail_out = w_tail / colscale
  *   (may be NULL when tail_total == 0).
- * dirotq_gemm_w4a4_int_f16: a_mode DIROTQ_INT4_SYM, DIROTQ_INT4_ASYM or DIROTQ_INT8_ASYM; workspace of
- *   dirotq_gemm_w4a4_int_f16_workspace_bytes(M, n_chunks, tail_pitch) bytes, 256-byte aligned
- *   (per-call activation multipliers and the scaled copy of the tail).
+ * dirotq_expand_weight_panel_f16: w_codes + w_mult -> panel, fp16 [N, n_chunks * 64]
+ *   (dirotq_weight_panel_bytes(n_chunks, N) bytes, 16-byte aligned): (q_w - 8) * s_w / colscale in the
+ *   K order the activation converters produce.  A caller that prefers 2 bytes per weight of resident memory to a
+ *   small per-call pre-pass builds it once and passes it as w_panel.
+ * dirotq_gemm_w4a4_int_f16: a_mode DIROTQ_INT4_SYM, DIROTQ_INT4_ASYM or DIROTQ_INT8_ASYM; w_panel NULL: the panel
+ *   is rebuilt from w_codes / w_mult in the workspace on every call (w_codes / w_mult may be NULL when w_panel
+ *   is given); workspace of dirotq_gemm_w4a4_int_f16_workspace_bytes(M, N_panel, n_chunks, tail_pitch) bytes,
+ *   256-byte aligned (per-call activation multipliers, the scaled copy of the tail and, for N_panel = N > 0,
+ *   the panel; N_panel = 0 for callers that pass their own).
  */
 size_t dirotq_fold_weight_records_bytes(int32_t n_chunks, int64_t N);
 int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_scales, const void* w_tail,
                                   int32_t tail_total, int32_t tail_pitch, void* w_mult, float* w_colscale,
                                   void* w_tail_out, void* stream);
-size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int32_t n_chunks, int32_t tail_pitch);
+size_t dirotq_weight_panel_bytes(int32_t n_chunks, int64_t N);
+int dirotq_expand_weight_panel_f16(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
+                                   void* stream);
+size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int64_t N_panel, int32_t n_chunks, int32_t tail_pitch);
 int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
                              const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
-                             const float* w_colscale, const void* x_tail, const void* w_tail_scaled,
-                             int32_t tail_total, int32_t tail_pitch, const void* bias, void* y, void* workspace,
-                             size_t workspace_bytes, int32_t* status, void* stream);
+                             const void* w_panel, const float* w_colscale, const void* x_tail,
+                             const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias, void* y,
+                             void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* NVFP4 (tcgen05 kind::mxf4nvf4, UE4M3 scale factors in TMEM):
  *   y = out_scale * (sum_blocks sfx sfw (e2m1.e2m1) + x_tail . w_tail_scaled) + bias
@@ -238,6 +248,9 @@ typedef struct dirotq_linear {
    * diffusers' GELU(approximate="tanh") around ff.net.0.proj).  Supported by the tensor-rate integer GEMM
    * and the NVFP4 GEMM; DIROTQ_E_UNSUPPORTED on the exact-integer route. */
   int32_t epilogue_act;
+  /* Optional resident fp16 weight panel from dirotq_expand_weight_panel_f16 (tensor-rate integer route only);
+   * NULL: rebuilt in the workspace on every call. */
+  const void* w_panel_f16;
 } dirotq_linear;
 
 size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M);
