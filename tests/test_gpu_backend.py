@@ -317,3 +317,26 @@ def test_empty_batch_through_the_wrapper():
     w = dit.make_wrapped_linear(dit.LayerDef("attn1.to_q", 256, 128, tail=64), "int4", 5, "cuda")
     y = w(torch.zeros(2, 0, 256, dtype=torch.bfloat16, device="cuda"))
     assert tuple(y.shape) == (2, 0, 128) and y.dtype == torch.bfloat16
+
+
+def test_resident_weight_panel_through_the_wrapper():
+    """backend.CACHE_WEIGHT_PANEL: the layer keeps its fp16 weight panel instead of rebuilding it per call; same bits."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    ld = dit.LayerDef("attn1.to_q", 384, 256, tail=64)
+    x = synth_activations(300, 384, torch.Generator().manual_seed(4)).reshape(1, 300, 384).cuda()
+    ys = []
+    for cache in (False, True):
+        old = backend.CACHE_WEIGHT_PANEL
+        backend.CACHE_WEIGHT_PANEL = cache
+        try:
+            w = dit.make_wrapped_linear(ld, "int4", 33, "cuda")
+            root = nn.Module()
+            root.add_module("to_q", w)
+            backend.preconvert_rotations_to_device(root, "cuda")
+            ys.append(w(x))
+            assert (w._b200_state.folded.panel is not None) == cache
+        finally:
+            backend.CACHE_WEIGHT_PANEL = old
+    ops.check_status()
+    assert torch.equal(ys[0].view(torch.int16), ys[1].view(torch.int16))

@@ -218,3 +218,54 @@ def test_int_f16_gemm_empty_batch():
     y = ops.gemm_w4a4_int_f16(empty, pk, folded, bias.cuda())
     assert tuple(y.shape) == (0, 16)
     ops.check_status()
+
+
+# K order of a 64-slot chunk in the expanded operands: per planar-32 block (byte j = code j | code 16+j << 4),
+# per 32-bit word wi of the block: low nibbles of bytes 0 and 2, high nibbles of bytes 0 and 2, then bytes 1 and 3
+def _panel_k_order():
+    order = []
+    for b in range(2):
+        for wi in range(4):
+            for j in (4 * wi, 4 * wi + 2, 16 + 4 * wi, 16 + 4 * wi + 2, 4 * wi + 1, 4 * wi + 3, 16 + 4 * wi + 1, 16 + 4 * wi + 3):
+                order.append(32 * b + j)
+    return torch.tensor(order)
+
+
+@pytest.mark.parametrize("N,D,tail", [(256, 320, 64), (1152, 1152, 64), (136, 160, 0)])
+def test_weight_panel_f16_is_the_single_rounding_of_the_folded_product(N, D, tail):
+    """dirotq_expand_weight_panel_f16: element = fp16((q + 8) * 2^-24 * mult - 8 s') with ONE rounding, mult and the
+    addend being the fp16 record of its (chunk, channel); checked bit for bit against float64 arithmetic."""
+    from dirotq_b200 import ops
+    fmt = ops.ActFormat(ops.INT4_SYM, D, tail_len=tail)
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, 8, N, fmt, 41)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, N, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
+    panel = ops.expand_weight_panel_f16(pk, folded).cpu()
+    assert panel.dtype == torch.float16 and tuple(panel.shape) == (N, lay.n_chunks * 64)
+    ldn = folded.mult.numel() // (8 * lay.n_chunks)
+    rec = folded.mult.cpu().view(torch.float16).reshape(lay.n_chunks, ldn, 4)[:, :N]       # {mult, mult, add, add}
+    mult, add = rec[..., 0].double().t(), rec[..., 2].double().t()                          # [N, n_chunks]
+    assert torch.equal(rec[..., 0], rec[..., 1]) and torch.equal(rec[..., 2], rec[..., 3])
+    q = torch.zeros(N, lay.n_chunks * 64, dtype=torch.float64)
+    q[:, : qw.shape[1]] = qw.double()
+    q = q.reshape(N, lay.n_chunks, 64)[:, :, _panel_k_order()]
+    # codes are stored offset-binary (q + 8) as subnormal fp16 (q + 8) * 2^-24
+    want = ((q + 8.0) * 2.0 ** -24 * mult.unsqueeze(-1) + add.unsqueeze(-1)).to(torch.float16).reshape(N, -1)
+    assert torch.equal(panel.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("mode", ["sym", "asym", "int8"])
+def test_resident_weight_panel_gives_the_same_bits_as_the_per_call_one(mode):
+    from dirotq_b200 import ops
+    m = {"sym": ops.INT4_SYM, "asym": ops.INT4_ASYM, "int8": ops.INT8_ASYM}[mode]
+    fmt = ops.ActFormat(m, 1152, tail_len=64)
+    x, act, dec, qw, sw, pk, w_tail, bias = _setup_int(ops, 700, 384, fmt, 42)
+    lay = act.layout
+    wt = ops.pad_tail_weight(w_tail, lay.tail_pitch, 384, "cuda")
+    folded = ops.fold_weight_scales_f16(pk, wt, lay.tail_total)
+    y0 = ops.gemm_w4a4_int_f16(act, pk, folded, bias.cuda())
+    folded.panel = ops.expand_weight_panel_f16(pk, folded)
+    y1 = ops.gemm_w4a4_int_f16(act, pk, folded, bias.cuda())
+    ops.check_status()
+    assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
