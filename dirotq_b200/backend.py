@@ -120,6 +120,24 @@ class LayerState:
         return ws
 
 
+def kernel_launches(st: Optional[LayerState]) -> int:
+    """Library kernels one forward of a wrapped linear launches.  A W4A16 layer (no LayerState): weight
+    dequantisation + GEMM.  W4A4: rotate/quantise + GEMM; the tensor-rate integer GEMM adds the scale-folding
+    kernel and, unless the layer keeps a resident panel, the weight-panel pre-pass; a sibling that reuses the
+    activations of the layer before it runs only its own GEMM (and pre-pass)."""
+    if st is None:
+        return 2
+    n = 1 if (st.shared is not None and st.member_id > 0) else 2
+    if st.folded is not None:
+        n += (0 if (st.shared is not None and st.member_id > 0) else 1) + (1 if st.folded.panel is None else 0)
+    follower = st.shared is not None and st.member_id > 0
+    if st.rot_t is None and st.layout.tail_total > 0 and not follower:
+        n += 1                              # quantise-only layers copy their passthrough channels in a kernel of its own
+    if st.hadamard_low_dim:
+        n += 1
+    return n
+
+
 def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One wrapped linear through the C ABI: x2d bf16 [M, D] -> bf16 [M, N]."""
     assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()

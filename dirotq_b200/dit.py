@@ -218,14 +218,8 @@ class LinearPathStep(nn.Module):
     def kernel_launches_per_step(self) -> int:
         """Library kernels per step: rotate/quantise (or weight dequantise) + GEMM per linear, plus the
         scale-folding kernel of the tensor-rate INT4 GEMM where a layer uses it."""
-        n = 0
-        for lyr in self.layers:
-            st = getattr(lyr, "_b200_state", None)
-            if st is not None and st.shared is not None and st.member_id > 0:
-                n += 1                      # GEMM only: the sibling before it left the codes in place
-            else:
-                n += 3 if (st is not None and st.folded is not None) else 2
-        return n
+        from . import backend
+        return sum(backend.kernel_launches(getattr(lyr, "_b200_state", None)) for lyr in self.layers)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = x

@@ -203,14 +203,8 @@ class FluxLinearStep:
         return lin, rot
 
     def kernel_launches_per_step(self) -> int:
-        n = 0
-        for l in self._flat:
-            st = getattr(l, "_b200_state", None)
-            if st is not None and st.shared is not None and st.member_id > 0:
-                n += 1
-            else:
-                n += 3 if (st is not None and st.folded is not None) else 2
-        return n
+        from . import backend
+        return sum(backend.kernel_launches(getattr(l, "_b200_state", None)) for l in self._flat)
 
     def rows_per_rank(self, stream: str) -> int:
         return self.rows[stream] // self.world
