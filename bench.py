@@ -404,9 +404,9 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
                               "the INT4 GEMM at M=16384, N=K=1152 over its algorithmic bytes; traffic grows with M and N)"}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the captured launch (14.3 MB: the 38 MB of output it wrote
+# dram__bytes_read.sum + dram__bytes_write.sum of the captured launch (16.3 MB: the 38 MB of output it wrote
 # were still in the 126 MB L2 when the launch ended) / its algorithmic bytes (52 MB); see profiles/
-NCU_TRAFFIC_RATIO = 0.275
+NCU_TRAFFIC_RATIO = 0.31
 
 
 def gemm_algorithmic_bytes(M, N, lay, quant):
