@@ -16,6 +16,7 @@ from __future__ import annotations
 import ctypes as C
 import sys
 import warnings
+import dataclasses
 from dataclasses import dataclass, field
 from typing import Dict, Optional
 
@@ -241,6 +242,23 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
         rot_t = torch.block_diag(*[U[h].t() for h in range(U.shape[0])]).contiguous().to(torch.bfloat16)
     elif fused and not had_dim and getattr(w, "perm_idx", None) is not None:
         perm = w.perm_idx.to(device=dev, dtype=torch.int64).contiguous()
+    packed = getattr(w, "_b200_packed", None)
+    if packed is not None:
+        if packed.get("kind") != "w4a4" or packed["fmt"] != dataclasses.asdict(fmt) or packed["out_features"] != N:
+            raise RuntimeError("packed-weight cache entry does not match this layer's quantiser configuration "
+                               f"(cached {packed.get('fmt')}, layer {dataclasses.asdict(fmt)}): rebuild the cache")
+        t = lambda v: None if v is None else v.to(dev).contiguous()
+        w_codes, w_scales, w_sum = t(packed["w_codes"]), t(packed["w_scales"]), t(packed["w_sum"])
+        w_tail_p, bias = t(packed["w_tail"]), t(packed["bias"])
+        folded = None
+        if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM, ops.INT8_ASYM):
+            pk = ops.PackedWeightInt4(N, lay.q_len, lay.group, lay.n_chunks, w_codes, w_scales, w_sum)
+            folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
+            if CACHE_WEIGHT_PANEL:
+                folded.panel = ops.expand_weight_panel_f16(pk, folded)
+        return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias,
+                          float(packed["w_tensor_scale"]), int(packed["n_lossy_groups"]), folded,
+                          hadamard_low_dim=had_dim, hadamard_flips=had_flips)
     have_codes = bool(explicit) and ("codes" in explicit or "nibbles" in explicit)
     have_tail = lay.tail_total == 0 or (bool(explicit) and "w_tail" in explicit)
     w_low = w_tail = None
@@ -309,6 +327,17 @@ def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int 
     if K % 64 or N % 8 or group != 64:
         return None
     dev = torch.device(device)
+    packed = getattr(w, "_b200_packed", None)
+    if packed is not None:
+        if packed.get("kind") != "w4a16" or packed["N"] != N or packed["K"] != K:
+            raise RuntimeError("packed-weight cache entry does not match this 16-bit-activation layer: rebuild the cache")
+        t = lambda v: None if v is None else v.to(dev).contiguous()
+        if packed["weight"] == "nvfp4":
+            pk = ops.PackedWeightNvfp4(N, K, K // 64, float(packed["tensor_scale"]), t(packed["codes"]), t(packed["sf"]))
+        else:
+            pk = ops.PackedWeightInt4(N, K, 64, K // 64, t(packed["codes"]), t(packed["scales"]), t(packed["wsum"]))
+        n = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(N, K))
+        return W4A16State(pk, t(packed["bias"]), torch.empty(n, dtype=torch.uint8, device=dev))
     if explicit and "nibbles" in explicit:
         pk = pack.convert_dirotq_low_weight_to_b200_fp4(None, explicit["tensor_scale"], explicit["nibbles"],
                                                         explicit["scales_e4m3"])
@@ -427,6 +456,59 @@ def _wrapper_classes():
     if ref is not None and hasattr(ref, "ActQuantWrapper"):
         classes.append(ref.ActQuantWrapper)     # drop-in use inside the reference project
     return classes
+
+
+PACKED_CACHE_VERSION = 1
+
+
+def save_packed_weights(transformer, path) -> int:
+    """Write the packed weights of every prepared wrapped linear (codes, group scales, group sums, 16-bit tail,
+    bias, tensor scale, and the activation format they were packed for) to ``path``; returns the number of
+    layers written.  The reference keeps its quantised model as a state_dict of DEQUANTISED bf16 weights
+    (apply_dirotq.py:231-257, 317-349), from which every start-up would have to recover the 4-bit grid and
+    pack again; this file sits next to that cache and can always be rebuilt from it (load the reference cache,
+    preconvert_rotations_to_device, save_packed_weights).  Rotations, permutations and sign flips are not
+    stored: they come from the wrapper's own attributes at load time."""
+    classes = tuple(_wrapper_classes())
+    layers = {}
+    cpu = lambda v: None if v is None else v.detach().cpu()
+    for name, mod in transformer.named_modules():
+        if not isinstance(mod, classes):
+            continue
+        st = getattr(mod, "_b200_state", None)
+        s16 = getattr(mod, "_b200_w4a16", None)
+        if st is not None:
+            layers[name] = {"kind": "w4a4", "fmt": dataclasses.asdict(st.fmt), "out_features": st.out_features,
+                            "w_codes": cpu(st.w_codes), "w_scales": cpu(st.w_scales), "w_sum": cpu(st.w_sum),
+                            "w_tail": cpu(st.w_tail), "bias": cpu(st.bias), "w_tensor_scale": float(st.w_tensor_scale),
+                            "n_lossy_groups": int(st.n_lossy_groups)}
+        elif s16 is not None:
+            pk = s16.w
+            e = {"kind": "w4a16", "N": pk.N, "K": pk.n_chunks * 64, "bias": cpu(s16.bias), "codes": cpu(pk.codes)}
+            if isinstance(pk, ops.PackedWeightNvfp4):
+                e.update(weight="nvfp4", tensor_scale=float(pk.tensor_scale), sf=cpu(pk.sf))
+            else:
+                e.update(weight="int4", scales=cpu(pk.scales), wsum=cpu(pk.wsum))
+            layers[name] = e
+    torch.save({"version": PACKED_CACHE_VERSION, "abi": int(_lib.lib().dirotq_abi_version()), "layers": layers}, path)
+    return len(layers)
+
+
+def load_packed_weights(transformer, path) -> int:
+    """Attach the entries of a save_packed_weights file to the wrapped linears of the same names; the next
+    preconvert_rotations_to_device (or first forward) then uploads them instead of recovering and packing the
+    weights again.  A layer whose quantiser configuration differs from the cached one raises at that point.
+    Returns the number of layers matched; layers absent from the file are packed from their weights as usual."""
+    blob = torch.load(path, map_location="cpu", weights_only=False)
+    if blob.get("version") != PACKED_CACHE_VERSION or blob.get("abi") != int(_lib.lib().dirotq_abi_version()):
+        raise RuntimeError(f"{path}: packed-weight cache of another layout version; rebuild it")
+    classes = tuple(_wrapper_classes())
+    n = 0
+    for name, mod in transformer.named_modules():
+        if isinstance(mod, classes) and name in blob["layers"]:
+            object.__setattr__(mod, "_b200_packed", blob["layers"][name])
+            n += 1
+    return n
 
 
 def patch_forward():

@@ -340,3 +340,48 @@ def test_resident_weight_panel_through_the_wrapper():
             backend.CACHE_WEIGHT_PANEL = old
     ops.check_status()
     assert torch.equal(ys[0].view(torch.int16), ys[1].view(torch.int16))
+
+
+def test_packed_weight_cache_round_trip(tmp_path, monkeypatch):
+    """save_packed_weights / load_packed_weights: a fresh model that loads the file produces the same bits
+    without running the grid recovery or the packing kernels again."""
+    from dirotq_b200 import backend, dit, ops, pack
+    from dirotq_b200.synth import synth_activations
+
+    def build():
+        root = nn.Module()
+        root.add_module("to_q", dit.make_wrapped_linear(dit.LayerDef("attn1.to_q", 384, 256, tail=64), "int4", 51, "cuda"))
+        root.add_module("to_out", dit.make_wrapped_linear(dit.LayerDef("attn1.to_out.0", 384, 384, tail=4, kind="perhead",
+                                                                         heads=12, head_dim=32), "int4", 52, "cuda"))
+        root.add_module("fp4", dit.make_wrapped_linear(dit.LayerDef("attn2.to_q", 384, 256, tail=64), "nvfp4", 53, "cuda"))
+        root.add_module("ff2", dit.make_wrapped_linear(dit.LayerDef("ff.net.2", 512, 384, kind="w4a16"), "int4", 54, "cuda"))
+        return root
+
+    x = synth_activations(260, 384, torch.Generator().manual_seed(6)).reshape(1, 260, 384).cuda()
+    x2 = synth_activations(260, 512, torch.Generator().manual_seed(7)).reshape(1, 260, 512).cuda()
+    a = build()
+    backend.preconvert_rotations_to_device(a, "cuda")
+    ya = [a.to_q(x), a.to_out(x), a.fp4(x), a.ff2(x2)]
+    path = tmp_path / "packed.pt"
+    assert backend.save_packed_weights(a, path) == 4
+
+    b = build()
+    assert backend.load_packed_weights(b, path) == 4
+
+    def boom(*args, **kw):
+        raise AssertionError("the packers must not run when a packed cache entry exists")
+    for mod, name in ((ops, "pack_weight_int4"), (ops, "pack_weight_nvfp4"), (pack, "recover_int4_grid"),
+                      (pack, "convert_dirotq_low_weight_to_b200"), (pack, "convert_dirotq_low_weight_to_b200_fp4")):
+        monkeypatch.setattr(mod, name, boom)
+    backend.preconvert_rotations_to_device(b, "cuda")
+    yb = [b.to_q(x), b.to_out(x), b.fp4(x), b.ff2(x2)]
+    ops.check_status()
+    for u, v in zip(ya, yb):
+        assert torch.equal(u.view(torch.int16), v.view(torch.int16))
+
+    # a layer configured differently from the cached entry is refused
+    c = build()
+    backend.load_packed_weights(c, path)
+    c.to_q.quantizer.high_bits_length = 128
+    with pytest.raises(RuntimeError, match="does not match"):
+        backend.preconvert_rotations_to_device(c, "cuda")
