@@ -235,3 +235,48 @@ class LinearPathStep(nn.Module):
                 else:
                     y = lyr(x)
         return y
+
+
+class HostStreamedStep:
+    """Runs a step whose input and output live in pinned host memory: the host -> device copy of call i + 1 and the
+    device -> host copy of call i run on side streams while the kernels of the neighbouring calls execute (two
+    device input buffers; stream-ordered with events; every call copies its own input and its own result)."""
+
+    def __init__(self, step, x_host: torch.Tensor, y_host: torch.Tensor, device):
+        assert x_host.is_pinned() and y_host.is_pinned()
+        self.step, self.x_host, self.y_host = step, x_host, y_host
+        self.dev = torch.device(device)
+        self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self.x_dev = [torch.empty(x_host.shape, dtype=x_host.dtype, device=self.dev) for _ in range(2)]
+        self.in_ready = [torch.cuda.Event() for _ in range(2)]
+        self.in_free = [torch.cuda.Event() for _ in range(2)]
+        self.out_done = torch.cuda.Event()
+        self.i = 0
+        main = torch.cuda.current_stream(self.dev)
+        for e in self.in_free:
+            e.record(main)
+        self.out_done.record(main)
+
+    def __call__(self):
+        b = self.i & 1
+        self.i += 1
+        main = torch.cuda.current_stream(self.dev)
+        with torch.cuda.stream(self.s_in):
+            self.s_in.wait_event(self.in_free[b])            # the kernels that last read this buffer are done
+            self.x_dev[b].copy_(self.x_host, non_blocking=True)
+            self.in_ready[b].record(self.s_in)
+        main.wait_event(self.in_ready[b])
+        y = self.step(self.x_dev[b])
+        self.in_free[b].record(main)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(done)
+            y.record_stream(self.s_out)
+            self.y_host.copy_(y.reshape(self.y_host.shape), non_blocking=True)
+            self.out_done.record(self.s_out)
+        return y
+
+    def finish(self):
+        """Make the calling stream wait for the last result copy (call before reading y_host or stopping a timer)."""
+        torch.cuda.current_stream(self.dev).wait_event(self.out_done)

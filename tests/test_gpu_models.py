@@ -132,3 +132,21 @@ def test_full_size_rows_are_independent(quant):
     perm = torch.randperm(M, generator=torch.Generator().manual_seed(1)).cuda()
     assert torch.equal(w(x[perm].reshape(1, M, D)).reshape(M, D), y[perm])
     ops.check_status()
+
+
+def test_host_streamed_step_returns_the_same_result():
+    """dit.HostStreamedStep: input copied from pinned memory and result copied back on side streams, call after call."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    step = dit.LinearPathStep(dit.pixart_block(64), 1, "int4", "cuda", seed=1000)
+    backend.preconvert_rotations_to_device(step, "cuda")
+    x_host = synth_activations(512, 1152, torch.Generator().manual_seed(9)).reshape(1, 512, 1152).pin_memory()
+    y_ref = step(x_host.cuda())
+    y_host = torch.empty(tuple(y_ref.shape), dtype=torch.bfloat16).pin_memory()
+    run = dit.HostStreamedStep(step, x_host, y_host, "cuda")
+    for _ in range(3):
+        run()
+    run.finish()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(y_host.view(torch.int16), y_ref.cpu().view(torch.int16))
