@@ -364,6 +364,7 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     ops_total = 0.0
     f16_ws, f16_used = None, False
     bytes_total = 0.0
+    k1_pairs, k1_flops, k1_bytes = [], 0.0, 0.0
     nb = len(step.block)
     for _ in range(max(1, min(steps, 2))):
         for idx, lyr in enumerate(step.layers):
@@ -376,7 +377,16 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
                 bufs[key] = ops.alloc_act(st.fmt, M, dev)
             buf = bufs[key]
             x2d = x_dev.reshape(M, -1)
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
             ops.rotate_quantize(x2d, st.rot_t, st.fmt, out=buf)
+            r1.record()
+            if st.fmt.num_heads == 0:
+                k1_pairs.append((r0, r1))
+                k1_flops += 2.0 * M * ld.in_f * ld.in_f
+                lay = st.layout
+                k1_bytes += 2.0 * M * ld.in_f + 2.0 * ld.in_f * ld.in_f + M * (lay.code_row_bytes + lay.n_chunks * 2
+                                                                               + lay.tail_pitch * 2)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             if quant == "nvfp4":
@@ -403,7 +413,15 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     achieved = ops_total / (t_ms * 1e-3) / 1e12
     kname = "gemm_nvfp4_kernel" if quant == "nvfp4" else (
         "gemm_int_f16_kernel (with its fold_scales_kernel and expand_weight_panel_kernel)" if f16_used else "gemm_int_kernel")
-    return {"bound": "tensor", "kernel": kname,
+    k1 = None
+    if k1_pairs:
+        k1_ms = sum(a.elapsed_time(b) for a, b in k1_pairs)
+        k1 = {"kernel": "rotate_quant_kernel (hidden rotation + split + quantise)", "bound": "tensor",
+              "achieved": k1_flops / (k1_ms * 1e-3) / 1e12, "peak": bf16_sust, "unit": "TFLOP/s",
+              "frac": k1_flops / (k1_ms * 1e-3) / 1e12 / bf16_sust,
+              "hbm_gbs": k1_bytes / (k1_ms * 1e-3) / 1e9, "hbm_peak_gbs": hbm, "hbm_frac": k1_bytes / (k1_ms * 1e-3) / 1e9 / hbm,
+              "launches_timed": len(k1_pairs), "avg_launch_us": k1_ms * 1e3 / len(k1_pairs)}
+    return {"bound": "tensor", "kernel": kname, "rotate_quantise": k1,
             "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained; the INT4 path computes in fp16 on the same tensor pipe, "
                            "dense FP4 is nominally 4x that figure",
