@@ -375,9 +375,19 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     if (lane == 0) {
       const uint32_t idesc_h = idesc_dense(ACC_F32, FMT_F16, FMT_F16, 128, BN);
       const uint32_t idesc_bf = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, BN);
-      int q = 0;
       int use = 0;
       bool ok = true;
+      // loop-invariant pieces of the per-stage operands: barrier addresses are 8 bytes per slot apart, the weight
+      // descriptor's low word holds the slot address >> 4, the activation slots are 32 tensor-memory columns apart
+      int es0 = 0;
+      uint32_t ph0 = 0;
+      const uint32_t expw0 = expw_bar(0);
+      constexpr uint32_t kFullOff = 8u * 2 * GF_EXP_STAGES;      // expw_bar(s) - expf_bar(s)
+      constexpr uint32_t kEmptyOff = 8u * GF_EXP_STAGES;         // expw_bar(s) - expe_bar(s)
+      const uint64_t bdesc0 = smem_desc_sw128(exp_base);
+      const uint32_t bdesc_lo0 = (uint32_t)bdesc0, bdesc_hi = (uint32_t)(bdesc0 >> 32);
+      constexpr uint32_t kDescStep = Cfg::EXP_STAGE >> 4;
+      const uint32_t a_tmem0 = tmem_base + Cfg::TMEM_A0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int buf = use & 1;
         if (!mbar_wait_hot(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
@@ -389,39 +399,34 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
         // overlap) and eight UMMAs follow without a break.
         const int ns = n_main + n_tail;
         for (int st = 0; st < ns && ok;) {
-          const int nb = min(2, ns - st);
-          int es[2];
-          uint32_t ph[2];
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int qi = q + (i < nb ? i : 0);
-            es[i] = qi % GF_EXP_STAGES;
-            ph[i] = (uint32_t)((qi / GF_EXP_STAGES) & 1);
-          }
-          const uint32_t rdy = mbar_test4(expw_bar(es[0]), ph[0], expf_bar(es[0]), ph[0], expw_bar(es[1]), ph[1],
-                                          expf_bar(es[1]), ph[1]);
+          const bool two = st + 1 < ns;
+          // slot / phase of the pair's second stage (the first stage's again when the tile ends on a single one)
+          int es1 = es0;
+          uint32_t ph1 = ph0;
+          if (two && ++es1 == GF_EXP_STAGES) { es1 = 0; ph1 ^= 1u; }
+          const uint32_t w0 = expw0 + 8u * es0, w1 = expw0 + 8u * es1;       // expf / expe lie at fixed offsets from expw
+          const uint32_t rdy = mbar_test4(w0, ph0, w0 - kFullOff, ph0, w1, ph1, w1 - kFullOff, ph1);
           if (rdy != 15u) {
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              if (!(rdy & (1u << (2 * i))) && ok) ok = mbar_wait_hot(expw_bar(es[i]), ph[i], abort_flag, a.status, ERR_WAIT_FULL);
-              if (!(rdy & (2u << (2 * i))) && ok) ok = mbar_wait_hot(expf_bar(es[i]), ph[i], abort_flag, a.status, ERR_WAIT_FULL);
-            }
+            if (!(rdy & 1u)) ok = mbar_wait_hot(w0, ph0, abort_flag, a.status, ERR_WAIT_FULL);
+            if (ok && !(rdy & 2u)) ok = mbar_wait_hot(w0 - kFullOff, ph0, abort_flag, a.status, ERR_WAIT_FULL);
+            if (ok && !(rdy & 4u)) ok = mbar_wait_hot(w1, ph1, abort_flag, a.status, ERR_WAIT_FULL);
+            if (ok && !(rdy & 8u)) ok = mbar_wait_hot(w1 - kFullOff, ph1, abort_flag, a.status, ERR_WAIT_FULL);
             if (!ok) break;
           }
           tc_fence_after();
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            if (i < nb) {
-              const uint64_t bdesc = smem_desc_sw128(exp_base + es[i] * Cfg::EXP_STAGE);
-              const uint32_t a_tmem = tmem_base + Cfg::TMEM_A0 + es[i] * 32;
-              const uint32_t idesc = (st + i) < n_main ? idesc_h : idesc_bf;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) umma_f16_ts(d, a_tmem + 8 * j, bdesc + 2 * j, idesc, (st + i > 0 || j > 0) ? 1u : 0u);
-              umma_commit(expe_bar(es[i]));
-            }
+          umma_f16_ts_x4(d, a_tmem0 + 32u * es0, bdesc_lo0 + kDescStep * es0, bdesc_hi, st < n_main ? idesc_h : idesc_bf,
+                         st > 0 ? 1u : 0u);
+          umma_commit(w0 - kEmptyOff);
+          if (two) {
+            umma_f16_ts_x4(d, a_tmem0 + 32u * es1, bdesc_lo0 + kDescStep * es1, bdesc_hi, st + 1 < n_main ? idesc_h : idesc_bf, 1u);
+            umma_commit(w1 - kEmptyOff);
+            st += 2;
+          } else {
+            st += 1;
           }
-          st += nb;
-          q += nb;
+          es0 = es1;
+          ph0 = ph1;
+          if (++es0 == GF_EXP_STAGES) { es0 = 0; ph0 ^= 1u; }
         }
         if (ok) { umma_commit(accf_bar(buf)); ++use; }
       }
