@@ -128,6 +128,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
       int buf = 0;
       uint32_t aph = 0;
       uint32_t sf_slot = 0;
+      const uint64_t op_d0 = smem_desc_sw128(smem_base), sf_d0 = smem_desc_rows16(smem_base);
+      const uint32_t op_lo0 = (uint32_t)op_d0, op_hi = (uint32_t)(op_d0 >> 32);
+      const uint32_t sf_lo0 = (uint32_t)sf_d0, sf_hi = (uint32_t)(sf_d0 >> 32);
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         if (!mbar_wait(acce_bar(buf), aph ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) break;
@@ -142,6 +145,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
             const uint32_t sfa_s = sA + 2 * GF_TILE_BYTES, sfb_s = sfa_s + GF_SF_BYTES;
             const uint32_t sfa_t = tmem_base + GF_SFA_COL + sf_slot * 16, sfb_t = tmem_base + GF_SFB_COL + sf_slot * 16;
             const int nkb = min(4, a.n_chunks - st * 4);
+            if (nkb == 4) {
+              // a whole stage: descriptors from loop-invariant words, eight copies + four UMMAs in one block
+              const uint32_t a_lo = op_lo0 + (uint32_t)r.s * (GF_STAGE_BYTES >> 4);
+              const uint32_t sf_lo = sf_lo0 + (uint32_t)r.s * (GF_STAGE_BYTES >> 4);
+              umma_nvf4_stage4(d, a_lo, a_lo + (GF_TILE_BYTES >> 4), op_hi, idesc_f4, st > 0 ? 1u : 0u, sfa_t, sfb_t,
+                               sf_lo + (2 * GF_TILE_BYTES >> 4), sf_lo + ((2 * GF_TILE_BYTES + GF_SF_BYTES) >> 4), sf_hi);
+            } else {
             for (int kb = 0; kb < nkb; ++kb) {
               tmem_cp_32x128b_x4(sfa_t + kb * 4, smem_desc_rows16(sfa_s + kb * 512));
               tmem_cp_32x128b_x4(sfb_t + kb * 4, smem_desc_rows16(sfb_s + kb * 512));
@@ -149,6 +159,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
             for (int kb = 0; kb < nkb; ++kb)
               umma_nvf4(d, adesc + 2 * kb, bdesc + 2 * kb, idesc_f4, (st > 0 || kb > 0) ? 1u : 0u, sfa_t + kb * 4,
                         sfb_t + kb * 4);
+            }
             sf_slot ^= 1;
           } else {
 #pragma unroll

@@ -269,6 +269,45 @@ __device__ __forceinline__ void umma_nvf4(uint32_t d_tmem, uint64_t adesc, uint6
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
+// One whole NVFP4 operand stage (four 64-element k-blocks) in one block: eight scale-factor copies shared memory ->
+// tensor memory (4 columns per k-block and operand), then four block-scaled UMMAs.  Descriptors are given as low
+// words (address >> 4, advancing by 2 per k-block for the operands and by 32 for the 512-byte scale tiles) with the
+// two constant high words; `accum0` = 0 clears the accumulator first.
+__device__ __forceinline__ void umma_nvf4_stage4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi_op, uint32_t idesc,
+                                                 uint32_t accum0, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t sfa_lo,
+                                                 uint32_t sfb_lo, uint32_t hi_sf) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 x, y, u, v;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      // scale factors of the four k-blocks
+      "mov.b64 da, {%8, %10};\n\tmov.b64 db, {%9, %10};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%6], da;\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%7], db;\n\t"
+      "add.u32 x, %8, 32;\n\tadd.u32 y, %9, 32;\n\tadd.u32 u, %6, 4;\n\tadd.u32 v, %7, 4;\n\t"
+      "mov.b64 da, {x, %10};\n\tmov.b64 db, {y, %10};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [u], da;\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [v], db;\n\t"
+      "add.u32 x, %8, 64;\n\tadd.u32 y, %9, 64;\n\tadd.u32 u, %6, 8;\n\tadd.u32 v, %7, 8;\n\t"
+      "mov.b64 da, {x, %10};\n\tmov.b64 db, {y, %10};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [u], da;\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [v], db;\n\t"
+      "add.u32 x, %8, 96;\n\tadd.u32 y, %9, 96;\n\tadd.u32 u, %6, 12;\n\tadd.u32 v, %7, 12;\n\t"
+      "mov.b64 da, {x, %10};\n\tmov.b64 db, {y, %10};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [u], da;\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [v], db;\n\t"
+      // the four UMMAs
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [%6], [%7], p;\n\t"
+      "add.u32 x, %1, 2;\n\tadd.u32 y, %2, 2;\n\tadd.u32 u, %6, 4;\n\tadd.u32 v, %7, 4;\n\t"
+      "mov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [u], [v], t;\n\t"
+      "add.u32 x, %1, 4;\n\tadd.u32 y, %2, 4;\n\tadd.u32 u, %6, 8;\n\tadd.u32 v, %7, 8;\n\t"
+      "mov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [u], [v], t;\n\t"
+      "add.u32 x, %1, 6;\n\tadd.u32 y, %2, 6;\n\tadd.u32 u, %6, 12;\n\tadd.u32 v, %7, 12;\n\t"
+      "mov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [u], [v], t;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi_op), "r"(idesc), "r"(accum0), "r"(sfa_tmem), "r"(sfb_tmem), "r"(sfa_lo),
+        "r"(sfb_lo), "r"(hi_sf)
+      : "memory");
+}
 // 32 rows x 16 bytes of smem -> TMEM lanes 0..31 (4 columns), replicated to all four lane quarters.
 __device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
