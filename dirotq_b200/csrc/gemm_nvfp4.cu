@@ -162,8 +162,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
             }
             sf_slot ^= 1;
           } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) umma_f16(d, adesc + 2 * j, bdesc + 2 * j, idesc_bf, 1u);
+            const uint32_t a_lo = op_lo0 + (uint32_t)r.s * (GF_STAGE_BYTES >> 4);
+            umma_f16_ss_x4(d, a_lo, a_lo + (GF_TILE_BYTES >> 4), op_hi, idesc_bf, 1u);
           }
           umma_commit(empty_bar(r.s));
           r.next();

@@ -469,6 +469,8 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       int s = 0, buf = 0;
       uint32_t ph = 0, aph = 0;
       bool ok = true;
+      const uint64_t op_d0 = smem_desc_sw128(smem_base);
+      const uint32_t op_lo0 = (uint32_t)op_d0, op_hi = (uint32_t)(op_d0 >> 32);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
         int kb, ke;
@@ -479,12 +481,10 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         for (int kc = kb; kc < ke; ++kc) {
           if (!mbar_wait(full_bar(s), ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_base + s * RQ_STAGE_BYTES;
-          const uint64_t adesc = smem_desc_sw128(sa);
-          const uint64_t bdesc = smem_desc_sw128(sa + RQ_A_BYTES);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            umma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kc > kb || j > 0) ? 1u : 0u);
+          // descriptors from loop-invariant words; the stage's four UMMAs in one block (what this thread does between
+          // UMMAs is time the tensor pipe idles)
+          const uint32_t a_lo = op_lo0 + (uint32_t)s * (RQ_STAGE_BYTES >> 4);
+          umma_f16_ss_x4(d_tmem, a_lo, a_lo + (RQ_A_BYTES >> 4), op_hi, idesc, kc > kb ? 1u : 0u);
           umma_commit(empty_bar(s));
           if (++s == RQ_STAGES) { s = 0; ph ^= 1; }
         }
