@@ -245,9 +245,18 @@ __device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t tadd
       if (nvalid < 16 && row_ok && a.tail) {
         __nv_bfloat16* tr = a.tail + row * g.tail_pitch;
         const int t0 = gcol - g.q_len;
+        if (nvalid == 0 && gcol + 16 <= g.D && ((t0 | g.tail_pitch) & 7) == 0) {
+          // a group that lies wholly in the 16-bit tail: two 16-byte stores instead of sixteen 2-byte ones
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (j >= nvalid && gcol + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+          for (int i = 0; i < 2; ++i)
+            *reinterpret_cast<uint4*>(tr + t0 + 8 * i) =
+                make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                           pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j >= nvalid && gcol + j < g.D) tr[t0 + j] = __float2bfloat16_rn(v[j]);
+        }
       }
     }
     if constexpr (MODE == MODE_NVFP4_HW)
