@@ -316,41 +316,57 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
     GroupParams p;
     if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
     else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+    const float rcp = __frcp_rn(p.scale);
     for (int b = 0; b < 2 * g.cpg; ++b) {
-      uint32_t q[32];
+      // eight codes per word: nibbles for the 4-bit modes (n8), bytes for the 8-bit mode (b8); whole octets inside the
+      // group take the division-free exact forms (guarded reciprocal, quant_math.cuh), the ragged end the plain ones
+      uint32_t n8[4] = {0u, 0u, 0u, 0u};
+      uint2 b8[4] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
       if (b < nblk) {
         uint32_t r[32];
         ld32_by8(taddr + cb + 32 * b, r);
+        float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          int c = 0;
-          if (32 * b + j < d_q) {
-            float f = rnd<true>(__uint_as_float(r[j]));
-            if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(f, p.scale, maxq);
-            else c = int_asym_code<true>(f, p.scale, p.zero, maxq);
+        for (int j = 0; j < 32; ++j) f[j] = rnd<true>(__uint_as_float(r[j]));
+#pragma unroll
+        for (int o = 0; o < 4; ++o) {
+          const int e0 = 32 * b + 8 * o;
+          if (e0 + 8 <= d_q) {
+            if constexpr (MODE == MODE_INT4_SYM) {
+              n8[o] = int_sym_nib8_fast(f + 8 * o, p.scale, rcp);
+            } else {
+              b8[o] = int_asym_byte8_fast(f + 8 * o, p.scale, rcp, p.zero, maxq);
+              if constexpr (MODE == MODE_INT4_ASYM) n8[o] = squeeze_nibbles(b8[o].x) | (squeeze_nibbles(b8[o].y) << 16);
+            }
+          } else if (e0 < d_q) {
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              int c = 0;
+              if (e0 + j < d_q) {
+                if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(f[8 * o + j], p.scale, maxq);
+                else c = int_asym_code<true>(f[8 * o + j], p.scale, p.zero, maxq);
+              }
+              if constexpr (MODE == MODE_INT8_ASYM) {
+                if (j < 4) lo |= ((uint32_t)c & 0xFFu) << (8 * j);
+                else hi |= ((uint32_t)c & 0xFFu) << (8 * (j - 4));
+              } else {
+                lo |= ((uint32_t)c & 0xFu) << (4 * j);
+              }
+            }
+            if constexpr (MODE == MODE_INT8_ASYM) b8[o] = make_uint2(lo, hi);
+            else n8[o] = lo;
           }
-          q[j] = (uint32_t)c;
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) q[j] = 0;
       }
       if (row_ok) {
         const int64_t slot = (int64_t)h * g.cpg * 64 + 32 * b;
         if constexpr (MODE == MODE_INT8_ASYM) {
           uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot);
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t* s = q + 16 * i + 4 * k;
-              w[k] = (s[0] & 0xFF) | ((s[1] & 0xFF) << 8) | ((s[2] & 0xFF) << 16) | ((s[3] & 0xFF) << 24);
-            }
-            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          dst[0] = make_uint4(b8[0].x, b8[0].y, b8[1].x, b8[1].y);
+          dst[1] = make_uint4(b8[2].x, b8[2].y, b8[3].x, b8[3].y);
         } else {
-          *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot / 2) = pack_planar32(q);
+          *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot / 2) = planar32_from_nib8(n8[0], n8[1], n8[2], n8[3]);
         }
       }
     }
@@ -366,10 +382,20 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
         tmem_ld8(taddr + cb + c8, r);
         tmem_wait_ld();
         if (row_ok) {
+          __nv_bfloat16* tr = a.tail + row * g.tail_pitch + h * g.hlen;
+          const int t0 = c8 - d_q;                                  // tail index of r[0] within the head (may be negative)
+          if (t0 >= 0 && ((t0 | g.hlen | g.tail_pitch) & 7) == 0) {        // a whole, 16-byte aligned octet of tail channels
+            *reinterpret_cast<uint4*>(tr + t0) =
+                make_uint4(pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])), pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                           pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])), pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+          } else if (t0 == -4 && ((g.hlen | g.tail_pitch) & 3) == 0) {     // the octet's upper half starts the head's tail
+            *reinterpret_cast<uint2*>(tr) = make_uint2(pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                                                       pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+          } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (c8 + j >= d_q)
-              a.tail[row * g.tail_pitch + h * g.hlen + (c8 + j - d_q)] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            for (int j = 0; j < 8; ++j)
+              if (c8 + j >= d_q) tr[c8 + j - d_q] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
         }
       }
     }
