@@ -37,8 +37,10 @@ template <int EPI> struct RqCfg {
   static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : 2;
   static constexpr int EPI_WARPS = 4 * WPQ;
   static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+  // plain-GEMM epilogue (EPI_ROT_ONLY = 0): a 32 x 32 bf16 staging patch per epilogue warp for its TMA stores
+  static constexpr int STG_BYTES = (EPI == 0) ? EPI_WARPS * 2048 : 0;
+  static constexpr int SMEM_BYTES = RQ_STAGES * RQ_STAGE_BYTES + STG_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
-constexpr int RQ_SMEM_BYTES = RQ_STAGES * RQ_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
 enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3 };
 
@@ -403,10 +405,15 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
 }
 
 // Plain GEMM epilogue: y[M, N] = acc (+ bias) as bf16; used for the stand-alone rotation and for
-// the bf16 GEMM behind the W4A16 layer.
-__device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn, int wpq = 2) {
+// the bf16 GEMM behind the W4A16 layer.  32 columns at a time: tcgen05.ld -> + bias -> bf16 -> the warp's 32 x 32
+// staging patch in shared memory (64-byte rows, 64-byte swizzle) -> one TMA store, which clips the patch at the
+// edges of y.  (A row-per-thread store straight to global memory puts 32 separate 16-byte segments per
+// instruction through the load/store unit.)
+__device__ __forceinline__ void epi_rot_only(const RotArgs& a, const CUtensorMap* tm_y, uint32_t stg, uint32_t taddr, int row0,
+                                             int lane, int n0, int half, uint32_t& turn, int wpq = 2) {
   const ActGeom& g = a.g;
-  const bool row_ok = row < a.M;
+  const uint32_t stg_row = stg + lane * 64;
+  const int sw = (lane >> 1) & 3;
   for (int c0 = 0; c0 < a.BN; c0 += 32) {
     const int col = n0 + c0;
     if (col >= g.D) break;
@@ -414,29 +421,45 @@ __device__ __forceinline__ void epi_rot_only(const RotArgs& a, uint32_t taddr, i
     uint32_t r[32];
     tmem_ld32(taddr + c0, r);
     tmem_wait_ld();
-    if (row_ok) {
+    if (lane == 0) bulk_wait_read0();              // the previous patch has left the staging buffer
+    __syncwarp();
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (col + 8 * i + 8 <= g.D) {
-          float f[8];
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            f[e] = __uint_as_float(r[8 * i + e]);
-            if (a.bias) f[e] += __bfloat162float(a.bias[col + 8 * i + e]);
-          }
-          *reinterpret_cast<uint4*>(a.x_rot + row * g.D + col + 8 * i) =
-              make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * i + e]);
+      if (a.bias && col + 8 * i + 8 <= g.D) {
+        const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col + 8 * i));
+        const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+          const float2 b2 = __bfloat1622float2(bh[e2]);
+          f[2 * e2] += b2.x;
+          f[2 * e2 + 1] += b2.y;
         }
+      }
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg_row + (uint32_t)((i ^ sw) << 4)),
+                   "r"(pack_bf16x2(f[0], f[1])), "r"(pack_bf16x2(f[2], f[3])), "r"(pack_bf16x2(f[4], f[5])),
+                   "r"(pack_bf16x2(f[6], f[7]))
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm_y, stg, col, row0);
+      bulk_commit_group();
     }
   }
 }
 
 template <int EPI, int MODE>
 __global__ void __launch_bounds__(RqCfg<EPI>::THREADS, 1)
-rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_u, const RotArgs a) {
+rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_u,
+                    const __grid_constant__ CUtensorMap tm_y, const RotArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RQ_STAGES * RQ_STAGE_BYTES);
+  uint8_t* stg_area = smem + RQ_STAGES * RQ_STAGE_BYTES;                  // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_area + RqCfg<EPI>::STG_BYTES);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) acc_full, [2S+2..2S+4) acc_empty
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * RQ_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -541,7 +564,8 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256;
       const int64_t row = (int64_t)mb * 128 + q * 32 + lane;
       const int n0 = nb * a.BN;
-      if constexpr (EPI == EPI_ROT_ONLY) epi_rot_only(a, taddr, row, n0, half, turn);
+      if constexpr (EPI == EPI_ROT_ONLY)
+        epi_rot_only(a, &tm_y, smem_u32(stg_area) + (warp - 2) * 2048, taddr, mb * 128 + q * 32, lane, n0, half, turn);
       else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0, half, turn);
       else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
       else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn);
@@ -551,6 +575,8 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       buf ^= 1;
       if (buf == 0) aph ^= 1;
     }
+    if constexpr (EPI == EPI_ROT_ONLY)
+      if (lane == 0) bulk_wait_all0();                 // the output is in global memory before the CTA retires
   }
   tc_fence_before();
   __syncthreads();
@@ -575,15 +601,22 @@ int num_sms() {
 
 template <int EPI, int MODE>
 static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs& a, cudaStream_t st) {
+  CUtensorMap ty = tx;                                 // only the plain-GEMM epilogue stores through a tensor map
+  if constexpr (EPI == EPI_ROT_ONLY) {
+    if ((a.g.D & 7) || (reinterpret_cast<uintptr_t>(a.x_rot) & 15)) return DIROTQ_E_ALIGN;
+    int rc = make_tmap_2d_sw(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x_rot, (uint64_t)a.g.D, (uint64_t)a.M,
+                             (uint64_t)a.g.D * 2, 32, 32, 64);
+    if (rc) return rc;
+  }
   auto k = rotate_quant_kernel<EPI, MODE>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, RqCfg<EPI>::SMEM_BYTES) != cudaSuccess)
       return DIROTQ_E_CUDA;
     attr_set = true;
   }
   const int grid = min(a.m_tiles * a.n_tiles, num_sms());
-  return launch_pdl(k, dim3(grid), dim3(RqCfg<EPI>::THREADS), RQ_SMEM_BYTES, st, tx, tu, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  return launch_pdl(k, dim3(grid), dim3(RqCfg<EPI>::THREADS), RqCfg<EPI>::SMEM_BYTES, st, tx, tu, ty, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 // Picks the N tile: hidden layouts want a multiple of 64 with the least padding of D; per-head

@@ -364,16 +364,3 @@ def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tens
     return y
 
 
-def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tensor],
-               workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """W4A16 linear: bf16 x [M, K] times INT4 group-64 weights (dequantised into scratch, then tcgen05 bf16 GEMM)."""
-    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous() and w.group == 64
-    M, K = x2d.shape
-    assert K == w.n_chunks * 64
-    need = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(w.N, K))
-    ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x2d.device)
-    y = out if out is not None else torch.empty(M, w.N, dtype=torch.bfloat16, device=x2d.device)
-    check(_lib.lib().dirotq_gemm_w4a16(M, w.N, K, _ptr(x2d), _ptr(w.codes), _ptr(w.scales), _ptr(bias), _ptr(y),
-                                       _ptr(ws), ws.numel(), _ptr(status_word(x2d.device)), _stream()),
-          "dirotq_gemm_w4a16")
-    return y
