@@ -113,14 +113,20 @@ static __device__ __noinline__ uint32_t int_sym_nib8_exact(float v0, float v1, f
   return w;
 }
 __device__ __forceinline__ uint32_t int_sym_nib8_fast(const float* v, float s, float rcp_s) {
+  // Two values per packed bf16 instruction: round the quotients to bf16, clamp to [-8, 7], add 192 (bf16 spacing 1 in
+  // [128, 256): the add rounds half-even to the integer, whose two's-complement nibble is the low mantissa bits).
+  const __nv_bfloat162 lo2 = __floats2bfloat162_rn(-8.f, -8.f), hi2 = __floats2bfloat162_rn(7.f, 7.f),
+                       magic = __floats2bfloat162_rn(192.f, 192.f);
   uint32_t w = 0, near = 0;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float qa = __fmul_rn(v[j], rcp_s);
-    near |= (uint32_t)(((__float_as_uint(qa) + 0x8003u) & 0xFFFFu) <= 6u);
-    float r = __bfloat162float(__float2bfloat16_rn(qa));
-    r = fminf(fmaxf(r, -8.f), 7.f);
-    w |= (int_bits(r) & 0xFu) << (4 * j);
+  for (int j = 0; j < 8; j += 2) {
+    const float q0 = __fmul_rn(v[j], rcp_s), q1 = __fmul_rn(v[j + 1], rcp_s);
+    near |= (uint32_t)(((__float_as_uint(q0) + 0x8003u) & 0xFFFFu) <= 6u) |
+            (uint32_t)(((__float_as_uint(q1) + 0x8003u) & 0xFFFFu) <= 6u);
+    __nv_bfloat162 r = __floats2bfloat162_rn(q0, q1);          // .x (low half) = q0
+    r = __hadd2(__hmin2(__hmax2(r, lo2), hi2), magic);
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(&r) & 0x000F000Fu;
+    w |= ((b & 0xFu) | (b >> 12)) << (4 * j);
   }
   if (near) w = int_sym_nib8_exact(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], s);
   return w;
