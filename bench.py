@@ -412,7 +412,7 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
     kname = "gemm_nvfp4_kernel" if quant == "nvfp4" else (
-        "gemm_int_f16_kernel (with its fold_scales_kernel and expand_weight_panel_kernel)" if f16_used else "gemm_int_kernel")
+        "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)" if f16_used else "gemm_int_kernel")
     k1 = None
     if k1_pairs:
         k1_ms = sum(a.elapsed_time(b) for a, b in k1_pairs)
@@ -472,7 +472,7 @@ def roofline_pass_flux(step, x_dev, dev):
     torch.cuda.synchronize()
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
-    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_scales_kernel and expand_weight_panel_kernel)", "achieved": achieved,
+    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)", "achieved": achieved,
             "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
             "peak_source": f"{which}: cuBLAS bf16 sustained (the kernel computes in fp16 on the same tensor pipe)",
             "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)),

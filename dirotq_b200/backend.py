@@ -123,14 +123,17 @@ class LayerState:
 
 def kernel_launches(st: Optional[LayerState]) -> int:
     """Library kernels one forward of a wrapped linear launches.  A W4A16 layer (no LayerState): weight
-    dequantisation + GEMM.  W4A4: rotate/quantise + GEMM; the tensor-rate integer GEMM adds the scale-folding
-    kernel and, unless the layer keeps a resident panel, the weight-panel pre-pass; a sibling that reuses the
+    dequantisation + GEMM.  W4A4: rotate/quantise + GEMM; the tensor-rate integer GEMM adds one preparation launch
+    (scale folding and, unless the layer keeps a resident panel, the weight-panel pre-pass); a sibling that reuses the
     activations of the layer before it runs only its own GEMM (and pre-pass)."""
     if st is None:
         return 2
     n = 1 if (st.shared is not None and st.member_id > 0) else 2
     if st.folded is not None:
-        n += (0 if (st.shared is not None and st.member_id > 0) else 1) + (1 if st.folded.panel is None else 0)
+        # scale folding (first user of the activations only) and the weight-panel pre-pass (unless resident): one launch
+        # when both are due, else one each
+        fold = not (st.shared is not None and st.member_id > 0)
+        n += 1 if (fold or st.folded.panel is None) else 0
     follower = st.shared is not None and st.member_id > 0
     if st.rot_t is None and st.layout.tail_total > 0 and not follower:
         n += 1                              # quantise-only layers copy their passthrough channels in a kernel of its own

@@ -307,18 +307,27 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   __nv_bfloat16* tail_s = tail_total > 0 ? reinterpret_cast<__nv_bfloat16*>(ws + c.tail) : nullptr;
-  if (!skip_fold) {
-    int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales),
-                                    a_mode != DIROTQ_INT4_SYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr,
-                                    n_chunks, M, ld_rows(M), ws + c.rec, reinterpret_cast<float*>(ws + c.rs),
-                                    tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr, tail_s, tp, st);
-    if (rc) return rc;
-  }
-  if (!w_panel) {
-    // the weights stay 4-bit in memory; their fp16 panel is rebuilt in scratch for this call
-    int rc = launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, ws + c.panel, st);
+  const __nv_bfloat16* zeros_in = a_mode != DIROTQ_INT4_SYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr;
+  const __nv_bfloat16* tail_in = tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr;
+  if (!skip_fold && !w_panel) {
+    // both per-call preparations in one launch: activation scales folded into FMA operands, and the fp16 weight
+    // panel rebuilt in scratch (the weights stay 4-bit in memory)
+    int rc = launch_fold_act_and_expand(static_cast<const __nv_bfloat16*>(x_scales), zeros_in, n_chunks, M, ld_rows(M),
+                                        ws + c.rec, reinterpret_cast<float*>(ws + c.rs), tail_in, tail_s, tp,
+                                        static_cast<const uint8_t*>(w_codes), N, w_mult, ws + c.panel, st);
     if (rc) return rc;
     w_panel = ws + c.panel;
+  } else {
+    if (!skip_fold) {
+      int rc = launch_fold_act_scales(static_cast<const __nv_bfloat16*>(x_scales), zeros_in, n_chunks, M, ld_rows(M),
+                                      ws + c.rec, reinterpret_cast<float*>(ws + c.rs), tail_in, tail_s, tp, st);
+      if (rc) return rc;
+    }
+    if (!w_panel) {
+      int rc = launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, ws + c.panel, st);
+      if (rc) return rc;
+      w_panel = ws + c.panel;
+    }
   }
   GemmIntF16Args a;
   a.a_mode = a_mode;

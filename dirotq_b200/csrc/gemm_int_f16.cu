@@ -533,16 +533,14 @@ __device__ __forceinline__ uint32_t half_twice(float v) {
 
 // Block = 64 rows x 4 chunk phases (thread tid: row tid & 63, chunks c = tid >> 6 (mod 4)).
 template <typename ST>
-__global__ void __launch_bounds__(256)
-fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z, int n_chunks, int64_t rows, int64_t ld_in,
-                   uint2* __restrict__ rec, int64_t ld_rec, float* __restrict__ rs,
-                   const __nv_bfloat16* __restrict__ tail, __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
+__device__ __forceinline__ void fold_scales_block(int block, const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z,
+                                                  int n_chunks, int64_t rows, int64_t ld_in, uint2* __restrict__ rec,
+                                                  int64_t ld_rec, float* __restrict__ rs, const __nv_bfloat16* __restrict__ tail,
+                                                  __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
   __shared__ float part_max[4][64];
   __shared__ float inv_s[64];
-  pdl_launch_dependents();
-  pdl_wait();
   const int lr = threadIdx.x & 63, part = threadIdx.x >> 6;
-  const int64_t r0 = (int64_t)blockIdx.x * 64;
+  const int64_t r0 = (int64_t)block * 64;
   const int64_t r = r0 + lr;
   // the tail tile's loads go out first: they do not depend on the scales
   const int units = tail ? kt_pitch / 8 : 0;             // 16-byte units per row
@@ -607,15 +605,23 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
   }
 }
 
+template <typename ST>
+__global__ void __launch_bounds__(256)
+fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z, int n_chunks, int64_t rows, int64_t ld_in,
+                   uint2* __restrict__ rec, int64_t ld_rec, float* __restrict__ rs,
+                   const __nv_bfloat16* __restrict__ tail, __nv_bfloat16* __restrict__ tail_out, int kt_pitch) {
+  pdl_launch_dependents();
+  pdl_wait();
+  fold_scales_block<ST>((int)blockIdx.x, s, z, n_chunks, rows, ld_in, rec, ld_rec, rs, tail, tail_out, kt_pitch);
+}
+
 // Weight pre-pass: codes + records -> the fp16 panel [N, n_chunks * 64] the GEMM's weight-tile TMA reads.
 // One thread = one row x one chunk: 32 bytes of codes in, 128 bytes out, with the arithmetic and the K
 // order of the activation converters (expand_word), so a dot product pairs the right values.
-__global__ void __launch_bounds__(256)
-expand_weight_panel_kernel(const uint8_t* __restrict__ wq, int64_t w_row_bytes, const uint2* __restrict__ rec, int64_t ld_rec,
-                           int64_t N, int n_chunks, uint4* __restrict__ panel) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+__device__ __forceinline__ void expand_weight_panel_block(int block, const uint8_t* __restrict__ wq, int64_t w_row_bytes,
+                                                          const uint2* __restrict__ rec, int64_t ld_rec, int64_t N, int n_chunks,
+                                                          uint4* __restrict__ panel) {
+  const int64_t tid = (int64_t)block * blockDim.x + threadIdx.x;
   if (tid >= N * n_chunks) return;
   const int64_t n = tid / n_chunks;
   const int c = (int)(tid - n * n_chunks);
@@ -631,6 +637,32 @@ expand_weight_panel_kernel(const uint8_t* __restrict__ wq, int64_t w_row_bytes, 
     expand_word(w8[i], 0x00080008u, k.x, mhi, k.y, y);
     dst[i] = make_uint4(y[0], y[1], y[2], y[3]);
   }
+}
+
+__global__ void __launch_bounds__(256)
+expand_weight_panel_kernel(const uint8_t* __restrict__ wq, int64_t w_row_bytes, const uint2* __restrict__ rec, int64_t ld_rec,
+                           int64_t N, int n_chunks, uint4* __restrict__ panel) {
+  pdl_launch_dependents();
+  pdl_wait();
+  expand_weight_panel_block((int)blockIdx.x, wq, w_row_bytes, rec, ld_rec, N, n_chunks, panel);
+}
+
+// Both per-call preparations of one GEMM in one launch (each alone is a few microseconds of launch and latency):
+// blocks [0, fold_blocks) fold the activation scales, the rest expand the weight panel.
+struct FoldExpandArgs {
+  const __nv_bfloat16* s; const __nv_bfloat16* z; int n_chunks; int64_t rows; int64_t ld_in; uint2* rec; int64_t ld_rec; float* rs;
+  const __nv_bfloat16* tail; __nv_bfloat16* tail_out; int kt_pitch;
+  const uint8_t* wq; int64_t w_row_bytes; const uint2* w_rec; int64_t ld_wrec; int64_t N; uint4* panel;
+  int fold_blocks;
+};
+__global__ void __launch_bounds__(256) fold_expand_kernel(const FoldExpandArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.x < a.fold_blocks)
+    fold_scales_block<__nv_bfloat16>((int)blockIdx.x, a.s, a.z, a.n_chunks, a.rows, a.ld_in, a.rec, a.ld_rec, a.rs, a.tail,
+                                     a.tail_out, a.kt_pitch);
+  else
+    expand_weight_panel_block((int)blockIdx.x - a.fold_blocks, a.wq, a.w_row_bytes, a.w_rec, a.ld_wrec, a.N, a.n_chunks, a.panel);
 }
 
 int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st) {
@@ -655,6 +687,20 @@ int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n
   return launch_pdl(fold_scales_kernel<__nv_bfloat16>, dim3((unsigned)(ld_rec / 64)), dim3(256), 0, st, s, z, n_chunks, M,
                     ldm, reinterpret_cast<uint2*>(rec), ld_rec, rs, tail, tail_out, kt_pitch) == cudaSuccess
              ? DIROTQ_OK : DIROTQ_E_CUDA;
+}
+
+int launch_fold_act_and_expand(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm, void* rec,
+                               float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, const uint8_t* wq,
+                               int64_t N, const void* w_rec, void* panel, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return DIROTQ_OK;
+  FoldExpandArgs a;
+  a.s = s; a.z = z; a.n_chunks = n_chunks; a.rows = M; a.ld_in = ldm; a.rec = reinterpret_cast<uint2*>(rec);
+  a.ld_rec = f16_ld_act(M); a.rs = rs; a.tail = tail; a.tail_out = tail_out; a.kt_pitch = kt_pitch;
+  a.wq = wq; a.w_row_bytes = (int64_t)n_chunks * 32; a.w_rec = reinterpret_cast<const uint2*>(w_rec);
+  a.ld_wrec = f16_ld_weight(N); a.N = N; a.panel = reinterpret_cast<uint4*>(panel);
+  a.fold_blocks = (int)(a.ld_rec / 64);
+  const unsigned blocks = (unsigned)a.fold_blocks + (unsigned)((N * n_chunks + 255) / 256);
+  return launch_pdl(fold_expand_kernel, dim3(blocks), dim3(256), 0, st, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
 int launch_fold_weight_scales(const float* s, int n_chunks, int64_t N, int64_t ldn, void* rec, float* cs,
