@@ -58,10 +58,12 @@ SIGNATURES = {
     "dirotq_gemm_w4a4_int_f16_workspace_bytes": (_SZ, [_I64, _I64, _I32, _I32]),
     "dirotq_gemm_w4a4_int_f16": (C.c_int, [_I32, _I64, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P,
                                             _P, _P, _SZ, _P, _P]),
-    "dirotq_gemm_w4a4_nvfp4": (C.c_int, [_I64, _I64, _I32, _P, _P, _P, _P, _F, _P, _P, _I32, _I32, _P, _P, _P, _P]),
+    "dirotq_pack_weight_nvfp4_rowscale": (C.c_int, [_P, _I64, _I64, _P, _P, _P, _P, _P]),
+    "dirotq_gemm_w4a4_nvfp4": (C.c_int, [_I64, _I64, _I32, _P, _P, _P, _P, _F, _P, _P, _P, _I32, _I32, _P, _P, _P, _P]),
     "dirotq_gemm_w4a16_workspace_bytes": (_SZ, [_I64, _I64]),
     "dirotq_gemm_w4a16": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _SZ, _P, _P]),
-    "dirotq_gemm_w4a16_nvfp4": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _F, _P, _P, _P, _SZ, _P, _P]),
+    "dirotq_gemm_w4a16_nvfp4": (C.c_int, [_I64, _I64, _I64, _P, _P, _P, _F, _P, _P, _P, _P, _SZ, _P, _P]),
+    "dirotq_dequant_weight_nvfp4": (C.c_int, [_I64, _I64, _P, _P, _F, _P, _P, _P]),
     "dirotq_linear_workspace_bytes": (_SZ, [C.POINTER(LinearC), _I64]),
     "dirotq_linear_forward": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_gemm": (C.c_int, [C.POINTER(LinearC), _I64, _P, _P, _SZ, _P, _P]),
@@ -69,6 +71,7 @@ SIGNATURES = {
     "dirotq_linear_forward_static": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _P]),
 }
 
+ABI_VERSION = 5
 _lib = None
 
 
@@ -84,7 +87,7 @@ def lib():
             fn = getattr(l, name)       # AttributeError if the library does not export it
             fn.restype = res
             fn.argtypes = args
-        if l.dirotq_abi_version() != 4:
+        if l.dirotq_abi_version() != ABI_VERSION:
             raise RuntimeError("libdirotq_b200.so ABI version mismatch")
         _lib = l
     return _lib

@@ -89,6 +89,7 @@ class LayerState:
     epilogue_act: int = 0                            # 1: GELU (tanh form) fused into the GEMM epilogue
     hadamard_low_dim: int = 0                        # use_hadamard layers: FWHT over the first channels
     hadamard_flips: Optional[torch.Tensor] = None
+    w_rowscale: Optional[torch.Tensor] = None        # NVFP4: fp32 per-channel weight scale (reference recipe)
     _c: Optional[LinearC] = None
     _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
 
@@ -98,7 +99,7 @@ class LayerState:
             f = self.folded
             self._c = LinearC(self.fmt.c(), self.out_features, p(self.rot_t), p(self.perm_idx), p(self.w_codes),
                               p(self.w_scales), p(self.w_sum), p(self.w_tail), p(self.bias), self.w_tensor_scale,
-                              p(f.mult if f else None), p(f.colscale if f else None), p(f.tail if f else None),
+                              p(f.mult if f else None), p(f.colscale if f else self.w_rowscale), p(f.tail if f else None),
                               int(self.epilogue_act), p(f.panel if f else None))
         return self._c
 
@@ -210,6 +211,11 @@ def _act_format(w) -> ops.ActFormat:
                          tensor_scale=_HW_NVFP4_ACT_SCALE)
 
 
+# How a dense NVFP4 weight (the reference's cache holds only dequantised weights) is put back on a 4-bit grid:
+# "rowscale" = the reference's own two-level recipe, per-output-channel scale + E4M3 micro-scales
+# (speedup/weight_only_nvfp4.py:42-72); "tensor" = one power-of-two scale per tensor with the accuracy path's tie rule.
+NVFP4_WEIGHT_RECIPE = "rowscale"
+
 # Integer-activation layers (W4A4 and W4A8) run the tensor-rate GEMM (codes expanded to fp16 next to the
 # tensor core).  Set to False to route them through the exact-integer kind::i8 kernel instead.
 INT4_TENSOR_RATE_GEMM = True
@@ -261,7 +267,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
                 folded.panel = ops.expand_weight_panel_f16(pk, folded)
         return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias,
                           float(packed["w_tensor_scale"]), int(packed["n_lossy_groups"]), folded,
-                          hadamard_low_dim=had_dim, hadamard_flips=had_flips)
+                          hadamard_low_dim=had_dim, hadamard_flips=had_flips, w_rowscale=t(packed.get("w_rowscale")))
     have_codes = bool(explicit) and ("codes" in explicit or "nibbles" in explicit)
     have_tail = lay.tail_total == 0 or (bool(explicit) and "w_tail" in explicit)
     w_low = w_tail = None
@@ -278,17 +284,25 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
             w_tail = Wf[:, lay.q_len:].contiguous() if lay.tail_total else None
     if explicit and "w_tail" in explicit:
         w_tail = explicit["w_tail"].to(device=dev, dtype=torch.float32)
-    n_lossy, Tw, w_sum = 0, 1.0, None
+    n_lossy, Tw, w_sum, w_rowscale = 0, 1.0, None, None
     if fmt.mode == ops.NVFP4_HW:
         if explicit and "nibbles" in explicit:
             pk = pack.convert_dirotq_low_weight_to_b200_fp4(None, explicit["tensor_scale"], explicit["nibbles"],
                                                             explicit["scales_e4m3"])
+        elif NVFP4_WEIGHT_RECIPE == "rowscale":
+            pk = ops.pack_weight_nvfp4_rowscale(w_low.to(dev))
         else:
             pk = pack.convert_dirotq_low_weight_to_b200_fp4(w_low)
         Tw = pk.tensor_scale
-        w_codes, w_scales = pk.codes, pk.sf
+        w_codes, w_scales, w_rowscale = pk.codes, pk.sf, pk.row_scale
         out_scale = fmt.tensor_scale * Tw
-        wt = None if w_tail is None else (w_tail / out_scale).to(torch.bfloat16)
+        if w_tail is None:
+            wt = None
+        elif w_rowscale is not None:
+            # the GEMM multiplies the whole accumulator by out_scale * scale[n]: the 16-bit branch is divided by it here
+            wt = (w_tail.to(dev) / (out_scale * w_rowscale[:N, None])).to(torch.bfloat16)
+        else:
+            wt = (w_tail / out_scale).to(torch.bfloat16)
     else:
         if explicit and "codes" in explicit:
             pk = pack.convert_dirotq_low_weight_to_b200(None, lay.group, scales=explicit["scales"], codes=explicit["codes"])
@@ -311,7 +325,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
         if CACHE_WEIGHT_PANEL:
             folded.panel = ops.expand_weight_panel_f16(pk, folded)
     return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded,
-                      hadamard_low_dim=had_dim, hadamard_flips=had_flips)
+                      hadamard_low_dim=had_dim, hadamard_flips=had_flips, w_rowscale=w_rowscale)
 
 
 @dataclass
@@ -336,7 +350,8 @@ def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int 
             raise RuntimeError("packed-weight cache entry does not match this 16-bit-activation layer: rebuild the cache")
         t = lambda v: None if v is None else v.to(dev).contiguous()
         if packed["weight"] == "nvfp4":
-            pk = ops.PackedWeightNvfp4(N, K, K // 64, float(packed["tensor_scale"]), t(packed["codes"]), t(packed["sf"]))
+            pk = ops.PackedWeightNvfp4(N, K, K // 64, float(packed["tensor_scale"]), t(packed["codes"]), t(packed["sf"]),
+                                       t(packed.get("row_scale")))
         else:
             pk = ops.PackedWeightInt4(N, K, 64, K // 64, t(packed["codes"]), t(packed["scales"]), t(packed["wsum"]))
         n = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(N, K))
@@ -484,12 +499,13 @@ def save_packed_weights(transformer, path) -> int:
             layers[name] = {"kind": "w4a4", "fmt": dataclasses.asdict(st.fmt), "out_features": st.out_features,
                             "w_codes": cpu(st.w_codes), "w_scales": cpu(st.w_scales), "w_sum": cpu(st.w_sum),
                             "w_tail": cpu(st.w_tail), "bias": cpu(st.bias), "w_tensor_scale": float(st.w_tensor_scale),
+                            "w_rowscale": cpu(st.w_rowscale),
                             "n_lossy_groups": int(st.n_lossy_groups)}
         elif s16 is not None:
             pk = s16.w
             e = {"kind": "w4a16", "N": pk.N, "K": pk.n_chunks * 64, "bias": cpu(s16.bias), "codes": cpu(pk.codes)}
             if isinstance(pk, ops.PackedWeightNvfp4):
-                e.update(weight="nvfp4", tensor_scale=float(pk.tensor_scale), sf=cpu(pk.sf))
+                e.update(weight="nvfp4", tensor_scale=float(pk.tensor_scale), sf=cpu(pk.sf), row_scale=cpu(pk.row_scale))
             else:
                 e.update(weight="int4", scales=cpu(pk.scales), wsum=cpu(pk.wsum))
             layers[name] = e

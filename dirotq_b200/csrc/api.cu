@@ -4,6 +4,8 @@
 #include "layout.cuh"
 #include "launchers.cuh"
 
+#include <atomic>
+
 using namespace dq;
 
 extern "C" {
@@ -166,6 +168,23 @@ int dirotq_pack_weight_nvfp4(const float* w_low, int64_t N, int64_t n_low, float
   a.codes = static_cast<uint8_t*>(codes);
   a.sf = static_cast<uint8_t*>(sf);
   return launch_pack_nvfp4(a, static_cast<cudaStream_t>(stream));
+}
+
+int dirotq_pack_weight_nvfp4_rowscale(const float* w_low, int64_t N, int64_t n_low, void* codes, void* sf,
+                                      float* row_scale, float* row_scale_exact, void* stream) {
+  if (!w_low || !codes || !sf || !row_scale || !row_scale_exact || N <= 0 || n_low <= 0) return DIROTQ_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(sf) & 15)) return DIROTQ_E_ALIGN;
+  PackFp4Args a;
+  a.w = w_low;
+  a.N = N;
+  a.n_low = n_low;
+  a.n_chunks = (int)((n_low + 63) / 64);
+  a.T = 1.f;
+  a.scale_in = nullptr;
+  a.w_is_codes = 0;
+  a.codes = static_cast<uint8_t*>(codes);
+  a.sf = static_cast<uint8_t*>(sf);
+  return launch_pack_nvfp4_rowscale(a, row_scale_exact, row_scale, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -364,14 +383,17 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
 }
 
 static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
-                                const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
+                                const void* w_codes, const void* w_sf, float out_scale, const float* w_colscale,
+                                const void* x_tail,
                                 const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
                                 void* y, int act, int32_t* status, void* stream) {
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_sf || !w_codes || !w_sf || !y) return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
   if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8))) return DIROTQ_E_ARG;
   const uintptr_t al = reinterpret_cast<uintptr_t>(x_sf) | reinterpret_cast<uintptr_t>(w_sf) | reinterpret_cast<uintptr_t>(y) |
-                       reinterpret_cast<uintptr_t>(bias);
+                       reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(x_codes) |
+                       reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(x_tail) |
+                       reinterpret_cast<uintptr_t>(w_tail_scaled) | reinterpret_cast<uintptr_t>(w_colscale);
   if (al & 15) return DIROTQ_E_ALIGN;
   GemmFp4Args a;
   a.M = M;
@@ -382,6 +404,7 @@ static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const vo
   a.wq = static_cast<const uint8_t*>(w_codes);
   a.wsf = static_cast<const uint8_t*>(w_sf);
   a.out_scale = out_scale;
+  a.col_scale = w_colscale;
   a.xt = static_cast<const __nv_bfloat16*>(x_tail);
   a.wt = static_cast<const __nv_bfloat16*>(w_tail_scaled);
   a.kt = tail_total;
@@ -394,11 +417,11 @@ static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const vo
 }
 
 int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
-                           const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
-                           const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
-                           void* y, int32_t* status, void* stream) {
-  return gemm_w4a4_nvfp4_impl(M, N, n_chunks, x_codes, x_sf, w_codes, w_sf, out_scale, x_tail, w_tail_scaled, tail_total,
-                              tail_pitch, bias, y, 0, status, stream);
+                           const void* w_codes, const void* w_sf, float out_scale, const float* w_colscale,
+                           const void* x_tail, const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch,
+                           const void* bias, void* y, int32_t* status, void* stream) {
+  return gemm_w4a4_nvfp4_impl(M, N, n_chunks, x_codes, x_sf, w_codes, w_sf, out_scale, w_colscale, x_tail, w_tail_scaled,
+                              tail_total, tail_pitch, bias, y, 0, status, stream);
 }
 
 struct WsCarve {
@@ -459,7 +482,7 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
   if (!(stages & 2)) return DIROTQ_OK;
   if (g.mode == DIROTQ_NVFP4_HW)
     return gemm_w4a4_nvfp4_impl(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
-                                lin->fmt.tensor_scale * lin->w_tensor_scale, tail, lin->w_tail, g.tail_total,
+                                lin->fmt.tensor_scale * lin->w_tensor_scale, lin->w_colscale, tail, lin->w_tail, g.tail_total,
                                 g.tail_pitch, lin->bias, y, lin->epilogue_act, status, stream);
   if (lin->epilogue_act < 0 || lin->epilogue_act > 1) return DIROTQ_E_ARG;
   if (uses_f16_gemm(lin, g)) {
@@ -496,18 +519,22 @@ int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* works
 static __device__ __align__(256) unsigned char g_static_scratch[DIROTQ_STATIC_SCRATCH_BYTES];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address; the real
-// address is looked up once per device (with that device current) and cached here.
-static void* g_static_scratch_addr[64] = {nullptr};
+// address is looked up once per device (with that device current) and published here.  Two host
+// threads that make the first call on a device at the same time both look it up and store the same
+// value.  The cache does not survive a device reset (cudaDeviceReset): a process that resets a
+// device must not call this entry point on it afterwards.
+static std::atomic<void*> g_static_scratch_addr[64];
 
 static int static_scratch_ptr(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DIROTQ_E_CUDA;
-  if (!g_static_scratch_addr[dev]) {
-    void* p = nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return DIROTQ_E_CUDA;
+  if (dev >= 64) return DIROTQ_E_UNSUPPORTED;      // more device ordinals than this table holds
+  void* p = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (!p) {
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return DIROTQ_E_CUDA;
-    g_static_scratch_addr[dev] = p;
+    g_static_scratch_addr[dev].store(p, std::memory_order_release);
   }
-  *out = g_static_scratch_addr[dev];
+  *out = p;
   return DIROTQ_OK;
 }
 
@@ -526,7 +553,11 @@ int dirotq_linear_forward_static(const dirotq_linear* lin, const void* x, int64_
   if (rc) return rc;
   // The array still holds whatever the previous call left.  Only the scale-factor tiles of the
   // NVFP4 format rely on zeros (their padding entries are never written), so that region is cleared
-  // here, in stream order, before the kernels run.
+  // here, in stream order, before the kernels run.  Nothing else reads stale bytes: every tensor map
+  // over the tail is built with tail_total columns and M rows (not tail_pitch / padded rows), so pad
+  // columns and rows are zero-filled by the copy engine; pad code slots of a partial last group are
+  // written as zero codes by the quantiser; scales of pad rows only feed output rows that are never
+  // stored.
   if (g.mode == DIROTQ_NVFP4_HW) {
     if (cudaMemsetAsync(static_cast<uint8_t*>(ws) + w.scales, 0, w.zeros - w.scales,
                         static_cast<cudaStream_t>(stream)) != cudaSuccess)

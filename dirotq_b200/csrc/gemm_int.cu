@@ -465,12 +465,8 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
 template <int A_MODE, bool DUMP>
 static int launch_gi(const GiMaps& tm, const GemmIntArgs& a, cudaStream_t st) {
   auto k = gemm_int_kernel<A_MODE, DUMP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, GiCfg<A_MODE>::SMEM_BYTES) != cudaSuccess)
-      return DIROTQ_E_CUDA;
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (int rc = set_max_dynamic_smem(attr_once, k, GiCfg<A_MODE>::SMEM_BYTES)) return rc;
   const int tiles = (int)((a.N + 127) / 128) * (int)((a.M + 127) / 128);
   const int grid = min(tiles, num_sms());
   k<<<grid, GI_THREADS, GiCfg<A_MODE>::SMEM_BYTES, st>>>(tm, a);

@@ -716,12 +716,8 @@ template <int BN, int AMODE>
 static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st) {
   using Cfg = GfCfg<BN, AMODE == 2>;
   auto k = gemm_int_f16_kernel<BN, AMODE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return DIROTQ_E_CUDA;
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (int rc = set_max_dynamic_smem(attr_once, k, Cfg::SMEM_BYTES)) return rc;
   const int tiles = (int)((a.N + BN - 1) / BN) * (int)((a.M + 127) / 128);
   const int grid = min(tiles, num_sms());
   return launch_pdl(k, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tm, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;

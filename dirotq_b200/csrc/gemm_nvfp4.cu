@@ -220,10 +220,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
 #pragma unroll
               for (int e = 0; e < 8; ++e) b[e] = 0.f;
             }
+            float sc[8];
+            if (a.col_scale) {
+              const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.col_scale + col));
+              const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.col_scale + col + 4));
+              sc[0] = c0.x * a.out_scale; sc[1] = c0.y * a.out_scale; sc[2] = c0.z * a.out_scale; sc[3] = c0.w * a.out_scale;
+              sc[4] = c1.x * a.out_scale; sc[5] = c1.y * a.out_scale; sc[6] = c1.z * a.out_scale; sc[7] = c1.w * a.out_scale;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) sc[e] = a.out_scale;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), a.out_scale, b[2 * e]);
-              float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), a.out_scale, b[2 * e + 1]);
+              float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e]), sc[2 * e], b[2 * e]);
+              float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e + 1]), sc[2 * e + 1], b[2 * e + 1]);
               if (a.act == 1) { f0 = gelu_tanh_bf16(f0); f1 = gelu_tanh_bf16(f1); }
               __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
               w[e] = *reinterpret_cast<uint32_t*>(&h);
@@ -275,12 +285,8 @@ int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
     txt = txq;
     twt = twq;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GF_SMEM_BYTES) != cudaSuccess)
-      return DIROTQ_E_CUDA;
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (int rc = set_max_dynamic_smem(attr_once, gemm_nvfp4_kernel, GF_SMEM_BYTES)) return rc;
   const int tiles = (int)((a.M + 127) / 128) * (int)((a.N + 127) / 128);
   const int grid = min(tiles, num_sms());
   return launch_pdl(gemm_nvfp4_kernel, dim3(grid), dim3(GF_THREADS), GF_SMEM_BYTES, st, txq, twq, txt, twt, ty, a) == cudaSuccess

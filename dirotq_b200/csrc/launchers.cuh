@@ -4,9 +4,29 @@
 #include <cuda_bf16.h>
 #include "layout.cuh"
 
+#include <atomic>
 #include <utility>
 
 namespace dq {
+
+// cudaFuncSetAttribute acts on the CURRENT device only, so "done" is remembered per device (bit = device ordinal),
+// not per process: a host that drives several GPUs from one process sets it on each of them.
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> done{0};
+};
+template <typename K>
+inline int set_max_dynamic_smem(PerDeviceOnce& once, K kernel, int bytes) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return DIROTQ_E_CUDA;
+  if (dev >= 64) return DIROTQ_E_UNSUPPORTED;
+  const unsigned long long bit = 1ull << dev;
+  if (!(once.done.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return DIROTQ_E_CUDA;
+    once.done.fetch_or(bit, std::memory_order_release);
+  }
+  return DIROTQ_OK;
+}
 
 // Launch with programmatic stream serialization allowed (see pdl_wait() in ptx.cuh).
 template <typename... KArgs, typename... Args>
@@ -139,6 +159,7 @@ struct GemmFp4Args {
   const uint8_t* wq;           // [N, n_chunks * 32]
   const uint8_t* wsf;
   float out_scale;
+  const float* col_scale;      // optional fp32 [N]: per-channel weight scale (the reference's two-level weight recipe)
   int act;                     // epilogue activation: 0 none, 1 GELU (tanh form)
   const __nv_bfloat16* xt;
   const __nv_bfloat16* wt;
@@ -172,8 +193,9 @@ int launch_hadamard_low(const void* x, int64_t M, int D, int n, const void* flip
 int num_sms();
 int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64_t K, const void* bias, void* y,
                      int* status, cudaStream_t st);
-int launch_dequant_nvfp4(const uint8_t* codes, const uint8_t* sf, float T, int64_t N, int n_chunks, __nv_bfloat16* w,
-                         cudaStream_t st);
+int launch_dequant_nvfp4(const uint8_t* codes, const uint8_t* sf, float T, const float* row_scale, int64_t N, int n_chunks,
+                         __nv_bfloat16* w, cudaStream_t st);
+int launch_pack_nvfp4_rowscale(const PackFp4Args& a, float* g_exact, float* g_stored, cudaStream_t st);
 int launch_dequant_int4(const uint8_t* codes, const float* scales, int64_t N, int n_chunks, int64_t ldn,
                         __nv_bfloat16* w, cudaStream_t st);
 

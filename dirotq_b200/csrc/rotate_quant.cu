@@ -589,12 +589,14 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 
 // ---- host side ----------------------------------------------------------------------------------
 int num_sms() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+  // per device: a process may drive GPUs of different sizes
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev].store(n, std::memory_order_relaxed);
   }
   return n;
 }
@@ -609,12 +611,8 @@ static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs
     if (rc) return rc;
   }
   auto k = rotate_quant_kernel<EPI, MODE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, RqCfg<EPI>::SMEM_BYTES) != cudaSuccess)
-      return DIROTQ_E_CUDA;
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (int rc = set_max_dynamic_smem(attr_once, k, RqCfg<EPI>::SMEM_BYTES)) return rc;
   const int grid = min(a.m_tiles * a.n_tiles, num_sms());
   return launch_pdl(k, dim3(grid), dim3(RqCfg<EPI>::THREADS), RqCfg<EPI>::SMEM_BYTES, st, tx, tu, ty, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }

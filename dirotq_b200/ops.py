@@ -205,6 +205,24 @@ class PackedWeightNvfp4:
     tensor_scale: float
     codes: torch.Tensor     # uint8 [N, n_chunks*32]
     sf: torch.Tensor        # uint8 tiled UE4M3
+    row_scale: Optional[torch.Tensor] = None   # fp32 [ldn]: per-channel second-level scale (reference recipe)
+
+
+def pack_weight_nvfp4_rowscale(w_low: torch.Tensor) -> PackedWeightNvfp4:
+    """Kernel 3 (NVFP4) with the reference's own two-level weight recipe (speedup/weight_only_nvfp4.py:42-72):
+    per-output-channel scale gscale[n] (kept as its bf16 value in fp32), E4M3 micro-scales relative to it, codes by
+    first-argmin against micro * gscale."""
+    w = w_low.to(torch.float32).contiguous()
+    N, n_low = w.shape
+    n_chunks = (n_low + 63) // 64
+    ldn = (N + 7) // 8 * 8
+    codes = torch.zeros(N, n_chunks * 32, dtype=torch.uint8, device=w.device)
+    sf = torch.zeros(((N + 127) // 128) * ((n_chunks + 3) // 4 * 4) * 512, dtype=torch.uint8, device=w.device)
+    rs = torch.ones(ldn, dtype=torch.float32, device=w.device)
+    rs_exact = torch.ones(ldn, dtype=torch.float32, device=w.device)
+    check(_lib.lib().dirotq_pack_weight_nvfp4_rowscale(_ptr(w), N, n_low, _ptr(codes), _ptr(sf), _ptr(rs), _ptr(rs_exact),
+                                                       _stream()), "dirotq_pack_weight_nvfp4_rowscale")
+    return PackedWeightNvfp4(N, n_low, n_chunks, 1.0, codes, sf, rs)
 
 
 def pack_weight_nvfp4(w_low: torch.Tensor, tensor_scale: float, scales_e4m3: Optional[torch.Tensor] = None,
@@ -318,14 +336,14 @@ def gemm_w4a4_int_f16(act: ActBuffers, w: PackedWeightInt4, folded: FoldedWeight
 
 def gemm_w4a4_nvfp4(act: ActBuffers, w: PackedWeightNvfp4, w_tail_scaled: Optional[torch.Tensor],
                     bias: Optional[torch.Tensor]) -> torch.Tensor:
-    """Kernel 2 (NVFP4).  w_tail_scaled = w_tail / (Tx * Tw), bf16 [N, tail_pitch]."""
+    """Kernel 2 (NVFP4).  w_tail_scaled = w_tail / (Tx * Tw [* w.row_scale[n]]), bf16 [N, tail_pitch]."""
     lay, M, N = act.layout, act.M, w.N
     assert act.fmt.mode == NVFP4_HW and lay.n_chunks == w.n_chunks
     dev = act.codes.device
     y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     out_scale = float(act.fmt.tensor_scale) * float(w.tensor_scale)
     check(_lib.lib().dirotq_gemm_w4a4_nvfp4(M, N, lay.n_chunks, _ptr(act.codes), _ptr(act.scales), _ptr(w.codes),
-                                            _ptr(w.sf), out_scale, _ptr(act.tail), _ptr(w_tail_scaled),
+                                            _ptr(w.sf), out_scale, _ptr(w.row_scale), _ptr(act.tail), _ptr(w_tail_scaled),
                                             lay.tail_total, lay.tail_pitch, _ptr(bias), _ptr(y),
                                             _ptr(status_word(dev)), _stream()), "dirotq_gemm_w4a4_nvfp4")
     return y
@@ -344,9 +362,18 @@ def gemm_w4a16_nvfp4(x2d: torch.Tensor, w: "PackedWeightNvfp4", bias: Optional[t
     if M == 0:
         return y
     check(_lib.lib().dirotq_gemm_w4a16_nvfp4(M, w.N, K, _ptr(x2d), _ptr(w.codes), _ptr(w.sf), float(w.tensor_scale),
-                                             _ptr(bias), _ptr(y), _ptr(ws), ws.numel(), _ptr(status_word(x2d.device)),
+                                             _ptr(w.row_scale), _ptr(bias), _ptr(y), _ptr(ws), ws.numel(), _ptr(status_word(x2d.device)),
                                              _stream()), "dirotq_gemm_w4a16_nvfp4")
     return y
+
+
+def dequant_weight_nvfp4(w: "PackedWeightNvfp4") -> torch.Tensor:
+    """bf16 [N, K] weight of a packed NVFP4 layer (K = n_chunks * 64), one rounding per value."""
+    K = w.n_chunks * 64
+    out = torch.empty(w.N, K, dtype=torch.bfloat16, device=w.codes.device)
+    check(_lib.lib().dirotq_dequant_weight_nvfp4(w.N, K, _ptr(w.codes), _ptr(w.sf), float(w.tensor_scale),
+                                                 _ptr(w.row_scale), _ptr(out), _stream()), "dirotq_dequant_weight_nvfp4")
+    return out
 
 
 def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tensor],

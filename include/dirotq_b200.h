@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DIROTQ_ABI_VERSION 4
+#define DIROTQ_ABI_VERSION 5
 
 /* ---- activation quantiser modes (ActQuantizer.configure, utils/quant_utils.py:182-199) ---- */
 enum {
@@ -138,6 +138,17 @@ int dirotq_pack_weight_int4(const float* w_low, int64_t N, int64_t n_low, int32_
 int dirotq_pack_weight_nvfp4(const float* w_low, int64_t N, int64_t n_low, float tensor_scale,
                              const uint8_t* scale_in, int32_t w_is_codes, void* codes, void* sf, void* stream);
 
+/* NVFP4 with the reference's own two-level recipe, bit for bit (speedup/weight_only_nvfp4.py:42-72, _quantize_nvfp4):
+ *   group_scale = max(amax_g / 6, 1e-12); gscale[n] = max(max_g(group_scale) / 448, 1e-12) per OUTPUT CHANNEL (fp32);
+ *   micro = e4m3(group_scale / gscale[n]); codes = first argmin |w / (micro * gscale[n]) - codebook| (an exact
+ *   midpoint goes to the value of smaller magnitude, no -0).
+ *   Outputs: codes and sf as dirotq_pack_weight_nvfp4 (the reference packs its nibbles planar, column j with column
+ *   j + K/2; here they are sequential, the order the tensor core reads); row_scale fp32 [N] = gscale rounded to bf16,
+ *   the value the reference stores and dequantises with; row_scale_exact fp32 [N] = the unrounded gscale the codes
+ *   were taken against (scratch the caller may discard).  The GEMMs take row_scale as their per-channel factor. */
+int dirotq_pack_weight_nvfp4_rowscale(const float* w_low, int64_t N, int64_t n_low, void* codes, void* sf,
+                                      float* row_scale, float* row_scale_exact, void* stream);
+
 /* Hadamard front end of layers with use_hadamard (dirotq_fused_unrotation_fast.py:106-128;
  * utils/hadamard_utils.py:56-80): y[:, :low_dim] = FWHT(x[:, :low_dim] * sign_flips) / sqrt(low_dim) with
  * fp32 butterflies in the reference's stage order (bit-identical to it), y[:, low_dim:] = x[:, low_dim:].
@@ -201,13 +212,15 @@ int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chu
                              void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* NVFP4 (tcgen05 kind::mxf4nvf4, UE4M3 scale factors in TMEM):
- *   y = out_scale * (sum_blocks sfx sfw (e2m1.e2m1) + x_tail . w_tail_scaled) + bias
- *   out_scale = Tx * Tw; w_tail_scaled = w_tail / out_scale (bf16, prepared once by the host).
+ *   y[m,n] = out_scale * c[n] * (sum_blocks sfx sfw (e2m1.e2m1) + x_tail . w_tail_scaled[n]) + bias[n]
+ *   out_scale = Tx * Tw; w_colscale: optional fp32 [N] (16-byte aligned) per-channel weight scale c[n] (row_scale of
+ *   dirotq_pack_weight_nvfp4_rowscale), NULL = 1; w_tail_scaled = w_tail / (out_scale * c[n]) (bf16, prepared once
+ *   by the host).
  */
 int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x_codes, const void* x_sf,
-                           const void* w_codes, const void* w_sf, float out_scale, const void* x_tail,
-                           const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
-                           void* y, int32_t* status, void* stream);
+                           const void* w_codes, const void* w_sf, float out_scale, const float* w_colscale,
+                           const void* x_tail, const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch,
+                           const void* bias, void* y, int32_t* status, void* stream);
 
 /* W4A16: bf16 activations x INT4 group-64 weights (PixArt ff.net.2 under --skip-quant-layers; the
  * reference's model of this layer is dequantise-then-GEMM, speedup/weight_only_nvfp4.py:128-178).
@@ -218,11 +231,19 @@ size_t dirotq_gemm_w4a16_workspace_bytes(int64_t N, int64_t K);
 int dirotq_gemm_w4a16(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const float* w_scales,
                       const void* bias, void* y, void* workspace, size_t workspace_bytes, int32_t* status,
                       void* stream);
-/* Same with an NVFP4 weight (codes / tiled UE4M3 scales / tensor scale from dirotq_pack_weight_nvfp4):
- * the forward of the reference's WeightOnlyNVFP4Linear (speedup/weight_only_nvfp4.py:128-178). */
+/* Same with an NVFP4 weight: the forward of the reference's WeightOnlyNVFP4Linear
+ * (speedup/weight_only_nvfp4.py:128-178).  Codes / tiled UE4M3 scales from either NVFP4 packer; the second-level
+ * scale is w_rowscale (fp32 [N], from dirotq_pack_weight_nvfp4_rowscale: the reference's per-channel gscale) when
+ * given, else the scalar w_tensor_scale.  Dequantised value = bf16(e2m1 * (micro * scale)), one rounding, as the
+ * reference's dequantiser computes it (:96-112). */
 int dirotq_gemm_w4a16_nvfp4(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const void* w_sf,
-                            float w_tensor_scale, const void* bias, void* y, void* workspace, size_t workspace_bytes,
-                            int32_t* status, void* stream);
+                            float w_tensor_scale, const float* w_rowscale, const void* bias, void* y, void* workspace,
+                            size_t workspace_bytes, int32_t* status, void* stream);
+
+/* The dequantisation step of the call above alone: w_out bf16 [N, K] (K a multiple of 64).  Replaces
+ * WeightOnlyNVFP4Linear.dequant (speedup/weight_only_nvfp4.py:75-125, 158-160). */
+int dirotq_dequant_weight_nvfp4(int64_t N, int64_t K, const void* w_codes, const void* w_sf, float w_tensor_scale,
+                                const float* w_rowscale, void* w_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * One wrapped linear end to end: what the patched ActQuantWrapper.forward runs
@@ -238,8 +259,10 @@ typedef struct dirotq_linear {
   const void* w_tail;       /* bf16 [N, tail_pitch] (NVFP4: divided by out_scale) */
   const void* bias;         /* bf16 [N] or NULL */
   float w_tensor_scale;     /* NVFP4 only */
-  /* Integer activations only, all three from dirotq_fold_weight_scales_f16.  When w_mult is set the
-   * forward runs dirotq_gemm_w4a4_int_f16; when NULL, the exact-integer dirotq_gemm_w4a4_int. */
+  /* Integer activations: all three from dirotq_fold_weight_scales_f16.  When w_mult is set the
+   * forward runs dirotq_gemm_w4a4_int_f16; when NULL, the exact-integer dirotq_gemm_w4a4_int.
+   * NVFP4: w_colscale alone may be set -- the per-channel scale of dirotq_pack_weight_nvfp4_rowscale (w_tail then
+   * holds w_tail / (Tx * w_tensor_scale * w_colscale[n])). */
   const void* w_mult;
   const float* w_colscale;
   const void* w_tail_f16;
@@ -276,7 +299,9 @@ int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* works
  *  - Sizes whose scratch need (dirotq_linear_workspace_bytes) exceeds the capacity are refused with
  *    DIROTQ_E_TOO_LARGE before anything is launched.
  *  - The first call on each device looks up the array's device address (a host-side runtime query);
- *    make that first call before starting any stream capture.
+ *    make that first call before starting any stream capture.  Host threads may race on that first
+ *    call (each stores the same address).  The address is cached per device ordinal (0..63; higher
+ *    ordinals are refused with DIROTQ_E_UNSUPPORTED) and does not survive a device reset.
  *  - All calls share the one array and it keeps the previous call's bytes; the entry point clears
  *    the part that must start at zero itself.  Two calls whose kernels may overlap on the GPU
  *    (different streams, no dependency) race on the array: serialise them. */

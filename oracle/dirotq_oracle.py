@@ -391,6 +391,65 @@ def weight_quant_nvfp4_hw(W: torch.Tensor, tensor_scale: Optional[float] = None)
     return deq, e2m1_nibbles(idx).reshape(N, K), micro.squeeze(-1), T
 
 
+# speedup/weight_only_nvfp4.py:35-36 -- codebook in hardware nibble order (index = nibble)
+_E2M1_BY_NIBBLE = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+
+
+def weight_quant_nvfp4_rowscale(W: torch.Tensor):
+    """The reference's own two-level NVFP4 weight quantiser, _quantize_nvfp4 (speedup/weight_only_nvfp4.py:42-72),
+    with the nibbles left unpacked:
+
+        group_scale = max(amax_g / 6, 1e-12)      gscale[n] = max(max_g group_scale / 448, 1e-12)      (fp32)
+        micro = e4m3(group_scale / gscale[n])     eff = float(micro) * gscale[n]
+        nibble = first argmin_i |W / eff - codebook[i]|
+
+    Returns (nibbles [N, K] uint8, micro [N, K/16] float8_e4m3fn, gscale [N] bf16, gscale_exact [N] fp32).
+    The reference stores the nibbles planar (column j with column j + K/2 in one byte, :66-71): see
+    ``pack_planar_halves``."""
+    N, K = W.shape
+    assert K % 16 == 0
+    Wg = W.float().reshape(N, K // 16, 16)
+    gs_full = (Wg.abs().amax(-1) / E2M1_MAX).clamp(min=1e-12)
+    gscale = (gs_full.amax(-1) / 448.0).clamp(min=1e-12)
+    micro = (gs_full / gscale[:, None]).to(torch.float8_e4m3fn)
+    eff = micro.float() * gscale[:, None]
+    # First argmin over [0 .5 1 1.5 2 3 4 6 -0 -.5 ... -6] restated as thresholds: the distances that compete are
+    # exact in fp32, a tie keeps the earlier index = the smaller magnitude, +0 precedes -0 and every negative value
+    # that rounds to zero, and a zero micro-scale (quotient inf / nan, all distances inf / nan) keeps index 0.
+    v = Wg / eff.unsqueeze(-1)
+    a = v.abs()
+    m = torch.zeros_like(v, dtype=torch.uint8)
+    for thr in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0):
+        m += (a > thr).to(torch.uint8)
+    m = torch.where(torch.isfinite(v), m, torch.zeros_like(m))
+    nib = torch.where((v < 0) & (m > 0), m + 8, m)
+    return nib.reshape(N, K), micro, gscale.to(torch.bfloat16), gscale
+
+
+def pack_planar_halves(nib: torch.Tensor) -> torch.Tensor:
+    """[N, K] nibbles -> [N, K/2] bytes, byte j = column j | column j + K/2 << 4 (weight_only_nvfp4.py:66-71)."""
+    K2 = nib.shape[1] // 2
+    return (nib[:, :K2] | (nib[:, K2:] << 4)).contiguous()
+
+
+def unpack_planar_halves(codes: torch.Tensor) -> torch.Tensor:
+    return torch.cat([codes & 0xF, codes >> 4], dim=1)
+
+
+def dequant_nvfp4_rowscale(nib: torch.Tensor, micro: torch.Tensor, gscale_bf16: torch.Tensor, eager: bool = False):
+    """bf16 weight of WeightOnlyNVFP4Linear.  eager=False: the fused dequantiser the forward uses
+    (weight_only_nvfp4.py:96-112: fp32 micro * gscale, times the codebook value, ONE rounding to bf16);
+    eager=True: dequant_torch (:162-171: bf16 product of the scales, then a bf16 product with the value)."""
+    N, K = nib.shape
+    if eager:
+        cb = torch.tensor(_E2M1_BY_NIBBLE, dtype=torch.bfloat16)
+        scale = (micro.to(torch.bfloat16) * gscale_bf16[:, None]).repeat_interleave(16, dim=1)
+        return cb[nib.long()] * scale
+    cb = torch.tensor(_E2M1_BY_NIBBLE, dtype=torch.float32)
+    scale = (micro.float() * gscale_bf16.float()[:, None]).repeat_interleave(16, dim=1)
+    return (cb[nib.long()] * scale).to(torch.bfloat16)
+
+
 def rotate_and_split_W(W: torch.Tensor, spec: LayerSpec):
     """_rotate_and_split_W (quant_utils.py:590-711), hidden / per-head / perm branches.
     Returns (W_low [N, n_low], W_tail [N, n_tail] or None, groupsize_override)."""
@@ -474,6 +533,39 @@ def w4a4_nvfp4_linear(nib_x, micro_x, Tx, nib_w, micro_w, Tw, x_tail, w_tail, bi
     if bias is not None:
         y = y + bias.double()
     return y.float()
+
+
+def qsnr_db(ref: torch.Tensor, test: torch.Tensor) -> float:
+    """10 log10(|ref|^2 / |ref - test|^2), the reference's layer-quality metric (diagnose_layer_qsnr.py:38-46)."""
+    ref, test = ref.double(), test.double()
+    noise = float(((ref - test) ** 2).sum())
+    return float("inf") if noise == 0 else 10.0 * math.log10(float((ref ** 2).sum()) / noise)
+
+
+def fused_forward_nvfp4_hw(x: torch.Tensor, spec: LayerSpec, tensor_scale: float = 1.0, x_rot: Optional[torch.Tensor] = None):
+    """What the block-scaled tensor-core NVFP4 layer computes, in fp64: activations by the two-level recipe
+    (act_quant_nvfp4_hw), the fused weight's low block put back on a 4-bit grid by the reference's own two-level
+    weight recipe (weight_quant_nvfp4_rowscale), the 16-bit branch and bias added.  ``x_rot`` overrides the rotated
+    tensor (pass the one the kernel produced to remove accumulation-order differences)."""
+    cfg = spec.cfg
+    if x_rot is None:
+        x_rot = rotate_hidden(x, spec.rotation.to(x.dtype), fp32=False) if spec.rotation is not None else x
+    lead = x_rot.shape[:-1]
+    x3 = x_rot.reshape(1, -1, x_rot.shape[-1])
+    r = act_quant_nvfp4_hw(x3, cfg, tensor_scale)
+    M, q_len = x3.shape[1], r.q_len
+    kq = (q_len + 15) // 16 * 16
+    w_low = F.pad(spec.weight[:, :q_len].float(), (0, kq - q_len))
+    nib_w, micro_w, g_bf16, _ = weight_quant_nvfp4_rowscale(w_low)
+    N = w_low.shape[0]
+    dw = (e2m1_values(nib_w, torch.float64).reshape(N, -1, 16) * (micro_w.double() * g_bf16.double()[:, None]).unsqueeze(-1))
+    dx = F.pad(r.deq.double().reshape(M, q_len), (0, kq - q_len))
+    y = dx @ dw.reshape(N, kq).T
+    if cfg.high_bits_length > 0:
+        y = y + r.tail.double().reshape(M, -1) @ spec.weight[:, q_len:].double().T
+    if spec.bias is not None:
+        y = y + spec.bias.double()
+    return y.float().reshape(*lead, N)
 
 
 # ---------------------------------------------------------------------------

@@ -265,6 +265,31 @@ def main(ref_root):
     np.savez_compressed(os.path.join(HERE, "weights.npz"), **to_np(out))
     print("wrote weights")
 
+    # 9. the two-level NVFP4 weight recipe on a wide dynamic range: group magnitudes spread over 2^-16 .. 1 inside a
+    #    row (micro-scales down to subnormal and zero), an all-zero row, all-zero and denormal-small groups, and one
+    #    group whose effective scale is exactly 1 with every codebook midpoint of both signs in it (tie rule)
+    try:
+        import weight_only_nvfp4 as wo
+        g = torch.Generator().manual_seed(43)
+        W2 = torch.randn(64, 512, generator=g)
+        W2 = W2 * torch.exp2(torch.randint(-16, 1, (64, 32, 1), generator=g).float()).expand(64, 32, 16).reshape(64, 512)
+        W2[3] = 0
+        W2[4, :16] = 0
+        W2[5, 16:32] = 1e-30
+        W2[6, :16] = torch.tensor([6., 0.25, -0.25, 0.75, -0.75, 1.25, -1.25, 1.75, -1.75, 2.5, -2.5, 3.5, -3.5, 5., -5., 0.])
+        W2[6, 16:] = W2[6, 16:].clamp(-6, 6)
+        codes, micro, gscale = wo._quantize_nvfp4(W2)
+        lin = wo.WeightOnlyNVFP4Linear(512, 64, bias=False, device="cpu")
+        lin.codes.copy_(codes)
+        lin.micro.copy_(micro)
+        lin.gscale.copy_(gscale)
+        out = {"W": W2, "wo_codes": codes, "wo_micro_u8": micro.view(torch.uint8), "wo_gscale": gscale,
+               "wo_dequant_torch": lin.dequant_torch()}
+        np.savez_compressed(os.path.join(HERE, "weights_nvfp4_rowscale.npz"), **to_np(out))
+        print("wrote weights_nvfp4_rowscale")
+    except Exception as e:  # pragma: no cover
+        print("weights_nvfp4_rowscale skipped:", e)
+
 
 if __name__ == "__main__":
     if len(sys.argv) < 2:

@@ -118,6 +118,38 @@ def test_nvfp4_gemm(M, N, D, tail):
     assert cosine(y.float().cpu(), y_ref) > 0.9999
 
 
+@pytest.mark.parametrize("M,N,D,tail", [(300, 256, 320, 64), (1000, 1152, 1152, 144), (260, 136, 256, 0)])
+def test_nvfp4_gemm_per_channel_weight_scale(M, N, D, tail):
+    """Weights by the reference's two-level recipe (per-output-channel scale, speedup/weight_only_nvfp4.py:42-72):
+    the GEMM applies the channel scale in its epilogue, the 16-bit branch is pre-divided by it."""
+    from dirotq_b200 import ops
+    from gpu_helpers import decode_act
+    g = torch.Generator().manual_seed(14)
+    Tx = 1.0
+    fmt = ops.ActFormat(ops.NVFP4_HW, D, tail_len=tail, group_size=16, tensor_scale=Tx)
+    x = O.synth_activations(M, D, g)
+    act = ops.quantize_act(x.cuda(), fmt)
+    lay = act.layout
+    dec = decode_act(act)
+    W = torch.randn(N, lay.q_len, generator=g) * 0.05 * torch.exp(torch.randn(N, 1, generator=g))   # channel scales vary
+    pk = ops.pack_weight_nvfp4_rowscale(W.cuda())
+    nib_w, micro_w, g_bf16, _ = O.weight_quant_nvfp4_rowscale(W)
+    assert torch.equal(O.unpack_seq_nibbles(pk.codes.cpu())[:, : lay.q_len], nib_w)
+    assert torch.equal(pk.row_scale.cpu()[:N], g_bf16.float())
+    w_tail = (torch.randn(N, lay.tail_total, generator=g) * 0.02).to(torch.bfloat16) if tail else None
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    wts = None
+    if tail:
+        wts = ops.pad_tail_weight((w_tail.float() / (Tx * g_bf16.float()[:, None])).to(torch.bfloat16), lay.tail_pitch, N, "cuda")
+    y = ops.gemm_w4a4_nvfp4(act, pk, wts, bias.cuda())
+    ops.check_status()
+    nib_x = dec["codes"].reshape(M, -1)[:, : lay.q_len]
+    eff_w = micro_w.float().double() * g_bf16.double()[:, None]           # per-group effective weight scale
+    y_ref = O.w4a4_nvfp4_linear(nib_x, dec["scale"], Tx, nib_w, eff_w, 1.0, dec.get("tail"), w_tail, bias)
+    assert rel_l2(y.float().cpu(), y_ref) < 3e-3
+    assert cosine(y.float().cpu(), y_ref) > 0.9999
+
+
 # ---- INT4 at tensor rate: codes expanded to fp16 next to the tensor core, one fp32 accumulator ----------
 @pytest.mark.parametrize("mode,M,N,D,tail", [("sym", 300, 256, 320, 64), ("sym", 1000, 1152, 1152, 64),
                                              ("asym", 520, 384, 1152, 64), ("sym", 260, 128, 256, 0),

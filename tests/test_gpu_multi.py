@@ -24,3 +24,42 @@ def test_tp_ffn_and_dp_on_two_gpus():
     for quant, r in res.items():
         assert r["dp_equal"], quant
         assert r["tp_rel_l2"] < 1e-2, (quant, r)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices():
+    """Per-device set-up inside the library (shared-memory attribute of every kernel, SM count, status word): the
+    same small layers on cuda:0 and then on cuda:1 from ONE process, both against the oracle.  No peer access."""
+    import torch.nn as nn
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.wrapper import ActQuantWrapper
+    from oracle import dirotq_oracle as O
+    saved = ActQuantWrapper.forward
+    backend.patch_forward()
+    try:
+        g = torch.Generator().manual_seed(11)
+        M, D, N, k = 300, 256, 128, 64
+        x = O.synth_activations(M, D, g).reshape(1, M, D)
+        U = O.random_orthogonal(D, g).float()
+        for quant, gs in (("int", 64), ("nvfp4", 16)):
+            W_rot = (torch.randn(N, D, generator=g) * 0.05) @ U
+            deq = O.weight_quant_int(W_rot[:, : D - k], 4, gs)[0] if quant == "int" else O.weight_quant_nvfp4(W_rot[:, : D - k])[0]
+            W = torch.cat([deq, W_rot[:, D - k:]], dim=1).to(torch.bfloat16)
+            outs = []
+            for dev in ("cuda:0", "cuda:1"):
+                with torch.cuda.device(dev):
+                    lin = nn.Linear(D, N).to(torch.bfloat16)
+                    lin.weight.data.copy_(W)
+                    w = ActQuantWrapper(lin)
+                    w.quantizer.configure(bits=4, groupsize=gs, sym=True, high_bits_length=k, quant_dtype=quant)
+                    w.rotation, w._unrot_fused = U, True
+                    y = w(x.to(dev))
+                    ops.check_status(dev)
+                    outs.append(y.float().cpu())
+            assert torch.equal(outs[0], outs[1]), quant
+            if quant == "int":
+                spec = O.LayerSpec(W, lin.bias.data.cpu(), O.QuantCfg(4, gs, True, 1.0, k, quant), rotation=U)
+                y_ref = O.fused_forward(x, spec, fp32=False).float()
+                assert float((outs[1] - y_ref).norm() / y_ref.norm()) < 0.05
+    finally:
+        ActQuantWrapper.forward = saved

@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(l, name), f"{name} declared in the header but not exported"
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
-    assert _lib.lib().dirotq_abi_version() == 4
+    assert _lib.lib().dirotq_abi_version() == _lib.ABI_VERSION == int(re.search(r"DIROTQ_ABI_VERSION (\d+)", hdr).group(1))
     assert b"aligned" in _lib.lib().dirotq_error_string(-3)
 
 

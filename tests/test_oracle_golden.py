@@ -125,6 +125,28 @@ def test_two_level_nvfp4_weight_quantizer_close_to_reference_recipe():
     assert bits_equal(again, deq)
 
 
+@pytest.mark.parametrize("name", ["weights", "weights_nvfp4_rowscale"])
+def test_reference_two_level_nvfp4_weight_recipe_bit_exact(name):
+    """speedup/weight_only_nvfp4.py:42-72 (_quantize_nvfp4): codes (planar nibble order), E4M3 micro-scales and the
+    per-channel bf16 scale of the unmodified reference, bit for bit -- incl. micro-scales that round to zero, an
+    all-zero row and every codebook midpoint of both signs (second fixture)."""
+    g = load_golden(name)
+    nib, micro, gscale, _ = O.weight_quant_nvfp4_rowscale(g["W"])
+    assert torch.equal(O.pack_planar_halves(nib), g["wo_codes"])
+    assert torch.equal(micro.view(torch.uint8), g["wo_micro_u8"])
+    assert bits_equal(gscale, g["wo_gscale"])
+    assert torch.equal(O.unpack_planar_halves(g["wo_codes"]), nib)
+    if "wo_dequant_torch" in g:
+        # eager dequantiser of the reference (:162-171), bit for bit; the fused one (:96-112) rounds once instead of twice
+        assert bits_equal(O.dequant_nvfp4_rowscale(nib, micro, gscale, eager=True), g["wo_dequant_torch"])
+        one = O.dequant_nvfp4_rowscale(nib, micro, gscale).float()
+        two = g["wo_dequant_torch"].float()
+        assert float((one - two).abs().max() / two.abs().max()) < 2.0 ** -7
+        if name == "weights_nvfp4_rowscale":
+            assert int((micro.float() == 0).sum()) > 0              # the zero-micro-scale rule is exercised
+            assert nib[6, :16].tolist() == [7, 0, 0, 1, 9, 2, 10, 3, 11, 4, 12, 5, 13, 6, 14, 0]
+
+
 def test_formats_roundtrip():
     g = torch.Generator().manual_seed(0)
     c = torch.randint(-8, 8, (5, 128), generator=g)

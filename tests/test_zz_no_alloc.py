@@ -50,3 +50,29 @@ def test_static_scratch_entry_point_matches_regular_one():
                                           C.c_void_p(ops.status_word(x.device).data_ptr()),
                                           C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == -5 and b"capacity" in lib.dirotq_error_string(rc)
+
+
+def test_static_scratch_pads_never_read_leftover_bytes():
+    """Shapes whose layouts have REAL padding -- a tail of 44 channels in a pitch of 48, a last INT4 group of 20 of
+    64 code slots, NVFP4 rows with a partial last 64-slot chunk, M not a multiple of 128 -- run right after a larger
+    call that leaves non-zero bytes over the whole carve.  The result must equal the regular entry point's on a
+    zeroed workspace: pad columns and rows reach the GEMM as zeros from the copy engine's bounds handling, pad code
+    slots as zero codes from the quantiser."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    g = torch.Generator().manual_seed(78)
+    big = _layer("int4", 1152, 256, 64, 950)
+    x_big = synth_activations(3000, 1152, g).cuda()
+    for quant, D, N, k, M, sym in [("int4", 320, 136, 44, 333, False), ("nvfp4", 320, 136, 48, 333, True),
+                                   ("int4", 320, 136, 44, 77, True)]:
+        ld = dit.LayerDef("probe", D, N, tail=k)
+        w = dit.make_wrapped_linear(ld, quant, 960, "cuda", a_sym=sym)
+        st = backend.prepare_layer(w, "cuda", w._b200_explicit)
+        assert st.layout.tail_pitch != st.layout.tail_total or st.layout.q_len % 64
+        x = synth_activations(M, D, g).cuda()
+        backend.linear_forward_static(big, x_big)           # fills the array with another layer's bytes
+        y_static = backend.linear_forward_static(st, x)
+        y_ref = backend.linear_forward(st, x)
+        ops.check_status()
+        assert bool(torch.isfinite(y_static.float()).all())
+        assert torch.equal(y_static, y_ref), (quant, D, k, M)
