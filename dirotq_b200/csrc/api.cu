@@ -32,6 +32,7 @@ const char* dirotq_status_string(int status) {
     case 3: return "timeout: epilogue waited for an accumulator";
     case 4: return "timeout: UMMA issuer waited for a drained accumulator";
     case 5: return "timeout: teardown waited for copies in flight";
+    case 6: return "timeout: scale factors did not reach tensor memory";
   }
   return "unknown device status";
 }

@@ -12,6 +12,8 @@
 //
 // Replaces `self.module(x)` of the fused forward (DiRotQ dirotq_fused_unrotation_fast.py:141) for
 // quant_dtype == "nvfp4"; the reference's speed path uses nunchaku's FP4 gemm_w4a4 here.
+#include <cstdlib>
+#include <cstring>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -264,9 +266,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
   }
 }
 
+// Tile choice.  DIROTQ_NVFP4_TILE = single | pair128 | pair256 forces one form (measurements, tests).
+static int pick_nvfp4_tile(const GemmFp4Args& a) {
+  if (const char* e = getenv("DIROTQ_NVFP4_TILE")) {
+    if (!strcmp(e, "single")) return 0;
+    if (!strcmp(e, "pair128")) return 128;
+    if (!strcmp(e, "pair256")) return 256;
+  }
+  return 0;
+}
+
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.n_chunks <= 0) return DIROTQ_E_ARG;
+  if (const int bn = pick_nvfp4_tile(a)) return launch_gemm_nvfp4_pair(a, bn, st);
   CUtensorMap txq, twq, txt, twt, ty;
   if (a.N % 8) return DIROTQ_E_UNSUPPORTED;
   const uint64_t row_bytes = (uint64_t)a.n_chunks * 32;

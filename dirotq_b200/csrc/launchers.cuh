@@ -172,6 +172,7 @@ struct GemmFp4Args {
 
 int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st);
+int launch_gemm_nvfp4_pair(const GemmFp4Args& a, int bn, cudaStream_t st);
 int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st);
 int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st);
 int launch_fold_act_and_expand(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm, void* rec,

@@ -70,7 +70,7 @@ def status_word(device) -> torch.Tensor:
     dev = torch.device(device)
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _status:
-        _status[key] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{key}")
+        _status[key] = torch.zeros(8, dtype=torch.int32, device=f"cuda:{key}")
     return _status[key]
 
 
