@@ -266,14 +266,21 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
   }
 }
 
-// Tile choice.  DIROTQ_NVFP4_TILE = single | pair128 | pair256 forces one form (measurements, tests).
+// Tile choice.  CTA pairs (gemm_nvfp4_pair.cu) halve the weight bytes each SM pulls through L2 per flop: 256 x 256 pair
+// tiles for long reductions (one accumulator, its hand-over to the epilogue is amortised over many stages), 256 x 128
+// with two accumulators for short ones; up to 128 rows a pair would idle half of itself, so the single-CTA 128 x 128
+// kernel of this file keeps those.  Measured (M = 16384 .. 32768): K = 3072 -> 1.5 .. 1.7 x the single-CTA kernel with
+// 256 x 256, K = 1152 -> 1.15 .. 1.2 x with 256 x 128.  DIROTQ_NVFP4_TILE = single | pair128 | pair256 forces one form
+// (measurements, tests).
 static int pick_nvfp4_tile(const GemmFp4Args& a) {
   if (const char* e = getenv("DIROTQ_NVFP4_TILE")) {
     if (!strcmp(e, "single")) return 0;
     if (!strcmp(e, "pair128")) return 128;
     if (!strcmp(e, "pair256")) return 256;
   }
-  return 0;
+  if (a.M <= 128) return 0;
+  const int64_t K = (int64_t)a.n_chunks * 64 + a.kt;
+  return K >= 2048 ? 256 : 128;
 }
 
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
