@@ -3,15 +3,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W]
                     [--workload pixart_int4|pixart_nvfp4|flux_int4|sana_int4|sana_w4a8] [--flux-ffn tp|dp]
-    python bench.py --impl reference ...      # the reference's fp32 CPU forward on a bounded sample
+    python bench.py --impl reference ...      # the reference's own fp32 CPU forward on a bounded sample
 
-One "step" = every wrapped linear of one denoising step of the named DiT (BASELINE config 1 by
-default: PixArt-Sigma shapes, 28 blocks x 8 linears, batch 8 x 4096 tokens per GPU), each through
-rotate -> split -> 4-bit quantise -> W4A4 GEMM + bf16 branch + dequant + bias.  `value` counts the
-algorithmic operations of the linears (2*M*N*D each; the online rotation is overhead, not credited)
-over the device time of the step.  Prints ONE JSON line on rank 0.
+One "step" = every wrapped linear of one denoising step of the named DiT (BASELINE config 1 by default: PixArt-Sigma
+shapes, 28 blocks x 8 linears, GLOBAL batch 8 x 4096 tokens split over the GPUs), each through rotate -> split ->
+4-bit quantise -> W4A4 GEMM + bf16 branch + dequant + bias.  `value` counts the algorithmic operations of the linears
+(2*M*N*D each; the online rotation is overhead, not credited) over the device time of the step.  Prints ONE JSON line
+on rank 0.  Beside the headline the line carries: `e2e` (host buffers, copies inside the timed region), `roofline`
+(dominant kernel against the measured peak of the pipe it runs on), `cpu_baseline` (the reference's fp32 forward on
+the host cores), `denoise_step` (a model-shaped step: the same linears inside attention / norm / modulation glue, with
+the path's share of it) and `sub` (NVFP4 FLUX-shaped GEMMs against an FP4 peak, the NVFP4 and FLUX steps; on several
+GPUs the tensor-parallel FLUX feed-forwards with their NCCL time).
 """
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -25,19 +30,18 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (block fn name, n_blocks, quant, tokens per sample, batch per GPU, description)
-    "pixart_int4": ("pixart_block", 28, "int4", 4096, 8,
+    # name: (block fn name, n_blocks, quant, tokens per sample, global batch, model family, description)
+    "pixart_int4": ("pixart_block", 28, "int4", 4096, 8, "pixart",
                     "BASELINE config 1: PixArt-Sigma-shaped step, 28 blocks x (7 INT W4A4 g64 k=64 + ff.net.2 W4A16), "
-                    "batch 8 x 4096 tokens per GPU"),
-    "pixart_nvfp4": ("pixart_block", 28, "nvfp4", 4096, 8,
+                    "global batch 8 x 4096 tokens"),
+    "pixart_nvfp4": ("pixart_block", 28, "nvfp4", 4096, 8, "pixart",
                      "BASELINE config 2: same step in NVFP4 W4A4 (E2M1 g16, UE4M3 group scales, fp32 tensor scale)"),
-    "sana_int4": ("sana_block", 20, "int4", 1024, 16,
+    "sana_int4": ("sana_block", 20, "int4", 1024, 16, "sana",
                   "BASELINE config 4 (W4A4): SANA-1.6B-shaped step, 20 blocks x 6 linears (hidden 2240, k=320, per-head "
-                  "70 x 32 out-projections), batch 16 x 1024 tokens per GPU"),
-    "sana_w4a8": ("sana_block", 20, "int8", 1024, 16,
+                  "70 x 32 out-projections), global batch 16 x 1024 tokens"),
+    "sana_w4a8": ("sana_block", 20, "int8", 1024, 16, "sana",
                   "BASELINE config 4 (W4A8): same step with asymmetric 8-bit activations"),
-    # FLUX runs at a FIXED global batch (strong scaling); see dirotq_b200.parallel.FluxLinearStep
-    "flux_int4": ("flux_double_block", 57, "int4", 4608, 4,
+    "flux_int4": ("flux_double_block", 57, "int4", 4608, 4, "flux",
                   "BASELINE config 3: FLUX.1-dev-shaped step, 19 double-stream (image 4096 + text 512 tokens) + 38 "
                   "single-stream blocks, INT W4A4 g64 k=384, per-head out-projections, K=12288 down-projections "
                   "without rotation, global batch 4"),
@@ -51,10 +55,14 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="pixart_int4", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong (default): the workload's global batch is split over the GPUs; weak: every GPU runs "
+                         "the whole batch (independent replicas)")
     ap.add_argument("--blocks", type=int, default=0, help="override the number of blocks (smoke runs only)")
     ap.add_argument("--flux-ffn", default="tp", choices=["tp", "dp"],
                     help="flux_int4 at N > 1: FFN pairs tensor-parallel (all-gather + reduce-scatter) or row-sharded")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub", action="store_true", help="skip the sub-records and the model-shaped step")
     ap.add_argument("--no-fuse-gelu", action="store_true",
                     help="keep the GELU between the FFN linears as a separate PyTorch kernel")
     ap.add_argument("--cache-weight-panel", action="store_true",
@@ -62,21 +70,86 @@ def parse():
                          "from the 4-bit codes on every call")
     ap.add_argument("--exact-int", action="store_true",
                     help="INT4 layers through the exact-integer kind::i8 GEMM instead of the tensor-rate fp16 one")
-    ap.add_argument("--profile-case", action="store_true",
-                    help="run a small case for ncu instead of the benchmark: one 1152->1152 k=64 layer at M=16384 "
-                         "(38 MB in, 38 MB out), INT4 then NVFP4, three forwards each")
+    ap.add_argument("--profile-case", default="", nargs="?", const="layers",
+                    help="run a small case for ncu instead of the benchmark: 'layers' = one 1152->1152 k=64 layer at "
+                         "M=16384, INT4 then NVFP4, three forwards each; 'flux_nvfp4' = one NVFP4 3072->12288 k=384 "
+                         "layer at M=4096; 'quantize' = the quantise-only kernel at M=4096, D=12288")
     return ap.parse_args()
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU arm: the reference's fp32 fused-unrotation forward (oracle port), bounded sample
+# CPU arm: the reference's own fp32 fused-unrotation forward, bounded sample
 # ---------------------------------------------------------------------------------------------
-def cpu_reference_tflops(workload, steps, warmup, budget_s=20.0):
-    """Times dirotq_fused_unrotation._fused_forward (fp32 rotation + fake quant + nn.Linear), restated in
-    oracle/dirotq_oracle.py, on one block of the workload at M = 2048 tokens with all host threads."""
+def _config0(seed=0, M=8192, D=1152, N=1152, k=64):
+    """BASELINE config 0: one PixArt-Sigma attention linear.  x bf16 [2, 4096, 1152] (N(0,1) + planted rank-32 subspace
+    + 8 heavy-tailed channels), orthogonal rotation, INT4 g64 weights with fp16 group scales + 64 bf16 coefficients."""
+    from oracle import dirotq_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    x = O.synth_activations(M, D, g).reshape(2, M // 2, D)
+    U = O.random_orthogonal(D, g).float()
+    qw = torch.randint(-8, 8, (N, D - k), generator=g)
+    sw = (torch.rand(N, (D - k) // 64, generator=g) * 0.015 + 0.005).to(torch.float16).float()
+    w_tail = (torch.randn(N, k, generator=g) * 0.02).to(torch.bfloat16)
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    w_low = (qw.reshape(N, -1, 64).float() * sw.unsqueeze(-1)).reshape(N, -1)
+    W = torch.cat([w_low, w_tail.float()], dim=1).to(torch.bfloat16)
+    return x, U, W, bias, k
+
+
+def cpu_reference_config0(runs=3, warm=1, budget_s=25.0):
+    """BASELINE config 0 through the reference's own `_fused_forward` (dirotq_fused_unrotation.py:62-148), imported
+    unmodified from oracle/_ref, all host threads: min and median of `runs` forwards and a per-stage split."""
+    from oracle import make_ref
+    qu, slow, _ = make_ref.load()
+    import torch.nn as nn
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, U, W, bias, k = _config0()
+    lin = nn.Linear(1152, 1152, bias=True).to(torch.bfloat16)
+    lin.weight.data.copy_(W)
+    lin.bias.data.copy_(bias)
+    w = qu.ActQuantWrapper(lin)
+    w.quantizer.configure(bits=4, groupsize=64, sym=True, high_bits_length=k, quant_dtype="int")
+    w.rotation = U
+    w._unrot_fused = True
+    ops = 2.0 * x.shape[0] * x.shape[1] * 1152 * 1152
+    with torch.no_grad():
+        for _ in range(warm):
+            slow._fused_forward(w, x)
+        times, t_all = [], time.perf_counter()
+        for _ in range(max(1, runs)):
+            t0 = time.perf_counter()
+            slow._fused_forward(w, x)
+            times.append(time.perf_counter() - t0)
+            if time.perf_counter() - t_all > budget_s:
+                break
+        # per-stage split: the same operations the forward runs, timed one after another
+        t0 = time.perf_counter()
+        xr = (x.float().reshape(-1, 1152) @ U).reshape(x.shape)
+        t1 = time.perf_counter()
+        w.quantizer.find_params(xr)
+        xq = w.quantizer(xr).to(torch.bfloat16)
+        w.quantizer.free()
+        t2 = time.perf_counter()
+        w.module(xq)
+        t3 = time.perf_counter()
+    t_med, t_min = statistics.median(times), min(times)
+    cb = {"value": ops / t_med / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "reference",
+          "value_best": ops / t_min / 1e12, "ms_median": t_med * 1e3, "ms_min": t_min * 1e3,
+          "stages_ms": {"cast_and_rotation_fp32": (t1 - t0) * 1e3, "find_params_and_quantise": (t2 - t1) * 1e3,
+                        "bf16_linear": (t3 - t2) * 1e3},
+          "sample": f"BASELINE config 0: one PixArt-Sigma attention linear, x bf16 [2,4096,1152], k=64, INT4 g64 symmetric, "
+                    f"through the reference's own dirotq_fused_unrotation._fused_forward (unmodified, oracle/_ref), torch "
+                    f"CPU {cores} threads, {warm} warm-up + {len(times)} timed forwards (median; best in value_best)"}
+    return cb, t_med
+
+
+def cpu_port_tflops(workload, steps, warmup, budget_s=20.0):
+    """Fallback when oracle/_ref is not populated: the fp32 forward restated in oracle/dirotq_oracle.py on one block of
+    the workload at M = 2048 tokens."""
     from oracle import dirotq_oracle as O
     from dirotq_b200 import dit
-    blk_name, _, quant, _, _, _ = WORKLOADS[workload]
+    blk_name, _, quant = WORKLOADS[workload][:3]
     block = getattr(dit, blk_name)()
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -90,9 +163,8 @@ def cpu_reference_tflops(workload, steps, warmup, budget_s=20.0):
         if ld.kind == "w4a16":
             specs.append((ld, None, W, b))
             continue
-        cfg = O.QuantCfg(4, 16 if quant == "nvfp4" else 64, True, 1.0, ld.tail, "nvfp4" if quant == "nvfp4" else "int")
         bits = 8 if quant == "int8" else 4
-        cfg = O.QuantCfg(bits, cfg.groupsize, bits == 4, 1.0, ld.tail, cfg.quant_dtype)
+        cfg = O.QuantCfg(bits, 16 if quant == "nvfp4" else 64, bits == 4, 1.0, ld.tail, "nvfp4" if quant == "nvfp4" else "int")
         U = O.random_orthogonal(ld.in_f, g).float() if ld.kind == "hidden" else None
         Uh = None
         if ld.kind == "perhead":
@@ -104,18 +176,14 @@ def cpu_reference_tflops(workload, steps, warmup, budget_s=20.0):
         ff = None
         for ld, spec, W, b in specs:
             src = x if ld.source == "x" else ff
-            if spec is None:
-                y = torch.nn.functional.linear(src, W, b)
-            else:
-                y = O.fused_forward(src, spec, fp32=True)
+            y = torch.nn.functional.linear(src, W, b) if spec is None else O.fused_forward(src, spec, fp32=True)
             if ld.out_f > ld.in_f:
                 ff = torch.nn.functional.gelu(y, approximate="tanh")
         return y
 
     for _ in range(max(1, warmup)):
         one_pass()
-    times = []
-    t_all = time.perf_counter()
+    times, t_all = [], time.perf_counter()
     for _ in range(max(1, steps)):
         t0 = time.perf_counter()
         one_pass()
@@ -125,19 +193,25 @@ def cpu_reference_tflops(workload, steps, warmup, budget_s=20.0):
     t = statistics.median(times)
     return {"value": ops / t / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
             "sample": f"one {blk_name} ({len(block)} linears) at M=2048 tokens, fp32 _fused_forward restated in "
-                      f"oracle/, torch CPU {cores} threads, median of {len(times)} passes ({t*1e3:.0f} ms each)"}, t
+                      f"oracle/ (oracle/_ref not populated), torch CPU {cores} threads, median of {len(times)} passes"}, t
+
+
+def cpu_baseline(workload, steps, warmup, budget_s):
+    from oracle import make_ref
+    if make_ref.available():
+        return cpu_reference_config0(runs=max(3, steps), warm=max(1, min(warmup, 2)), budget_s=budget_s)
+    return cpu_port_tflops(workload, steps, warmup, budget_s)
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cb, t = cpu_reference_tflops(args.workload, args.steps, args.warmup, budget_s=120.0)
+    cb, t = cpu_baseline(args.workload, args.steps, args.warmup, budget_s=120.0)
     line = {"impl": "reference", "metric": "w4a4_linear_tflops", "value": cb["value"], "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
-            "higher_is_better": True, "scaling": "strong" if args.workload.startswith("flux") else "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOADS[args.workload][5], "sample": cb["sample"]},
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOADS[args.workload][6], "sample": cb["sample"]},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -185,8 +259,7 @@ class ClockSampler:
             for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        # samples under load = upper half by power
-        if sm:
+        if sm:   # samples under load = upper half by power
             order = sorted(range(len(sm)), key=lambda i: pw[i])
             load = [sm[i] for i in order[len(order) // 2:]]
             return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
@@ -202,12 +275,67 @@ def measured_peaks():
     return 6650.0, 1590.0, 1400.0, "fallback"
 
 
+def tensor_peak(kind):
+    """(peak TFLOP/s, description) of the tensor pipe a kernel kind runs on.  Only bf16 is MEASURED on this pool
+    (cuBLAS, seconds-long loop under the power cap); dense FP4 is derived as 4 x that figure, dense INT8 as 2 x."""
+    _, _, bf16_sust, which = measured_peaks()
+    if kind == "nvfp4":
+        return 4.0 * bf16_sust, f"derived: 4 x the {which} cuBLAS bf16 sustained figure ({bf16_sust:.0f} TFLOP/s); no FP4 measurement exists"
+    if kind == "i8":
+        return 2.0 * bf16_sust, f"derived: 2 x the {which} cuBLAS bf16 sustained figure ({bf16_sust:.0f} TFLOP/s); no INT8 measurement exists"
+    return bf16_sust, f"{which}: cuBLAS bf16 sustained (fp16 and bf16 share the pipe and the rate)"
+
+
+class Dist:
+    def __init__(self):
+        import torch.distributed as dist
+        self.dist = dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dev = torch.device("cuda", self.local)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, steps):
+        """Device milliseconds of `steps` calls, bracketed by barrier + synchronize, max over ranks."""
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        self.barrier()
+        ms = e0.elapsed_time(e1)
+        if self.world > 1:
+            t = torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+
+def effective_rotation_ops(layers, block, M):
+    """Rotation work that actually runs: sibling layers that reuse the activations of the layer before them
+    (to_k / to_v after to_q) rotate nothing."""
+    from dirotq_b200 import dit
+    nb = len(block)
+    tot = 0.0
+    for idx, lyr in enumerate(layers):
+        st = getattr(lyr, "_b200_state", None)
+        if st is None or (st.shared is not None and st.member_id > 0):
+            continue
+        tot += dit.rotation_ops(block[idx % nb], M)
+    return tot
+
+
 def run_ours(args):
-    import torch.distributed as dist
     from dirotq_b200 import backend, dit, ops
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    from dirotq_b200.synth import synth_activations
+    D_ = Dist()
+    world, rank, dev = D_.world, D_.rank, D_.dev
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
     # stdout carries the JSON line only: everything else written to file descriptor 1 until then (library
@@ -215,23 +343,24 @@ def run_ours(args):
     sys.stdout.flush()
     saved_stdout_fd = os.dup(1)
     os.dup2(2, 1)
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    torch.cuda.set_device(D_.local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    blk_name, n_blocks, quant, tokens, batch, desc = WORKLOADS[args.workload]
+        D_.dist.init_process_group("nccl", device_id=dev)
+    blk_name, n_blocks, quant, tokens, gbatch, family, desc = WORKLOADS[args.workload]
     if args.blocks:
         n_blocks = args.blocks
     is_flux = args.workload.startswith("flux")
-    from dirotq_b200.synth import synth_activations
-    import contextlib
+    strong = is_flux or args.scaling == "strong"
+    if strong and gbatch % world and not is_flux:
+        raise SystemExit(f"global batch {gbatch} does not split over {world} GPUs; use --scaling weak")
+    batch = gbatch // world if (strong and not is_flux) else gbatch
     g = torch.Generator().manual_seed(1234 + rank)
-    with contextlib.redirect_stdout(sys.stderr):     # stdout carries the JSON line only
+    with contextlib.redirect_stdout(sys.stderr):
         backend.patch_forward()
         if is_flux:
             from dirotq_b200.parallel import FluxLinearStep
             n_double = args.blocks if args.blocks else 19
-            step = FluxLinearStep(world, rank, dev, batch=batch, n_double=n_double, n_single=2 * n_double,
+            step = FluxLinearStep(world, rank, dev, batch=gbatch, n_double=n_double, n_single=2 * n_double,
                                   ffn=args.flux_ffn, quant=quant)
             backend.preconvert_rotations_to_device(step.layers, dev)
             n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else step.fuse_gelu()
@@ -240,50 +369,28 @@ def run_ours(args):
                 lyr.rotation = lyr.rotation_per_head = None
             torch.cuda.empty_cache()
             n_blocks = 3 * n_double
-            M, D, out_f = step.rows_per_rank("single"), 3072, 3072   # rows per GPU (strong scaling: global batch fixed)
+            M, D, out_f = step.rows_per_rank("single"), 3072, 3072
             lin_ops, rot_ops = step.ops_per_step()
             lin_ops, rot_ops = lin_ops / world, rot_ops / world      # per-GPU share; the JSON line reports world x this
             x_host = synth_activations(M, D, g).pin_memory()
             y_shape = (M, out_f)
-            scaling = "strong"
             l2_note = f"inputs larger than L2 ({len(step._flat)} distinct weight sets per step)"
         else:
             block = getattr(dit, blk_name)()
-            M = tokens * batch                           # rows per GPU (weak scaling: fixed per-GPU batch)
+            M = tokens * batch
             D, out_f = block[0].in_f, block[-1].out_f
             step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=1000 + 7919 * rank)
             backend.preconvert_rotations_to_device(step, dev)
             n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else backend.fuse_gelu_modules(step)
-            lin_ops, rot_ops = step.ops_per_step(M)
-            # step input: synthetic activations with the config-0 distribution, in PINNED host memory
+            lin_ops, _ = step.ops_per_step(M)
+            rot_ops = effective_rotation_ops(step.layers, step.block, M)
             x_host = synth_activations(M, D, g).reshape(batch, tokens, D).pin_memory()
             y_shape = (batch, tokens, out_f)
-            scaling = "weak"
             l2_note = (f"inputs larger than L2 ({M * D * 2 / 1e6:.0f} MB activations + {len(step.layers)} distinct "
                        f"weight sets per step)")
     x_dev = x_host.to(dev, non_blocking=True)
     y_host = torch.empty(*y_shape, dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
 
     def step_resident():
         return step(x_dev)
@@ -293,48 +400,70 @@ def run_ours(args):
     from dirotq_b200.dit import HostStreamedStep
     streamed = HostStreamedStep(step, x_host, y_host, dev)
 
-    def step_e2e():
-        return streamed()
-
     for _ in range(max(3, args.warmup)):
         step_resident()
     ops.check_status(dev)
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(D_.local)
     if rank == 0:
         sampler.start()
     torch.cuda.profiler.start()          # lets `ncu --profile-from-start off` see the timed region only
-    ms = timed(step_resident, args.steps)
+    ms = D_.timed(step_resident, args.steps)
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
-    step_e2e()
-    step_e2e()
+    streamed()
+    streamed()
 
     def e2e_steps():
         for _ in range(args.steps):
-            step_e2e()
+            streamed()
         streamed.finish()                  # the timer's closing event waits for the last result copy
-    ms_e2e = timed(e2e_steps, 1) / args.steps
+    ms_e2e = D_.timed(e2e_steps, 1) / args.steps
     ops.check_status(dev)
 
     # roofline pass: the same launches, the dominant kernel bracketed by CUDA events on its stream
-    roof = roofline_pass(step, x_dev, M, quant, dev, args.steps) if rank == 0 and not is_flux else None
-    if rank == 0 and is_flux:
-        roof = roofline_pass_flux(step, x_dev, dev)
+    roof = None
+    if rank == 0:
+        roof = roofline_pass_flux(step, x_dev, dev) if is_flux else roofline_pass(step, x_dev, M, quant, dev, args.steps,
+                                                                                  exact_int=args.exact_int)
+    launches = step.kernel_launches_per_step() * args.steps
+
+    # ---- model-shaped step and sub-records ---------------------------------------------------------------------
+    denoise, sub = None, {}
+    if not args.no_sub and not args.blocks:
+        del streamed
+        if not is_flux:
+            step.blocks = None
+        step = None
+        torch.cuda.empty_cache()
+        with contextlib.redirect_stdout(sys.stderr):
+            denoise = denoise_record(D_, family, quant, gbatch, world, strong, args)
+            if world == 1:
+                sub["nvfp4_flux_gemm"] = sub_nvfp4_flux_gemms(dev)
+                if args.workload != "pixart_nvfp4":
+                    sub["pixart_nvfp4"] = sub_linear_step(D_, "pixart_nvfp4", 28)
+                if not is_flux:
+                    sub["flux_int4"] = sub_flux_step(D_, 4, "dp")
+            elif not is_flux:
+                sub["flux_int4_tp"] = sub_flux_step(D_, 2, "tp")
 
     cb = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cb, _ = cpu_reference_tflops(args.workload, 10, 1)
+        cb, _ = cpu_baseline(args.workload, 5, 1, budget_s=25.0)
 
     if rank == 0:
+        int_dtype = "s8" if args.exact_int else "f16"
         line = {
             "metric": "w4a4_linear_tflops", "value": world * lin_ops / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": "e2m1" if quant == "nvfp4" else "s8", "data": "synthetic",
-            "config": {"workload": desc, "blocks": n_blocks, "rows_per_gpu": M,
-                       "global_batch": batch if is_flux else batch * world,
-                       "parallelism": (f"rows/{world} + ffn-{step.ffn}" if is_flux else f"dp{world}"),
+            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "e2m1" if quant == "nvfp4" else int_dtype, "data": "synthetic",
+            "config": {"workload": desc, "blocks": n_blocks, "rows_per_gpu": M, "global_batch": gbatch if strong else gbatch * world,
+                       "parallelism": (f"rows/{world} + ffn-{args.flux_ffn if world > 1 else 'dp'}" if is_flux else f"dp{world}"),
+                       "arithmetic": ("E2M1 x E2M1 block-scaled (tcgen05 kind::mxf4nvf4), fp32 accumulation" if quant == "nvfp4"
+                                      else "int8 x int8 -> int32 per 64-chunk (tcgen05 kind::i8)" if args.exact_int
+                                      else "4-bit codes expanded to fp16 beside the tensor core, fp16 x fp16 -> fp32 "
+                                           "(tcgen05 kind::f16); the exact-integer kind::i8 route is --exact-int"),
                        "gelu": (f"fused into the up-projection GEMM epilogue ({n_fused} layers)" if n_fused
                                 else "separate PyTorch kernel"),
                        "l2": l2_note,
@@ -342,11 +471,11 @@ def run_ours(args):
             "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
                     "copies": "pinned host memory, side streams, two device input buffers (dit.HostStreamedStep)"},
-            "gpu_launches": step.kernel_launches_per_step() * args.steps,
-            "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
+            "gpu_launches": launches,
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cb, "denoise_step": denoise, "sub": sub or None,
         }
     if world > 1:
-        dist.destroy_process_group()
+        D_.dist.destroy_process_group()
     sys.stdout.flush()
     os.dup2(saved_stdout_fd, 1)
     os.close(saved_stdout_fd)
@@ -354,16 +483,164 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
 
 
-def roofline_pass(step, x_dev, M, quant, dev, steps):
+# ---------------------------------------------------------------------------------------------
+# model-shaped step, sub-records
+# ---------------------------------------------------------------------------------------------
+def denoise_record(D_, family, quant, gbatch, world, strong, args):
+    """One model-shaped denoising step (dirotq_b200.denoise): the wrapped linears inside attention / norm /
+    modulation / residual glue, chained block to block.  Batch-sharded over the GPUs, no collective."""
+    from dirotq_b200 import backend, denoise, ops
+    dev = D_.dev
+    n_blocks = None
+    note = "all blocks"
+    if family == "flux":                 # 57 blocks at batch 4 take a while to build: a slice of the stack is timed
+        n_blocks, note = 3, "3 of 19 double-stream + 6 of 38 single-stream blocks"
+    batch = gbatch // world if strong else gbatch
+    if batch < 1:
+        return {"skipped": f"global batch {gbatch} does not split over {world} GPUs"}
+    step = denoise.DenoiseStep(family, quant, dev, n_blocks=n_blocks, seed=5000 + 7919 * D_.rank, prepare=True)
+    n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else backend.fuse_gelu_modules(step)
+    inputs = step.example_inputs(batch, dev, seed=D_.rank)
+    with torch.no_grad():
+        for _ in range(3):
+            step(*inputs)
+        ops.check_status(dev)
+        ms = D_.timed(lambda: step(*inputs), 4) / 4
+        lin_ms = denoise.time_wrapped_linears(step, inputs)
+    lin, _ = step.ops_per_step(batch)
+    rec = {"family": family, "quant": quant, "blocks": note, "batch_per_gpu": batch, "tokens": step.shape["tokens"],
+           "text_tokens": step.shape["text"], "step_ms": ms, "wrapped_linears_ms": lin_ms,
+           "linear_path_share": lin_ms / ms if ms > 0 else None,
+           "linear_tflops_inside_step": D_.world * lin / (lin_ms * 1e-3) / 1e12 if lin_ms > 0 else None,
+           "gelu_fused_layers": n_fused, "launches_per_step": step.kernel_launches_per_step(),
+           "glue": "PyTorch bf16: adaLN modulation, LayerNorm / RMSNorm, rotary embedding, scaled_dot_product_attention "
+                   "(SANA: ReLU linear attention, Mix-FFN convolutions), residuals",
+           "timing": "CUDA events, 3 warm-up + 4 timed steps, max over ranks; wrapped_linears_ms = events around every "
+                     "wrapped-linear call of one further step"}
+    del step, inputs
+    torch.cuda.empty_cache()
+    return rec
+
+
+def _time_call(fn, n=20, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+def sub_nvfp4_flux_gemms(dev):
+    """The NVFP4 W4A4 GEMM alone on the two FLUX linear shapes at M = 16384 (batch 4 x 4096 image tokens), k = 384
+    bf16 coefficients: CUDA events around 20 back-to-back launches, operands resident, 3 warm-ups.  Fraction against
+    dense FP4 = 4 x the measured bf16 sustained figure (derived)."""
+    from dirotq_b200 import ops
+    peak, src = tensor_peak("nvfp4")
+    out = {"peak_tflops": peak, "peak_source": src, "layers": []}
+    g = torch.Generator(device=dev).manual_seed(0)
+    M, D, k = 16384, 3072, 384
+    x = torch.randn(M, D, generator=g, device=dev).to(torch.bfloat16)
+    fmt = ops.ActFormat(ops.NVFP4_HW, D, tail_len=k, group_size=16)
+    act = ops.quantize_act(x, fmt)
+    lay = act.layout
+    for N in (12288, 3072):
+        wt = (torch.randn(N, lay.tail_pitch, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        bias = torch.randn(N, generator=g, device=dev).to(torch.bfloat16)
+        pk = ops.pack_weight_nvfp4(torch.randn(N, lay.q_len, generator=g, device=dev) * 0.05, 2.0 ** -12)
+        ms = _time_call(lambda: ops.gemm_w4a4_nvfp4(act, pk, wt, bias))
+        tf = 2.0 * M * N * D / (ms * 1e-3) / 1e12
+        tf4 = 2.0 * M * N * lay.q_len / (ms * 1e-3) / 1e12
+        out["layers"].append({"shape": f"{D}->{N}", "M": M, "k_bf16": k, "us": ms * 1e3, "tflops": tf, "frac_of_fp4_peak": tf / peak,
+                              "tflops_4bit_part_only": tf4,
+                              "note": "tflops counts 2*M*N*D over the whole call; one eighth of K runs as bf16 UMMAs at a "
+                                      "quarter of the FP4 rate in the same kernel"})
+    ops.check_status(dev)
+    return out
+
+
+def sub_linear_step(D_, workload, n_blocks):
+    """Another workload's linear-path step on one GPU (resident inputs, 3 warm-up + 5 timed steps)."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    blk_name, _, quant, tokens, gbatch, family, desc = WORKLOADS[workload]
+    dev = D_.dev
+    block = getattr(dit, blk_name)()
+    M = tokens * gbatch
+    step = dit.LinearPathStep(block, n_blocks, quant, device=dev, seed=2000)
+    backend.preconvert_rotations_to_device(step, dev)
+    n_fused = backend.fuse_gelu_modules(step)
+    x = synth_activations(M, block[0].in_f, torch.Generator().manual_seed(3)).reshape(gbatch, tokens, -1).to(dev)
+    for _ in range(3):
+        step(x)
+    ops.check_status(dev)
+    ms = D_.timed(lambda: step(x), 5) / 5
+    lin, _ = step.ops_per_step(M)
+    peak, src = tensor_peak("nvfp4" if quant == "nvfp4" else "f16")
+    rec = {"workload": desc, "blocks": n_blocks, "rows": M, "ms_per_step": ms, "tflops": lin / (ms * 1e-3) / 1e12,
+           "frac_of_peak": lin / (ms * 1e-3) / 1e12 / peak, "peak_tflops": peak, "peak_source": src,
+           "gelu_fused_layers": n_fused, "launches_per_step": step.kernel_launches_per_step(),
+           "note": "whole linear-path step (rotate + quantise kernels included in the time, only the linears' 2*M*N*D credited)"}
+    del step, x
+    torch.cuda.empty_cache()
+    return rec
+
+
+def sub_flux_step(D_, n_double, ffn):
+    """FLUX linear path on a slice of the stack (n_double double-stream blocks on both streams + 2 n_double
+    single-stream blocks), fixed global batch 4.  Several GPUs: rows sharded, feed-forwards tensor-parallel; the NCCL
+    time is the sum of CUDA-event pairs around every all-gather and reduce-scatter of one step."""
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.parallel import FluxLinearStep
+    from dirotq_b200.synth import synth_activations
+    dev, world, rank = D_.dev, D_.world, D_.rank
+    step = FluxLinearStep(world, rank, dev, batch=4, n_double=n_double, n_single=2 * n_double, ffn=ffn, quant="int4")
+    backend.preconvert_rotations_to_device(step.layers, dev)
+    step.fuse_gelu()
+    for lyr in step._flat:
+        lyr._b200_explicit = None
+        lyr.rotation = lyr.rotation_per_head = None
+    torch.cuda.empty_cache()
+    M = step.rows_per_rank("single")
+    x = synth_activations(M, 3072, torch.Generator().manual_seed(7 + rank)).to(dev)
+    for _ in range(3):
+        step(x)
+    ops.check_status(dev)
+    ms = D_.timed(lambda: step(x), 4) / 4
+    rec = {"blocks": f"{n_double} double-stream (image + text) + {2 * n_double} single-stream of 19 + 38", "global_batch": 4,
+           "rows_per_gpu": M, "ffn": step.ffn, "ms_per_step": ms,
+           "tflops": step.ops_per_step()[0] / (ms * 1e-3) / 1e12}
+    if world > 1 and step.ffn == "tp":
+        step.comm_pairs = []
+        step(x)
+        torch.cuda.synchronize()
+        nccl_ms = sum(a.elapsed_time(b) for a, b in step.comm_pairs)
+        t = torch.tensor([nccl_ms], device=dev)
+        D_.dist.all_reduce(t, op=D_.dist.ReduceOp.MAX)
+        step.comm_pairs = None
+        rec.update(nccl_ms_per_step=float(t.item()), nccl_share=float(t.item()) / ms, collectives_per_step=3 * 4 * n_double,
+                   overlap="the all-gather of single-stream blocks runs on a side stream beside the attention linears "
+                           "(their inputs coincide); nccl_ms is device time of the collectives, overlapped or not")
+    del step, x
+    torch.cuda.empty_cache()
+    return rec
+
+
+# ---------------------------------------------------------------------------------------------
+# roofline
+# ---------------------------------------------------------------------------------------------
+def roofline_pass(step, x_dev, M, quant, dev, steps, exact_int=False):
     """Runs the step's layers through the two C-ABI stages separately and brackets every launch of the
     W4A4 GEMM (the kernel with the largest share of the step) with CUDA events on the launching stream."""
     from dirotq_b200 import ops
-    hbm, bf16_burst, bf16_sust, which = measured_peaks()
-    pairs = []
-    bufs = {}
-    ops_total = 0.0
+    hbm, _, bf16_sust, which = measured_peaks()
+    pairs, bufs = [], {}
+    ops_total = bytes_total = 0.0
     f16_ws, f16_used = None, False
-    bytes_total = 0.0
     k1_pairs, k1_flops, k1_bytes = [], 0.0, 0.0
     nb = len(step.block)
     for _ in range(max(1, min(steps, 2))):
@@ -391,7 +668,7 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
             e0.record()
             if quant == "nvfp4":
                 w = ops.PackedWeightNvfp4(st.out_features, st.layout.q_len, st.layout.n_chunks, st.w_tensor_scale,
-                                          st.w_codes, st.w_scales)
+                                          st.w_codes, st.w_scales, st.w_rowscale)
                 ops.gemm_w4a4_nvfp4(buf, w, st.w_tail, st.bias)
             else:
                 w = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks,
@@ -411,8 +688,13 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
     torch.cuda.synchronize()
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
-    kname = "gemm_nvfp4_kernel" if quant == "nvfp4" else (
-        "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)" if f16_used else "gemm_int_kernel")
+    if quant == "nvfp4":
+        kname, kind = "gemm_nvfp4_pair_kernel (CTA pairs; gemm_nvfp4_kernel up to 128 rows)", "nvfp4"
+    elif f16_used:
+        kname, kind = "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)", "f16"
+    else:
+        kname, kind = "gemm_int_kernel", "i8"
+    peak, peak_src = tensor_peak(kind)
     k1 = None
     if k1_pairs:
         k1_ms = sum(a.elapsed_time(b) for a, b in k1_pairs)
@@ -421,14 +703,16 @@ def roofline_pass(step, x_dev, M, quant, dev, steps):
               "frac": k1_flops / (k1_ms * 1e-3) / 1e12 / bf16_sust,
               "hbm_gbs": k1_bytes / (k1_ms * 1e-3) / 1e9, "hbm_peak_gbs": hbm, "hbm_frac": k1_bytes / (k1_ms * 1e-3) / 1e9 / hbm,
               "launches_timed": len(k1_pairs), "avg_launch_us": k1_ms * 1e3 / len(k1_pairs)}
+    n = max(1, len(pairs))
     return {"bound": "tensor", "kernel": kname, "rotate_quantise": k1,
-            "achieved": achieved, "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
-            "peak_source": f"{which}: cuBLAS bf16 sustained; the INT4 path computes in fp16 on the same tensor pipe, "
-                           "dense FP4 is nominally 4x that figure",
-            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)),
-            "traffic": NCU_TRAFFIC_RATIO * bytes_total / max(1, len(pairs)),
-            "traffic_source": f"algorithmic bytes per launch x {NCU_TRAFFIC_RATIO} (dram read + write of one ncu capture of "
-                              "the INT4 GEMM at M=16384, N=K=1152 over its algorithmic bytes; traffic grows with M and N)"}
+            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
+            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / n,
+            "algorithmic_bytes_per_launch": bytes_total / n,
+            "traffic": None,
+            "traffic_estimated": {"bytes_per_launch": NCU_TRAFFIC_RATIO * bytes_total / n,
+                                  "how": f"NOT a measurement of this run: algorithmic bytes per launch x {NCU_TRAFFIC_RATIO}, the dram "
+                                         "read + write over algorithmic bytes of one ncu capture of the INT4 GEMM at M=16384, N=K=1152 "
+                                         "(profiles/); the output of a launch is still in the 126 MB L2 when it ends"}}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the captured launch (16.3 MB: the 38 MB of output it wrote
@@ -449,7 +733,6 @@ def gemm_algorithmic_bytes(M, N, lay, quant):
 def roofline_pass_flux(step, x_dev, dev):
     """FLUX: the same bracketing over the hidden-rotation attention linears of the single-stream blocks."""
     from dirotq_b200 import ops
-    hbm, bf16_burst, bf16_sust, which = measured_peaks()
     pairs, ops_total, buf, f16_ws = [], 0.0, None, None
     M = x_dev.shape[0]
     for stream, ws, wu, wd in step.blocks:
@@ -472,31 +755,46 @@ def roofline_pass_flux(step, x_dev, dev):
     torch.cuda.synchronize()
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
-    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)", "achieved": achieved,
-            "peak": bf16_sust, "unit": "TFLOP/s", "frac": achieved / bf16_sust,
-            "peak_source": f"{which}: cuBLAS bf16 sustained (the kernel computes in fp16 on the same tensor pipe)",
-            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)),
-            "traffic": NCU_TRAFFIC_RATIO * gemm_algorithmic_bytes(M, 3072, st.layout, "int4"),
-            "traffic_source": f"algorithmic bytes per launch x {NCU_TRAFFIC_RATIO} (ratio of one ncu capture of the INT4 "
-                              "GEMM at M=16384, N=K=1152)"}
+    peak, peak_src = tensor_peak("f16")
+    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)",
+            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
+            "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None,
+            "traffic_estimated": {"bytes_per_launch": NCU_TRAFFIC_RATIO * gemm_algorithmic_bytes(M, 3072, st.layout, "int4"),
+                                  "how": f"NOT a measurement of this run: algorithmic bytes x {NCU_TRAFFIC_RATIO} (ratio of one ncu "
+                                         "capture of the INT4 GEMM at M=16384, N=K=1152)"}}
 
 
-def profile_case():
-    import contextlib
+def profile_case(which):
     from dirotq_b200 import backend, dit, ops
     from dirotq_b200.synth import synth_activations
     torch.cuda.set_device(0)
-    M = 16384
-    x = synth_activations(M, 1152, torch.Generator().manual_seed(0)).cuda()
     with contextlib.redirect_stdout(sys.stderr):
-        for quant in ("int4", "nvfp4"):
-            w = dit.make_wrapped_linear(dit.LayerDef("probe", 1152, 1152, tail=64), quant, 5, "cuda")
+        if which == "flux_nvfp4":
+            M = 4096
+            x = synth_activations(M, 3072, torch.Generator().manual_seed(0)).cuda()
+            w = dit.make_wrapped_linear(dit.LayerDef("probe", 3072, 12288, tail=384), "nvfp4", 5, "cuda")
             st = backend.prepare_layer(w, "cuda", w._b200_explicit)
             for _ in range(3):
                 backend.linear_forward(st, x)
+        elif which == "quantize":
+            M = 4096
+            x = synth_activations(M, 12288, torch.Generator().manual_seed(0)).cuda()
+            for mode in (ops.INT4_SYM, ops.NVFP4_HW):
+                fmt = ops.ActFormat(mode, 12288, tail_len=0, group_size=16 if mode == ops.NVFP4_HW else 64)
+                buf = ops.alloc_act(fmt, M, "cuda")
+                for _ in range(3):
+                    ops.quantize_act(x, fmt, out=buf)
+        else:
+            M = 16384
+            x = synth_activations(M, 1152, torch.Generator().manual_seed(0)).cuda()
+            for quant in ("int4", "nvfp4"):
+                w = dit.make_wrapped_linear(dit.LayerDef("probe", 1152, 1152, tail=64), quant, 5, "cuda")
+                st = backend.prepare_layer(w, "cuda", w._b200_explicit)
+                for _ in range(3):
+                    backend.linear_forward(st, x)
     torch.cuda.synchronize()
     ops.check_status()
-    print(json.dumps({"profile_case": "ok", "rows": M}))
+    print(json.dumps({"profile_case": which, "rows": M}))
 
 
 if __name__ == "__main__":
@@ -508,7 +806,7 @@ if __name__ == "__main__":
         from dirotq_b200 import backend as _backend
         _backend.INT4_TENSOR_RATE_GEMM = False
     if a.profile_case:
-        profile_case()
+        profile_case(a.profile_case)
     elif a.impl == "reference":
         run_reference(a)
     else:

@@ -407,12 +407,15 @@ def _fused_forward_b200(self, x):
 # Sibling layers with equal rotation and format (to_q / to_k / to_v) rotate and quantise their common
 # input once.  Set to False to give every layer its own pass.
 SHARE_SIBLING_ACTIVATIONS = True
-_SIBLING_SUFFIXES = ("to_q", "to_k", "to_v")
+# groups of leaf names whose members read one tensor through one rotation: the image-stream and (FLUX double blocks,
+# models/flux-schnell/model_utils.py:180-186) the text-stream projections of an attention
+_SIBLING_GROUPS = (("to_q", "to_k", "to_v"), ("add_q_proj", "add_k_proj", "add_v_proj"))
 
 
 def share_sibling_activations(transformer, classes=None) -> int:
-    """Group prepared sibling wrappers (same parent module, names to_q / to_k / to_v) whose rotations are
-    equal element for element and whose activation formats are identical.  Returns the number of groups."""
+    """Group prepared sibling wrappers (same parent module, names to_q / to_k / to_v or add_q_proj / add_k_proj /
+    add_v_proj) whose rotations are equal element for element and whose activation formats are identical.  Returns
+    the number of groups."""
     classes = tuple(classes or _wrapper_classes())
     buckets: Dict[str, list] = {}
     for name, mod in transformer.named_modules():
@@ -420,9 +423,10 @@ def share_sibling_activations(transformer, classes=None) -> int:
             continue
         st = getattr(mod, "_b200_state", None)
         parent, _, leaf = name.rpartition(".")
-        if st is None or st.rot_t is None or leaf not in _SIBLING_SUFFIXES:
+        gid = next((i for i, grp in enumerate(_SIBLING_GROUPS) if leaf in grp), None)
+        if st is None or st.rot_t is None or gid is None:
             continue
-        buckets.setdefault(parent, []).append(st)
+        buckets.setdefault((parent, gid), []).append(st)
     n_groups = 0
     for members in buckets.values():
         first = members[0]

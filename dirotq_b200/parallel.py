@@ -180,6 +180,13 @@ class FluxLinearStep:
         self._flat = layers
         self._gather = {}
         self.fused_gelu = False
+        # Tensor-parallel mode: CUDA-event pairs around every collective when `comm_pairs` is a list (bench.py sums
+        # them into the NCCL time per step).  In single-stream blocks proj_mlp reads the SAME tokens as to_q / to_k /
+        # to_v, so its all-gather does not depend on the attention linears and is issued on a side stream while they
+        # run; in double-stream blocks the feed-forward reads what follows the attention, so nothing can be hoisted.
+        self.comm_pairs = None
+        self.overlap_gather = True
+        self._comm_stream = None
 
     def fuse_gelu(self) -> int:
         """GELU of the FFN pairs into the up-projection's GEMM epilogue (call after the layers are prepared)."""
@@ -209,19 +216,48 @@ class FluxLinearStep:
     def rows_per_rank(self, stream: str) -> int:
         return self.rows[stream] // self.world
 
-    def _ffn(self, x, wu, wd):
-        act = (lambda t: t) if self.fused_gelu else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
-        if self.ffn == "dp":
-            return wd(act(wu(x)))
+    def _buffers(self, x):
         m = x.shape[0]
         key = (m, x.dtype)
         if key not in self._gather:
             self._gather[key] = (torch.empty(self.world * m, self.hidden, dtype=x.dtype, device=x.device),
                                  torch.empty(m, self.hidden, dtype=x.dtype, device=x.device))
-        full, out = self._gather[key]
-        dist.all_gather_into_tensor(full, x.contiguous())
+        return self._gather[key]
+
+    def _timed(self, fn):
+        if self.comm_pairs is None:
+            return fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        self.comm_pairs.append((e0, e1))
+
+    def _start_gather(self, x):
+        """all-gather of this rank's rows on the side stream; returns the event the main stream waits for."""
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(x.device)
+        full, _ = self._buffers(x)
+        main = torch.cuda.current_stream(x.device)
+        self._comm_stream.wait_stream(main)
+        with torch.cuda.stream(self._comm_stream):
+            self._timed(lambda: dist.all_gather_into_tensor(full, x.contiguous()))
+            done = torch.cuda.Event()
+            done.record(self._comm_stream)
+        return done
+
+    def _ffn(self, x, wu, wd, gathered=None):
+        act = (lambda t: t) if self.fused_gelu else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+        if self.ffn == "dp":
+            return wd(act(wu(x)))
+        m = x.shape[0]
+        full, out = self._buffers(x)
+        if gathered is not None:
+            torch.cuda.current_stream(x.device).wait_event(gathered)
+        else:
+            self._timed(lambda: dist.all_gather_into_tensor(full, x.contiguous()))
         part = wd(act(wu(full.unsqueeze(0)))).reshape(self.world * m, self.hidden)
-        dist.reduce_scatter_tensor(out, part, op=dist.ReduceOp.SUM)
+        self._timed(lambda: dist.reduce_scatter_tensor(out, part, op=dist.ReduceOp.SUM))
         return out
 
     def __call__(self, x_rows: torch.Tensor) -> torch.Tensor:
@@ -232,7 +268,9 @@ class FluxLinearStep:
         for stream, ws, wu, wd in self.blocks:
             x = views[stream]
             x3 = x.unsqueeze(0)
+            hoist = self.ffn == "tp" and self.overlap_gather and stream == "single"
+            gathered = self._start_gather(x) if hoist else None
             for w in ws:
                 y = w(x3)
-            y = self._ffn(x, wu, wd) if self.ffn == "tp" else self._ffn(x3, wu, wd)
+            y = self._ffn(x, wu, wd, gathered) if self.ffn == "tp" else self._ffn(x3, wu, wd)
         return y

@@ -60,10 +60,13 @@ class ActQuantWrapper(nn.Module):
         self.perm_idx = None
 
     def extra_repr(self):
-        s = f"Input Quant: {self.quantizer.bits}b"
-        if self.quantizer.high_bits_length > 0:
-            s += f", fp16_tail={self.quantizer.high_bits_length}d"
-        return s
+        q = self.quantizer
+        if q.bits >= 16:
+            return "activations 16-bit"
+        kind = "nvfp4" if q.quant_dtype == "nvfp4" else ("int%d %s" % (q.bits, "sym" if q.sym else "asym"))
+        rot = "rotation" if self.rotation is not None else ("per-head rotation" if self.rotation_per_head is not None else
+              ("hadamard" if self.use_hadamard else ("permutation" if self.perm_idx is not None else "no rotation")))
+        return f"activations {kind}, group {q.groupsize}, {q.high_bits_length} channels kept 16-bit, {rot}"
 
     def forward(self, x):
         if self.quantizer.bits >= 16:
