@@ -37,6 +37,7 @@ _FMT, _LAY = C.POINTER(ActFormatC), C.POINTER(ActLayoutC)
 # name -> (restype, argtypes); mirrors include/dirotq_b200.h one to one
 SIGNATURES = {
     "dirotq_abi_version": (C.c_int, []),
+    "dirotq_set_wait_limit_cycles": (C.c_int, [_I64]),
     "dirotq_error_string": (C.c_char_p, [C.c_int]),
     "dirotq_status_string": (C.c_char_p, [C.c_int]),
     "dirotq_act_layout_of": (C.c_int, [_FMT, _LAY]),

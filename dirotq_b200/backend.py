@@ -153,6 +153,9 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     if st.hadamard_low_dim:
         x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
     ws = st.workspace(M, x2d.device)
+    watch = ops.status_watch(x2d.device) if WATCH_STATUS else None
+    if watch is not None:
+        watch.poll()                    # a wait that ran out in an earlier call surfaces here (no synchronisation)
     if st.shared is not None:
         if st.shared.lookup(x2d, st.member_id):
             check(_lib.lib().dirotq_linear_gemm(C.byref(st.c_struct()), M, C.c_void_p(y.data_ptr()),
@@ -160,6 +163,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
                                                 C.c_void_p(ops.status_word(x2d.device).data_ptr()),
                                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)),
                   "dirotq_linear_gemm")
+            if watch is not None:
+                watch.post()
             return y
         st.shared.store(x2d, st.member_id)
     check(_lib.lib().dirotq_linear_forward(C.byref(st.c_struct()), C.c_void_p(x2d.data_ptr()), M,
@@ -167,6 +172,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
                                            C.c_void_p(ops.status_word(x2d.device).data_ptr()),
                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)),
           "dirotq_linear_forward")
+    if watch is not None:
+        watch.post()
     return y
 
 
@@ -210,6 +217,10 @@ def _act_format(w) -> ops.ActFormat:
     return ops.ActFormat(mode, D, tail_len=hlen, group_size=gs, clip_ratio=float(q.clip_ratio),
                          tensor_scale=_HW_NVFP4_ACT_SCALE)
 
+
+# The forward watches the device status word without synchronising (ops.StatusWatch): a bounded device-side wait that
+# ran out raises at the next forward on that device.  False leaves the check to explicit ops.check_status() calls.
+WATCH_STATUS = True
 
 # How a dense NVFP4 weight (the reference's cache holds only dequantised weights) is put back on a 4-bit grid:
 # "rowscale" = the reference's own two-level recipe, per-output-channel scale + E4M3 micro-scales

@@ -8,9 +8,20 @@
 
 using namespace dq;
 
+static std::atomic<int> g_wait_limit_k{0};
+namespace dq {
+int wait_limit_k() { return g_wait_limit_k.load(std::memory_order_relaxed); }
+}
+
 extern "C" {
 
 int dirotq_abi_version(void) { return DIROTQ_ABI_VERSION; }
+
+int dirotq_set_wait_limit_cycles(int64_t cycles) {
+  if (cycles < 0 || cycles > (int64_t)2000000000 * 1024) return DIROTQ_E_ARG;
+  g_wait_limit_k.store(cycles == 0 ? 0 : (int)((cycles + 1023) / 1024), std::memory_order_relaxed);
+  return DIROTQ_OK;
+}
 
 const char* dirotq_error_string(int code) {
   switch (code) {
@@ -127,6 +138,7 @@ int dirotq_rotate_quantize(const dirotq_act_format* fmt, const void* x, const vo
   a.zeros = static_cast<__nv_bfloat16*>(zeros);
   a.tail = static_cast<__nv_bfloat16*>(tail);
   a.status = status;
+  a.wait_limit_k = wait_limit_k();
   return launch_rotate_quantize(g, x, rot_t, M, a, static_cast<cudaStream_t>(stream));
 }
 
@@ -232,6 +244,7 @@ int dirotq_gemm_w4a4_int(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks,
   a.y = static_cast<__nv_bfloat16*>(y);
   a.acc_dump = acc_dump;
   a.status = status;
+  a.wait_limit_k = wait_limit_k();
   return launch_gemm_int(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -368,6 +381,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   a.bias = static_cast<const __nv_bfloat16*>(bias);
   a.y = static_cast<__nv_bfloat16*>(y);
   a.status = status;
+  a.wait_limit_k = wait_limit_k();
   a.force_bn = 0;
   a.act = act;
   return launch_gemm_int_f16(a, st);
@@ -413,6 +427,7 @@ static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const vo
   a.bias = static_cast<const __nv_bfloat16*>(bias);
   a.y = static_cast<__nv_bfloat16*>(y);
   a.status = status;
+  a.wait_limit_k = wait_limit_k();
   a.act = act;
   return launch_gemm_nvfp4(a, static_cast<cudaStream_t>(stream));
 }

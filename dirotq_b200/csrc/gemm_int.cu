@@ -97,7 +97,8 @@ gemm_int_kernel(const __grid_constant__ GiMaps tm, const GemmIntArgs a) {
     for (int s = 0; s < GI_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), GI_CONV_WARPS); }
     for (int s = 0; s < GI_EXP_STAGES; ++s) { mbar_init(expf_bar(s), GI_CONV_WARPS); mbar_init(expe_bar(s), 1 + GI_EPI_WARPS); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GI_EPI_WARPS); }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = a.wait_limit_k;
     fence_mbar_init();
     prefetch_tmap(&tm.xq);
     prefetch_tmap(&tm.wq);

@@ -174,7 +174,8 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     for (int s = 0; s < GF_RAW_STAGES; ++s) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), Cfg::CONV_WARPS); }
     for (int s = 0; s < GF_EXP_STAGES; ++s) { mbar_init(expf_bar(s), Cfg::GROUP_WARPS); mbar_init(expe_bar(s), 1); mbar_init(expw_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = a.wait_limit_k;
     fence_mbar_init();
     prefetch_tmap(&tm.xq);
     prefetch_tmap(&tm.wp);

@@ -63,7 +63,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < GF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), GF_EPI_WARPS); }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = a.wait_limit_k;
     fence_mbar_init();
     prefetch_tmap(&tm_xq);
     prefetch_tmap(&tm_wq);

@@ -111,7 +111,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_c
       mbar_init(tab_bar(b, 0), 4);
       mbar_init(tab_bar(b, 1), 4);
     }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = a.wait_limit_k;
     fence_mbar_init();
     prefetch_tmap(&tm_xq);
     prefetch_tmap(&tm_wq);

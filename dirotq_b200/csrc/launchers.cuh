@@ -87,6 +87,7 @@ struct PackFp4Args {
 };
 
 struct RotArgs {
+  int wait_limit_k = 0;        // bounded device waits give up after this many units of 1024 cycles (0 = default)
   ActGeom g;
   int64_t M;
   int64_t ldm;
@@ -106,6 +107,7 @@ struct RotArgs {
 };
 
 struct GemmIntArgs {
+  int wait_limit_k = 0;        // bounded device waits give up after this many units of 1024 cycles (0 = default)
   int a_mode;
   int64_t M, N;
   int n_chunks;
@@ -130,6 +132,7 @@ struct GemmIntArgs {
 };
 
 struct GemmIntF16Args {
+  int wait_limit_k = 0;        // bounded device waits give up after this many units of 1024 cycles (0 = default)
   int a_mode;                  // DIROTQ_INT4_SYM or DIROTQ_INT4_ASYM
   int64_t M, N;
   int n_chunks;
@@ -152,6 +155,7 @@ struct GemmIntF16Args {
 };
 
 struct GemmFp4Args {
+  int wait_limit_k = 0;        // bounded device waits give up after this many units of 1024 cycles (0 = default)
   int64_t M, N;
   int n_chunks;
   const uint8_t* xq;           // [M, n_chunks * 32]
@@ -192,6 +196,7 @@ int launch_pack_nvfp4(const PackFp4Args& a, cudaStream_t st);
 int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, int64_t M, RotArgs a, cudaStream_t st);
 int launch_hadamard_low(const void* x, int64_t M, int D, int n, const void* flips, void* y, cudaStream_t st);
 int num_sms();
+int wait_limit_k();   // process-wide setting of dirotq_set_wait_limit_cycles, in units of 1024 cycles
 int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64_t K, const void* bias, void* y,
                      int* status, cudaStream_t st);
 int launch_dequant_nvfp4(const uint8_t* codes, const uint8_t* sf, float T, const float* row_scale, int64_t N, int n_chunks,

@@ -93,7 +93,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try(bar, parity, 20000u)) return true;
     __nanosleep(128);            // keep pollers off the issue ports of the working warps
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    // abort_flag[1]: the launch's wait limit in units of 1024 cycles (0 = the default above)
+    const long long limit = abort_flag[1] > 0 ? ((long long)abort_flag[1] << 10) : kWaitLimitCycles;
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, code);
       return false;

@@ -474,7 +474,8 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < RQ_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), RqCfg<EPI>::EPI_WARPS); }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = a.wait_limit_k;
     fence_mbar_init();
     prefetch_tmap(&tm_x);
     prefetch_tmap(&tm_u);
@@ -697,6 +698,7 @@ int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64
   a.x_rot = static_cast<__nv_bfloat16*>(y);
   a.bias = static_cast<const __nv_bfloat16*>(bias);
   a.status = status;
+  a.wait_limit_k = wait_limit_k();
   CUtensorMap tx, tu;
   int rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 128);
   if (rc) return rc;

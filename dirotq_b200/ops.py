@@ -74,6 +74,53 @@ def status_word(device) -> torch.Tensor:
     return _status[key]
 
 
+class StatusWatch:
+    """Consumer of the status word on the product path, without a synchronisation: after a forward the word is copied
+    to pinned host memory on the forward's stream; before the next forward the copy, if it has landed, is looked at.
+    A bounded device-side wait that ran out therefore surfaces as an exception one call later at the latest
+    (or at the next check_status), instead of feeding a pipeline with undefined outputs in silence."""
+
+    def __init__(self, device):
+        self.dev = torch.device(device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+    def poll(self):
+        """Raises if the last landed copy shows a non-zero status.  Never blocks."""
+        if self.pending and self.event.query():
+            self.pending = False
+            s = int(self.host[0])
+            if s != 0:
+                status_word(self.dev).zero_()
+                self.host.zero_()
+                raise RuntimeError("dirotq_b200 kernel reported: " + _lib.lib().dirotq_status_string(s).decode())
+
+    def post(self):
+        """Queue the copy of the status word behind the kernels just launched on the current stream."""
+        if self.pending and not self.event.query():
+            return                      # an earlier copy is still in flight: it will be looked at first
+        self.host.copy_(status_word(self.dev)[:1], non_blocking=True)
+        self.event.record()
+        self.pending = True
+
+
+_watch = {}
+
+
+def status_watch(device) -> StatusWatch:
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _watch:
+        _watch[key] = StatusWatch(torch.device("cuda", key))
+    return _watch[key]
+
+
+def set_wait_limit_cycles(cycles: int):
+    """Process-wide bound of the device-side waits in SM clock cycles (0 = default, about 1.5 s)."""
+    check(_lib.lib().dirotq_set_wait_limit_cycles(int(cycles)), "dirotq_set_wait_limit_cycles")
+
+
 def check_status(device=None):
     """Synchronising read of the status word; raises if a bounded device-side wait ran out."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -311,6 +311,12 @@ int dirotq_linear_forward_static(const dirotq_linear* lin, const void* x, int64_
 
 /* ---- misc ---- */
 int dirotq_abi_version(void);
+/* Every device-side wait (on a shared-memory stage, an accumulator, scale factors) is bounded: after `cycles` SM clock
+ * cycles (0 = the default of 3e9, about 1.5 s) the waiting role writes its code into the caller's status word, raises
+ * the CTA's abort flag, the kernel awaits its copies in flight (bounded), frees its tensor memory and returns; the
+ * context stays usable and the outputs of that launch are undefined.  The setting is process-wide and applies to
+ * launches made after the call.  No counterpart in the reference (its eager kernels have no waits of their own). */
+int dirotq_set_wait_limit_cycles(int64_t cycles);
 const char* dirotq_error_string(int code);
 /* Text for a positive device status code (which wait ran out). */
 const char* dirotq_status_string(int status);

@@ -423,3 +423,39 @@ def test_packed_weight_cache_round_trip(tmp_path, monkeypatch):
     c.to_q.quantizer.high_bits_length = 128
     with pytest.raises(RuntimeError, match="does not match"):
         backend.preconvert_rotations_to_device(c, "cuda")
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """Failure detection without a fault: with the wait limit set to a few thousand cycles, the epilogue warps of a
+    GEMM give up waiting for their first accumulator (a main loop of this size takes far longer), write their code to
+    the status word, the kernel drains its copies, frees its tensor memory and RETURNS.  The status is positive and
+    has a text; the forward's own watch raises at the next call; after the limit is restored the same call gives
+    bit-identical results to a run before the incident."""
+    from dirotq_b200 import _lib, backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    torch.cuda.synchronize()
+    ops.check_status()
+    # K = 12288: a tile's main loop runs for tens of microseconds, longer than one suspended poll of a waiting warp
+    # (20 us), so the epilogue's wait for its first accumulator is certain to see the limit exceeded
+    w = dit.make_wrapped_linear(dit.LayerDef("probe", 12288, 3072, kind="norot", tail=0, source="ff"), "int4", 77, "cuda")
+    st = backend.prepare_layer(w, "cuda", w._b200_explicit)
+    x = synth_activations(2048, 12288, torch.Generator().manual_seed(2)).cuda()
+    y_good = backend.linear_forward(st, x).clone()
+    torch.cuda.synchronize()
+    ops.check_status()
+    try:
+        ops.set_wait_limit_cycles(4096)
+        backend.linear_forward(st, x)                  # launches; some wait inside runs out and the kernels return
+        torch.cuda.synchronize()                       # returns: nothing hangs
+    finally:
+        ops.set_wait_limit_cycles(0)
+    code = int(ops.status_word("cuda")[0].item())
+    assert 1 <= code <= 6 and b"timeout" in _lib.lib().dirotq_status_string(code)
+    with pytest.raises(RuntimeError, match="timeout"):
+        backend.linear_forward(st, x)                  # the product path's own watch reports it, one call later
+    torch.cuda.synchronize()
+    assert int(ops.status_word("cuda")[0].item()) == 0  # the watch cleared the word when it raised
+    y_again = backend.linear_forward(st, x)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(y_again, y_good)
