@@ -36,7 +36,9 @@ class SharedActivation:
     The first member called on a tensor rotates and quantises it into the group's workspace; members
     called next on the SAME tensor run only their GEMM.  "Same" = same storage address, shape and
     in-place version counter, with a reference held so that the storage cannot be recycled in between;
-    the reference is dropped once every member has used it."""
+    the reference is dropped once every member has used it (or by release()).  Buffers that this library
+    itself fills through raw pointers (`out=` arguments) have their version counter advanced explicitly
+    (ops.mark_written), so a reused output buffer is never mistaken for the tensor quantised before."""
 
     def __init__(self, n_members: int):
         self.n_members = n_members
@@ -66,6 +68,11 @@ class SharedActivation:
     def store(self, x: torch.Tensor, member_id: int):
         self.misses += 1
         self.x_ref, self.key, self.seen = x, self._key(x), {member_id}
+
+    def release(self):
+        """Forget the held activation tensor (it stays referenced until every member has used it, which never
+        happens when the members of a group do not all see the same input, e.g. a cross-attention)."""
+        self.x_ref, self.key, self.seen = None, None, set()
 
 
 @dataclass
@@ -163,6 +170,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
                                                 C.c_void_p(ops.status_word(x2d.device).data_ptr()),
                                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)),
                   "dirotq_linear_gemm")
+            if out is not None:
+                ops.mark_written(out)
             if watch is not None:
                 watch.post()
             return y
@@ -172,6 +181,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
                                            C.c_void_p(ops.status_word(x2d.device).data_ptr()),
                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)),
           "dirotq_linear_forward")
+    if out is not None:
+        ops.mark_written(out)
     if watch is not None:
         watch.post()
     return y
@@ -455,6 +466,20 @@ def share_sibling_activations(transformer, classes=None) -> int:
             m._ws = {}
         n_groups += 1
     return n_groups
+
+
+def release_shared_activations(transformer, classes=None) -> int:
+    """Drop the input tensors that sibling groups still hold (call between denoising steps, or when a pipeline is
+    parked, if activation memory matters); the next forward simply rotates and quantises again."""
+    classes = tuple(classes or _wrapper_classes())
+    groups = {}
+    for _, mod in transformer.named_modules():
+        st = getattr(mod, "_b200_state", None) if isinstance(mod, classes) else None
+        if st is not None and st.shared is not None:
+            groups[id(st.shared)] = st.shared
+    for grp in groups.values():
+        grp.release()
+    return len(groups)
 
 
 def fuse_gelu_modules(transformer, classes=None) -> int:

@@ -3,7 +3,7 @@
 // (DiRotQ utils/quant_utils.py:63-85, :148-180, :201-216) on a bf16 (or fp32) tensor.
 // Every step is an IEEE round-to-nearest operation followed, in bf16 mode, by a round to bf16 --
 // exactly the sequence of eager tensor ops.  The "fast" forms further down replace the per-element
-// divide by a guarded reciprocal multiply that is proven bit-identical (see div_round_bf16).
+// divide by a reciprocal multiply that is bit-identical for bf16 operands (see div_round_bf16).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -50,15 +50,16 @@ __device__ __forceinline__ int int_sym_code(float x, float scale, float maxq) {
   return (int)q;
 }
 // ---- fast exact forms used by the fused kernel's epilogue ---------------------------------------
-// bf16_rn(fl32(x / s)) without a divide per element: multiply by the correctly rounded reciprocal
-// (one per group) and fall back to the IEEE divide only when the approximate quotient lies within
-// 3 fp32 ulps of a bf16 rounding boundary (low half in [0x7FFD, 0x8003], probability ~1e-4), where
-// the <= 2 ulp error of the product could change the bf16 result.  Bit-identical to the slow form.
+// bf16_rn(fl32(x / s)) without a divide: multiply by the correctly rounded reciprocal of s (one per group).
+// Bit-identical to the divide whenever x and s are bf16 values (they always are here: x is the bf16-rounded rotated
+// tensor, s a scale already cast to bf16).  Reason: x = a 2^e and s = b 2^f with integer significands a <= 255,
+// 128 <= b <= 255, so the exact quotient a / b is either dyadic with at most 8 significant bits (then both forms
+// give it exactly) or at least 1 / (512 b) >= 2^-17 (relative) away from every bf16 rounding boundary -- two orders
+// of magnitude more than the 2^-23 the product x * fl32(1 / s) can be off.  Checked exhaustively over all
+// significand pairs and exponent differences: the product never comes closer than 129 fp32 ulps to a boundary.
 __device__ __forceinline__ float div_round_bf16(float x, float s, float rcp_s) {
-  float qa = __fmul_rn(x, rcp_s);
-  const uint32_t b = __float_as_uint(qa);
-  if (((b + 0x8003u) & 0xFFFFu) <= 6u) qa = __fdiv_rn(x, s);
-  return __bfloat162float(__float2bfloat16_rn(qa));
+  (void)s;
+  return __bfloat162float(__float2bfloat16_rn(__fmul_rn(x, rcp_s)));
 }
 // round-half-even of a bf16-valued float: the 1.5 * 2^23 trick below 2^22, identity above (bf16
 // values >= 256 are integers already)
@@ -100,59 +101,50 @@ __device__ __forceinline__ int int_asym_code(float x, float scale, float zero, f
   return (int)q;
 }
 
-// Eight consecutive values -> eight codes (nibble i = value i; bytes for the 8-bit mode).  The guard
-// of div_round_bf16 is evaluated for all eight and OR-ed; only if one of them is close to a rounding
-// boundary are the eight redone with the IEEE divide, in an out-of-line function so that the compiler
-// cannot if-convert the expensive path into the common one.
-static __device__ __noinline__ uint32_t int_sym_nib8_exact(float v0, float v1, float v2, float v3, float v4, float v5,
-                                                           float v6, float v7, float s) {
-  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
-  uint32_t w = 0;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) w |= ((uint32_t)int_sym_code<true>(v[j], s, 7.f) & 0xFu) << (4 * j);
-  return w;
-}
+// Eight consecutive values -> eight codes (nibble i = value i; bytes for the 8-bit mode), by the reciprocal multiply
+// of div_round_bf16 (no divide, no guard: see there).
 __device__ __forceinline__ uint32_t int_sym_nib8_fast(const float* v, float s, float rcp_s) {
   // Two values per packed bf16 instruction: round the quotients to bf16, clamp to [-8, 7], add 192 (bf16 spacing 1 in
   // [128, 256): the add rounds half-even to the integer, whose two's-complement nibble is the low mantissa bits).
+  (void)s;
   const __nv_bfloat162 lo2 = __floats2bfloat162_rn(-8.f, -8.f), hi2 = __floats2bfloat162_rn(7.f, 7.f),
                        magic = __floats2bfloat162_rn(192.f, 192.f);
-  uint32_t w = 0, near = 0;
+  uint32_t w = 0;
 #pragma unroll
   for (int j = 0; j < 8; j += 2) {
-    const float q0 = __fmul_rn(v[j], rcp_s), q1 = __fmul_rn(v[j + 1], rcp_s);
-    near |= (uint32_t)(((__float_as_uint(q0) + 0x8003u) & 0xFFFFu) <= 6u) |
-            (uint32_t)(((__float_as_uint(q1) + 0x8003u) & 0xFFFFu) <= 6u);
-    __nv_bfloat162 r = __floats2bfloat162_rn(q0, q1);          // .x (low half) = q0
+    __nv_bfloat162 r = __floats2bfloat162_rn(__fmul_rn(v[j], rcp_s), __fmul_rn(v[j + 1], rcp_s));   // .x (low half) = value j
     r = __hadd2(__hmin2(__hmax2(r, lo2), hi2), magic);
     const uint32_t b = *reinterpret_cast<const uint32_t*>(&r) & 0x000F000Fu;
     w |= ((b & 0xFu) | (b >> 12)) << (4 * j);
   }
-  if (near) w = int_sym_nib8_exact(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], s);
+  return w;
+}
+// The same from four words of packed bf16 pairs (as loaded): value 2 i in the low half of word i.
+__device__ __forceinline__ uint32_t int_sym_nib8_packed(const uint32_t* p, float rcp_s) {
+  const __nv_bfloat162 lo2 = __floats2bfloat162_rn(-8.f, -8.f), hi2 = __floats2bfloat162_rn(7.f, 7.f),
+                       magic = __floats2bfloat162_rn(192.f, 192.f);
+  uint32_t w = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float f0 = __uint_as_float(p[i] << 16), f1 = __uint_as_float(p[i] & 0xFFFF0000u);
+    __nv_bfloat162 r = __floats2bfloat162_rn(__fmul_rn(f0, rcp_s), __fmul_rn(f1, rcp_s));
+    r = __hadd2(__hmin2(__hmax2(r, lo2), hi2), magic);
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(&r) & 0x000F000Fu;
+    w |= ((b & 0xFu) | (b >> 12)) << (8 * i);
+  }
   return w;
 }
 // asymmetric: codes in [0, maxq]; returned as eight bytes in two words
-static __device__ __noinline__ uint2 int_asym_byte8_exact(float v0, float v1, float v2, float v3, float v4, float v5,
-                                                          float v6, float v7, float s, float zero, float maxq) {
-  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int j = 0; j < 8; ++j) w[j >> 2] |= ((uint32_t)int_asym_code<true>(v[j], s, zero, maxq) & 0xFFu) << (8 * (j & 3));
-  return make_uint2(w[0], w[1]);
-}
 __device__ __forceinline__ uint2 int_asym_byte8_fast(const float* v, float s, float rcp_s, float zero, float maxq) {
+  (void)s;
   uint32_t w[2] = {0u, 0u};
-  uint32_t near = 0;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float qa = __fmul_rn(v[j], rcp_s);
-    near |= (uint32_t)(((__float_as_uint(qa) + 0x8003u) & 0xFFFFu) <= 6u);
-    const float r = rint_bf16(__bfloat162float(__float2bfloat16_rn(qa)));
+    const float r = rint_bf16(__bfloat162float(__float2bfloat16_rn(__fmul_rn(v[j], rcp_s))));
     float q = __bfloat162float(__float2bfloat16_rn(__fadd_rn(r, zero)));
     q = fminf(fmaxf(q, 0.f), maxq);
     w[j >> 2] |= (int_bits(q) & 0xFFu) << (8 * (j & 3));
   }
-  if (near) return int_asym_byte8_exact(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], s, zero, maxq);
   return make_uint2(w[0], w[1]);
 }
 // four bytes holding 4-bit values -> four nibbles in the low 16 bits
@@ -264,6 +256,51 @@ __device__ __forceinline__ uint2 nvfp4_hw_group_fast(const float* v, float eff) 
     w[j >> 3] |= (m | ((m != 0u ? neg : 0u) << 3)) << (4 * (j & 7));
   }
   return make_uint2(w[0], w[1]);
+}
+
+// The same decision on PACKED bf16 pairs, two values per instruction and no conversion to fp32.  For a power-of-two
+// tensor scale the seven threshold products thr * eff have at most 3 + 4 significant bits, so they are exact in bf16
+// too, and  |x| > thr * eff  can be taken on the bf16 values themselves (positive floats order like their bit
+// patterns; adding the sign bit to the magnitude bits turns '>=' into '>' for negative x).  Per pair: seven packed
+// compares that yield 1.0 / 0.0, six packed adds (the count, exact), one add of 128 that leaves the count in the low
+// mantissa bits, and a handful of logic operations for the sign (no negative zero) and the nibble packing.
+// w[i] holds values 2 i (low half) and 2 i + 1; returns the sixteen nibbles in sequential order.
+__device__ __forceinline__ bool nvfp4_pow2_tensor_scale(float T) { return (__float_as_uint(T) & 0x7FFFFFu) == 0u; }
+__device__ __forceinline__ uint2 nvfp4_hw_group_packed(const uint32_t* w, float eff) {
+  __nv_bfloat162 t[7];
+  const float thr[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.f};
+#pragma unroll
+  for (int i = 0; i < 7; ++i) {
+    const float p = __fmul_rn(thr[i], eff);
+    t[i] = __floats2bfloat162_rn(p, p);
+  }
+  const __nv_bfloat162 c128 = __floats2bfloat162_rn(128.f, 128.f);
+  uint32_t out[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t neg2 = (w[i] >> 15) & 0x00010001u;
+    const uint32_t a2 = (w[i] & 0x7FFF7FFFu) + neg2;
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&a2);
+    __nv_bfloat162 m = __hadd2(__hadd2(__hadd2(__hgt2(a, t[0]), __hgt2(a, t[1])), __hadd2(__hgt2(a, t[2]), __hgt2(a, t[3]))),
+                               __hadd2(__hadd2(__hgt2(a, t[4]), __hgt2(a, t[5])), __hgt2(a, t[6])));
+    m = __hadd2(m, c128);
+    const uint32_t mi = *reinterpret_cast<const uint32_t*>(&m) & 0x00070007u;
+    const uint32_t nz2 = ((mi + 0x00070007u) >> 3) & 0x00010001u;           // 1 where the magnitude index is not zero
+    const uint32_t c2 = mi | ((neg2 & nz2) << 3);
+    out[i >> 2] |= ((c2 & 0xFu) | (c2 >> 12)) << (8 * (i & 3));
+  }
+  return make_uint2(out[0], out[1]);
+}
+// largest magnitude of sixteen packed bf16 values
+__device__ __forceinline__ float amax_bf16x16(const uint32_t* w) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t a = w[i] & 0x7FFF7FFFu;
+    const __nv_bfloat162 x = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&m));
+    m = *reinterpret_cast<const uint32_t*>(&x);
+  }
+  return fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xFFFF0000u));
 }
 
 }  // namespace dq

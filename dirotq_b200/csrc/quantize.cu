@@ -95,6 +95,21 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   const int c0 = src_col(g, grp, e0);
   const bool vec_ok = (a.perm == nullptr) && ((c0 & 7) == 0) && ((a.x_pitch & 7) == 0) &&
                       ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) && (c0 + 32 <= g.D);
+  // Whole groups of a symmetric 4-bit layer (the common case) stay on the packed bf16 pairs as loaded: largest magnitude
+  // by packed max, codes by int_sym_nib8_packed, no conversion to fp32 beyond the multiply.  The choice is the same for
+  // every thread of a group; the shuffles below run outside it, on all lanes of the warp.
+  const bool packed_path = (MODE == MODE_INT4_SYM) && vec_ok && glen == 64 * g.cpg;
+  uint32_t w[16];
+  float mx = -INFINITY, mn = INFINITY;
+  if (packed_path) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(xr + c0) + i);
+      w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+    }
+    mx = fmaxf(amax_bf16x16(w), amax_bf16x16(w + 8));
+    mn = -mx;
+  } else
   if (vec_ok) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -119,12 +134,11 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
       v[j] = f;
     }
   }
-  float mx = -INFINITY, mn = INFINITY;
+  if (!packed_path) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    if (j < nvalid) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
-  }
-  if (padded || nvalid == 0) {
+    for (int j = 0; j < 32; ++j) {
+      if (j < nvalid) { mx = fmaxf(mx, v[j]); mn = fminf(mn, v[j]); }
+    }
     // an all-padding block of a real group, or zero padding inside the group
     if (padded) { mx = fmaxf(mx, 0.f); mn = fminf(mn, 0.f); }
   }
@@ -139,8 +153,13 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   else p = int_asym_params<true>(mx, mn, g.clip, maxq);
 
   if (!live) return;
-  if (nvalid == 32) {
-    // full block: the division-free exact forms (guarded reciprocal, see quant_math.cuh)
+  if (packed_path) {
+    const float rcp = __frcp_rn(p.scale);
+    *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 16) =
+        planar32_from_nib8(int_sym_nib8_packed(w, rcp), int_sym_nib8_packed(w + 4, rcp), int_sym_nib8_packed(w + 8, rcp),
+                           int_sym_nib8_packed(w + 12, rcp));
+  } else if (nvalid == 32) {
+    // full block: the division-free exact forms (reciprocal multiply, see quant_math.cuh)
     const float rcp = __frcp_rn(p.scale);
     if constexpr (MODE == MODE_INT4_SYM) {
       uint32_t n8[4];
@@ -188,6 +207,34 @@ __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const QuantArgs a) {
   const bool short_T = nvfp4_short_tensor_scale(g.T);
   uint32_t packed[8];
   uint32_t sfw = 0;
+  if constexpr (MODE == MODE_NVFP4_HW) {
+    // whole chunk inside the quantised region, 16-byte aligned, power-of-two tensor scale: everything on packed bf16
+    // pairs as loaded, no conversion to fp32 (see nvfp4_hw_group_packed)
+    if (a.perm == nullptr && (a.x_pitch & 7) == 0 && c0 + 64 <= g.q_len && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
+        nvfp4_pow2_tensor_scale(g.T)) {
+      uint32_t w[32];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(xr + c0) + i);
+        w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+      }
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        float eff;
+        const uint8_t sb = nvfp4_hw_scale(amax_bf16x16(w + 8 * gi), g.clip, g.T, &eff);
+        uint2 c = make_uint2(0u, 0u);
+        if (eff > 0.f) c = nvfp4_hw_group_packed(w + 8 * gi, eff);
+        packed[2 * gi] = c.x;
+        packed[2 * gi + 1] = c.y;
+        sfw |= (uint32_t)sb << (8 * gi);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, chunk * 4, n_kb64_pad)) = sfw;
+      return;
+    }
+  }
   // whole chunk in range and 16-byte aligned: eight 16-byte loads instead of 64 scalar ones
   const bool vec_ok = (a.perm == nullptr) && ((a.x_pitch & 7) == 0) && (c0 + 64 <= g.D) &&
                       ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);

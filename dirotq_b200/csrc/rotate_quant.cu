@@ -184,6 +184,7 @@ __device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t tadd
   const bool row_ok = row < a.M;
   const int n_kb64_pad = (g.n_chunks + 3) & ~3;
   const bool short_T = nvfp4_short_tensor_scale(g.T);
+  const bool pow2_T = nvfp4_pow2_tensor_scale(g.T);
   for (int c0 = 0; c0 < a.BN; c0 += 64) {
     const int col = n0 + c0;
     if (col >= g.D) break;
@@ -198,19 +199,36 @@ __device__ __forceinline__ void epi_nvfp4_hidden(const RotArgs& a, uint32_t tadd
       uint32_t r[16];
       tmem_ld16(taddr + c0 + 16 * gi, r);
       tmem_wait_ld();
-      float v[16];
+      // the rotated values, rounded to bf16 and packed in pairs: what the quantiser is defined on
+      uint32_t w[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = rnd<true>(__uint_as_float(r[j]));
+      for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
       if (a.x_rot && row_ok) {
 #pragma unroll
         for (int i = 0; i < 2; ++i)
           if (gcol + 8 * i + 8 <= g.D)
-            *reinterpret_cast<uint4*>(a.x_rot + row * g.D + gcol + 8 * i) =
-                make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
-                           pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+            *reinterpret_cast<uint4*>(a.x_rot + row * g.D + gcol + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
       if (!a.codes) continue;
       const int nvalid = max(0, min(16, nq - 16 * gi));
+      if constexpr (MODE == MODE_NVFP4_HW) {
+        if (nvalid == 16 && pow2_T) {
+          // whole group, power-of-two tensor scale: decided on the packed pairs (nvfp4_hw_group_packed)
+          float eff = 0.f;
+          const uint8_t sb = nvfp4_hw_scale(amax_bf16x16(w), g.clip, g.T, &eff);
+          uint2 c = make_uint2(0u, 0u);
+          if (eff > 0.f) c = nvfp4_hw_group_packed(w, eff);
+          sfw |= (uint32_t)sb << (8 * gi);
+          if (row_ok) *reinterpret_cast<uint2*>(a.codes + row * g.code_row_bytes + (int64_t)chunk * 32 + gi * 8) = c;
+          continue;
+        }
+      }
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+      }
       if (nvalid > 0) {
         float amax = 0.f;
 #pragma unroll

@@ -54,6 +54,12 @@ def act_layout(fmt: ActFormat) -> ActLayout:
     return ActLayout(*[getattr(out, f) for f, _ in ActLayoutC._fields_])
 
 
+def mark_written(t: torch.Tensor):
+    """Advance a tensor's in-place version counter after the library wrote it through a raw pointer: torch has not
+    seen that write, and callers (backend.SharedActivation) use the counter to tell whether a tensor changed."""
+    torch.autograd.graph.increment_version(t)
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return C.c_void_p(0 if t is None else t.data_ptr())
 
@@ -199,6 +205,8 @@ def hadamard_low(x2d: torch.Tensor, low_dim: int, sign_flips: Optional[torch.Ten
     y = out if out is not None else torch.empty_like(x2d)
     check(_lib.lib().dirotq_hadamard_low(_ptr(x2d), x2d.shape[0], x2d.shape[1], low_dim, _ptr(sign_flips), _ptr(y),
                                          _stream()), "dirotq_hadamard_low")
+    if out is not None:
+        mark_written(out)
     return y
 
 
@@ -435,6 +443,8 @@ def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tens
     check(_lib.lib().dirotq_gemm_w4a16(M, w.N, K, _ptr(x2d), _ptr(w.codes), _ptr(w.scales), _ptr(bias), _ptr(y),
                                        _ptr(ws), ws.numel(), _ptr(status_word(x2d.device)), _stream()),
           "dirotq_gemm_w4a16")
+    if out is not None:
+        mark_written(out)
     return y
 
 

@@ -137,6 +137,26 @@ def test_shared_activation_bookkeeping():
     assert (g.hits, g.misses) == (3, 2)
 
 
+def test_shared_activation_survives_reused_output_buffers():
+    """A buffer the library itself fills through a raw pointer (out=) must not be mistaken for the tensor quantised
+    before: to_q and to_k run on `buf`, a library call then overwrites `buf`, to_v must miss.  And a group whose
+    members do not all see the same tensor lets go of it on release()."""
+    import torch
+    from dirotq_b200 import ops
+    from dirotq_b200.backend import SharedActivation
+    g = SharedActivation(3)
+    buf = torch.zeros(4, 8)
+    g.store(buf, 0)
+    assert g.lookup(buf, 1)
+    ops.mark_written(buf)                          # what every out= path of the library does after its launch
+    assert not g.lookup(buf, 2)
+    g.store(buf, 2)
+    assert g.lookup(buf, 0)
+    assert g.x_ref is buf                          # member 1 never came: still held ...
+    g.release()
+    assert g.x_ref is None and not g.lookup(buf, 1)  # ... until released
+
+
 def test_sibling_grouping_needs_equal_rotations_and_formats():
     import torch
     import torch.nn as nn
