@@ -134,6 +134,77 @@ __device__ __forceinline__ uint32_t int_sym_nib8_packed(const uint32_t* p, float
   }
   return w;
 }
+// Thirty-two values as sixteen words of packed pairs -> the sixteen bytes of the planar-32 layout directly: value j is
+// paired with value 16 + j BEFORE the packed rounding, so that the two nibbles of byte j come out of one register
+// (no re-ordering of nibbles afterwards).  The two quotients of a pair are one packed fp32 multiply.  `clamp` is
+// needed only when the scale was clipped (clip_ratio < 1): with scale = bf16(amax / 7) no quotient exceeds 7.03.
+__device__ __forceinline__ uint4 int_sym_planar32_packed(const uint32_t* p, float rcp_s, bool clamp) {
+  const __nv_bfloat162 lo2 = __floats2bfloat162_rn(-8.f, -8.f), hi2 = __floats2bfloat162_rn(7.f, 7.f),
+                       magic = __floats2bfloat162_rn(192.f, 192.f);
+  const uint64_t rr = ((uint64_t)__float_as_uint(rcp_s) << 32) | __float_as_uint(rcp_s);
+  uint32_t out[4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = 4 * wd + k;                          // byte j: slots j and 16 + j
+      const uint32_t a = p[j >> 1], b = p[8 + (j >> 1)];
+      const uint32_t fa = (j & 1) ? (a & 0xFFFF0000u) : (a << 16), fb = (j & 1) ? (b & 0xFFFF0000u) : (b << 16);
+      uint64_t q;
+      asm("{\n\t.reg .b64 x;\n\tmov.b64 x, {%1, %2};\n\tmul.rn.f32x2 %0, x, %3;\n\t}" : "=l"(q) : "r"(fa), "r"(fb), "l"(rr));
+      __nv_bfloat162 r = __floats2bfloat162_rn(__uint_as_float((uint32_t)q), __uint_as_float((uint32_t)(q >> 32)));
+      if (clamp) r = __hmin2(__hmax2(r, lo2), hi2);
+      r = __hadd2(r, magic);
+      const uint32_t c = *reinterpret_cast<const uint32_t*>(&r) & 0x000F000Fu;
+      acc |= ((c & 0xFu) | (c >> 12)) << (8 * k);
+    }
+    out[wd] = acc;
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+// The asymmetric 4-bit form of the same: code = clamp(rint(bf16(x / s)) + zero, 0, 15).  On packed bf16 pairs: adding
+// 192 rounds the quotient (|q| <= 15.1) half-even to an integer (bf16 spacing is 1 in [128, 256)); adding (zero - 192)
+// gives rint(q) + zero exactly (both are integers below 2^8); clamp; adding 128 leaves the code in the low mantissa bits.
+__device__ __forceinline__ uint4 int_asym_planar32_packed(const uint32_t* p, float rcp_s, float zero) {
+  const __nv_bfloat162 c192 = __floats2bfloat162_rn(192.f, 192.f), c0 = __floats2bfloat162_rn(0.f, 0.f),
+                       c15 = __floats2bfloat162_rn(15.f, 15.f), c128 = __floats2bfloat162_rn(128.f, 128.f),
+                       zm = __floats2bfloat162_rn(zero - 192.f, zero - 192.f);
+  const uint64_t rr = ((uint64_t)__float_as_uint(rcp_s) << 32) | __float_as_uint(rcp_s);
+  uint32_t out[4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = 4 * wd + k;
+      const uint32_t a = p[j >> 1], b = p[8 + (j >> 1)];
+      const uint32_t fa = (j & 1) ? (a & 0xFFFF0000u) : (a << 16), fb = (j & 1) ? (b & 0xFFFF0000u) : (b << 16);
+      uint64_t q;
+      asm("{\n\t.reg .b64 x;\n\tmov.b64 x, {%1, %2};\n\tmul.rn.f32x2 %0, x, %3;\n\t}" : "=l"(q) : "r"(fa), "r"(fb), "l"(rr));
+      __nv_bfloat162 r = __floats2bfloat162_rn(__uint_as_float((uint32_t)q), __uint_as_float((uint32_t)(q >> 32)));
+      r = __hadd2(__hadd2(r, c192), zm);
+      r = __hadd2(__hmin2(__hmax2(r, c0), c15), c128);
+      const uint32_t c = *reinterpret_cast<const uint32_t*>(&r) & 0x000F000Fu;
+      acc |= ((c & 0xFu) | (c >> 12)) << (8 * k);
+    }
+    out[wd] = acc;
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+// largest and smallest of sixteen packed bf16 values
+__device__ __forceinline__ void minmax_bf16x16(const uint32_t* w, float& mx, float& mn) {
+  __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&w[0]), lo = hi;
+#pragma unroll
+  for (int i = 1; i < 8; ++i) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    hi = __hmax2(hi, x);
+    lo = __hmin2(lo, x);
+  }
+  const uint32_t h = *reinterpret_cast<const uint32_t*>(&hi), l = *reinterpret_cast<const uint32_t*>(&lo);
+  mx = fmaxf(mx, fmaxf(__uint_as_float(h << 16), __uint_as_float(h & 0xFFFF0000u)));
+  mn = fminf(mn, fminf(__uint_as_float(l << 16), __uint_as_float(l & 0xFFFF0000u)));
+}
 // asymmetric: codes in [0, maxq]; returned as eight bytes in two words
 __device__ __forceinline__ uint2 int_asym_byte8_fast(const float* v, float s, float rcp_s, float zero, float maxq) {
   (void)s;

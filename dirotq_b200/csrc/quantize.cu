@@ -95,10 +95,10 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   const int c0 = src_col(g, grp, e0);
   const bool vec_ok = (a.perm == nullptr) && ((c0 & 7) == 0) && ((a.x_pitch & 7) == 0) &&
                       ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) && (c0 + 32 <= g.D);
-  // Whole groups of a symmetric 4-bit layer (the common case) stay on the packed bf16 pairs as loaded: largest magnitude
-  // by packed max, codes by int_sym_nib8_packed, no conversion to fp32 beyond the multiply.  The choice is the same for
+  // Whole groups of a 4-bit layer (the common case) stay on the packed bf16 pairs as loaded: extrema by packed max / min,
+  // codes by int_sym_planar32_packed / int_asym_planar32_packed, no conversion to fp32 beyond the multiply.  The choice is the same for
   // every thread of a group; the shuffles below run outside it, on all lanes of the warp.
-  const bool packed_path = (MODE == MODE_INT4_SYM) && vec_ok && glen == 64 * g.cpg;
+  const bool packed_path = (MODE == MODE_INT4_SYM || MODE == MODE_INT4_ASYM) && vec_ok && glen == 64 * g.cpg;
   uint32_t w[16];
   float mx = -INFINITY, mn = INFINITY;
   if (packed_path) {
@@ -107,8 +107,13 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
       const uint4 q = __ldg(reinterpret_cast<const uint4*>(xr + c0) + i);
       w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
     }
-    mx = fmaxf(amax_bf16x16(w), amax_bf16x16(w + 8));
-    mn = -mx;
+    if constexpr (MODE == MODE_INT4_SYM) {
+      mx = fmaxf(amax_bf16x16(w), amax_bf16x16(w + 8));
+      mn = -mx;
+    } else {
+      minmax_bf16x16(w, mx, mn);
+      minmax_bf16x16(w + 8, mx, mn);
+    }
   } else
   if (vec_ok) {
 #pragma unroll
@@ -156,8 +161,7 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   if (packed_path) {
     const float rcp = __frcp_rn(p.scale);
     *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)b * 16) =
-        planar32_from_nib8(int_sym_nib8_packed(w, rcp), int_sym_nib8_packed(w + 4, rcp), int_sym_nib8_packed(w + 8, rcp),
-                           int_sym_nib8_packed(w + 12, rcp));
+        (MODE == MODE_INT4_SYM) ? int_sym_planar32_packed(w, rcp, g.clip < 1.f) : int_asym_planar32_packed(w, rcp, p.zero);
   } else if (nvalid == 32) {
     // full block: the division-free exact forms (reciprocal multiply, see quant_math.cuh)
     const float rcp = __frcp_rn(p.scale);
