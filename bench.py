@@ -59,6 +59,9 @@ def parse():
                     help="strong (default): the workload's global batch is split over the GPUs; weak: every GPU runs "
                          "the whole batch (independent replicas)")
     ap.add_argument("--blocks", type=int, default=0, help="override the number of blocks (smoke runs only)")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="override the workload's global batch (experiments: e.g. 1 with --gpus 1 is the per-GPU share of "
+                         "the default workload on 8 GPUs)")
     ap.add_argument("--flux-ffn", default="tp", choices=["tp", "dp"],
                     help="flux_int4 at N > 1: FFN pairs tensor-parallel (all-gather + reduce-scatter) or row-sharded")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -349,6 +352,8 @@ def run_ours(args):
     blk_name, n_blocks, quant, tokens, gbatch, family, desc = WORKLOADS[args.workload]
     if args.blocks:
         n_blocks = args.blocks
+    if args.global_batch:
+        gbatch = args.global_batch
     is_flux = args.workload.startswith("flux")
     strong = is_flux or args.scaling == "strong"
     if strong and gbatch % world and not is_flux:

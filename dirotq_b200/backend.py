@@ -159,6 +159,13 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
         return y
     if st.hadamard_low_dim:
         x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
+    if CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and M <= PANEL_CACHE_MAX_ROWS:
+        pk = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks, st.w_codes,
+                                  st.w_scales, st.w_sum)
+        st.folded.panel = ops.expand_weight_panel_f16(pk, st.folded)
+        st._c = None
+        if st.shared is None:
+            st._ws = {}                 # the workspace no longer needs room for a per-call panel
     ws = st.workspace(M, x2d.device)
     watch = ops.status_watch(x2d.device) if WATCH_STATUS else None
     if watch is not None:
@@ -243,8 +250,11 @@ NVFP4_WEIGHT_RECIPE = "rowscale"
 INT4_TENSOR_RATE_GEMM = True
 # The tensor-rate GEMM reads the weight as an fp16 panel.  False: the panel is rebuilt from the 4-bit codes in
 # scratch on every call (weights stay 4-bit in memory; a pre-pass of N x K work per M x N x K GEMM).  True: built once
-# per layer and kept (2 bytes per weight of device memory, no pre-pass).
-CACHE_WEIGHT_PANEL = False
+# per layer and kept (2 bytes per weight of device memory, no pre-pass).  "auto" (default): kept only by layers that are
+# called with few rows (at most PANEL_CACHE_MAX_ROWS: a batch shard on one of several GPUs, a small batch), where the
+# pre-pass, whose cost does not shrink with the batch, is a fifth of the call; large batches keep 0.5 byte per weight.
+CACHE_WEIGHT_PANEL = "auto"
+PANEL_CACHE_MAX_ROWS = 8192
 
 
 def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerState:
@@ -285,7 +295,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
         if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM, ops.INT8_ASYM):
             pk = ops.PackedWeightInt4(N, lay.q_len, lay.group, lay.n_chunks, w_codes, w_scales, w_sum)
             folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
-            if CACHE_WEIGHT_PANEL:
+            if CACHE_WEIGHT_PANEL is True:
                 folded.panel = ops.expand_weight_panel_f16(pk, folded)
         return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias,
                           float(packed["w_tensor_scale"]), int(packed["n_lossy_groups"]), folded,
@@ -344,7 +354,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     folded = None
     if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM, ops.INT8_ASYM):
         folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
-        if CACHE_WEIGHT_PANEL:
+        if CACHE_WEIGHT_PANEL is True:
             folded.panel = ops.expand_weight_panel_f16(pk, folded)
     return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded,
                       hadamard_low_dim=had_dim, hadamard_flips=had_flips, w_rowscale=w_rowscale)

@@ -724,16 +724,21 @@ static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st)
   return launch_pdl(k, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tm, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
-// Column-tile width: the candidate that wastes the fewest padded columns; ties go to the wider tile
-// (fewer conversions of the activation tile per output column).  256 does not fit: two accumulators
-// of 256 columns would leave no tensor memory for the activation operand.
-static int pick_bn_f16(int64_t N) {
+// Column-tile width.  The persistent grid runs ceil(tiles / SMs) rounds, each as long as its widest tile, so the choice
+// minimises rounds x (tile width + a fixed per-tile cost of about 48 columns' worth of time: pipeline fill, epilogue
+// hand-over) -- padded columns and a nearly empty last round both count.  Large M: 192 (fewer conversions of the
+// activation tile per output column); a 4096-row shard of a 1152-wide layer: 128 (288 tiles fill two rounds of 148
+// SMs, where 192 tiles of width 192 leave the second round 30 % full).  256 does not fit: two accumulators of 256
+// columns would leave no tensor memory for the activation operand.
+static int pick_bn_f16(int64_t M, int64_t N) {
   const int cand[2] = {192, 128};
+  const int64_t m_tiles = (M + 127) / 128, sms = num_sms();
   int best = 128;
-  int64_t best_pad = -1;
+  int64_t best_cost = -1;
   for (int i = 0; i < 2; ++i) {
-    const int64_t pad = (N + cand[i] - 1) / cand[i] * cand[i] - N;
-    if (best_pad < 0 || pad < best_pad) { best_pad = pad; best = cand[i]; }
+    const int64_t tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
+    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 48);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
   }
   return best;
 }
@@ -744,7 +749,7 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
       (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_panel) & 15) || !a.w_panel)
     return DIROTQ_E_ALIGN;
-  int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.N);
+  int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.M, a.N);
 #ifdef GF_FORCE_BN
   BN = GF_FORCE_BN;
 #endif

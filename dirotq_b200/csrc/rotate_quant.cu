@@ -636,20 +636,25 @@ static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs
   return launch_pdl(k, dim3(grid), dim3(RqCfg<EPI>::THREADS), RqCfg<EPI>::SMEM_BYTES, st, tx, tu, ty, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
-// Picks the N tile: hidden layouts want a multiple of 64 with the least padding of D; per-head
-// layouts a whole number of heads (and a multiple of 16 for the UMMA shape).
-int pick_bn(const ActGeom& g) {
+// Picks the N tile.  Per-head layouts: a whole number of heads (and a multiple of 16 for the UMMA shape).  Hidden
+// layouts: a multiple of 64; the persistent grid runs ceil(tiles / SMs) rounds, each as long as its tile is wide, so
+// the choice minimises rounds x (width + a fixed per-tile cost of about 48 columns' worth of time) -- padding of D and
+// a nearly empty last round both count (a 4096-row shard of a 1152-wide layer takes 128, a 32768-row batch 192).
+int pick_bn(const ActGeom& g, int64_t M) {
   if (g.H > 0) {
     int best = 0;
     for (int k = 1; k * g.d <= 256; ++k)
       if ((k * g.d) % 16 == 0) best = k * g.d;
     return best;
   }
-  int best = 256, waste = 1 << 30;
   const int cand[3] = {256, 192, 128};
+  const int64_t m_tiles = (M + 127) / 128, sms = num_sms();
+  int best = 256;
+  int64_t best_cost = -1;
   for (int i = 0; i < 3; ++i) {
-    int w = ceil_div(g.D, cand[i]) * cand[i] - g.D;
-    if (w < waste) { waste = w; best = cand[i]; }
+    const int64_t tiles = m_tiles * ceil_div(g.D, cand[i]);
+    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 48);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
   }
   return best;
 }
@@ -661,7 +666,7 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
   a.K = g.D;
   a.bias = nullptr;
   a.ldm = ld_rows(M);
-  a.BN = pick_bn(g);
+  a.BN = pick_bn(g, M);
   if (a.BN <= 0) return DIROTQ_E_UNSUPPORTED;
   a.n_tiles = ceil_div(g.D, a.BN);
   a.m_tiles = (int)((M + 127) / 128);
@@ -709,7 +714,7 @@ int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64
   a.M = M;
   a.K = (int)K;
   a.ldm = ld_rows(M);
-  a.BN = pick_bn(a.g);
+  a.BN = pick_bn(a.g, M);
   a.n_tiles = ceil_div((int)N, a.BN);
   a.m_tiles = (int)((M + 127) / 128);
   a.band = 0;
