@@ -89,4 +89,25 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, u
       : "memory");
 }
 
+// The four K = 16 pair UMMAs of one 64-wide bf16 operand stage, both operands through shared-memory descriptors given as
+// low words (address >> 4, advancing by 2 = 32 bytes per step) and one common high word; `accum0` = 0 clears the
+// accumulator first.
+__device__ __forceinline__ void umma_f16_ss_x4_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                                    uint32_t accum0) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 x, y;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
+      "add.u32 x, %1, 2;\n\tadd.u32 y, %2, 2;\n\tmov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, t;\n\t"
+      "add.u32 x, %1, 4;\n\tadd.u32 y, %2, 4;\n\tmov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, t;\n\t"
+      "add.u32 x, %1, 6;\n\tadd.u32 y, %2, 6;\n\tmov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accum0)
+      : "memory");
+}
+
 }  // namespace dq

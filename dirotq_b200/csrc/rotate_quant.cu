@@ -13,33 +13,41 @@
 // Replaces: `x_flat @ self.rotation` + find_params + quantizer (DiRotQ
 // dirotq_fused_unrotation_fast.py:69-74), the per-head branch (:76-104) and the stand-alone
 // rotation kernels speedup/kernels/{int8,fp8,bf16}_rotation.py.
+#include <cstdlib>
+#include <cstring>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include "layout.cuh"
 #include "launchers.cuh"
 #include "ptx.cuh"
+#include "ptx_pair.cuh"
 #include "tma_host.cuh"
 #include "quant_math.cuh"
 
 namespace dq {
 
-constexpr int RQ_STAGES = 4;
 constexpr int RQ_A_BYTES = 128 * 128;           // 128 rows x 64 bf16
-constexpr int RQ_B_BYTES = 256 * 128;           // up to 256 rows x 64 bf16
-constexpr int RQ_STAGE_BYTES = RQ_A_BYTES + RQ_B_BYTES;
+// One CTA per tile: the whole rotation tile (up to 256 rows x 64 bf16) per stage, four stages.  CTA pairs
+// (tcgen05 cta_group::2, 256 token rows per pair): each CTA fetches only HALF of the rotation tile -- the tensor core
+// reads the other half from the peer's shared memory -- so a stage is 32 KB instead of 48 and six fit.
+template <bool PAIR> struct RqStage {
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int B_BYTES = (PAIR ? 128 : 256) * 128;
+  static constexpr int STAGE_BYTES = RQ_A_BYTES + B_BYTES;
+};
 // Epilogue warps per TMEM lane quarter: they take the 64-column chunks of their rows in turns.  The NVFP4
 // epilogue is the longest (seven threshold compares per value) and latency-bound, so it gets more warps.
 #ifndef RQ_WPQ_NVFP4
 #define RQ_WPQ_NVFP4 4
 #endif
-template <int EPI> struct RqCfg {
+template <int EPI, bool PAIR = false> struct RqCfg {
   static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : 2;
   static constexpr int EPI_WARPS = 4 * WPQ;
   static constexpr int THREADS = (2 + EPI_WARPS) * 32;
   // plain-GEMM epilogue (EPI_ROT_ONLY = 0): a 32 x 32 bf16 staging patch per epilogue warp for its TMA stores
   static constexpr int STG_BYTES = (EPI == 0) ? EPI_WARPS * 2048 : 0;
-  static constexpr int SMEM_BYTES = RQ_STAGES * RQ_STAGE_BYTES + STG_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = RqStage<PAIR>::STAGES * RqStage<PAIR>::STAGE_BYTES + STG_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3 };
@@ -463,17 +471,22 @@ __device__ __forceinline__ void epi_rot_only(const RotArgs& a, const CUtensorMap
     }
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) {
+    if (lane == 0 && row0 < a.M) {
       tma_store_2d(tm_y, stg, col, row0);
       bulk_commit_group();
     }
   }
 }
 
-template <int EPI, int MODE>
+// PAIR: clusters of two CTAs share one 256-row tile through tcgen05.mma.cta_group::2 (each CTA its own 128 token
+// rows and half of the rotation tile); completions of both CTAs' loads are counted on the leader's full barrier, the
+// leader commits to both CTAs' empty / accumulator-full barriers, epilogue warps of both arrive on the leader's
+// accumulator-empty barrier (the peer's arrivals carry no memory ordering: their payload is tensor memory).
+template <int EPI, int MODE, bool PAIR>
 __global__ void __launch_bounds__(RqCfg<EPI>::THREADS, 1)
 rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_u,
                     const __grid_constant__ CUtensorMap tm_y, const RotArgs a) {
+  constexpr int RQ_STAGES = RqStage<PAIR>::STAGES, RQ_STAGE_BYTES = RqStage<PAIR>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stg_area = smem + RQ_STAGES * RQ_STAGE_BYTES;                  // 1024-byte aligned
@@ -483,6 +496,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;      // 0 = leader (issues the UMMAs)
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (RQ_STAGES + s); };
@@ -491,21 +505,28 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RQ_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), RqCfg<EPI>::EPI_WARPS); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), (PAIR ? 2 : 1) * RqCfg<EPI>::EPI_WARPS); }
     abort_flag[0] = 0;
     abort_flag[1] = a.wait_limit_k;
     fence_mbar_init();
     prefetch_tmap(&tm_x);
     prefetch_tmap(&tm_u);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    else tmem_alloc(smem_u32(tmem_slot), 512);
+  }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anything arrives on them remotely
   tc_fence_after();
   pdl_launch_dependents();
   pdl_wait();                       // whatever produced x (and last used the output buffers) has completed
   const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = a.m_tiles * a.n_tiles;
+  // tiles: (128-row block, column block), or (256-row pair block, column block) walked by clusters
+  const int total_tiles = (PAIR ? (a.m_tiles + 1) / 2 : a.m_tiles) * a.n_tiles;
+  const int first = PAIR ? (int)cluster_id_x() : (int)blockIdx.x, step = PAIR ? (int)cluster_count_x() : (int)gridDim.x;
+  const int bn_own = PAIR ? a.BN / 2 : a.BN;                 // rotation-tile rows this CTA fetches
   const uint32_t smem_base = smem_u32(smem);
 
   if (warp == 0) {
@@ -514,21 +535,34 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       uint32_t ph = 0;
       uint32_t issued = 0;   // bit s set: a load into stage s has been issued at least once
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
+      for (int t = first; t < total_tiles && ok; t += step) {
+        const int mt = t / a.n_tiles, nb = t - mt * a.n_tiles;
+        const int mb = PAIR ? 2 * mt + (int)rank : mt;
         int kb, ke;
         tile_k_range(a, nb, kb, ke);
         for (int kc = kb; kc < ke; ++kc) {
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sa = smem_base + s * RQ_STAGE_BYTES;
-          mbar_expect_tx(full_bar(s), RQ_A_BYTES + a.BN * 128);
-          tma_load_2d(sa, &tm_x, full_bar(s), kc * 64, mb * 128);
-          tma_load_2d(sa + RQ_A_BYTES, &tm_u, full_bar(s), kc * 64, nb * a.BN);
+          if constexpr (PAIR) {
+            const uint32_t fb = map_to_rank(full_bar(s), 0);
+            if (rank == 0) mbar_expect_tx(full_bar(s), 2u * (RQ_A_BYTES + bn_own * 128));
+            tma_load_2d_pair(sa, &tm_x, fb, kc * 64, mb * 128);
+            tma_load_2d_pair(sa + RQ_A_BYTES, &tm_u, fb, kc * 64, nb * a.BN + (int)rank * bn_own);
+          } else {
+            mbar_expect_tx(full_bar(s), RQ_A_BYTES + a.BN * 128);
+            tma_load_2d(sa, &tm_x, full_bar(s), kc * 64, mb * 128);
+            tma_load_2d(sa + RQ_A_BYTES, &tm_u, full_bar(s), kc * 64, nb * a.BN);
+          }
           issued |= 1u << s;
           if (++s == RQ_STAGES) { s = 0; ph ^= 1; }
         }
       }
-      if (!ok) {
+      if (PAIR && !ok) {
+        // the completions of this CTA's copies are counted in the leader, where the peer cannot test them: give
+        // copies in flight a bounded time to land before the CTA may retire
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+      } else if (!ok) {
         // unwind: let copies already in flight land before the CTA exits (bounded)
         const long long t0 = clock64();
         for (int i = 0; i < RQ_STAGES; ++i) {
@@ -541,15 +575,15 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, 128, (uint32_t)a.BN);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = idesc_dense(ACC_F32, FMT_BF16, FMT_BF16, PAIR ? 256 : 128, (uint32_t)a.BN);
       int s = 0, buf = 0;
       uint32_t ph = 0, aph = 0;
       bool ok = true;
       const uint64_t op_d0 = smem_desc_sw128(smem_base);
       const uint32_t op_lo0 = (uint32_t)op_d0, op_hi = (uint32_t)(op_d0 >> 32);
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
+      for (int t = first; t < total_tiles && ok; t += step) {
+        const int nb = t % a.n_tiles;
         int kb, ke;
         tile_k_range(a, nb, kb, ke);
         if (!mbar_wait(acce_bar(buf), aph ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) break;
@@ -561,12 +595,23 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           // descriptors from loop-invariant words; the stage's four UMMAs in one block (what this thread does between
           // UMMAs is time the tensor pipe idles)
           const uint32_t a_lo = op_lo0 + (uint32_t)s * (RQ_STAGE_BYTES >> 4);
-          umma_f16_ss_x4(d_tmem, a_lo, a_lo + (RQ_A_BYTES >> 4), op_hi, idesc, kc > kb ? 1u : 0u);
-          umma_commit(empty_bar(s));
+          if constexpr (PAIR) {
+            umma_f16_ss_x4_pair(d_tmem, a_lo, a_lo + (RQ_A_BYTES >> 4), op_hi, idesc, kc > kb ? 1u : 0u);
+            umma_commit_pair(empty_bar(s));
+            umma_commit_pair(map_to_rank(empty_bar(s), 1));
+          } else {
+            umma_f16_ss_x4(d_tmem, a_lo, a_lo + (RQ_A_BYTES >> 4), op_hi, idesc, kc > kb ? 1u : 0u);
+            umma_commit(empty_bar(s));
+          }
           if (++s == RQ_STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(accf_bar(buf));
+        if constexpr (PAIR) {
+          umma_commit_pair(accf_bar(buf));
+          umma_commit_pair(map_to_rank(accf_bar(buf), 1));
+        } else {
+          umma_commit(accf_bar(buf));
+        }
         buf ^= 1;
         if (buf == 0) aph ^= 1;
       }
@@ -575,8 +620,10 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const int q = warp & 3, half = (warp - 2) >> 2;
     int buf = 0;
     uint32_t aph = 0, turn = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      const int mb = t / a.n_tiles, nb = t - mb * a.n_tiles;
+    const uint32_t acce_leader = PAIR ? map_to_rank(acce_bar(0), 0) : 0u;
+    for (int t = first; t < total_tiles; t += step) {
+      const int mt = t / a.n_tiles, nb = t - mt * a.n_tiles;
+      const int mb = PAIR ? 2 * mt + (int)rank : mt;
       if (!mbar_wait(accf_bar(buf), aph, abort_flag, a.status, ERR_WAIT_ACC_FULL)) break;
       __syncwarp();
       tc_fence_after();
@@ -590,7 +637,10 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acce_bar(buf));
+      if (lane == 0) {
+        if (PAIR && rank != 0) mbar_arrive_cluster_relaxed(acce_leader + 8u * buf);
+        else mbar_arrive(acce_bar(buf));
+      }
       buf ^= 1;
       if (buf == 0) aph ^= 1;
     }
@@ -599,10 +649,12 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA retires while the other may still read its shared memory
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -620,8 +672,50 @@ int num_sms() {
   return n;
 }
 
+template <int EPI, int MODE, bool PAIR>
+static int launch_rq_impl(const CUtensorMap& tx, const CUtensorMap& tu, const CUtensorMap& ty, const RotArgs& a, cudaStream_t st) {
+  using Cfg = RqCfg<EPI, PAIR>;
+  auto k = rotate_quant_kernel<EPI, MODE, PAIR>;
+  static PerDeviceOnce attr_once;
+  if (int rc = set_max_dynamic_smem(attr_once, k, Cfg::SMEM_BYTES)) return rc;
+  if constexpr (!PAIR) {
+    const int grid = min(a.m_tiles * a.n_tiles, num_sms());
+    return launch_pdl(k, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tx, tu, ty, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // persistent grid: as many pairs as can be resident at once, remembered per device
+    static std::atomic<int> resident[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DIROTQ_E_CUDA;
+    int max_pairs = resident[dev].load(std::memory_order_relaxed);
+    if (max_pairs <= 0) {
+      cfg.gridDim = dim3(2 * (num_sms() / 2));
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&max_pairs, k, &cfg) != cudaSuccess || max_pairs <= 0) max_pairs = num_sms() / 2;
+      resident[dev].store(max_pairs, std::memory_order_relaxed);
+    }
+    const int tiles = ((a.m_tiles + 1) / 2) * a.n_tiles;
+    cfg.gridDim = dim3(2 * min(tiles, max_pairs));
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, k, tx, tu, ty, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  }
+}
+
+// tu_pair: the rotation's tensor map with a box of BN / 2 rows (what one CTA of a pair fetches); used when the call
+// has more than one 128-row block (DIROTQ_ROTATE_TILE = single | pair forces one form: measurements, tests).
 template <int EPI, int MODE>
-static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs& a, cudaStream_t st) {
+static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const CUtensorMap& tu_pair, const RotArgs& a, cudaStream_t st) {
   CUtensorMap ty = tx;                                 // only the plain-GEMM epilogue stores through a tensor map
   if constexpr (EPI == EPI_ROT_ONLY) {
     if ((a.g.D & 7) || (reinterpret_cast<uintptr_t>(a.x_rot) & 15)) return DIROTQ_E_ALIGN;
@@ -629,11 +723,13 @@ static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const RotArgs
                              (uint64_t)a.g.D * 2, 32, 32, 64);
     if (rc) return rc;
   }
-  auto k = rotate_quant_kernel<EPI, MODE>;
-  static PerDeviceOnce attr_once;
-  if (int rc = set_max_dynamic_smem(attr_once, k, RqCfg<EPI>::SMEM_BYTES)) return rc;
-  const int grid = min(a.m_tiles * a.n_tiles, num_sms());
-  return launch_pdl(k, dim3(grid), dim3(RqCfg<EPI>::THREADS), RqCfg<EPI>::SMEM_BYTES, st, tx, tu, ty, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
+  bool pair = a.m_tiles >= 2 && (a.BN / 2) % 8 == 0;
+  if (const char* e = getenv("DIROTQ_ROTATE_TILE")) {
+    if (!strcmp(e, "single")) pair = false;
+    else if (!strcmp(e, "pair")) pair = (a.BN / 2) % 8 == 0;
+  }
+  if (pair) return launch_rq_impl<EPI, MODE, true>(tx, tu_pair, ty, a, st);
+  return launch_rq_impl<EPI, MODE, false>(tx, tu, ty, a, st);
 }
 
 // Picks the N tile.  Per-head layouts: a whole number of heads (and a multiple of 16 for the UMMA shape).  Hidden
@@ -684,21 +780,27 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
   rc = make_tmap_2d(&tu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rot_t, (uint64_t)g.D, (uint64_t)g.D, (uint64_t)g.D * 2,
                     (uint32_t)a.BN);
   if (rc) return rc;
-  if (rot_only) return launch_rq<EPI_ROT_ONLY, 0>(tx, tu, a, st);
+  CUtensorMap tu2 = tu;
+  if ((a.BN / 2) % 8 == 0) {
+    rc = make_tmap_2d(&tu2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rot_t, (uint64_t)g.D, (uint64_t)g.D, (uint64_t)g.D * 2,
+                      (uint32_t)(a.BN / 2));
+    if (rc) return rc;
+  }
+  if (rot_only) return launch_rq<EPI_ROT_ONLY, 0>(tx, tu, tu2, a, st);
   if (g.H > 0) {
     switch (g.mode) {
-      case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_SYM>(tx, tu, a, st);
-      case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_ASYM>(tx, tu, a, st);
-      case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT8_ASYM>(tx, tu, a, st);
+      case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_SYM>(tx, tu, tu2, a, st);
+      case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_ASYM>(tx, tu, tu2, a, st);
+      case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT8_ASYM>(tx, tu, tu2, a, st);
       default: return DIROTQ_E_UNSUPPORTED;
     }
   }
   switch (g.mode) {
-    case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT4_SYM>(tx, tu, a, st);
-    case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT4_ASYM>(tx, tu, a, st);
-    case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT8_ASYM>(tx, tu, a, st);
-    case DIROTQ_NVFP4_REF: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_REF>(tx, tu, a, st);
-    case DIROTQ_NVFP4_HW: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_HW>(tx, tu, a, st);
+    case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT4_SYM>(tx, tu, tu2, a, st);
+    case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT4_ASYM>(tx, tu, tu2, a, st);
+    case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_HIDDEN, MODE_INT8_ASYM>(tx, tu, tu2, a, st);
+    case DIROTQ_NVFP4_REF: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_REF>(tx, tu, tu2, a, st);
+    case DIROTQ_NVFP4_HW: return launch_rq<EPI_NVFP4_HIDDEN, MODE_NVFP4_HW>(tx, tu, tu2, a, st);
   }
   return DIROTQ_E_UNSUPPORTED;
 }
@@ -727,7 +829,10 @@ int launch_gemm_bf16(const void* x, const void* w_t, int64_t M, int64_t N, int64
   if (rc) return rc;
   rc = make_tmap_2d(&tu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_t, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, (uint32_t)a.BN);
   if (rc) return rc;
-  return launch_rq<EPI_ROT_ONLY, 0>(tx, tu, a, st);
+  CUtensorMap tu2;
+  rc = make_tmap_2d(&tu2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_t, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, (uint32_t)(a.BN / 2));
+  if (rc) return rc;
+  return launch_rq<EPI_ROT_ONLY, 0>(tx, tu, tu2, a, st);
 }
 
 }  // namespace dq

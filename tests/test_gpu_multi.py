@@ -45,11 +45,13 @@ def test_one_process_drives_two_devices():
             W_rot = (torch.randn(N, D, generator=g) * 0.05) @ U
             deq = O.weight_quant_int(W_rot[:, : D - k], 4, gs)[0] if quant == "int" else O.weight_quant_nvfp4(W_rot[:, : D - k])[0]
             W = torch.cat([deq, W_rot[:, D - k:]], dim=1).to(torch.bfloat16)
+            bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
             outs = []
             for dev in ("cuda:0", "cuda:1"):
                 with torch.cuda.device(dev):
                     lin = nn.Linear(D, N).to(torch.bfloat16)
                     lin.weight.data.copy_(W)
+                    lin.bias.data.copy_(bias)
                     w = ActQuantWrapper(lin)
                     w.quantizer.configure(bits=4, groupsize=gs, sym=True, high_bits_length=k, quant_dtype=quant)
                     w.rotation, w._unrot_fused = U, True
@@ -58,7 +60,7 @@ def test_one_process_drives_two_devices():
                     outs.append(y.float().cpu())
             assert torch.equal(outs[0], outs[1]), quant
             if quant == "int":
-                spec = O.LayerSpec(W, lin.bias.data.cpu(), O.QuantCfg(4, gs, True, 1.0, k, quant), rotation=U)
+                spec = O.LayerSpec(W, bias, O.QuantCfg(4, gs, True, 1.0, k, quant), rotation=U)
                 y_ref = O.fused_forward(x, spec, fp32=False).float()
                 assert float((outs[1] - y_ref).norm() / y_ref.norm()) < 0.05
     finally:
