@@ -68,11 +68,14 @@ SIGNATURES = {
     "dirotq_linear_workspace_bytes": (_SZ, [C.POINTER(LinearC), _I64]),
     "dirotq_linear_forward": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_gemm": (C.c_int, [C.POINTER(LinearC), _I64, _P, _P, _SZ, _P, _P]),
+    "dirotq_linear_chain_supported": (C.c_int, [C.POINTER(LinearC), C.POINTER(LinearC)]),
+    "dirotq_linear_forward_chain": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _SZ, C.POINTER(LinearC), _P, _SZ, _P, _P]),
+    "dirotq_linear_gemm_prequantised": (C.c_int, [C.POINTER(LinearC), _I64, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_forward_static_capacity": (_SZ, []),
     "dirotq_linear_forward_static": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _P]),
 }
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 _lib = None
 
 

@@ -97,6 +97,12 @@ class LayerState:
     hadamard_low_dim: int = 0                        # use_hadamard layers: FWHT over the first channels
     hadamard_flips: Optional[torch.Tensor] = None
     w_rowscale: Optional[torch.Tensor] = None        # NVFP4: fp32 per-channel weight scale (reference recipe)
+    chain_next: Optional["LayerState"] = None        # this layer's GEMM epilogue quantises its output for that layer
+    chain_keep_output: bool = True                   # False: the bf16 output itself is never written (nobody else reads it)
+    handed: Optional[torch.Tensor] = None            # consumer side: the producer's output whose codes the workspace holds
+    handed_key: Optional[tuple] = None
+    chain_hits: int = 0
+    chain_fed: bool = False                          # a producer's epilogue quantises for this layer
     _c: Optional[LinearC] = None
     _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
 
@@ -137,12 +143,14 @@ def kernel_launches(st: Optional[LayerState]) -> int:
     if st is None:
         return 2
     n = 1 if (st.shared is not None and st.member_id > 0) else 2
+    if st.chain_fed:
+        n -= 1                              # its activations arrive quantised from the producer's epilogue
     if st.folded is not None:
         # scale folding (first user of the activations only) and the weight-panel pre-pass (unless resident): one launch
         # when both are due, else one each
         fold = not (st.shared is not None and st.member_id > 0)
         n += 1 if (fold or st.folded.panel is None) else 0
-    follower = st.shared is not None and st.member_id > 0
+    follower = (st.shared is not None and st.member_id > 0) or st.chain_fed
     if st.rot_t is None and st.layout.tail_total > 0 and not follower:
         n += 1                              # quantise-only layers copy their passthrough channels in a kernel of its own
     if st.hadamard_low_dim:
@@ -164,12 +172,42 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
                                   st.w_scales, st.w_sum)
         st.folded.panel = ops.expand_weight_panel_f16(pk, st.folded)
         st._c = None
-        if st.shared is None:
+        if st.shared is None and st.handed is None:
             st._ws = {}                 # the workspace no longer needs room for a per-call panel
     ws = st.workspace(M, x2d.device)
     watch = ops.status_watch(x2d.device) if WATCH_STATUS else None
     if watch is not None:
         watch.poll()                    # a wait that ran out in an earlier call surfaces here (no synchronisation)
+    status = C.c_void_p(ops.status_word(x2d.device).data_ptr())
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if st.handed is not None:
+        hit = st.handed_key == SharedActivation._key(x2d)
+        st.handed, st.handed_key = None, None
+        if hit:
+            # the producer's epilogue left this tensor's codes, scales and 16-bit channels in the workspace
+            st.chain_hits += 1
+            check(_lib.lib().dirotq_linear_gemm_prequantised(C.byref(st.c_struct()), M, C.c_void_p(y.data_ptr()),
+                                                             C.c_void_p(ws.data_ptr()), ws.numel(), status, stream),
+                  "dirotq_linear_gemm_prequantised")
+            if out is not None:
+                ops.mark_written(out)
+            if watch is not None:
+                watch.post()
+            return y
+    nxt = st.chain_next
+    if nxt is not None and st.shared is None and not nxt.hadamard_low_dim:
+        nws = nxt.workspace(M, x2d.device)
+        yp = C.c_void_p(y.data_ptr() if st.chain_keep_output else 0)
+        check(_lib.lib().dirotq_linear_forward_chain(C.byref(st.c_struct()), C.c_void_p(x2d.data_ptr()), M, yp,
+                                                     C.c_void_p(ws.data_ptr()), ws.numel(), C.byref(nxt.c_struct()),
+                                                     C.c_void_p(nws.data_ptr()), nws.numel(), status, stream),
+              "dirotq_linear_forward_chain")
+        if out is not None:
+            ops.mark_written(out)
+        nxt.handed, nxt.handed_key = y, SharedActivation._key(y)
+        if watch is not None:
+            watch.post()
+        return y
     if st.shared is not None:
         if st.shared.lookup(x2d, st.member_id):
             check(_lib.lib().dirotq_linear_gemm(C.byref(st.c_struct()), M, C.c_void_p(y.data_ptr()),
@@ -514,6 +552,64 @@ def fuse_gelu_modules(transformer, classes=None) -> int:
         st.epilogue_act, st._c = 1, None
         object.__setattr__(mod, "_b200_gelu_fused", True)
         mod.forward = (lambda p: (lambda hidden_states, *a, **k: p(hidden_states)))(proj)
+        n += 1
+    return n
+
+
+def chain_supported(up: LayerState, down: LayerState) -> bool:
+    """Whether `up`'s GEMM epilogue can quantise for `down` (dirotq_linear_chain_supported of the C ABI)."""
+    if up.shared is not None or down.shared is not None or down.hadamard_low_dim:
+        return False
+    return bool(_lib.lib().dirotq_linear_chain_supported(C.byref(up.c_struct()), C.byref(down.c_struct())))
+
+
+def fuse_ffn_quantise(transformer=None, pairs=None, keep_hidden: bool = True, classes=None) -> int:
+    """Let the up-projection of a feed-forward pair quantise its own output for the down-projection.
+
+    The reference runs two ActQuantWrapper forwards with the activation between them
+    (models/pixart-sigma/model_utils.py:120-127): GELU(up(x)) goes to memory as [M, inner] bf16 and the second
+    wrapper reads it back to quantise it.  After this call the up-projection's GEMM epilogue (which already applies
+    the GELU, fuse_gelu_modules) emits the down-projection's 4-bit codes, group scales, zero points and 16-bit
+    channels directly -- bit for bit what the down-projection's own quantiser would have produced -- and the
+    down-projection, recognising the tensor it is called on (storage, shape, version counter; the producer's output
+    is kept referenced until then), runs only its GEMM.
+
+    Pairs come from `transformer` (modules with a `net` container: first entry a GELU head fused by
+    fuse_gelu_modules, last entry a prepared wrapped linear, only Dropout / Identity between them; and blocks with a
+    fused head `proj_mlp_act` beside a split `proj_out.linears`) and / or from `pairs` (explicit
+    (up_wrapper, down_wrapper) tuples).  Only pairs the
+    library supports are fused (chain_supported); the others keep their two-step forward.
+
+    keep_hidden=False additionally stops writing the [M, inner] tensor: the tensor the up-projection returns is
+    then an UNWRITTEN buffer that only the down-projection may consume.  Use it only where nothing else reads the
+    hidden activation (not for the reference's FLUX single block, whose split proj_out slices a concatenation).
+    Returns the number of fused pairs."""
+    classes = tuple(classes or _wrapper_classes())
+    cand = list(pairs or [])
+    if transformer is not None:
+        for _, mod in transformer.named_modules():
+            # a FLUX single block after the proj_out split (models/flux-schnell/split_proj_out.py:38-48) whose MLP
+            # branch is handed over directly: GELU head `proj_mlp_act`, down-projection `proj_out.linears[1]`
+            head, split = getattr(mod, "proj_mlp_act", None), getattr(getattr(mod, "proj_out", None), "linears", None)
+            if head is not None and split is not None and getattr(head, "_b200_gelu_fused", False):
+                split = list(split.children())
+                if len(split) == 2 and isinstance(split[1], classes) and isinstance(getattr(head, "proj", None), classes):
+                    cand.append((head.proj, split[1]))
+            net = getattr(mod, "net", None)
+            net = list(net.children()) if isinstance(net, torch.nn.Module) else None
+            if not net or len(net) < 2 or not getattr(net[0], "_b200_gelu_fused", False):
+                continue
+            if not all(isinstance(m, (torch.nn.Dropout, torch.nn.Identity)) for m in net[1:-1]):
+                continue
+            if isinstance(net[-1], classes) and isinstance(getattr(net[0], "proj", None), classes):
+                cand.append((net[0].proj, net[-1]))
+    n = 0
+    for up, down in cand:
+        su, sd = getattr(up, "_b200_state", None), getattr(down, "_b200_state", None)
+        if su is None or sd is None or su.chain_next is not None or not chain_supported(su, sd):
+            continue
+        su.chain_next, su.chain_keep_output = sd, bool(keep_hidden)
+        sd.chain_fed = True
         n += 1
     return n
 

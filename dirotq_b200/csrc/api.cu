@@ -312,16 +312,31 @@ size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int64_t N_panel, int3
   return carve_f16(M, n_chunks, tail_pitch, N_panel).total;
 }
 
+// Where the GEMM's epilogue also quantises its output for a following layer: that layer's activation buffers.
+struct QuantOut {
+  void* codes;
+  void* scales;
+  void* zeros;
+  int64_t ldm;
+  int64_t q_len;
+  void* tail;
+  int tail_pitch;
+  int row_bytes;
+  int mode;
+  float clip;
+};
+
 // skip_fold != 0: the workspace already holds the activation records and the scaled tail of these codes
-// (left there by an earlier call on the same activations).
+// (left there by an earlier call on the same activations).  qo != null: see QuantOut; y may then be null.
 static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
                                   const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
                                   const void* w_panel, const float* w_colscale, const void* x_tail,
                                   const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
                                   void* y, void* workspace, size_t workspace_bytes, int skip_fold, int act,
-                                  int32_t* status, void* stream) {
+                                  int32_t* status, void* stream, const QuantOut* qo = nullptr) {
   if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM && a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
-  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_colscale || !y || !workspace) return DIROTQ_E_ARG;
+  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_colscale || (!y && !qo) || !workspace)
+    return DIROTQ_E_ARG;
   if (!w_panel && (!w_codes || !w_mult)) return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
   if (a_mode != DIROTQ_INT4_SYM && !x_zeros) return DIROTQ_E_ARG;
@@ -384,6 +399,18 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   a.wait_limit_k = wait_limit_k();
   a.force_bn = 0;
   a.act = act;
+  if (qo) {
+    a.q_codes = static_cast<uint8_t*>(qo->codes);
+    a.q_scales = static_cast<__nv_bfloat16*>(qo->scales);
+    a.q_zeros = static_cast<__nv_bfloat16*>(qo->zeros);
+    a.q_ldm = qo->ldm;
+    a.q_row_bytes = qo->row_bytes;
+    a.q_len = qo->q_len;
+    a.q_tail = static_cast<__nv_bfloat16*>(qo->tail);
+    a.q_tail_pitch = qo->tail_pitch;
+    a.q_mode = qo->mode;
+    a.q_clip = qo->clip;
+  }
   return launch_gemm_int_f16(a, st);
 }
 
@@ -472,10 +499,14 @@ size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M) {
   return w.total;
 }
 
-// stages: 1 = rotate / quantise into the workspace, 2 = GEMM from the workspace, 3 = both
+// stages: 1 = rotate / quantise into the workspace, 2 = GEMM from the workspace, 3 = both; 4 (with 2) = the
+// workspace holds codes, scales and zero points written by someone else (a producer's epilogue): the per-call
+// folding of the scales, normally part of stage 1's bookkeeping, runs before the GEMM.
+// qo != null: the GEMM's epilogue quantises its output into these buffers as well (16-bit-conversion INT path only).
 static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
-                         size_t workspace_bytes, int stages, int32_t* status, void* stream) {
-  if (!lin || !workspace || ((stages & 1) && !x) || ((stages & 2) && !y)) return DIROTQ_E_ARG;
+                         size_t workspace_bytes, int stages, int32_t* status, void* stream,
+                         const QuantOut* qo = nullptr) {
+  if (!lin || !workspace || ((stages & 1) && !x) || ((stages & 2) && !y && !qo)) return DIROTQ_E_ARG;
   ActGeom g;
   WsCarve w;
   int rc = carve(lin, M, &g, &w);
@@ -496,6 +527,7 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
     if (rc) return rc;
   }
   if (!(stages & 2)) return DIROTQ_OK;
+  if (qo && !(uses_f16_gemm(lin, g) && g.mode != DIROTQ_INT8_ASYM)) return DIROTQ_E_UNSUPPORTED;
   if (g.mode == DIROTQ_NVFP4_HW)
     return gemm_w4a4_nvfp4_impl(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
                                 lin->fmt.tensor_scale * lin->w_tensor_scale, lin->w_colscale, tail, lin->w_tail, g.tail_total,
@@ -506,8 +538,8 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
     // the activation-side folding belongs to the first stage: a GEMM-only call finds its results in place
     return gemm_w4a4_int_f16_impl(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
                                   lin->w_mult, lin->w_panel_f16, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
-                                  lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 1) ? 0 : 1, lin->epilogue_act,
-                                  status, stream);
+                                  lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 5) ? 0 : 1, lin->epilogue_act,
+                                  status, stream, qo);
   }
   if (lin->epilogue_act != 0) return DIROTQ_E_UNSUPPORTED;
   return dirotq_gemm_w4a4_int(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
@@ -523,6 +555,57 @@ int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, vo
 int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* workspace, size_t workspace_bytes,
                        int32_t* status, void* stream) {
   return linear_stages(lin, nullptr, M, y, workspace, workspace_bytes, 2, status, stream);
+}
+
+// A following layer can take its activations from the producer's epilogue when its quantiser needs nothing but the
+// producer's output row: 4-bit integer groups of 64 over the leading channels, the rest (a multiple of 64, possibly
+// none) kept in 16 bits, no rotation, no channel selection, and the 16-bit-conversion GEMM (whose per-call folding
+// step reads the scales back).
+static int next_takes_epilogue_codes(const dirotq_linear* lin, const dirotq_linear* next, const ActGeom& gn) {
+  if (next->rot_t || next->perm_idx) return 0;
+  if (gn.mode != DIROTQ_INT4_SYM && gn.mode != DIROTQ_INT4_ASYM) return 0;
+  if (gn.H != 0 || gn.group != 64 || gn.q_len % 64 != 0 || gn.tail_total % 64 != 0) return 0;
+  if (gn.D != lin->out_features) return 0;
+  return uses_f16_gemm(next, gn) ? 1 : 0;
+}
+
+int dirotq_linear_chain_supported(const dirotq_linear* lin, const dirotq_linear* next) {
+  if (!lin || !next) return 0;
+  ActGeom g, gn;
+  if (make_geom(&lin->fmt, &g) || make_geom(&next->fmt, &gn)) return 0;
+  if (!uses_f16_gemm(lin, g) || g.mode == DIROTQ_INT8_ASYM) return 0;
+  return next_takes_epilogue_codes(lin, next, gn);
+}
+
+int dirotq_linear_forward_chain(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
+                                size_t workspace_bytes, const dirotq_linear* next, void* next_workspace,
+                                size_t next_workspace_bytes, int32_t* status, void* stream) {
+  if (!lin || !next || !next_workspace) return DIROTQ_E_ARG;
+  if (!dirotq_linear_chain_supported(lin, next)) return DIROTQ_E_UNSUPPORTED;
+  ActGeom gn;
+  WsCarve wn;
+  int rc = carve(next, M, &gn, &wn);
+  if (rc) return rc;
+  if (next_workspace_bytes < wn.total) return DIROTQ_E_ARG;
+  if (reinterpret_cast<uintptr_t>(next_workspace) & 255) return DIROTQ_E_ALIGN;
+  uint8_t* nws = static_cast<uint8_t*>(next_workspace);
+  QuantOut qo;
+  qo.codes = nws + wn.codes;
+  qo.scales = nws + wn.scales;
+  qo.zeros = is_asym(gn.mode) ? nws + wn.zeros : nullptr;
+  qo.ldm = ld_rows(M);
+  qo.q_len = gn.q_len;
+  qo.tail = gn.tail_total > 0 ? nws + wn.tail : nullptr;
+  qo.tail_pitch = gn.tail_pitch;
+  qo.row_bytes = gn.code_row_bytes;
+  qo.mode = gn.mode;
+  qo.clip = gn.clip;
+  return linear_stages(lin, x, M, y, workspace, workspace_bytes, 3, status, stream, &qo);
+}
+
+int dirotq_linear_gemm_prequantised(const dirotq_linear* lin, int64_t M, void* y, void* workspace,
+                                    size_t workspace_bytes, int32_t* status, void* stream) {
+  return linear_stages(lin, nullptr, M, y, workspace, workspace_bytes, 2 | 4, status, stream);
 }
 
 

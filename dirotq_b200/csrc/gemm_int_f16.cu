@@ -48,6 +48,7 @@
 #include "launchers.cuh"
 #include "ptx.cuh"
 #include "tma_host.cuh"
+#include "quant_math.cuh"
 
 namespace dq {
 
@@ -457,6 +458,100 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       tc_fence_after();
       ++use;
       const uint32_t tl = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + ch * CW;
+      if (a.q_codes) {
+        // ---- quantise-out: every 64 columns of the tile are one group of the following layer; the two warps of a
+        // lane quarter take them alternately (a 192-wide tile: groups 0 and 2 here, group 1 there) ----
+#pragma unroll 1
+        for (int gi = ch; gi < BN / 64; gi += 2) {
+          uint32_t v[64];
+          const uint32_t tg = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + gi * 64;
+          tmem_ld32(tg, v);
+          tmem_ld32(tg + 32, v + 32);
+          tmem_wait_ld();
+          if (gi + 2 >= BN / 64) {                      // the accumulator is out of TMEM: hand it back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(buf));
+          }
+          const int64_t col0 = (int64_t)n0 + gi * 64;
+          if (col0 + 64 > a.N) continue;               // padding of the last tile (N is a multiple of 64 here)
+          uint32_t w[32];                               // the activated output, bf16 pairs: what the next quantiser sees
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i));
+            const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.cs + col0 + 8 * i + 4));
+            const float cs8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float b[8];
+            if (a.bias) {
+              const uint4 bb = __ldg(reinterpret_cast<const uint4*>(a.bias + col0 + 8 * i));
+              const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) { float2 f = __bfloat1622float2(bh[e2]); b[2 * e2] = f.x; b[2 * e2 + 1] = f.y; }
+            } else {
+#pragma unroll
+              for (int e2 = 0; e2 < 8; ++e2) b[e2] = 0.f;
+            }
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              float f0 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2]), rs * cs8[2 * e2], b[2 * e2]);
+              float f1 = __fmaf_rn(__uint_as_float(v[8 * i + 2 * e2 + 1]), rs * cs8[2 * e2 + 1], b[2 * e2 + 1]);
+              if (a.act == 1) { f0 = gelu_tanh_bf16(f0); f1 = gelu_tanh_bf16(f1); }
+              __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+              w[4 * i + e2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+          }
+          if (a.y) {                                    // the bf16 tensor as well, when the caller wants it
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              if (lane == 0) bulk_wait_read0();
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                gf_sts128(stg_row + (uint32_t)((i ^ stg_sw) << 4), w[16 * g + 4 * i], w[16 * g + 4 * i + 1], w[16 * g + 4 * i + 2],
+                          w[16 * g + 4 * i + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tm.y, stg, (int)col0 + 32 * g, m0 + q * 32);
+                bulk_commit_group();
+              }
+            }
+          }
+          if (col0 >= a.q_len) {                        // the following layer's 16-bit channels
+            if (row < a.M) {
+              uint4* t = reinterpret_cast<uint4*>(a.q_tail + row * a.q_tail_pitch + (col0 - a.q_len));
+#pragma unroll
+              for (int i = 0; i < 8; ++i) t[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+            continue;
+          }
+          if (row < a.M) {
+            const int chunk = (int)(col0 >> 6);
+            uint4* dst = reinterpret_cast<uint4*>(a.q_codes + row * a.q_row_bytes + (int64_t)chunk * 32);
+            GroupParams p;
+            if (a.q_mode == DIROTQ_INT4_SYM) {
+              const float amax = fmaxf(fmaxf(amax_bf16x16(w), amax_bf16x16(w + 8)), fmaxf(amax_bf16x16(w + 16), amax_bf16x16(w + 24)));
+              p = int_sym_params<true>(amax, -amax, a.q_clip, 7.f);
+              const float rcp = __frcp_rn(p.scale);
+              dst[0] = int_sym_planar32_packed(w, rcp, a.q_clip < 1.f);
+              dst[1] = int_sym_planar32_packed(w + 16, rcp, a.q_clip < 1.f);
+            } else {
+              float mx = -INFINITY, mn = INFINITY;
+              minmax_bf16x16(w, mx, mn);
+              minmax_bf16x16(w + 8, mx, mn);
+              minmax_bf16x16(w + 16, mx, mn);
+              minmax_bf16x16(w + 24, mx, mn);
+              p = int_asym_params<true>(mx, mn, a.q_clip, 15.f);
+              const float rcp = __frcp_rn(p.scale);
+              dst[0] = int_asym_planar32_packed(w, rcp, p.zero);
+              dst[1] = int_asym_planar32_packed(w + 16, rcp, p.zero);
+              a.q_zeros[(int64_t)chunk * a.q_ldm + row] = __float2bfloat16_rn(p.zero);
+            }
+            a.q_scales[(int64_t)chunk * a.q_ldm + row] = __float2bfloat16_rn(p.scale);
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int g = 0; g < CW / 32; ++g) {
         uint32_t v[32];
@@ -750,6 +845,16 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
       (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_panel) & 15) || !a.w_panel)
     return DIROTQ_E_ALIGN;
   int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.M, a.N);
+  if (a.q_codes) {
+    if (a.N % 64 || a.q_len % 64 || a.q_len <= 0 || a.q_len > a.N || a.q_row_bytes < a.q_len / 2 || (a.q_row_bytes & 15) ||
+        (a.q_len < a.N && (!a.q_tail || a.q_tail_pitch < a.N - a.q_len || (a.q_tail_pitch & 7) ||
+                           (reinterpret_cast<uintptr_t>(a.q_tail) & 15))) ||
+        !a.q_scales || (a.q_mode != DIROTQ_INT4_SYM && a.q_mode != DIROTQ_INT4_ASYM) ||
+        (a.q_mode == DIROTQ_INT4_ASYM && !a.q_zeros) || (reinterpret_cast<uintptr_t>(a.q_codes) & 15))
+      return DIROTQ_E_ARG;
+  } else if (!a.y) {
+    return DIROTQ_E_ARG;
+  }
 #ifdef GF_FORCE_BN
   BN = GF_FORCE_BN;
 #endif
@@ -760,7 +865,8 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   rc = make_tmap_2d(&tm.wp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.w_panel, (uint64_t)a.n_chunks * 64, (uint64_t)a.N,
                     (uint64_t)a.n_chunks * 128, BN);
   if (rc) return rc;
-  rc = make_tmap_2d_sw(&tm.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2,
+  // without an output tensor (quantise-out only) the map is never used: any valid address will do
+  rc = make_tmap_2d_sw(&tm.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y ? (const void*)a.y : a.w_panel, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2,
                        32, 32, 64);
   if (rc) return rc;
   if (a.kt > 0) {

@@ -152,6 +152,20 @@ struct GemmIntF16Args {
   int* status;
   int force_bn;                // 0 = pick the column-tile width from N
   int act;                     // epilogue activation: 0 none, 1 GELU (tanh form) on the bf16-rounded output
+  // Optional: the epilogue ALSO quantises its (activated, bf16-rounded) output rows for a following un-rotated INT4
+  // layer of width N with groups of 64 (and, optionally, its last columns kept in 16 bits) -- codes / scales / zero points in that layer's activation
+  // layout -- so that the layer's quantise-only kernel and a round trip of the [M, N] tensor disappear; y may then be
+  // null.
+  uint8_t* q_codes = nullptr;       // [M, N / 2]
+  __nv_bfloat16* q_scales = nullptr;  // [N / 64, q_ldm]
+  __nv_bfloat16* q_zeros = nullptr;   // asymmetric mode only
+  int64_t q_ldm = 0;
+  int64_t q_len = 0;                // quantised columns (multiple of 64); columns beyond go to q_tail as bf16
+  __nv_bfloat16* q_tail = nullptr;  // [M, q_tail_pitch], (N - q_len) columns used
+  int q_tail_pitch = 0;
+  int q_row_bytes = 0;              // bytes between code rows
+  int q_mode = 0;                   // DIROTQ_INT4_SYM or DIROTQ_INT4_ASYM
+  float q_clip = 1.f;
 };
 
 struct GemmFp4Args {

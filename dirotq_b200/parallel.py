@@ -201,6 +201,15 @@ class FluxLinearStep:
         self.fused_gelu = n > 0
         return n
 
+    def fuse_ffn_quantise(self) -> int:
+        """The up-projections' epilogues quantise for their un-rotated down-projections (backend.fuse_ffn_quantise);
+        the [M, inner] hidden tensor is never written, since only the down-projection reads it here.  Needs
+        fuse_gelu first: the hand-off recognises the tensor the up-projection returned."""
+        from . import backend
+        if not self.fused_gelu:
+            return 0
+        return backend.fuse_ffn_quantise(pairs=[(wu, wd) for _, _, wu, wd in self.blocks], keep_hidden=False)
+
     def ops_per_step(self):
         """(linear, rotation) operations of the whole step at the global batch."""
         from . import dit

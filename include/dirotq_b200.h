@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DIROTQ_ABI_VERSION 5
+#define DIROTQ_ABI_VERSION 6
 
 /* ---- activation quantiser modes (ActQuantizer.configure, utils/quant_utils.py:182-199) ---- */
 enum {
@@ -287,6 +287,28 @@ int dirotq_linear_forward(const dirotq_linear* lin, const void* x, int64_t M, vo
  * both).  The caller guarantees that the activations are unchanged since. */
 int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* workspace, size_t workspace_bytes,
                        int32_t* status, void* stream);
+
+/* Producer -> consumer hand-off inside a feed-forward pair (up-projection with its fused GELU, then
+ * the down-projection; the reference runs them as two ActQuantWrapper forwards with the activation
+ * between them, models/pixart-sigma/model_utils.py:120-127, utils/quant_utils.py:255-326): the
+ * producer's GEMM epilogue quantises its own output rows for `next` -- codes, scales and zero points
+ * land in next_workspace exactly as next's quantise stage would have left them, bit for bit -- so the
+ * separate quantise launch and one round trip of the [M, out_features] tensor disappear.  `y` may be
+ * NULL when nobody else reads the producer's output.  Afterwards dirotq_linear_gemm_prequantised
+ * (next, M, ...) on next_workspace finishes the pair.
+ *   Supported (dirotq_linear_chain_supported returns 1): `lin` a 4-bit integer layer on the
+ * 16-bit-conversion GEMM (w_mult set); `next` a 4-bit integer layer, hidden layout, groups of 64, its
+ * quantised part and its 16-bit tail both multiples of 64 channels (the tail may be empty), no
+ * rotation, no channel selection, width == lin->out_features, w_mult set.  Anything else: DIROTQ_E_UNSUPPORTED, nothing launched. */
+int dirotq_linear_chain_supported(const dirotq_linear* lin, const dirotq_linear* next);
+int dirotq_linear_forward_chain(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
+                                size_t workspace_bytes, const dirotq_linear* next, void* next_workspace,
+                                size_t next_workspace_bytes, int32_t* status, void* stream);
+/* The GEMM of `lin` on codes / scales / zero points that a producer's epilogue wrote into `workspace`
+ * (dirotq_linear_forward_chain): like dirotq_linear_gemm, plus the per-call folding of the scales
+ * that dirotq_linear_forward does in its first half. */
+int dirotq_linear_gemm_prequantised(const dirotq_linear* lin, int64_t M, void* y, void* workspace,
+                                    size_t workspace_bytes, int32_t* status, void* stream);
 
 /* Same computation as dirotq_linear_forward, for callers that can hand over nothing but the input
  * and the output.  (No counterpart in the reference: its eager forward allocates freely through

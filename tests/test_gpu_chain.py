@@ -1,0 +1,172 @@
+"""GPU parity of the feed-forward hand-off: the up-projection's GEMM epilogue quantises GELU(up(x)) for the
+down-projection (dirotq_linear_forward_chain + dirotq_linear_gemm_prequantised).  Integer work: the codes, group
+scales, zero points and 16-bit channels it leaves must equal, bit for bit, what the reference quantiser
+(utils/quant_utils.py:255-326, restated in the oracle) makes of the unfused hidden tensor, and the pair's output
+must equal the two-step forward's exactly."""
+import ctypes as C
+
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import dirotq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _patched():
+    from dirotq_b200 import backend
+    from dirotq_b200.wrapper import ActQuantWrapper
+    saved = ActQuantWrapper.forward
+    backend.patch_forward()
+    yield
+    ActQuantWrapper.forward = saved
+
+
+def _pair(inner, tail_down, a_sym, seed, dim=384, k=64):
+    from dirotq_b200 import backend, dit
+    up = dit.make_wrapped_linear(dit.LayerDef("ff.net.0.proj", dim, inner, tail=k), "int4", seed, "cuda", a_sym=a_sym)
+    down = dit.make_wrapped_linear(dit.LayerDef("ff.net.2", inner, dim, kind="norot", tail=tail_down, source="ff"),
+                                   "int4", seed + 1, "cuda", a_sym=a_sym)
+    ff = nn.Module()
+    ff.net = nn.ModuleList([dit.GeluProj(up), nn.Identity(), down])
+    root = nn.Module()
+    root.add_module("ff", ff)
+    backend.preconvert_rotations_to_device(root, "cuda")
+    assert backend.fuse_gelu_modules(root) == 1
+    return root, ff, up, down
+
+
+def _regions(st, M):
+    """(name, offset, bytes) of the activation buffers at the head of a layer's workspace."""
+    from dirotq_b200 import _lib
+    L = _lib.lib()
+    fmt = st.fmt.c()
+    l = _lib.ActLayoutC()
+    assert L.dirotq_act_layout_of(C.byref(fmt), C.byref(l)) == 0
+    sizes = [("codes", L.dirotq_act_codes_bytes(C.byref(l), M)), ("scales", L.dirotq_act_scales_bytes(C.byref(fmt), C.byref(l), M)),
+             ("zeros", L.dirotq_act_zeros_bytes(C.byref(fmt), C.byref(l), M)),
+             ("tail", L.dirotq_act_tail_bytes(C.byref(l), M) if l.tail_total > 0 else 0)]
+    out, off = [], 0
+    for name, n in sizes:
+        out.append((name, off, int(n)))
+        off += int(n)
+    return out, l
+
+
+@pytest.mark.parametrize("a_sym", [True, False])
+@pytest.mark.parametrize("M,inner,tail_down", [(520, 1536, 0), (300, 1536, 128), (129, 1472, 64),
+                                                (4700, 1536, 128)])     # the last one takes 192-wide column tiles
+def test_epilogue_quantises_for_the_down_projection(a_sym, M, inner, tail_down):
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.synth import synth_activations
+    root, ff, up, down = _pair(inner, tail_down, a_sym, 71)
+    x = synth_activations(M, 384, torch.Generator().manual_seed(9)).reshape(1, M, 384).cuda()
+    hidden = ff.net[0](x)
+    y_two_step = ff.net[2](hidden)
+    ops.check_status()
+    sd = down._b200_state
+    ws_two_step = sd.workspace(M, x.device).clone()
+
+    assert backend.fuse_ffn_quantise(root) == 1
+    assert backend.fuse_ffn_quantise(root) == 0                 # idempotent
+    sd.workspace(M, x.device).zero_()
+    hidden2 = ff.net[0](x)
+    regions, lay = _regions(sd, M)
+    ws_chain = sd.workspace(M, x.device).clone()
+    y_chain = ff.net[2](hidden2)
+    ops.check_status()
+    assert sd.chain_hits == 1
+    assert torch.equal(hidden2, hidden)                         # keep_hidden: the bf16 tensor is written as before
+    assert torch.equal(y_chain, y_two_step)
+
+    # what the producer's epilogue left, against the quantise-only kernel's buffers ...
+    for name, off, n in regions:
+        if n == 0:
+            continue
+        a, b = ws_chain[off:off + n].cpu(), ws_two_step[off:off + n].cpu()
+        if name in ("scales", "zeros"):                         # [n_chunks, ldm] bf16, rows beyond M are padding
+            ldm = (M + 7) // 8 * 8
+            a = a[:lay.n_scales * ldm * 2].view(torch.int16).reshape(lay.n_scales, ldm)[:, :M]
+            b = b[:lay.n_scales * ldm * 2].view(torch.int16).reshape(lay.n_scales, ldm)[:, :M]
+        elif name == "codes":
+            a, b = a[:M * lay.code_row_bytes], b[:M * lay.code_row_bytes]
+        else:
+            a, b = a[:M * lay.tail_pitch * 2], b[:M * lay.tail_pitch * 2]
+        assert torch.equal(a, b), name
+
+    # ... and against the reference quantiser applied to the hidden tensor
+    cfg = O.QuantCfg(bits=4, groupsize=64, sym=a_sym, high_bits_length=tail_down)
+    r = O.act_quant(hidden.cpu(), cfg)
+    codes_off, codes_n = regions[0][1], regions[0][2]
+    got = O.unpack_planar32(ws_chain[codes_off:codes_off + M * lay.code_row_bytes].cpu().reshape(M, -1), a_sym)
+    want = r.codes.reshape(M, -1).to(got.dtype)
+    assert torch.equal(got[:, :want.shape[1]], want)
+    s_off = regions[1][1]
+    ldm = (M + 7) // 8 * 8
+    got_s = ws_chain[s_off:s_off + lay.n_scales * ldm * 2].cpu().view(torch.bfloat16).reshape(lay.n_scales, ldm)[:, :M]
+    assert torch.equal(got_s.t().contiguous().view(torch.int16), r.scale.reshape(M, -1).contiguous().view(torch.int16))
+    if tail_down:
+        t_off = regions[3][1]
+        got_t = ws_chain[t_off:t_off + M * lay.tail_pitch * 2].cpu().view(torch.bfloat16).reshape(M, lay.tail_pitch)
+        assert torch.equal(got_t[:, :tail_down].view(torch.int16), hidden.cpu().reshape(M, -1)[:, -tail_down:].contiguous().view(torch.int16))
+
+
+def test_hidden_tensor_not_written_when_nobody_else_reads_it():
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.synth import synth_activations
+    M = 700
+    root, ff, up, down = _pair(1536, 128, True, 83)
+    x = synth_activations(M, 384, torch.Generator().manual_seed(2)).reshape(1, M, 384).cuda()
+    y_two_step = ff.net[2](ff.net[0](x))
+    assert backend.fuse_ffn_quantise(root, keep_hidden=False) == 1
+    y_chain = ff.net[2](ff.net[0](x))
+    ops.check_status()
+    assert torch.equal(y_chain, y_two_step)
+    # a pair fused before its first forward (the down-projection's workspace and resident panel do not exist yet)
+    root_b, ff_b, _, down_b = _pair(1536, 128, True, 83)
+    assert backend.fuse_ffn_quantise(root_b, keep_hidden=False) == 1
+    y_first = ff_b.net[2](ff_b.net[0](x))
+    ops.check_status()
+    assert down_b._b200_state.chain_hits == 1 and torch.equal(y_first, y_two_step)
+    # a tensor that is not the producer's output takes the ordinary path, and the stale hand-off is dropped
+    ff.net[0](x)
+    other = torch.randn(1, M, 1536, device="cuda").to(torch.bfloat16)
+    hits = down._b200_state.chain_hits
+    y_other = ff.net[2](other)
+    assert down._b200_state.chain_hits == hits and down._b200_state.handed is None
+    y_plain = backend.linear_forward(down._b200_state, other.reshape(M, 1536))
+    assert torch.equal(y_other.reshape(M, -1), y_plain)
+
+
+def test_unsupported_pairs_are_left_alone():
+    from dirotq_b200 import backend, dit
+    # a rotated down-projection needs the whole row before it can quantise: no hand-off
+    up = dit.make_wrapped_linear(dit.LayerDef("ff.net.0.proj", 384, 1536, tail=64), "int4", 5, "cuda")
+    down = dit.make_wrapped_linear(dit.LayerDef("ff.net.2", 1536, 384, tail=64, source="ff"), "int4", 6, "cuda")
+    ff = nn.Module()
+    ff.net = nn.ModuleList([dit.GeluProj(up), nn.Identity(), down])
+    root = nn.Module()
+    root.add_module("ff", ff)
+    backend.preconvert_rotations_to_device(root, "cuda")
+    backend.fuse_gelu_modules(root)
+    assert backend.fuse_ffn_quantise(root) == 0
+    assert not backend.chain_supported(up._b200_state, down._b200_state)
+
+
+def test_flux_blocks_give_the_same_step_with_the_hand_off():
+    """One double-stream and two single-stream FLUX blocks: every feed-forward pair (image, text, single) hands its
+    activations over in the epilogue and the step's output does not change by a bit."""
+    from dirotq_b200 import backend, denoise, ops
+    step = denoise.DenoiseStep("flux", "int4", "cuda", n_blocks=1, seed=6100, prepare=True)
+    assert backend.fuse_gelu_modules(step) == 4
+    inputs = step.example_inputs(1, "cuda", seed=4, tokens=640, text=128)
+    with torch.no_grad():
+        y_two_step = step(*inputs)
+        before = step.kernel_launches_per_step()
+        assert backend.fuse_ffn_quantise(step, keep_hidden=False) == 4
+        y_chain = step(*inputs)
+    ops.check_status()
+    assert torch.equal(y_chain, y_two_step)
+    assert step.kernel_launches_per_step() == before - 4
