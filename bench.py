@@ -68,6 +68,9 @@ def parse():
     ap.add_argument("--no-sub", action="store_true", help="skip the sub-records and the model-shaped step")
     ap.add_argument("--no-fuse-gelu", action="store_true",
                     help="keep the GELU between the FFN linears as a separate PyTorch kernel")
+    ap.add_argument("--no-fuse-qkv", action="store_true",
+                    help="keep to_q / to_k / to_v (and add_*_proj) as three GEMMs on the shared codes instead of one GEMM "
+                         "on concatenated weights")
     ap.add_argument("--no-fuse-ffn", action="store_true",
                     help="keep the quantise kernel between an FFN pair's GELU and its un-rotated down-projection instead of "
                          "quantising in the up-projection's GEMM epilogue")
@@ -373,6 +376,7 @@ def run_ours(args):
             backend.preconvert_rotations_to_device(step.layers, dev)
             n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else step.fuse_gelu()
             n_chained = 0 if args.no_fuse_ffn else step.fuse_ffn_quantise()
+            n_qkv = 0 if args.no_fuse_qkv else backend.fuse_sibling_gemms(step.layers)
             for lyr in step._flat:                   # the packed device state is all the forward needs
                 lyr._b200_explicit = None
                 lyr.rotation = lyr.rotation_per_head = None
@@ -392,6 +396,7 @@ def run_ours(args):
             backend.preconvert_rotations_to_device(step, dev)
             n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else backend.fuse_gelu_modules(step)
             n_chained = 0 if args.no_fuse_ffn else backend.fuse_ffn_quantise(step, keep_hidden=False)
+            n_qkv = 0 if args.no_fuse_qkv else backend.fuse_sibling_gemms(step)
             lin_ops, _ = step.ops_per_step(M)
             rot_ops = effective_rotation_ops(step.layers, step.block, M)
             x_host = synth_activations(M, D, g).reshape(batch, tokens, D).pin_memory()
@@ -451,11 +456,11 @@ def run_ours(args):
             if world == 1:
                 sub["nvfp4_flux_gemm"] = sub_nvfp4_flux_gemms(dev)
                 if args.workload != "pixart_nvfp4":
-                    sub["pixart_nvfp4"] = sub_linear_step(D_, "pixart_nvfp4", 28, not args.no_fuse_ffn)
+                    sub["pixart_nvfp4"] = sub_linear_step(D_, "pixart_nvfp4", 28, not args.no_fuse_ffn, not args.no_fuse_qkv)
                 if not is_flux:
-                    sub["flux_int4"] = sub_flux_step(D_, 4, "dp", not args.no_fuse_ffn)
+                    sub["flux_int4"] = sub_flux_step(D_, 4, "dp", not args.no_fuse_ffn, not args.no_fuse_qkv)
             elif not is_flux:
-                sub["flux_int4_tp"] = sub_flux_step(D_, 2, "tp", not args.no_fuse_ffn)
+                sub["flux_int4_tp"] = sub_flux_step(D_, 2, "tp", not args.no_fuse_ffn, not args.no_fuse_qkv)
 
     cb = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -476,7 +481,7 @@ def run_ours(args):
                                            "(tcgen05 kind::f16); the exact-integer kind::i8 route is --exact-int"),
                        "gelu": (f"fused into the up-projection GEMM epilogue ({n_fused} layers)" if n_fused
                                 else "separate PyTorch kernel"),
-                       "ffn_pairs_quantised_in_epilogue": n_chained,
+                       "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
                        "l2": l2_note,
                        "linear_gflop_per_step_per_gpu": lin_ops / 1e9, "rotation_gflop_per_step_per_gpu": rot_ops / 1e9},
             "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
@@ -512,6 +517,7 @@ def denoise_record(D_, family, quant, gbatch, world, strong, args):
     step = denoise.DenoiseStep(family, quant, dev, n_blocks=n_blocks, seed=5000 + 7919 * D_.rank, prepare=True)
     n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else backend.fuse_gelu_modules(step)
     n_chained = 0 if args.no_fuse_ffn else backend.fuse_ffn_quantise(step, keep_hidden=False)
+    n_qkv = 0 if args.no_fuse_qkv else backend.fuse_sibling_gemms(step)
     inputs = step.example_inputs(batch, dev, seed=D_.rank)
     with torch.no_grad():
         for _ in range(3):
@@ -524,7 +530,7 @@ def denoise_record(D_, family, quant, gbatch, world, strong, args):
            "text_tokens": step.shape["text"], "step_ms": ms, "wrapped_linears_ms": lin_ms,
            "linear_path_share": lin_ms / ms if ms > 0 else None,
            "linear_tflops_inside_step": D_.world * lin / (lin_ms * 1e-3) / 1e12 if lin_ms > 0 else None,
-           "gelu_fused_layers": n_fused, "ffn_pairs_quantised_in_epilogue": n_chained,
+           "gelu_fused_layers": n_fused, "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
            "launches_per_step": step.kernel_launches_per_step(),
            "glue": "PyTorch bf16: adaLN modulation, LayerNorm / RMSNorm, rotary embedding, scaled_dot_product_attention "
                    "(SANA: ReLU linear attention, Mix-FFN convolutions), residuals",
@@ -576,7 +582,7 @@ def sub_nvfp4_flux_gemms(dev):
     return out
 
 
-def sub_linear_step(D_, workload, n_blocks, chain=True):
+def sub_linear_step(D_, workload, n_blocks, chain=True, qkv=True):
     """Another workload's linear-path step on one GPU (resident inputs, 3 warm-up + 5 timed steps)."""
     from dirotq_b200 import backend, dit, ops
     from dirotq_b200.synth import synth_activations
@@ -588,6 +594,7 @@ def sub_linear_step(D_, workload, n_blocks, chain=True):
     backend.preconvert_rotations_to_device(step, dev)
     n_fused = backend.fuse_gelu_modules(step)
     n_chained = backend.fuse_ffn_quantise(step, keep_hidden=False) if chain else 0
+    n_qkv = backend.fuse_sibling_gemms(step) if qkv else 0
     x = synth_activations(M, block[0].in_f, torch.Generator().manual_seed(3)).reshape(gbatch, tokens, -1).to(dev)
     for _ in range(3):
         step(x)
@@ -597,7 +604,7 @@ def sub_linear_step(D_, workload, n_blocks, chain=True):
     peak, src = tensor_peak("nvfp4" if quant == "nvfp4" else "f16")
     rec = {"workload": desc, "blocks": n_blocks, "rows": M, "ms_per_step": ms, "tflops": lin / (ms * 1e-3) / 1e12,
            "frac_of_peak": lin / (ms * 1e-3) / 1e12 / peak, "peak_tflops": peak, "peak_source": src,
-           "gelu_fused_layers": n_fused, "ffn_pairs_quantised_in_epilogue": n_chained,
+           "gelu_fused_layers": n_fused, "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
            "launches_per_step": step.kernel_launches_per_step(),
            "note": "whole linear-path step (rotate + quantise kernels included in the time, only the linears' 2*M*N*D credited)"}
     del step, x
@@ -605,7 +612,7 @@ def sub_linear_step(D_, workload, n_blocks, chain=True):
     return rec
 
 
-def sub_flux_step(D_, n_double, ffn, chain=True):
+def sub_flux_step(D_, n_double, ffn, chain=True, qkv=True):
     """FLUX linear path on a slice of the stack (n_double double-stream blocks on both streams + 2 n_double
     single-stream blocks), fixed global batch 4.  Several GPUs: rows sharded, feed-forwards tensor-parallel; the NCCL
     time is the sum of CUDA-event pairs around every all-gather and reduce-scatter of one step."""
@@ -617,6 +624,7 @@ def sub_flux_step(D_, n_double, ffn, chain=True):
     backend.preconvert_rotations_to_device(step.layers, dev)
     step.fuse_gelu()
     n_chained = step.fuse_ffn_quantise() if chain else 0
+    n_qkv = backend.fuse_sibling_gemms(step.layers) if qkv else 0
     for lyr in step._flat:
         lyr._b200_explicit = None
         lyr.rotation = lyr.rotation_per_head = None
@@ -630,7 +638,7 @@ def sub_flux_step(D_, n_double, ffn, chain=True):
     rec = {"blocks": f"{n_double} double-stream (image + text) + {2 * n_double} single-stream of 19 + 38", "global_batch": 4,
            "rows_per_gpu": M, "ffn": step.ffn, "ms_per_step": ms,
            "tflops": step.ops_per_step()[0] / (ms * 1e-3) / 1e12, "ffn_pairs_quantised_in_epilogue": n_chained,
-           "launches_per_step": step.kernel_launches_per_step()}
+           "qkv_groups_as_one_gemm": n_qkv, "launches_per_step": step.kernel_launches_per_step()}
     if world > 1 and step.ffn == "tp":
         step.comm_pairs = []
         step(x)

@@ -49,6 +49,10 @@ class SharedActivation:
         self.seen = set()
         self.hits = 0
         self.misses = 0
+        self.fused: Optional["LayerState"] = None     # one layer over the members' weights, concatenated along N
+        self.offsets: list = []                        # first output column of each member in the fused layer
+        self.y_all: Optional[torch.Tensor] = None      # [M, sum N]: output of the fused GEMM for the held tensor
+        self.incomplete = 0                            # fused passes whose result some member never picked up
 
     @staticmethod
     def _key(x: torch.Tensor):
@@ -67,12 +71,14 @@ class SharedActivation:
 
     def store(self, x: torch.Tensor, member_id: int):
         self.misses += 1
+        if self.x_ref is not None and len(self.seen) < self.n_members:
+            self.incomplete += 1
         self.x_ref, self.key, self.seen = x, self._key(x), {member_id}
 
     def release(self):
         """Forget the held activation tensor (it stays referenced until every member has used it, which never
         happens when the members of a group do not all see the same input, e.g. a cross-attention)."""
-        self.x_ref, self.key, self.seen = None, None, set()
+        self.x_ref, self.key, self.seen, self.y_all = None, None, set(), None
 
 
 @dataclass
@@ -142,6 +148,8 @@ def kernel_launches(st: Optional[LayerState]) -> int:
     activations of the layer before it runs only its own GEMM (and pre-pass)."""
     if st is None:
         return 2
+    if st.shared is not None and st.shared.fused is not None:
+        return kernel_launches(st.shared.fused) if st.member_id == 0 else 0     # one pass and one GEMM for the group
     n = 1 if (st.shared is not None and st.member_id > 0) else 2
     if st.chain_fed:
         n -= 1                              # its activations arrive quantised from the producer's epilogue
@@ -165,6 +173,23 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
     if M == 0:
         return y
+    grp = st.shared
+    if grp is not None and grp.fused is not None:
+        # siblings fused into one layer: the first member called on a tensor runs it, the others take their columns
+        if grp.incomplete > 2:
+            grp.fused, grp.y_all = None, None            # the members do not see the same tensor after all: separate GEMMs
+        else:
+            if not grp.lookup(x2d, st.member_id):
+                grp.store(x2d, st.member_id)
+                grp.y_all = linear_forward(grp.fused, x2d)
+            off = grp.offsets[st.member_id]
+            part = grp.y_all[:, off:off + st.out_features]
+            if grp.x_ref is None:
+                grp.y_all = None                         # every member has its view
+            if out is not None:
+                out.copy_(part)
+                return out
+            return part
     if st.hadamard_low_dim:
         x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
     if CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and M <= PANEL_CACHE_MAX_ROWS:
@@ -514,6 +539,76 @@ def share_sibling_activations(transformer, classes=None) -> int:
             m._ws = {}
         n_groups += 1
     return n_groups
+
+
+def _concat_states(members) -> Optional[LayerState]:
+    """One LayerState whose weight is the members' weights stacked along the output dimension (same activation format,
+    rotation and GEMM variant).  None where the packed layouts do not concatenate (NVFP4 scale tiles span 128 output
+    channels; the members' weight tensor scales and epilogues must agree)."""
+    first = members[0]
+    fmt, lay, dev = first.fmt, first.layout, first.w_codes.device
+    if any(m.hadamard_low_dim or m.perm_idx is not None or m.epilogue_act != first.epilogue_act or m.chain_next is not None
+           or m.w_tensor_scale != first.w_tensor_scale or (m.w_rowscale is None) != (first.w_rowscale is None)
+           or (m.folded is None) != (first.folded is None) or m.out_features % 8 for m in members):
+        return None
+    nvfp4 = fmt.mode == ops.NVFP4_HW
+    if nvfp4 and any(m.out_features % 128 for m in members):
+        return None
+    N = sum(m.out_features for m in members)
+    w_codes = torch.cat([m.w_codes[: m.out_features] for m in members], 0).contiguous()
+    has_bias = any(m.bias is not None for m in members)
+    bias = None
+    if has_bias:
+        bias = torch.cat([m.bias if m.bias is not None else torch.zeros(m.out_features, dtype=torch.bfloat16, device=dev)
+                          for m in members]).contiguous()
+    w_tail = None
+    if lay.tail_total > 0:
+        w_tail = torch.cat([m.w_tail[: m.out_features] for m in members], 0).contiguous()
+    if nvfp4:
+        w_scales = torch.cat([m.w_scales for m in members]).contiguous()              # whole 128-channel tiles
+        rs = None
+        if first.w_rowscale is not None:
+            rs = torch.cat([m.w_rowscale[: m.out_features] for m in members]).contiguous()
+        return LayerState(fmt, lay, N, first.rot_t, None, w_codes, w_scales, None, w_tail, bias, first.w_tensor_scale,
+                          0, None, epilogue_act=first.epilogue_act, w_rowscale=rs)
+    w_scales = torch.cat([m.w_scales[:, : m.out_features] for m in members], 1).contiguous()
+    w_sum = torch.cat([m.w_sum[:, : m.out_features] for m in members], 1).contiguous()
+    folded = None
+    if first.folded is not None:
+        pk = ops.PackedWeightInt4(N, lay.q_len, lay.group, lay.n_chunks, w_codes, w_scales, w_sum)
+        folded = ops.fold_weight_scales_f16(pk, w_tail, lay.tail_total)                # per-channel: same constants
+    return LayerState(fmt, lay, N, first.rot_t, None, w_codes, w_scales, w_sum, w_tail, bias, first.w_tensor_scale, 0,
+                      folded, epilogue_act=first.epilogue_act)
+
+
+def fuse_sibling_gemms(transformer, classes=None) -> int:
+    """Sibling layers that already share one rotate + quantise pass (share_sibling_activations: to_q / to_k / to_v,
+    add_q_proj / add_k_proj / add_v_proj) also run as ONE GEMM on their weights concatenated along the output
+    dimension -- the shape the reference's speed path gives its fused qkv projection
+    (speedup/report_flux_w4a4_no_rot_ffdown.py:336-345).  The first member called on a tensor launches the pass and
+    the GEMM; every member returns its own columns of the [M, sum N] result (a strided view; values are bit-identical
+    to the separate GEMMs, whose per-element arithmetic does not depend on the tiling).  A group whose members turn out
+    to see different tensors (a cross-attention) falls back to separate GEMMs after three unconsumed passes.
+    Returns the number of fused groups."""
+    classes = tuple(classes or _wrapper_classes())
+    groups = {}
+    for _, mod in transformer.named_modules():
+        st = getattr(mod, "_b200_state", None) if isinstance(mod, classes) else None
+        if st is not None and st.shared is not None:
+            groups[id(st.shared)] = st.shared
+    n = 0
+    for grp in groups.values():
+        if grp.fused is not None or len(grp.members) < 2:
+            continue
+        fused = _concat_states(grp.members)
+        if fused is None:
+            continue
+        grp.fused, grp.offsets, off = fused, [], 0
+        for m in grp.members:
+            grp.offsets.append(off)
+            off += m.out_features
+        n += 1
+    return n
 
 
 def release_shared_activations(transformer, classes=None) -> int:

@@ -1,8 +1,9 @@
-"""GPU parity of the feed-forward hand-off: the up-projection's GEMM epilogue quantises GELU(up(x)) for the
+"""GPU parity of the producer-side fusions.  (1) The feed-forward hand-off: the up-projection's GEMM epilogue quantises GELU(up(x)) for the
 down-projection (dirotq_linear_forward_chain + dirotq_linear_gemm_prequantised).  Integer work: the codes, group
 scales, zero points and 16-bit channels it leaves must equal, bit for bit, what the reference quantiser
 (utils/quant_utils.py:255-326, restated in the oracle) makes of the unfused hidden tensor, and the pair's output
-must equal the two-step forward's exactly."""
+must equal the two-step forward's exactly.  (2) q / k / v as one GEMM on weights concatenated along the output
+dimension: every member's columns must equal its own GEMM's output exactly."""
 import ctypes as C
 
 import pytest
@@ -170,3 +171,51 @@ def test_flux_blocks_give_the_same_step_with_the_hand_off():
     ops.check_status()
     assert torch.equal(y_chain, y_two_step)
     assert step.kernel_launches_per_step() == before - 4
+
+
+@pytest.mark.parametrize("quant,widths", [("int4", (256, 320, 192)), ("nvfp4", (256, 384, 128)), ("int8", (128, 128, 128))])
+def test_sibling_layers_run_as_one_gemm(quant, widths):
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+
+    def build(seed0):
+        attn = nn.Module()
+        ws = []
+        for i, leaf in enumerate(("to_q", "to_k", "to_v")):
+            w = dit.make_wrapped_linear(dit.LayerDef("attn1." + leaf, 384, widths[i], tail=64), quant, seed0 + i, "cuda")
+            if ws:
+                w.rotation = ws[0].rotation.clone()
+            attn.add_module(leaf, w)
+            ws.append(w)
+        root = nn.Module()
+        root.add_module("attn1", attn)
+        backend.preconvert_rotations_to_device(root, "cuda")
+        return root, ws
+
+    root, ws = build(177)
+    root2, ws2 = build(177)                                     # same weights, separate GEMMs
+    before = sum(backend.kernel_launches(w._b200_state) for w in ws)
+    assert backend.fuse_sibling_gemms(root) == 1
+    assert backend.fuse_sibling_gemms(root) == 0                # idempotent
+    grp = ws[0]._b200_state.shared
+    assert grp.fused is not None and grp.fused.out_features == sum(widths)
+    after = sum(backend.kernel_launches(w._b200_state) for w in ws)
+    assert after <= before - 2                                  # two GEMM launches fewer (at least)
+    M = 700
+    x = synth_activations(M, 384, torch.Generator().manual_seed(19)).reshape(1, M, 384).cuda()
+    ys = [w(x) for w in ws]
+    ops.check_status()
+    assert (grp.misses, grp.hits) == (1, 2) and grp.x_ref is None and grp.y_all is None
+    for y, w2, n in zip(ys, ws2, widths):
+        assert y.shape == (1, M, n)
+        assert torch.equal(y, w2(x))
+    # head split as the attention does it: a view of the strided columns
+    q = ys[0].view(1, -1, widths[0] // 64, 64).transpose(1, 2)
+    assert q.shape == (1, widths[0] // 64, M, 64)
+    # a group whose members see different tensors gives correct results and stops fusing
+    xs = [synth_activations(M, 384, torch.Generator().manual_seed(30 + i)).reshape(1, M, 384).cuda() for i in range(8)]
+    for i, xi in enumerate(xs):
+        w, w2 = ws[i % 3], ws2[i % 3]
+        assert torch.equal(w(xi), w2(xi))
+    assert grp.fused is None
+    ops.check_status()
