@@ -159,8 +159,11 @@ def kernel_launches(st: Optional[LayerState]) -> int:
         fold = not (st.shared is not None and st.member_id > 0)
         n += 1 if (fold or st.folded.panel is None) else 0
     follower = (st.shared is not None and st.member_id > 0) or st.chain_fed
-    if st.rot_t is None and st.layout.tail_total > 0 and not follower:
-        n += 1                              # quantise-only layers copy their passthrough channels in a kernel of its own
+    two_step = st.rot_t is not None and (st.perm_idx is not None or st.fmt.group_size <= 0) and st.fmt.num_heads == 0
+    if two_step and not follower:
+        n += 1                              # rotation into scratch, then the quantise kernel
+    if (st.rot_t is None or two_step) and st.layout.tail_total > 0 and not follower:
+        n += 1                              # the quantise kernel copies the passthrough channels in a launch of its own
     if st.hadamard_low_dim:
         n += 1
     return n
@@ -288,15 +291,35 @@ def _act_format(w) -> ops.ActFormat:
     per_head = w.rotation_per_head is not None and getattr(w, "_unrot_fused", False) and hlen > 0
     if per_head:
         if nvfp4:
-            raise NotImplementedError("per-head NVFP4 groups (head_dim - tail) are not multiples of 16: no "
-                                      "block-scaled tensor-core form; use INT4 for per-head layers")
+            # The reference quantises each head's d - tail coefficients as one E2M1 group
+            # (dirotq_fused_unrotation_fast.py:89-93).  The tensor cores scale blocks of 16: the heads' low
+            # coefficients are gathered in front (as the reference's rearrangement does, :94-99) and quantised in
+            # blocks of 16, which never straddle a head when d - tail is a multiple of 16.
+            H, d = int(w.num_heads), int(w.head_dim)
+            if (d - hlen) % 16:
+                raise NotImplementedError(f"per-head NVFP4 with head_dim - tail = {d - hlen}: not a multiple of the "
+                                          "16-element scale block of the FP4 tensor cores; use INT4 for this layer")
+            return ops.ActFormat(mode, D, tail_len=H * hlen, group_size=16, clip_ratio=float(q.clip_ratio),
+                                 tensor_scale=_HW_NVFP4_ACT_SCALE)
         return ops.ActFormat(mode, D, tail_len=hlen, num_heads=int(w.num_heads), head_dim=int(w.head_dim),
                              clip_ratio=float(q.clip_ratio))
     gs = int(q.groupsize)
     if gs <= 0:
-        raise NotImplementedError("per-token (groupsize <= 0) activation quantisation has no sm_100a kernel")
+        if nvfp4:
+            raise NotImplementedError("per-token NVFP4 (one bf16 scale per row, no block scales) has no block-scaled "
+                                      "tensor-core form; use groupsize=16")
+        gs = -1                         # per-token scales: ActQuantizer._find_params (utils/quant_utils.py:242-271)
     return ops.ActFormat(mode, D, tail_len=hlen, group_size=gs, clip_ratio=float(q.clip_ratio),
                          tensor_scale=_HW_NVFP4_ACT_SCALE)
+
+
+def _per_head_selection(w):
+    """(H, d, tail) for a per-head layer whose format is expressed as rotation + channel selection (NVFP4), else None."""
+    q = w.quantizer
+    if (q.quant_dtype == "nvfp4" and w.rotation_per_head is not None and getattr(w, "_unrot_fused", False)
+            and int(q.high_bits_length) > 0):
+        return int(w.num_heads), int(w.head_dim), int(q.high_bits_length)
+    return None
 
 
 # The forward watches the device status word without synchronising (ops.StatusWatch): a bounded device-side wait that
@@ -328,6 +351,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     "scales_e4m3" uint8 [N,n_low/16], "tensor_scale" float}; optional "w_tail" [N, tail_total]."""
     fmt = _act_format(w)
     lay = ops.act_layout(fmt)
+    ph_sel = _per_head_selection(w)
     fused = getattr(w, "_unrot_fused", False)
     N, D = w.module.out_features, w.module.in_features
     dev = torch.device(device)
@@ -344,6 +368,10 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     elif fused and w.rotation_per_head is not None:
         U = w.rotation_per_head.to(device=dev, dtype=torch.float32)
         rot_t = torch.block_diag(*[U[h].t() for h in range(U.shape[0])]).contiguous().to(torch.bfloat16)
+        if ph_sel is not None:
+            H, d, hl = ph_sel
+            cols = torch.arange(H * d, device=dev).reshape(H, d)
+            perm = torch.cat([cols[:, : d - hl].reshape(-1), cols[:, d - hl:].reshape(-1)]).to(torch.int64).contiguous()
     elif fused and not had_dim and getattr(w, "perm_idx", None) is not None:
         perm = w.perm_idx.to(device=dev, dtype=torch.int64).contiguous()
     packed = getattr(w, "_b200_packed", None)
@@ -369,8 +397,8 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     if not (have_codes and have_tail):
         # split the fused weight into the quantised block and the 16-bit tail (quant_utils.py:574-587, :659-685)
         Wf = w.module.weight.data.to(device=dev, dtype=torch.float32)
-        if fmt.num_heads > 0:
-            H, d, hl = fmt.num_heads, fmt.head_dim, fmt.tail_len
+        if fmt.num_heads > 0 or ph_sel is not None:
+            H, d, hl = ph_sel if ph_sel is not None else (fmt.num_heads, fmt.head_dim, fmt.tail_len)
             W3 = Wf.reshape(N, H, d)
             w_low = W3[:, :, : d - hl].reshape(N, H * (d - hl)).contiguous()
             w_tail = W3[:, :, d - hl:].reshape(N, H * hl).contiguous()

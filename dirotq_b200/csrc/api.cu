@@ -468,8 +468,13 @@ int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x
 }
 
 struct WsCarve {
-  size_t codes, scales, zeros, tail, fold, total;
+  size_t codes, scales, zeros, tail, xrot, fold, total;
 };
+// Layers whose quantiser cannot run in the rotation's epilogue -- a channel selection after the rotation, or one scale
+// per row -- rotate into a bf16 scratch tensor first and quantise from there.
+static bool rotates_then_quantises(const dirotq_linear* lin, const ActGeom& g) {
+  return lin->rot_t != nullptr && (lin->perm_idx != nullptr || g.per_token);
+}
 static bool uses_f16_gemm(const dirotq_linear* lin, const ActGeom& g) {
   return lin->w_mult != nullptr &&
          (g.mode == DIROTQ_INT4_SYM || g.mode == DIROTQ_INT4_ASYM || g.mode == DIROTQ_INT8_ASYM);
@@ -483,7 +488,9 @@ static int carve(const dirotq_linear* lin, int64_t M, ActGeom* g, WsCarve* w) {
   w->scales = w->codes + dirotq_act_codes_bytes(&l, M);
   w->zeros = w->scales + dirotq_act_scales_bytes(&lin->fmt, &l, M);
   w->tail = w->zeros + dirotq_act_zeros_bytes(&lin->fmt, &l, M);
-  w->fold = w->tail + (g->tail_total > 0 ? dirotq_act_tail_bytes(&l, M) : 0);
+  w->xrot = w->tail + (g->tail_total > 0 ? dirotq_act_tail_bytes(&l, M) : 0);
+  w->xrot = (w->xrot + 255) & ~size_t(255);
+  w->fold = w->xrot + (rotates_then_quantises(lin, *g) ? pad256((size_t)M * (size_t)g->D * 2) : 0);
   w->fold = (w->fold + 255) & ~size_t(255);
   w->total = w->fold;
   if (uses_f16_gemm(lin, *g))
@@ -520,7 +527,11 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
   void* zeros = is_asym(g.mode) ? ws + w.zeros : nullptr;
   void* tail = g.tail_total > 0 ? ws + w.tail : nullptr;
   if (stages & 1) {
-    if (lin->rot_t)
+    if (rotates_then_quantises(lin, g)) {
+      void* x_rot = ws + w.xrot;
+      rc = dirotq_rotate_quantize(&lin->fmt, x, lin->rot_t, M, x_rot, nullptr, nullptr, nullptr, nullptr, status, stream);
+      if (!rc) rc = dirotq_quantize_act(&lin->fmt, x_rot, g.D, lin->perm_idx, M, codes, scales, zeros, tail, stream);
+    } else if (lin->rot_t)
       rc = dirotq_rotate_quantize(&lin->fmt, x, lin->rot_t, M, nullptr, codes, scales, zeros, tail, status, stream);
     else
       rc = dirotq_quantize_act(&lin->fmt, x, g.D, lin->perm_idx, M, codes, scales, zeros, tail, stream);

@@ -27,6 +27,7 @@ struct ActGeom {
   int n_scales;
   float clip;
   float T;        // NVFP4_HW tensor scale
+  int per_token;  // integer modes, hidden layout: one scale (and zero point) per row, stored once per 64-chunk
 };
 
 inline bool is_nvfp4(int mode) { return mode == DIROTQ_NVFP4_REF || mode == DIROTQ_NVFP4_HW; }
@@ -38,6 +39,7 @@ inline int make_geom(const dirotq_act_format* f, ActGeom* g) {
   if (f->width <= 0 || f->width % 8 != 0 || f->tail_len < 0) return DIROTQ_E_ARG;
   g->mode = f->mode;
   g->D = f->width;
+  g->per_token = 0;
   g->H = f->num_heads;
   g->d = f->head_dim;
   g->hlen = f->tail_len;
@@ -57,7 +59,12 @@ inline int make_geom(const dirotq_act_format* f, ActGeom* g) {
     g->q_len = g->D - g->hlen;
     g->group = is_nvfp4(f->mode) ? 16 : f->group_size;
     if (is_nvfp4(f->mode) && f->group_size != 16) return DIROTQ_E_UNSUPPORTED;
-    if (g->group <= 0) return DIROTQ_E_UNSUPPORTED;
+    if (g->group <= 0) {
+      // per-token scales (ActQuantizer with groupsize <= 0, utils/quant_utils.py:236-240, :242-271): the codes keep
+      // the 64-slot chunk layout the GEMMs read and every chunk of a row carries the row's scale
+      g->per_token = 1;
+      g->group = 64;
+    }
     g->n_groups = ceil_div(g->q_len, g->group);
     g->tail_total = g->hlen;
   }

@@ -196,6 +196,45 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   }
 }
 
+// Per-token scales: one CTA per row.  Pass 1: extrema of the quantised channels, zero included
+// (utils/quant_utils.py:246-249 starts the reduction from a zero tensor); pass 2: codes in the chunk layout, the row's
+// scale and zero point repeated for every chunk.  The row (a few KB) is read twice; the second read hits L1 / L2.
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_int_token_kernel(const QuantArgs a) {
+  const ActGeom& g = a.g;
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* xr = a.x + row * a.x_pitch;
+  float mx = 0.f, mn = 0.f;
+  for (int c = threadIdx.x; c < g.q_len; c += blockDim.x) {
+    const float f = __bfloat162float(xr[a.perm ? a.perm[c] : c]);
+    mx = fmaxf(mx, f);
+    mn = fminf(mn, f);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  }
+  __shared__ float s_mx[8], s_mn[8];
+  if ((threadIdx.x & 31) == 0) { s_mx[threadIdx.x >> 5] = mx; s_mn[threadIdx.x >> 5] = mn; }
+  __syncthreads();
+  mx = s_mx[0];
+  mn = s_mn[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) { mx = fmaxf(mx, s_mx[i]); mn = fminf(mn, s_mn[i]); }
+  constexpr float maxq = (MODE == MODE_INT4_SYM) ? 7.f : (MODE == MODE_INT4_ASYM ? 15.f : 255.f);
+  GroupParams p;
+  if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
+  else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+  for (int b = threadIdx.x; b < g.n_chunks * 2; b += blockDim.x) {
+    const int nvalid = max(0, min(32, g.q_len - b * 32));
+    quant_int_block_slow<MODE>(a.x, a.x_pitch, a.perm, a.codes, g.code_row_bytes, p.scale, p.zero, nvalid, b * 32, row, b);
+  }
+  for (int chunk = threadIdx.x; chunk < g.n_chunks; chunk += blockDim.x) {
+    a.scales[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.scale);
+    if constexpr (MODE != MODE_INT4_SYM) a.zeros[(int64_t)chunk * a.ldm + row] = __float2bfloat16_rn(p.zero);
+  }
+}
+
 // One thread = one 64-slot chunk (4 groups of 16) of one row; hidden layout only.
 template <int MODE>
 __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const QuantArgs a) {
@@ -352,6 +391,11 @@ int launch_quantize(const QuantArgs& a, cudaStream_t st) {
     unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (g.mode == DIROTQ_NVFP4_REF) quant_nvfp4_kernel<MODE_NVFP4_REF><<<blocks, threads, 0, st>>>(a);
     else quant_nvfp4_kernel<MODE_NVFP4_HW><<<blocks, threads, 0, st>>>(a);
+  } else if (g.per_token) {
+    if (a.M > 0x7fffffff) return DIROTQ_E_TOO_LARGE;
+    if (g.mode == DIROTQ_INT4_SYM) quant_int_token_kernel<MODE_INT4_SYM><<<(unsigned)a.M, threads, 0, st>>>(a);
+    else if (g.mode == DIROTQ_INT4_ASYM) quant_int_token_kernel<MODE_INT4_ASYM><<<(unsigned)a.M, threads, 0, st>>>(a);
+    else quant_int_token_kernel<MODE_INT8_ASYM><<<(unsigned)a.M, threads, 0, st>>>(a);
   } else {
     int64_t total = a.M * g.n_chunks * 2;
     unsigned blocks = (unsigned)((total + threads - 1) / threads);

@@ -774,6 +774,7 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
     if (((g.group + 31) / 32) * 32 > g.d) return DIROTQ_E_UNSUPPORTED;
   }
   if (!rot_only && g.H == 0 && !is_nvfp4(g.mode) && g.group != 64) return DIROTQ_E_UNSUPPORTED;
+  if (!rot_only && g.per_token) return DIROTQ_E_UNSUPPORTED;     // a row's scale needs the whole rotated row: rotate, then quantise
   CUtensorMap tx, tu;
   int rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)g.D, (uint64_t)M, (uint64_t)g.D * 2, 128);
   if (rc) return rc;

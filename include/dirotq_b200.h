@@ -52,7 +52,14 @@ typedef struct dirotq_act_format {
   int32_t num_heads;    /* 0: hidden layout [low | tail]; H > 0: per-head layout */
   int32_t head_dim;     /* d (per-head only; H * d == D) */
   int32_t tail_len;     /* high_bits_length: hidden = total, per-head = per head */
-  int32_t group_size;   /* hidden: 64 (INT) or 16 (NVFP4); per-head: ignored, group = d - tail_len */
+  int32_t group_size;   /* hidden: 64 (INT) or 16 (NVFP4); per-head: ignored, group = d - tail_len.
+                         * <= 0 (integer modes, hidden layout): ONE scale / zero point per row over the quantised
+                         * channels, zero included in the extrema (ActQuantizer._find_params,
+                         * utils/quant_utils.py:242-271); codes keep the 64-slot chunk layout and the row's scale
+                         * is stored for every chunk, so the GEMMs read it like any other format.  The fused
+                         * rotate + quantise kernel cannot produce it (a row spans several column tiles):
+                         * dirotq_rotate_quantize returns DIROTQ_E_UNSUPPORTED with codes != NULL, and
+                         * dirotq_linear_forward rotates into scratch and quantises from there. */
   float clip_ratio;     /* ActQuantizer.clip_ratio */
   float tensor_scale;   /* DIROTQ_NVFP4_HW only: fp32 per-tensor scale T (> 0) */
 } dirotq_act_format;
@@ -252,7 +259,10 @@ typedef struct dirotq_linear {
   dirotq_act_format fmt;
   int64_t out_features;
   const void* rot_t;        /* NULL: no rotation (quantise only) */
-  const int64_t* perm_idx;  /* optional, only when rot_t == NULL */
+  const int64_t* perm_idx;  /* optional channel selection x[..., perm_idx].  With rot_t == NULL it is applied to the input
+                             * (dirotq_fused_unrotation_fast.py:130-134); with rot_t != NULL to the ROTATED tensor
+                             * (two launches: rotate into scratch, then gather + quantise) -- how a per-head
+                             * rotation meets a format whose groups are not one per head. */
   const void* w_codes;
   const void* w_scales;     /* INT: fp32 [n_chunks, ldn]; NVFP4: tiled UE4M3 */
   const float* w_sum;       /* INT only */

@@ -113,14 +113,22 @@ def act_quant_int(x: torch.Tensor, cfg: QuantCfg) -> ActQuantResult:
     All arithmetic runs in ``x.dtype`` exactly as torch evaluates the reference
     expressions (bf16 ops round after every operation).
     """
-    assert x.dim() == 3 and cfg.groupsize > 0 and cfg.quant_dtype == "int"
+    assert x.dim() == 3 and cfg.quant_dtype == "int"
     hlen = cfg.high_bits_length
     q_len = x.shape[-1] - hlen
     x_l, x_h = x[..., :q_len], x[..., q_len:]
-    xg = _group(x_l, cfg.groupsize)
     maxq = torch.tensor(cfg.maxq)           # 0-dim int64, does not promote
-    xmax = torch.amax(xg, dim=-1, keepdim=True) * cfg.clip_ratio
-    xmin = torch.amin(xg, dim=-1, keepdim=True) * cfg.clip_ratio
+    if cfg.groupsize > 0:
+        xg = _group(x_l, cfg.groupsize)
+        xmax = torch.amax(xg, dim=-1, keepdim=True) * cfg.clip_ratio
+        xmin = torch.amin(xg, dim=-1, keepdim=True) * cfg.clip_ratio
+    else:
+        # per-token scales (quant_utils.py:236-240 -> _find_params :242-271): one group = the whole quantised
+        # region of a row; the extrema start from zero (:248-249)
+        xg = x_l.reshape(x.shape[0], x.shape[1], 1, q_len)
+        zero_ref = torch.zeros((), dtype=x.dtype)
+        xmax = torch.maximum(torch.amax(xg, dim=-1, keepdim=True), zero_ref) * cfg.clip_ratio
+        xmin = torch.minimum(torch.amin(xg, dim=-1, keepdim=True), zero_ref) * cfg.clip_ratio
     if cfg.sym:
         xmax = torch.maximum(torch.abs(xmin), xmax)
         tmp = xmax == 0

@@ -54,7 +54,7 @@ def main(ref_root):
             x[..., 3] = x[..., 3] * 9.0
         return x.to(torch.bfloat16)
 
-    def build(D, N, seed, *, rotation=None, rph=None, H=None, d=None, cfg=None, weight_mode="int"):
+    def build(D, N, seed, *, rotation=None, rph=None, H=None, d=None, cfg=None, weight_mode="int", w_groupsize=None):
         torch.manual_seed(seed)
         lin = nn.Linear(D, N, bias=True).to(torch.bfloat16)
         w = qu.ActQuantWrapper(lin)
@@ -65,10 +65,11 @@ def main(ref_root):
             w.rotation_per_head = rph
             w.num_heads, w.head_dim = H, d
         holder = nn.ModuleDict({"l": w})
+        wg = cfg["groupsize"] if w_groupsize is None else w_groupsize
         if weight_mode == "int":
-            qu.rtn_quantize_weights(holder, bits=4, groupsize=cfg["groupsize"], sym=True)
+            qu.rtn_quantize_weights(holder, bits=4, groupsize=wg, sym=True)
         else:
-            qu.nvfp4_rtn_quantize_weights(holder, groupsize=cfg["groupsize"])
+            qu.nvfp4_rtn_quantize_weights(holder, groupsize=wg)
         assert w._unrot_fused
         return w
 
@@ -121,11 +122,11 @@ def main(ref_root):
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **to_np(out))
         print("wrote", name, {k: tuple(v.shape) for k, v in out.items() if hasattr(v, "shape")})
 
-    only_had = os.environ.get("GOLDEN_ONLY") == "hadamard"     # add the Hadamard fixtures without rewriting the others
-    _run_case = run_case
-    if only_had:
+    # GOLDEN_ONLY=hadamard | pertoken: add those fixtures without rewriting the others
+    only = os.environ.get("GOLDEN_ONLY")
+    _run_case, build_saved = run_case, build
+    if only:
         run_case = lambda *a, **k: None
-        build_saved = build
         build = lambda *a, **k: None
     # 1. hidden rotation, INT4 symmetric g64, k=64 passthrough
     D, N = 192, 96
@@ -164,6 +165,8 @@ def main(ref_root):
     # Hadamard layers (use_hadamard: FWHT over the first low_dim channels with sign flips, the rest untouched)
     from utils.hadamard_utils import generate_sign_flips, fast_hadamard_transform
     for name, D, low_dim, hl, seed in (("hadamard_int4_sym", 320, 256, 64, 9), ("hadamard_int4_sym_n128", 192, 128, 64, 10)):
+        if only not in (None, "hadamard"):
+            break
         cfg = dict(bits=4, groupsize=64, sym=True, high_bits_length=hl, quant_dtype="int")
         torch.manual_seed(seed)
         lin = nn.Linear(D, N, bias=True).to(torch.bfloat16)
@@ -192,7 +195,22 @@ def main(ref_root):
             out["y_slow"] = slow._fused_forward(w, x)
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **to_np(out))
         print("wrote", name, {k: tuple(v.shape) for k, v in out.items() if hasattr(v, "shape")})
-    if os.environ.get("GOLDEN_ONLY") == "hadamard":
+    if only in (None, "pertoken"):
+        # per-token activation scales (groupsize <= 0: ActQuantizer._find_params), weights in groups of 64; q_len = 128
+        # and (no tail) q_len = 160, whose last 64-chunk is half padding
+        for name, D, hl, sym, seed in (("hidden_int4_sym_pertoken", 192, 64, True, 18), ("hidden_int4_asym_pertoken", 192, 64, False, 19),
+                                       ("hidden_int4_asym_pertoken_pad", 160, 0, False, 20)):
+            cfg = dict(bits=4, groupsize=-1, sym=sym, high_bits_length=hl, quant_dtype="int")
+            _run_case(name, build_saved(D, N, seed, rotation=orth(D, 40 + seed), cfg=cfg, w_groupsize=64), acts(2, 24, D, 50 + seed))
+        # per-head rotation with NVFP4 activations (FLUX to_out family: 16 of d channels per head in 16 bits);
+        # the reference quantises each head's d - 16 coefficients as one E2M1 group with an unrounded scale
+        H, d = 4, 64
+        torch.manual_seed(21)
+        rph = torch.stack([random_orthogonal_matrix(d, device="cpu").float() for _ in range(H)])
+        cfg = dict(bits=4, groupsize=16, sym=True, high_bits_length=16, quant_dtype="nvfp4")
+        _run_case("perhead_nvfp4", build_saved(H * d, N, 22, rph=rph, H=H, d=d, cfg=cfg, weight_mode="nvfp4"),
+                  acts(2, 24, H * d, 62))
+    if only:
         return
 
     # 7. quantiser-only adversarial inputs (already "rotated"): exact .5 ties after the

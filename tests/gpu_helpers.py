@@ -47,7 +47,8 @@ def oracle_cfg(fmt: ops.ActFormat, lay: ops.ActLayout) -> O.QuantCfg:
     if fmt.mode in (ops.NVFP4_REF, ops.NVFP4_HW):
         return O.QuantCfg(4, 16, True, fmt.clip_ratio, lay.tail_total, "nvfp4")
     bits = 8 if fmt.mode == ops.INT8_ASYM else 4
-    return O.QuantCfg(bits, lay.group, fmt.mode == ops.INT4_SYM, fmt.clip_ratio, lay.tail_total, "int")
+    group = -1 if (fmt.num_heads == 0 and fmt.group_size <= 0) else lay.group      # per-token scales
+    return O.QuantCfg(bits, group, fmt.mode == ops.INT4_SYM, fmt.clip_ratio, lay.tail_total, "int")
 
 
 def to_reference_layout(x_rot2d: torch.Tensor, fmt: ops.ActFormat) -> torch.Tensor:

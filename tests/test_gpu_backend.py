@@ -83,6 +83,77 @@ def test_forward_matches_reference_int(name):
         assert rel_l2(yc, g["y_slow"].float()) <= max(REL, 1.5 * gap), name
 
 
+@pytest.mark.parametrize("name", ["hidden_int4_sym_pertoken", "hidden_int4_asym_pertoken", "hidden_int4_asym_pertoken_pad"])
+def test_per_token_activation_scales(name):
+    """groupsize <= 0: one scale (and zero point) per token (ActQuantizer._find_params, utils/quant_utils.py:242-271).
+    The layer rotates into scratch and quantises from there; codes, scale and zero point are bit-exact against the
+    reference quantiser applied to the rotated tensor the kernel produced, the output within the layer tolerance."""
+    from dirotq_b200 import backend, ops
+    from gpu_helpers import decode_act, oracle_cfg
+    g = load_golden(name)
+    w = _wrapper_from_golden(g)
+    holder = nn.ModuleDict({"l": w})
+    assert backend.preconvert_rotations_to_device(holder, "cuda") == 1
+    st = w._b200_state
+    assert st.fmt.group_size <= 0 and st.n_lossy_groups == 0
+    y = w(g["x"].cuda())
+    ops.check_status()
+    yc = y.float().cpu()
+    x2d = g["x"].reshape(-1, g["x"].shape[-1]).cuda()
+    M = x2d.shape[0]
+    x_rot = ops.rotate(x2d, st.rot_t)
+    with pytest.raises(RuntimeError):                       # the fused kernel cannot see a whole row
+        ops.rotate_quantize(x2d, st.rot_t, st.fmt)
+    buf = ops.quantize_act(x_rot, st.fmt)
+    d = decode_act(buf)
+    cfg = oracle_cfg(st.fmt, st.layout)
+    assert cfg.groupsize == -1
+    r = O.act_quant(x_rot.cpu().unsqueeze(0), cfg)
+    q_len = st.layout.q_len
+    assert torch.equal(d["codes_padded"].reshape(M, -1)[:, :q_len], r.codes.reshape(M, q_len))
+    assert not d["codes_padded"].reshape(M, -1)[:, q_len:].any() or not cfg.sym   # symmetric padding slots hold code 0
+    want_s = r.scale.reshape(M, 1).expand(M, st.layout.n_chunks).contiguous()
+    assert torch.equal(d["scale_chunks"].view(torch.int16), want_s.view(torch.int16))
+    if not cfg.sym:
+        want_z = r.zero.reshape(M, 1).expand(M, st.layout.n_chunks).contiguous()
+        assert torch.equal(d["zero"].view(torch.int16), want_z.view(torch.int16))
+    if st.layout.tail_total:
+        assert torch.equal(d["tail"].view(torch.int16), r.tail.reshape(M, -1).contiguous().view(torch.int16))
+    y_same = torch.nn.functional.linear(r.full.to(torch.bfloat16), g["weight"], g["bias"]).float().reshape(yc.shape)
+    assert rel_l2(yc, y_same) <= REL and cosine(yc, y_same) >= COS
+    gap = rel_l2(g["y_fast"].float(), g["y_slow"].float())
+    assert rel_l2(yc, g["y_fast"].float()) <= max(REL, 1.5 * gap) and cosine(yc, g["y_fast"].float()) >= 0.995
+    # the allocation-free entry point sizes the extra scratch from the same layout
+    assert torch.equal(backend.linear_forward_static(st, x2d), y.reshape(M, -1))
+
+
+def test_per_head_rotation_with_nvfp4_activations():
+    """Per-head rotation + NVFP4 (head_dim - tail a multiple of 16): block-diagonal rotation into scratch, then the
+    heads' low coefficients gathered in front and quantised in blocks of 16.  Bit contract: the hardware-recipe oracle
+    on the gathered tensor; against the reference (one unrounded scale per head group) the layer is pinned by QSNR."""
+    from dirotq_b200 import backend, ops
+    g = load_golden("perhead_nvfp4")
+    w = _wrapper_from_golden(g)
+    y = w(g["x"].cuda()).float().cpu()
+    ops.check_status()
+    st = w._b200_state
+    H, d, hl = 4, 64, 16
+    assert st.fmt.num_heads == 0 and st.perm_idx is not None and st.layout.tail_total == H * hl
+    x2d = g["x"].reshape(-1, H * d).cuda()
+    x_rot = ops.rotate(x2d, st.rot_t).cpu()
+    xre = O.per_head_rearrange(x_rot.reshape(-1, H, d), hl).reshape(g["x"].shape)     # [H * (d - hl) | H * hl]
+    assert torch.equal(xre.reshape(-1, H * d), x_rot[:, st.perm_idx.cpu()])
+    W3 = g["weight"].float().reshape(-1, H, d)
+    W_re = torch.cat([W3[:, :, : d - hl].reshape(-1, H * (d - hl)), W3[:, :, d - hl:].reshape(-1, H * hl)], 1).to(torch.bfloat16)
+    spec = O.LayerSpec(W_re, g["bias"], O.QuantCfg(4, 16, True, 1.0, H * hl, "nvfp4"))
+    y_hw = O.fused_forward_nvfp4_hw(xre, spec, st.fmt.tensor_scale, x_rot=xre)
+    assert rel_l2(y, y_hw) <= 5e-3 and cosine(y, y_hw) >= 0.9999
+    y_fp = torch.nn.functional.linear(xre.float(), W_re.float(), g["bias"].float())
+    q_ref, q_ours = O.qsnr_db(y_fp, g["y_fast"].float()), O.qsnr_db(y_fp, y)
+    print(f"perhead_nvfp4: QSNR reference fake-quant {q_ref:.2f} dB, B200 NVFP4 {q_ours:.2f} dB")
+    assert q_ours >= q_ref - 0.5
+
+
 def test_forward_nvfp4_against_hw_oracle_and_reference():
     """The tensor-core format needs UE4M3 group scales, which the reference's activation quantiser does not have.
     Bit contract: the hw oracle (two-level recipe on the activations, the reference's own two-level weight recipe

@@ -5,8 +5,9 @@ import torch
 from conftest import bits_equal, load_golden, rel_l2
 from oracle import dirotq_oracle as O
 
-HIDDEN = ["hidden_int4_sym", "hidden_int4_asym", "hidden_int4_pad_notail", "hidden_int8_asym", "hidden_nvfp4"]
-PERHEAD = ["perhead_int4_sym", "perhead_int4_asym", "perhead_d32_int4_sym"]
+HIDDEN = ["hidden_int4_sym", "hidden_int4_asym", "hidden_int4_pad_notail", "hidden_int8_asym", "hidden_nvfp4",
+          "hidden_int4_sym_pertoken", "hidden_int4_asym_pertoken", "hidden_int4_asym_pertoken_pad"]
+PERHEAD = ["perhead_int4_sym", "perhead_int4_asym", "perhead_d32_int4_sym", "perhead_nvfp4"]
 HADAMARD = ["hadamard_int4_sym", "hadamard_int4_sym_n128"]
 
 
@@ -28,9 +29,9 @@ def test_fast_path_bit_exact(name):
     assert bits_equal(x_rot, g["x_rot_fast"])
     assert bits_equal(r.full, g["xq_fast"])
     if "scale_fast" in g:
-        assert bits_equal(r.scale, g["scale_fast"])
+        assert bits_equal(r.scale.reshape(g["scale_fast"].shape), g["scale_fast"])
         if not spec.cfg.sym:
-            assert bits_equal(r.zero, g["zero_fast"])
+            assert bits_equal(r.zero.reshape(g["zero_fast"].shape), g["zero_fast"])
     assert bits_equal(O.fused_forward(g["x"], spec, fp32=False), g["y_fast"])
 
 
