@@ -2,7 +2,7 @@
 """Benchmark of the DiRotQ quantized-linear path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W]
-                    [--workload pixart_int4|pixart_nvfp4|flux_int4|sana_int4|sana_w4a8] [--flux-ffn tp|dp]
+                    [--workload pixart_int4|pixart_nvfp4|flux_int4|flux_nvfp4|sana_int4|sana_w4a8] [--flux-ffn tp|dp]
     python bench.py --impl reference ...      # the reference's own fp32 CPU forward on a bounded sample
 
 One "step" = every wrapped linear of one denoising step of the named DiT (BASELINE config 1 by default: PixArt-Sigma
@@ -45,6 +45,9 @@ WORKLOADS = {
                   "BASELINE config 3: FLUX.1-dev-shaped step, 19 double-stream (image 4096 + text 512 tokens) + 38 "
                   "single-stream blocks, INT W4A4 g64 k=384, per-head out-projections, K=12288 down-projections "
                   "without rotation, global batch 4"),
+    "flux_nvfp4": ("flux_double_block", 57, "nvfp4", 4608, 4, "flux",
+                   "FLUX.1-dev-shaped step as config 3, in NVFP4 W4A4 (E2M1 g16, UE4M3 group scales; per-head "
+                   "out-projections stay INT4), K=12288 down-projections without rotation, global batch 4"),
 }
 
 
@@ -769,22 +772,29 @@ def roofline_pass_flux(step, x_dev, dev):
             ops.rotate_quantize(x_dev, st.rot_t, st.fmt, out=buf)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            pw = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks,
-                                      st.w_codes, st.w_scales, st.w_sum)
-            if f16_ws is None:
-                f16_ws = torch.empty(ops.f16_workspace_bytes(buf, st.out_features), dtype=torch.uint8, device=dev)
-            ops.gemm_w4a4_int_f16(buf, pw, st.folded, st.bias, workspace=f16_ws)
+            if st.fmt.mode == ops.NVFP4_HW:
+                pw = ops.PackedWeightNvfp4(st.out_features, st.layout.q_len, st.layout.n_chunks, st.w_tensor_scale,
+                                           st.w_codes, st.w_scales, st.w_rowscale)
+                ops.gemm_w4a4_nvfp4(buf, pw, st.w_tail, st.bias)
+            else:
+                pw = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks,
+                                          st.w_codes, st.w_scales, st.w_sum)
+                if f16_ws is None:
+                    f16_ws = torch.empty(ops.f16_workspace_bytes(buf, st.out_features), dtype=torch.uint8, device=dev)
+                ops.gemm_w4a4_int_f16(buf, pw, st.folded, st.bias, workspace=f16_ws)
             e1.record()
             pairs.append((e0, e1))
             ops_total += 2.0 * M * 3072 * 3072
     torch.cuda.synchronize()
     t_ms = sum(a.elapsed_time(b) for a, b in pairs)
     achieved = ops_total / (t_ms * 1e-3) / 1e12
-    peak, peak_src = tensor_peak("f16")
-    return {"bound": "tensor", "kernel": "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)",
+    nvfp4 = st.fmt.mode == ops.NVFP4_HW
+    peak, peak_src = tensor_peak("nvfp4" if nvfp4 else "f16")
+    return {"bound": "tensor", "kernel": ("gemm_nvfp4_pair_kernel (CTA pairs)" if nvfp4 else
+                                          "gemm_int_f16_kernel (with its fold_expand_kernel or expand_weight_panel_kernel)"),
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
             "launches_timed": len(pairs), "avg_launch_us": t_ms * 1e3 / max(1, len(pairs)), "traffic": None,
-            "traffic_estimated": {"bytes_per_launch": NCU_TRAFFIC_RATIO * gemm_algorithmic_bytes(M, 3072, st.layout, "int4"),
+            "traffic_estimated": {"bytes_per_launch": NCU_TRAFFIC_RATIO * gemm_algorithmic_bytes(M, 3072, st.layout, "nvfp4" if nvfp4 else "int4"),
                                   "how": f"NOT a measurement of this run: algorithmic bytes x {NCU_TRAFFIC_RATIO} (ratio of one ncu "
                                          "capture of the INT4 GEMM at M=16384, N=K=1152)"}}
 

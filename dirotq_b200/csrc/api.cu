@@ -5,6 +5,7 @@
 #include "launchers.cuh"
 
 #include <atomic>
+#include <cstring>
 
 using namespace dq;
 
@@ -324,6 +325,8 @@ struct QuantOut {
   int row_bytes;
   int mode;
   float clip;
+  float T;            // NVFP4 consumer: its activation tensor scale
+  int n_kb64_pad;     // NVFP4 consumer: 64-column blocks per row of its scale-factor tile array
 };
 
 // skip_fold != 0: the workspace already holds the activation records and the scaled tail of these codes
@@ -428,8 +431,8 @@ static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const vo
                                 const void* w_codes, const void* w_sf, float out_scale, const float* w_colscale,
                                 const void* x_tail,
                                 const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
-                                void* y, int act, int32_t* status, void* stream) {
-  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_sf || !w_codes || !w_sf || !y) return DIROTQ_E_ARG;
+                                void* y, int act, int32_t* status, void* stream, const QuantOut* qo = nullptr) {
+  if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_sf || !w_codes || !w_sf || (!y && !qo)) return DIROTQ_E_ARG;
   if (N % 8 != 0) return DIROTQ_E_UNSUPPORTED;
   if (tail_total < 0 || (tail_total > 0 && (!x_tail || !w_tail_scaled || tail_pitch < tail_total || tail_pitch % 8))) return DIROTQ_E_ARG;
   const uintptr_t al = reinterpret_cast<uintptr_t>(x_sf) | reinterpret_cast<uintptr_t>(w_sf) | reinterpret_cast<uintptr_t>(y) |
@@ -456,6 +459,17 @@ static int gemm_w4a4_nvfp4_impl(int64_t M, int64_t N, int32_t n_chunks, const vo
   a.status = status;
   a.wait_limit_k = wait_limit_k();
   a.act = act;
+  if (qo) {
+    a.q_codes = static_cast<uint8_t*>(qo->codes);
+    a.q_sf = static_cast<uint8_t*>(qo->scales);
+    a.q_len = qo->q_len;
+    a.q_tail = static_cast<__nv_bfloat16*>(qo->tail);
+    a.q_tail_pitch = qo->tail_pitch;
+    a.q_row_bytes = qo->row_bytes;
+    a.q_n_kb64_pad = qo->n_kb64_pad;
+    a.q_clip = qo->clip;
+    a.q_T = qo->T;
+  }
   return launch_gemm_nvfp4(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -506,6 +520,14 @@ size_t dirotq_linear_workspace_bytes(const dirotq_linear* lin, int64_t M) {
   return w.total;
 }
 
+// Which producers can quantise in their epilogue, and for which consumer format: the 16-bit-conversion integer GEMM
+// for 4-bit integer consumers, the block-scaled FP4 GEMM for NVFP4 consumers.
+static bool produces_epilogue_codes(const dirotq_linear* lin, const ActGeom& g, int consumer_mode) {
+  if (g.mode == DIROTQ_NVFP4_HW) return consumer_mode == DIROTQ_NVFP4_HW;
+  if (!uses_f16_gemm(lin, g) || g.mode == DIROTQ_INT8_ASYM) return false;
+  return consumer_mode == DIROTQ_INT4_SYM || consumer_mode == DIROTQ_INT4_ASYM;
+}
+
 // stages: 1 = rotate / quantise into the workspace, 2 = GEMM from the workspace, 3 = both; 4 (with 2) = the
 // workspace holds codes, scales and zero points written by someone else (a producer's epilogue): the per-call
 // folding of the scales, normally part of stage 1's bookkeeping, runs before the GEMM.
@@ -538,11 +560,11 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
     if (rc) return rc;
   }
   if (!(stages & 2)) return DIROTQ_OK;
-  if (qo && !(uses_f16_gemm(lin, g) && g.mode != DIROTQ_INT8_ASYM)) return DIROTQ_E_UNSUPPORTED;
+  if (qo && !produces_epilogue_codes(lin, g, qo->mode)) return DIROTQ_E_UNSUPPORTED;
   if (g.mode == DIROTQ_NVFP4_HW)
     return gemm_w4a4_nvfp4_impl(M, lin->out_features, g.n_chunks, codes, scales, lin->w_codes, lin->w_scales,
                                 lin->fmt.tensor_scale * lin->w_tensor_scale, lin->w_colscale, tail, lin->w_tail, g.tail_total,
-                                g.tail_pitch, lin->bias, y, lin->epilogue_act, status, stream);
+                                g.tail_pitch, lin->bias, y, lin->epilogue_act, status, stream, qo);
   if (lin->epilogue_act < 0 || lin->epilogue_act > 1) return DIROTQ_E_ARG;
   if (uses_f16_gemm(lin, g)) {
     if (!lin->w_colscale || (g.tail_total > 0 && !lin->w_tail_f16)) return DIROTQ_E_ARG;
@@ -574,9 +596,15 @@ int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* works
 // step reads the scales back).
 static int next_takes_epilogue_codes(const dirotq_linear* lin, const dirotq_linear* next, const ActGeom& gn) {
   if (next->rot_t || next->perm_idx) return 0;
-  if (gn.mode != DIROTQ_INT4_SYM && gn.mode != DIROTQ_INT4_ASYM) return 0;
-  if (gn.H != 0 || gn.group != 64 || gn.q_len % 64 != 0 || gn.tail_total % 64 != 0) return 0;
+  if (gn.H != 0 || gn.per_token || gn.q_len % 64 != 0 || gn.tail_total % 64 != 0) return 0;
   if (gn.D != lin->out_features) return 0;
+  if (gn.mode == DIROTQ_NVFP4_HW) {
+    uint32_t u;
+    memcpy(&u, &gn.T, 4);
+    return (u & 0x7FFFFFu) == 0u ? 1 : 0;            // the packed quantiser needs a power-of-two tensor scale
+  }
+  if (gn.mode != DIROTQ_INT4_SYM && gn.mode != DIROTQ_INT4_ASYM) return 0;
+  if (gn.group != 64) return 0;
   return uses_f16_gemm(next, gn) ? 1 : 0;
 }
 
@@ -584,7 +612,7 @@ int dirotq_linear_chain_supported(const dirotq_linear* lin, const dirotq_linear*
   if (!lin || !next) return 0;
   ActGeom g, gn;
   if (make_geom(&lin->fmt, &g) || make_geom(&next->fmt, &gn)) return 0;
-  if (!uses_f16_gemm(lin, g) || g.mode == DIROTQ_INT8_ASYM) return 0;
+  if (!produces_epilogue_codes(lin, g, gn.mode)) return 0;
   return next_takes_epilogue_codes(lin, next, gn);
 }
 
@@ -611,6 +639,8 @@ int dirotq_linear_forward_chain(const dirotq_linear* lin, const void* x, int64_t
   qo.row_bytes = gn.code_row_bytes;
   qo.mode = gn.mode;
   qo.clip = gn.clip;
+  qo.T = gn.T;
+  qo.n_kb64_pad = (gn.n_chunks + 3) & ~3;
   return linear_stages(lin, x, M, y, workspace, workspace_bytes, 3, status, stream, &qo);
 }
 

@@ -288,6 +288,8 @@ int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.n_chunks <= 0) return DIROTQ_E_ARG;
   if (const int bn = pick_nvfp4_tile(a)) return launch_gemm_nvfp4_pair(a, bn, st);
+  if (a.q_codes) return launch_gemm_nvfp4_pair(a, 128, st);          // quantise-out lives in the CTA-pair kernels
+  if (!a.y) return DIROTQ_E_ARG;
   CUtensorMap txq, twq, txt, twt, ty;
   if (a.N % 8) return DIROTQ_E_UNSUPPORTED;
   const uint64_t row_bytes = (uint64_t)a.n_chunks * 32;

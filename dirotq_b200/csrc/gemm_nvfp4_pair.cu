@@ -28,6 +28,8 @@
 //
 // Replaces `self.module(x)` of the fused forward (DiRotQ dirotq_fused_unrotation_fast.py:141) for
 // quant_dtype == "nvfp4"; the reference's speed path uses nunchaku's FP4 gemm_w4a4 here.
+#include <cstring>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -36,6 +38,7 @@
 #include "ptx.cuh"
 #include "ptx_pair.cuh"
 #include "tma_host.cuh"
+#include "quant_math.cuh"
 
 namespace dq {
 
@@ -73,7 +76,9 @@ struct GfRingT {
   __device__ __forceinline__ void next() { if (++s == STAGES) { s = 0; ph ^= 1; } }
 };
 
-template <int BN>
+// QOUT: the epilogue also quantises its output for a following NVFP4 layer (GemmFp4Args::q_codes).  A separate
+// instantiation, so that the registers this costs do not weigh on the plain kernel.
+template <int BN, bool QOUT>
 __global__ void __launch_bounds__(GpCfg<BN>::THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_constant__ CUtensorMap tm_wq,
                        const __grid_constant__ CUtensorMap tm_xsf, const __grid_constant__ CUtensorMap tm_wsf,
@@ -318,6 +323,71 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_c
       }
       // bf16 results leave through 32 x 32 staging patches (64-byte rows, 64-byte swizzle; two per warp, used in turn)
       // and TMA stores, which clip at the edges of y
+      if constexpr (QOUT) {
+        // ---- quantise-out: every 64 columns are one scale-factor word (four blocks of 16) of the following layer ----
+        const int64_t row = (int64_t)row0 + lane;
+#pragma unroll
+        for (int c = 0; c < WCOLS / 64; ++c) {
+          const int64_t col0 = n0 + 64 * c;
+          if (col0 + 64 > a.N || row0 >= a.M) continue;  // warp-uniform
+          uint32_t w[32];                                // the activated output as bf16 pairs: what that layer's quantiser reads
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float4 sb = *reinterpret_cast<const float4*>(tab + 64 * c + 2 * i);
+            float f0 = __fmaf_rn(__uint_as_float(v[64 * c + 2 * i]), sb.x, sb.y);
+            float f1 = __fmaf_rn(__uint_as_float(v[64 * c + 2 * i + 1]), sb.z, sb.w);
+            if (a.act == 1) { f0 = gelu_tanh_bf16(f0); f1 = gelu_tanh_bf16(f1); }
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(f0, f1);
+            w[i] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          if (a.y != nullptr) {                          // the bf16 tensor as well, when the caller wants it
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+              const uint32_t sp = stg + (patch & 1u) * 2048;
+              ++patch;
+              if (lane == 0) bulk_wait_read1();
+              __syncwarp();
+#pragma unroll
+              for (int i4 = 0; i4 < 4; ++i4)
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                             ::"r"(sp + lane * 64 + (uint32_t)((i4 ^ ((lane >> 1) & 3)) << 4)), "r"(w[16 * p + 4 * i4]),
+                               "r"(w[16 * p + 4 * i4 + 1]), "r"(w[16 * p + 4 * i4 + 2]), "r"(w[16 * p + 4 * i4 + 3])
+                             : "memory");
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tm_y, sp, (int)col0 + 32 * p, row0);
+                bulk_commit_group();
+              }
+            }
+          }
+          if (row >= a.M) continue;
+          if (col0 >= a.q_len) {                         // that layer's 16-bit channels
+            uint4* t = reinterpret_cast<uint4*>(a.q_tail + row * a.q_tail_pitch + (col0 - a.q_len));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            continue;
+          }
+          uint32_t packed[8];
+          uint32_t sfw = 0;
+#pragma unroll
+          for (int gi = 0; gi < 4; ++gi) {
+            float eff;
+            const uint8_t sbyte = nvfp4_hw_scale(amax_bf16x16(w + 8 * gi), a.q_clip, a.q_T, &eff);
+            uint2 cc = make_uint2(0u, 0u);
+            if (eff > 0.f) cc = nvfp4_hw_group_packed(w + 8 * gi, eff);
+            packed[2 * gi] = cc.x;
+            packed[2 * gi + 1] = cc.y;
+            sfw |= (uint32_t)sbyte << (8 * gi);
+          }
+          const int chunk = (int)(col0 >> 6);
+          uint4* dst = reinterpret_cast<uint4*>(a.q_codes + row * a.q_row_bytes + (int64_t)chunk * 32);
+          dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          *reinterpret_cast<uint32_t*>(a.q_sf + sf_offset(row, chunk * 4, a.q_n_kb64_pad)) = sfw;
+        }
+      }
+      if constexpr (!QOUT) {
 #pragma unroll
       for (int p = 0; p < WCOLS / 32; ++p) {
         const int64_t pcol = n0 + 32 * p;
@@ -350,6 +420,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_c
           bulk_commit_group();
         }
       }
+      }
       if (NACC == 2) {
         buf ^= 1;
         if (buf == 0) aph ^= 1;
@@ -369,7 +440,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tm_xq, const __grid_c
   }
 }
 
-template <int BN>
+static bool nvfp4_pow2_tensor_scale_host(float T) {
+  uint32_t u;
+  memcpy(&u, &T, 4);
+  return T > 0.f && (u & 0x7FFFFFu) == 0u;
+}
+
+template <int BN, bool QOUT>
 static int launch_pair(const GemmFp4Args& a, cudaStream_t st) {
   using Cfg = GpCfg<BN>;
   CUtensorMap txq, twq, txsf, twsf, txt, twt, ty;
@@ -384,7 +461,9 @@ static int launch_pair(const GemmFp4Args& a, cudaStream_t st) {
   if (rc) return rc;
   rc = make_tmap_2d_sw(&twsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.wsf, 128, (uint64_t)((a.N + 127) / 128) * nkb_pad, 512, 128, 4, 0);
   if (rc) return rc;
-  rc = make_tmap_2d_sw(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2, 32, 32, 64);
+  // without an output tensor (quantise-out only) the map is never used: any valid address will do
+  rc = make_tmap_2d_sw(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y ? (const void*)a.y : (const void*)a.wq, (uint64_t)a.N,
+                       (uint64_t)a.M, (uint64_t)a.N * 2, 32, 32, 64);
   if (rc) return rc;
   if (a.kt > 0) {
     rc = make_tmap_2d(&txt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.xt, (uint64_t)a.kt, (uint64_t)a.M, (uint64_t)a.kt_pitch * 2, 128);
@@ -395,7 +474,7 @@ static int launch_pair(const GemmFp4Args& a, cudaStream_t st) {
     txt = txq;
     twt = twq;
   }
-  auto k = gemm_nvfp4_pair_kernel<BN>;
+  auto k = gemm_nvfp4_pair_kernel<BN, QOUT>;
   static PerDeviceOnce attr_once;
   if (int rc2 = set_max_dynamic_smem(attr_once, k, Cfg::SMEM_BYTES)) return rc2;
   const int tiles = (int)((a.M + 255) / 256) * (int)((a.N + BN - 1) / BN);
@@ -433,7 +512,23 @@ int launch_gemm_nvfp4_pair(const GemmFp4Args& a, int bn, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.n_chunks <= 0) return DIROTQ_E_ARG;
   if (a.N % 8) return DIROTQ_E_UNSUPPORTED;
-  return bn == 256 ? launch_pair<256>(a, st) : launch_pair<128>(a, st);
+  if (a.q_codes) {
+    if (a.N % 64 || a.q_len % 64 || a.q_len <= 0 || a.q_len > a.N || a.q_row_bytes < a.q_len / 2 || (a.q_row_bytes & 15) ||
+        !a.q_sf || (reinterpret_cast<uintptr_t>(a.q_codes) & 15) || (reinterpret_cast<uintptr_t>(a.q_sf) & 15) ||
+        a.q_n_kb64_pad * 64 < a.q_len || (a.q_n_kb64_pad & 3) || !nvfp4_pow2_tensor_scale_host(a.q_T) ||
+        (a.q_len < a.N && (!a.q_tail || a.q_tail_pitch < a.N - a.q_len || (a.q_tail_pitch & 7) ||
+                           (reinterpret_cast<uintptr_t>(a.q_tail) & 15))))
+      return DIROTQ_E_ARG;
+  } else if (!a.y) {
+    return DIROTQ_E_ARG;
+  }
+  if (a.q_codes) {
+    // DIROTQ_NVFP4_QOUT_TILE=128 forces the narrower tile (measurements)
+    const char* e = getenv("DIROTQ_NVFP4_QOUT_TILE");
+    if (e && !strcmp(e, "128")) bn = 128;
+    return bn == 256 ? launch_pair<256, true>(a, st) : launch_pair<128, true>(a, st);
+  }
+  return bn == 256 ? launch_pair<256, false>(a, st) : launch_pair<128, false>(a, st);
 }
 
 }  // namespace dq

@@ -186,6 +186,19 @@ struct GemmFp4Args {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y;
   int* status;
+  // Optional (CTA-pair kernels): the epilogue also quantises its activated, bf16-rounded output rows for a following
+  // un-rotated NVFP4 layer of width N (power-of-two tensor scale) -- E2M1 codes, UE4M3 block scales in their tile
+  // layout, the layer's trailing 16-bit channels -- so that its quantise kernel and a round trip of the [M, N] tensor
+  // disappear; y may then be null.
+  uint8_t* q_codes = nullptr;        // [M, q_row_bytes]
+  uint8_t* q_sf = nullptr;           // tiled UE4M3 (pad entries stay as the owner zeroed them)
+  int64_t q_len = 0;                 // quantised columns (multiple of 64); columns beyond go to q_tail as bf16
+  __nv_bfloat16* q_tail = nullptr;   // [M, q_tail_pitch]
+  int q_tail_pitch = 0;
+  int q_row_bytes = 0;
+  int q_n_kb64_pad = 0;              // 64-column blocks per row of the scale-factor tile array (rounded up to 4)
+  float q_clip = 1.f;
+  float q_T = 1.f;
 };
 
 int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
