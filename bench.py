@@ -558,7 +558,7 @@ def _time_call(fn, n=20, warm=3):
 
 
 def sub_nvfp4_flux_gemms(dev):
-    """The NVFP4 W4A4 GEMM alone on the two FLUX linear shapes at M = 16384 (batch 4 x 4096 image tokens), k = 384
+    """The NVFP4 W4A4 GEMM alone on the three FLUX linear shapes at M = 16384 (batch 4 x 4096 image tokens), k = 384
     bf16 coefficients: CUDA events around 20 back-to-back launches, operands resident, 3 warm-ups.  Fraction against
     dense FP4 = 4 x the measured bf16 sustained figure (derived)."""
     from dirotq_b200 import ops
@@ -581,6 +581,24 @@ def sub_nvfp4_flux_gemms(dev):
                               "tflops_4bit_part_only": tf4,
                               "note": "tflops counts 2*M*N*D over the whole call; one eighth of K runs as bf16 UMMAs at a "
                                       "quarter of the FP4 rate in the same kernel"})
+    # the K = 12288 down-projection of the speed path: no rotation, no 16-bit branch (dirotq_b200.dit.flux_double_block with
+    # tail 0, as parallel.FluxLinearStep and denoise.py build it)
+    D2, N2 = 12288, 3072
+    x2 = torch.randn(M, D2, generator=g, device=dev).to(torch.bfloat16)
+    fmt2 = ops.ActFormat(ops.NVFP4_HW, D2, tail_len=0, group_size=16)
+    act2 = ops.quantize_act(x2, fmt2)
+    pk2 = ops.pack_weight_nvfp4(torch.randn(N2, D2, generator=g, device=dev) * 0.05, 2.0 ** -12)
+    bias2 = torch.randn(N2, generator=g, device=dev).to(torch.bfloat16)
+    ms = _time_call(lambda: ops.gemm_w4a4_nvfp4(act2, pk2, None, bias2))
+    tf = 2.0 * M * N2 * D2 / (ms * 1e-3) / 1e12
+    out["layers"].append({"shape": f"{D2}->{N2}", "M": M, "k_bf16": 0, "us": ms * 1e3, "tflops": tf, "frac_of_fp4_peak": tf / peak,
+                          "tflops_4bit_part_only": tf, "note": "un-rotated down-projection: all of K is 4-bit"})
+    # one FLUX block's linears: q, k, v, out (3072 -> 3072 each), up, down
+    us = {l["shape"]: l["us"] for l in out["layers"]}
+    t_block = 4 * us["3072->3072"] + us["3072->12288"] + us["12288->3072"]
+    f_block = 2.0 * M * (4 * 3072 * 3072 + 2 * 3072 * 12288)
+    out["flux_block_linears"] = {"us": t_block, "tflops": f_block / t_block / 1e6, "frac_of_fp4_peak": f_block / t_block / 1e6 / peak,
+                                 "note": "GEMM time of the six linears of one FLUX block (four 3072 -> 3072, up, down) at M = 16384"}
     ops.check_status(dev)
     return out
 

@@ -141,13 +141,13 @@ class LayerState:
         return ws
 
 
-def kernel_launches(st: Optional[LayerState]) -> int:
+def kernel_launches(st: Optional[LayerState], w4a16=None) -> int:
     """Library kernels one forward of a wrapped linear launches.  A W4A16 layer (no LayerState): weight
     dequantisation + GEMM.  W4A4: rotate/quantise + GEMM; the tensor-rate integer GEMM adds one preparation launch
     (scale folding and, unless the layer keeps a resident panel, the weight-panel pre-pass); a sibling that reuses the
     activations of the layer before it runs only its own GEMM (and pre-pass)."""
     if st is None:
-        return 2
+        return 1 if (w4a16 is not None and w4a16.dense is not None) else 2    # resident dequantised weight: GEMM only
     if st.shared is not None and st.shared.fused is not None:
         return kernel_launches(st.shared.fused) if st.member_id == 0 else 0     # one pass and one GEMM for the group
     n = 1 if (st.shared is not None and st.member_id > 0) else 2
@@ -458,7 +458,38 @@ class W4A16State:
     WeightOnlyNVFP4Linear (speedup/weight_only_nvfp4.py:128-178)."""
     w: object                       # ops.PackedWeightInt4 or ops.PackedWeightNvfp4
     bias: Optional[torch.Tensor]
-    scratch: torch.Tensor
+    dense: Optional[torch.Tensor] = None      # resident dequantised weight (bf16 [N, K]), see w4a16_forward
+
+
+# Dequantised weights of W4A16 layers follow the policy of CACHE_WEIGHT_PANEL: resident (2 bytes per weight) for layers
+# called with at most PANEL_CACHE_MAX_ROWS rows, where the dequantisation is a visible share of the call; otherwise
+# rebuilt on every call in ONE scratch buffer per device and stream, shared by all layers (stream order keeps it safe).
+_W4A16_SCRATCH: Dict[tuple, torch.Tensor] = {}
+
+
+def _w4a16_scratch(nbytes: int, device) -> torch.Tensor:
+    key = (torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _W4A16_SCRATCH.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _W4A16_SCRATCH[key] = buf
+    return buf
+
+
+def w4a16_forward(s16: W4A16State, x2d: torch.Tensor) -> torch.Tensor:
+    """bf16 activations x 4-bit weight: x2d bf16 [M, K] -> bf16 [M, N]."""
+    M = x2d.shape[0]
+    nvfp4 = isinstance(s16.w, ops.PackedWeightNvfp4)
+    resident = CACHE_WEIGHT_PANEL is True or (CACHE_WEIGHT_PANEL == "auto" and M <= PANEL_CACHE_MAX_ROWS)
+    if resident or s16.dense is not None:
+        if s16.dense is None:
+            s16.dense = ops.dequant_weight_nvfp4(s16.w) if nvfp4 else ops.dequant_weight_int4(s16.w)
+        return ops.gemm_bf16(x2d, s16.dense, s16.bias)
+    K = s16.w.n_chunks * 64
+    scratch = _w4a16_scratch(int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(s16.w.N, K)), x2d.device)
+    if nvfp4:
+        return ops.gemm_w4a16_nvfp4(x2d, s16.w, s16.bias, workspace=scratch)
+    return ops.gemm_w4a16(x2d, s16.w, s16.bias, workspace=scratch)
 
 
 def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int = 64) -> Optional[W4A16State]:
@@ -477,8 +508,7 @@ def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int 
                                        t(packed.get("row_scale")))
         else:
             pk = ops.PackedWeightInt4(N, K, 64, K // 64, t(packed["codes"]), t(packed["scales"]), t(packed["wsum"]))
-        n = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(N, K))
-        return W4A16State(pk, t(packed["bias"]), torch.empty(n, dtype=torch.uint8, device=dev))
+        return W4A16State(pk, t(packed["bias"]))
     if explicit and "nibbles" in explicit:
         pk = pack.convert_dirotq_low_weight_to_b200_fp4(None, explicit["tensor_scale"], explicit["nibbles"],
                                                         explicit["scales_e4m3"])
@@ -494,8 +524,7 @@ def prepare_w4a16(w, device="cuda", explicit: Optional[dict] = None, group: int 
         pk = ops.pack_weight_int4(W, 64, scales=rec.scales.to(dev))
         bias = w.module.bias.data if w.module.bias is not None else None
     bias = None if bias is None else bias.to(device=dev, dtype=torch.bfloat16).contiguous()
-    n = int(_lib.lib().dirotq_gemm_w4a16_workspace_bytes(N, K))
-    return W4A16State(pk, bias, torch.empty(n, dtype=torch.uint8, device=dev))
+    return W4A16State(pk, bias)
 
 
 def _fused_forward_b200(self, x):
@@ -509,10 +538,7 @@ def _fused_forward_b200(self, x):
             return self.module(x).to(x.dtype)
         shp = x.shape
         x2d = x.reshape(-1, shp[-1]).to(torch.bfloat16).contiguous()
-        if isinstance(s16.w, ops.PackedWeightNvfp4):
-            y = ops.gemm_w4a16_nvfp4(x2d, s16.w, s16.bias, workspace=s16.scratch)
-        else:
-            y = ops.gemm_w4a16(x2d, s16.w, s16.bias, workspace=s16.scratch)
+        y = w4a16_forward(s16, x2d)
         return y.reshape(*shp[:-1], s16.w.N).to(x.dtype)
     st = getattr(self, "_b200_state", None)
     if st is None:

@@ -392,7 +392,7 @@ class DenoiseStep(nn.Module):
 
     def kernel_launches_per_step(self) -> int:
         from . import backend
-        return sum(backend.kernel_launches(getattr(w, "_b200_state", None)) for w in self.wrapped())
+        return sum(backend.kernel_launches(getattr(w, "_b200_state", None), getattr(w, "_b200_w4a16", None)) for w in self.wrapped())
 
 
 def time_wrapped_linears(step: nn.Module, inputs, classes=(ActQuantWrapper,)) -> float:

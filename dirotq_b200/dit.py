@@ -219,7 +219,7 @@ class LinearPathStep(nn.Module):
         """Library kernels per step: rotate/quantise (or weight dequantise) + GEMM per linear, plus the
         scale-folding kernel of the tensor-rate INT4 GEMM where a layer uses it."""
         from . import backend
-        return sum(backend.kernel_launches(getattr(lyr, "_b200_state", None)) for lyr in self.layers)
+        return sum(backend.kernel_launches(getattr(lyr, "_b200_state", None), getattr(lyr, "_b200_w4a16", None)) for lyr in self.layers)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = x

@@ -431,6 +431,31 @@ def dequant_weight_nvfp4(w: "PackedWeightNvfp4") -> torch.Tensor:
     return out
 
 
+def dequant_weight_int4(w: PackedWeightInt4) -> torch.Tensor:
+    """bf16 [N, K] weight of a packed INT4 group-64 layer (K = n_chunks * 64), one rounding per value."""
+    assert w.group == 64
+    K = w.n_chunks * 64
+    out = torch.empty(w.N, K, dtype=torch.bfloat16, device=w.codes.device)
+    check(_lib.lib().dirotq_dequant_weight_int4(w.N, K, _ptr(w.codes), _ptr(w.scales), _ptr(out), _stream()),
+          "dirotq_dequant_weight_int4")
+    return out
+
+
+def gemm_bf16(x2d: torch.Tensor, w_dense: torch.Tensor, bias: Optional[torch.Tensor],
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w^T + bias on the bf16 tensor cores (the GEMM half of the W4A16 layers, on a resident dequantised weight)."""
+    assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
+    assert w_dense.dtype == torch.bfloat16 and w_dense.is_contiguous() and w_dense.shape[1] == x2d.shape[1]
+    M, K = x2d.shape
+    N = w_dense.shape[0]
+    y = out if out is not None else torch.empty(M, N, dtype=torch.bfloat16, device=x2d.device)
+    check(_lib.lib().dirotq_gemm_bf16(M, N, K, _ptr(x2d), _ptr(w_dense), _ptr(bias), _ptr(y), _ptr(status_word(x2d.device)),
+                                      _stream()), "dirotq_gemm_bf16")
+    if out is not None:
+        mark_written(out)
+    return y
+
+
 def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tensor],
                workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """W4A16 linear: bf16 x [M, K] times INT4 group-64 weights (dequantised into scratch, then tcgen05 bf16 GEMM)."""

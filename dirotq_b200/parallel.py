@@ -222,7 +222,7 @@ class FluxLinearStep:
 
     def kernel_launches_per_step(self) -> int:
         from . import backend
-        return sum(backend.kernel_launches(getattr(l, "_b200_state", None)) for l in self._flat)
+        return sum(backend.kernel_launches(getattr(l, "_b200_state", None), getattr(l, "_b200_w4a16", None)) for l in self._flat)
 
     def rows_per_rank(self, stream: str) -> int:
         return self.rows[stream] // self.world

@@ -238,6 +238,16 @@ size_t dirotq_gemm_w4a16_workspace_bytes(int64_t N, int64_t K);
 int dirotq_gemm_w4a16(int64_t M, int64_t N, int64_t K, const void* x, const void* w_codes, const float* w_scales,
                       const void* bias, void* y, void* workspace, size_t workspace_bytes, int32_t* status,
                       void* stream);
+
+/* The two halves of dirotq_gemm_w4a16 / dirotq_gemm_w4a16_nvfp4 on their own, for callers that keep the dequantised
+ * weight (N * K * 2 bytes) resident instead of rebuilding it on every call -- worth it when the batch is small and the
+ * dequantisation is a visible share of the layer (a 4096-row call of PixArt's 4608 -> 1152 ff.net.2: 13 of 58 us).
+ *   dirotq_dequant_weight_int4: w_out bf16 [N, K] = code * scale, K = n_chunks * 64, one rounding per value (what
+ *   WeightOnlyNVFP4Linear.dequant does for its format, speedup/weight_only_nvfp4.py:162-171).
+ *   dirotq_gemm_bf16: y = x @ w^T + bias on the bf16 tensor cores; x [M, K], w [N, K] (K-major), y [M, N]. */
+int dirotq_dequant_weight_int4(int64_t N, int64_t K, const void* w_codes, const float* w_scales, void* w_out, void* stream);
+int dirotq_gemm_bf16(int64_t M, int64_t N, int64_t K, const void* x, const void* w, const void* bias, void* y,
+                     int32_t* status, void* stream);
 /* Same with an NVFP4 weight: the forward of the reference's WeightOnlyNVFP4Linear
  * (speedup/weight_only_nvfp4.py:128-178).  Codes / tiled UE4M3 scales from either NVFP4 packer; the second-level
  * scale is w_rowscale (fp32 [N], from dirotq_pack_weight_nvfp4_rowscale: the reference's per-channel gscale) when
