@@ -192,3 +192,63 @@ def test_sibling_grouping_needs_equal_rotations_and_formats():
     assert sb[0].shared is sb[1].shared and sb[2].shared is None and sb[0].shared.n_members == 2
     sc = [m._b200_state for m in root.c.children()]
     assert sc[0].shared is sc[2].shared and sc[1].shared is None
+
+
+def _linear_c(fmt, out_features, rot=False, perm=False, w_mult=True):
+    """A dirotq_linear with dummy (never dereferenced) pointers: enough for the host-side checks of the C ABI."""
+    from dirotq_b200._lib import LinearC
+    p = lambda on: C.c_void_p(0x1000 if on else 0)
+    return LinearC(fmt.c(), out_features, p(rot), p(perm), p(True), p(True), p(True), p(True), p(False), 1.0,
+                   p(w_mult), p(True), p(True), 0, p(False))
+
+
+def test_per_token_layout_and_two_step_workspace():
+    """groupsize <= 0: chunks of 64 code slots, one scale slot per chunk; a rotated per-token layer (and a rotated layer
+    with a channel selection) asks for M * D * 2 more workspace bytes: the rotation's scratch."""
+    from dirotq_b200 import _lib, ops
+    tok = ops.ActFormat(ops.INT4_ASYM, 1152, 64, group_size=-1)
+    g64 = ops.ActFormat(ops.INT4_ASYM, 1152, 64, group_size=64)
+    lt, lg = ops.act_layout(tok), ops.act_layout(g64)
+    assert (lt.q_len, lt.group, lt.n_chunks, lt.n_scales, lt.code_row_bytes) == (lg.q_len, 64, lg.n_chunks, lg.n_scales, lg.code_row_bytes)
+    l = ops.act_layout(ops.ActFormat(ops.INT4_SYM, 160, 0, group_size=0))
+    assert (l.q_len, l.n_chunks, l.k_pad) == (160, 3, 192)
+    with pytest.raises(RuntimeError):
+        ops.act_layout(ops.ActFormat(ops.NVFP4_HW, 1152, 64, group_size=-1))      # no block-scaled per-token form
+    L = _lib.lib()
+    M = 1000
+    ws = lambda lin: int(L.dirotq_linear_workspace_bytes(C.byref(lin), M))
+    base = ws(_linear_c(g64, 1152, rot=True))
+    assert ws(_linear_c(tok, 1152, rot=True)) >= base + M * 1152 * 2
+    assert ws(_linear_c(g64, 1152, rot=True, perm=True)) >= base + M * 1152 * 2
+    assert ws(_linear_c(tok, 1152, rot=False)) == ws(_linear_c(g64, 1152, rot=False))
+
+
+def test_chain_support_matrix():
+    """Which producer / consumer pairs the epilogue hand-off accepts (dirotq_linear_chain_supported); refusals of
+    dirotq_linear_forward_chain come back before anything is launched."""
+    from dirotq_b200 import _lib, ops
+    L = _lib.lib()
+    ok = lambda a, b: bool(L.dirotq_linear_chain_supported(C.byref(a), C.byref(b)))
+    up = _linear_c(ops.ActFormat(ops.INT4_SYM, 3072, 384), 12288, rot=True)
+    down = lambda **kw: _linear_c(ops.ActFormat(kw.pop("mode", ops.INT4_SYM), 12288, kw.pop("tail", 0), group_size=kw.pop("gs", 64)),
+                                  3072, **kw)
+    assert ok(up, down()) and ok(up, down(tail=1536)) and ok(up, down(mode=ops.INT4_ASYM))
+    assert not ok(up, down(rot=True))                       # a rotation mixes the whole row
+    assert not ok(up, down(perm=True))
+    assert not ok(up, down(tail=1000))                      # tail not a multiple of 64
+    assert not ok(up, down(gs=-1))                          # per-token scale needs the whole row
+    assert not ok(up, down(mode=ops.INT8_ASYM))
+    assert not ok(up, down(w_mult=False))                   # consumer on the exact-integer GEMM: no folding step
+    assert not ok(_linear_c(ops.ActFormat(ops.INT4_SYM, 3072, 384), 12288, rot=True, w_mult=False), down())
+    assert not ok(up, _linear_c(ops.ActFormat(ops.INT4_SYM, 6144, 0), 3072))          # width != producer's out_features
+    fp4 = lambda D, N, tail, **kw: _linear_c(ops.ActFormat(ops.NVFP4_HW, D, tail, group_size=16, tensor_scale=kw.pop("T", 1.0)),
+                                            N, w_mult=False, **kw)
+    assert ok(fp4(3072, 12288, 384, rot=True), fp4(12288, 3072, 0))
+    assert ok(fp4(3072, 12288, 384, rot=True), fp4(12288, 3072, 1536, T=0.5))
+    assert not ok(fp4(3072, 12288, 384, rot=True), fp4(12288, 3072, 0, T=0.75))       # packed quantiser: power-of-two scale
+    assert not ok(fp4(3072, 12288, 384, rot=True), down())                            # formats do not mix
+    assert not ok(up, fp4(12288, 3072, 0))
+    bad = _linear_c(ops.ActFormat(ops.INT4_SYM, 12288, 0), 3072, rot=True)
+    rc = L.dirotq_linear_forward_chain(C.byref(up), C.c_void_p(0x1000), 128, None, C.c_void_p(0x1000), 1 << 30, C.byref(bad),
+                                       C.c_void_p(0x1000), 1 << 30, None, None)
+    assert rc == -2 and b"not supported" in L.dirotq_error_string(rc)
