@@ -71,6 +71,9 @@ def parse():
     ap.add_argument("--no-sub", action="store_true", help="skip the sub-records and the model-shaped step")
     ap.add_argument("--no-fuse-gelu", action="store_true",
                     help="keep the GELU between the FFN linears as a separate PyTorch kernel")
+    ap.add_argument("--no-fused-glue", action="store_true",
+                    help="denoise_step: keep modulated LayerNorm, gated residuals and q/k RMSNorm + rotary embedding as "
+                         "chains of PyTorch elementwise kernels instead of the library's single-pass kernels")
     ap.add_argument("--no-fuse-qkv", action="store_true",
                     help="keep to_q / to_k / to_v (and add_*_proj) as three GEMMs on the shared codes instead of one GEMM "
                          "on concatenated weights")
@@ -517,6 +520,7 @@ def denoise_record(D_, family, quant, gbatch, world, strong, args):
     batch = gbatch // world if strong else gbatch
     if batch < 1:
         return {"skipped": f"global batch {gbatch} does not split over {world} GPUs"}
+    denoise.FUSED_GLUE = not args.no_fused_glue
     step = denoise.DenoiseStep(family, quant, dev, n_blocks=n_blocks, seed=5000 + 7919 * D_.rank, prepare=True)
     n_fused = 0 if (args.no_fuse_gelu or args.exact_int) else backend.fuse_gelu_modules(step)
     n_chained = 0 if args.no_fuse_ffn else backend.fuse_ffn_quantise(step, keep_hidden=False)
@@ -535,8 +539,11 @@ def denoise_record(D_, family, quant, gbatch, world, strong, args):
            "linear_tflops_inside_step": D_.world * lin / (lin_ms * 1e-3) / 1e12 if lin_ms > 0 else None,
            "gelu_fused_layers": n_fused, "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
            "launches_per_step": step.kernel_launches_per_step(),
-           "glue": "PyTorch bf16: adaLN modulation, LayerNorm / RMSNorm, rotary embedding, scaled_dot_product_attention "
-                   "(SANA: ReLU linear attention, Mix-FFN convolutions), residuals",
+           "glue": ("library single-pass kernels (csrc/glue.cu): modulated LayerNorm, gated residuals, q / k RMSNorm + rotary "
+                    "embedding into joint token-major buffers; PyTorch: scaled_dot_product_attention, modulation projections "
+                    "(SANA: ReLU linear attention, Mix-FFN convolutions)" if denoise.FUSED_GLUE else
+                    "PyTorch bf16: adaLN modulation, LayerNorm / RMSNorm, rotary embedding, scaled_dot_product_attention "
+                    "(SANA: ReLU linear attention, Mix-FFN convolutions), residuals"),
            "timing": "CUDA events, 3 warm-up + 4 timed steps, max over ranks; wrapped_linears_ms = events around every "
                      "wrapped-linear call of one further step"}
     del step, inputs

@@ -27,6 +27,27 @@ from .dit import GeluProj, LayerDef, linear_ops, make_wrapped_linear, rotation_o
 from .wrapper import ActQuantWrapper
 
 
+# The row-wise passes between the wrapped linears (modulated LayerNorm, gated residuals, q / k RMSNorm + rotary embedding)
+# run as single-pass kernels of the library (csrc/glue.cu) by default; False keeps them as chains of PyTorch elementwise
+# kernels, the form the reference's model forwards have (speedup/report_flux_w4a4_no_rot_ffdown.py:199-252).
+FUSED_GLUE = True
+
+
+def _ln_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
+    if FUSED_GLUE and x.is_cuda:
+        from . import ops
+        return ops.layernorm_modulate(x.contiguous(), scale, shift)
+    return F.layer_norm(x, (x.shape[-1],), eps=1e-6) * (1 + scale) + shift
+
+
+def _gated(h: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None):
+    if FUSED_GLUE and h.is_cuda:
+        from . import ops
+        return ops.gated_residual(h.contiguous(), y, gate, y2)
+    y = y if y2 is None else y + y2
+    return h + (y if gate is None else gate * y)
+
+
 def _heads(x: torch.Tensor, h: int) -> torch.Tensor:
     B, T, C = x.shape
     return x.view(B, T, h, C // h).transpose(1, 2)
@@ -110,17 +131,17 @@ class PixArtBlock(nn.Module, _Census):
         """h [B, T, D] image tokens, enc [B, S, D] projected text tokens, temb [B, 6 D] adaLN-single embedding."""
         B, _, D = h.shape
         sh_a, sc_a, g_a, sh_m, sc_m, g_m = (self.scale_shift_table[None] + temb.reshape(B, 6, D)).chunk(6, dim=1)
-        n = F.layer_norm(h, (D,), eps=1e-6) * (1 + sc_a) + sh_a
+        n = _ln_mod(h, sc_a, sh_a)
         a = self.attn1
         o = F.scaled_dot_product_attention(_heads(a.to_q(n), self.heads), _heads(a.to_k(n), self.heads),
                                            _heads(a.to_v(n), self.heads))
-        h = h + g_a * a.to_out[0](_merge(o))
+        h = _gated(h, a.to_out[0](_merge(o)), g_a)
         c = self.attn2                                       # ada_norm_single: no norm in front of the cross-attention
         o = F.scaled_dot_product_attention(_heads(c.to_q(h), self.heads), _heads(c.to_k(enc), self.heads),
                                            _heads(c.to_v(enc), self.heads))
-        h = h + c.to_out[0](_merge(o))
-        n = F.layer_norm(h, (D,), eps=1e-6) * (1 + sc_m) + sh_m
-        return h + g_m * self.ff.net[2](self.ff.net[0](n))
+        h = _gated(h, c.to_out[0](_merge(o)))
+        n = _ln_mod(h, sc_m, sh_m)
+        return _gated(h, self.ff.net[2](self.ff.net[0](n)), g_m)
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -187,19 +208,30 @@ class FluxDoubleBlock(nn.Module, _Census):
         D, H, a = self.dim, self.heads, self.attn
         mi = self.norm1(F.silu(temb))[:, None].chunk(6, dim=-1)
         mt = self.norm1_context(F.silu(temb))[:, None].chunk(6, dim=-1)
-        ni = F.layer_norm(img, (D,), eps=1e-6) * (1 + mi[1]) + mi[0]
-        nt = F.layer_norm(txt, (D,), eps=1e-6) * (1 + mt[1]) + mt[0]
-        q = torch.cat([_rms(_heads(a.add_q_proj(nt), H), a.norm_added_q), _rms(_heads(a.to_q(ni), H), a.norm_q)], dim=2)
-        kk = torch.cat([_rms(_heads(a.add_k_proj(nt), H), a.norm_added_k), _rms(_heads(a.to_k(ni), H), a.norm_k)], dim=2)
-        v = torch.cat([_heads(a.add_v_proj(nt), H), _heads(a.to_v(ni), H)], dim=2)
-        o = _merge(F.scaled_dot_product_attention(_rope(q, cos, sin), _rope(kk, cos, sin), v))
+        ni = _ln_mod(img, mi[1], mi[0])
+        nt = _ln_mod(txt, mt[1], mt[0])
         S = txt.shape[1]
-        txt = txt + mt[2] * a.to_add_out(o[:, :S])
-        img = img + mi[2] * a.to_out[0](o[:, S:])
-        ni = F.layer_norm(img, (D,), eps=1e-6) * (1 + mi[4]) + mi[3]
-        nt = F.layer_norm(txt, (D,), eps=1e-6) * (1 + mt[4]) + mt[3]
-        img = img + mi[5] * self.ff.net[2](self.ff.net[0](ni))
-        txt = txt + mt[5] * self.ff_context.net[2](self.ff_context.net[0](nt))
+        if FUSED_GLUE and img.is_cuda:
+            # text rows then image rows of q / k / v, normalised and rotated, straight into token-major buffers: no
+            # concatenation, and the attention output comes back in the layout the out-projections read
+            from . import ops
+            B, T = img.shape[0], img.shape[1]
+            bufs = tuple(torch.empty(B, S + T, H, D // H, dtype=img.dtype, device=img.device) for _ in range(3))
+            ops.qkv_norm_rope(a.add_q_proj(nt), a.add_k_proj(nt), a.add_v_proj(nt), H, a.norm_added_q, a.norm_added_k,
+                              cos, sin, out=bufs, t0=0)
+            ops.qkv_norm_rope(a.to_q(ni), a.to_k(ni), a.to_v(ni), H, a.norm_q, a.norm_k, cos, sin, out=bufs, t0=S)
+            o = _merge(F.scaled_dot_product_attention(*(t.transpose(1, 2) for t in bufs)))
+        else:
+            q = torch.cat([_rms(_heads(a.add_q_proj(nt), H), a.norm_added_q), _rms(_heads(a.to_q(ni), H), a.norm_q)], dim=2)
+            kk = torch.cat([_rms(_heads(a.add_k_proj(nt), H), a.norm_added_k), _rms(_heads(a.to_k(ni), H), a.norm_k)], dim=2)
+            v = torch.cat([_heads(a.add_v_proj(nt), H), _heads(a.to_v(ni), H)], dim=2)
+            o = _merge(F.scaled_dot_product_attention(_rope(q, cos, sin), _rope(kk, cos, sin), v))
+        txt = _gated(txt, a.to_add_out(o[:, :S]), mt[2])
+        img = _gated(img, a.to_out[0](o[:, S:]), mi[2])
+        ni = _ln_mod(img, mi[4], mi[3])
+        nt = _ln_mod(txt, mt[4], mt[3])
+        img = _gated(img, self.ff.net[2](self.ff.net[0](ni)), mi[5])
+        txt = _gated(txt, self.ff_context.net[2](self.ff_context.net[0](nt)), mt[5])
         return img, txt
 
 
@@ -233,10 +265,15 @@ class FluxSingleBlock(nn.Module, _Census):
     def forward(self, x: torch.Tensor, temb: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         D, H, a = self.dim, self.heads, self.attn
         shift, scale, gate = self.norm(F.silu(temb))[:, None].chunk(3, dim=-1)
-        n = F.layer_norm(x, (D,), eps=1e-6) * (1 + scale) + shift
-        q, kk, v = _rms(_heads(a.to_q(n), H), a.norm_q), _rms(_heads(a.to_k(n), H), a.norm_k), _heads(a.to_v(n), H)
-        o = _merge(F.scaled_dot_product_attention(_rope(q, cos, sin), _rope(kk, cos, sin), v))
-        return x + gate * (self.proj_out.linears[0](o) + self.proj_out.linears[1](self.proj_mlp_act(n)))
+        n = _ln_mod(x, scale, shift)
+        if FUSED_GLUE and x.is_cuda:
+            from . import ops
+            q, kk, v = ops.qkv_norm_rope(a.to_q(n), a.to_k(n), a.to_v(n), H, a.norm_q, a.norm_k, cos, sin)
+            o = _merge(F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), v.transpose(1, 2)))
+        else:
+            q, kk, v = _rms(_heads(a.to_q(n), H), a.norm_q), _rms(_heads(a.to_k(n), H), a.norm_k), _heads(a.to_v(n), H)
+            o = _merge(F.scaled_dot_product_attention(_rope(q, cos, sin), _rope(kk, cos, sin), v))
+        return _gated(x, self.proj_out.linears[0](o), gate, self.proj_out.linears[1](self.proj_mlp_act(n)))
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -284,17 +321,17 @@ class SanaBlock(nn.Module, _Census):
     def forward(self, h: torch.Tensor, enc: torch.Tensor, temb: torch.Tensor) -> torch.Tensor:
         B, T, D = h.shape
         sh_a, sc_a, g_a, sh_m, sc_m, g_m = (self.scale_shift_table[None] + temb.reshape(B, 6, D)).chunk(6, dim=1)
-        n = F.layer_norm(h, (D,), eps=1e-6) * (1 + sc_a) + sh_a
-        h = h + g_a * self.attn1.to_out[0](self._linear_attention(n))
+        n = _ln_mod(h, sc_a, sh_a)
+        h = _gated(h, self.attn1.to_out[0](self._linear_attention(n)), g_a)
         c, H = self.attn2, self.heads
         o = F.scaled_dot_product_attention(_heads(c.to_q(h), H), _heads(c.to_k(enc), H), _heads(c.to_v(enc), H))
-        h = h + c.to_out[0](_merge(o))
-        n = F.layer_norm(h, (D,), eps=1e-6) * (1 + sc_m) + sh_m
+        h = _gated(h, c.to_out[0](_merge(o)))
+        n = _ln_mod(h, sc_m, sh_m)
         side = int(math.isqrt(T))
         f = self.ff.conv_depth(F.silu(self.ff.conv_inverted(n.transpose(1, 2).reshape(B, D, side, side))))
         f, gate = f.chunk(2, dim=1)
         f = self.ff.conv_point(f * F.silu(gate)).reshape(B, D, T).transpose(1, 2)
-        return h + g_m * f
+        return _gated(h, f, g_m)
 
 
 # ---------------------------------------------------------------------------------------------------------------------

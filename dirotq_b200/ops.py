@@ -473,3 +473,75 @@ def gemm_w4a16(x2d: torch.Tensor, w: PackedWeightInt4, bias: Optional[torch.Tens
     return y
 
 
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# block glue (row-wise passes between two wrapped linears)
+# ---------------------------------------------------------------------------------------------------------------------
+def _mod_vec(v: Optional[torch.Tensor], B: int, D: int):
+    """(pointer tensor, per-sample pitch) of a modulation vector given as [B, D], [B, 1, D] or [1, D] / [D] (shared)."""
+    if v is None:
+        return None, 0
+    v2 = v.reshape(-1, D) if v.dim() != 2 else v
+    assert v2.dtype == torch.bfloat16 and v2.stride(1) == 1 and v2.shape[0] in (1, B)
+    return v2, (0 if v2.shape[0] == 1 else v2.stride(0))
+
+
+def layernorm_modulate(x: torch.Tensor, scale: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+                       eps: float = 1e-6) -> torch.Tensor:
+    """y = LayerNorm(x) * (1 + scale) + shift over the last dimension, no affine parameters; x bf16 [B, T, D], scale /
+    shift per sample ([B, D] or [B, 1, D], views into a larger tensor allowed).  One pass, fp32 inside."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 3
+    B, T, D = x.shape
+    sc, p1 = _mod_vec(scale, B, D)
+    sh, p2 = _mod_vec(shift, B, D)
+    if sc is not None and sh is not None and p1 != p2:
+        sh = sh.expand(B, D).contiguous() if p2 == 0 else sh.contiguous()
+        sc = sc.expand(B, D).contiguous() if p1 == 0 else sc.contiguous()
+        p1 = p2 = D
+    y = torch.empty_like(x)
+    check(_lib.lib().dirotq_layernorm_modulate(_ptr(x), B * T, D, T, _ptr(sc), _ptr(sh), p1 if sc is not None else p2,
+                                               float(eps), _ptr(y), _stream()), "dirotq_layernorm_modulate")
+    return y
+
+
+def gated_residual(h: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                   y2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h + gate * (y + y2): h, y, y2 bf16 [B, T, D]; gate per sample ([B, D] / [B, 1, D]) or None."""
+    assert h.is_cuda and h.dtype == torch.bfloat16 and h.is_contiguous() and h.dim() == 3
+    B, T, D = h.shape
+    y = y.reshape(B, T, D)
+    y = y if y.is_contiguous() else y.contiguous()
+    if y2 is not None:
+        y2 = y2.reshape(B, T, D)
+        y2 = y2 if y2.is_contiguous() else y2.contiguous()
+    g, pitch = _mod_vec(gate, B, D)
+    out = torch.empty_like(h)
+    check(_lib.lib().dirotq_gated_residual(_ptr(h), _ptr(y), _ptr(y2), _ptr(g), pitch, B * T, D, T, _ptr(out), _stream()),
+          "dirotq_gated_residual")
+    return out
+
+
+def qkv_norm_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, w_q: Optional[torch.Tensor],
+                  w_k: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                  out: Optional[tuple] = None, t0: int = 0, eps: float = 1e-6):
+    """q, k, v bf16 [B, T, H * d] (columns of one fused projection output or separate tensors, common row pitch): RMSNorm
+    per head times w_q / w_k and the rotary embedding on q and k, v copied, all written token-major into
+    out = (q, k, v) buffers [B, T_total, H, d] at token offset t0 (allocated with T_total = T when out is None)."""
+    B, T, C = q.shape
+    d = C // heads
+    pitch = q.stride(1)
+    for t in (q, k, v):
+        assert t.is_cuda and t.dtype == torch.bfloat16 and t.shape == q.shape and t.stride(2) == 1
+        assert t.stride(1) == pitch and t.stride(0) == T * pitch, "q, k, v: rows of all samples at one pitch"
+    if out is None:
+        out = tuple(torch.empty(B, T, heads, d, dtype=torch.bfloat16, device=q.device) for _ in range(3))
+    T_total = out[0].shape[1]
+    for o in out:
+        assert o.is_contiguous() and o.shape == (B, T_total, heads, d)
+    if cos is not None:
+        assert cos.shape == (T_total, d) and sin.shape == (T_total, d) and cos.is_contiguous() and sin.is_contiguous()
+    check(_lib.lib().dirotq_qkv_norm_rope(_ptr(q), _ptr(k), _ptr(v), pitch, B, T, heads, d, _ptr(w_q), _ptr(w_k), _ptr(cos),
+                                          _ptr(sin), T_total, t0, float(eps), _ptr(out[0]), _ptr(out[1]), _ptr(out[2]),
+                                          _stream()), "dirotq_qkv_norm_rope")
+    return out

@@ -330,6 +330,32 @@ int dirotq_linear_forward_chain(const dirotq_linear* lin, const void* x, int64_t
 int dirotq_linear_gemm_prequantised(const dirotq_linear* lin, int64_t M, void* y, void* workspace,
                                     size_t workspace_bytes, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Block glue: the row-wise passes between two wrapped linears of a DiT block.  Not part of the
+ * ActQuantWrapper forward; the reference's model forwards run them as separate PyTorch / nunchaku
+ * calls (speedup/report_flux_w4a4_no_rot_ffdown.py:199-228, :240-252, :261-276).  bf16 in and out,
+ * fp32 inside, one rounding; every input is read once.
+ *
+ * dirotq_layernorm_modulate: y[r, :] = LayerNorm(x[r, :]) * (1 + scale[b, :]) + shift[b, :] with
+ *   b = r / rows_per_sample; no affine parameters, biased variance.  scale / shift: bf16, sample b at
+ *   scale + b * mod_pitch (elements; either may be NULL).  D % 8 == 0, D <= 4096.
+ * dirotq_gated_residual: out = h + gate[b, :] * (y + y2); y2 and gate may be NULL (gate NULL: out =
+ *   h + y + y2).  out may alias h.
+ * dirotq_qkv_norm_rope: q, k, v bf16 [B * T, H * d] with a common row pitch (elements; columns of one
+ *   fused projection output, or three tensors).  q and k: RMSNorm over each head's d values times
+ *   w_q / w_k (bf16 [d], NULL: no normalisation), then the rotary embedding out[2i] = x[2i] cos[p, 2i]
+ *   - x[2i+1] sin[p, 2i], out[2i+1] = x[2i+1] cos[p, 2i+1] + x[2i] sin[p, 2i+1] at position p = t0 + t
+ *   (cos / sin bf16 [T_total, d], NULL: none); v is copied.  Outputs are token-major [B, T_total, H, d]
+ *   and receive rows t0 .. t0 + T - 1 of every sample: two calls (text at t0 = 0, image at t0 = S)
+ *   fill one buffer for a joint attention.  d = 64 or 128. */
+int dirotq_layernorm_modulate(const void* x, int64_t M, int32_t D, int64_t rows_per_sample, const void* scale,
+                              const void* shift, int64_t mod_pitch, float eps, void* y, void* stream);
+int dirotq_gated_residual(const void* h, const void* y, const void* y2, const void* gate, int64_t mod_pitch, int64_t M,
+                          int32_t D, int64_t rows_per_sample, void* out, void* stream);
+int dirotq_qkv_norm_rope(const void* q, const void* k, const void* v, int64_t pitch, int64_t B, int64_t T, int32_t H,
+                         int32_t d, const void* w_q, const void* w_k, const void* cos, const void* sin, int64_t T_total,
+                         int64_t t0, float eps, void* out_q, void* out_k, void* out_v, void* stream);
+
 /* Same computation as dirotq_linear_forward, for callers that can hand over nothing but the input
  * and the output.  (No counterpart in the reference: its eager forward allocates freely through
  * torch.)  Meant for hosts that give a plug-in no allocator at all -- an inference server whose
