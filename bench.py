@@ -47,7 +47,7 @@ WORKLOADS = {
                   "without rotation, global batch 4"),
     "flux_nvfp4": ("flux_double_block", 57, "nvfp4", 4608, 4, "flux",
                    "FLUX.1-dev-shaped step as config 3, in NVFP4 W4A4 (E2M1 g16, UE4M3 group scales; per-head "
-                   "out-projections stay INT4), K=12288 down-projections without rotation, global batch 4"),
+                   "out-projections in blocks of 16 inside each head), K=12288 down-projections without rotation, global batch 4"),
 }
 
 

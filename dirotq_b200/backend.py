@@ -299,6 +299,11 @@ def _act_format(w) -> ops.ActFormat:
             if (d - hlen) % 16:
                 raise NotImplementedError(f"per-head NVFP4 with head_dim - tail = {d - hlen}: not a multiple of the "
                                           "16-element scale block of the FP4 tensor cores; use INT4 for this layer")
+            if PER_HEAD_NVFP4_FUSED and d % 16 == 0:
+                # the rotation kernel's own per-head epilogue writes this layout (one launch)
+                return ops.ActFormat(mode, D, tail_len=hlen, num_heads=H, head_dim=d, group_size=16,
+                                     clip_ratio=float(q.clip_ratio), tensor_scale=_HW_NVFP4_ACT_SCALE)
+            # rotation into scratch, then gather + quantise (two launches): hidden layout + channel selection
             return ops.ActFormat(mode, D, tail_len=H * hlen, group_size=16, clip_ratio=float(q.clip_ratio),
                                  tensor_scale=_HW_NVFP4_ACT_SCALE)
         return ops.ActFormat(mode, D, tail_len=hlen, num_heads=int(w.num_heads), head_dim=int(w.head_dim),
@@ -313,11 +318,16 @@ def _act_format(w) -> ops.ActFormat:
                          tensor_scale=_HW_NVFP4_ACT_SCALE)
 
 
+# Per-head rotation + NVFP4: True = the rotation kernel's per-head NVFP4 epilogue (head_dim a multiple of 16); False = the
+# general two-launch form (rotate into scratch, gather + quantise), which also serves head dims the epilogue does not take.
+PER_HEAD_NVFP4_FUSED = True
+
+
 def _per_head_selection(w):
     """(H, d, tail) for a per-head layer whose format is expressed as rotation + channel selection (NVFP4), else None."""
     q = w.quantizer
     if (q.quant_dtype == "nvfp4" and w.rotation_per_head is not None and getattr(w, "_unrot_fused", False)
-            and int(q.high_bits_length) > 0):
+            and int(q.high_bits_length) > 0 and not (PER_HEAD_NVFP4_FUSED and int(w.head_dim) % 16 == 0)):
         return int(w.num_heads), int(w.head_dim), int(q.high_bits_length)
     return None
 

@@ -49,10 +49,19 @@ inline int make_geom(const dirotq_act_format* f, ActGeom* g) {
   if (g->H > 0) {
     if (g->d <= 0 || g->H * g->d != g->D || g->d % 8 != 0) return DIROTQ_E_ARG;
     if (g->hlen <= 0 || g->hlen >= g->d) return DIROTQ_E_ARG;  // hlen == 0 is a hidden layout
-    if (is_nvfp4(f->mode)) return DIROTQ_E_UNSUPPORTED;
-    g->group = g->d - g->hlen;
-    g->q_len = g->H * g->group;
-    g->n_groups = g->H;
+    if (is_nvfp4(f->mode)) {
+      // per head, the tensor-core form: the heads' low coefficients side by side in blocks of 16 (never straddling a
+      // head), the heads' high coefficients behind them -- the reference's rearrangement
+      // (dirotq_fused_unrotation_fast.py:94-99) with its one group per head cut into the hardware's scale blocks
+      if (f->mode != DIROTQ_NVFP4_HW || (g->d - g->hlen) % 16 != 0 || g->d % 16 != 0) return DIROTQ_E_UNSUPPORTED;
+      g->group = 16;
+      g->q_len = g->H * (g->d - g->hlen);
+      g->n_groups = g->q_len / 16;
+    } else {
+      g->group = g->d - g->hlen;
+      g->q_len = g->H * g->group;
+      g->n_groups = g->H;
+    }
     g->tail_total = g->H * g->hlen;
   } else {
     if (g->hlen >= g->D) return DIROTQ_E_ARG;

@@ -386,6 +386,7 @@ int launch_quantize(const QuantArgs& a, cudaStream_t st) {
   const ActGeom& g = a.g;
   if (a.M <= 0) return DIROTQ_OK;
   const int threads = 256;
+  if (is_nvfp4(g.mode) && g.H > 0) return DIROTQ_E_UNSUPPORTED;   // per-head NVFP4 exists only fused with its rotation
   if (is_nvfp4(g.mode)) {
     int64_t total = a.M * g.n_chunks;
     unsigned blocks = (unsigned)((total + threads - 1) / threads);

@@ -50,7 +50,7 @@ template <int EPI, bool PAIR = false> struct RqCfg {
   static constexpr int SMEM_BYTES = RqStage<PAIR>::STAGES * RqStage<PAIR>::STAGE_BYTES + STG_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3 };
+enum : int { EPI_ROT_ONLY = 0, EPI_INT_HIDDEN = 1, EPI_NVFP4_HIDDEN = 2, EPI_INT_PERHEAD = 3, EPI_NVFP4_PERHEAD = 4 };
 
 
 __device__ __forceinline__ void tile_k_range(const RotArgs& a, int nb, int& kb, int& ke) {
@@ -430,6 +430,78 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
   }
 }
 
+// Per-head layout, NVFP4 (hardware recipe): head h = tile columns [hh*d, hh*d + d): its first d - hlen coefficients go to
+// code slots h * (d - hlen) .. in blocks of 16 (one UE4M3 scale each, byte-addressed: a head's blocks need not fill a
+// scale-factor word), its last hlen to the 16-bit tail.  The GEMM then reads the codes as one hidden-layout row.
+__device__ __forceinline__ void epi_nvfp4_perhead(const RotArgs& a, uint32_t taddr, int64_t row, int n0, int half, uint32_t& turn, int wpq = 2) {
+  const ActGeom& g = a.g;
+  const bool row_ok = row < a.M;
+  const int d = g.d, d_q = g.d - g.hlen;
+  const int n_kb64_pad = (g.n_chunks + 3) & ~3;
+  const bool pow2_T = nvfp4_pow2_tensor_scale(g.T);
+  for (int cb = 0; cb < a.BN; cb += d) {
+    const int h = (n0 + cb) / d;
+    if (h >= g.H) break;
+    if (((turn++) % (uint32_t)wpq) != (uint32_t)half) continue;
+#pragma unroll 1
+    for (int c16 = 0; c16 < d; c16 += 16) {
+      uint32_t r[16];
+      tmem_ld16(taddr + cb + c16, r);
+      tmem_wait_ld();
+      uint32_t w[8];                       // the rotated values, rounded to bf16 and packed in pairs
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+      if (!row_ok) continue;
+      if (a.x_rot) {
+        uint4* xr = reinterpret_cast<uint4*>(a.x_rot + row * g.D + n0 + cb + c16);
+        xr[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        xr[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      if (!a.codes) continue;
+      if (c16 < d_q) {
+        const int slot = h * d_q + c16;                       // first code slot of this block (a multiple of 16)
+        float eff = 0.f;
+        uint8_t sb;
+        uint2 c = make_uint2(0u, 0u);
+        if (pow2_T) {
+          sb = nvfp4_hw_scale(amax_bf16x16(w), g.clip, g.T, &eff);
+          if (eff > 0.f) c = nvfp4_hw_group_packed(w, eff);
+        } else {
+          float v[16];
+          float amax = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+          }
+          sb = nvfp4_hw_scale(amax, g.clip, g.T, &eff);
+          c = nvfp4_hw_group_partial(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12], v[13],
+                                     v[14], v[15], 16, eff);
+        }
+        *reinterpret_cast<uint2*>(a.codes + row * g.code_row_bytes + (slot >> 1)) = c;
+        a.sf[sf_offset(row, slot >> 4, n_kb64_pad)] = sb;
+      } else {
+        __nv_bfloat16* tr = a.tail + row * g.tail_pitch + h * g.hlen + (c16 - d_q);
+        const int left = d - c16;                             // 16, or fewer at the end of a head whose tail is no multiple of 16
+        if (left >= 16 && (((h * g.hlen + c16 - d_q) | g.tail_pitch) & 7) == 0) {
+          reinterpret_cast<uint4*>(tr)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          reinterpret_cast<uint4*>(tr)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < left) tr[j] = __ushort_as_bfloat16((unsigned short)((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xFFFFu)));
+        }
+      }
+    }
+    // code slots between the last head's blocks and the end of the last 64-slot chunk: zero codes under zero scales
+    if (row_ok && a.codes && h == g.H - 1) {
+      for (int slot = g.q_len; slot < g.k_pad; slot += 16)
+        *reinterpret_cast<uint2*>(a.codes + row * g.code_row_bytes + (slot >> 1)) = make_uint2(0u, 0u);
+    }
+  }
+}
+
 // Plain GEMM epilogue: y[M, N] = acc (+ bias) as bf16; used for the stand-alone rotation and for
 // the bf16 GEMM behind the W4A16 layer.  32 columns at a time: tcgen05.ld -> + bias -> bf16 -> the warp's 32 x 32
 // staging patch in shared memory (64-byte rows, 64-byte swizzle) -> one TMA store, which clips the patch at the
@@ -634,6 +706,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         epi_rot_only(a, &tm_y, smem_u32(stg_area) + (warp - 2) * 2048, taddr, mb * 128 + q * 32, lane, n0, half, turn);
       else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0, half, turn);
       else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
+      else if constexpr (EPI == EPI_NVFP4_PERHEAD) epi_nvfp4_perhead(a, taddr, row, n0, half, turn);
       else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn);
       tc_fence_before();
       __syncwarp();
@@ -793,6 +866,7 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
       case DIROTQ_INT4_SYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_SYM>(tx, tu, tu2, a, st);
       case DIROTQ_INT4_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT4_ASYM>(tx, tu, tu2, a, st);
       case DIROTQ_INT8_ASYM: return launch_rq<EPI_INT_PERHEAD, MODE_INT8_ASYM>(tx, tu, tu2, a, st);
+      case DIROTQ_NVFP4_HW: return launch_rq<EPI_NVFP4_PERHEAD, MODE_NVFP4_HW>(tx, tu, tu2, a, st);
       default: return DIROTQ_E_UNSUPPORTED;
     }
   }

@@ -23,7 +23,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .dit import GeluProj, LayerDef, linear_ops, make_wrapped_linear, rotation_ops
+from .dit import GeluProj, LayerDef, layer_quant, linear_ops, make_wrapped_linear, rotation_ops
 from .wrapper import ActQuantWrapper
 
 
@@ -77,8 +77,7 @@ class _Census:
         self.census = []          # (LayerDef, rows-per-sample factor name)
 
     def _wrap(self, ld: LayerDef, quant: str, seed: int, device, rows: str = "img") -> ActQuantWrapper:
-        q = "int4" if (quant == "nvfp4" and ld.kind == "perhead") else quant     # groups of d - tail: no block-16 form
-        w = make_wrapped_linear(ld, q, seed, device)
+        w = make_wrapped_linear(ld, layer_quant(ld, quant), seed, device)     # PixArt / SANA per-head layers stay INT4
         self.census.append((ld, rows))
         return w
 

@@ -74,6 +74,16 @@ def sana_block(k: int = 320) -> List[LayerDef]:
             LayerDef("attn2.to_q", 2240, 2240, tail=k), LayerDef("attn2.to_out.0", 2240, 2240, **ph)]
 
 
+def per_head_nvfp4_ok(ld: LayerDef) -> bool:
+    """Whether a per-head layer has a block-16 NVFP4 form (FLUX: 128 - 16 = 112; not PixArt's 63 or SANA's 28)."""
+    return ld.kind == "perhead" and ld.head_dim % 16 == 0 and (ld.head_dim - ld.tail) % 16 == 0
+
+
+def layer_quant(ld: LayerDef, quant: str) -> str:
+    """The format a layer runs in under a model-wide choice: per-head layers without an NVFP4 form stay INT4."""
+    return "int4" if (quant == "nvfp4" and ld.kind == "perhead" and not per_head_nvfp4_ok(ld)) else quant
+
+
 def linear_ops(ld: LayerDef, M: int) -> float:
     """Algorithmic operations of the linear itself (4-bit part + 16-bit branch): 2 M N D."""
     return 2.0 * M * ld.in_f * ld.out_f
@@ -130,7 +140,7 @@ def make_wrapped_linear(ld: LayerDef, quant: str, seed: int, device="cuda", a_sy
     w._unrot_fused = True
     w_tail = (torch.randn(N, tail_total, generator=gen, device=dev) * 0.02) if tail_total else None
     if quant == "nvfp4":
-        assert ld.kind != "perhead", "per-head layers run INT4 (their groups are not multiples of 16)"
+        assert ld.kind != "perhead" or per_head_nvfp4_ok(ld), "per-head NVFP4 needs head_dim and head_dim - tail in multiples of 16"
         w.quantizer.configure(bits=4, groupsize=16, high_bits_length=ld.tail, quant_dtype="nvfp4")
         nib = torch.randint(0, 16, (N, n_low), generator=gen, device=dev).to(torch.uint8)
         s = torch.exp(torch.randn(N, (n_low + 15) // 16, generator=gen, device=dev) * 0.5 - 4.0)
@@ -191,8 +201,7 @@ class LinearPathStep(nn.Module):
             blk = nn.Module()
             qkv_rotation = {}
             for i, ld in enumerate(block):
-                q = "int4" if (quant == "nvfp4" and ld.kind == "perhead") else quant
-                w = make_wrapped_linear(ld, q, seed + b * len(block) + i, device, a_sym)
+                w = make_wrapped_linear(ld, layer_quant(ld, quant), seed + b * len(block) + i, device, a_sym)
                 # to_q / to_k / to_v of one attention see the same input and get the same rotation
                 # (evec @ R1 of one basis: models/pixart-sigma/model_utils.py:84-92, flux-schnell:165-178)
                 parent, _, leaf = ld.name.rpartition(".")

@@ -159,9 +159,7 @@ class FluxLinearStep:
         s = seed + 104729 * rank
         for stream, n in (("img", n_double), ("txt", n_double), ("single", n_single)):
             for _ in range(n):
-                # per-head out-projections stay INT4 under NVFP4 (dit.LinearPathStep does the same)
-                ws = [dit.make_wrapped_linear(ld, "int4" if (quant == "nvfp4" and ld.kind == "perhead") else quant,
-                                              s + i, device) for i, ld in enumerate(attn)]
+                ws = [dit.make_wrapped_linear(ld, dit.layer_quant(ld, quant), s + i, device) for i, ld in enumerate(attn)]
                 for w_ in ws[1:3]:      # to_k, to_v: same input, same rotation as to_q (flux-schnell/model_utils.py:165-178)
                     w_.rotation = ws[0].rotation.clone()
                 wu = dit.make_wrapped_linear(up, quant, s + 4, device)

@@ -49,7 +49,10 @@ enum {
 typedef struct dirotq_act_format {
   int32_t mode;         /* DIROTQ_* above */
   int32_t width;        /* D, input features */
-  int32_t num_heads;    /* 0: hidden layout [low | tail]; H > 0: per-head layout */
+  int32_t num_heads;    /* 0: hidden layout [low | tail]; H > 0: per-head layout.  Per-head DIROTQ_NVFP4_HW (head_dim
+                         * and head_dim - tail_len multiples of 16): every head's low coefficients in blocks of 16,
+                         * side by side, the heads' high coefficients behind them; produced only by
+                         * dirotq_rotate_quantize (dirotq_quantize_act returns DIROTQ_E_UNSUPPORTED). */
   int32_t head_dim;     /* d (per-head only; H * d == D) */
   int32_t tail_len;     /* high_bits_length: hidden = total, per-head = per head */
   int32_t group_size;   /* hidden: 64 (INT) or 16 (NVFP4); per-head: ignored, group = d - tail_len.

@@ -127,22 +127,28 @@ def test_per_token_activation_scales(name):
     assert torch.equal(backend.linear_forward_static(st, x2d), y.reshape(M, -1))
 
 
-def test_per_head_rotation_with_nvfp4_activations():
-    """Per-head rotation + NVFP4 (head_dim - tail a multiple of 16): block-diagonal rotation into scratch, then the
-    heads' low coefficients gathered in front and quantised in blocks of 16.  Bit contract: the hardware-recipe oracle
-    on the gathered tensor; against the reference (one unrounded scale per head group) the layer is pinned by QSNR."""
+@pytest.mark.parametrize("fused", [True, False])
+def test_per_head_rotation_with_nvfp4_activations(fused, monkeypatch):
+    """Per-head rotation + NVFP4 (head_dim - tail a multiple of 16): the heads' low coefficients side by side in blocks
+    of 16, by the rotation kernel's per-head epilogue (fused) or by a block-diagonal rotation into scratch followed by
+    gather + quantise (two launches).  Bit contract: the hardware-recipe oracle on the gathered tensor; against the
+    reference (one unrounded scale per head group) the layer is pinned by QSNR."""
     from dirotq_b200 import backend, ops
+    monkeypatch.setattr(backend, "PER_HEAD_NVFP4_FUSED", fused)
     g = load_golden("perhead_nvfp4")
     w = _wrapper_from_golden(g)
     y = w(g["x"].cuda()).float().cpu()
     ops.check_status()
     st = w._b200_state
     H, d, hl = 4, 64, 16
-    assert st.fmt.num_heads == 0 and st.perm_idx is not None and st.layout.tail_total == H * hl
+    assert st.layout.tail_total == H * hl and st.layout.q_len == H * (d - hl)
+    assert (st.fmt.num_heads == H and st.perm_idx is None) if fused else (st.fmt.num_heads == 0 and st.perm_idx is not None)
+    if not fused:
+        cols = torch.arange(H * d).reshape(H, d)
+        assert torch.equal(st.perm_idx.cpu(), torch.cat([cols[:, : d - hl].reshape(-1), cols[:, d - hl:].reshape(-1)]))
     x2d = g["x"].reshape(-1, H * d).cuda()
     x_rot = ops.rotate(x2d, st.rot_t).cpu()
     xre = O.per_head_rearrange(x_rot.reshape(-1, H, d), hl).reshape(g["x"].shape)     # [H * (d - hl) | H * hl]
-    assert torch.equal(xre.reshape(-1, H * d), x_rot[:, st.perm_idx.cpu()])
     W3 = g["weight"].float().reshape(-1, H, d)
     W_re = torch.cat([W3[:, :, : d - hl].reshape(-1, H * (d - hl)), W3[:, :, d - hl:].reshape(-1, H * hl)], 1).to(torch.bfloat16)
     spec = O.LayerSpec(W_re, g["bias"], O.QuantCfg(4, 16, True, 1.0, H * hl, "nvfp4"))

@@ -108,7 +108,8 @@ def test_fused_rotate_quantize_hidden(name, M, D):
 
 
 @pytest.mark.parametrize("H,d,hlen,mode", [(16, 72, 9, "sym"), (16, 72, 9, "asym"), (70, 32, 4, "sym"),
-                                           (24, 128, 16, "sym")])
+                                           (24, 128, 16, "sym"), (24, 128, 16, "nvfp4"), (5, 64, 16, "nvfp4"),
+                                           (9, 64, 32, "nvfp4")])     # 5 x 48 and 9 x 32 slots: a partly filled last chunk
 def test_fused_rotate_quantize_per_head(H, d, hlen, mode):
     ops = _ops()
     from gpu_helpers import assert_act_matches_oracle
@@ -117,7 +118,12 @@ def test_fused_rotate_quantize_per_head(H, d, hlen, mode):
     x = O.synth_activations(M, D, g).cuda()
     U_ph = torch.stack([O.random_orthogonal(d, g) for _ in range(H)]).to(torch.bfloat16)
     rot_t = torch.block_diag(*[U_ph[h].T for h in range(H)]).contiguous().cuda()
-    fmt = ops.ActFormat(ops.INT4_SYM if mode == "sym" else ops.INT4_ASYM, D, tail_len=hlen, num_heads=H, head_dim=d)
+    if mode == "nvfp4":
+        fmt = ops.ActFormat(ops.NVFP4_HW, D, tail_len=hlen, num_heads=H, head_dim=d, group_size=16, tensor_scale=0.5)
+        with pytest.raises(RuntimeError):                     # this layout exists only fused with its rotation
+            ops.quantize_act(x, fmt)
+    else:
+        fmt = ops.ActFormat(ops.INT4_SYM if mode == "sym" else ops.INT4_ASYM, D, tail_len=hlen, num_heads=H, head_dim=d)
     buf, x_rot = ops.rotate_quantize(x, rot_t, fmt, want_x_rot=True)
     ops.check_status()
     ref = O.rotate_per_head(x.cpu().unsqueeze(0), U_ph, fp32=True).reshape(M, D)
