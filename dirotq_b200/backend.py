@@ -173,9 +173,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     """One wrapped linear through the C ABI: x2d bf16 [M, D] -> bf16 [M, N]."""
     assert x2d.is_cuda and x2d.dtype == torch.bfloat16 and x2d.is_contiguous()
     M = x2d.shape[0]
-    y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
     if M == 0:
-        return y
+        return out if out is not None else torch.empty(0, st.out_features, dtype=torch.bfloat16, device=x2d.device)
     grp = st.shared
     if grp is not None and grp.fused is not None:
         # siblings fused into one layer: the first member called on a tensor runs it, the others take their columns
@@ -193,6 +192,7 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
                 out.copy_(part)
                 return out
             return part
+    y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
     if st.hadamard_low_dim:
         x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
     if CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and M <= PANEL_CACHE_MAX_ROWS:
@@ -652,7 +652,8 @@ def fuse_sibling_gemms(transformer, classes=None) -> int:
     (speedup/report_flux_w4a4_no_rot_ffdown.py:336-345).  The first member called on a tensor launches the pass and
     the GEMM; every member returns its own columns of the [M, sum N] result (a strided view; values are bit-identical
     to the separate GEMMs, whose per-element arithmetic does not depend on the tiling).  A group whose members turn out
-    to see different tensors (a cross-attention) falls back to separate GEMMs after three unconsumed passes.
+    to see different tensors (a cross-attention) falls back to separate GEMMs after three unconsumed passes; for that
+    the members keep their own packed weights, so a fused group holds its 4-bit weights twice.
     Returns the number of fused groups."""
     classes = tuple(classes or _wrapper_classes())
     groups = {}
