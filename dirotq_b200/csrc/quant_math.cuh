@@ -38,7 +38,10 @@ __device__ __forceinline__ GroupParams int_sym_params(float mx, float mn, float 
   float xmin = rnd<BF16>(__fmul_rn(mn, clip));
   float a = fmaxf(fabsf(xmin), xmax);
   GroupParams p;
-  p.scale = (a == 0.f) ? 1.f : rnd<BF16>(__fdiv_rn(a, maxq));
+  // a and maxq (7, 15, 255) are bf16 values: the reciprocal multiply rounds to the same bf16 as the divide (see
+  // div_round_bf16 below); the fp32 forms of the slow path keep the divide
+  if constexpr (BF16) p.scale = (a == 0.f) ? 1.f : rnd<true>(__fmul_rn(a, __frcp_rn(maxq)));
+  else p.scale = (a == 0.f) ? 1.f : __fdiv_rn(a, maxq);
   p.zero = 0.f;
   return p;
 }
@@ -89,8 +92,14 @@ __device__ __forceinline__ GroupParams int_asym_params(float mx, float mn, float
   float d = rnd<BF16>(__fsub_rn(xmax, xmin));
   d = fmaxf(d, rnd<BF16>(1e-5f));
   GroupParams p;
-  p.scale = rnd<BF16>(__fdiv_rn(d, maxq));
-  p.zero = rnd<BF16>(rintf(rnd<BF16>(__fdiv_rn(-xmin, p.scale))));
+  if constexpr (BF16) {
+    // d, maxq, xmin and the scale are bf16 values: reciprocal multiplies round to the same bf16 as the divides
+    p.scale = rnd<true>(__fmul_rn(d, __frcp_rn(maxq)));
+    p.zero = rnd<true>(rintf(rnd<true>(__fmul_rn(-xmin, __frcp_rn(p.scale)))));
+  } else {
+    p.scale = __fdiv_rn(d, maxq);
+    p.zero = rintf(__fdiv_rn(-xmin, p.scale));
+  }
   return p;
 }
 // quant_utils.py:80

@@ -80,8 +80,16 @@ __global__ void __launch_bounds__(256) quant_int_kernel(const QuantArgs a) {
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool live = tid < total;
   const int64_t t = live ? tid : total - 1;
-  const int64_t row = t / bpr;
-  const int b = (int)(t - row * bpr);
+  int64_t row;
+  int b;
+  if (total <= 0x7fffffffLL) {                         // the usual case: a 32-bit divide instead of the 64-bit routine
+    const uint32_t r32 = (uint32_t)t / (uint32_t)bpr;
+    row = r32;
+    b = (int)((uint32_t)t - r32 * (uint32_t)bpr);
+  } else {
+    row = t / bpr;
+    b = (int)(t - row * bpr);
+  }
   const int chunk = b >> 1, half = b & 1;
   const int grp = chunk / g.cpg;
   const int e0 = (chunk % g.cpg) * 64 + half * 32;     // first element of the group this block covers
@@ -242,8 +250,16 @@ __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const QuantArgs a) {
   const int64_t total = a.M * g.n_chunks;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (tid >= total) return;
-  const int64_t row = tid / g.n_chunks;
-  const int chunk = (int)(tid - row * g.n_chunks);
+  int64_t row;
+  int chunk;
+  if (total <= 0x7fffffffLL) {                         // 32-bit divide in the usual case
+    const uint32_t r32 = (uint32_t)tid / (uint32_t)g.n_chunks;
+    row = r32;
+    chunk = (int)((uint32_t)tid - r32 * (uint32_t)g.n_chunks);
+  } else {
+    row = tid / g.n_chunks;
+    chunk = (int)(tid - row * g.n_chunks);
+  }
   const __nv_bfloat16* xr = a.x + row * a.x_pitch;
   const int c0 = chunk * 64;
   const int n_kb64_pad = (g.n_chunks + 3) & ~3;
