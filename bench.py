@@ -88,7 +88,8 @@ def parse():
     ap.add_argument("--profile-case", default="", nargs="?", const="layers",
                     help="run a small case for ncu instead of the benchmark: 'layers' = one 1152->1152 k=64 layer at "
                          "M=16384, INT4 then NVFP4, three forwards each; 'flux_nvfp4' = one NVFP4 3072->12288 k=384 "
-                         "layer at M=4096; 'quantize' = the quantise-only kernel at M=4096, D=12288")
+                         "layer at M=4096; 'quantize' = the quantise-only kernel at M=4096, D=12288; 'glue' = the three "
+                         "block-glue kernels on FLUX-shaped tensors (4 x 4096 x 3072)")
     return ap.parse_args()
 
 
@@ -836,6 +837,23 @@ def profile_case(which):
             st = backend.prepare_layer(w, "cuda", w._b200_explicit)
             for _ in range(3):
                 backend.linear_forward(st, x)
+        elif which == "glue":
+            from dirotq_b200 import denoise
+            B, T, S, D, H = 4, 4096, 512, 3072, 24         # FLUX-shaped: 151 MB per [B, T, D] tensor
+            M = B * T
+            g = torch.Generator().manual_seed(0)
+            x = synth_activations(M, D, g).reshape(B, T, D).cuda()
+            y = synth_activations(M, D, g).reshape(B, T, D).cuda()
+            mod = (torch.randn(B, 6 * D, generator=g) * 0.3).to(torch.bfloat16).cuda()[:, None].chunk(6, dim=-1)
+            qkv = synth_activations(M, 3 * D, g).cuda()
+            q, k, v = [qkv[:, j * D:(j + 1) * D].reshape(B, T, D) for j in range(3)]
+            cos, sin = denoise.rope_tables(S + T, D // H, "cuda")
+            w = torch.ones(D // H, dtype=torch.bfloat16, device="cuda")
+            bufs = tuple(torch.empty(B, S + T, H, D // H, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+            for _ in range(3):
+                ops.layernorm_modulate(x, mod[1], mod[0])
+                ops.gated_residual(x, y, mod[2])
+                ops.qkv_norm_rope(q, k, v, H, w, w, cos, sin, out=bufs, t0=S)
         elif which == "quantize":
             M = 4096
             x = synth_activations(M, 12288, torch.Generator().manual_seed(0)).cuda()

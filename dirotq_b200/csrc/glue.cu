@@ -10,7 +10,8 @@
 //                        ([B, T_total, H, d], at a token offset) so that text and image streams land in one buffer
 //                        without a concatenation and the attention output needs no transpose.
 //
-// One warp per row (layernorm_modulate), one thread per 8 values (the other two); 16-byte loads and stores.
+// Four warps per row (layernorm_modulate), one thread per 8 values (the other two); 16-byte loads and stores, 32-bit
+// index arithmetic.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include "layout.cuh"
@@ -35,24 +36,29 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return q;
 }
 
-// NV = 16-byte vectors per lane (D <= 256 * NV)
-template <int NV>
+// WPR warps per row (1: short rows, no shared memory; 4: long rows, more loads in flight per row), 8 / WPR rows per CTA;
+// NV = 16-byte vectors per thread (D <= 256 * WPR * NV).  The row stays in registers between the two reductions (mean,
+// then centred sum of squares) and the output pass.
+template <int NV, int WPR>
 __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int D,
                                                                  int64_t rows_per_sample, const __nv_bfloat16* __restrict__ scale,
                                                                  const __nv_bfloat16* __restrict__ shift, int64_t mod_pitch,
                                                                  float eps, __nv_bfloat16* __restrict__ y) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= M) return;
+  constexpr int TPR = 32 * WPR, RPC = 8 / WPR;                                               // threads per row, rows per CTA
+  __shared__ float red[2][RPC][WPR];
+  const int lane = threadIdx.x & 31, wr = (threadIdx.x >> 5) % WPR, rr = threadIdx.x / TPR;  // warp in row, row in CTA
+  const int tr = threadIdx.x % TPR;                                                          // thread in row
+  const int64_t row = (int64_t)blockIdx.x * RPC + rr;
+  const bool live = row < M;
   const int nvec = D >> 3;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (live ? row : 0) * D);
   uint4 v[NV];
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int idx = lane + 32 * i;
+    const int idx = tr + TPR * i;
     v[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (idx < nvec) {
+    if (live && idx < nvec) {
       v[i] = __ldg(xr + idx);
       float f[8];
       unpack8(v[i], f);
@@ -62,11 +68,18 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bflo
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if constexpr (WPR > 1) {
+    if (lane == 0) red[0][rr][wr] = sum;
+    __syncthreads();
+    sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPR; ++w) sum += red[0][rr][w];
+  }
   const float mean = sum / (float)D;
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    if (lane + 32 * i < nvec) {
+    if (tr + TPR * i < nvec) {
       float f[8];
       unpack8(v[i], f);
 #pragma unroll
@@ -75,6 +88,14 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bflo
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if constexpr (WPR > 1) {
+    if (lane == 0) red[1][rr][wr] = sq;
+    __syncthreads();
+    sq = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPR; ++w) sq += red[1][rr][w];
+  }
+  if (!live) return;
   const float rstd = rsqrtf(sq / (float)D + eps);
   const int64_t b = row / rows_per_sample;
   const uint4* sc = scale ? reinterpret_cast<const uint4*>(scale + b * mod_pitch) : nullptr;
@@ -82,7 +103,7 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bflo
   uint4* yr = reinterpret_cast<uint4*>(y + row * D);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int idx = lane + 32 * i;
+    const int idx = tr + TPR * i;
     if (idx < nvec) {
       float f[8], s[8], t[8];
       unpack8(v[i], f);
@@ -106,9 +127,20 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(const __nv_bfloat16
                                                              int D, int64_t rows_per_sample, __nv_bfloat16* __restrict__ out) {
   const int nvec = D >> 3;
   const int64_t total = M * nvec;
+  const bool small = total <= 0x7fffffffLL && rows_per_sample <= 0x7fffffffLL;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / nvec;
-    const int c = (int)(i - row * nvec);
+    int64_t row, smp = 0;
+    int c;
+    if (small) {                                   // 32-bit divides in the usual case
+      const uint32_t r32 = (uint32_t)i / (uint32_t)nvec;
+      row = r32;
+      c = (int)((uint32_t)i - r32 * (uint32_t)nvec);
+      if (gate) smp = r32 / (uint32_t)rows_per_sample;
+    } else {
+      row = i / nvec;
+      c = (int)(i - row * nvec);
+      if (gate) smp = row / rows_per_sample;
+    }
     float a[8], b[8], g[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(h) + i), a);
     unpack8(__ldg(reinterpret_cast<const uint4*>(y) + i), b);
@@ -119,7 +151,7 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(const __nv_bfloat16
       for (int e = 0; e < 8; ++e) b[e] += b2[e];
     }
     if (gate) {
-      unpack8(__ldg(reinterpret_cast<const uint4*>(gate + (row / rows_per_sample) * mod_pitch) + c), g);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(gate + smp * mod_pitch) + c), g);
 #pragma unroll
       for (int e = 0; e < 8; ++e) a[e] = fmaf(g[e], b[e], a[e]);
     } else {
@@ -145,16 +177,16 @@ struct QkvArgs {
 // LPH = lanes per head (d / 8): 8 or 16; a head's lanes are consecutive and aligned inside a warp
 template <int LPH>
 __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(const QkvArgs a) {
-  const int vec_per_row = a.H * LPH;
-  const int64_t total = a.B * a.T * 3 * vec_per_row;
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t vec_per_row = (uint32_t)(a.H * LPH);
+  const uint32_t total = (uint32_t)(a.B * a.T) * vec_per_row;      // per part; the launcher keeps it below 2^32
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   const bool live = i < total;
-  const int64_t ii = live ? i : total - 1;               // keep whole warps in the shuffles
-  const int64_t rp = ii / vec_per_row;                   // (row, part)
-  const int c = (int)(ii - rp * vec_per_row);            // vector inside the row
-  const int part = (int)(rp % 3);
-  const int64_t row = rp / 3;
-  const int64_t b = row / a.T, t = row - b * a.T;
+  const uint32_t ii = live ? i : total - 1;              // keep whole warps in the shuffles
+  const int part = blockIdx.y;                           // 0 = q, 1 = k, 2 = v
+  const uint32_t row32 = ii / vec_per_row;
+  const int c = (int)(ii - row32 * vec_per_row);         // vector inside the row
+  const uint32_t b32 = row32 / (uint32_t)a.T;
+  const int64_t row = row32, b = b32, t = row32 - b32 * (uint32_t)a.T;
   float f[8];
   const __nv_bfloat16* in = part == 0 ? a.in[0] : (part == 1 ? a.in[1] : a.in[2]);
   unpack8(__ldg(reinterpret_cast<const uint4*>(in + row * a.pitch) + c), f);
@@ -170,14 +202,14 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(const QkvArgs a) {
     if (wp) {
       const float r = rsqrtf(ss / (float)a.d + a.eps);
       float w[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(wp) + (c % LPH)), w);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(wp) + (c & (LPH - 1))), w);
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = f[e] * r * w[e];
     }
     if (a.cos) {
       float cs[8], sn[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(a.cos + pos * a.d) + (c % LPH)), cs);
-      unpack8(__ldg(reinterpret_cast<const uint4*>(a.sin + pos * a.d) + (c % LPH)), sn);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(a.cos + pos * a.d) + (c & (LPH - 1))), cs);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(a.sin + pos * a.d) + (c & (LPH - 1))), sn);
 #pragma unroll
       for (int e = 0; e < 8; e += 2) {
         const float x0 = f[e], x1 = f[e + 1];
@@ -204,16 +236,21 @@ int dirotq_layernorm_modulate(const void* x, int64_t M, int32_t D, int64_t rows_
        reinterpret_cast<uintptr_t>(shift)) & 15)
     return DIROTQ_E_ALIGN;
   if (M == 0) return DIROTQ_OK;
+  if ((M + 1) / 2 > 0x7fffffff) return DIROTQ_E_TOO_LARGE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned blocks = (unsigned)((M + 7) / 8);
   const __nv_bfloat16 *xp = static_cast<const __nv_bfloat16*>(x), *sc = static_cast<const __nv_bfloat16*>(scale),
                       *sh = static_cast<const __nv_bfloat16*>(shift);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
-  const int nv = (D / 8 + 31) / 32;
-  if (nv <= 4) layernorm_modulate_kernel<4><<<blocks, 256, 0, st>>>(xp, M, D, rows_per_sample, sc, sh, mod_pitch, eps, yp);
-  else if (nv <= 8) layernorm_modulate_kernel<8><<<blocks, 256, 0, st>>>(xp, M, D, rows_per_sample, sc, sh, mod_pitch, eps, yp);
-  else if (nv <= 12) layernorm_modulate_kernel<12><<<blocks, 256, 0, st>>>(xp, M, D, rows_per_sample, sc, sh, mod_pitch, eps, yp);
-  else layernorm_modulate_kernel<16><<<blocks, 256, 0, st>>>(xp, M, D, rows_per_sample, sc, sh, mod_pitch, eps, yp);
+  const int nvec = D / 8;
+#define DQ_LN(NV, WPR)                                                                                            \
+  layernorm_modulate_kernel<NV, WPR><<<(unsigned)((M + 8 / WPR - 1) / (8 / WPR)), 256, 0, st>>>(xp, M, D, rows_per_sample, sc, \
+                                                                                                 sh, mod_pitch, eps, yp)
+  if (nvec <= 64) DQ_LN(2, 1);
+  else if (nvec <= 160) DQ_LN(5, 1);           // PixArt's 1152: a warp per row
+  else if (nvec <= 256) DQ_LN(2, 4);
+  else if (nvec <= 384) DQ_LN(3, 4);           // SANA's 2240, FLUX's 3072: four warps per row
+  else DQ_LN(4, 4);
+#undef DQ_LN
   return cudaGetLastError() == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
@@ -261,9 +298,9 @@ int dirotq_qkv_norm_rope(const void* q, const void* k, const void* v, int64_t pi
   a.B = B; a.T = T; a.T_total = T_total; a.t0 = t0;
   a.H = H; a.d = d;
   a.eps = eps;
-  const int64_t total = B * T * 3 * H * (d / 8);
-  if ((total + 255) / 256 > 0x7fffffff) return DIROTQ_E_TOO_LARGE;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
+  const int64_t total = B * T * H * (d / 8);             // 16-byte vectors per part
+  if (total > 0xffffff00LL) return DIROTQ_E_TOO_LARGE;
+  const dim3 blocks((unsigned)((total + 255) / 256), 3);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (d == 128) qkv_norm_rope_kernel<16><<<blocks, 256, 0, st>>>(a);
   else qkv_norm_rope_kernel<8><<<blocks, 256, 0, st>>>(a);
