@@ -71,6 +71,9 @@ def parse():
     ap.add_argument("--no-sub", action="store_true", help="skip the sub-records and the model-shaped step")
     ap.add_argument("--no-fuse-gelu", action="store_true",
                     help="keep the GELU between the FFN linears as a separate PyTorch kernel")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every kernel from Python instead of replaying the step from a CUDA graph (resident-input "
+                         "timing of the non-FLUX workloads and the model-shaped step)")
     ap.add_argument("--no-fused-glue", action="store_true",
                     help="denoise_step: keep modulated LayerNorm, gated residuals and q/k RMSNorm + rotary embedding as "
                          "chains of PyTorch elementwise kernels instead of the library's single-pass kernels")
@@ -414,8 +417,10 @@ def run_ours(args):
     y_host = torch.empty(*y_shape, dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
 
+    graphed = [None]
+
     def step_resident():
-        return step(x_dev)
+        return graphed[0]() if graphed[0] is not None else step(x_dev)
 
     # end to end: every step copies its input from pinned host memory and its result back; the copies run on side
     # streams (two input buffers) so that they overlap the kernels of the neighbouring steps
@@ -425,6 +430,18 @@ def run_ours(args):
     for _ in range(max(3, args.warmup)):
         step_resident()
     ops.check_status(dev)
+    # small shards (one or two samples per GPU) are short enough for Python's launch cost to show: replay them from a
+    # CUDA graph captured once; larger batches gain nothing and keep plain launches
+    if not is_flux and not args.no_graph and M <= 8192:
+        try:
+            from dirotq_b200.dit import GraphedCall
+            graphed[0] = GraphedCall(lambda: step(x_dev))
+            for _ in range(2):
+                step_resident()
+            ops.check_status(dev)
+        except Exception as e:      # capture is an optimisation, never a requirement
+            graphed[0] = None
+            print(f"CUDA graph capture failed ({type(e).__name__}: {e}); plain launches", file=sys.stderr)
     sampler = ClockSampler(D_.local)
     if rank == 0:
         sampler.start()
@@ -489,6 +506,8 @@ def run_ours(args):
                        "gelu": (f"fused into the up-projection GEMM epilogue ({n_fused} layers)" if n_fused
                                 else "separate PyTorch kernel"),
                        "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
+                       "execution": ("CUDA graph replay of the step (captured once after the warm-up)" if graphed[0] is not None
+                                     else "kernels launched from Python, programmatic dependent launch between them"),
                        "l2": l2_note,
                        "linear_gflop_per_step_per_gpu": lin_ops / 1e9, "rotation_gflop_per_step_per_gpu": rot_ops / 1e9},
             "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
@@ -527,16 +546,28 @@ def denoise_record(D_, family, quant, gbatch, world, strong, args):
     n_chained = 0 if args.no_fuse_ffn else backend.fuse_ffn_quantise(step, keep_hidden=False)
     n_qkv = 0 if args.no_fuse_qkv else backend.fuse_sibling_gemms(step)
     inputs = step.example_inputs(batch, dev, seed=D_.rank)
+    ms_graph = None
     with torch.no_grad():
         for _ in range(3):
             step(*inputs)
         ops.check_status(dev)
         ms = D_.timed(lambda: step(*inputs), 4) / 4
         lin_ms = denoise.time_wrapped_linears(step, inputs)
+        if not args.no_graph:
+            try:
+                from dirotq_b200.dit import GraphedCall
+                replay = GraphedCall(lambda: step(*inputs))
+                replay()
+                ops.check_status(dev)
+                ms_graph = D_.timed(replay, 4) / 4
+                del replay
+            except Exception as e:
+                print(f"CUDA graph capture of the model-shaped step failed ({type(e).__name__}: {e})", file=sys.stderr)
     lin, _ = step.ops_per_step(batch)
     rec = {"family": family, "quant": quant, "blocks": note, "batch_per_gpu": batch, "tokens": step.shape["tokens"],
-           "text_tokens": step.shape["text"], "step_ms": ms, "wrapped_linears_ms": lin_ms,
-           "linear_path_share": lin_ms / ms if ms > 0 else None,
+           "text_tokens": step.shape["text"], "step_ms": ms if ms_graph is None else min(ms, ms_graph),
+           "step_ms_launched": ms, "step_ms_graph_replay": ms_graph, "wrapped_linears_ms": lin_ms,
+           "linear_path_share": lin_ms / ms if ms > 0 else None,     # both from the launched form
            "linear_tflops_inside_step": D_.world * lin / (lin_ms * 1e-3) / 1e12 if lin_ms > 0 else None,
            "gelu_fused_layers": n_fused, "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
            "launches_per_step": step.kernel_launches_per_step(),

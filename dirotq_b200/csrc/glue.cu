@@ -52,18 +52,17 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bflo
   const bool live = row < M;
   const int nvec = D >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (live ? row : 0) * D);
-  uint4 v[NV];
+  float f[NV][8];                         // the row, unpacked once
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int idx = tr + TPR * i;
-    v[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (live && idx < nvec) {
-      v[i] = __ldg(xr + idx);
-      float f[8];
-      unpack8(v[i], f);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sum += f[e];
+    for (int e = 0; e < 8; ++e) f[i][e] = 0.f;
+    if (live && idx < nvec) {
+      unpack8(__ldg(xr + idx), f[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += f[i][e];
     }
   }
 #pragma unroll
@@ -80,10 +79,8 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bflo
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (tr + TPR * i < nvec) {
-      float f[8];
-      unpack8(v[i], f);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { const float c = f[e] - mean; sq = fmaf(c, c, sq); }
+      for (int e = 0; e < 8; ++e) { const float c = f[i][e] - mean; sq = fmaf(c, c, sq); }
     }
   }
 #pragma unroll
@@ -105,18 +102,17 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(const __nv_bflo
   for (int i = 0; i < NV; ++i) {
     const int idx = tr + TPR * i;
     if (idx < nvec) {
-      float f[8], s[8], t[8];
-      unpack8(v[i], f);
+      // y = (x - mean) * rstd * (1 + scale) + shift = x * a + c with a = rstd * (1 + scale), c = shift - mean * a
+      float s[8], t[8], r[8];
       if (sc) unpack8(__ldg(sc + idx), s);
       if (sh) unpack8(__ldg(sh + idx), t);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        float r = (f[e] - mean) * rstd;
-        if (sc) r *= 1.f + s[e];
-        if (sh) r += t[e];
-        f[e] = r;
+        const float a = sc ? fmaf(rstd, s[e], rstd) : rstd;
+        const float c = fmaf(-mean, a, sh ? t[e] : 0.f);
+        r[e] = fmaf(f[i][e], a, c);
       }
-      yr[idx] = pack8(f);
+      yr[idx] = pack8(r);
     }
   }
 }

@@ -533,7 +533,7 @@ def qkv_norm_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int,
     pitch = q.stride(1)
     for t in (q, k, v):
         assert t.is_cuda and t.dtype == torch.bfloat16 and t.shape == q.shape and t.stride(2) == 1
-        assert t.stride(1) == pitch and t.stride(0) == T * pitch, "q, k, v: rows of all samples at one pitch"
+        assert t.stride(1) == pitch and (B == 1 or t.stride(0) == T * pitch), "q, k, v: rows of all samples at one pitch"
     if out is None:
         out = tuple(torch.empty(B, T, heads, d, dtype=torch.bfloat16, device=q.device) for _ in range(3))
     T_total = out[0].shape[1]

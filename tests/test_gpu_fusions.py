@@ -212,3 +212,26 @@ def test_sibling_layers_run_as_one_gemm(quant, widths):
         assert torch.equal(w(xi), w2(xi))
     assert grp.fused is None
     ops.check_status()
+
+
+def test_step_replayed_from_a_cuda_graph():
+    """dit.GraphedCall: a linear-path step with all fusions on, captured once and replayed, returns what the launched
+    step returns, follows in-place changes of its input buffer, and leaves the status word clean."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    step = dit.LinearPathStep(dit.flux_double_block(k_down=0), 1, "int4", device="cuda", seed=4100)
+    backend.preconvert_rotations_to_device(step, "cuda")
+    assert backend.fuse_gelu_modules(step) == 1 and backend.fuse_ffn_quantise(step, keep_hidden=False) == 1
+    assert backend.fuse_sibling_gemms(step) == 1
+    x = synth_activations(640, 3072, torch.Generator().manual_seed(1)).reshape(1, 640, 3072).cuda()
+    with torch.no_grad():
+        y_launched = step(x).clone()
+        replay = dit.GraphedCall(lambda: step(x))
+        assert torch.equal(replay(), y_launched)
+        x2 = synth_activations(640, 3072, torch.Generator().manual_seed(2)).reshape(1, 640, 3072).cuda()
+        x.copy_(x2)                                             # same buffer, new contents
+        y_replayed = replay().clone()
+        y2 = step(x2)
+    ops.check_status()
+    assert torch.equal(y_replayed, y2) and not torch.equal(y_replayed, y_launched)
+    assert backend.WATCH_STATUS is True

@@ -252,3 +252,19 @@ def test_chain_support_matrix():
     rc = L.dirotq_linear_forward_chain(C.byref(up), C.c_void_p(0x1000), 128, None, C.c_void_p(0x1000), 1 << 30, C.byref(bad),
                                        C.c_void_p(0x1000), 1 << 30, None, None)
     assert rc == -2 and b"not supported" in L.dirotq_error_string(rc)
+
+
+def test_modulation_vectors_are_taken_through_their_views():
+    """ops._mod_vec: the per-sample pitch of a modulation vector given as a chunk of a larger tensor (no copy)."""
+    from dirotq_b200 import ops
+    B, D = 3, 64
+    mod = torch.zeros(B, 6 * D, dtype=torch.bfloat16)
+    shift, scale = mod[:, None].chunk(6, dim=-1)[:2]                       # [B, 1, D] views, sample stride 6 D
+    v, pitch = ops._mod_vec(scale, B, D)
+    assert pitch == 6 * D and v.data_ptr() == scale.data_ptr() and v.shape == (B, D)
+    table = torch.zeros(B, 6, D, dtype=torch.bfloat16).chunk(6, dim=1)[3]  # adaLN-single: [B, 1, D] of a [B, 6, D] tensor
+    v, pitch = ops._mod_vec(table, B, D)
+    assert pitch == 6 * D and v.data_ptr() == table.data_ptr()
+    v, pitch = ops._mod_vec(torch.zeros(1, D, dtype=torch.bfloat16), B, D)   # one vector shared by all samples
+    assert pitch == 0
+    assert ops._mod_vec(None, B, D) == (None, 0)
