@@ -68,6 +68,8 @@ SIGNATURES = {
     "dirotq_linear_workspace_bytes": (_SZ, [C.POINTER(LinearC), _I64]),
     "dirotq_linear_forward": (C.c_int, [C.POINTER(LinearC), _P, _I64, _P, _P, _SZ, _P, _P]),
     "dirotq_linear_gemm": (C.c_int, [C.POINTER(LinearC), _I64, _P, _P, _SZ, _P, _P]),
+    "dirotq_expand_weight_panel_f16_layout": (C.c_int, [_I32, _I64, _P, _P, _P, _I32, _P]),
+    "dirotq_linear_uses_half_chunks": (C.c_int, [C.POINTER(LinearC)]),
     "dirotq_layernorm_modulate": (C.c_int, [_P, _I64, _I32, _I64, _P, _P, _I64, _F, _P, _P]),
     "dirotq_gated_residual": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _I32, _I64, _P, _P]),
     "dirotq_qkv_norm_rope": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _P, _P, _P, _P, _I64, _I64, _F, _P, _P, _P, _P]),

@@ -198,7 +198,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     if CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and M <= PANEL_CACHE_MAX_ROWS:
         pk = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks, st.w_codes,
                                   st.w_scales, st.w_sum)
-        st.folded.panel = ops.expand_weight_panel_f16(pk, st.folded)
+        half = bool(_lib.lib().dirotq_linear_uses_half_chunks(C.byref(st.c_struct())))
+        st.folded.panel = ops.expand_weight_panel_f16(pk, st.folded, half)
         st._c = None
         if st.shared is None and st.handed is None:
             st._ws = {}                 # the workspace no longer needs room for a per-call panel
@@ -353,6 +354,11 @@ CACHE_WEIGHT_PANEL = "auto"
 PANEL_CACHE_MAX_ROWS = 8192
 
 
+def _half_chunks(fmt: ops.ActFormat, lay: ops.ActLayout) -> bool:
+    """dirotq_linear_uses_half_chunks for a layer on the 16-bit-conversion GEMM, before its LayerState exists."""
+    return fmt.num_heads > 0 and lay.chunks_per_group == 1 and lay.group <= 32 and fmt.mode != ops.NVFP4_HW
+
+
 def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerState:
     """Build the packed device state of one ActQuantWrapper.
 
@@ -397,7 +403,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
             pk = ops.PackedWeightInt4(N, lay.q_len, lay.group, lay.n_chunks, w_codes, w_scales, w_sum)
             folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
             if CACHE_WEIGHT_PANEL is True:
-                folded.panel = ops.expand_weight_panel_f16(pk, folded)
+                folded.panel = ops.expand_weight_panel_f16(pk, folded, _half_chunks(fmt, lay))
         return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias,
                           float(packed["w_tensor_scale"]), int(packed["n_lossy_groups"]), folded,
                           hadamard_low_dim=had_dim, hadamard_flips=had_flips, w_rowscale=t(packed.get("w_rowscale")))
@@ -456,7 +462,7 @@ def prepare_layer(w, device="cuda", explicit: Optional[dict] = None) -> LayerSta
     if INT4_TENSOR_RATE_GEMM and fmt.mode in (ops.INT4_SYM, ops.INT4_ASYM, ops.INT8_ASYM):
         folded = ops.fold_weight_scales_f16(pk, w_tail_p, lay.tail_total)
         if CACHE_WEIGHT_PANEL is True:
-            folded.panel = ops.expand_weight_panel_f16(pk, folded)
+            folded.panel = ops.expand_weight_panel_f16(pk, folded, _half_chunks(fmt, lay))
     return LayerState(fmt, lay, N, rot_t, perm, w_codes, w_scales, w_sum, w_tail_p, bias, Tw, n_lossy, folded,
                       hadamard_low_dim=had_dim, hadamard_flips=had_flips, w_rowscale=w_rowscale)
 

@@ -299,18 +299,29 @@ size_t dirotq_weight_panel_bytes(int32_t n_chunks, int64_t N) {
   return panel_bytes(n_chunks, N);
 }
 
-int dirotq_expand_weight_panel_f16(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
-                                   void* stream) {
+int dirotq_expand_weight_panel_f16_layout(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
+                                          int32_t half_chunks, void* stream) {
   if (n_chunks <= 0 || N <= 0 || !w_codes || !w_mult || !panel) return DIROTQ_E_ARG;
   if ((reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(w_mult) | reinterpret_cast<uintptr_t>(panel)) & 15)
     return DIROTQ_E_ALIGN;
   return launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, panel,
-                                    static_cast<cudaStream_t>(stream));
+                                    static_cast<cudaStream_t>(stream), half_chunks ? 1 : 0);
+}
+
+int dirotq_expand_weight_panel_f16(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
+                                   void* stream) {
+  return dirotq_expand_weight_panel_f16_layout(n_chunks, N, w_codes, w_mult, panel, 0, stream);
 }
 
 size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int64_t N_panel, int32_t n_chunks, int32_t tail_pitch) {
   if (M < 0 || N_panel < 0 || n_chunks <= 0 || tail_pitch < 0) return 0;
   return carve_f16(M, n_chunks, tail_pitch, N_panel).total;
+}
+
+// Per-head groups of at most 32 channels (SANA: 28) fill less than half of their 64-slot chunk: the 16-bit-conversion GEMM
+// then puts the first halves of two chunks into one operand stage (half the stages, and the stage count sets its time).
+static bool half_chunk_geometry(const ActGeom& g) {
+  return g.H > 0 && g.cpg == 1 && g.group <= 32 && !is_nvfp4(g.mode);
 }
 
 // Where the GEMM's epilogue also quantises its output for a following layer: that layer's activation buffers.
@@ -336,7 +347,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
                                   const void* w_panel, const float* w_colscale, const void* x_tail,
                                   const void* w_tail_scaled, int32_t tail_total, int32_t tail_pitch, const void* bias,
                                   void* y, void* workspace, size_t workspace_bytes, int skip_fold, int act,
-                                  int32_t* status, void* stream, const QuantOut* qo = nullptr) {
+                                  int32_t* status, void* stream, const QuantOut* qo = nullptr, const ActGeom* geom = nullptr) {
   if (a_mode != DIROTQ_INT4_SYM && a_mode != DIROTQ_INT4_ASYM && a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
   if (M < 0 || N <= 0 || n_chunks <= 0 || !x_codes || !x_scales || !w_colscale || (!y && !qo) || !workspace)
     return DIROTQ_E_ARG;
@@ -357,6 +368,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   if (M == 0) return DIROTQ_OK;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int hc = geom && half_chunk_geometry(*geom) ? 1 : 0;      // a resident panel of such a layer has the same layout
   __nv_bfloat16* tail_s = tail_total > 0 ? reinterpret_cast<__nv_bfloat16*>(ws + c.tail) : nullptr;
   const __nv_bfloat16* zeros_in = a_mode != DIROTQ_INT4_SYM ? static_cast<const __nv_bfloat16*>(x_zeros) : nullptr;
   const __nv_bfloat16* tail_in = tail_total > 0 ? static_cast<const __nv_bfloat16*>(x_tail) : nullptr;
@@ -365,7 +377,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
     // panel rebuilt in scratch (the weights stay 4-bit in memory)
     int rc = launch_fold_act_and_expand(static_cast<const __nv_bfloat16*>(x_scales), zeros_in, n_chunks, M, ld_rows(M),
                                         ws + c.rec, reinterpret_cast<float*>(ws + c.rs), tail_in, tail_s, tp,
-                                        static_cast<const uint8_t*>(w_codes), N, w_mult, ws + c.panel, st);
+                                        static_cast<const uint8_t*>(w_codes), N, w_mult, ws + c.panel, st, hc);
     if (rc) return rc;
     w_panel = ws + c.panel;
   } else {
@@ -375,7 +387,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
       if (rc) return rc;
     }
     if (!w_panel) {
-      int rc = launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, ws + c.panel, st);
+      int rc = launch_expand_weight_panel(static_cast<const uint8_t*>(w_codes), n_chunks, N, w_mult, ws + c.panel, st, hc);
       if (rc) return rc;
       w_panel = ws + c.panel;
     }
@@ -402,6 +414,7 @@ static int gemm_w4a4_int_f16_impl(int32_t a_mode, int64_t M, int64_t N, int32_t 
   a.wait_limit_k = wait_limit_k();
   a.force_bn = 0;
   a.act = act;
+  a.half_chunks = hc;
   if (qo) {
     a.q_codes = static_cast<uint8_t*>(qo->codes);
     a.q_scales = static_cast<__nv_bfloat16*>(qo->scales);
@@ -572,7 +585,7 @@ static int linear_stages(const dirotq_linear* lin, const void* x, int64_t M, voi
     return gemm_w4a4_int_f16_impl(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
                                   lin->w_mult, lin->w_panel_f16, lin->w_colscale, tail, lin->w_tail_f16, g.tail_total, g.tail_pitch,
                                   lin->bias, y, ws + w.fold, w.total - w.fold, (stages & 5) ? 0 : 1, lin->epilogue_act,
-                                  status, stream, qo);
+                                  status, stream, qo, &g);
   }
   if (lin->epilogue_act != 0) return DIROTQ_E_UNSUPPORTED;
   return dirotq_gemm_w4a4_int(g.mode, M, lin->out_features, g.n_chunks, codes, scales, zeros, lin->w_codes,
@@ -606,6 +619,12 @@ static int next_takes_epilogue_codes(const dirotq_linear* lin, const dirotq_line
   if (gn.mode != DIROTQ_INT4_SYM && gn.mode != DIROTQ_INT4_ASYM) return 0;
   if (gn.group != 64) return 0;
   return uses_f16_gemm(next, gn) ? 1 : 0;
+}
+
+int dirotq_linear_uses_half_chunks(const dirotq_linear* lin) {
+  ActGeom g;
+  if (!lin || make_geom(&lin->fmt, &g)) return 0;
+  return (uses_f16_gemm(lin, g) && half_chunk_geometry(g)) ? 1 : 0;
 }
 
 int dirotq_linear_chain_supported(const dirotq_linear* lin, const dirotq_linear* next) {

@@ -191,7 +191,9 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   const uint32_t exp_base = smem_u32(smem);
   const uint32_t raw_base = smem_u32(raw_area);
 
-  const int n_main = a.n_chunks;
+  const int n_raw = a.n_chunks;                                    // chunks of codes in the raw stream
+  const bool hc = a.half_chunks != 0;                              // two half-padded chunks per operand stage
+  const int n_main = hc ? (a.n_chunks + 1) >> 1 : a.n_chunks;      // operand stages of codes
   const int n_tail = (a.kt + 63) >> 6;
   const int n_tiles_n = (int)((a.N + BN - 1) / BN);
   const int total_tiles = n_tiles_n * (int)((a.M + 127) / 128);
@@ -208,11 +210,11 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int m0 = (t / n_tiles_n) * 128;
-        for (int c = 0; c < n_main; c += GF_CPS) {
+        for (int c = 0; c < n_raw; c += GF_CPS) {
           if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
           const uint32_t bar = rawf_bar(r.s);
-          const int nv = min(GF_CPS, n_main - c);
+          const int nv = min(GF_CPS, n_raw - c);
           // 8-bit codes: the second 128-byte box is issued only when it holds a chunk (a box that lies
           // wholly outside the tensor is never requested; its bytes are not part of the count either)
           const bool second_box = A8 && nv > 2;
@@ -289,15 +291,60 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     auto exp_slot = [](int qq) { return qq % Cfg::EXP_STAGES; };
     auto exp_phase = [](int qq) { return (uint32_t)((qq / Cfg::EXP_STAGES) & 1); };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      for (int c = 0; c < n_main && ok; c += GF_CPS) {
+      for (int c = 0; c < n_raw && ok; c += GF_CPS) {
         if (!mbar_wait_hot(rawf_bar(r.s), r.ph, abort_flag, a.status, ERR_WAIT_FULL)) { ok = false; break; }
         const uint32_t sraw = raw_base + r.s * Cfg::RAW_STAGE;
-        const int nv = min(GF_CPS, n_main - c);
-        for (int jc = 0; jc < nv; ++jc, ++q) {
+        const int nv = min(GF_CPS, n_raw - c);
+        const int njc = hc ? (nv + 1) >> 1 : nv;               // operand stages this raw stage feeds
+        for (int jc = 0; jc < njc; ++jc, ++q) {
           if (q % Cfg::GROUPS != grp) continue;
           // The row is expanded into registers before the slot is known to be free, so that only the
           // tensor-memory store remains on the path between "slot free" and "stage ready".
           uint32_t y1[32];
+          if (hc) {
+            // half chunks: the first 32 slots of chunks 2 jc and 2 jc + 1, each with its own record, side by side
+            const int c0 = 2 * jc, c1 = 2 * jc + 1;
+            const bool has1 = c1 < nv;
+            const uint2 ka0 = gf_lds64(sraw + Cfg::OFF_C + c0 * 128 * 8 + rowA * 8);
+            const uint2 ka1 = has1 ? gf_lds64(sraw + Cfg::OFF_C + c1 * 128 * 8 + rowA * 8) : make_uint2(0u, 0u);
+            const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (A8) {
+              const uint32_t rb0 = sraw + (c0 >> 1) * (128 * 128) + rowA * 128, rb1 = sraw + (c1 >> 1) * (128 * 128) + rowA * 128;
+              uint4 pq[4];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                pq[u] = gf_lds128(rb0 + ((((c0 & 1) * 4 + u) ^ (rowA & 7)) << 4));
+                pq[2 + u] = has1 ? gf_lds128(rb1 + ((((c1 & 1) * 4 + u) ^ (rowA & 7)) << 4)) : z4;
+              }
+              const uint32_t w16[16] = {pq[0].x, pq[0].y, pq[0].z, pq[0].w, pq[1].x, pq[1].y, pq[1].z, pq[1].w,
+                                        pq[2].x, pq[2].y, pq[2].z, pq[2].w, pq[3].x, pq[3].y, pq[3].z, pq[3].w};
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint2 ka = h ? ka1 : ka0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const uint32_t wl = w16[8 * h + i], wh = w16[8 * h + 4 + i];
+                  uint32_t* y = y1 + 16 * h + 4 * i;
+                  y[0] = hfma2_u(__byte_perm(wl, 0u, 0x4240), ka.x, ka.y);
+                  y[1] = hfma2_u(__byte_perm(wh, 0u, 0x4240), ka.x, ka.y);
+                  y[2] = hfma2_u(__byte_perm(wl, 0u, 0x4341), ka.x, ka.y);
+                  y[3] = hfma2_u(__byte_perm(wh, 0u, 0x4341), ka.x, ka.y);
+                }
+              }
+            } else {
+              const uint32_t rb = sraw + rowA * 128;
+              const int sw = rowA & 7;
+              const uint4 pa0 = gf_lds128(rb + (((2 * c0) ^ sw) << 4));
+              const uint4 pa1 = has1 ? gf_lds128(rb + (((2 * c1) ^ sw) << 4)) : z4;
+              const uint32_t w8[8] = {pa0.x, pa0.y, pa0.z, pa0.w, pa1.x, pa1.y, pa1.z, pa1.w};
+              const uint32_t xr1 = ASYM ? 0u : 0x00080008u;
+              const uint32_t mhi0 = hmul2_2m4(ka0.x), mhi1 = hmul2_2m4(ka1.x);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) expand_word(w8[i], xr1, ka0.x, mhi0, ka0.y, y1 + 4 * i);
+#pragma unroll
+              for (int i = 4; i < 8; ++i) expand_word(w8[i], xr1, ka1.x, mhi1, ka1.y, y1 + 4 * i);
+            }
+          } else {
           const uint2 ka = gf_lds64(sraw + Cfg::OFF_C + jc * 128 * 8 + rowA * 8);
           if constexpr (A8) {
             // 8-bit codes: 64 bytes of this row = four 16-byte pieces of box jc >> 1.  A byte alone in a zero
@@ -331,6 +378,7 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
             const uint32_t xr1 = ASYM ? 0u : 0x00080008u;
 #pragma unroll
             for (int i = 0; i < 8; ++i) expand_word(w8[i], xr1, ka.x, mhi, ka.y, y1 + 4 * i);
+          }
           }
           const int es = exp_slot(q);
           if (!mbar_wait_hot(expe_bar(es), exp_phase(q) ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -714,9 +762,11 @@ fold_scales_kernel(const ST* __restrict__ s, const __nv_bfloat16* __restrict__ z
 // Weight pre-pass: codes + records -> the fp16 panel [N, n_chunks * 64] the GEMM's weight-tile TMA reads.
 // One thread = one row x one chunk: 32 bytes of codes in, 128 bytes out, with the arithmetic and the K
 // order of the activation converters (expand_word), so a dot product pairs the right values.
+// hc != 0 (half chunks: per-head groups of at most 32 channels, whose chunks are half padding): only the first 32 code slots of
+// a chunk are expanded and two chunks share one 64-wide stage of the panel, [N, ceil(n_chunks / 2) * 64].
 __device__ __forceinline__ void expand_weight_panel_block(int block, const uint8_t* __restrict__ wq, int64_t w_row_bytes,
                                                           const uint2* __restrict__ rec, int64_t ld_rec, int64_t N, int n_chunks,
-                                                          uint4* __restrict__ panel) {
+                                                          uint4* __restrict__ panel, int hc) {
   const int64_t tid = (int64_t)block * blockDim.x + threadIdx.x;
   if (tid >= N * n_chunks) return;
   const int64_t n = tid / n_chunks;
@@ -726,6 +776,21 @@ __device__ __forceinline__ void expand_weight_panel_block(int block, const uint8
   const uint2 k = __ldg(rec + (int64_t)c * ld_rec + n);
   const uint32_t w8[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
   const uint32_t mhi = hmul2_2m4(k.x);
+  if (hc) {
+    const int n_stage = (n_chunks + 1) >> 1;
+    uint4* dst = panel + (n * n_stage + (c >> 1)) * 8 + (c & 1) * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t y[4];
+      expand_word(w8[i], 0x00080008u, k.x, mhi, k.y, y);
+      dst[i] = make_uint4(y[0], y[1], y[2], y[3]);
+    }
+    if (c == n_chunks - 1 && !(c & 1)) {              // odd chunk count: the last stage's second half is empty
+#pragma unroll
+      for (int i = 4; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    return;
+  }
   uint4* dst = panel + tid * 8;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -737,10 +802,10 @@ __device__ __forceinline__ void expand_weight_panel_block(int block, const uint8
 
 __global__ void __launch_bounds__(256)
 expand_weight_panel_kernel(const uint8_t* __restrict__ wq, int64_t w_row_bytes, const uint2* __restrict__ rec, int64_t ld_rec,
-                           int64_t N, int n_chunks, uint4* __restrict__ panel) {
+                           int64_t N, int n_chunks, uint4* __restrict__ panel, int hc) {
   pdl_launch_dependents();
   pdl_wait();
-  expand_weight_panel_block((int)blockIdx.x, wq, w_row_bytes, rec, ld_rec, N, n_chunks, panel);
+  expand_weight_panel_block((int)blockIdx.x, wq, w_row_bytes, rec, ld_rec, N, n_chunks, panel, hc);
 }
 
 // Both per-call preparations of one GEMM in one launch (each alone is a few microseconds of launch and latency):
@@ -750,6 +815,7 @@ struct FoldExpandArgs {
   const __nv_bfloat16* tail; __nv_bfloat16* tail_out; int kt_pitch;
   const uint8_t* wq; int64_t w_row_bytes; const uint2* w_rec; int64_t ld_wrec; int64_t N; uint4* panel;
   int fold_blocks;
+  int hc;
 };
 __global__ void __launch_bounds__(256) fold_expand_kernel(const FoldExpandArgs a) {
   pdl_launch_dependents();
@@ -758,15 +824,16 @@ __global__ void __launch_bounds__(256) fold_expand_kernel(const FoldExpandArgs a
     fold_scales_block<__nv_bfloat16>((int)blockIdx.x, a.s, a.z, a.n_chunks, a.rows, a.ld_in, a.rec, a.ld_rec, a.rs, a.tail,
                                      a.tail_out, a.kt_pitch);
   else
-    expand_weight_panel_block((int)blockIdx.x - a.fold_blocks, a.wq, a.w_row_bytes, a.w_rec, a.ld_wrec, a.N, a.n_chunks, a.panel);
+    expand_weight_panel_block((int)blockIdx.x - a.fold_blocks, a.wq, a.w_row_bytes, a.w_rec, a.ld_wrec, a.N, a.n_chunks, a.panel,
+                              a.hc);
 }
 
-int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st) {
+int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st, int hc) {
   if (N <= 0 || n_chunks <= 0) return DIROTQ_OK;
   const int64_t total = N * n_chunks;
   return launch_pdl(expand_weight_panel_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, wq,
                     (int64_t)n_chunks * 32, reinterpret_cast<const uint2*>(rec), f16_ld_weight(N), N, n_chunks,
-                    reinterpret_cast<uint4*>(panel)) == cudaSuccess
+                    reinterpret_cast<uint4*>(panel), hc) == cudaSuccess
              ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
@@ -787,9 +854,10 @@ int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n
 
 int launch_fold_act_and_expand(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm, void* rec,
                                float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, const uint8_t* wq,
-                               int64_t N, const void* w_rec, void* panel, cudaStream_t st) {
+                               int64_t N, const void* w_rec, void* panel, cudaStream_t st, int hc) {
   if (M <= 0 || N <= 0) return DIROTQ_OK;
   FoldExpandArgs a;
+  a.hc = hc;
   a.s = s; a.z = z; a.n_chunks = n_chunks; a.rows = M; a.ld_in = ldm; a.rec = reinterpret_cast<uint2*>(rec);
   a.ld_rec = f16_ld_act(M); a.rs = rs; a.tail = tail; a.tail_out = tail_out; a.kt_pitch = kt_pitch;
   a.wq = wq; a.w_row_bytes = (int64_t)n_chunks * 32; a.w_rec = reinterpret_cast<const uint2*>(w_rec);
@@ -862,8 +930,8 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
   int rc = make_tmap_2d_sw(&tm.xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, (uint64_t)a.x_row_bytes, (uint64_t)a.M,
                            (uint64_t)a.x_row_bytes, 32 * GF_CPS, 128, 32 * GF_CPS);
   if (rc) return rc;
-  rc = make_tmap_2d(&tm.wp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.w_panel, (uint64_t)a.n_chunks * 64, (uint64_t)a.N,
-                    (uint64_t)a.n_chunks * 128, BN);
+  const uint64_t n_stage = a.half_chunks ? (uint64_t)((a.n_chunks + 1) / 2) : (uint64_t)a.n_chunks;
+  rc = make_tmap_2d(&tm.wp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.w_panel, n_stage * 64, (uint64_t)a.N, n_stage * 128, BN);
   if (rc) return rc;
   // without an output tensor (quantise-out only) the map is never used: any valid address will do
   rc = make_tmap_2d_sw(&tm.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y ? (const void*)a.y : a.w_panel, (uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.N * 2,

@@ -150,6 +150,8 @@ struct GemmIntF16Args {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y;            // [M, N]
   int* status;
+  int half_chunks = 0;         // per-head groups of at most 32 channels: two chunks' first halves per operand stage (the
+                               // weight panel is laid out to match: [N, ceil(n_chunks / 2) * 64])
   int force_bn;                // 0 = pick the column-tile width from N
   int act;                     // epilogue activation: 0 none, 1 GELU (tanh form) on the bf16-rounded output
   // Optional: the epilogue ALSO quantises its (activated, bf16-rounded) output rows for a following un-rotated INT4
@@ -205,10 +207,11 @@ int launch_gemm_int(const GemmIntArgs& a, cudaStream_t st);
 int launch_gemm_nvfp4(const GemmFp4Args& a, cudaStream_t st);
 int launch_gemm_nvfp4_pair(const GemmFp4Args& a, int bn, cudaStream_t st);
 int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st);
-int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st);
+int launch_expand_weight_panel(const uint8_t* wq, int n_chunks, int64_t N, const void* rec, void* panel, cudaStream_t st,
+                               int half_chunks = 0);
 int launch_fold_act_and_expand(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm, void* rec,
                                float* rs, const __nv_bfloat16* tail, __nv_bfloat16* tail_out, int kt_pitch, const uint8_t* wq,
-                               int64_t N, const void* w_rec, void* panel, cudaStream_t st);
+                               int64_t N, const void* w_rec, void* panel, cudaStream_t st, int half_chunks = 0);
 int64_t f16_ld_act(int64_t M);
 int64_t f16_ld_weight(int64_t N);
 int launch_fold_act_scales(const __nv_bfloat16* s, const __nv_bfloat16* z, int n_chunks, int64_t M, int64_t ldm,

@@ -350,14 +350,17 @@ def fold_weight_scales_f16(w: PackedWeightInt4, w_tail: Optional[torch.Tensor], 
     return FoldedWeightF16(mult, cs, tail_out)
 
 
-def expand_weight_panel_f16(w: PackedWeightInt4, folded: FoldedWeightF16) -> torch.Tensor:
+def expand_weight_panel_f16(w: PackedWeightInt4, folded: FoldedWeightF16, half_chunks: bool = False) -> torch.Tensor:
     """fp16 [N, n_chunks * 64] panel of (q_w - 8) * s_w / colscale, in the K order of the GEMM's activation
-    converters: what dirotq_gemm_w4a4_int_f16 otherwise rebuilds in its workspace on every call."""
+    converters: what dirotq_gemm_w4a4_int_f16 otherwise rebuilds in its workspace on every call.  half_chunks: the
+    layout of layers with per-head groups of at most 32 channels, [N, ceil(n_chunks / 2) * 64]."""
     n = int(_lib.lib().dirotq_weight_panel_bytes(w.n_chunks, w.N))
     panel = torch.empty(n // 2, dtype=torch.float16, device=w.codes.device)
-    check(_lib.lib().dirotq_expand_weight_panel_f16(w.n_chunks, w.N, _ptr(w.codes), _ptr(folded.mult), _ptr(panel),
-                                                    _stream()), "dirotq_expand_weight_panel_f16")
-    return panel[: w.N * w.n_chunks * 64].view(w.N, w.n_chunks * 64)
+    check(_lib.lib().dirotq_expand_weight_panel_f16_layout(w.n_chunks, w.N, _ptr(w.codes), _ptr(folded.mult), _ptr(panel),
+                                                           1 if half_chunks else 0, _stream()),
+          "dirotq_expand_weight_panel_f16_layout")
+    cols = ((w.n_chunks + 1) // 2 if half_chunks else w.n_chunks) * 64
+    return panel[: w.N * cols].view(w.N, cols)
 
 
 def f16_workspace_bytes(act: ActBuffers, N_panel: int = 0) -> int:

@@ -214,6 +214,12 @@ int dirotq_fold_weight_scales_f16(int32_t n_chunks, int64_t N, const float* w_sc
 size_t dirotq_weight_panel_bytes(int32_t n_chunks, int64_t N);
 int dirotq_expand_weight_panel_f16(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
                                    void* stream);
+/* The same with the panel layout of layers whose per-head groups have at most 32 channels (half_chunks != 0; SANA's
+ * 28): only the first 32 code slots of each chunk are expanded, two chunks per 64-wide stage, panel [N,
+ * ceil(n_chunks / 2) * 64].  dirotq_linear_uses_half_chunks tells whether dirotq_linear_forward reads a resident
+ * panel (dirotq_linear.w_panel_f16) of `lin` in that layout. */
+int dirotq_expand_weight_panel_f16_layout(int32_t n_chunks, int64_t N, const void* w_codes, const void* w_mult, void* panel,
+                                          int32_t half_chunks, void* stream);
 size_t dirotq_gemm_w4a4_int_f16_workspace_bytes(int64_t M, int64_t N_panel, int32_t n_chunks, int32_t tail_pitch);
 int dirotq_gemm_w4a4_int_f16(int32_t a_mode, int64_t M, int64_t N, int32_t n_chunks, const void* x_codes,
                              const void* x_scales, const void* x_zeros, const void* w_codes, const void* w_mult,
@@ -323,6 +329,7 @@ int dirotq_linear_gemm(const dirotq_linear* lin, int64_t M, void* y, void* works
  * 16-bit-conversion GEMM (w_mult set); `next` a 4-bit integer layer, hidden layout, groups of 64, its
  * quantised part and its 16-bit tail both multiples of 64 channels (the tail may be empty), no
  * rotation, no channel selection, width == lin->out_features, w_mult set.  Anything else: DIROTQ_E_UNSUPPORTED, nothing launched. */
+int dirotq_linear_uses_half_chunks(const dirotq_linear* lin);
 int dirotq_linear_chain_supported(const dirotq_linear* lin, const dirotq_linear* next);
 int dirotq_linear_forward_chain(const dirotq_linear* lin, const void* x, int64_t M, void* y, void* workspace,
                                 size_t workspace_bytes, const dirotq_linear* next, void* next_workspace,

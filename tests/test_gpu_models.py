@@ -150,3 +150,26 @@ def test_host_streamed_step_returns_the_same_result():
     torch.cuda.synchronize()
     ops.check_status()
     assert torch.equal(y_host.view(torch.int16), y_ref.cpu().view(torch.int16))
+
+
+@pytest.mark.parametrize("quant,a_sym", [("int4", True), ("int4", False), ("int8", False)])
+@pytest.mark.parametrize("H,M", [(70, 300), (5, 300), (7, 9000)])
+def test_short_per_head_groups_share_operand_stages(quant, a_sym, H, M):
+    """Per-head groups of 28 channels (SANA: d = 32, 4 of them 16-bit) occupy 64-slot chunks that are half padding; the
+    16-bit-conversion GEMM packs the first halves of two chunks into one operand stage.  Odd and even head counts,
+    a small batch (resident weight panel) and a large one (panel rebuilt per call), all three activation formats."""
+    from dirotq_b200 import _lib, backend, dit
+    from dirotq_b200.synth import synth_activations
+    import ctypes as C
+    ld = dit.LayerDef("attn1.to_out.0", H * 32, 256, kind="perhead", tail=4, heads=H, head_dim=32)
+    w = dit.make_wrapped_linear(ld, quant, 900 + H, "cuda", a_sym=a_sym)
+    holder = torch.nn.ModuleDict({"l": w})
+    backend.preconvert_rotations_to_device(holder, "cuda")
+    st = w._b200_state
+    assert _lib.lib().dirotq_linear_uses_half_chunks(C.byref(st.c_struct())) == 1
+    x = synth_activations(M, H * 32, torch.Generator().manual_seed(H)).reshape(1, M, H * 32).cuda()
+    y = _check_layer(w, ld, x)
+    assert (st.folded.panel is not None) == (M <= backend.PANEL_CACHE_MAX_ROWS)
+    if st.folded.panel is not None:
+        assert st.folded.panel.shape == (256, (H + 1) // 2 * 64)
+    assert torch.equal(w(x), y)                                 # second call: same result with the panel in place
