@@ -235,3 +235,31 @@ def test_step_replayed_from_a_cuda_graph():
     ops.check_status()
     assert torch.equal(y_replayed, y2) and not torch.equal(y_replayed, y_launched)
     assert backend.WATCH_STATUS is True
+
+
+def test_fusions_at_the_edges():
+    """Empty and one-row batches through fused q/k/v groups and feed-forward hand-offs; an explicit output buffer for a
+    member of a fused group; dropping held tensors between steps."""
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    step = dit.LinearPathStep(dit.flux_double_block(k_down=0), 1, "int4", device="cuda", seed=4300)
+    backend.preconvert_rotations_to_device(step, "cuda")
+    backend.fuse_gelu_modules(step)
+    assert backend.fuse_ffn_quantise(step, keep_hidden=False) == 1 and backend.fuse_sibling_gemms(step) == 1
+    ref = dit.LinearPathStep(dit.flux_double_block(k_down=0), 1, "int4", device="cuda", seed=4300)   # same weights, no fusion
+    backend.preconvert_rotations_to_device(ref, "cuda")
+    backend.fuse_gelu_modules(ref)
+    for M in (0, 1, 77):
+        x = synth_activations(max(M, 1), 3072, torch.Generator().manual_seed(M))[:M].reshape(1, M, 3072).cuda()
+        with torch.no_grad():
+            y, y_ref = step(x), ref(x)
+        assert y.shape == (1, M, 3072) and torch.equal(y, y_ref)
+    ops.check_status()
+    # a member of a fused group asked to write into the caller's buffer
+    q = step.layers[0]._b200_state
+    x2d = synth_activations(64, 3072, torch.Generator().manual_seed(5)).cuda()
+    out = torch.empty(64, q.out_features, dtype=torch.bfloat16, device="cuda")
+    got = backend.linear_forward(q, x2d, out=out)
+    assert got is out and torch.equal(out, backend.linear_forward(ref.layers[0]._b200_state, x2d))
+    assert backend.release_shared_activations(step) >= 1 and q.shared.x_ref is None and q.shared.y_all is None
+    ops.check_status()
