@@ -292,11 +292,19 @@ class HostStreamedStep:
         self.in_ready = [torch.cuda.Event() for _ in range(2)]
         self.in_free = [torch.cuda.Event() for _ in range(2)]
         self.out_done = torch.cuda.Event()
+        self.out_free = [torch.cuda.Event() for _ in range(2)]
+        self.replay = None
         self.i = 0
         main = torch.cuda.current_stream(self.dev)
-        for e in self.in_free:
+        for e in self.in_free + self.out_free:
             e.record(main)
         self.out_done.record(main)
+
+    def enable_graphs(self):
+        """Replay the step from a CUDA graph, one per input buffer (small batches: Python's launch cost shows).  The
+        result of a replay lives in the graph's own memory; it is overwritten two calls later, after its copy to the
+        host has completed."""
+        self.replay = [GraphedCall(lambda b=b: self.step(self.x_dev[b])) for b in range(2)]
 
     def __call__(self):
         b = self.i & 1
@@ -307,15 +315,21 @@ class HostStreamedStep:
             self.x_dev[b].copy_(self.x_host, non_blocking=True)
             self.in_ready[b].record(self.s_in)
         main.wait_event(self.in_ready[b])
-        y = self.step(self.x_dev[b])
+        if self.replay is not None:
+            main.wait_event(self.out_free[b])                # the host copy of this graph's previous result is done
+            y = self.replay[b]()
+        else:
+            y = self.step(self.x_dev[b])
         self.in_free[b].record(main)
         done = torch.cuda.Event()
         done.record(main)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(done)
-            y.record_stream(self.s_out)
+            if self.replay is None:
+                y.record_stream(self.s_out)
             self.y_host.copy_(y.reshape(self.y_host.shape), non_blocking=True)
             self.out_done.record(self.s_out)
+            self.out_free[b].record(self.s_out)
         return y
 
     def finish(self):

@@ -150,6 +150,17 @@ def test_host_streamed_step_returns_the_same_result():
     torch.cuda.synchronize()
     ops.check_status()
     assert torch.equal(y_host.view(torch.int16), y_ref.cpu().view(torch.int16))
+    # the same replayed from CUDA graphs (one per input buffer), with a new input on every call
+    run.enable_graphs()
+    for seed in (10, 11, 12, 13, 14):
+        x_new = synth_activations(512, 1152, torch.Generator().manual_seed(seed)).reshape(1, 512, 1152)
+        torch.cuda.synchronize()                            # the previous call's copy of x_host has been made
+        x_host.copy_(x_new)
+        run()
+        run.finish()
+        torch.cuda.synchronize()
+        assert torch.equal(y_host.view(torch.int16), step(x_new.cuda()).cpu().view(torch.int16)), seed
+    ops.check_status()
 
 
 @pytest.mark.parametrize("quant,a_sym", [("int4", True), ("int4", False), ("int8", False)])
