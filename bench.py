@@ -435,11 +435,16 @@ def run_ours(args):
     if not is_flux and not args.no_graph and M <= 8192:
         try:
             from dirotq_b200.dit import GraphedCall
-            graphed[0] = GraphedCall(lambda: step(x_dev))
+            replay = GraphedCall(lambda: step(x_dev))
             for _ in range(2):
-                step_resident()
+                replay()
             ops.check_status(dev)
-            streamed.enable_graphs()                     # the end-to-end path replays too (one graph per input buffer)
+            # keep whichever form is faster here (max over ranks, so every rank decides alike): replay wins when Python's
+            # launch cost shows, plain launches keep their programmatic overlap between consecutive kernels
+            t_launch, t_replay = D_.timed(lambda: step(x_dev), 3), D_.timed(replay, 3)
+            if t_replay < t_launch:
+                graphed[0] = replay
+                streamed.enable_graphs()                 # the end-to-end path replays too (one graph per input buffer)
         except Exception as e:      # capture is an optimisation, never a requirement
             graphed[0] = None
             print(f"CUDA graph capture failed ({type(e).__name__}: {e}); plain launches", file=sys.stderr)
