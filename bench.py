@@ -319,6 +319,14 @@ class Dist:
             self.dist.barrier()
         torch.cuda.synchronize()
 
+    def all_true(self, flag: bool) -> bool:
+        """True if `flag` holds on every rank (so that all ranks take the same branch around later collectives)."""
+        if self.world == 1:
+            return bool(flag)
+        t = torch.tensor([1 if flag else 0], device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(int(t.item()))
+
     def timed(self, fn, steps):
         """Device milliseconds of `steps` calls, bracketed by barrier + synchronize, max over ranks."""
         self.barrier()
@@ -433,21 +441,26 @@ def run_ours(args):
     # small shards (one or two samples per GPU) are short enough for Python's launch cost to show: replay them from a
     # CUDA graph captured once; larger batches gain nothing and keep plain launches
     if not is_flux and not args.no_graph and M <= 8192:
+        replay = None
         try:
             from dirotq_b200.dit import GraphedCall
             replay = GraphedCall(lambda: step(x_dev))
             for _ in range(2):
                 replay()
             ops.check_status(dev)
+        except Exception as e:      # capture is an optimisation, never a requirement
+            replay = None
+            print(f"CUDA graph capture failed ({type(e).__name__}: {e}); plain launches", file=sys.stderr)
+        if D_.all_true(replay is not None):
             # keep whichever form is faster here (max over ranks, so every rank decides alike): replay wins when Python's
             # launch cost shows, plain launches keep their programmatic overlap between consecutive kernels
             t_launch, t_replay = D_.timed(lambda: step(x_dev), 3), D_.timed(replay, 3)
             if t_replay < t_launch:
                 graphed[0] = replay
-                streamed.enable_graphs()                 # the end-to-end path replays too (one graph per input buffer)
-        except Exception as e:      # capture is an optimisation, never a requirement
-            graphed[0] = None
-            print(f"CUDA graph capture failed ({type(e).__name__}: {e}); plain launches", file=sys.stderr)
+                try:
+                    streamed.enable_graphs()             # the end-to-end path replays too (one graph per input buffer)
+                except Exception as e:
+                    print(f"CUDA graph capture of the streamed step failed ({type(e).__name__}: {e})", file=sys.stderr)
     sampler = ClockSampler(D_.local)
     if rank == 0:
         sampler.start()
@@ -561,15 +574,18 @@ def denoise_record(D_, family, quant, gbatch, world, strong, args):
         ms = D_.timed(lambda: step(*inputs), 4) / 4
         lin_ms = denoise.time_wrapped_linears(step, inputs)
         if not args.no_graph:
+            replay = None
             try:
                 from dirotq_b200.dit import GraphedCall
                 replay = GraphedCall(lambda: step(*inputs))
                 replay()
                 ops.check_status(dev)
-                ms_graph = D_.timed(replay, 4) / 4
-                del replay
             except Exception as e:
+                replay = None
                 print(f"CUDA graph capture of the model-shaped step failed ({type(e).__name__}: {e})", file=sys.stderr)
+            if D_.all_true(replay is not None):          # every rank takes the timed (collective) branch, or none
+                ms_graph = D_.timed(replay, 4) / 4
+            del replay
     lin, _ = step.ops_per_step(batch)
     rec = {"family": family, "quant": quant, "blocks": note, "batch_per_gpu": batch, "tokens": step.shape["tokens"],
            "text_tokens": step.shape["text"], "step_ms": ms if ms_graph is None else min(ms, ms_graph),
