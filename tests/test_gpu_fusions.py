@@ -263,3 +263,44 @@ def test_fusions_at_the_edges():
     assert got is out and torch.equal(out, backend.linear_forward(ref.layers[0]._b200_state, x2d))
     assert backend.release_shared_activations(step) >= 1 and q.shared.x_ref is None and q.shared.y_all is None
     ops.check_status()
+
+
+def test_sibling_gemm_on_dense_nvfp4_weights_with_per_channel_scales():
+    """Dense NVFP4 layers (the reference's quantised cache holds dequantised weights) are packed by the two-level recipe
+    with one scale per output channel: a fused q / k / v layer carries the members' scales side by side and the 16-bit
+    branch divided by them; every member's columns equal its own GEMM's output."""
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.wrapper import ActQuantWrapper
+    g = torch.Generator().manual_seed(21)
+    D, k = 384, 64
+    U = O.random_orthogonal(D, g).float()
+
+    def build():
+        attn = nn.Module()
+        gw = torch.Generator().manual_seed(22)
+        for i, (leaf, N) in enumerate((("to_q", 256), ("to_k", 128), ("to_v", 384))):
+            W_rot = (torch.randn(N, D, generator=gw) * 0.05 * (1 + i)) @ U
+            deq, _, _ = O.weight_quant_nvfp4(W_rot[:, : D - k])
+            lin = nn.Linear(D, N, bias=(i != 1)).to(torch.bfloat16)
+            lin.weight.data.copy_(torch.cat([deq, W_rot[:, D - k:]], dim=1).to(torch.bfloat16))
+            if lin.bias is not None:  # nn.Linear draws its bias from the global generator: both copies take this one
+                lin.bias.data.copy_(torch.randn(N, generator=gw).to(torch.bfloat16))
+            w = ActQuantWrapper(lin)
+            w.quantizer.configure(bits=4, groupsize=16, sym=True, high_bits_length=k, quant_dtype="nvfp4")
+            w.rotation = U.clone()
+            w._unrot_fused = True
+            attn.add_module(leaf, w)
+        root = nn.Module()
+        root.add_module("attn1", attn)
+        backend.preconvert_rotations_to_device(root, "cuda")
+        return root, [attn.to_q, attn.to_k, attn.to_v]
+
+    root, ws = build()
+    root2, ws2 = build()
+    assert all(w._b200_state.w_rowscale is not None for w in ws)
+    assert backend.fuse_sibling_gemms(root) == 1
+    x = O.synth_activations(500, D, g).reshape(1, 500, D).to(torch.bfloat16).cuda()
+    for w, w2 in zip(ws, ws2):
+        assert torch.equal(w(x), w2(x))
+    assert ws[0]._b200_state.shared.hits == 2
+    ops.check_status()
