@@ -159,7 +159,7 @@ def kernel_launches(st: Optional[LayerState], w4a16=None) -> int:
         fold = not (st.shared is not None and st.member_id > 0)
         n += 1 if (fold or st.folded.panel is None) else 0
     follower = (st.shared is not None and st.member_id > 0) or st.chain_fed
-    two_step = st.rot_t is not None and (st.perm_idx is not None or st.fmt.group_size <= 0) and st.fmt.num_heads == 0
+    two_step = _rotates_then_quantises(st)
     if two_step and not follower:
         n += 1                              # rotation into scratch, then the quantise kernel
     if (st.rot_t is None or two_step) and st.layout.tail_total > 0 and not follower:
@@ -167,6 +167,22 @@ def kernel_launches(st: Optional[LayerState], w4a16=None) -> int:
     if st.hadamard_low_dim:
         n += 1
     return n
+
+
+def _rotates_then_quantises(st: LayerState) -> bool:
+    """Mirror of the library's routing: formats the rotation kernel's epilogue cannot quantise (a channel selection after
+    the rotation, per-token scales, integer groups other than 64 under a hidden rotation, per-head groups whose 32-column
+    reads would leave the head) rotate into scratch and quantise in a second launch."""
+    f = st.fmt
+    if st.rot_t is None:
+        return False
+    if st.perm_idx is not None or f.group_size <= 0:
+        return True
+    if f.mode in (ops.NVFP4_HW, ops.NVFP4_REF):
+        return False
+    if f.num_heads == 0:
+        return f.group_size != 64
+    return (f.head_dim - f.tail_len + 31) // 32 * 32 > f.head_dim
 
 
 def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -497,10 +497,16 @@ int dirotq_gemm_w4a4_nvfp4(int64_t M, int64_t N, int32_t n_chunks, const void* x
 struct WsCarve {
   size_t codes, scales, zeros, tail, xrot, fold, total;
 };
-// Layers whose quantiser cannot run in the rotation's epilogue -- a channel selection after the rotation, or one scale
-// per row -- rotate into a bf16 scratch tensor first and quantise from there.
+// Layers whose quantiser cannot run in the rotation's epilogue rotate into a bf16 scratch tensor first and quantise
+// from there: a channel selection after the rotation, one scale per row, integer groups of another size than the hidden
+// epilogue's 64, or a per-head group whose 32-column reads would run past the head (head_dim - tail, rounded up to 32,
+// above head_dim).
 static bool rotates_then_quantises(const dirotq_linear* lin, const ActGeom& g) {
-  return lin->rot_t != nullptr && (lin->perm_idx != nullptr || g.per_token);
+  if (!lin->rot_t) return false;
+  if (lin->perm_idx || g.per_token) return true;
+  if (is_nvfp4(g.mode)) return false;
+  if (g.H == 0) return g.group != 64;
+  return ((g.group + 31) / 32) * 32 > g.d;
 }
 static bool uses_f16_gemm(const dirotq_linear* lin, const ActGeom& g) {
   return lin->w_mult != nullptr &&

@@ -835,13 +835,18 @@ int launch_rotate_quantize(const ActGeom& g, const void* x, const void* rot_t, i
   a.K = g.D;
   a.bias = nullptr;
   a.ldm = ld_rows(M);
-  a.BN = pick_bn(g, M);
+  const bool rot_only = a.codes == nullptr;
+  if (rot_only && !a.x_rot) return DIROTQ_E_ARG;
+  // The rotation-only epilogue stores whole 32-column patches, so it takes the tile widths of the hidden layouts even
+  // under a per-head rotation (whose whole-head widths, 144 for 72-wide heads, are not multiples of 32); the K range of
+  // a tile follows the heads its columns touch either way.
+  ActGeom g_tile = g;
+  if (rot_only) g_tile.H = 0;
+  a.BN = pick_bn(g_tile, M);
   if (a.BN <= 0) return DIROTQ_E_UNSUPPORTED;
   a.n_tiles = ceil_div(g.D, a.BN);
   a.m_tiles = (int)((M + 127) / 128);
   a.band = g.H > 0 ? g.d : 0;
-  const bool rot_only = a.codes == nullptr;
-  if (rot_only && !a.x_rot) return DIROTQ_E_ARG;
   if (!rot_only && g.H > 0) {
     // 32-column TMEM reads of a head's group must stay inside the head
     if (((g.group + 31) / 32) * 32 > g.d) return DIROTQ_E_UNSUPPORTED;

@@ -55,7 +55,12 @@ typedef struct dirotq_act_format {
                          * dirotq_rotate_quantize (dirotq_quantize_act returns DIROTQ_E_UNSUPPORTED). */
   int32_t head_dim;     /* d (per-head only; H * d == D) */
   int32_t tail_len;     /* high_bits_length: hidden = total, per-head = per head */
-  int32_t group_size;   /* hidden: 64 (INT) or 16 (NVFP4); per-head: ignored, group = d - tail_len.
+  int32_t group_size;   /* hidden: 1..128 (INT; a group takes one or two 64-slot chunks) or 16 (NVFP4); per-head:
+                         * ignored, group = d - tail_len.  The fused rotate + quantise kernel quantises hidden INT
+                         * groups of 64 and per-head groups with ceil32(d - tail_len) <= d; for the other integer
+                         * formats dirotq_rotate_quantize returns DIROTQ_E_UNSUPPORTED with codes != NULL and
+                         * dirotq_linear_forward rotates into scratch and quantises from there (M * D * 2 bytes of
+                         * workspace more, counted by dirotq_linear_workspace_bytes).
                          * <= 0 (integer modes, hidden layout): ONE scale / zero point per row over the quantised
                          * channels, zero included in the extrema (ActQuantizer._find_params,
                          * utils/quant_utils.py:242-271); codes keep the 64-slot chunk layout and the row's scale

@@ -127,6 +127,94 @@ def test_per_token_activation_scales(name):
     assert torch.equal(backend.linear_forward_static(st, x2d), y.reshape(M, -1))
 
 
+@pytest.mark.parametrize("gs,sym,bits,D,k,N,M", [(128, True, 4, 1152, 8, 1160, 128), (32, False, 4, 576, 16, 64, 2048),
+                                                (32, True, 4, 2240, 320, 1160, 7), (128, False, 8, 576, 72, 200, 129),
+                                                (32, False, 8, 1000, 72, 1152, 128)])
+def test_hidden_rotation_with_other_integer_group_sizes(gs, sym, bits, D, k, N, M):
+    """The reference's quantiser takes any groupsize (ActQuantizer.configure, utils/quant_utils.py:182-199); the rotation
+    kernel's epilogue quantises groups of 64 only.  Other sizes rotate into scratch and quantise from there: codes and
+    scales bit-exact against the reference quantiser on the rotated tensor the kernel produced, output within the
+    layer tolerance."""
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.wrapper import ActQuantWrapper
+    from gpu_helpers import assert_act_matches_oracle
+    g = torch.Generator().manual_seed(gs * 7 + D)
+    x = O.synth_activations(M, D, g).reshape(1, M, D)
+    U = O.random_orthogonal(D, g).float()
+    q_len = D - k
+    ng = (q_len + gs - 1) // gs
+    Wp = torch.nn.functional.pad(torch.randn(N, q_len, generator=g) * 0.05, (0, ng * gs - q_len)).reshape(N, ng, gs)
+    s = (Wp.abs().amax(-1, keepdim=True) / 7).clamp(min=1e-5).to(torch.float16).float()
+    deq = ((Wp / s).round().clamp(-8, 7) * s).reshape(N, -1)[:, :q_len]
+    lin = nn.Linear(D, N, bias=True).to(torch.bfloat16)
+    lin.weight.data.copy_(torch.cat([deq, torch.randn(N, k, generator=g) * 0.02], dim=1).to(torch.bfloat16))
+    lin.bias.data.copy_((torch.randn(N, generator=g) * 0.1).to(torch.bfloat16))
+    w = ActQuantWrapper(lin)
+    w.quantizer.configure(bits=bits, groupsize=gs, sym=sym, high_bits_length=k, quant_dtype="int")
+    w.rotation = U
+    w._unrot_fused = True
+    y = w(x.cuda())
+    ops.check_status()
+    st = w._b200_state
+    assert st.fmt.group_size == gs and backend.kernel_launches(st) >= 4      # rotate, quantise, tail copy, (fold +) GEMM
+    x2d = x.reshape(M, D).cuda()
+    x_rot = ops.rotate(x2d, st.rot_t)
+    with pytest.raises(RuntimeError):                       # the fused epilogue has groups of 64 only
+        ops.rotate_quantize(x2d, st.rot_t, st.fmt)
+    assert_act_matches_oracle(ops.quantize_act(x_rot, st.fmt), x_rot)
+    r = O.act_quant(x_rot.cpu().unsqueeze(0), O.QuantCfg(bits, gs, sym, 1.0, k, "int"))
+    y_same = torch.nn.functional.linear(r.full.to(torch.bfloat16), lin.weight.data.cpu(), lin.bias.data.cpu()).float()
+    assert rel_l2(y.float().cpu(), y_same) <= REL and cosine(y.float().cpu(), y_same) >= COS
+    assert torch.equal(backend.linear_forward_static(st, x2d), y.reshape(M, -1))
+
+
+@pytest.mark.parametrize("H,d,t,bits,sym,N,M", [(5, 48, 8, 4, True, 1160, 128), (16, 72, 1, 8, False, 200, 500),
+                                                (12, 40, 1, 4, False, 64, 1), (5, 48, 9, 4, True, 1152, 500)])
+def test_per_head_groups_that_do_not_fit_the_fused_epilogue(H, d, t, bits, sym, N, M):
+    """The per-head epilogue of the rotation kernel reads a head's group 32 columns at a time; a group whose rounded-up
+    width exceeds the head (head_dim 48 with 8 high channels, 72 with 1, ...) rotates into scratch and quantises from
+    there instead.  Weight columns are per head [low | high] (the reference re-interleaves before its linear,
+    dirotq_fused_unrotation_fast.py:99-102)."""
+    from dirotq_b200 import backend, ops
+    from dirotq_b200.wrapper import ActQuantWrapper
+    from gpu_helpers import assert_act_matches_oracle
+    g = torch.Generator().manual_seed(H * 100 + d + t)
+    D, gl = H * d, d - t
+    x = O.synth_activations(M, D, g).reshape(1, M, D)
+    Uph = torch.stack([O.random_orthogonal(d, g).float() for _ in range(H)])
+    W_low = torch.randn(N, H, gl, generator=g) * 0.05
+    s = (W_low.abs().amax(-1, keepdim=True) / 7).clamp(min=1e-5).to(torch.float16).float()
+    deq = (W_low / s).round().clamp(-8, 7) * s
+    W = torch.cat([deq, torch.randn(N, H, t, generator=g) * 0.02], dim=2).reshape(N, D).to(torch.bfloat16)
+    lin = nn.Linear(D, N, bias=True).to(torch.bfloat16)
+    lin.weight.data.copy_(W)
+    lin.bias.data.copy_((torch.randn(N, generator=g) * 0.1).to(torch.bfloat16))
+    w = ActQuantWrapper(lin)
+    w.quantizer.configure(bits=bits, groupsize=64, sym=sym, high_bits_length=t, quant_dtype="int")
+    w.rotation_per_head = Uph
+    w.num_heads, w.head_dim = H, d
+    w._unrot_fused = True
+    y = w(x.cuda())
+    ops.check_status()
+    st = w._b200_state
+    assert st.n_lossy_groups == 0 and backend._rotates_then_quantises(st)
+    x2d = x.reshape(M, D).cuda()
+    with pytest.raises(RuntimeError):
+        ops.rotate_quantize(x2d, st.rot_t, st.fmt)
+    x_rot = ops.rotate(x2d, st.rot_t, H, d)
+    # rotation-only launches under a per-head rotation: whole-head tile widths (144 for 72-wide heads) are not multiples
+    # of the epilogue's 32-column store patches
+    want_rot = O.rotate_per_head(x, Uph, fp32=True).reshape(M, D)
+    assert rel_l2(x_rot.float().cpu(), want_rot) <= 5e-3
+    assert_act_matches_oracle(ops.quantize_act(x_rot, st.fmt), x_rot)
+    spec = O.LayerSpec(lin.weight.data.cpu(), lin.bias.data.cpu(), O.QuantCfg(bits, 64, sym, 1.0, t, "int"), rotation_per_head=Uph)
+    y_fast, y_slow = O.fused_forward(x, spec, fp32=False).float(), O.fused_forward(x, spec, fp32=True).float()
+    gap = rel_l2(y_fast, y_slow)
+    yc = y.float().cpu()
+    assert rel_l2(yc, y_fast) <= max(REL, 1.5 * gap) and cosine(yc, y_fast) >= 0.995
+    assert torch.equal(backend.linear_forward_static(st, x2d), y.reshape(M, -1))
+
+
 @pytest.mark.parametrize("fused", [True, False])
 def test_per_head_rotation_with_nvfp4_activations(fused, monkeypatch):
     """Per-head rotation + NVFP4 (head_dim - tail a multiple of 16): the heads' low coefficients side by side in blocks

@@ -221,6 +221,16 @@ def test_per_token_layout_and_two_step_workspace():
     assert ws(_linear_c(tok, 1152, rot=True)) >= base + M * 1152 * 2
     assert ws(_linear_c(g64, 1152, rot=True, perm=True)) >= base + M * 1152 * 2
     assert ws(_linear_c(tok, 1152, rot=False)) == ws(_linear_c(g64, 1152, rot=False))
+    # other formats the rotation's epilogue does not quantise: integer groups of 32 / 128 under a hidden rotation, and
+    # per-head groups whose 32-column reads would leave the head (72-wide heads with 1 high channel; not with 9)
+    for gs in (32, 128):
+        f = ops.ActFormat(ops.INT4_SYM, 1152, 64, group_size=gs)
+        assert ws(_linear_c(f, 1152, rot=True)) >= ws(_linear_c(f, 1152, rot=False)) + M * 1152 * 2
+    ph = lambda t: ops.ActFormat(ops.INT4_SYM, 1152, t, num_heads=16, head_dim=72)
+    assert ws(_linear_c(ph(1), 1152, rot=True)) >= ws(_linear_c(ph(1), 1152, rot=False)) + M * 1152 * 2
+    assert ws(_linear_c(ph(9), 1152, rot=True)) == ws(_linear_c(ph(9), 1152, rot=False))
+    f16 = ops.ActFormat(ops.NVFP4_HW, 1152, 64, group_size=16)
+    assert ws(_linear_c(f16, 1152, rot=True, w_mult=False)) == ws(_linear_c(f16, 1152, rot=False, w_mult=False))
 
 
 def test_chain_support_matrix():
