@@ -544,6 +544,9 @@ def qkv_norm_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int,
         assert o.is_contiguous() and o.shape == (B, T_total, heads, d)
     if cos is not None:
         assert cos.shape == (T_total, d) and sin.shape == (T_total, d) and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.dtype == torch.bfloat16 and sin.dtype == torch.bfloat16, "rotary tables: bf16 [T_total, d]"
+    for w_ in (w_q, w_k):
+        assert w_ is None or (w_.dtype == torch.bfloat16 and w_.shape == (d,) and w_.is_contiguous()), "norm weights: bf16 [d]"
     check(_lib.lib().dirotq_qkv_norm_rope(_ptr(q), _ptr(k), _ptr(v), pitch, B, T, heads, d, _ptr(w_q), _ptr(w_k), _ptr(cos),
                                           _ptr(sin), T_total, t0, float(eps), _ptr(out[0]), _ptr(out[1]), _ptr(out[2]),
                                           _stream()), "dirotq_qkv_norm_rope")
