@@ -86,6 +86,9 @@ def parse():
     ap.add_argument("--cache-weight-panel", action="store_true",
                     help="keep each INT4 layer's fp16 weight panel resident (2 bytes per weight) instead of rebuilding it "
                          "from the 4-bit codes on every call")
+    ap.add_argument("--no-resident-panels", action="store_true",
+                    help="large-batch INT4 layers rebuild their fp16 weight panel on every call (weights stay 0.5 byte each "
+                         "in device memory) instead of keeping it while the device's budget for 16-bit weight copies lasts")
     ap.add_argument("--exact-int", action="store_true",
                     help="INT4 layers through the exact-integer kind::i8 GEMM instead of the tensor-rate fp16 one")
     ap.add_argument("--profile-case", default="", nargs="?", const="layers",
@@ -527,6 +530,11 @@ def run_ours(args):
                        "ffn_pairs_quantised_in_epilogue": n_chained, "qkv_groups_as_one_gemm": n_qkv,
                        "execution": ("CUDA graph replay of the step (captured once after the warm-up)" if graphed[0] is not None
                                      else "kernels launched from Python, programmatic dependent launch between them"),
+                       "weight_copies": ("4-bit only" if quant == "nvfp4" or args.exact_int else
+                                         "4-bit + resident fp16 panels (--cache-weight-panel)" if args.cache_weight_panel else
+                                         "4-bit; fp16 panels rebuilt per call (--no-resident-panels)" if args.no_resident_panels
+                                         else "4-bit + fp16 panels kept while under a sixteenth of device memory "
+                                              f"({backend.resident_weight_copy_bytes() / 2**20:.0f} MiB resident)"),
                        "l2": l2_note,
                        "linear_gflop_per_step_per_gpu": lin_ops / 1e9, "rotation_gflop_per_step_per_gpu": rot_ops / 1e9},
             "e2e": {"value": world * lin_ops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
@@ -934,6 +942,9 @@ if __name__ == "__main__":
     if a.cache_weight_panel:
         from dirotq_b200 import backend as _backend
         _backend.CACHE_WEIGHT_PANEL = True
+    if a.no_resident_panels:
+        from dirotq_b200 import backend as _backend
+        _backend.PANEL_CACHE_BUDGET_FRACTION = 0.0
     if a.exact_int:
         from dirotq_b200 import backend as _backend
         _backend.INT4_TENSOR_RATE_GEMM = False

@@ -16,6 +16,7 @@ from __future__ import annotations
 import ctypes as C
 import sys
 import warnings
+import weakref
 import dataclasses
 from dataclasses import dataclass, field
 from typing import Dict, Optional
@@ -109,6 +110,7 @@ class LayerState:
     handed_key: Optional[tuple] = None
     chain_hits: int = 0
     chain_fed: bool = False                          # a producer's epilogue quantises for this layer
+    panel_declined: bool = False                     # a large-batch call found the resident-panel budget spent
     _c: Optional[LinearC] = None
     _ws: Dict[int, torch.Tensor] = field(default_factory=dict)
 
@@ -211,7 +213,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
     y = out if out is not None else torch.empty(M, st.out_features, dtype=torch.bfloat16, device=x2d.device)
     if st.hadamard_low_dim:
         x2d = ops.hadamard_low(x2d, st.hadamard_low_dim, st.hadamard_flips)
-    if CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and M <= PANEL_CACHE_MAX_ROWS:
+    if (CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and not st.panel_declined and
+            _panel_budget_take(st, x2d.device, 2 * st.out_features * st.layout.n_chunks * 64, M <= PANEL_CACHE_MAX_ROWS)):
         pk = ops.PackedWeightInt4(st.out_features, st.layout.q_len, st.layout.group, st.layout.n_chunks, st.w_codes,
                                   st.w_scales, st.w_sum)
         half = bool(_lib.lib().dirotq_linear_uses_half_chunks(C.byref(st.c_struct())))
@@ -219,6 +222,8 @@ def linear_forward(st: LayerState, x2d: torch.Tensor, out: Optional[torch.Tensor
         st._c = None
         if st.shared is None and st.handed is None:
             st._ws = {}                 # the workspace no longer needs room for a per-call panel
+    elif CACHE_WEIGHT_PANEL == "auto" and st.folded is not None and st.folded.panel is None and M > PANEL_CACHE_MAX_ROWS:
+        st.panel_declined = True        # over the budget: asked once, not on every call
     ws = st.workspace(M, x2d.device)
     watch = ops.status_watch(x2d.device) if WATCH_STATUS else None
     if watch is not None:
@@ -363,11 +368,40 @@ NVFP4_WEIGHT_RECIPE = "rowscale"
 INT4_TENSOR_RATE_GEMM = True
 # The tensor-rate GEMM reads the weight as an fp16 panel.  False: the panel is rebuilt from the 4-bit codes in
 # scratch on every call (weights stay 4-bit in memory; a pre-pass of N x K work per M x N x K GEMM).  True: built once
-# per layer and kept (2 bytes per weight of device memory, no pre-pass).  "auto" (default): kept only by layers that are
+# per layer and kept (2 bytes per weight of device memory, no pre-pass).  "auto" (default): kept by layers that are
 # called with few rows (at most PANEL_CACHE_MAX_ROWS: a batch shard on one of several GPUs, a small batch), where the
-# pre-pass, whose cost does not shrink with the batch, is a fifth of the call; large batches keep 0.5 byte per weight.
+# pre-pass, whose cost does not shrink with the batch, is a fifth of the call; and by layers called with more rows for
+# as long as all 16-bit weight copies on the device (these panels and the dense weights of W4A16 layers) stay within
+# PANEL_CACHE_BUDGET_FRACTION of its memory (a sixteenth: 11 GB of a B200's 180 -- every PixArt / SANA layer, where the
+# pre-pass is 2-3 % of a batch-8 step; two thirds of a 12-billion-parameter FLUX, whose long GEMMs hardly notice it);
+# layers beyond the budget keep 0.5 byte per weight and rebuild per call.
 CACHE_WEIGHT_PANEL = "auto"
 PANEL_CACHE_MAX_ROWS = 8192
+PANEL_CACHE_BUDGET_FRACTION = 1.0 / 16
+_PANEL_RESIDENT_BYTES: Dict[int, int] = {}
+
+
+def resident_weight_copy_bytes(device=None) -> int:
+    """Bytes of 16-bit weight copies (fp16 panels, dense W4A16 weights) currently kept on the device."""
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    return _PANEL_RESIDENT_BYTES.get(idx, 0)
+
+
+def _panel_budget_release(idx: int, nbytes: int):
+    _PANEL_RESIDENT_BYTES[idx] = max(0, _PANEL_RESIDENT_BYTES.get(idx, 0) - nbytes)
+
+
+def _panel_budget_take(owner, device, nbytes: int, always: bool) -> bool:
+    """Account nbytes of 16-bit weight copy to `owner` (released when it is collected); False when a large-batch layer
+    would exceed the device's budget."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    used = _PANEL_RESIDENT_BYTES.get(idx, 0)
+    if not always and used + nbytes > PANEL_CACHE_BUDGET_FRACTION * torch.cuda.get_device_properties(idx).total_memory:
+        return False
+    _PANEL_RESIDENT_BYTES[idx] = used + nbytes
+    weakref.finalize(owner, _panel_budget_release, idx, nbytes)
+    return True
 
 
 def _half_chunks(fmt: ops.ActFormat, lay: ops.ActLayout) -> bool:
@@ -491,11 +525,13 @@ class W4A16State:
     w: object                       # ops.PackedWeightInt4 or ops.PackedWeightNvfp4
     bias: Optional[torch.Tensor]
     dense: Optional[torch.Tensor] = None      # resident dequantised weight (bf16 [N, K]), see w4a16_forward
+    declined: bool = False                    # a large-batch call found the budget for resident 16-bit copies spent
 
 
 # Dequantised weights of W4A16 layers follow the policy of CACHE_WEIGHT_PANEL: resident (2 bytes per weight) for layers
-# called with at most PANEL_CACHE_MAX_ROWS rows, where the dequantisation is a visible share of the call; otherwise
-# rebuilt on every call in ONE scratch buffer per device and stream, shared by all layers (stream order keeps it safe).
+# called with at most PANEL_CACHE_MAX_ROWS rows, where the dequantisation is a visible share of the call, and for the
+# others while the device's budget lasts; otherwise rebuilt on every call in ONE scratch buffer per device and stream,
+# shared by all layers (stream order keeps it safe).
 _W4A16_SCRATCH: Dict[tuple, torch.Tensor] = {}
 
 
@@ -512,8 +548,11 @@ def w4a16_forward(s16: W4A16State, x2d: torch.Tensor) -> torch.Tensor:
     """bf16 activations x 4-bit weight: x2d bf16 [M, K] -> bf16 [M, N]."""
     M = x2d.shape[0]
     nvfp4 = isinstance(s16.w, ops.PackedWeightNvfp4)
-    resident = CACHE_WEIGHT_PANEL is True or (CACHE_WEIGHT_PANEL == "auto" and M <= PANEL_CACHE_MAX_ROWS)
-    if resident or s16.dense is not None:
+    resident = s16.dense is not None or CACHE_WEIGHT_PANEL is True
+    if not resident and CACHE_WEIGHT_PANEL == "auto" and not s16.declined:
+        resident = _panel_budget_take(s16, x2d.device, 2 * s16.w.N * s16.w.n_chunks * 64, M <= PANEL_CACHE_MAX_ROWS)
+        s16.declined = not resident and M > PANEL_CACHE_MAX_ROWS
+    if resident:
         if s16.dense is None:
             s16.dense = ops.dequant_weight_nvfp4(s16.w) if nvfp4 else ops.dequant_weight_int4(s16.w)
         return ops.gemm_bf16(x2d, s16.dense, s16.bias)

@@ -165,13 +165,14 @@ def test_host_streamed_step_returns_the_same_result():
 
 @pytest.mark.parametrize("quant,a_sym", [("int4", True), ("int4", False), ("int8", False)])
 @pytest.mark.parametrize("H,M", [(70, 300), (5, 300), (7, 9000)])
-def test_short_per_head_groups_share_operand_stages(quant, a_sym, H, M):
+def test_short_per_head_groups_share_operand_stages(quant, a_sym, H, M, monkeypatch):
     """Per-head groups of 28 channels (SANA: d = 32, 4 of them 16-bit) occupy 64-slot chunks that are half padding; the
     16-bit-conversion GEMM packs the first halves of two chunks into one operand stage.  Odd and even head counts,
     a small batch (resident weight panel) and a large one (panel rebuilt per call), all three activation formats."""
     from dirotq_b200 import _lib, backend, dit
     from dirotq_b200.synth import synth_activations
     import ctypes as C
+    monkeypatch.setattr(backend, "PANEL_CACHE_BUDGET_FRACTION", 0.0)      # large batches rebuild the panel per call
     ld = dit.LayerDef("attn1.to_out.0", H * 32, 256, kind="perhead", tail=4, heads=H, head_dim=32)
     w = dit.make_wrapped_linear(ld, quant, 900 + H, "cuda", a_sym=a_sym)
     holder = torch.nn.ModuleDict({"l": w})
@@ -184,3 +185,9 @@ def test_short_per_head_groups_share_operand_stages(quant, a_sym, H, M):
     if st.folded.panel is not None:
         assert st.folded.panel.shape == (256, (H + 1) // 2 * 64)
     assert torch.equal(w(x), y)                                 # second call: same result with the panel in place
+    if M > backend.PANEL_CACHE_MAX_ROWS:
+        # with room in the device's budget for 16-bit weight copies a large batch keeps its panel too: same bits
+        monkeypatch.setattr(backend, "PANEL_CACHE_BUDGET_FRACTION", 1.0 / 16)
+        st.panel_declined = False
+        assert torch.equal(w(x), y) and st.folded.panel is not None and st.folded.panel.shape == (256, (H + 1) // 2 * 64)
+        assert torch.equal(w(x), y)
