@@ -196,7 +196,18 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
   const int n_main = hc ? (a.n_chunks + 1) >> 1 : a.n_chunks;      // operand stages of codes
   const int n_tail = (a.kt + 63) >> 6;
   const int n_tiles_n = (int)((a.N + BN - 1) / BN);
-  const int total_tiles = n_tiles_n * (int)((a.M + 127) / 128);
+  const int n_tiles_m = (int)((a.M + 127) / 128);
+  const int total_tiles = n_tiles_n * n_tiles_m;
+  // Tile order: column tiles in groups of `a.raster` (n fastest inside a group, then m, then the next group), so the
+  // tiles in flight at one time share a bounded set of weight columns and activation rows in L2.
+  const int rast = a.raster > 0 && a.raster < n_tiles_n ? a.raster : n_tiles_n;
+  auto tile_mn = [&](int t, int& tm_, int& tn_) {
+    const int per_group = rast * n_tiles_m;
+    const int grp = t / per_group, r = t - grp * per_group;
+    const int width = min(rast, n_tiles_n - grp * rast);
+    tm_ = r / width;
+    tn_ = grp * rast + (r - tm_ * width);
+  };
   // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... with n fastest, so CTAs running at
   // the same time read the same activation rows through L2.  Rings and the accumulator counter run on
   // across tiles.  Operand stage q of the kernel-wide sequence (chunks and tail stages of all tiles)
@@ -209,7 +220,9 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       uint32_t issued = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / n_tiles_n) * 128;
+        int tm_, tn_;
+        tile_mn(t, tm_, tn_);
+        const int m0 = tm_ * 128;
         for (int c = 0; c < n_raw; c += GF_CPS) {
           if (!mbar_wait_hot(rawe_bar(r.s), r.ph ^ 1, abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sb = raw_base + r.s * Cfg::RAW_STAGE;
@@ -257,7 +270,9 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       int q = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int n0 = (t % n_tiles_n) * BN;
+        int tm_, tn_;
+        tile_mn(t, tm_, tn_);
+        const int n0 = tn_ * BN;
         for (int st = 0; st < n_main + n_tail; ++st, ++q) {
           const int es = q % GF_EXP_STAGES;
           if (!mbar_wait_hot(expe_bar(es), (uint32_t)(((q / GF_EXP_STAGES) & 1) ^ 1), abort_flag, a.status, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -497,7 +512,9 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
     int use = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int m0 = (t / n_tiles_n) * 128, n0 = (t % n_tiles_n) * BN;
+      int tm_, tn_;
+      tile_mn(t, tm_, tn_);
+      const int m0 = tm_ * 128, n0 = tn_ * BN;
       const int64_t row = (int64_t)m0 + trow;
       const float rs = (row < a.M) ? __ldg(a.rs + row) : 0.f;
       const int buf = use & 1;
@@ -906,7 +923,21 @@ static int pick_bn_f16(int64_t M, int64_t N) {
   return best;
 }
 
-int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
+// Column tiles per rasterisation group.  With n fastest over the whole width, the CTAs of one round read every weight
+// column tile of the layer; once the fp16 panel no longer sits in L2 next to the activation and output streams (3072 ->
+// 12288: 75 MB) those reads go to HBM again on every round.  Groups bound the weight tiles in flight to about 24 MB
+// (3072 -> 12288 at 18432 rows: 1325 -> 1169 us, 3072 -> 9216: 927 -> 880, 12288 -> 3072: 1172 -> 1126); layers whose
+// panel fits (under 32 MB) keep the plain order, which was 1-2 % faster for them.  DIROTQ_GF_RASTER overrides.
+static int pick_raster_f16(int BN, int64_t N, int64_t k_total) {
+  if (const char* e = getenv("DIROTQ_GF_RASTER")) return atoi(e);
+  const int64_t tile_bytes = (int64_t)BN * k_total * 2, panel_bytes = N * k_total * 2;
+  if (panel_bytes <= (32ll << 20) || tile_bytes <= 0) return 0;
+  const int64_t g = ((24ll << 20) + tile_bytes / 2) / tile_bytes;
+  return (int)(g < 4 ? 4 : g > 16 ? 16 : g);
+}
+
+int launch_gemm_int_f16(const GemmIntF16Args& a_in, cudaStream_t st) {
+  GemmIntF16Args a = a_in;
   if (a.M <= 0 || a.N <= 0) return DIROTQ_OK;
   if (a.a_mode != DIROTQ_INT4_SYM && a.a_mode != DIROTQ_INT4_ASYM && a.a_mode != DIROTQ_INT8_ASYM) return DIROTQ_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
@@ -931,6 +962,7 @@ int launch_gemm_int_f16(const GemmIntF16Args& a, cudaStream_t st) {
                            (uint64_t)a.x_row_bytes, 32 * GF_CPS, 128, 32 * GF_CPS);
   if (rc) return rc;
   const uint64_t n_stage = a.half_chunks ? (uint64_t)((a.n_chunks + 1) / 2) : (uint64_t)a.n_chunks;
+  if (a.raster == 0) a.raster = pick_raster_f16(BN, a.N, (int64_t)n_stage * 64 + ((a.kt + 63) / 64) * 64);
   rc = make_tmap_2d(&tm.wp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.w_panel, n_stage * 64, (uint64_t)a.N, n_stage * 128, BN);
   if (rc) return rc;
   // without an output tensor (quantise-out only) the map is never used: any valid address will do

@@ -153,6 +153,7 @@ struct GemmIntF16Args {
   int half_chunks = 0;         // per-head groups of at most 32 channels: two chunks' first halves per operand stage (the
                                // weight panel is laid out to match: [N, ceil(n_chunks / 2) * 64])
   int force_bn;                // 0 = pick the column-tile width from N
+  int raster = 0;              // column tiles per rasterisation group (0 = all: n fastest over the whole width)
   int act;                     // epilogue activation: 0 none, 1 GELU (tanh form) on the bf16-rounded output
   // Optional: the epilogue ALSO quantises its (activated, bf16-rounded) output rows for a following un-rotated INT4
   // layer of width N with groups of 64 (and, optionally, its last columns kept in 16 bits) -- codes / scales / zero points in that layer's activation
