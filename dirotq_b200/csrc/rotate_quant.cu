@@ -42,7 +42,10 @@ template <bool PAIR> struct RqStage {
 #define RQ_WPQ_NVFP4 4
 #endif
 template <int EPI, bool PAIR = false> struct RqCfg {
-  static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : 2;
+#ifndef RQ_WPQ_PERHEAD
+#define RQ_WPQ_PERHEAD 4
+#endif
+  static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : (EPI == 3 /* EPI_INT_PERHEAD */) ? RQ_WPQ_PERHEAD : 2;
   static constexpr int EPI_WARPS = 4 * WPQ;
   static constexpr int THREADS = (2 + EPI_WARPS) * 32;
   // plain-GEMM epilogue (EPI_ROT_ONLY = 0): a 32 x 32 bf16 staging patch per epilogue warp for its TMA stores
@@ -302,6 +305,19 @@ __device__ __forceinline__ void ld32_by8(uint32_t taddr, uint32_t* r) {
   tmem_wait_ld();
 }
 
+// Planar-32 codes (byte j = slots j and 16 + j): the nibbles of the first nv slots.
+__device__ __forceinline__ uint4 planar32_valid_mask(int nv) {
+  const int nlo = min(nv, 16), nhi = max(nv - 16, 0);
+  uint32_t w[4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    const int lc = min(max(nlo - 4 * wd, 0), 4), hc = min(max(nhi - 4 * wd, 0), 4);
+    const uint32_t lm = lc == 4 ? 0xFFFFFFFFu : ((1u << (8 * lc)) - 1u), hm = hc == 4 ? 0xFFFFFFFFu : ((1u << (8 * hc)) - 1u);
+    w[wd] = (0x0F0F0F0Fu & lm) | (0xF0F0F0F0u & hm);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Per-head layout: head h = tile columns [hh*d, hh*d + d): first d_q quantised as ONE group,
 // last hlen passthrough.  Two passes over TMEM (extrema, then codes) keep registers small.
 template <int MODE>
@@ -330,6 +346,58 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
     }
     if (!a.codes) continue;
     float mx = -INFINITY, mn = INFINITY;
+    GroupParams p;
+    if constexpr (MODE != MODE_INT8_ASYM) {
+      // 4-bit modes, on packed bf16 pairs: a block of 32 columns becomes 16 words (one conversion per pair = the bf16
+      // rounding of x_rot), the extrema are packed min / max, the codes come out in the planar layout directly
+      // (quant_math.cuh).  A ragged last block takes part with its invalid slots replaced (extrema) or cleared (codes).
+      // A head of one block (SANA: 28 of 32 columns) keeps its words between the two passes.
+      uint32_t pw[16];
+      for (int b = 0; b < nblk; ++b) {
+        uint32_t r[32];
+        ld32_by8(taddr + cb + 32 * b, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pw[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        const int nv = min(32, d_q - 32 * b);
+        if (nv == 32) {
+          minmax_bf16x16(pw, mx, mn);
+          minmax_bf16x16(pw + 8, mx, mn);
+        } else {
+          const uint32_t fill = (pw[0] << 16) | (pw[0] & 0xFFFFu);      // slot 0 of the block (always valid) twice
+          uint32_t pm[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t vm = (2 * i + 1 < nv) ? 0xFFFFFFFFu : ((2 * i < nv) ? 0x0000FFFFu : 0u);
+            pm[i] = (pw[i] & vm) | (fill & ~vm);
+          }
+          minmax_bf16x16(pm, mx, mn);
+          minmax_bf16x16(pm + 8, mx, mn);
+        }
+      }
+      if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
+      else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+      const float rcp = __frcp_rn(p.scale);
+      for (int b = 0; b < 2 * g.cpg; ++b) {
+        uint4 c4 = make_uint4(0u, 0u, 0u, 0u);
+        if (b < nblk) {
+          if (nblk > 1) {
+            uint32_t r[32];
+            ld32_by8(taddr + cb + 32 * b, r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pw[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+          }
+          if constexpr (MODE == MODE_INT4_SYM) c4 = int_sym_planar32_packed(pw, rcp, g.clip < 1.f);
+          else c4 = int_asym_planar32_packed(pw, rcp, p.zero);
+          const int nv = d_q - 32 * b;
+          if (nv < 32) {
+            const uint4 m4 = planar32_valid_mask(nv);
+            c4 = make_uint4(c4.x & m4.x, c4.y & m4.y, c4.z & m4.z, c4.w & m4.w);
+          }
+        }
+        if (row_ok)
+          *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + ((int64_t)h * g.cpg * 64 + 32 * b) / 2) = c4;
+      }
+    } else {
     for (int b = 0; b < nblk; ++b) {
       uint32_t r[32];
       ld32_by8(taddr + cb + 32 * b, r);
@@ -341,14 +409,11 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
           mn = fminf(mn, f);
         }
     }
-    GroupParams p;
-    if constexpr (MODE == MODE_INT4_SYM) p = int_sym_params<true>(mx, mn, g.clip, maxq);
-    else p = int_asym_params<true>(mx, mn, g.clip, maxq);
+    p = int_asym_params<true>(mx, mn, g.clip, maxq);
     const float rcp = __frcp_rn(p.scale);
     for (int b = 0; b < 2 * g.cpg; ++b) {
-      // eight codes per word: nibbles for the 4-bit modes (n8), bytes for the 8-bit mode (b8); whole octets inside the
-      // group take the division-free exact forms (guarded reciprocal, quant_math.cuh), the ragged end the plain ones
-      uint32_t n8[4] = {0u, 0u, 0u, 0u};
+      // 8-bit mode: eight codes per pair of words by the division-free exact form (guarded reciprocal, quant_math.cuh);
+      // an octet that straddles the end of the group is computed whole and its invalid bytes cleared
       uint2 b8[4] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
       if (b < nblk) {
         uint32_t r[32];
@@ -358,45 +423,23 @@ __device__ __forceinline__ void epi_int_perhead(const RotArgs& a, uint32_t taddr
         for (int j = 0; j < 32; ++j) f[j] = rnd<true>(__uint_as_float(r[j]));
 #pragma unroll
         for (int o = 0; o < 4; ++o) {
-          const int e0 = 32 * b + 8 * o;
-          if (e0 + 8 <= d_q) {
-            if constexpr (MODE == MODE_INT4_SYM) {
-              n8[o] = int_sym_nib8_fast(f + 8 * o, p.scale, rcp);
-            } else {
-              b8[o] = int_asym_byte8_fast(f + 8 * o, p.scale, rcp, p.zero, maxq);
-              if constexpr (MODE == MODE_INT4_ASYM) n8[o] = squeeze_nibbles(b8[o].x) | (squeeze_nibbles(b8[o].y) << 16);
+          const int nvo = d_q - (32 * b + 8 * o);                // valid values of this octet
+          if (nvo > 0) {
+            b8[o] = int_asym_byte8_fast(f + 8 * o, p.scale, rcp, p.zero, maxq);
+            if (nvo < 8) {
+              const uint32_t lo_m = nvo >= 4 ? 0xFFFFFFFFu : ((1u << (8 * nvo)) - 1u);
+              const uint32_t hi_m = nvo > 4 ? ((1u << (8 * (nvo - 4))) - 1u) : 0u;
+              b8[o] = make_uint2(b8[o].x & lo_m, b8[o].y & hi_m);
             }
-          } else if (e0 < d_q) {
-            uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              int c = 0;
-              if (e0 + j < d_q) {
-                if constexpr (MODE == MODE_INT4_SYM) c = int_sym_code<true>(f[8 * o + j], p.scale, maxq);
-                else c = int_asym_code<true>(f[8 * o + j], p.scale, p.zero, maxq);
-              }
-              if constexpr (MODE == MODE_INT8_ASYM) {
-                if (j < 4) lo |= ((uint32_t)c & 0xFFu) << (8 * j);
-                else hi |= ((uint32_t)c & 0xFFu) << (8 * (j - 4));
-              } else {
-                lo |= ((uint32_t)c & 0xFu) << (4 * j);
-              }
-            }
-            if constexpr (MODE == MODE_INT8_ASYM) b8[o] = make_uint2(lo, hi);
-            else n8[o] = lo;
           }
         }
       }
       if (row_ok) {
-        const int64_t slot = (int64_t)h * g.cpg * 64 + 32 * b;
-        if constexpr (MODE == MODE_INT8_ASYM) {
-          uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot);
-          dst[0] = make_uint4(b8[0].x, b8[0].y, b8[1].x, b8[1].y);
-          dst[1] = make_uint4(b8[2].x, b8[2].y, b8[3].x, b8[3].y);
-        } else {
-          *reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + slot / 2) = planar32_from_nib8(n8[0], n8[1], n8[2], n8[3]);
-        }
+        uint4* dst = reinterpret_cast<uint4*>(a.codes + row * g.code_row_bytes + (int64_t)h * g.cpg * 64 + 32 * b);
+        dst[0] = make_uint4(b8[0].x, b8[0].y, b8[1].x, b8[1].y);
+        dst[1] = make_uint4(b8[2].x, b8[2].y, b8[3].x, b8[3].y);
       }
+    }
     }
     if (row_ok) {
       for (int c = 0; c < g.cpg; ++c) {
@@ -707,7 +750,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0, half, turn);
       else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
       else if constexpr (EPI == EPI_NVFP4_PERHEAD) epi_nvfp4_perhead(a, taddr, row, n0, half, turn);
-      else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn);
+      else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
