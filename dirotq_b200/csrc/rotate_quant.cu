@@ -45,7 +45,7 @@ template <int EPI, bool PAIR = false> struct RqCfg {
 #ifndef RQ_WPQ_PERHEAD
 #define RQ_WPQ_PERHEAD 4
 #endif
-  static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : (EPI == 3 /* EPI_INT_PERHEAD */) ? RQ_WPQ_PERHEAD : 2;
+  static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : (EPI == 3 || EPI == 4 /* per-head */) ? RQ_WPQ_PERHEAD : 2;
   static constexpr int EPI_WARPS = 4 * WPQ;
   static constexpr int THREADS = (2 + EPI_WARPS) * 32;
   // plain-GEMM epilogue (EPI_ROT_ONLY = 0): a 32 x 32 bf16 staging patch per epilogue warp for its TMA stores
@@ -749,7 +749,7 @@ rotate_quant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         epi_rot_only(a, &tm_y, smem_u32(stg_area) + (warp - 2) * 2048, taddr, mb * 128 + q * 32, lane, n0, half, turn);
       else if constexpr (EPI == EPI_INT_HIDDEN) epi_int_hidden<MODE>(a, taddr, row, n0, half, turn);
       else if constexpr (EPI == EPI_NVFP4_HIDDEN) epi_nvfp4_hidden<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
-      else if constexpr (EPI == EPI_NVFP4_PERHEAD) epi_nvfp4_perhead(a, taddr, row, n0, half, turn);
+      else if constexpr (EPI == EPI_NVFP4_PERHEAD) epi_nvfp4_perhead(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
       else epi_int_perhead<MODE>(a, taddr, row, n0, half, turn, RqCfg<EPI>::WPQ);
       tc_fence_before();
       __syncwarp();
