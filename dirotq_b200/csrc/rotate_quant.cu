@@ -36,15 +36,16 @@ template <bool PAIR> struct RqStage {
   static constexpr int B_BYTES = (PAIR ? 128 : 256) * 128;
   static constexpr int STAGE_BYTES = RQ_A_BYTES + B_BYTES;
 };
-// Epilogue warps per TMEM lane quarter: they take the 64-column chunks of their rows in turns.  The NVFP4
-// epilogue is the longest (seven threshold compares per value) and latency-bound, so it gets more warps.
+// Epilogue warps per TMEM lane quarter: they take the 64-column chunks (per-head layouts: the heads) of their rows in
+// turns.  The NVFP4 epilogue is the longest (seven threshold compares per value) and latency-bound, and the per-head
+// epilogues wait on several tensor-memory reads per head, so those get more warps.
 #ifndef RQ_WPQ_NVFP4
 #define RQ_WPQ_NVFP4 4
 #endif
-template <int EPI, bool PAIR = false> struct RqCfg {
 #ifndef RQ_WPQ_PERHEAD
 #define RQ_WPQ_PERHEAD 4
 #endif
+template <int EPI, bool PAIR = false> struct RqCfg {
   static constexpr int WPQ = (EPI == 2 /* EPI_NVFP4_HIDDEN */) ? RQ_WPQ_NVFP4 : (EPI == 3 || EPI == 4 /* per-head */) ? RQ_WPQ_PERHEAD : 2;
   static constexpr int EPI_WARPS = 4 * WPQ;
   static constexpr int THREADS = (2 + EPI_WARPS) * 32;
