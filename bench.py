@@ -94,7 +94,8 @@ def parse():
     ap.add_argument("--profile-case", default="", nargs="?", const="layers",
                     help="run a small case for ncu instead of the benchmark: 'layers' = one 1152->1152 k=64 layer at "
                          "M=16384, INT4 then NVFP4, three forwards each; 'flux_nvfp4' = one NVFP4 3072->12288 k=384 "
-                         "layer at M=4096; 'quantize' = the quantise-only kernel at M=4096, D=12288; 'glue' = the three "
+                         "layer at M=4096; 'flux_int4' = one INT4 3072->12288 k=384 layer at M=18432 (its fp16 weight panel, 75 MB, "
+                         "does not stay in L2); 'quantize' = the quantise-only kernel at M=4096, D=12288; 'glue' = the three "
                          "block-glue kernels on FLUX-shaped tensors (4 x 4096 x 3072)")
     return ap.parse_args()
 
@@ -896,6 +897,13 @@ def profile_case(which):
             M = 4096
             x = synth_activations(M, 3072, torch.Generator().manual_seed(0)).cuda()
             w = dit.make_wrapped_linear(dit.LayerDef("probe", 3072, 12288, tail=384), "nvfp4", 5, "cuda")
+            st = backend.prepare_layer(w, "cuda", w._b200_explicit)
+            for _ in range(3):
+                backend.linear_forward(st, x)
+        elif which == "flux_int4":
+            M = 18432                                       # FLUX single-stream rows at batch 4: the up-projection
+            x = synth_activations(M, 3072, torch.Generator().manual_seed(0)).cuda()
+            w = dit.make_wrapped_linear(dit.LayerDef("probe", 3072, 12288, tail=384), "int4", 5, "cuda")
             st = backend.prepare_layer(w, "cuda", w._b200_explicit)
             for _ in range(3):
                 backend.linear_forward(st, x)
