@@ -304,3 +304,57 @@ def test_sibling_gemm_on_dense_nvfp4_weights_with_per_channel_scales():
         assert torch.equal(w(x), w2(x))
     assert ws[0]._b200_state.shared.hits == 2
     ops.check_status()
+
+
+def test_fused_layers_over_changing_row_counts():
+    """Workspaces, resident weight panels, shared activations and hand-offs are reused from call to call: a fused q / k / v
+    group and a fused feed-forward pair called with a sequence of different row counts return, every time, exactly what
+    freshly built, unfused layers return for that input."""
+    import contextlib
+    import io
+    import random
+    from dirotq_b200 import backend, dit, ops
+    from dirotq_b200.synth import synth_activations
+    rnd = random.Random(5)
+
+    def quiet(fn, *a, **k):
+        with contextlib.redirect_stdout(io.StringIO()):
+            return fn(*a, **k)
+
+    for case in range(6):
+        quant, a_sym = rnd.choice(["int4", "nvfp4", "int8"]), rnd.random() < 0.5
+        dim, inner, k = rnd.choice([(384, 1536, 64), (1152, 4608, 64), (256, 512, 0)])
+
+        def build():
+            attn = nn.Module()
+            ws = [dit.make_wrapped_linear(dit.LayerDef(n, dim, dim, tail=k), quant, 40 + case * 9 + i, "cuda", a_sym=a_sym)
+                  for i, n in enumerate(("to_q", "to_k", "to_v"))]
+            for n, w in zip(("to_q", "to_k", "to_v"), ws):
+                w.rotation = ws[0].rotation
+                attn.add_module(n, w)
+            up = dit.make_wrapped_linear(dit.LayerDef("ff.net.0.proj", dim, inner, tail=k), quant, 44 + case * 9, "cuda", a_sym=a_sym)
+            down = dit.make_wrapped_linear(dit.LayerDef("ff.net.2", inner, dim, kind="norot", tail=0, source="ff"), quant,
+                                           45 + case * 9, "cuda", a_sym=a_sym)
+            ff = nn.Module()
+            ff.net = nn.ModuleList([dit.GeluProj(up), nn.Identity(), down])
+            root = nn.Module()
+            root.add_module("attn1", attn)
+            root.add_module("ff", ff)
+            quiet(backend.preconvert_rotations_to_device, root, "cuda")
+            quiet(backend.fuse_gelu_modules, root)
+            return root, ws, ff
+
+        def run(ws_, ff_, x):
+            return [w(x).clone() for w in ws_] + [ff_.net[2](ff_.net[0](x)).clone()]
+
+        root, ws, ff = build()
+        assert quiet(backend.fuse_sibling_gemms, root) == 1
+        quiet(backend.fuse_ffn_quantise, root, keep_hidden=False)
+        for j in range(5):
+            M = rnd.choice([1, 7, 129, 500, 2048, 4100, 9000])
+            x = synth_activations(M, dim, torch.Generator().manual_seed(case * 100 + j)).reshape(1, M, dim).cuda()
+            got = run(ws, ff, x)
+            _, ws_f, ff_f = build()
+            want = run(ws_f, ff_f, x)
+            ops.check_status()
+            assert all(torch.equal(a, b) for a, b in zip(got, want)), (case, quant, a_sym, dim, M)
