@@ -95,7 +95,8 @@ def parse():
                     help="run a small case for ncu instead of the benchmark: 'layers' = one 1152->1152 k=64 layer at "
                          "M=16384, INT4 then NVFP4, three forwards each; 'flux_nvfp4' = one NVFP4 3072->12288 k=384 "
                          "layer at M=4096; 'flux_int4' = one INT4 3072->12288 k=384 layer at M=18432 (its fp16 weight panel, 75 MB, "
-                         "does not stay in L2); 'quantize' = the quantise-only kernel at M=4096, D=12288; 'glue' = the three "
+                         "does not stay in L2); 'perhead' = one INT4 per-head layer, 70 heads x 32 with 4 high channels each, at "
+                         "M=16384; 'quantize' = the quantise-only kernel at M=4096, D=12288; 'glue' = the three "
                          "block-glue kernels on FLUX-shaped tensors (4 x 4096 x 3072)")
     return ap.parse_args()
 
@@ -904,6 +905,14 @@ def profile_case(which):
             M = 18432                                       # FLUX single-stream rows at batch 4: the up-projection
             x = synth_activations(M, 3072, torch.Generator().manual_seed(0)).cuda()
             w = dit.make_wrapped_linear(dit.LayerDef("probe", 3072, 12288, tail=384), "int4", 5, "cuda")
+            st = backend.prepare_layer(w, "cuda", w._b200_explicit)
+            for _ in range(3):
+                backend.linear_forward(st, x)
+        elif which == "perhead":
+            M = 16384                                       # SANA out-projection: 70 heads x 32, 4 channels per head 16-bit
+            x = synth_activations(M, 2240, torch.Generator().manual_seed(0)).cuda()
+            w = dit.make_wrapped_linear(dit.LayerDef("probe", 2240, 2240, kind="perhead", tail=4, heads=70, head_dim=32),
+                                        "int4", 5, "cuda")
             st = backend.prepare_layer(w, "cuda", w._b200_explicit)
             for _ in range(3):
                 backend.linear_forward(st, x)
