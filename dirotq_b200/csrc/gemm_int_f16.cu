@@ -904,12 +904,13 @@ static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st)
   return launch_pdl(k, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tm, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
-// Column-tile width.  The persistent grid runs ceil(tiles / SMs) rounds, each as long as its widest tile, so the choice
-// minimises rounds x (tile width + a fixed per-tile cost of about 48 columns' worth of time: pipeline fill, epilogue
-// hand-over) -- padded columns and a nearly empty last round both count.  Large M: 192 (fewer conversions of the
-// activation tile per output column); a 4096-row shard of a 1152-wide layer: 128 (288 tiles fill two rounds of 148
-// SMs, where 192 tiles of width 192 leave the second round 30 % full).  256 does not fit: two accumulators of 256
-// columns would leave no tensor memory for the activation operand.
+// Column-tile width.  The persistent grid runs ceil(tiles / SMs) rounds; a round costs a part proportional to the tile
+// width (the UMMAs) and a part that is the same for every width (the issuer's per-stage barrier protocol): 6.84 us for
+// 128 columns and 7.81 us for 192 at K = 1152, i.e. the fixed part is worth about 320 columns.  The choice minimises
+// rounds x (width + 320) -- padded columns and a nearly empty last round both count: 192 nearly everywhere (1152 x 1152 at
+// 16384 rows: 47.9 us against 59.2 with 128; 1152 -> 4608 at 4096 rows: 49.6 against 59.3), 128 where 192 would leave
+// the last of two rounds a third full (1152 x 1152 at 4096 rows: 19.7 us against 21.6).  256 does not fit: two
+// accumulators of 256 columns would leave no tensor memory for the activation operand.
 static int pick_bn_f16(int64_t M, int64_t N) {
   const int cand[2] = {192, 128};
   const int64_t m_tiles = (M + 127) / 128, sms = num_sms();
@@ -917,7 +918,7 @@ static int pick_bn_f16(int64_t M, int64_t N) {
   int64_t best_cost = -1;
   for (int i = 0; i < 2; ++i) {
     const int64_t tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
-    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 48);
+    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 320);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
   }
   return best;

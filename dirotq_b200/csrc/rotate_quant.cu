@@ -850,9 +850,11 @@ static int launch_rq(const CUtensorMap& tx, const CUtensorMap& tu, const CUtenso
 }
 
 // Picks the N tile.  Per-head layouts: a whole number of heads (and a multiple of 16 for the UMMA shape).  Hidden
-// layouts: a multiple of 64; the persistent grid runs ceil(tiles / SMs) rounds, each as long as its tile is wide, so
-// the choice minimises rounds x (width + a fixed per-tile cost of about 48 columns' worth of time) -- padding of D and
-// a nearly empty last round both count (a 4096-row shard of a 1152-wide layer takes 128, a 32768-row batch 192).
+// layouts: a multiple of 64; the persistent grid runs ceil(tiles / SMs) rounds, and a round costs a part that grows with
+// the tile width (the UMMAs) plus a part that does not (the per-stage barrier protocol of the issuer, the same for every
+// width).  Measured at D = 1152, 32768 rows: 6.03 / 6.68 / 7.59 us per round for 128 / 192 / 256 columns, i.e. the fixed
+// part is worth about 370 columns; the choice minimises rounds x (width + 370) -- padding of D and a nearly empty last
+// round both count (32768 rows of a 1152-wide layer take 256: 68 us against 74 with 192; a 4096-row shard takes 128).
 int pick_bn(const ActGeom& g, int64_t M) {
   if (g.H > 0) {
     int best = 0;
@@ -866,7 +868,7 @@ int pick_bn(const ActGeom& g, int64_t M) {
   int64_t best_cost = -1;
   for (int i = 0; i < 3; ++i) {
     const int64_t tiles = m_tiles * ceil_div(g.D, cand[i]);
-    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 48);
+    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 370);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
   }
   return best;
