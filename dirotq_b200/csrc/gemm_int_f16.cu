@@ -79,16 +79,21 @@ template <int BN, bool A8 = false> struct GfCfg {
   static constexpr int RAW_A = 128 * 32 * GF_CPS * (A8 ? 2 : 1);   // 8-bit activation codes: two 128-byte boxes per row
   static constexpr int OFF_C = RAW_A;                      // [chunk][128] 8-byte records
   static constexpr int RAW_STAGE = OFF_C + GF_CPS * 128 * 8;
-  // Operand stages in flight: every tensor-memory column the two accumulators leave free holds activations
-  // (32 columns per 64-wide chunk).
-  static constexpr int EXP_TMEM = (512 - 2 * BN) / 32;
-  static constexpr int EXP_STAGES = EXP_TMEM < GF_EXP_MAX ? EXP_TMEM : GF_EXP_MAX;
+  // Accumulators: two (the next tile's UMMAs overlap the epilogue) up to 192 columns; a 256-wide tile has one, and its
+  // UMMAs wait until the epilogue has read the previous tile out of tensor memory.
+  static constexpr int NACC = BN > 192 ? 1 : 2;
+  // Operand stages in flight: every tensor-memory column the accumulators leave free holds activations
+  // (32 columns per 64-wide chunk), as far as shared memory holds the weight tiles beside them.
   static constexpr int RAW_STAGES = GF_RAW_DEF;
   static constexpr int STG_BYTES = GF_EPI_WARPS * 2048;     // per epilogue warp: 32 rows x 32 bf16 output staging
+  static constexpr int EXP_TMEM = (512 - NACC * BN) / 32;
+  static constexpr int EXP_SMEM = (232448 - 1024 - 256 - STG_BYTES - RAW_STAGES * RAW_STAGE) / EXP_STAGE;
+  static constexpr int EXP_CAP = EXP_TMEM < GF_EXP_MAX ? EXP_TMEM : GF_EXP_MAX;
+  static constexpr int EXP_STAGES = EXP_CAP < EXP_SMEM ? EXP_CAP : EXP_SMEM;
   static constexpr int SMEM_BYTES = EXP_STAGES * EXP_STAGE + RAW_STAGES * RAW_STAGE + STG_BYTES + 1024 + 256;
-  static constexpr int TMEM_A0 = 2 * BN;                    // first column of the activation operand slots
-  static constexpr int TMEM_COLS = 512;                     // 2 accumulators + EXP_STAGES x 32 columns of A
-  static_assert(2 * BN + EXP_STAGES * 32 <= 512, "tensor memory");
+  static constexpr int TMEM_A0 = NACC * BN;                 // first column of the activation operand slots
+  static constexpr int TMEM_COLS = 512;                     // accumulators + EXP_STAGES x 32 columns of A
+  static_assert(NACC * BN + EXP_STAGES * 32 <= 512 && EXP_STAGES >= 2, "tensor memory");
   static_assert(SMEM_BYTES <= 232448, "shared memory");
   static_assert(RAW_A >= 128 * 128 && GF_CPS == 4, "a raw stage must hold one 128 x 64 bf16 tail tile of the activations");
 };
@@ -454,8 +459,9 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       constexpr uint32_t kDescStep = Cfg::EXP_STAGE >> 4;
       const uint32_t a_tmem0 = tmem_base + Cfg::TMEM_A0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int buf = use & 1;
-        if (!mbar_wait_hot(acce_bar(buf), ((use >> 1) & 1) ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
+        const int buf = Cfg::NACC == 2 ? (use & 1) : 0;
+        const uint32_t acc_ph = (uint32_t)(Cfg::NACC == 2 ? (use >> 1) & 1 : use & 1);
+        if (!mbar_wait_hot(acce_bar(buf), acc_ph ^ 1, abort_flag, a.status, ERR_WAIT_ACC_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d = tmem_base + buf * BN;
         // A UMMA occupies the issuing thread until the tensor pipe has taken it, so whatever else this thread
@@ -517,8 +523,8 @@ gemm_int_f16_kernel(const __grid_constant__ GfMaps tm, const GemmIntF16Args a) {
       const int m0 = tm_ * 128, n0 = tn_ * BN;
       const int64_t row = (int64_t)m0 + trow;
       const float rs = (row < a.M) ? __ldg(a.rs + row) : 0.f;
-      const int buf = use & 1;
-      if (!mbar_wait(accf_bar(buf), (use >> 1) & 1, abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
+      const int buf = Cfg::NACC == 2 ? (use & 1) : 0;
+      if (!mbar_wait(accf_bar(buf), (uint32_t)(Cfg::NACC == 2 ? (use >> 1) & 1 : use & 1), abort_flag, a.status, ERR_WAIT_ACC_FULL)) { ok = false; break; }
       __syncwarp();
       tc_fence_after();
       ++use;
@@ -904,21 +910,25 @@ static int launch_gf(const GfMaps& tm, const GemmIntF16Args& a, cudaStream_t st)
   return launch_pdl(k, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tm, a) == cudaSuccess ? DIROTQ_OK : DIROTQ_E_CUDA;
 }
 
-// Column-tile width.  The persistent grid runs ceil(tiles / SMs) rounds; a round costs a part proportional to the tile
-// width (the UMMAs) and a part that is the same for every width (the issuer's per-stage barrier protocol): 6.84 us for
-// 128 columns and 7.81 us for 192 at K = 1152, i.e. the fixed part is worth about 320 columns.  The choice minimises
-// rounds x (width + 320) -- padded columns and a nearly empty last round both count: 192 nearly everywhere (1152 x 1152 at
-// 16384 rows: 47.9 us against 59.2 with 128; 1152 -> 4608 at 4096 rows: 49.6 against 59.3), 128 where 192 would leave
-// the last of two rounds a third full (1152 x 1152 at 4096 rows: 19.7 us against 21.6).  256 does not fit: two
-// accumulators of 256 columns would leave no tensor memory for the activation operand.
-static int pick_bn_f16(int64_t M, int64_t N) {
-  const int cand[2] = {192, 128};
+// Column-tile width.  The persistent grid runs ceil(tiles / SMs) rounds; a round costs, per 64-wide K stage, a part
+// proportional to the tile width (the UMMAs) and a part that is the same for every width (the issuer's per-stage barrier
+// protocol): 6.84 us for 128 columns and 7.81 us for 192 at K = 1152, i.e. the fixed part is worth about 320 columns.  A
+// 256-wide tile has a single accumulator (tensor memory: 256 + 8 x 32 activation columns), so the part of its epilogue
+// that reads the accumulator is not hidden behind the next tile's UMMAs: about 2300 column-stages per round more.  The
+// choice minimises rounds x ((width + 320) x stages [+ 2300]) -- padded columns and a nearly empty last round both count:
+// 256 for long K and widths that divide (3072 -> 12288 at 18432 rows: 1050 us against 1151 with 192; 12288 -> 3072: 968
+// against 1112; 2240 x 2240: 143 against 152), 192 for K = 1152 (1152 x 1152 at 16384 rows: 48 us against 59 with 128 or
+// 256), 128 where 192 would leave the last of two rounds a third full (1152 x 1152 at 4096 rows: 19.7 us against 21.6).
+// DIROTQ_GF_BN overrides.
+static int pick_bn_f16(int64_t M, int64_t N, int64_t stages) {
+  if (const char* e = getenv("DIROTQ_GF_BN")) return atoi(e);
+  const int cand[3] = {256, 192, 128};
   const int64_t m_tiles = (M + 127) / 128, sms = num_sms();
   int best = 128;
   int64_t best_cost = -1;
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < 3; ++i) {
     const int64_t tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
-    const int64_t cost = ((tiles + sms - 1) / sms) * (cand[i] + 320);
+    const int64_t cost = ((tiles + sms - 1) / sms) * ((cand[i] + 320) * stages + (cand[i] > 192 ? 2300 : 0));
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
   }
   return best;
@@ -944,7 +954,8 @@ int launch_gemm_int_f16(const GemmIntF16Args& a_in, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.cs) & 15) || (a.N & 7) ||
       (reinterpret_cast<uintptr_t>(a.a_const) & 15) || (reinterpret_cast<uintptr_t>(a.w_panel) & 15) || !a.w_panel)
     return DIROTQ_E_ALIGN;
-  int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.M, a.N);
+  const int64_t k_stages = (a.half_chunks ? (a.n_chunks + 1) / 2 : a.n_chunks) + (a.kt + 63) / 64;
+  int BN = a.force_bn ? a.force_bn : pick_bn_f16(a.M, a.N, k_stages);
   if (a.q_codes) {
     if (a.N % 64 || a.q_len % 64 || a.q_len <= 0 || a.q_len > a.N || a.q_row_bytes < a.q_len / 2 || (a.q_row_bytes & 15) ||
         (a.q_len < a.N && (!a.q_tail || a.q_tail_pitch < a.N - a.q_len || (a.q_tail_pitch & 7) ||
@@ -981,6 +992,9 @@ int launch_gemm_int_f16(const GemmIntF16Args& a_in, cudaStream_t st) {
   }
   const int amode = a.a_mode == DIROTQ_INT4_SYM ? 0 : a.a_mode == DIROTQ_INT4_ASYM ? 1 : 2;
   switch (BN * 4 + amode) {
+    case 256 * 4 + 0: return launch_gf<256, 0>(tm, a, st);
+    case 256 * 4 + 1: return launch_gf<256, 1>(tm, a, st);
+    case 256 * 4 + 2: return launch_gf<256, 2>(tm, a, st);
     case 192 * 4 + 0: return launch_gf<192, 0>(tm, a, st);
     case 192 * 4 + 1: return launch_gf<192, 1>(tm, a, st);
     case 192 * 4 + 2: return launch_gf<192, 2>(tm, a, st);
